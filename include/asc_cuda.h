@@ -1,0 +1,159 @@
+/*
+ * libasc_cuda — C ABI of the CUDA (sm_100a / B200) platform behind PyAsc's asc2 surface.
+ *
+ * This is the boundary the Python runtime binding (asc.lib.runtime) loads with ctypes,
+ * exactly as the reference loads its rt_wrapper shared object
+ * (python/asc/lib/runtime/state.py:25-75; wrappers in python/asc/lib/runtime/rt_wrapper.cpp:23-244).
+ *
+ * Conventions (same as the reference wrappers):
+ *   - extern "C", plain pointers and sizes, no C++/torch types;
+ *   - every function returns an integer status, 0 == OK; the Python side turns any other
+ *     value into RuntimeError("Function <name> returned <code>") (state.py:64-66);
+ *   - the caller owns every buffer; the library keeps no reference after return;
+ *   - kernel entry points are asynchronous on `stream` (a cudaStream_t passed as void*,
+ *     NULL == the legacy default stream) and touch device memory only;
+ *   - no entry point ever falls back to a CPU implementation.
+ *
+ * Status codes: 0 OK, 1 invalid argument, 2 misaligned pointer/stride, 3 unsupported shape or
+ * dtype, 4 CUDA call failed (asc_cuda_last_cuda_error gives the text), 5 a bounded device-side
+ * wait ran out, 6 size beyond a documented maximum, 7 no usable device.
+ */
+#ifndef ASC_CUDA_H_
+#define ASC_CUDA_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------------
+ * Device / stream / memory wrappers.  Same names and argument order as the reference's CANN
+ * wrappers so that asc.lib.runtime.interface keeps calling them unchanged.
+ * ---------------------------------------------------------------------------------------- */
+
+/* replaces rt_wrapper.cpp:23 — writes "B200" style SoC name (the CUDA device name). */
+int32_t GetSocVersionWrapper(char* ver, uint32_t maxLen);
+/* replaces rt_wrapper.cpp:32 */
+int32_t GetDeviceCountWrapper(int32_t* cnt);
+/* replaces rt_wrapper.cpp:66 — moduleType is ignored; infoType: 0 SM count, 1 HBM bytes,
+ * 2 L2 bytes, 3 max SM clock kHz, 4 compute capability (major*10+minor). */
+int32_t GetDeviceInfoWrapper(uint32_t deviceId, int32_t moduleType, int32_t infoType, int64_t* val);
+/* replaces rt_wrapper.cpp:77 — destroys the streams the library created on the device; never
+ * resets the GPU itself (the GPU is shared). */
+int32_t DeviceResetWrapper(int32_t devId);
+/* replaces rt_wrapper.cpp:86 */
+int32_t SetDeviceWrapper(int32_t devId);
+/* replaces rt_wrapper.cpp:96 */
+int32_t StreamCreateWrapper(void** stm, int32_t priority);
+/* replaces rt_wrapper.cpp:105 */
+int32_t StreamDestroyWrapper(void* stm);
+/* replaces rt_wrapper.cpp:156 — `type` and `moduleId` are accepted and ignored. */
+int32_t MallocWrapper(void** devPtr, uint64_t size, int32_t type, uint16_t moduleId);
+/* replaces rt_wrapper.cpp:172 — kind: 0 H2H, 1 H2D, 2 D2H, 3 D2D (reference enum values,
+ * python/asc/lib/runtime/support.py:96-105).  Synchronous. */
+int32_t MemcpyWrapper(void* dst, uint64_t destMax, const void* src, uint64_t cnt, int32_t kind);
+/* no reference counterpart: asynchronous copy on `stm` (pinned host memory recommended). */
+int32_t MemcpyAsyncWrapper(void* dst, uint64_t destMax, const void* src, uint64_t cnt, int32_t kind, void* stm);
+/* replaces rt_wrapper.cpp:203 — timeout in milliseconds; non-zero status when it runs out. */
+int32_t StreamSynchronizeWithTimeoutWrapper(void* stm, int32_t timeout);
+/* replaces rt_wrapper.cpp:215 */
+int32_t StreamSynchronizeWrapper(void* stm);
+/* replaces rt_wrapper.cpp:224 */
+int32_t FreeWrapper(void* devPtr);
+/* replaces rt_wrapper.cpp:232 */
+int32_t DeviceSynchronizeWrapper(void);
+/* no reference counterpart: page-locked host staging buffers for the launcher's H2D/D2H path
+ * (the reference stages through pageable memory, python/asc/runtime/memory_handle.py:82-91). */
+int32_t HostMallocWrapper(void** hostPtr, uint64_t size);
+int32_t HostFreeWrapper(void* hostPtr);
+/* no reference counterpart: pin / unpin a caller-owned host range in place. */
+int32_t HostRegisterWrapper(void* hostPtr, uint64_t size);
+int32_t HostUnregisterWrapper(void* hostPtr);
+
+/* ------------------------------------------------------------------------------------------
+ * Timing (stands in for the reference's msprof task timing,
+ * python/asc/lib/profiling/profiler.py:59-129): CUDA events on the launching stream.
+ * ---------------------------------------------------------------------------------------- */
+int32_t asc_cuda_event_create(void** ev);
+int32_t asc_cuda_event_record(void* ev, void* stream);
+int32_t asc_cuda_event_synchronize(void* ev);
+int32_t asc_cuda_event_elapsed_ms(void* start, void* stop, float* ms);
+int32_t asc_cuda_event_destroy(void* ev);
+
+/* ------------------------------------------------------------------------------------------
+ * Diagnostics
+ * ---------------------------------------------------------------------------------------- */
+/* Human-readable text for a status code. */
+int32_t asc_cuda_status_string(int32_t code, char* buf, uint32_t n);
+/* Text of the last failing CUDA call on this thread ("" when none). */
+int32_t asc_cuda_last_cuda_error(char* buf, uint32_t n);
+/* Synchronises `stream`, then reads and clears the current device's status word.  *dev_code is 0
+ * when every kernel finished normally; otherwise the code a kernel left when one of its bounded
+ * waits ran out, and the function returns 5. */
+int32_t asc_cuda_check_device_status(void* stream, uint32_t* dev_code);
+/* Number of kernels this library has launched since load (all threads). */
+int32_t asc_cuda_launch_count(uint64_t* count);
+
+/* ------------------------------------------------------------------------------------------
+ * Kernels.  Each replaces what the reference's launcher starts for the matching asc2 kernel
+ * (python/asc/runtime/launcher.py:156-195 -> rt_wrapper.cpp:189 KernelLaunchWrapper) together
+ * with the Ascend C routines its lowering calls.
+ * ---------------------------------------------------------------------------------------- */
+
+/* out[i] = x[i] + y[i], fp32, i in [0, n).  Bit-exact IEEE add.
+ * Replaces the vector-add tile loop of python/test/asc2/kernels/test_vadd.py:16-28
+ * (arith.addf -> AddL2Op, lib/Conversion/LowerToAsc/LowerArithBinary.cpp:113). */
+int32_t asc_cuda_vadd_f32(const float* x, const float* y, float* out, int64_t n, void* stream);
+
+/* out[i] = x[i] * y[i] + z[i] with separately rounded multiply and add (no FMA contraction),
+ * matching NumPy.  Replaces python/test/asc2/kernels/test_vmuladd.py:16-31. */
+int32_t asc_cuda_vmuladd_f32(const float* x, const float* y, const float* z, float* out, int64_t n, void* stream);
+
+/* Row softmax over the last dimension of a contiguous [rows, cols] fp32 matrix with max
+ * subtraction.  `ld` is the row pitch in elements (>= cols).  Replaces both asc2 softmax forms:
+ * the manual reduce_max/exp/reduce_sum kernel (python/test/asc2/kernels/test_softmax.py:16-27;
+ * LowerAscTile.cpp:428-459, LowerMath.cpp:95) and asc2.softmax
+ * (python/asc/language/tile/unary_ops.py:215-223 -> SoftMaxOp, LowerAscTile.cpp:155-188). */
+int32_t asc_cuda_softmax_f32(const float* x, float* out, int64_t rows, int64_t cols, int64_t ld, void* stream);
+
+/* C[M,N] = epilogue(A[M,K] @ B[K,N]), row-major operands, fp32 accumulation on tcgen05 tensor
+ * cores.  in_dtype: 0 fp16, 1 bf16.  out_dtype: 0 fp16, 1 bf16, 2 fp32.
+ * flags: bit0 ReLU before the cast; bit1 accumulate into C (C += A@B, fp32 out only).
+ * lda/ldb/ldc are row pitches in elements.  Requirements: base pointers 16-byte aligned,
+ * lda*2 and ldb*2 multiples of 16 bytes.
+ * Replaces asc2.matmul / matmul_acc + the fixpipe store
+ * (python/asc/language/tile/binary_ops.py:181-221; MmadOp, LowerAscTile.cpp:291-315,577-603;
+ * FixpipeOp, LowerAscTileDataTransfer.cpp:273-325). */
+int32_t asc_cuda_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                          int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype, int32_t flags,
+                          void* stream);
+
+/* fp32-input matmul with the same epilogue options (CUDA-core FMA; exists so that the fp32 case of
+ * python/test/asc2/kernels/test_matmul_fixpipe.py:36-48 runs; not a tuned path). */
+int32_t asc_cuda_gemm_f32(const float* A, const float* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                          int64_t ldb, int64_t ldc, int32_t out_dtype, int32_t flags, void* stream);
+
+/* acc[M,N] = A[M,K] @ B[K,N] with signed int8 operands and exact int32 accumulation
+ * (tcgen05 kind::i8); optionally deq[M,N] = fp16( (float(acc) * a_scale[row]) * b_scale[col] ).
+ * Either output pointer may be NULL (not both).  a_scale/b_scale are required when deq != NULL.
+ * Requirements: A, B 16-byte aligned; lda, ldb multiples of 16.
+ * The reference has no asc2 int8 matmul; the nearest definition is the golden of
+ * python/test/generalization/adv/test_matmul_quant.py:124-138 (int32 = a.int32 @ b.int32). */
+int32_t asc_cuda_gemm_i8(const int8_t* A, const int8_t* B, int32_t* acc, void* deq, const float* a_scale,
+                         const float* b_scale, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                         int64_t ldc, void* stream);
+
+/* O = softmax(scale * Q K^T [+ causal mask]) V for contiguous [B, H, S, D] tensors, fp32
+ * online-softmax accumulation.  dtype: 0 fp16, 1 bf16.  D must be 128 (the only head size of the
+ * workload this library targets) and S a multiple of 8.  causal != 0 masks key j > query i.
+ * No counterpart in the reference (it has no attention kernel); defined by the torch expression
+ * softmax((Q.float() @ K.float().transpose(-1,-2)) * scale + mask, -1) @ V.float(). */
+int32_t asc_cuda_attn_fwd_f16(const void* q, const void* k, const void* v, void* o, int32_t B, int32_t H,
+                              int32_t S, int32_t D, float scale, int32_t causal, int32_t dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* ASC_CUDA_H_ */

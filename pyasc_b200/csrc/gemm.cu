@@ -1,0 +1,551 @@
+// Tensor-core GEMMs for sm_100a: fp16/bf16 -> fp32 accumulate (tcgen05 kind::f16) and
+// int8 -> int32 (tcgen05 kind::i8), row-major A[M,K] and B[K,N], with a fused epilogue
+// (ReLU, down-cast, per-row/per-column dequantisation).
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer: streams 128 x 128-byte A tiles (K-major) and 128-byte-wide B column
+//               blocks (N contiguous, i.e. MN-major for the MMA) into a 4-stage 128B-swizzled
+//               shared-memory ring, one mbarrier per stage.
+//   warp 1      MMA issuer: four tcgen05.mma (128 x 256 x 32 bytes of K) per stage into one of
+//               two 128-lane x 256-column fp32/int32 accumulators in tensor memory;
+//               tcgen05.commit releases the stage and, after the last K block, publishes the
+//               accumulator.
+//   warps 2-5   epilogue: tcgen05.ld their 32-lane quarter of the accumulator, apply the
+//               epilogue and store 16-byte vectors; the other accumulator is being filled
+//               meanwhile, so the epilogue of tile i overlaps the main loop of tile i+1.
+// B is never transposed in memory: the MN-major shared-memory descriptor lets the tensor core
+// read it as stored.  All waits are bounded (see common.cuh).
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+
+#include "../../include/asc_cuda.h"
+#include "host_common.h"
+
+namespace {
+
+using namespace ascdev;
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kKBytes = 128;  // bytes of K per stage and per swizzle span
+constexpr int kStages = 4;
+constexpr int kGemmThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kGroupM = 16;  // tile rasterisation: M blocks per L2 reuse group
+
+constexpr uint32_t kSmemA = kBlockM * kKBytes;                // 16 KiB per stage
+constexpr uint32_t kSmemB = kBlockN * kKBytes;                // 32 KiB per stage
+constexpr uint32_t kStageBytes = kSmemA + kSmemB;             // 48 KiB
+constexpr uint32_t kGemmSmem = kStages * kStageBytes + 1024;  // + slack for 1024-byte alignment
+
+enum EpiMode : int { EPI_F16 = 0, EPI_BF16 = 1, EPI_F32 = 2, EPI_I8 = 3 };
+
+struct GemmParams {
+  void* c;              // fp16 / bf16 / fp32 output, or int32 accumulator output for EPI_I8 (nullable there)
+  void* deq;            // EPI_I8 only: fp16 dequantised output (nullable)
+  const float* a_scale; // EPI_I8 only: per-row scale
+  const float* b_scale; // EPI_I8 only: per-column scale
+  int64_t M, N, K;      // K in elements
+  int64_t ldc;
+  int32_t relu;
+  int32_t accumulate;   // EPI_F32 only: C += A @ B
+  int32_t vec_ok;       // 16-byte vector stores allowed (alignment of c/deq and ldc)
+  uint32_t* status;
+  // bring-up overrides of the shared-memory descriptor fields (0 = use the built-in value)
+  uint32_t dbg_a_sbo, dbg_a_kstep, dbg_b_lbo, dbg_b_sbo, dbg_b_kstep;
+};
+
+struct SharedCtl {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+__device__ __forceinline__ void tile_coords(int64_t tile, int64_t num_m, int64_t num_n, int64_t& m_blk,
+                                            int64_t& n_blk) {
+  const int64_t group_sz = static_cast<int64_t>(kGroupM) * num_n;
+  const int64_t g = tile / group_sz;
+  const int64_t first_m = g * kGroupM;
+  const int64_t gm = (num_m - first_m) < kGroupM ? (num_m - first_m) : kGroupM;
+  const int64_t r = tile - g * group_sz;
+  m_blk = first_m + r % gm;
+  n_blk = r / gm;
+}
+
+template <int kMode>
+__device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const uint32_t (&r)[32], int64_t row,
+                                                     int64_t col0) {
+  // this thread owns 32 consecutive columns [col0, col0+32) of output row `row`
+  if (row >= p.M || col0 >= p.N) return;
+  const bool full = (col0 + 32 <= p.N) && p.vec_ok;
+  if (kMode == EPI_F16 || kMode == EPI_BF16) {
+    uint32_t packed[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float a = __uint_as_float(r[2 * i]), b = __uint_as_float(r[2 * i + 1]);
+      if (p.relu) {
+        a = fmaxf(a, 0.f);
+        b = fmaxf(b, 0.f);
+      }
+      if (kMode == EPI_F16) {
+        __half2 h = __floats2half2_rn(a, b);
+        packed[i] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        packed[i] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    uint16_t* dst = reinterpret_cast<uint16_t*>(p.c) + row * p.ldc + col0;
+    if (full) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        reinterpret_cast<uint4*>(dst)[i] =
+            make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) dst[i] = static_cast<uint16_t>((packed[i >> 1] >> ((i & 1) * 16)) & 0xffffu);
+    }
+  } else if (kMode == EPI_F32) {
+    float* dst = reinterpret_cast<float*>(p.c) + row * p.ldc + col0;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+    if (p.accumulate) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) v[i] += dst[i];
+    }
+    if (p.relu) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
+    }
+    if (full) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < p.N) dst[i] = v[i];
+    }
+  } else {  // EPI_I8
+    if (p.c != nullptr) {
+      int32_t* dst = reinterpret_cast<int32_t*>(p.c) + row * p.ldc + col0;
+      if (full) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          reinterpret_cast<uint4*>(dst)[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (col0 + i < p.N) dst[i] = static_cast<int32_t>(r[i]);
+      }
+    }
+    if (p.deq != nullptr) {
+      const float as = __ldg(p.a_scale + row);
+      uint16_t* dst = reinterpret_cast<uint16_t*>(p.deq) + row * p.ldc + col0;
+      uint32_t packed[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const int64_t c = col0 + 2 * i;
+        const float s0 = (c < p.N) ? __ldg(p.b_scale + c) : 0.f;
+        const float s1 = (c + 1 < p.N) ? __ldg(p.b_scale + c + 1) : 0.f;
+        // left-to-right in fp32: (acc * a_scale[row]) * b_scale[col]
+        const float a = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[2 * i])), as), s0);
+        const float b = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[2 * i + 1])), as), s1);
+        __half2 h = __floats2half2_rn(a, b);
+        packed[i] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      if (full) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          reinterpret_cast<uint4*>(dst)[i] =
+              make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (col0 + i < p.N) dst[i] = static_cast<uint16_t>((packed[i >> 1] >> ((i & 1) * 16)) & 0xffffu);
+      }
+    }
+  }
+}
+
+// kElemBytes: 2 (fp16/bf16, kind::f16, UMMA K = 16) or 1 (int8, kind::i8, UMMA K = 32)
+template <int kElemBytes, int kMode>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const GemmParams p, const uint32_t idesc) {
+  constexpr int kBlockK = kKBytes / kElemBytes;        // elements of K per stage: 64 or 128
+  constexpr int kUmmaK = 32 / kElemBytes;              // elements of K per MMA: 16 or 32
+  constexpr int kNBlockCols = 128 / kElemBytes;        // columns of B per 128-byte block: 64 or 128
+  constexpr int kNBlocks = kBlockN / kNBlockCols;      // 4 or 2
+  constexpr uint32_t kBBlockBytes = kBlockK * 128;     // one column block: kBlockK rows of 128 B
+  constexpr uint32_t kBKStep = kUmmaK * 128;           // bytes between consecutive MMA K slices of B
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ SharedCtl ctl;
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  volatile uint32_t* abort_flag = &ctl.abort_flag;
+
+  const int64_t num_m = (p.M + kBlockM - 1) / kBlockM;
+  const int64_t num_n = (p.N + kBlockN - 1) / kBlockN;
+  const int64_t num_tiles = num_m * num_n;
+  const int64_t num_kb = (p.K + kBlockK - 1) / kBlockK;
+
+  if (threadIdx.x == 0) {
+    ctl.abort_flag = 0;
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&ctl.full[s]), 1);
+      mbar_init(smem_u32(&ctl.empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&ctl.tmem_full[a]), 1);
+      mbar_init(smem_u32(&ctl.tmem_empty[a]), 4);
+    }
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctl.tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl.tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int64_t m_blk, n_blk;
+      tile_coords(tile, num_m, num_n, m_blk, n_blk);
+      const int32_t m0 = static_cast<int32_t>(m_blk * kBlockM);
+      const int32_t n0 = static_cast<int32_t>(n_blk * kBlockN);
+      for (int64_t kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&ctl.empty[stage]), phase ^ 1, abort_flag, p.status, ASC_DEV_TIMEOUT_EMPTY);
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t full = smem_u32(&ctl.full[stage]);
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint32_t sb = sa + kSmemA;
+          const int32_t k0 = static_cast<int32_t>(kb * kBlockK);
+          mbar_arrive_expect_tx(full, kStageBytes);
+          tma_load_2d(sa, &tmap_a, full, k0, m0);
+#pragma unroll
+          for (int j = 0; j < kNBlocks; ++j)
+            tma_load_2d(sb + j * kBBlockBytes, &tmap_b, full, n0 + j * kNBlockCols, k0);
+        }
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    int64_t local = 0;
+    for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      const uint32_t acc = static_cast<uint32_t>(local & 1);
+      const uint32_t acc_phase = static_cast<uint32_t>((local >> 1) & 1);
+      ok = mbar_wait(smem_u32(&ctl.tmem_empty[acc]), acc_phase ^ 1, abort_flag, p.status,
+                     ASC_DEV_TIMEOUT_TMEM_EMPTY);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * kBlockN;
+      for (int64_t kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&ctl.full[stage]), phase, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = smem_base + stage * kStageBytes;
+          const uint32_t sb = sa + kSmemA;
+          const uint64_t adesc = make_smem_desc_sw128(sa, 16, p.dbg_a_sbo ? p.dbg_a_sbo : 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(sb, p.dbg_b_lbo ? p.dbg_b_lbo : kBBlockBytes,
+                                                      p.dbg_b_sbo ? p.dbg_b_sbo : 1024);
+          const uint32_t a_kstep = p.dbg_a_kstep ? p.dbg_a_kstep : 32;
+          const uint32_t b_kstep = p.dbg_b_kstep ? p.dbg_b_kstep : kBKStep;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const uint64_t ad = adesc + static_cast<uint64_t>((k * a_kstep) >> 4);
+            const uint64_t bd = bdesc + static_cast<uint64_t>((k * b_kstep) >> 4);
+            const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+            if (kElemBytes == 2) {
+              umma_f16_ss(d_tmem, ad, bd, idesc, accumulate);
+            } else {
+              umma_i8_ss(d_tmem, ad, bd, idesc, accumulate);
+            }
+          }
+          umma_commit(smem_u32(&ctl.empty[stage]));
+          if (kb == num_kb - 1) umma_commit(smem_u32(&ctl.tmem_full[acc]));
+        }
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // -------------------------------- epilogue --------------------------------
+    const uint32_t quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    bool ok = true;
+    int64_t local = 0;
+    for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      int64_t m_blk, n_blk;
+      tile_coords(tile, num_m, num_n, m_blk, n_blk);
+      const uint32_t acc = static_cast<uint32_t>(local & 1);
+      const uint32_t acc_phase = static_cast<uint32_t>((local >> 1) & 1);
+      ok = mbar_wait(smem_u32(&ctl.tmem_full[acc]), acc_phase, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      const int64_t row = m_blk * kBlockM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * kBlockN;
+#pragma unroll 1
+      for (int c = 0; c < kBlockN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        epilogue_store_chunk<kMode>(p, r, row, n_blk * kBlockN + c * 32);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctl.tmem_empty[acc]));
+    }
+  }
+
+  if (*abort_flag) {
+    // a wait ran out somewhere: give copies and MMAs still in flight time to land before
+    // shared and tensor memory are released
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Plain fp32 matmul on CUDA cores (32 x 32 tiles), used only for fp32 operands.
+__global__ void __launch_bounds__(256)
+    gemm_f32_simt_kernel(const float* __restrict__ A, const float* __restrict__ B, void* __restrict__ C, int64_t M,
+                         int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int out_dtype, int relu,
+                         int accumulate) {
+  __shared__ float as[32][33];
+  __shared__ float bs[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  const int64_t m0 = static_cast<int64_t>(blockIdx.y) * 32, n0 = static_cast<int64_t>(blockIdx.x) * 32;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int64_t k0 = 0; k0 < K; k0 += 32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = ty + 8 * i;
+      as[r][tx] = (m0 + r < M && k0 + tx < K) ? A[(m0 + r) * lda + k0 + tx] : 0.f;
+      bs[r][tx] = (k0 + r < K && n0 + tx < N) ? B[(k0 + r) * ldb + n0 + tx] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 32; ++kk) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i] = fmaf(as[ty + 8 * i][kk], bs[kk][tx], acc[i]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t r = m0 + ty + 8 * i, c = n0 + tx;
+    if (r < M && c < N) {
+      float v = acc[i];
+      if (accumulate && out_dtype == 2) v += reinterpret_cast<float*>(C)[r * ldc + c];
+      if (relu) v = fmaxf(v, 0.f);
+      if (out_dtype == 2) {
+        reinterpret_cast<float*>(C)[r * ldc + c] = v;
+      } else if (out_dtype == 0) {
+        reinterpret_cast<__half*>(C)[r * ldc + c] = __float2half_rn(v);
+      } else {
+        reinterpret_cast<__nv_bfloat16*>(C)[r * ldc + c] = __float2bfloat16_rn(v);
+      }
+    }
+  }
+}
+
+template <int kElemBytes, int kMode>
+int32_t launch_gemm(const void* A, const void* B, int64_t lda, int64_t ldb, CUtensorMapDataType dt, uint32_t idesc,
+                    GemmParams p, int32_t max_ctas, cudaStream_t stream) {
+  constexpr int kBlockK = kKBytes / kElemBytes;
+  constexpr int kNBlockCols = 128 / kElemBytes;
+  CUtensorMap tmap_a, tmap_b;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(lda) * kElemBytes};
+    const uint32_t box[2] = {kBlockK, kBlockM};
+    int32_t rc = aschost::encode_tmap(&tmap_a, dt, 2, A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (rc != ASC_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.K)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(ldb) * kElemBytes};
+    const uint32_t box[2] = {kNBlockCols, kBlockK};
+    int32_t rc = aschost::encode_tmap(&tmap_b, dt, 2, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (rc != ASC_OK) return rc;
+  }
+  int32_t rc = aschost::device_status_word(&p.status);
+  if (rc != ASC_OK) return rc;
+  int sms = 0;
+  rc = aschost::sm_count(&sms);
+  if (rc != ASC_OK) return rc;
+
+  auto kernel = gemm_tcgen05_kernel<kElemBytes, kMode>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  ASC_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    ASC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
+    attr_set[dev] = true;
+  }
+  const int64_t num_tiles = ((p.M + kBlockM - 1) / kBlockM) * ((p.N + kBlockN - 1) / kBlockN);
+  int64_t grid = num_tiles < sms ? num_tiles : sms;
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  kernel<<<static_cast<unsigned>(grid), kGemmThreads, kGemmSmem, stream>>>(tmap_a, tmap_b, p, idesc);
+  aschost::count_launch();
+  ASC_CUDA_TRY(cudaGetLastError());
+  return ASC_OK;
+}
+
+int32_t check_gemm_args(const void* A, const void* B, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                        int64_t ldc, int elem_bytes) {
+  if (A == nullptr || B == nullptr) return ASC_ERR_INVALID_ARG;
+  if (M <= 0 || N <= 0 || K <= 0) return ASC_ERR_INVALID_ARG;
+  if (lda < K || ldb < N || ldc < N) return ASC_ERR_INVALID_ARG;
+  if (M > 0x7fffff00ll || N > 0x7fffff00ll || K > 0x7fffff00ll) return ASC_ERR_TOO_LARGE;
+  if (!aschost::aligned16(A) || !aschost::aligned16(B)) return ASC_ERR_MISALIGNED;
+  if ((lda * elem_bytes) % 16 != 0 || (ldb * elem_bytes) % 16 != 0) return ASC_ERR_MISALIGNED;
+  return ASC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t asc_cuda_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                          int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype, int32_t flags,
+                          void* stream) {
+  if (C == nullptr) return ASC_ERR_INVALID_ARG;
+  if (in_dtype < 0 || in_dtype > 1 || out_dtype < 0 || out_dtype > 2 || (flags & ~3) != 0) return ASC_ERR_INVALID_ARG;
+  if ((flags & 2) && out_dtype != 2) return ASC_ERR_UNSUPPORTED;
+  int32_t rc = check_gemm_args(A, B, M, N, K, lda, ldb, ldc, 2);
+  if (rc != ASC_OK) return rc;
+  GemmParams p{};
+  p.c = C;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldc = ldc;
+  p.relu = flags & 1;
+  p.accumulate = (flags >> 1) & 1;
+  const int out_bytes = out_dtype == 2 ? 4 : 2;
+  p.vec_ok = aschost::aligned16(C) && ((ldc * out_bytes) % 16 == 0);
+  const uint32_t idesc = make_idesc(/*c_fmt F32*/ 1, in_dtype, in_dtype, /*a K-major*/ 0, /*b MN-major*/ 1, kBlockM,
+                                    kBlockN);
+  const CUtensorMapDataType dt = in_dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (out_dtype) {
+    case 0: return launch_gemm<2, EPI_F16>(A, B, lda, ldb, dt, idesc, p, 0, s);
+    case 1: return launch_gemm<2, EPI_BF16>(A, B, lda, ldb, dt, idesc, p, 0, s);
+    default: return launch_gemm<2, EPI_F32>(A, B, lda, ldb, dt, idesc, p, 0, s);
+  }
+}
+
+int32_t asc_cuda_gemm_f32(const float* A, const float* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                          int64_t ldb, int64_t ldc, int32_t out_dtype, int32_t flags, void* stream) {
+  if (A == nullptr || B == nullptr || C == nullptr) return ASC_ERR_INVALID_ARG;
+  if (M <= 0 || N <= 0 || K <= 0 || lda < K || ldb < N || ldc < N) return ASC_ERR_INVALID_ARG;
+  if (out_dtype < 0 || out_dtype > 2 || (flags & ~3) != 0) return ASC_ERR_INVALID_ARG;
+  if ((flags & 2) && out_dtype != 2) return ASC_ERR_UNSUPPORTED;
+  const int64_t gx = (N + 31) / 32, gy = (M + 31) / 32;
+  if (gy > 65535) return ASC_ERR_TOO_LARGE;
+  dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
+  gemm_f32_simt_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(A, B, C, M, N, K, lda, ldb, ldc, out_dtype,
+                                                                           flags & 1, (flags >> 1) & 1);
+  aschost::count_launch();
+  ASC_CUDA_TRY(cudaGetLastError());
+  return ASC_OK;
+}
+
+int32_t asc_cuda_gemm_i8(const int8_t* A, const int8_t* B, int32_t* acc, void* deq, const float* a_scale,
+                         const float* b_scale, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                         int64_t ldc, void* stream) {
+  if (acc == nullptr && deq == nullptr) return ASC_ERR_INVALID_ARG;
+  if (deq != nullptr && (a_scale == nullptr || b_scale == nullptr)) return ASC_ERR_INVALID_ARG;
+  int32_t rc = check_gemm_args(A, B, M, N, K, lda, ldb, ldc, 1);
+  if (rc != ASC_OK) return rc;
+  GemmParams p{};
+  p.c = acc;
+  p.deq = deq;
+  p.a_scale = a_scale;
+  p.b_scale = b_scale;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldc = ldc;
+  p.vec_ok = (acc == nullptr || (aschost::aligned16(acc) && (ldc * 4) % 16 == 0)) &&
+             (deq == nullptr || (aschost::aligned16(deq) && (ldc * 2) % 16 == 0));
+  const uint32_t idesc = make_idesc(/*c_fmt S32*/ 2, /*S8*/ 1, 1, 0, 1, kBlockM, kBlockN);
+  return launch_gemm<1, EPI_I8>(A, B, lda, ldb, CU_TENSOR_MAP_DATA_TYPE_UINT8, idesc, p, 0,
+                                static_cast<cudaStream_t>(stream));
+}
+
+// Bring-up hook: same GEMM with descriptor-field overrides and a CTA cap.
+// in_dtype: 0 fp16, 1 bf16, 2 int8 (int32 output); out_dtype as asc_cuda_gemm_f16 (ignored for int8).
+int32_t asc_cuda_gemm_debug(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                            int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype, uint32_t a_sbo,
+                            uint32_t a_kstep, uint32_t b_lbo, uint32_t b_sbo, uint32_t b_kstep, int32_t max_ctas,
+                            void* stream) {
+  if (C == nullptr) return ASC_ERR_INVALID_ARG;
+  int32_t rc = check_gemm_args(A, B, M, N, K, lda, ldb, ldc, in_dtype == 2 ? 1 : 2);
+  if (rc != ASC_OK) return rc;
+  GemmParams p{};
+  p.c = C;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldc = ldc;
+  p.dbg_a_sbo = a_sbo;
+  p.dbg_a_kstep = a_kstep;
+  p.dbg_b_lbo = b_lbo;
+  p.dbg_b_sbo = b_sbo;
+  p.dbg_b_kstep = b_kstep;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (in_dtype == 2) {
+    p.vec_ok = aschost::aligned16(C) && (ldc * 4) % 16 == 0;
+    const uint32_t idesc = make_idesc(2, 1, 1, 0, 1, kBlockM, kBlockN);
+    return launch_gemm<1, EPI_I8>(A, B, lda, ldb, CU_TENSOR_MAP_DATA_TYPE_UINT8, idesc, p, max_ctas, s);
+  }
+  const int out_bytes = out_dtype == 2 ? 4 : 2;
+  p.vec_ok = aschost::aligned16(C) && ((ldc * out_bytes) % 16 == 0);
+  const uint32_t idesc = make_idesc(1, in_dtype, in_dtype, 0, 1, kBlockM, kBlockN);
+  const CUtensorMapDataType dt = in_dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  switch (out_dtype) {
+    case 0: return launch_gemm<2, EPI_F16>(A, B, lda, ldb, dt, idesc, p, max_ctas, s);
+    case 1: return launch_gemm<2, EPI_BF16>(A, B, lda, ldb, dt, idesc, p, max_ctas, s);
+    default: return launch_gemm<2, EPI_F32>(A, B, lda, ldb, dt, idesc, p, max_ctas, s);
+  }
+}
+
+}  // extern "C"

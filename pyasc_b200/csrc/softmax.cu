@@ -1,0 +1,213 @@
+// Row softmax (fp32, last dimension, max-subtracted) for sm_100a.
+//
+// HBM-bound: 8 algorithmic bytes per element (one 4-byte read, one 4-byte write).  One CTA owns a
+// row at a time; the row lives in registers between the single global read and the single global
+// write (128-bit accesses), row maximum and row sum are reduced with warp shuffles and a small
+// shared-memory exchange between warps, and the next row's loads are issued before the current
+// row's arithmetic so that memory latency overlaps the exp work.  Rows too long for registers are
+// staged in shared memory instead (one global read, one global write); rows too long for shared
+// memory are re-read from global memory.
+#include <cfloat>
+
+#include "../../include/asc_cuda.h"
+#include "host_common.h"
+
+namespace {
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+template <int kWarps, bool kIsMax>
+__device__ __forceinline__ float cta_reduce(float v, float* red) {
+  v = kIsMax ? warp_max(v) : warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = red[0];
+#pragma unroll
+  for (int w = 1; w < kWarps; ++w) r = kIsMax ? fmaxf(r, red[w]) : r + red[w];
+  return r;
+}
+
+// Register-resident rows: cols % 4 == 0, cols <= kThreads * kVec * 4, rows 16-byte aligned.
+template <int kThreads, int kVec>
+__global__ void __launch_bounds__(kThreads)
+    softmax_rows_reg_kernel(const float* __restrict__ x, float* __restrict__ out, int64_t rows, int cols4,
+                            int64_t ld4) {
+  constexpr int kWarps = kThreads / 32;
+  __shared__ float red_max[kWarps];
+  __shared__ float red_sum[kWarps];
+  const float4* x4 = reinterpret_cast<const float4*>(x);
+  float4* o4 = reinterpret_cast<float4*>(out);
+  const float4 neg = make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+
+  int64_t row = blockIdx.x;
+  if (row >= rows) return;
+  float4 v[kVec];
+#pragma unroll
+  for (int u = 0; u < kVec; ++u) {
+    const int c = threadIdx.x + u * kThreads;
+    v[u] = (c < cols4) ? __ldcs(x4 + row * ld4 + c) : neg;
+  }
+  for (; row < rows; row += gridDim.x) {
+    const int64_t next = row + gridDim.x;
+    float4 nv[kVec];
+    if (next < rows) {
+#pragma unroll
+      for (int u = 0; u < kVec; ++u) {
+        const int c = threadIdx.x + u * kThreads;
+        nv[u] = (c < cols4) ? __ldcs(x4 + next * ld4 + c) : neg;
+      }
+    }
+    float m = -FLT_MAX;
+#pragma unroll
+    for (int u = 0; u < kVec; ++u) m = fmaxf(m, fmaxf(fmaxf(v[u].x, v[u].y), fmaxf(v[u].z, v[u].w)));
+    m = cta_reduce<kWarps, true>(m, red_max);
+    float s = 0.f;
+#pragma unroll
+    for (int u = 0; u < kVec; ++u) {
+      v[u].x = expf(v[u].x - m);
+      v[u].y = expf(v[u].y - m);
+      v[u].z = expf(v[u].z - m);
+      v[u].w = expf(v[u].w - m);
+      s += (v[u].x + v[u].y) + (v[u].z + v[u].w);
+    }
+    s = cta_reduce<kWarps, false>(s, red_sum);
+    const float inv = __frcp_rn(s);
+#pragma unroll
+    for (int u = 0; u < kVec; ++u) {
+      const int c = threadIdx.x + u * kThreads;
+      if (c < cols4) {
+        float4 r = make_float4(v[u].x * inv, v[u].y * inv, v[u].z * inv, v[u].w * inv);
+        __stcs(o4 + row * ld4 + c, r);
+      }
+    }
+    if (next < rows) {
+#pragma unroll
+      for (int u = 0; u < kVec; ++u) v[u] = nv[u];
+    }
+  }
+}
+
+// Any cols / alignment.  kStage: the row is kept in dynamic shared memory between the passes.
+template <bool kStage>
+__global__ void __launch_bounds__(256)
+    softmax_rows_generic_kernel(const float* __restrict__ x, float* __restrict__ out, int64_t rows, int64_t cols,
+                                int64_t ld) {
+  extern __shared__ float row_buf[];
+  __shared__ float red_a[8];
+  __shared__ float red_b[8];
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* xr = x + row * ld;
+    float* orow = out + row * ld;
+    float m = -FLT_MAX;
+    for (int64_t c = threadIdx.x; c < cols; c += 256) {
+      const float t = xr[c];
+      if (kStage) row_buf[c] = t;
+      m = fmaxf(m, t);
+    }
+    m = cta_reduce<8, true>(m, red_a);
+    float s = 0.f;
+    for (int64_t c = threadIdx.x; c < cols; c += 256) {
+      const float e = expf((kStage ? row_buf[c] : xr[c]) - m);
+      if (kStage) row_buf[c] = e;
+      s += e;
+    }
+    s = cta_reduce<8, false>(s, red_b);
+    const float inv = __frcp_rn(s);
+    for (int64_t c = threadIdx.x; c < cols; c += 256) {
+      const float e = kStage ? row_buf[c] : expf(xr[c] - m);
+      orow[c] = e * inv;
+    }
+    __syncthreads();  // red_a / red_b / row_buf are reused by the next row
+  }
+}
+
+template <int kThreads, int kVec>
+int32_t launch_reg(const float* x, float* out, int64_t rows, int64_t cols, int64_t ld, int ctas_per_sm,
+                   cudaStream_t stream) {
+  int sms = 0;
+  int32_t rc = aschost::sm_count(&sms);
+  if (rc != ASC_OK) return rc;
+  int64_t grid = static_cast<int64_t>(sms) * ctas_per_sm;
+  if (grid > rows) grid = rows;
+  softmax_rows_reg_kernel<kThreads, kVec><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
+      x, out, rows, static_cast<int>(cols / 4), ld / 4);
+  aschost::count_launch();
+  ASC_CUDA_TRY(cudaGetLastError());
+  return ASC_OK;
+}
+
+int32_t launch_softmax(const float* x, float* out, int64_t rows, int64_t cols, int64_t ld, int32_t variant,
+                       cudaStream_t stream) {
+  if (rows < 0 || cols < 0 || ld < cols) return ASC_ERR_INVALID_ARG;
+  if (rows == 0 || cols == 0) return ASC_OK;
+  if (x == nullptr || out == nullptr) return ASC_ERR_INVALID_ARG;
+  const bool vec_ok = (cols % 4 == 0) && (ld % 4 == 0) && aschost::aligned16(x) && aschost::aligned16(out);
+  const int per_sm = (variant >> 8) & 0xff;
+  const int shape = variant & 0xff;
+  if (vec_ok && cols <= 8192 && shape != 0xff) {
+    if (cols <= 512) return launch_reg<128, 1>(x, out, rows, cols, ld, per_sm ? per_sm : 12, stream);
+    if (cols <= 1024) return launch_reg<128, 2>(x, out, rows, cols, ld, per_sm ? per_sm : 12, stream);
+    if (cols <= 2048) return launch_reg<128, 4>(x, out, rows, cols, ld, per_sm ? per_sm : 8, stream);
+    if (cols <= 4096) {
+      if (shape == 1) return launch_reg<128, 8>(x, out, rows, cols, ld, per_sm ? per_sm : 6, stream);
+      if (shape == 2) return launch_reg<512, 2>(x, out, rows, cols, ld, per_sm ? per_sm : 3, stream);
+      return launch_reg<256, 4>(x, out, rows, cols, ld, per_sm ? per_sm : 6, stream);
+    }
+    return launch_reg<256, 8>(x, out, rows, cols, ld, per_sm ? per_sm : 4, stream);
+  }
+  int sms = 0;
+  int32_t rc = aschost::sm_count(&sms);
+  if (rc != ASC_OK) return rc;
+  const size_t row_bytes = static_cast<size_t>(cols) * sizeof(float);
+  constexpr size_t kMaxStage = 200 * 1024;
+  if (row_bytes <= kMaxStage) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    ASC_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+      ASC_CUDA_TRY(cudaFuncSetAttribute(softmax_rows_generic_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(kMaxStage)));
+      attr_set[dev] = true;
+    }
+    int64_t per = static_cast<int64_t>((220 * 1024) / (row_bytes + 1024));
+    if (per < 1) per = 1;
+    if (per > 8) per = 8;
+    int64_t grid = static_cast<int64_t>(sms) * per;
+    if (grid > rows) grid = rows;
+    softmax_rows_generic_kernel<true><<<static_cast<unsigned>(grid), 256, row_bytes, stream>>>(x, out, rows, cols, ld);
+  } else {
+    int64_t grid = static_cast<int64_t>(sms) * 8;
+    if (grid > rows) grid = rows;
+    softmax_rows_generic_kernel<false><<<static_cast<unsigned>(grid), 256, 0, stream>>>(x, out, rows, cols, ld);
+  }
+  aschost::count_launch();
+  ASC_CUDA_TRY(cudaGetLastError());
+  return ASC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t asc_cuda_softmax_f32(const float* x, float* out, int64_t rows, int64_t cols, int64_t ld, void* stream) {
+  return launch_softmax(x, out, rows, cols, ld, 0, static_cast<cudaStream_t>(stream));
+}
+
+// variant: bits 0-7 CTA shape selector for 2048 < cols <= 4096 (0: 256x4, 1: 128x8, 2: 512x2,
+// 0xff: force the generic staged kernel); bits 8-15 CTAs per SM (0: default).
+int32_t asc_cuda_softmax_f32_variant(const float* x, float* out, int64_t rows, int64_t cols, int64_t ld,
+                                     int32_t variant, void* stream) {
+  return launch_softmax(x, out, rows, cols, ld, variant, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"
