@@ -1,0 +1,807 @@
+"""Maps a recorded kernel onto the hand-written CUDA kernels of libasc_cuda.
+
+The reference lowers the recorded tile ops through ``asctile`` -> ``ascendc`` -> Ascend C and runs
+``core_num`` blocks (lib/Conversion/LowerToAsc/*.cpp).  The CUDA platform instead recognises the
+whole-kernel pattern and launches one fused CUDA kernel that produces the same result over the part
+of each tensor the blocks would have touched together.  For that it
+
+1. evaluates every load/store offset for all blocks and loop iterations at once (NumPy), honouring
+   the reference's boundary rules: loads past the tensor end are padded, stores are clipped
+   (LowerAscTileDataTransfer.cpp:184-218, 254-261);
+2. checks that the touched tiles form contiguous ranges / full tile grids and merges them;
+3. emits :class:`Step` objects, each one C-ABI call with concrete sizes and byte offsets.
+
+A kernel that fits no pattern raises ``NotImplementedError``: there is no interpreter, Triton or CPU
+fallback behind this module.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from ..language.core.dtype import DataType, KnownTypes as KT
+from ..language.core.ir_value import PlainValue, same_scalar
+from ..language.tile.tensor import Tensor
+from ..language.tile.tile import Tile
+from ..language.tile.trace import Effect, Loop, Node
+from .tracer import KernelTrace
+
+MAX_INSTANCES = 1 << 26     # (block, iteration) combinations the matcher is willing to enumerate
+MAX_CALLS = 4096            # C-ABI calls one kernel launch may expand to
+
+_DTYPE_CODE_16 = {"float16": 0, "bfloat16": 1}
+_OUT_CODE = {"float16": 0, "bfloat16": 1, "float32": 2}
+
+
+class UnsupportedKernelError(NotImplementedError):
+    pass
+
+
+def _unsupported(msg: str) -> UnsupportedKernelError:
+    return UnsupportedKernelError(f"The CUDA platform has no kernel for this pattern: {msg}")
+
+
+# --------------------------------------------------------------------------------------------------
+# Plan
+# --------------------------------------------------------------------------------------------------
+class Step:
+    """One C-ABI call.  ``build(ptrs, stream)`` returns the ctypes argument list; ``ptrs`` maps a
+    runtime-argument index (or a temp-buffer key) to a device address."""
+
+    def __init__(self, fn_name: str, build: Callable[[Dict[Any, int], Any], Sequence[Any]], note: str = ""):
+        self.fn_name = fn_name
+        self.build = build
+        self.note = note
+
+    def __repr__(self) -> str:
+        return f"Step({self.fn_name}: {self.note})"
+
+
+class Plan:
+
+    def __init__(self, pattern: str):
+        self.pattern = pattern
+        self.steps: List[Step] = []
+        self.reads: set = set()       # runtime-argument indices the kernel reads
+        self.writes: set = set()      # ... and writes
+        self.temps: Dict[str, int] = {}  # temp-buffer key -> bytes
+
+    def __repr__(self) -> str:
+        return f"Plan({self.pattern}, steps={self.steps}, reads={sorted(self.reads)}, writes={sorted(self.writes)})"
+
+
+def _p(addr: int) -> ctypes.c_void_p:
+    return ctypes.c_void_p(addr)
+
+
+# --------------------------------------------------------------------------------------------------
+# Enumerating (block, iteration) instances of a loop nest
+# --------------------------------------------------------------------------------------------------
+def enumerate_instances(core_num: int, loops: Tuple[Loop, ...]) -> Dict[str, np.ndarray]:
+    """Symbol bindings, one array entry per (block, iteration...) combination of ``loops``."""
+    env: Dict[str, np.ndarray] = {"block_idx": np.arange(core_num, dtype=np.int64)}
+    count = core_num
+    for loop in loops:
+        start = np.broadcast_to(np.asarray(loop.start.evaluate(env), dtype=np.int64), (count, ))
+        stop = np.broadcast_to(np.asarray(loop.stop.evaluate(env), dtype=np.int64), (count, ))
+        step = np.broadcast_to(np.asarray(loop.step.evaluate(env), dtype=np.int64), (count, ))
+        if np.any(step <= 0):
+            raise _unsupported("loop with a non-positive step")
+        trips = np.maximum(0, -((start - stop) // step))
+        total = int(trips.sum())
+        if total > MAX_INSTANCES:
+            raise _unsupported(f"loop nest expands to {total} iterations; use larger tiles")
+        rep = np.repeat(np.arange(count), trips)
+        first = np.cumsum(trips) - trips
+        k = np.arange(total, dtype=np.int64) - np.repeat(first, trips)
+        env = {name: arr[rep] for name, arr in env.items()}
+        env[loop.name] = start[rep] + k * step[rep]
+        count = total
+    return env
+
+
+def eval_int(value: PlainValue, env: Dict[str, np.ndarray], count: int) -> np.ndarray:
+    return np.broadcast_to(np.asarray(value.evaluate(env), dtype=np.int64), (count, )).copy()
+
+
+def env_count(env: Dict[str, np.ndarray]) -> int:
+    return int(next(iter(env.values())).shape[0])
+
+
+def merge_intervals(starts: np.ndarray, ends: np.ndarray) -> List[Tuple[int, int]]:
+    """Union of half-open intervals as a sorted list of disjoint ones."""
+    keep = ends > starts
+    starts, ends = starts[keep], ends[keep]
+    if starts.size == 0:
+        return []
+    order = np.argsort(starts, kind="stable")
+    starts, ends = starts[order], ends[order]
+    run_max = np.maximum.accumulate(ends)
+    breaks = np.nonzero(starts[1:] > run_max[:-1])[0] + 1
+    firsts = np.concatenate(([0], breaks))
+    lasts = np.concatenate((breaks, [starts.size])) - 1
+    return [(int(starts[f]), int(run_max[l])) for f, l in zip(firsts, lasts)]
+
+
+# --------------------------------------------------------------------------------------------------
+# Views of global tensors
+# --------------------------------------------------------------------------------------------------
+class GmView:
+    """A tile that is (a sub-window of) a load from a global tensor."""
+
+    def __init__(self, tensor: Tensor, offsets: Tuple[PlainValue, ...], shape: Tuple[int, ...], pad_value: Any = 0):
+        self.tensor = tensor
+        self.offsets = offsets
+        self.shape = shape
+        self.pad_value = pad_value
+
+
+def resolve_view(tile: Any) -> Optional[GmView]:
+    if not isinstance(tile, Tile):
+        return None
+    node = tile.node
+    if node.kind == "load":
+        return GmView(node.args[0], node.attrs["offsets"], node.attrs["shape"], node.attrs["pad_value"])
+    if node.kind == "copy":
+        inner = resolve_view(node.args[0])
+        if inner is None:
+            return None
+        offs = tuple(a + b for a, b in zip(inner.offsets, node.attrs["offsets"]))
+        return GmView(inner.tensor, offs, node.attrs["shape"], inner.pad_value)
+    return None
+
+
+def _is_zero_pad(view: GmView) -> bool:
+    pv = view.pad_value
+    if isinstance(pv, PlainValue):
+        return pv.is_const and pv.value == 0
+    return pv == 0 or pv is None
+
+
+def _row_major_2d(t: Tensor) -> Tuple[int, int]:
+    shape = t.static_shape()
+    if len(shape) == 1:
+        return 1, shape[0]
+    if len(shape) == 2:
+        return shape
+    raise _unsupported(f"tensor of rank {len(shape)}")
+
+
+def _check_fits(t: Tensor) -> None:
+    n = 1
+    for d in t.static_shape():
+        n *= d
+    if n > t.base.numel:
+        raise RuntimeError(f"asc2.tensor({t.base.name}, {list(t.static_shape())}) describes {n} elements but the "
+                           f"argument holds {t.base.numel}")
+
+
+# --------------------------------------------------------------------------------------------------
+# Small structural helpers
+# --------------------------------------------------------------------------------------------------
+def _node(tile: Any, _kind: str, /, **attrs) -> Optional[Node]:
+    """The tile's defining node if it is of ``kind`` with the given attribute values."""
+    if not isinstance(tile, Tile) or tile.node.kind != _kind:
+        return None
+    for k, v in attrs.items():
+        if tile.node.attrs.get(k) != v:
+            return None
+    return tile.node
+
+
+def _tile_scalar_node(value: Any, _kind: str, /, **attrs) -> Optional[Node]:
+    """``value`` is the scalar result of a no-axis reduction (or scalar load) node of ``kind``."""
+    if not isinstance(value, PlainValue) or value.op != "tile_scalar":
+        return None
+    node = value.args[0]
+    if node.kind != _kind:
+        return None
+    for k, v in attrs.items():
+        if node.attrs.get(k) != v:
+            return None
+    return node
+
+
+def _same_offsets(a: Sequence[PlainValue], b: Sequence[PlainValue]) -> bool:
+    return len(a) == len(b) and all(same_scalar(x, y) for x, y in zip(a, b))
+
+
+def _flat_window(view_tensor: Tensor, offsets: Sequence[PlainValue], shape: Tuple[int, ...]):
+    """For a tile that covers whole rows of a row-major tensor (or any 1-D tile): returns
+    ``(flat_offset_expr, elements)``; ``None`` when the tile is not one contiguous range."""
+    tshape = view_tensor.static_shape()
+    if len(tshape) != len(shape):
+        return None
+    if len(shape) == 1:
+        return offsets[0], shape[0]
+    # all trailing dims must span the tensor fully and start at 0
+    for d in range(1, len(shape)):
+        if shape[d] != tshape[d] or not (offsets[d].is_const and offsets[d].value == 0):
+            return None
+    inner = 1
+    for d in tshape[1:]:
+        inner *= d
+    return offsets[0] * inner, shape[0] * inner
+
+
+# --------------------------------------------------------------------------------------------------
+# Pattern: elementwise map over same-offset loads (x + y, x * y + z)
+# --------------------------------------------------------------------------------------------------
+def _match_elementwise(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
+    value, out_t = eff.args
+    offsets = eff.attrs["offsets"]
+    if not isinstance(value, Tile):
+        return None
+
+    def leaf(tile: Any) -> Optional[GmView]:
+        v = resolve_view(tile) if _node(tile, "load") else None
+        if v is None or v.shape != value.shape or not _same_offsets(v.offsets, offsets):
+            return None
+        if v.tensor.static_shape() != out_t.static_shape():
+            return None
+        return v
+
+    top = _node(value, "binary", op="add")
+    if top is None:
+        return None
+    lhs, rhs = top.args
+    operands: List[GmView] = []
+    fn_name = None
+    if leaf(lhs) is not None and leaf(rhs) is not None:
+        operands = [leaf(lhs), leaf(rhs)]
+        fn_name = "asc_cuda_vadd_f32"
+    else:
+        for prod, addend in ((lhs, rhs), (rhs, lhs)):
+            m = _node(prod, "binary", op="mul")
+            if m is not None and leaf(m.args[0]) is not None and leaf(m.args[1]) is not None \
+                    and leaf(addend) is not None:
+                operands = [leaf(m.args[0]), leaf(m.args[1]), leaf(addend)]
+                fn_name = "asc_cuda_vmuladd_f32"
+                break
+    if fn_name is None:
+        return None
+    if value.dtype != KT.float32 or out_t.dtype != KT.float32 or any(v.tensor.dtype != KT.float32 for v in operands):
+        raise _unsupported(f"elementwise add / multiply-add on {value.dtype} tiles (float32 only)")
+    window = _flat_window(out_t, offsets, value.shape)
+    if window is None:
+        raise _unsupported("elementwise kernel whose tiles are not contiguous ranges of the tensor")
+    _check_fits(out_t)
+    for v in operands:
+        _check_fits(v.tensor)
+    flat_off, tile_elems = window
+    numel = 1
+    for d in out_t.static_shape():
+        numel *= d
+    env = enumerate_instances(trace.core_num, eff.loops)
+    n = env_count(env)
+    starts = eval_int(flat_off, env, n)
+    if starts.size and starts.min() < 0:
+        raise RuntimeError("Negative tile offset in kernel")
+    ends = np.minimum(starts + tile_elems, numel)
+    intervals = merge_intervals(starts, ends)
+    if len(intervals) > MAX_CALLS:
+        raise _unsupported("elementwise kernel touching more than 4096 disjoint ranges")
+
+    plan = Plan("elementwise:" + fn_name)
+    out_idx = out_t.base.index
+    in_idx = [v.tensor.base.index for v in operands]
+    plan.reads.update(in_idx)
+    plan.writes.add(out_idx)
+    for lo, hi in intervals:
+        def build(ptrs, stream, lo=lo, hi=hi):
+            args = [_p(ptrs[i] + 4 * lo) for i in in_idx]
+            return (*args, _p(ptrs[out_idx] + 4 * lo), ctypes.c_int64(hi - lo), stream)
+        plan.steps.append(Step(fn_name, build, f"[{lo}, {hi})"))
+    return plan
+
+
+# --------------------------------------------------------------------------------------------------
+# Pattern: row softmax (manual reduce_max / exp / reduce_sum form, and asc2.softmax)
+# --------------------------------------------------------------------------------------------------
+def _softmax_source(value: Tile) -> Optional[Tile]:
+    """The tile X such that ``value == softmax(X)`` over all of X's elements per row, or None."""
+    sm = _node(value, "softmax")
+    if sm is not None:
+        return sm.args[0]
+    div = _node(value, "binary", op="div")
+    if div is None:
+        return None
+    numer, denom = div.args
+    rs = _tile_scalar_node(denom, "reduce", kind="sum")
+    if rs is None or not isinstance(numer, Tile) or rs.args[0].node is not numer.node:
+        return None
+    ex = _node(numer, "unary", op="exp")
+    if ex is None:
+        return None
+    sub = _node(ex.args[0], "binary", op="sub")
+    if sub is None:
+        return None
+    row, mx = sub.args
+    rm = _tile_scalar_node(mx, "reduce", kind="max")
+    if rm is None or not isinstance(row, Tile) or rm.args[0].node is not row.node:
+        return None
+    # the no-axis reductions span the whole tile, so this equals a row softmax only for 1-row tiles
+    rows = 1
+    for d in row.shape[:-1]:
+        rows *= d
+    if rows != 1:
+        return None
+    return row
+
+
+def _match_softmax(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
+    value, out_t = eff.args
+    if not isinstance(value, Tile):
+        return None
+    src = _softmax_source(value)
+    if src is None:
+        return None
+    view = resolve_view(src) if _node(src, "load") else None
+    if view is None:
+        raise _unsupported("softmax of a tile that is not loaded directly from global memory")
+    if not _same_offsets(view.offsets, eff.attrs["offsets"]) or view.shape != value.shape:
+        raise _unsupported("softmax stored at a different position than it was loaded from")
+    if value.dtype != KT.float32 or out_t.dtype != KT.float32 or view.tensor.dtype != KT.float32:
+        raise _unsupported(f"softmax on {value.dtype} tiles (float32 only)")
+    if view.tensor.static_shape() != out_t.static_shape():
+        raise _unsupported("softmax between tensors of different shapes")
+    _check_fits(out_t)
+    _check_fits(view.tensor)
+    R, C = _row_major_2d(out_t)
+    tile_rows = 1 if len(value.shape) == 1 else value.shape[0]
+    tile_cols = value.shape[-1]
+    if len(value.shape) == 1:
+        row_off, col_off = PlainValue.const(0), view.offsets[0]
+    else:
+        row_off, col_off = view.offsets
+    env = enumerate_instances(trace.core_num, eff.loops)
+    n = env_count(env)
+    r0 = eval_int(row_off, env, n)
+    c0 = eval_int(col_off, env, n)
+    if n and (r0.min() < 0 or c0.min() < 0):
+        raise RuntimeError("Negative tile offset in kernel")
+    if n and not np.all(c0 == c0[0]):
+        raise _unsupported("softmax tiles at varying column offsets")
+    col0 = int(c0[0]) if n else 0
+    if col0 + tile_cols > C:
+        # the reference pads the load with zeros, which then take part in max and sum
+        raise _unsupported("softmax tile wider than the tensor row (zero padding would enter the softmax)")
+    intervals = merge_intervals(r0, np.minimum(r0 + tile_rows, R))
+    if len(intervals) > MAX_CALLS:
+        raise _unsupported("softmax kernel touching more than 4096 disjoint row ranges")
+    plan = Plan("softmax")
+    in_idx, out_idx = view.tensor.base.index, out_t.base.index
+    plan.reads.add(in_idx)
+    plan.writes.add(out_idx)
+    for lo, hi in intervals:
+        def build(ptrs, stream, lo=lo, hi=hi):
+            byte_off = 4 * (lo * C + col0)
+            return (_p(ptrs[in_idx] + byte_off), _p(ptrs[out_idx] + byte_off), ctypes.c_int64(hi - lo),
+                    ctypes.c_int64(tile_cols), ctypes.c_int64(C), stream)
+        plan.steps.append(Step("asc_cuda_softmax_f32", build, f"rows [{lo}, {hi}) x {tile_cols} cols"))
+    return plan
+
+
+# --------------------------------------------------------------------------------------------------
+# Pattern: matmul (+ K loop with matmul_acc) with a fused store epilogue
+# --------------------------------------------------------------------------------------------------
+class _Epilogue:
+    relu = False
+    out_dtype: Optional[DataType] = None
+    row_scale: Optional[GmView] = None   # int8 dequant: per-row scale vector
+    col_scale: Optional[GmView] = None   # int8 dequant: per-column scale vector
+
+
+def _peel_identity_copies(tile: Tile) -> Tile:
+    """Skip copies that keep shape and start at offset 0 (L0C -> L1 -> L0A round trips)."""
+    while isinstance(tile, Tile) and tile.node.kind == "copy":
+        node = tile.node
+        src = node.args[0]
+        if node.attrs["shape"] != src.shape or not all(o.is_const and o.value == 0 for o in node.attrs["offsets"]):
+            break
+        tile = src
+    return tile
+
+
+def _scale_vector(tile: Any, full_shape: Tuple[int, int]) -> Optional[Tuple[str, GmView]]:
+    """``tile`` is a 1-D load broadcast along rows or columns of ``full_shape``: ("row"|"col", view)."""
+    b = _node(tile, "broadcast")
+    if b is None or tile.shape != full_shape:
+        return None
+    src = b.args[0]
+    if not isinstance(src, Tile) or len(src.shape) != 2:
+        return None
+    kind = "row" if src.shape == (full_shape[0], 1) else "col" if src.shape == (1, full_shape[1]) else None
+    if kind is None:
+        return None
+    while isinstance(src, Tile) and src.node.kind == "reshape":
+        src = src.node.args[0]
+    view = resolve_view(src) if _node(src, "load") else None
+    if view is None or len(view.shape) != 1 or view.tensor.dtype != KT.float32:
+        return None
+    return kind, view
+
+
+def _strip_epilogue(value: Tile) -> Tuple[Tile, _Epilogue]:
+    epi = _Epilogue()
+    epi.out_dtype = value.dtype
+    v = value
+    for _ in range(3):  # cast and relu in either order
+        c = _node(v, "cast")
+        if c is not None:
+            v = c.args[0]
+            continue
+        r = _node(v, "unary", op="relu")
+        if r is not None:
+            epi.relu = True
+            v = r.args[0]
+            continue
+        break
+    # int8 dequantisation: cast_f32(acc) * row_scale * col_scale (either order)
+    m1 = _node(v, "binary", op="mul")
+    if m1 is not None and v.dtype == KT.float32 and len(v.shape) == 2:
+        found = {}
+        inner = None
+        lhs, rhs = m1.args
+        for first, second in ((lhs, rhs), (rhs, lhs)):
+            sv = _scale_vector(second, v.shape)
+            m2 = _node(first, "binary", op="mul")
+            if sv is None or m2 is None:
+                continue
+            for core, other in ((m2.args[0], m2.args[1]), (m2.args[1], m2.args[0])):
+                sv2 = _scale_vector(other, v.shape)
+                c = _node(core, "cast")
+                if sv2 is not None and c is not None and c.args[0].dtype == KT.int32 and sv2[0] != sv[0]:
+                    found = {sv[0]: sv[1], sv2[0]: sv2[1]}
+                    inner = c.args[0]
+                    outer_is_col = sv[0] == "col"
+            if inner is not None:
+                break
+        if inner is not None:
+            if not outer_is_col:
+                # (acc * b_scale) * a_scale rounds differently from (acc * a_scale) * b_scale
+                raise _unsupported("int8 dequantisation must be written as acc * a_scale[row] * b_scale[col]")
+            epi.row_scale, epi.col_scale = found["row"], found["col"]
+            v = inner
+    return v, epi
+
+
+def _product_terms(node: Node, store_loops: Tuple[Loop, ...]) -> Optional[List[Tuple[Tile, Tile, bool, Tuple[Loop, ...]]]]:
+    if node.kind == "matmul":
+        return [(node.args[0], node.args[1], node.attrs["trans_b"], ())]
+    if node.kind == "zeros_acc":
+        return []
+    if node.kind == "acc":
+        prev, a, b = node.args
+        head = _product_terms(prev, store_loops)
+        if head is None:
+            return None
+        red = tuple(l for l in node.loops if l not in store_loops)
+        return head + [(a, b, False, red)]
+    return None
+
+
+class _Window:
+    """Rows x cols window of a 2-D row-major tensor with symbolic row/col offsets."""
+
+    def __init__(self, tensor: Tensor, row: PlainValue, col: PlainValue, rows: int, cols: int):
+        self.tensor, self.row, self.col, self.rows, self.cols = tensor, row, col, rows, cols
+
+
+def _fake_tensor(key: str, shape: Tuple[int, int], dtype: DataType) -> Tensor:
+    from ..language.core.ir_value import GlobalAddress
+    base = GlobalAddress(key, dtype, key, shape[0] * shape[1])  # type: ignore[arg-type]
+    return Tensor(base, tuple(PlainValue.const(d) for d in shape))
+
+
+def _operand_window(trace: KernelTrace, tile: Tile, plan: Plan) -> _Window:
+    tile = _peel_identity_copies(tile)
+    view = resolve_view(tile)
+    if view is not None:
+        if len(view.shape) != 2 or len(view.tensor.static_shape()) != 2:
+            raise _unsupported("matmul operand that is not a 2-D tile of a 2-D tensor")
+        if not _is_zero_pad(view):
+            raise _unsupported("matmul operand loaded with a non-zero pad value")
+        _check_fits(view.tensor)
+        plan.reads.add(view.tensor.base.index)
+        return _Window(view.tensor, view.offsets[0], view.offsets[1], view.shape[0], view.shape[1])
+    # an operand computed on chip (chained matmul): materialise it in a temporary device buffer
+    key = f"tmp{len(plan.temps)}"
+    tmp = _fake_tensor(key, tile.shape, tile.dtype)
+    plan.temps[key] = tile.size * tile.dtype.sizeof()
+    zero = (PlainValue.const(0), PlainValue.const(0))
+    if not _plan_matmul_value(trace, tile, tmp, zero, (), plan):
+        raise _unsupported(f"matmul operand produced by '{tile.node.kind}'")
+    return _Window(tmp, zero[0], zero[1], tile.shape[0], tile.shape[1])
+
+
+def _merge_k_loop(a: _Window, b: _Window, red: Tuple[Loop, ...]) -> Tuple[_Window, _Window]:
+    """Fold a K loop ``for k: acc += A[:, f(k):f(k)+kt] @ B[f(k):f(k)+kt, :]`` into one product."""
+    if not red:
+        return a, b
+    if len(red) != 1:
+        raise _unsupported("matmul_acc inside more than one reduction loop")
+    loop = red[0]
+    if not (loop.start.is_const and loop.stop.is_const and loop.step.is_const):
+        raise _unsupported("K loop with run-time bounds")
+    ks = np.arange(int(loop.start.value), int(loop.stop.value), int(loop.step.value), dtype=np.int64)
+    if ks.size == 0:
+        raise _unsupported("empty K loop")
+    name = loop.name
+    if name in a.row.symbols() or name in b.col.symbols():
+        raise _unsupported("matmul_acc whose M or N offset changes inside the K loop")
+    if not a.col.symbols() <= {name} or not b.row.symbols() <= {name}:
+        raise _unsupported("K offset that depends on the block or an outer loop")
+    ak = np.sort(eval_int(a.col, {name: ks}, ks.size))
+    bk = np.sort(eval_int(b.row, {name: ks}, ks.size))
+    kt = a.cols
+    if b.rows != kt or not np.array_equal(ak, bk) or not np.array_equal(ak, ak[0] + kt * np.arange(ks.size)):
+        raise _unsupported("K loop whose slices do not tile the K dimension contiguously")
+    k_lo, k_tot = int(ak[0]), int(kt * ks.size)
+    return (_Window(a.tensor, a.row, PlainValue.const(k_lo), a.rows, k_tot),
+            _Window(b.tensor, PlainValue.const(k_lo), b.col, k_tot, b.cols))
+
+
+def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offsets: Sequence[PlainValue],
+                       loops: Tuple[Loop, ...], plan: Plan) -> bool:
+    """Append the steps computing ``value`` (a matmul with epilogue) into ``out_t`` at ``out_offsets``.
+    Returns False when ``value`` is not a matmul expression."""
+    if not isinstance(value, Tile) or len(value.shape) != 2:
+        return False
+    core, epi = _strip_epilogue(value)
+    terms = _product_terms(core.node, loops) if isinstance(core, Tile) else None
+    if terms is None:
+        return False
+    if len(terms) != 1:
+        raise _unsupported(f"accumulator fed by {len(terms)} matmul_acc calls (exactly one is supported)")
+    a_tile, b_tile, trans_b, red = terms[0]
+    if trans_b:
+        raise _unsupported("matmul with trans_b outside the attention pattern")
+    a_w, b_w = _merge_k_loop(_operand_window(trace, a_tile, plan), _operand_window(trace, b_tile, plan), red)
+    in_dtype = a_w.tensor.dtype
+    if b_w.tensor.dtype != in_dtype:
+        raise _unsupported("matmul operands of different types")
+    if len(out_t.static_shape()) != 2:
+        raise _unsupported("matmul result stored to a tensor that is not 2-D")
+    if epi.out_dtype != out_t.dtype:
+        raise _unsupported(f"storing a {epi.out_dtype} tile into a {out_t.dtype} tensor")
+    if (epi.row_scale is None) != (in_dtype != KT.int8 or epi.out_dtype == KT.int32):
+        raise _unsupported("int8 matmul must be stored as int32 or dequantised with row and column scales")
+    _check_fits(out_t)
+    mt, nt = value.shape
+    a_rows, a_cols = a_w.tensor.static_shape()
+    b_rows, b_cols = b_w.tensor.static_shape()
+    c_rows, c_cols = out_t.static_shape()
+
+    env = enumerate_instances(trace.core_num, loops)
+    n = env_count(env)
+    ro, co = eval_int(out_offsets[0], env, n), eval_int(out_offsets[1], env, n)
+    ar, ak = eval_int(a_w.row, env, n), eval_int(a_w.col, env, n)
+    bk, bc = eval_int(b_w.row, env, n), eval_int(b_w.col, env, n)
+    cols = [ro, co, ar, ak, bk, bc]
+    if epi.row_scale is not None:
+        cols += [eval_int(epi.row_scale.offsets[0], env, n), eval_int(epi.col_scale.offsets[0], env, n)]
+    inst = np.unique(np.stack(cols, axis=1), axis=0)   # identical instances (e.g. every block) collapse
+    if inst.size and inst.min() < 0:
+        raise RuntimeError("Negative tile offset in kernel")
+    ro, co, ar, ak, bk, bc = (inst[:, i] for i in range(6))
+    if np.any(ak != bk):
+        raise _unsupported("A and B operands read different K ranges")
+    if epi.row_scale is not None and (np.any(inst[:, 6] != ar) or np.any(inst[:, 7] != bc)
+                                      or epi.row_scale.shape[0] != mt or epi.col_scale.shape[0] != nt):
+        raise _unsupported("dequantisation scales that are not indexed by the tile's rows / columns")
+    k_eff = np.minimum(np.minimum(a_w.cols, a_cols - ak), b_rows - bk)
+    m_eff = np.minimum(mt, c_rows - ro)
+    n_eff = np.minimum(nt, c_cols - co)
+    if np.any(k_eff <= 0):
+        raise _unsupported("matmul tile outside the K extent of its operands")
+    if np.any(a_rows - ar < m_eff) or np.any(b_cols - bc < n_eff):
+        raise _unsupported("matmul tile that reads padded rows of A or padded columns of B")
+    keep = (m_eff > 0) & (n_eff > 0)
+
+    # one call when the tiles form a full grid over a rectangle, else one call per tile
+    calls: List[Tuple[int, ...]] = []   # (ro, co, ar, bc, k0, M, N, K)
+    ru, cu = np.unique(ro[keep]), np.unique(co[keep])
+    grid_ok = (keep.all() and inst.shape[0] == ru.size * cu.size and np.all(ak == ak[0]) and
+               np.all(k_eff == k_eff[0]) and np.all(ar - ro == ar[0] - ro[0]) and np.all(bc - co == bc[0] - co[0]) and
+               np.array_equal(ru, ru[0] + mt * np.arange(ru.size)) and
+               np.array_equal(cu, cu[0] + nt * np.arange(cu.size)) and
+               np.unique(np.stack([ro, co], axis=1), axis=0).shape[0] == inst.shape[0])
+    if inst.shape[0] and grid_ok:
+        M = int(min(ru[-1] + mt, c_rows) - ru[0])
+        N = int(min(cu[-1] + nt, c_cols) - cu[0])
+        calls.append((int(ru[0]), int(cu[0]), int(ru[0] + ar[0] - ro[0]), int(cu[0] + bc[0] - co[0]), int(ak[0]),
+                      M, N, int(k_eff[0])))
+    else:
+        for i in np.nonzero(keep)[0]:
+            calls.append((int(ro[i]), int(co[i]), int(ar[i]), int(bc[i]), int(ak[i]), int(m_eff[i]), int(n_eff[i]),
+                          int(k_eff[i])))
+        if len(calls) > MAX_CALLS:
+            raise _unsupported("matmul kernel whose tiles do not form a grid and exceed 4096 calls")
+
+    a_idx, b_idx, c_idx = a_w.tensor.base.index, b_w.tensor.base.index, out_t.base.index
+    plan.writes.add(c_idx)
+    es = in_dtype.sizeof()
+    osz = out_t.dtype.sizeof()
+    lda, ldb, ldc = a_cols, b_cols, c_cols
+    flags = 1 if epi.relu else 0
+    for (r0, c0, a0, b0, k0, M, N, K) in calls:
+        a_off, b_off, c_off = (a0 * lda + k0) * es, (k0 * ldb + b0) * es, (r0 * ldc + c0) * osz
+        dims = (ctypes.c_int64(M), ctypes.c_int64(N), ctypes.c_int64(K), ctypes.c_int64(lda), ctypes.c_int64(ldb),
+                ctypes.c_int64(ldc))
+        note = f"C[{r0}:{r0 + M}, {c0}:{c0 + N}] = A[{a0}:, {k0}:{k0 + K}] @ B[{k0}:, {b0}:]"
+        if in_dtype == KT.int8:
+            if epi.relu:
+                raise _unsupported("ReLU on an int8 matmul")
+            if epi.row_scale is not None:
+                if out_t.dtype != KT.float16:
+                    raise _unsupported("dequantised int8 matmul must be stored as float16")
+                sa_idx, sb_idx = epi.row_scale.tensor.base.index, epi.col_scale.tensor.base.index
+                plan.reads.update((sa_idx, sb_idx))
+
+                def build(ptrs, stream, a_off=a_off, b_off=b_off, c_off=c_off, dims=dims, a0=a0, b0=b0,
+                          sa_idx=sa_idx, sb_idx=sb_idx):
+                    return (_p(ptrs[a_idx] + a_off), _p(ptrs[b_idx] + b_off), None, _p(ptrs[c_idx] + c_off),
+                            _p(ptrs[sa_idx] + 4 * a0), _p(ptrs[sb_idx] + 4 * b0), *dims, stream)
+            else:
+                def build(ptrs, stream, a_off=a_off, b_off=b_off, c_off=c_off, dims=dims):
+                    return (_p(ptrs[a_idx] + a_off), _p(ptrs[b_idx] + b_off), _p(ptrs[c_idx] + c_off), None, None,
+                            None, *dims, stream)
+            plan.steps.append(Step("asc_cuda_gemm_i8", build, note))
+        elif in_dtype == KT.float32:
+            if out_t.dtype.name not in _OUT_CODE:
+                raise _unsupported(f"matmul result type {out_t.dtype}")
+            oc = _OUT_CODE[out_t.dtype.name]
+
+            def build(ptrs, stream, a_off=a_off, b_off=b_off, c_off=c_off, dims=dims, oc=oc):
+                return (_p(ptrs[a_idx] + a_off), _p(ptrs[b_idx] + b_off), _p(ptrs[c_idx] + c_off), *dims,
+                        ctypes.c_int32(oc), ctypes.c_int32(flags), stream)
+            plan.steps.append(Step("asc_cuda_gemm_f32", build, note))
+        elif in_dtype.name in _DTYPE_CODE_16:
+            if out_t.dtype.name not in _OUT_CODE:
+                raise _unsupported(f"matmul result type {out_t.dtype}")
+            ic, oc = _DTYPE_CODE_16[in_dtype.name], _OUT_CODE[out_t.dtype.name]
+
+            def build(ptrs, stream, a_off=a_off, b_off=b_off, c_off=c_off, dims=dims, ic=ic, oc=oc):
+                return (_p(ptrs[a_idx] + a_off), _p(ptrs[b_idx] + b_off), _p(ptrs[c_idx] + c_off), *dims,
+                        ctypes.c_int32(ic), ctypes.c_int32(oc), ctypes.c_int32(flags), stream)
+            plan.steps.append(Step("asc_cuda_gemm_f16", build, note))
+        else:
+            raise _unsupported(f"matmul on {in_dtype} operands")
+    return True
+
+
+def _match_matmul(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
+    value, out_t = eff.args
+    plan = Plan("matmul")
+    if not _plan_matmul_value(trace, value, out_t, eff.attrs["offsets"], eff.loops, plan):
+        return None
+    return plan
+
+
+# --------------------------------------------------------------------------------------------------
+# Pattern: attention forward, written per query tile as softmax(scale * Q K^T [+ causal mask]) V
+# --------------------------------------------------------------------------------------------------
+def _match_attention(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
+    value, out_t = eff.args
+    if not isinstance(value, Tile) or len(value.shape) != 2:
+        return None
+    v = value
+    c = _node(v, "cast")
+    if c is not None:
+        v = c.args[0]
+    pv = _node(v, "matmul", trans_b=False)
+    if pv is None:
+        return None
+    p_tile, v_tile = pv.args
+    pc = _node(p_tile, "cast")
+    sm = _node(pc.args[0] if pc is not None else p_tile, "softmax")
+    if sm is None:
+        return None
+    s_tile = sm.args[0]
+    causal = False
+    q_off = kv_off = None
+    cm = _node(s_tile, "causal_mask")
+    if cm is not None:
+        causal = True
+        q_off, kv_off = cm.attrs["q_offset"], cm.attrs["kv_offset"]
+        s_tile = cm.args[0]
+    mul = _node(s_tile, "binary", op="mul")
+    if mul is None:
+        raise _unsupported("attention scores must be scaled as (q @ k^T) * scale")
+    qk = scale = None
+    for x, y in ((mul.args[0], mul.args[1]), (mul.args[1], mul.args[0])):
+        if _node(x, "matmul", trans_b=True) is not None and isinstance(y, PlainValue) and y.is_const:
+            qk, scale = x.node, float(y.value)
+    if qk is None:
+        raise _unsupported("attention scores must be asc2.matmul(q, k, trans_b=True) times a constant scale")
+    q_tile, k_tile = qk.args
+    views = [resolve_view(t) if _node(t, "load") else None for t in (q_tile, k_tile, v_tile)]
+    if any(x is None for x in views):
+        raise _unsupported("attention operands must be loaded directly from global memory")
+    qv, kv, vv = views
+    dt = qv.tensor.dtype
+    if dt.name not in _DTYPE_CODE_16 or kv.tensor.dtype != dt or vv.tensor.dtype != dt or out_t.dtype != dt \
+            or value.dtype != dt:
+        raise _unsupported("attention needs float16 or bfloat16 Q, K, V and O of one type")
+    for t in (qv.tensor, kv.tensor, vv.tensor, out_t):
+        _check_fits(t)
+        if len(t.static_shape()) != 2:
+            raise _unsupported("attention tensors must be viewed as [batch*heads*seq, head_dim]")
+    rows, D = out_t.static_shape()
+    tq = qv.shape[0]
+    S = kv.shape[0]
+    if any(t.static_shape() != (rows, D) for t in (qv.tensor, kv.tensor, vv.tensor)):
+        raise _unsupported("attention Q, K, V, O must have the same [rows, head_dim] shape")
+    if qv.shape[1] != D or kv.shape != (S, D) or vv.shape != (S, D) or rows % S != 0 or S % tq != 0:
+        raise _unsupported("attention tiles must span the head dimension, K/V tiles one whole sequence")
+    env = enumerate_instances(trace.core_num, eff.loops)
+    n = env_count(env)
+    row0 = eval_int(eff.attrs["offsets"][0], env, n)
+    checks = [
+        np.array_equal(np.sort(row0), np.arange(0, rows, tq)),
+        np.array_equal(eval_int(qv.offsets[0], env, n), row0),
+        np.array_equal(eval_int(kv.offsets[0], env, n), (row0 // S) * S),
+        np.array_equal(eval_int(vv.offsets[0], env, n), (row0 // S) * S),
+        all(not np.any(eval_int(x.offsets[1], env, n)) for x in (qv, kv, vv)),
+        not np.any(eval_int(eff.attrs["offsets"][1], env, n)),
+    ]
+    if causal:
+        checks.append(np.array_equal(eval_int(q_off, env, n), row0 % S))
+        checks.append(not np.any(eval_int(kv_off, env, n)))
+    if not all(checks):
+        raise _unsupported("attention kernel whose tiles do not cover every query tile of every head exactly once")
+    plan = Plan("attention")
+    idx = [t.base.index for t in (qv.tensor, kv.tensor, vv.tensor, out_t)]
+    plan.reads.update(idx[:3])
+    plan.writes.add(idx[3])
+    heads = rows // S
+
+    def build(ptrs, stream):
+        return (_p(ptrs[idx[0]]), _p(ptrs[idx[1]]), _p(ptrs[idx[2]]), _p(ptrs[idx[3]]), ctypes.c_int32(heads),
+                ctypes.c_int32(1), ctypes.c_int32(S), ctypes.c_int32(D), ctypes.c_float(scale),
+                ctypes.c_int32(int(causal)), ctypes.c_int32(_DTYPE_CODE_16[dt.name]), stream)
+    plan.steps.append(Step("asc_cuda_attn_fwd_f16", build, f"{heads} heads x {S} x {D}, causal={causal}"))
+    return plan
+
+
+# --------------------------------------------------------------------------------------------------
+# Entry point
+# --------------------------------------------------------------------------------------------------
+_MATCHERS = (_match_attention, _match_softmax, _match_elementwise, _match_matmul)
+
+
+def build_plan(trace: KernelTrace) -> Plan:
+    """The C-ABI calls that reproduce the traced kernel's effect on global memory."""
+    stores = [e for e in trace.effects if e.kind == "store"]
+    others = [e for e in trace.effects if e.kind not in ("store", "matmul_acc")]
+    if others:
+        raise _unsupported(f"'{others[0].kind}' side effect")
+    if not stores:
+        raise _unsupported("kernel without a tile store")
+    total = Plan("")
+    names = []
+    for eff in stores:
+        plan = None
+        for matcher in _MATCHERS:
+            plan = matcher(trace, eff)
+            if plan is not None:
+                break
+        if plan is None:
+            value = eff.args[0]
+            kind = value.node.kind if isinstance(value, Tile) else type(value).__name__
+            raise _unsupported(f"store of a tile produced by '{kind}' in kernel '{trace.fn_name}'")
+        names.append(plan.pattern)
+        total.steps += plan.steps
+        total.reads |= plan.reads
+        total.writes |= plan.writes
+        for k, v in plan.temps.items():
+            if k in total.temps:
+                raise _unsupported("several stores that each need temporary buffers")
+            total.temps[k] = v
+    total.pattern = "+".join(names)
+    total.reads = {i for i in total.reads if isinstance(i, int)}
+    total.writes = {i for i in total.writes if isinstance(i, int)}
+    return total

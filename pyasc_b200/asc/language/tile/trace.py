@@ -1,0 +1,126 @@
+"""Recording context of the CUDA platform's kernel tracer.
+
+The reference walks the kernel's AST and emits one ``asctile`` MLIR op per asc2 call
+(python/asc/codegen/function_visitor.py:463-583; ops in
+include/ascir/Dialect/AscTile/IR/Ops.td:28-394).  Here the kernel function itself is executed once
+with proxy arguments: every asc2 call appends a :class:`Node` to the active :class:`TraceContext`,
+``asc2.range`` loops run their body once with a symbolic induction variable, and stores /
+accumulations are kept as an ordered effect list.  The result carries the same information as the
+reference's recorded IR and is what the launcher pattern-matches against the CUDA kernels.
+"""
+from __future__ import annotations
+
+import itertools
+from typing import Any, List, Optional, Tuple
+
+from ..core.ir_value import PlainValue
+
+_current: Optional["TraceContext"] = None
+
+
+class Loop:
+    """One ``for`` over ``asc2.range``: ``var`` takes start, start+step, ... < stop."""
+
+    __slots__ = ("var", "start", "stop", "step", "unroll_factor", "parallel")
+
+    def __init__(self, var: PlainValue, start, stop, step, unroll_factor: int, parallel: bool):
+        self.var = var
+        self.start = PlainValue.wrap(start)
+        self.stop = PlainValue.wrap(stop)
+        self.step = PlainValue.wrap(step)
+        self.unroll_factor = unroll_factor
+        self.parallel = parallel
+
+    @property
+    def name(self) -> str:
+        return self.var.args[0]
+
+    def __repr__(self) -> str:
+        return f"for %{self.name} in range({self.start!r}, {self.stop!r}, {self.step!r})"
+
+
+class Node:
+    """One recorded tile operation."""
+
+    __slots__ = ("kind", "args", "attrs", "loops", "uid")
+    _ids = itertools.count()
+
+    def __init__(self, kind: str, args: Tuple[Any, ...] = (), attrs: Optional[dict] = None,
+                 loops: Tuple[Loop, ...] = ()):
+        self.kind = kind
+        self.args = args
+        self.attrs = attrs or {}
+        self.loops = loops
+        self.uid = next(Node._ids)
+
+    def __repr__(self) -> str:
+        return f"Node#{self.uid}({self.kind}, attrs={self.attrs})"
+
+
+class Effect:
+    """A side effect in program order: ``store``, ``matmul_acc`` or ``atomic``."""
+
+    __slots__ = ("kind", "args", "attrs", "loops")
+
+    def __init__(self, kind: str, args: Tuple[Any, ...], attrs: dict, loops: Tuple[Loop, ...]):
+        self.kind = kind
+        self.args = args
+        self.attrs = attrs
+        self.loops = loops
+
+    def __repr__(self) -> str:
+        return f"Effect({self.kind}, {self.attrs}, loops={list(self.loops)})"
+
+
+class TraceContext:
+
+    def __init__(self, fn_name: str, core_num: int):
+        self.fn_name = fn_name
+        self.core_num = core_num
+        self.block_idx = PlainValue.sym("block_idx")
+        self.loops: List[Loop] = []
+        self.effects: List[Effect] = []
+        self.tensors: List[Any] = []
+        self._loop_ids = itertools.count()
+
+    # -- loops ------------------------------------------------------------------------------------
+    def push_loop(self, start, stop, step, unroll_factor: int, parallel: bool) -> Loop:
+        var = PlainValue.sym(f"i{next(self._loop_ids)}")
+        loop = Loop(var, start, stop, step, unroll_factor, parallel)
+        self.loops.append(loop)
+        return loop
+
+    def pop_loop(self, loop: Loop) -> None:
+        assert self.loops and self.loops[-1] is loop
+        self.loops.pop()
+
+    def loop_nest(self) -> Tuple[Loop, ...]:
+        return tuple(self.loops)
+
+    # -- recording --------------------------------------------------------------------------------
+    def node(self, _kind: str, /, *args, **attrs) -> Node:
+        return Node(_kind, args, attrs, self.loop_nest())
+
+    def effect(self, _kind: str, /, *args, **attrs) -> None:
+        self.effects.append(Effect(_kind, args, attrs, self.loop_nest()))
+
+    def __enter__(self) -> "TraceContext":
+        global _current
+        if _current is not None:
+            raise RuntimeError("Nested kernel tracing is not supported")
+        _current = self
+        return self
+
+    def __exit__(self, *exc) -> None:
+        global _current
+        _current = None
+
+
+def current() -> TraceContext:
+    if _current is None:
+        raise RuntimeError("asc2 operations can only be used inside a function decorated with @asc2.jit")
+    return _current
+
+
+def is_tracing() -> bool:
+    return _current is not None

@@ -1,0 +1,177 @@
+"""``JITFunction``: what ``@asc2.jit`` returns (reference: python/asc/runtime/jit.py:33-223).
+
+Same call shape as the reference — ``kernel[core_num](...)`` or ``kernel[core_num, stream](...)``,
+option keywords from the three option dataclasses accepted at decoration and call time, ConstExpr
+parameters split from run-time ones — but the body behind ``_run`` is: trace the kernel once
+(:mod:`asc.codegen.tracer`), match it to CUDA kernels (:mod:`asc.codegen.matcher`), launch
+(:mod:`asc.runtime.launcher`).  Plans are cached per (options, ConstExpr values, argument kinds and
+shapes, scalar values, core_num); ``always_compile=True`` re-traces on every call.
+"""
+from __future__ import annotations
+
+import inspect
+from dataclasses import fields
+from typing import Any, Callable, Dict, List, Optional, Tuple, Type, Union
+
+import numpy as np
+
+from ..codegen.function import Function, P, T, get_annotations
+from ..codegen.matcher import Plan, build_plan
+from ..codegen.tracer import trace_kernel
+from ..language.core.dtype import DataType, KnownTypes as KT
+from ..language.tile.range import range as asc2_range
+from .launcher import Launcher
+from .options import CodegenOptions, CompileOptions, LaunchOptions
+
+
+class PlainArgType:
+
+    def __init__(self, dtype: DataType):
+        self.dtype = dtype
+
+
+class PointerArgType:
+
+    def __init__(self, dtype: DataType):
+        self.dtype = dtype
+
+
+class JITFunction(Function[P, T]):
+    launcher: Type[Launcher] = Launcher
+
+    def __init__(self, fn: Callable[P, T], **options):
+        super().__init__(fn)
+        clashed_args = self.get_clashed_args(fn)
+        if clashed_args:
+            raise RuntimeError("The following argument names conflict with JIT configuration options: " +
+                               ", ".join(clashed_args))
+        unknown_options = set(options).difference(self.get_config_keywords())
+        if unknown_options:
+            raise RuntimeError("The following option names are unknown: " + ", ".join(unknown_options))
+        self.default_options: Dict[str, Any] = options
+        self.launch_options = LaunchOptions()
+        self.kernel_cache: Dict[Any, Plan] = {}
+        self.last_plan: Optional[Plan] = None
+
+    def __getitem__(self, user_launch_options: Union[int, tuple]) -> Callable:
+        try:
+            if isinstance(user_launch_options, int):
+                self.launch_options = LaunchOptions(core_num=user_launch_options)
+            else:
+                self.launch_options = LaunchOptions(*user_launch_options)
+        except Exception as e:
+            raise TypeError("Parse user launch options failed") from e
+        else:
+            return self._run
+
+    @staticmethod
+    def get_clashed_args(fn: Callable) -> List[str]:
+        keywords = set(__class__.get_config_keywords())
+        keywords.intersection_update(inspect.signature(fn).parameters)
+        return list(keywords)
+
+    @staticmethod
+    def get_arg_type(value: Any):
+        """Argument kind (reference: jit.py:70-96)."""
+        if isinstance(value, bool):
+            return PlainArgType(KT.bool_)
+        if isinstance(value, int):
+            return PlainArgType(KT.int_)
+        if isinstance(value, float):
+            return PlainArgType(KT.float_)
+        if isinstance(value, np.ndarray):
+            return PointerArgType(DataType(str(np.dtype(value.dtype))))
+        if isinstance(value, np.generic):
+            return PlainArgType(DataType(str(value.dtype)))
+        try:
+            import torch
+            if isinstance(value, torch.Tensor):
+                dtype = DataType(str(value.dtype))
+                return PlainArgType(dtype) if value.dim() == 0 else PointerArgType(dtype)
+        except ModuleNotFoundError:
+            pass
+        raise TypeError(f"Argument type in JIT function is not supported: {value.__class__.__name__}")
+
+    @staticmethod
+    def extract_kwargs(dataclass: Type, base_kwargs: Dict[str, Any]) -> Any:
+        kwargs = {}
+        for f in fields(dataclass):
+            if f.name in base_kwargs:
+                kwargs[f.name] = base_kwargs.pop(f.name)
+        return dataclass(**kwargs)
+
+    @classmethod
+    def get_config_keywords(cls) -> List[str]:
+        cached = getattr(cls, "_config_keywords", None)
+        if cached is not None:
+            return cached
+        keywords: List[str] = []
+        for dataclass in CodegenOptions, CompileOptions, LaunchOptions:
+            keywords.extend(f.name for f in fields(dataclass))
+        cls._config_keywords = keywords
+        return keywords
+
+    @staticmethod
+    def _arg_signature(value: Any) -> Tuple:
+        """What about a run-time argument shapes the plan: kind, dtype, element count, scalar value."""
+        if isinstance(value, (bool, int, float)):
+            return ("s", type(value).__name__, value)
+        if isinstance(value, np.generic):
+            return ("s", str(value.dtype), value.item())
+        if isinstance(value, np.ndarray):
+            return ("p", str(value.dtype), int(value.size))
+        try:
+            import torch
+            if isinstance(value, torch.Tensor):
+                if value.dim() == 0:
+                    return ("s", str(value.dtype), value.item())
+                return ("p", str(value.dtype), int(value.numel()))
+        except ModuleNotFoundError:
+            pass
+        raise TypeError(f"Argument type in JIT function is not supported: {value.__class__.__name__}")
+
+    def _cache_kernel(self, runtime_args: Dict[str, Any], constexprs: Dict[str, Any], codegen_options: CodegenOptions,
+                      compile_options: CompileOptions) -> Plan:
+        for value in runtime_args.values():
+            self.get_arg_type(value)  # TypeError for unsupported arguments, as in the reference
+        try:
+            key = (self.launch_options.core_num, tuple((k, repr(v)) for k, v in constexprs.items()),
+                   tuple((k, ) + self._arg_signature(v) for k, v in runtime_args.items()))
+            hash(key)
+        except TypeError:
+            raise
+        enable_cache = not compile_options.always_compile
+        if enable_cache and key in self.kernel_cache:
+            return self.kernel_cache[key]
+        builtins = dict(codegen_options.custom_builtins) or {"range": asc2_range}
+        trace = trace_kernel(self.fn, runtime_args, constexprs, self.launch_options.core_num, builtins)
+        plan = build_plan(trace)
+        if enable_cache:
+            self.kernel_cache[key] = plan
+        return plan
+
+    def _run(self, *args: P.args, **kwargs: P.kwargs) -> None:
+        merged = dict(self.default_options)
+        merged.update(kwargs)
+        codegen_options = self.extract_kwargs(CodegenOptions, merged)
+        compile_options = self.extract_kwargs(CompileOptions, merged)
+        if self.launch_options.core_num <= 0:
+            raise ValueError("Core number should be large than 0")
+        call_args = inspect.signature(self.fn).bind(*args, **merged).arguments
+        runtime_args, constexprs = self.split_args(call_args, get_annotations(self.fn))
+        plan = self._cache_kernel(runtime_args, constexprs, codegen_options, compile_options)
+        self.last_plan = plan
+        self.launcher(self.launch_options).run(plan, self.fn_name, tuple(runtime_args.values()))
+
+
+def jit(fn: Optional[Callable[P, T]] = None, **options):
+    """``asc.jit``: decorator form with or without options (reference: jit.py:240-249)."""
+    from ..language.tile.range import range as default_range
+    options.setdefault("custom_builtins", {"range": default_range})
+
+    def decorator(fn: Callable[P, T]) -> JITFunction[P, T]:
+        return JITFunction(fn, **options)
+
+    if fn is None:
+        return decorator
+    return decorator(fn)

@@ -1,0 +1,106 @@
+"""Runs a matched kernel plan on the device (reference: python/asc/runtime/launcher.py:80-238).
+
+Argument handling follows the reference launcher: host tensors (NumPy / torch CPU) get device
+mirrors for the duration of the call and are copied back afterwards, device tensors pass through
+untouched, and the call returns only after the stream has drained, so results are visible to the
+caller on return.  Differences, all invisible in results: only arguments the kernel reads are
+uploaded and only arguments it writes are copied back (the reference moves every argument both
+ways, launcher.py:176-195); device mirrors come from a pool instead of malloc/free per call; and
+when the caller passes its own stream (``kernel[cores, stream]``) and every argument already
+lives on the device, the launch is left asynchronous on that stream.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Any, Dict, Iterable, List, Optional, Tuple
+
+import numpy as np
+
+from ..codegen.matcher import Plan
+from ..lib import runtime as rt
+from .memory_handle import MemoryHandle, TorchCudaTensorArgument, _HostMirror, resolve_memory_handle
+from .options import LaunchOptions
+
+
+def _torch_current_stream() -> Optional[ctypes.c_void_p]:
+    try:
+        import torch
+        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    except Exception:
+        return None
+
+
+class Launcher:
+
+    def __init__(self, options: LaunchOptions):
+        self.options = options
+
+    @staticmethod
+    def get_core_num(device_id: Optional[int] = None) -> int:
+        return rt.device_info(rt.DeviceModuleType.RT_MODULE_TYPE_AICORE, rt.DeviceInfoType.INFO_TYPE_CORE_NUM,
+                              device_id)
+
+    @staticmethod
+    def is_scalar(value: Any) -> bool:
+        if isinstance(value, (bool, int, float, np.generic)):
+            return True
+        try:
+            import torch
+            return isinstance(value, torch.Tensor) and value.dim() == 0
+        except ModuleNotFoundError:
+            return False
+
+    def run(self, plan: Plan, function_name: str, user_args: Tuple[Any, ...]) -> None:
+        if self.options.core_num <= 0:
+            raise ValueError("Core number should be large than 0")
+        if os.environ.get("DRY_RUN"):
+            return
+        handles: Dict[int, MemoryHandle] = {}
+        for index, arg in enumerate(user_args):
+            if self.is_scalar(arg):
+                continue
+            try:
+                handles[index] = resolve_memory_handle(arg)
+            except RuntimeError as e:
+                raise TypeError(f"Unsupported kernel argument of type {type(arg)}") from e
+        all_on_device = all(isinstance(h, TorchCudaTensorArgument) for h in handles.values())
+        user_stream = self.options.stream
+        if user_stream is not None:
+            stream = user_stream if isinstance(user_stream, ctypes.c_void_p) else ctypes.c_void_p(int(user_stream))
+        elif any(isinstance(h, TorchCudaTensorArgument) for h in handles.values()):
+            # stay ordered with the torch work that produced / will consume the device tensors
+            stream = _torch_current_stream() or rt.current_stream()
+        else:
+            stream = rt.current_stream()
+
+        ptrs: Dict[Any, int] = {}
+        temps: List[ctypes.c_void_p] = []
+        try:
+            for index, handle in handles.items():
+                if isinstance(handle, _HostMirror) and index not in plan.reads:
+                    ptrs[index] = handle.device_alloc_only()
+                else:
+                    ptrs[index] = handle.copy_to_device(stream)
+            for key, nbytes in plan.temps.items():
+                mem = rt.malloc(nbytes)
+                temps.append(mem)
+                ptrs[key] = int(mem.value)
+            for step in plan.steps:
+                rt.state.lib.call(step.fn_name, *step.build(ptrs, stream))
+            for index, handle in handles.items():
+                if index in plan.writes:
+                    handle.copy_from_device(stream)
+            if not (all_on_device and user_stream is not None):
+                rt.check_device_status(stream)
+        finally:
+            if temps or not all_on_device:
+                # buffers go back to the pool only once nothing on the stream can still touch them
+                try:
+                    rt.synchronize(stream)
+                except RuntimeError:
+                    pass
+            for handle in handles.values():
+                handle.release_memory()
+            for mem in temps:
+                rt.free(mem)
