@@ -1,0 +1,36 @@
+/*
+ * Tuning and bring-up hooks of libasc_cuda.  Not part of the drop-in boundary: the Python runtime
+ * never calls them; they exist so that variants of a kernel can be timed against each other from a
+ * script.  No counterpart in the reference.
+ */
+#ifndef ASC_CUDA_TUNING_H_
+#define ASC_CUDA_TUNING_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* variant: bits 0-3 vectors per thread (1, 2, 4, 8; 0 = default), bits 8-15 CTAs per SM for a
+ * grid-stride launch (0 = one chunk per CTA). */
+int32_t asc_cuda_vadd_f32_variant(const float* x, const float* y, float* out, int64_t n, int32_t variant,
+                                  void* stream);
+
+/* variant: bits 0-7 CTA shape for 2048 < cols <= 4096 (0: 256 threads x 4 vectors, 1: 128 x 8,
+ * 2: 512 x 2, 0xff: the shared-memory staged kernel), bits 8-15 CTAs per SM (0 = default). */
+int32_t asc_cuda_softmax_f32_variant(const float* x, float* out, int64_t rows, int64_t cols, int64_t ld,
+                                     int32_t variant, void* stream);
+
+/* GEMM with a cap on the number of CTAs.  in_dtype: 0 fp16, 1 bf16, 2 int8 (int32 output);
+ * out_dtype as asc_cuda_gemm_f16 (ignored for int8); max_ctas 0 = one per SM. */
+int32_t asc_cuda_gemm_debug(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                            int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype, uint32_t a_sbo,
+                            uint32_t a_kstep, uint32_t b_lbo, uint32_t b_sbo, uint32_t b_kstep, int32_t max_ctas,
+                            void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* ASC_CUDA_TUNING_H_ */

@@ -1,0 +1,121 @@
+"""asc2 kernels in the forms the reference's kernel tests exercise
+(python/test/asc2/kernels/test_{vadd,vmuladd,softmax,softmax_fused,matmul_tiled,matmul_mnblock,
+matmul_fixpipe,matmul_l0c_to_l1}.py), used by the CPU matcher tests and the GPU parity tests.
+Written against the public asc / asc2 names only, exactly as a user script would be."""
+import asc
+import asc2
+
+L0A, L0B, L1 = asc2.TileLocation.L0A, asc2.TileLocation.L0B, asc2.TileLocation.L1
+
+
+@asc2.jit(always_compile=True)
+def vadd(x_ptr: asc.GlobalAddress, y_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, size: int,
+         tile_size: asc.ConstExpr[int], tile_per_block: asc.ConstExpr[int]):
+    x_gm, y_gm, out_gm = (asc2.tensor(p, [size]) for p in (x_ptr, y_ptr, out_ptr))
+    first = asc2.block_idx() * tile_size * tile_per_block
+    for i in range(tile_per_block):
+        off = first + i * tile_size
+        asc2.store(asc2.load(x_gm, [tile_size], offsets=[off]) + asc2.load(y_gm, [tile_size], offsets=[off]),
+                   out_gm, offsets=[off])
+
+
+@asc2.jit(always_compile=True, vf_fusion=True)
+def vmuladd(x_ptr: asc.GlobalAddress, y_ptr: asc.GlobalAddress, z_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress,
+            size: int, tile_size: asc.ConstExpr[int], tile_per_block: asc.ConstExpr[int],
+            buffer_factor: asc.ConstExpr[int]):
+    x_gm, y_gm, z_gm, out_gm = (asc2.tensor(p, [size]) for p in (x_ptr, y_ptr, z_ptr, out_ptr))
+    first = asc2.block_idx() * tile_size * tile_per_block
+    for i in range(tile_per_block, unroll_factor=buffer_factor, parallel=True):
+        off = first + i * tile_size
+        x = asc2.load(x_gm, [tile_size], offsets=[off])
+        y = asc2.load(y_gm, [tile_size], offsets=[off])
+        z = asc2.load(z_gm, [tile_size], offsets=[off])
+        asc2.store(x * y + z, out_gm, offsets=[off])
+
+
+@asc2.jit(always_compile=True, vf_fusion=True)
+def softmax_rows(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, num_rows: int, num_cols: int,
+                 tile_size: asc.ConstExpr[int]):
+    x_gm = asc2.tensor(x_ptr, [num_rows, num_cols])
+    out_gm = asc2.tensor(out_ptr, [num_rows, num_cols])
+    for i in range(asc2.block_idx(), num_rows, asc2.block_num(), parallel=True):
+        row = asc2.load(x_gm, [1, tile_size], offsets=[i, 0])
+        shifted = row - asc2.reduce_max(row)
+        e = asc2.exp(shifted)
+        asc2.store(e / asc2.reduce_sum(e), out_gm, offsets=[i, 0])
+
+
+@asc2.jit(always_compile=True)
+def softmax_blocks(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, num_rows: int, num_cols: asc.ConstExpr[int],
+                   block_size: asc.ConstExpr[int]):
+    x_gm = asc2.tensor(x_ptr, [num_rows, num_cols])
+    out_gm = asc2.tensor(out_ptr, [num_rows, num_cols])
+    r0 = asc2.block_idx() * block_size
+    asc2.store(asc2.softmax(asc2.load(x_gm, [block_size, num_cols], offsets=[r0, 0])), out_gm, offsets=[r0, 0])
+
+
+@asc2.jit(always_compile=True)
+def matmul_k_tiled(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, c_ptr: asc.GlobalAddress,
+                   a_shape: asc.ConstExpr, b_shape: asc.ConstExpr, c_shape: asc.ConstExpr, k_tiles: asc.ConstExpr):
+    a_gm, b_gm, c_gm = asc2.tensor(a_ptr, a_shape), asc2.tensor(b_ptr, b_shape), asc2.tensor(c_ptr, c_shape)
+    acc = asc2.zeros_acc(c_shape, dtype=asc.float32)
+    kt = a_shape[1] // k_tiles
+    a_l1 = asc2.load(a_gm, a_shape, offsets=[0, 0], location=L1)
+    b_l1 = asc2.load(b_gm, b_shape, offsets=[0, 0], location=L1)
+    for i in range(k_tiles, unroll_factor=2, parallel=True):
+        a_i = asc2.copy(a_l1, [a_shape[0], kt], offsets=[0, i * kt], location=L0A)
+        b_i = asc2.copy(b_l1, [kt, b_shape[1]], offsets=[i * kt, 0], location=L0B)
+        asc2.matmul_acc(a_i, b_i, acc)
+    asc2.store(acc, c_gm, offsets=[0, 0])
+
+
+@asc2.jit(always_compile=True)
+def matmul_mn_blocked(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, c_ptr: asc.GlobalAddress,
+                      a_shape: asc.ConstExpr, b_shape: asc.ConstExpr, c_shape: asc.ConstExpr,
+                      m_tile: asc.ConstExpr[int], m_tiles_per_block: asc.ConstExpr[int], n_tile: asc.ConstExpr[int],
+                      n_tiles_per_block: asc.ConstExpr[int]):
+    a_gm, b_gm, c_gm = asc2.tensor(a_ptr, a_shape), asc2.tensor(b_ptr, b_shape), asc2.tensor(c_ptr, c_shape)
+    block = asc2.block_idx()
+    m_per_block = m_tile * m_tiles_per_block
+    m_base = (m_per_block * block) % a_shape[0]
+    n_base = ((m_per_block * block) // a_shape[0]) * (n_tile * n_tiles_per_block)
+    for j in range(n_tiles_per_block):
+        n_off = n_base + j * n_tile
+        b_j = asc2.load(b_gm, [b_shape[0], n_tile], offsets=[0, n_off], location=L0B)
+        for i in range(m_tiles_per_block):
+            m_off = m_base + i * m_tile
+            a_i = asc2.load(a_gm, [m_tile, a_shape[1]], offsets=[m_off, 0], location=L0A)
+            asc2.store(a_i @ b_j, c_gm, offsets=[m_off, n_off])
+
+
+@asc2.jit(always_compile=True)
+def matmul_relu_cast(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, c_ptr: asc.GlobalAddress,
+                     a_shape: asc.ConstExpr, b_shape: asc.ConstExpr, c_shape: asc.ConstExpr):
+    a_gm, b_gm, c_gm = asc2.tensor(a_ptr, a_shape), asc2.tensor(b_ptr, b_shape), asc2.tensor(c_ptr, c_shape)
+    a = asc2.load(a_gm, a_shape, offsets=[0, 0], location=L0A)
+    b = asc2.load(b_gm, b_shape, offsets=[0, 0], location=L0B)
+    c = asc2.relu(a @ b).to(asc.float16)
+    asc2.store(c, c_gm, offsets=[0, 0])
+
+
+@asc2.jit(always_compile=True)
+def matmul_chained(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, c_ptr: asc.GlobalAddress,
+                   a_shape: asc.ConstExpr, b_shape: asc.ConstExpr, c_shape: asc.ConstExpr, dtype: asc.ConstExpr):
+    a_gm, b_gm, c_gm = asc2.tensor(a_ptr, a_shape), asc2.tensor(b_ptr, b_shape), asc2.tensor(c_ptr, c_shape)
+    a = asc2.load(a_gm, a_shape, offsets=[0, 0], location=L0A)
+    b = asc2.load(b_gm, b_shape, offsets=[0, 0], location=L0B)
+    c = (a @ b).to(dtype)
+    c_l1 = asc2.copy(c, c_shape, offsets=[0, 0], location=L1)
+    c_l0a = asc2.copy(c_l1, c_shape, offsets=[0, 0], location=L0A)
+    asc2.store(c_l0a @ b, c_gm, offsets=[0, 0])
+
+
+def mn_tiles_per_block(m, n, core_num, m_tile, n_tile, n_tiles_per_block):
+    """Host-side tile bookkeeping of the M/N-blocked kernel (even distribution over blocks)."""
+    m_tiles, n_tiles = m // m_tile, n // n_tile
+    assert m % m_tile == 0 and n % n_tile == 0 and (m_tiles * n_tiles) % core_num == 0
+    per_core = (m_tiles * n_tiles) // core_num
+    assert n_tiles % n_tiles_per_block == 0 and per_core % n_tiles_per_block == 0
+    m_tiles_per_block = per_core // n_tiles_per_block
+    assert m_tiles % m_tiles_per_block == 0
+    return m_tiles_per_block

@@ -1,0 +1,197 @@
+"""The reference's asc2 kernel tests, run on the CUDA platform through the public surface
+(``@asc2.jit`` kernels launched as ``kernel[core_num](...)`` after
+``asc.runtime.config.set_platform(backend, platform, device_id)``), plus the five workload scripts.
+Test bodies follow python/test/asc2/kernels/test_*.py: same shapes, same input distributions, same
+CPU goldens and tolerances."""
+import numpy as np
+import pytest
+import torch
+
+import asc
+import asc.runtime.config as config
+import asc2  # noqa: F401
+
+import asc2_scripts as K
+from oracle import golden as G
+from pyasc_b200 import tutorials as T
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def select_platform(backend, platform, device_id):
+    config.set_platform(backend, platform, device_id)
+
+
+def test_vadd_numpy(backend):
+    rng = np.random.default_rng(seed=2026)
+    size = 8192
+    x = rng.random(size, dtype=np.float32) * 10
+    y = rng.random(size, dtype=np.float32) * 10
+    out = np.empty_like(x)
+    tile_size, core_num = 128, 16
+    K.vadd[core_num](x, y, out, size, tile_size, asc.ceildiv(asc.ceildiv(size, tile_size), core_num))
+    np.testing.assert_allclose(out, x + y)
+    G.assert_exact(out, x + y)
+
+
+def test_vadd_readme_form_torch_cpu():
+    x = torch.rand(8192, dtype=torch.float32)
+    y = torch.rand_like(x)
+    out = torch.empty_like(x)
+    tile_size, cores = 128, 16
+    T.vadd_kernel[cores](x, y, out, out.numel(), tile_size, asc.ceildiv(out.numel() // tile_size, cores))
+    torch.testing.assert_close(out, x + y)
+    G.assert_exact(out, x + y)
+
+
+def test_vadd_partial_coverage_leaves_tail_untouched():
+    x, y = G.vadd_inputs(8192)
+    out = torch.full_like(x, -1.0)
+    K.vadd[16](x, y, out, 8192, 128, 3)                     # 16 * 3 * 128 = 6144 elements
+    G.assert_exact(out[:6144], (x + y)[:6144])
+    assert bool((out[6144:] == -1.0).all())
+
+
+def test_vmuladd():
+    rng = np.random.default_rng(seed=2026)
+    size = 8192
+    x, y, z = (rng.random(size, dtype=np.float32) * 10 for _ in range(3))
+    out = np.empty_like(x)
+    K.vmuladd[16](x, y, z, out, size, 32, asc.ceildiv(asc.ceildiv(size, 32), 16), buffer_factor=2)
+    np.testing.assert_allclose(out, x * y + z)
+    G.assert_exact(out, x * y + z)
+
+
+def test_softmax_both_forms():
+    x = torch.rand((64, 1024), dtype=torch.float32)
+    out = torch.empty_like(x)
+    K.softmax_rows[16](x, out, 64, 1024, tile_size=1024)
+    torch.testing.assert_close(out, torch.softmax(x, dim=1))
+    G.assert_softmax_close(out, G.softmax(x))
+    out2 = torch.empty_like(x)
+    K.softmax_blocks[16](x, out2, 64, 1024, 4)
+    torch.testing.assert_close(out2, torch.softmax(x, dim=1))
+
+
+@pytest.mark.parametrize("k_tiles", [2, 4, 8])
+def test_matmul_tiled(k_tiles):
+    m, k, n = 64, 128, 256
+    a = torch.rand((m, k), dtype=torch.float16)
+    b = torch.rand((k, n), dtype=torch.float16)
+    c = torch.zeros((m, n), dtype=torch.float32)
+    K.matmul_k_tiled[1](a, b, c, a.shape, b.shape, c.shape, k_tiles)
+    torch.testing.assert_close(c, a.to(torch.float32) @ b.to(torch.float32))
+
+
+@pytest.mark.parametrize("m, k, n, core_num, m_tile, n_tile, n_tiles_per_block", [
+    (16, 16, 16, 1, 16, 16, 1), (16, 160, 16, 1, 16, 16, 1), (32, 16, 16, 2, 16, 16, 1), (16, 16, 32, 2, 16, 16, 1),
+    (32, 16, 32, 2, 16, 16, 1), (32, 16, 32, 2, 16, 16, 2), (32, 16, 32, 4, 16, 16, 1),
+    (480, 224, 1344, 30, 48, 32, 7)])
+def test_matmul_mnblock(m, k, n, core_num, m_tile, n_tile, n_tiles_per_block):
+    a = torch.rand((m, k), dtype=torch.float16)
+    b = torch.rand((k, n), dtype=torch.float16)
+    c = torch.zeros((m, n), dtype=torch.float32)
+    mtpb = K.mn_tiles_per_block(m, n, core_num, m_tile, n_tile, n_tiles_per_block)
+    K.matmul_mn_blocked[core_num](a, b, c, a.shape, b.shape, c.shape, m_tile, mtpb, n_tile, n_tiles_per_block)
+    torch.testing.assert_close(c, a.to(torch.float32) @ b.to(torch.float32))
+
+
+@pytest.mark.parametrize("m, k, n, dtype", [(64, 128, 128, torch.float32), (64, 128, 256, torch.float16),
+                                            (64, 128, 256, torch.bfloat16)])
+def test_matmul_fixpipe(m, k, n, dtype):
+    a = (torch.rand((m, k), dtype=dtype) - .5) * 10
+    b = (torch.rand((k, n), dtype=dtype) - .5) * 10
+    c = torch.zeros((m, n), dtype=torch.float16)
+    K.matmul_relu_cast[1](a, b, c, a.shape, b.shape, c.shape)
+    c_ref = (a.to(torch.float32) @ b.to(torch.float32)).relu().to(torch.float16)
+    torch.testing.assert_close(c, c_ref, atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("m, k, n, torch_dtype, pyasc_dtype", [(32, 64, 64, torch.float16, asc.float16),
+                                                              (64, 64, 64, torch.bfloat16, asc.bfloat16)])
+def test_matmul_l0c_to_l1(m, k, n, torch_dtype, pyasc_dtype):
+    torch.manual_seed(0)
+    a = (torch.rand((m, k), dtype=torch_dtype) - .5) * 10
+    b = (torch.rand((k, n), dtype=torch_dtype) - .5) * 10
+    c = torch.zeros((m, n), dtype=torch.float32)
+    K.matmul_chained[1](a, b, c, a.shape, b.shape, c.shape, pyasc_dtype)
+    c_ref = (a.to(torch.float32) @ b.to(torch.float32)).to(torch_dtype)
+    c_ref = c_ref.to(torch.float32) @ b.to(torch.float32)
+    torch.testing.assert_close(c, c_ref, atol=1e-3, rtol=1e-3)
+
+
+# ------------------------------------------------------------------------- the five workload scripts
+def test_workload_softmax_device_tensors_zero_copy():
+    x = G.softmax_input(2048, 4096).cuda()
+    out = torch.empty_like(x)
+    T.softmax_launch(x, out)
+    G.assert_softmax_close(out, G.softmax(x.cpu()))
+    out2 = torch.empty_like(x)
+    T.softmax_fused_launch(x, out2)
+    assert torch.equal(out, out2)
+
+
+def test_workload_vadd_host_and_device_paths_agree():
+    x, y = G.vadd_inputs(1 << 22)
+    out_h = torch.empty_like(x)
+    T.vadd_launch(x, y, out_h, core_num=16, tile_size=4096)
+    xd, yd = x.cuda(), y.cuda()
+    out_d = torch.empty_like(xd)
+    T.vadd_launch(xd, yd, out_d, core_num=16, tile_size=4096)
+    G.assert_exact(out_h, x + y)
+    G.assert_exact(out_d, x + y)
+    xp, yp = x.pin_memory(), y.pin_memory()
+    out_p = torch.empty_like(x).pin_memory()
+    T.vadd_launch(xp, yp, out_p, core_num=16, tile_size=4096)
+    G.assert_exact(out_p, x + y)
+
+
+def test_workload_matmul_fp16_script():
+    a, b = G.gemm_f16_inputs(1024, 1536, 2048)
+    c = torch.empty(1024, 1536, dtype=torch.float16)
+    T.matmul_fp16_launch(a, b, c, core_num=32)
+    G.assert_half_close(c, G.gemm_f16(a, b))
+    c_relu = torch.empty_like(c)
+    T.matmul_fp16_launch(a, b, c_relu, core_num=32, relu=True)
+    G.assert_half_close(c_relu, G.gemm_f16(a, b, relu=True))
+
+
+def test_workload_matmul_int8_scripts():
+    a, b, sa, sb = G.gemm_i8_inputs(512, 768, 1024)
+    acc = torch.empty(512, 768, dtype=torch.int32)
+    T.matmul_int8_launch(a, b, acc, core_num=8)
+    ref = G.gemm_i8(a, b)
+    G.assert_exact(acc, ref)
+    out = torch.empty(512, 768, dtype=torch.float16)
+    T.matmul_int8_dequant_launch(a, b, sa, sb, out, core_num=8)
+    G.assert_exact(out, G.dequant(ref, sa, sb))
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_workload_attention_script(causal):
+    q, k, v = G.attention_inputs(2, 3, 512)
+    o = torch.empty_like(q)
+    T.attention_launch(q, k, v, o, causal=causal, core_num=24)
+    G.assert_half_close(o, G.attention(q, k, v, causal))
+
+
+def test_user_stream_and_profiler():
+    import ctypes
+    from asc.lib import runtime as rt
+    from asc.lib.profiling import Profiler, task_time_median
+    x, y = (t.cuda() for t in G.vadd_inputs(1 << 20))
+    out = torch.empty_like(x)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        T.vadd_launch(x, y, out, core_num=16, tile_size=65536, stream=ctypes.c_void_p(stream.cuda_stream))
+    stream.synchronize()
+    G.assert_exact(out, x.cpu() + y.cpu())
+    prof = Profiler()
+    xh, yh = G.vadd_inputs(1 << 16)
+    oh = torch.empty_like(xh)
+    for _ in range(3):
+        with prof.profile():
+            T.vadd_launch(xh, yh, oh, core_num=16, tile_size=4096)
+    assert task_time_median(prof.last_result.tasks, skip=1) > 0
+    assert rt.launch_count() > 0

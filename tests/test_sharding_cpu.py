@@ -1,0 +1,58 @@
+"""Multi-GPU plumbing on CPU: shard arithmetic and the output all-gather over gloo, world size 2."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from pyasc_b200 import sharding
+
+
+def test_shard_ranges_cover_and_align():
+    for units, world, gran in [(1 << 28, 8, 4), (16384, 8, 1), (8192, 8, 128), (128, 8, 1), (1000, 3, 4), (5, 8, 1),
+                               (0, 2, 1), (130, 4, 128)]:
+        ranges = sharding.all_shard_ranges(units, world, gran)
+        assert ranges[0][0] == 0 and ranges[-1][1] == units
+        for (l0, h0), (l1, h1) in zip(ranges, ranges[1:]):
+            assert h0 == l1 and l0 <= h0
+        for lo, hi in ranges:
+            assert lo % gran == 0 or lo == units
+    assert sharding.shard_range(8192, 8, 3, 128) == (3072, 4096)
+    with pytest.raises(ValueError):
+        sharding.shard_range(10, 2, 2)
+
+
+def test_partitions_name_the_replicated_operands():
+    assert sharding.partition_for("gemm_f16", m=8192).replicated == ("B", )
+    assert sharding.partition_for("gemm_i8", m=8192).replicated == ("B", "b_scale")
+    assert sharding.partition_for("attention", batch=4, heads=32).units == 128
+    assert sharding.partition_for("vadd", n=1 << 28).granule == 4
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, units: int, gran: int):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        full = torch.arange(units * 3, dtype=torch.float32).reshape(units, 3)
+        lo, hi = sharding.shard_range(units, world, rank, gran)
+        # each rank "computes" only its shard (here: x + 1) and the gather reassembles the whole output
+        local = full[lo:hi] + 1
+        out = sharding.all_gather_units(local, units, world, gran)
+        assert torch.equal(out, full + 1), f"rank {rank}"
+        with pytest.raises(ValueError):
+            sharding.all_gather_units(local[:-1] if hi > lo else torch.zeros(1, 3), units, world, gran)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("units, gran", [(64, 1), (1000, 4), (130, 128)])
+def test_all_gather_over_gloo(units, gran):
+    mp.spawn(_worker, args=(2, _free_port(), units, gran), nprocs=2, join=True)

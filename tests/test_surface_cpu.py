@@ -1,0 +1,204 @@
+"""The asc / asc2 surface on CPU: tracing, pattern matching and launch planning without a device
+(``DRY_RUN=1`` stops before the launch, as in the reference: python/asc/runtime/launcher.py:208-210),
+plus the argument / option error behaviour of the reference's JITFunction and config."""
+import numpy as np
+import pytest
+import torch
+
+import asc
+import asc2
+from asc.codegen import matcher
+from asc.language.core.ir_value import PlainValue
+from asc.runtime import config
+
+import asc2_scripts as K
+from pyasc_b200 import tutorials as T
+
+
+@pytest.fixture(autouse=True)
+def dry_run(monkeypatch):
+    monkeypatch.setenv("DRY_RUN", "1")
+
+
+def only_step(jit_fn):
+    plan = jit_fn.last_plan
+    assert len(plan.steps) == 1, plan
+    return plan, plan.steps[0]
+
+
+# ----------------------------------------------------------------------------- scalar semantics
+def test_plain_value_arithmetic_is_truncating():
+    a = PlainValue.const(-7)
+    assert (a // 2).value == -3 and (a / 2).value == -3 and (a % 2).value == -1   # C semantics, not Python's
+    b = PlainValue.sym("block_idx")
+    expr = (b * 6) % 4 + (b * 6) // 4
+    vals = expr.evaluate({"block_idx": np.arange(5)})
+    assert vals.tolist() == [0, 3, 3, 6, 6]
+    assert asc.ceildiv(10, 4) == 3
+    with pytest.raises(NotImplementedError):
+        bool(b < 3)
+
+
+def test_instances_and_intervals():
+    ctx_loops = []
+    env = matcher.enumerate_instances(3, tuple(ctx_loops))
+    assert env["block_idx"].tolist() == [0, 1, 2]
+    assert matcher.merge_intervals(np.array([0, 8, 4, 20]), np.array([4, 12, 8, 24])) == [(0, 12), (20, 24)]
+    assert matcher.merge_intervals(np.array([5]), np.array([5])) == []
+
+
+# ----------------------------------------------------------------------------- pattern matching
+def test_vadd_plan_full_and_ragged():
+    x = np.zeros(8192, np.float32)
+    K.vadd[16](x, x, x.copy(), 8192, 128, 4)
+    plan, step = only_step(K.vadd)
+    assert step.fn_name == "asc_cuda_vadd_f32" and step.note == "[0, 8192)"
+    assert plan.reads == {0, 1} and plan.writes == {2}
+    # fewer tiles than elements: the tail stays untouched
+    K.vadd[16](x, x, x.copy(), 8192, 128, 3)
+    assert only_step(K.vadd)[1].note == "[0, 6144)"
+    # more tiles than elements: stores are clipped to the tensor
+    y = np.zeros(1000, np.float32)
+    K.vadd[4](y, y, y.copy(), 1000, 128, 2)
+    assert only_step(K.vadd)[1].note == "[0, 1000)"
+
+
+def test_vmuladd_plan():
+    x = np.zeros(8192, np.float32)
+    K.vmuladd[16](x, x, x, x.copy(), 8192, 32, 16, buffer_factor=2)
+    plan, step = only_step(K.vmuladd)
+    assert step.fn_name == "asc_cuda_vmuladd_f32" and plan.reads == {0, 1, 2} and plan.writes == {3}
+
+
+def test_softmax_plans():
+    x = torch.zeros(64, 1024)
+    K.softmax_rows[16](x, torch.empty_like(x), 64, 1024, tile_size=1024)
+    assert only_step(K.softmax_rows)[1].note == "rows [0, 64) x 1024 cols"
+    K.softmax_blocks[16](x, torch.empty_like(x), 64, 1024, 4)
+    assert only_step(K.softmax_blocks)[1].note == "rows [0, 64) x 1024 cols"
+    # blocks that cover only part of the rows
+    K.softmax_blocks[4](x, torch.empty_like(x), 64, 1024, 4)
+    assert only_step(K.softmax_blocks)[1].note == "rows [0, 16) x 1024 cols"
+    # a tile wider than the row would feed zero padding into the softmax: refused, not approximated
+    with pytest.raises(NotImplementedError):
+        K.softmax_rows[16](x, torch.empty_like(x), 64, 1024, tile_size=2048)
+
+
+@pytest.mark.parametrize("k_tiles", [2, 4, 8])
+def test_matmul_k_tiled_plan(k_tiles):
+    a = torch.zeros(64, 128, dtype=torch.float16)
+    b = torch.zeros(128, 256, dtype=torch.float16)
+    c = torch.zeros(64, 256)
+    K.matmul_k_tiled[1](a, b, c, a.shape, b.shape, c.shape, k_tiles)
+    _, step = only_step(K.matmul_k_tiled)
+    assert step.fn_name == "asc_cuda_gemm_f16" and "C[0:64, 0:256] = A[0:, 0:128]" in step.note
+
+
+@pytest.mark.parametrize("m, k, n, core_num, m_tile, n_tile, ntpb", [
+    (16, 16, 16, 1, 16, 16, 1), (32, 16, 32, 2, 16, 16, 2), (32, 16, 32, 4, 16, 16, 1), (480, 224, 1344, 30, 48, 32, 7)])
+def test_matmul_mn_blocked_merges_into_one_gemm(m, k, n, core_num, m_tile, n_tile, ntpb):
+    a = torch.zeros(m, k, dtype=torch.float16)
+    b = torch.zeros(k, n, dtype=torch.float16)
+    c = torch.zeros(m, n)
+    mtpb = K.mn_tiles_per_block(m, n, core_num, m_tile, n_tile, ntpb)
+    K.matmul_mn_blocked[core_num](a, b, c, a.shape, b.shape, c.shape, m_tile, mtpb, n_tile, ntpb)
+    _, step = only_step(K.matmul_mn_blocked)
+    assert f"C[0:{m}, 0:{n}] = A[0:, 0:{k}]" in step.note
+
+
+def test_matmul_epilogue_and_chain_plans():
+    for dt, fn in ((torch.float32, "asc_cuda_gemm_f32"), (torch.float16, "asc_cuda_gemm_f16"),
+                   (torch.bfloat16, "asc_cuda_gemm_f16")):
+        a, b = torch.zeros(64, 128, dtype=dt), torch.zeros(128, 256, dtype=dt)
+        c = torch.zeros(64, 256, dtype=torch.float16)
+        K.matmul_relu_cast[1](a, b, c, a.shape, b.shape, c.shape)
+        assert only_step(K.matmul_relu_cast)[1].fn_name == fn
+    a, b = torch.zeros(32, 64, dtype=torch.float16), torch.zeros(64, 64, dtype=torch.float16)
+    c = torch.zeros(32, 64)
+    K.matmul_chained[1](a, b, c, a.shape, b.shape, c.shape, asc.float16)
+    plan = K.matmul_chained.last_plan
+    assert [s.fn_name for s in plan.steps] == ["asc_cuda_gemm_f16"] * 2 and plan.temps == {"tmp0": 32 * 64 * 2}
+
+
+def test_workload_scripts_match_at_full_size():
+    m = n = k = 8192
+    a, b = torch.empty(m, k, dtype=torch.float16), torch.empty(k, n, dtype=torch.float16)
+    c = torch.empty(m, n, dtype=torch.float16)
+    T.matmul_fp16_launch(a, b, c)
+    assert "C[0:8192, 0:8192] = A[0:, 0:8192]" in only_step(T.matmul_fp16_kernel)[1].note
+    a8, b8 = torch.empty(m, k, dtype=torch.int8), torch.empty(k, n, dtype=torch.int8)
+    T.matmul_int8_launch(a8, b8, torch.empty(m, n, dtype=torch.int32))
+    assert only_step(T.matmul_int8_kernel)[1].fn_name == "asc_cuda_gemm_i8"
+    T.matmul_int8_dequant_launch(a8, b8, torch.empty(m), torch.empty(n), c)
+    plan, step = only_step(T.matmul_int8_dequant_kernel)
+    assert step.fn_name == "asc_cuda_gemm_i8" and plan.reads == {0, 1, 2, 3} and plan.writes == {4}
+    q = torch.empty(4, 32, 4096, 128, dtype=torch.float16)
+    for causal in (False, True):
+        T.attention_launch(q, q, q, torch.empty_like(q), causal=causal)
+        assert only_step(T.attention_kernel)[1].note == f"128 heads x 4096 x 128, causal={causal}"
+    s = torch.empty(16384, 4096)
+    T.softmax_launch(s, torch.empty_like(s))
+    assert only_step(T.softmax_kernel)[1].note == "rows [0, 16384) x 4096 cols"
+
+
+def test_unsupported_pattern_raises_not_implemented():
+    @asc2.jit
+    def sin_kernel(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, size: int, tile: asc.ConstExpr[int]):
+        x_gm, out_gm = asc2.tensor(x_ptr, [size]), asc2.tensor(out_ptr, [size])
+        off = asc2.block_idx() * tile
+        asc2.store(asc2.sin(asc2.load(x_gm, [tile], offsets=[off])), out_gm, offsets=[off])
+    x = np.zeros(256, np.float32)
+    with pytest.raises(NotImplementedError, match="no kernel for this pattern"):
+        sin_kernel[2](x, x.copy(), 256, 128)
+
+
+# ----------------------------------------------------------------------------- reference error behaviour
+def test_jit_option_and_argument_errors():
+    with pytest.raises(RuntimeError, match="unknown"):
+        asc2.jit(not_an_option=True)(lambda x_ptr: None)
+    with pytest.raises(RuntimeError, match="conflict"):
+        asc2.jit(lambda core_num: None)
+    x = np.zeros(128, np.float32)
+    with pytest.raises(ValueError, match="Core number"):
+        K.vadd[0](x, x, x, 128, 128, 1)
+    with pytest.raises(TypeError):
+        K.vadd[1]("not a tensor", x, x, 128, 128, 1)
+    with pytest.raises(RuntimeError, match="ConstExpr"):
+        K.vadd[1](x, x, x, 128, 12.5, 1)
+    with pytest.raises(TypeError):
+        K.vadd["sixteen"]
+    with pytest.raises(RuntimeError, match="aligned by 32 bytes"):
+        @asc2.jit
+        def bad_tile(x_ptr: asc.GlobalAddress):
+            asc2.load(asc2.tensor(x_ptr, [4, 6]), [2, 6], offsets=[0, 0])
+        bad_tile[1](np.zeros((4, 6), np.float32))
+    with pytest.raises(ValueError, match="Exactly one"):
+        @asc2.jit
+        def both(x_ptr: asc.GlobalAddress):
+            asc2.load(asc2.tensor(x_ptr, [8]), [8], offsets=[0], tile_id=[0])
+        both[1](np.zeros(8, np.float32))
+
+
+def test_matmul_argument_checks():
+    @asc2.jit
+    def mixed(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress):
+        a = asc2.load(asc2.tensor(a_ptr, [16, 16]), [16, 16], offsets=[0, 0])
+        b = asc2.load(asc2.tensor(b_ptr, [16, 16]), [16, 16], offsets=[0, 0])
+        a @ b
+    with pytest.raises(RuntimeError, match="same types"):
+        mixed[1](torch.zeros(16, 16, dtype=torch.float16), torch.zeros(16, 16))
+
+
+def test_config_backend_selection():
+    assert config.Backend("CUDA") is config.Backend.CUDA
+    assert config.platform_to_arch(config.Platform.B200) is config.CompilationArch.SM100A
+    assert config.platform_to_arch(config.Platform.Ascend950PR_9599) is config.CompilationArch.C310
+    with pytest.raises(ValueError):
+        config.set_platform("TPU")
+    with pytest.raises(ValueError, match="not available"):
+        config.set_platform("NPU")
+    # no device in this process: check=True must fail loudly, check=False must not touch the device
+    config.set_platform("CUDA", check=False)
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="not available"):
+            config.set_platform("CUDA")
