@@ -66,6 +66,7 @@ class Plan:
         self.steps: List[Step] = []
         self.reads: set = set()       # runtime-argument indices the kernel reads
         self.writes: set = set()      # ... and writes
+        self.partial_writes: set = set()  # written arguments whose buffer is not overwritten completely
         self.temps: Dict[str, int] = {}  # temp-buffer key -> bytes
 
     def __repr__(self) -> str:
@@ -289,6 +290,8 @@ def _match_elementwise(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     in_idx = [v.tensor.base.index for v in operands]
     plan.reads.update(in_idx)
     plan.writes.add(out_idx)
+    if intervals != [(0, out_t.base.numel)]:
+        plan.partial_writes.add(out_idx)
     for lo, hi in intervals:
         def build(ptrs, stream, lo=lo, hi=hi):
             args = [_p(ptrs[i] + 4 * lo) for i in in_idx]
@@ -375,6 +378,8 @@ def _match_softmax(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     in_idx, out_idx = view.tensor.base.index, out_t.base.index
     plan.reads.add(in_idx)
     plan.writes.add(out_idx)
+    if not (intervals == [(0, R)] and col0 == 0 and tile_cols == C and R * C == out_t.base.numel):
+        plan.partial_writes.add(out_idx)
     for lo, hi in intervals:
         def build(ptrs, stream, lo=lo, hi=hi):
             byte_off = 4 * (lo * C + col0)
@@ -623,6 +628,9 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
 
     a_idx, b_idx, c_idx = a_w.tensor.base.index, b_w.tensor.base.index, out_t.base.index
     plan.writes.add(c_idx)
+    if not (len(calls) == 1 and calls[0][0] == 0 and calls[0][1] == 0 and calls[0][5] == c_rows and
+            calls[0][6] == c_cols and c_rows * c_cols == out_t.base.numel):
+        plan.partial_writes.add(c_idx)
     es = in_dtype.sizeof()
     osz = out_t.dtype.sizeof()
     lda, ldb, ldc = a_cols, b_cols, c_cols
@@ -757,6 +765,8 @@ def _match_attention(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     idx = [t.base.index for t in (qv.tensor, kv.tensor, vv.tensor, out_t)]
     plan.reads.update(idx[:3])
     plan.writes.add(idx[3])
+    if rows * D != out_t.base.numel:
+        plan.partial_writes.add(idx[3])
     heads = rows // S
 
     def build(ptrs, stream):
@@ -797,6 +807,7 @@ def build_plan(trace: KernelTrace) -> Plan:
         total.steps += plan.steps
         total.reads |= plan.reads
         total.writes |= plan.writes
+        total.partial_writes |= plan.partial_writes
         for k, v in plan.temps.items():
             if k in total.temps:
                 raise _unsupported("several stores that each need temporary buffers")
@@ -804,4 +815,5 @@ def build_plan(trace: KernelTrace) -> Plan:
     total.pattern = "+".join(names)
     total.reads = {i for i in total.reads if isinstance(i, int)}
     total.writes = {i for i in total.writes if isinstance(i, int)}
+    total.partial_writes = {i for i in total.partial_writes if isinstance(i, int)}
     return total

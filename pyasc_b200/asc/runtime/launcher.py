@@ -3,8 +3,8 @@
 Argument handling follows the reference launcher: host tensors (NumPy / torch CPU) get device
 mirrors for the duration of the call and are copied back afterwards, device tensors pass through
 untouched, and the call returns only after the stream has drained, so results are visible to the
-caller on return.  Differences, all invisible in results: only arguments the kernel reads are
-uploaded and only arguments it writes are copied back (the reference moves every argument both
+caller on return.  Differences, all invisible in results: only arguments the kernel reads (or overwrites
+only in part) are uploaded and only arguments it writes are copied back (the reference moves every argument both
 ways, launcher.py:176-195); device mirrors come from a pool instead of malloc/free per call; and
 when the caller passes its own stream (``kernel[cores, stream]``) and every argument already
 lives on the device, the launch is left asynchronous on that stream.
@@ -78,7 +78,7 @@ class Launcher:
         temps: List[ctypes.c_void_p] = []
         try:
             for index, handle in handles.items():
-                if isinstance(handle, _HostMirror) and index not in plan.reads:
+                if isinstance(handle, _HostMirror) and index not in plan.reads and index not in plan.partial_writes:
                     ptrs[index] = handle.device_alloc_only()
                 else:
                     ptrs[index] = handle.copy_to_device(stream)
