@@ -1,0 +1,603 @@
+#!/usr/bin/env python
+"""Benchmark of the five hot-path kernels on B200: HBM GB/s and tensor TFLOP/s per GPU against the
+measured roofline, next to the same computation on the host CPU.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workloads a,b,...]
+
+One JSON line on stdout (rank 0).  The headline workload is the fp32 row softmax [16384, 4096]; the
+other four workloads (vadd 2^28, fp16 GEMM 8192^3, int8 GEMM 8192^3 with dequant, attention forward
+[4,32,4096,128] non-causal and causal) are reported under "workloads" with the same sub-keys.
+
+value      device-resident throughput: K back-to-back C-ABI launches timed with CUDA events on the
+           launching stream (max over ranks), algorithmic bytes or FLOPs per launch / time.
+e2e        the same metric through the public asc2 surface (`kernel[cores](host tensors)`): pinned host
+           tensors in, host tensor out, H2D and D2H copies inside the timed region.
+roofline   achieved (= value per GPU) over the measured peak from MEASURED_PEAKS.json.
+cpu_baseline / --impl reference
+           the reference's own CPU computation of the path (the torch expressions its tests assert
+           against, oracle/golden.py) timed on a bounded sample with all host threads.
+
+Multi-GPU (launched under torchrun, one rank per GPU): weak scaling, every rank runs the full
+single-GPU workload on its own shard; there is no data-path collective.  The output all-gather over
+NCCL is timed separately and reported as "allgather_ms".
+All inputs are seeded synthetic data with the workloads' shapes and distributions; every timed input
+set is larger than the 126 MB L2.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from typing import Any, Callable, Dict, List, Optional
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+HEADLINE = "softmax"
+ALL_WORKLOADS = ["softmax", "vadd", "gemm_f16", "gemm_i8", "gemm_i8_dequant", "attention", "attention_causal"]
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks() -> Dict[str, Any]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            peaks = json.load(f)
+        peaks["source"] = "measured"
+        return peaks
+    peaks = dict(FALLBACK_PEAKS)
+    peaks["source"] = "fallback"
+    return peaks
+
+
+# ---------------------------------------------------------------------------------------------------
+# clocks: nvidia-smi sampled while the timed regions run
+# ---------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc: Optional[subprocess.Popen] = None
+        self.gpu_index = gpu_index
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> Dict[str, Any]:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, smax, power = [], [], []
+        reasons = set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+                power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [s for s, p in zip(sm, power) if p > 300.0] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------------
+# workloads
+# ---------------------------------------------------------------------------------------------------
+def P(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+class Workload:
+    """One benchmarked configuration.  `work` is algorithmic bytes (HBM-bound) or FLOPs (tensor-bound)
+    per launch; `units` names what a launch processes."""
+    name = ""
+    label = ""
+    unit = "GB/s"
+    bound = "hbm"
+    dtype = "f32"
+    work = 0.0
+    h2d_bytes = 0
+    d2h_bytes = 0
+
+    def setup_device(self, dev: torch.device) -> None: ...
+    def launch(self, lib, stream) -> int: ...
+    def setup_host(self) -> None: ...
+    def e2e_step(self) -> None: ...
+    def cpu_sample(self) -> float: ...          # runs the bounded CPU sample once, returns its work
+    cpu_sample_desc = ""
+
+    def throughput(self, work: float, seconds: float) -> float:
+        return work / seconds / (1e9 if self.unit == "GB/s" else 1e12)
+
+    def peak(self, peaks: Dict[str, Any]) -> float:
+        return float(peaks["hbm_gbs"]) if self.bound == "hbm" else float(peaks["bf16_tflops"])
+
+
+class Softmax(Workload):
+    name, label, dtype = "softmax", "softmax_f32_16384x4096", "f32"
+    R, C = 16384, 4096
+    work = 2.0 * 4 * R * C                      # one 4-byte read + one 4-byte write per element
+    h2d_bytes, d2h_bytes = 4 * R * C, 4 * R * C
+    cpu_sample_desc = "torch.softmax(x, -1) on the full [16384, 4096] input"
+
+    def setup_device(self, dev):
+        from oracle import golden as G
+        self.x = G.softmax_input(self.R, self.C).to(dev)
+        self.out = torch.empty_like(self.x)
+
+    def launch(self, lib, stream):
+        return lib.asc_cuda_softmax_f32(P(self.x), P(self.out), self.R, self.C, self.C, stream)
+
+    def setup_host(self):
+        from oracle import golden as G
+        self.hx = G.softmax_input(self.R, self.C).pin_memory()
+        self.hout = torch.empty_like(self.hx).pin_memory()
+
+    def e2e_step(self):
+        from pyasc_b200 import tutorials as T
+        T.softmax_launch(self.hx, self.hout, core_num=148)
+
+    def cpu_sample(self):
+        if not hasattr(self, "cx"):
+            from oracle import golden as G
+            self.cx = G.softmax_input(self.R, self.C)
+        from oracle import golden as G
+        G.softmax(self.cx)
+        return self.work
+
+
+class VAdd(Workload):
+    name, label, dtype = "vadd", "vadd_f32_2^28", "f32"
+    N = 1 << 28
+    work = 3.0 * 4 * N
+    h2d_bytes, d2h_bytes = 2 * 4 * N, 4 * N
+    CPU_N = 1 << 26
+    cpu_sample_desc = "x + y on 2^26 of the 2^28 elements"
+
+    def setup_device(self, dev):
+        g = torch.Generator(device=dev).manual_seed(2026)
+        self.x = torch.rand(self.N, device=dev, generator=g)
+        self.y = torch.rand(self.N, device=dev, generator=g)
+        self.out = torch.empty_like(self.x)
+
+    def launch(self, lib, stream):
+        return lib.asc_cuda_vadd_f32(P(self.x), P(self.y), P(self.out), self.N, stream)
+
+    def setup_host(self):
+        g = torch.Generator().manual_seed(2026)
+        self.hx = torch.rand(self.N, generator=g).pin_memory()
+        self.hy = torch.rand(self.N, generator=g).pin_memory()
+        self.hout = torch.empty(self.N).pin_memory()
+
+    def e2e_step(self):
+        from pyasc_b200 import tutorials as T
+        T.vadd_launch(self.hx, self.hy, self.hout, core_num=148, tile_size=1 << 16)
+
+    def cpu_sample(self):
+        if not hasattr(self, "cx"):
+            from oracle import golden as G
+            self.cx, self.cy = G.vadd_inputs(self.CPU_N)
+        from oracle import golden as G
+        G.vadd(self.cx, self.cy)
+        return 3.0 * 4 * self.CPU_N
+
+
+class GemmF16(Workload):
+    name, label, dtype, unit, bound = "gemm_f16", "gemm_f16_8192x8192x8192_f32acc_f16out", "f16", "TFLOP/s", "tensor"
+    M = N = K = 8192
+    work = 2.0 * M * N * K
+    h2d_bytes, d2h_bytes = 2 * (M * K + K * N), 2 * M * N
+    CPU_M = 1024
+    cpu_sample_desc = "(A.float() @ B.float()).half() on 1024 of the 8192 rows of A"
+
+    def setup_device(self, dev):
+        from oracle import golden as G
+        a, b = G.gemm_f16_inputs(self.M, self.N, self.K)
+        self.a, self.b = a.to(dev), b.to(dev)
+        self.c = torch.empty(self.M, self.N, dtype=torch.float16, device=dev)
+
+    def launch(self, lib, stream):
+        return lib.asc_cuda_gemm_f16(P(self.a), P(self.b), P(self.c), self.M, self.N, self.K, self.K, self.N, self.N,
+                                     0, 0, 0, stream)
+
+    def setup_host(self):
+        from oracle import golden as G
+        a, b = G.gemm_f16_inputs(self.M, self.N, self.K)
+        self.ha, self.hb = a.pin_memory(), b.pin_memory()
+        self.hc = torch.empty(self.M, self.N, dtype=torch.float16).pin_memory()
+
+    def e2e_step(self):
+        from pyasc_b200 import tutorials as T
+        T.matmul_fp16_launch(self.ha, self.hb, self.hc, core_num=148)
+
+    def cpu_sample(self):
+        from oracle import golden as G
+        if not hasattr(self, "ca"):
+            a, b = G.gemm_f16_inputs(self.CPU_M, self.N, self.K)
+            self.ca, self.cb = a, b
+        G.gemm_f16(self.ca, self.cb)
+        return 2.0 * self.CPU_M * self.N * self.K
+
+
+class GemmI8(Workload):
+    name, label, dtype, unit, bound = "gemm_i8", "gemm_i8_8192x8192x8192_int32out", "s8", "TFLOP/s", "tensor"
+    M = N = K = 8192
+    work = 2.0 * M * N * K
+    h2d_bytes, d2h_bytes = M * K + K * N, 4 * M * N
+    CPU_M = 256
+    dequant = False
+    cpu_sample_desc = "A.int32 @ B.int32 (evaluated exactly in fp64) on 256 of the 8192 rows of A"
+
+    def peak(self, peaks):
+        return 2.0 * float(peaks["bf16_tflops"])    # dense int8 runs at twice the 16-bit rate
+
+    def setup_device(self, dev):
+        from oracle import golden as G
+        a, b, sa, sb = G.gemm_i8_inputs(self.M, self.N, self.K)
+        self.a, self.b, self.sa, self.sb = a.to(dev), b.to(dev), sa.to(dev), sb.to(dev)
+        self.acc = None if self.dequant else torch.empty(self.M, self.N, dtype=torch.int32, device=dev)
+        self.deq = torch.empty(self.M, self.N, dtype=torch.float16, device=dev) if self.dequant else None
+
+    def launch(self, lib, stream):
+        return lib.asc_cuda_gemm_i8(P(self.a), P(self.b), P(self.acc), P(self.deq),
+                                    P(self.sa) if self.dequant else None, P(self.sb) if self.dequant else None,
+                                    self.M, self.N, self.K, self.K, self.N, self.N, stream)
+
+    def setup_host(self):
+        from oracle import golden as G
+        a, b, sa, sb = G.gemm_i8_inputs(self.M, self.N, self.K)
+        self.ha, self.hb, self.hsa, self.hsb = a.pin_memory(), b.pin_memory(), sa.pin_memory(), sb.pin_memory()
+        self.hacc = torch.empty(self.M, self.N, dtype=torch.int32).pin_memory() if not self.dequant else None
+        self.hdeq = torch.empty(self.M, self.N, dtype=torch.float16).pin_memory() if self.dequant else None
+
+    def e2e_step(self):
+        from pyasc_b200 import tutorials as T
+        if self.dequant:
+            T.matmul_int8_dequant_launch(self.ha, self.hb, self.hsa, self.hsb, self.hdeq, core_num=148)
+        else:
+            T.matmul_int8_launch(self.ha, self.hb, self.hacc, core_num=148)
+
+    def cpu_sample(self):
+        from oracle import golden as G
+        if not hasattr(self, "ca"):
+            self.ca, self.cb, self.csa, self.csb = G.gemm_i8_inputs(self.CPU_M, self.N, self.K)
+        acc = G.gemm_i8(self.ca, self.cb)
+        if self.dequant:
+            G.dequant(acc, self.csa, self.csb)
+        return 2.0 * self.CPU_M * self.N * self.K
+
+
+class GemmI8Dequant(GemmI8):
+    name, label = "gemm_i8_dequant", "gemm_i8_8192x8192x8192_dequant_f16out"
+    dequant = True
+    d2h_bytes = 2 * GemmI8.M * GemmI8.N
+    h2d_bytes = GemmI8.h2d_bytes + 4 * (GemmI8.M + GemmI8.N)
+    cpu_sample_desc = "A.int32 @ B.int32 then acc * a_scale[row] * b_scale[col] -> fp16 on 256 of the 8192 rows"
+
+
+class Attention(Workload):
+    name, label, dtype, unit, bound = "attention", "attention_fwd_f16_b4_h32_s4096_d128", "f16", "TFLOP/s", "tensor"
+    B, H, S, D = 4, 32, 4096, 128
+    causal = False
+    work = 4.0 * B * H * S * S * D
+    h2d_bytes, d2h_bytes = 3 * 2 * B * H * S * D, 2 * B * H * S * D
+    CPU_HEADS = 2
+    cpu_sample_desc = "fp32 softmax(QK^T*scale)V on 2 of the 128 (batch, head) pairs"
+
+    def setup_device(self, dev):
+        from oracle import golden as G
+        q, k, v = G.attention_inputs(self.B, self.H, self.S, self.D)
+        self.q, self.k, self.v = q.to(dev), k.to(dev), v.to(dev)
+        self.o = torch.empty_like(self.q)
+
+    def launch(self, lib, stream):
+        return lib.asc_cuda_attn_fwd_f16(P(self.q), P(self.k), P(self.v), P(self.o), self.B, self.H, self.S, self.D,
+                                         ctypes.c_float(self.D ** -0.5), int(self.causal), 0, stream)
+
+    def setup_host(self):
+        from oracle import golden as G
+        q, k, v = G.attention_inputs(self.B, self.H, self.S, self.D)
+        self.hq, self.hk, self.hv = q.pin_memory(), k.pin_memory(), v.pin_memory()
+        self.ho = torch.empty_like(q).pin_memory()
+
+    def e2e_step(self):
+        from pyasc_b200 import tutorials as T
+        T.attention_launch(self.hq, self.hk, self.hv, self.ho, causal=self.causal, core_num=148)
+
+    def cpu_sample(self):
+        from oracle import golden as G
+        if not hasattr(self, "cq"):
+            self.cq, self.ck, self.cv = G.attention_inputs(1, self.CPU_HEADS, self.S, self.D)
+        G.attention(self.cq, self.ck, self.cv, self.causal)
+        return self.work * self.CPU_HEADS / (self.B * self.H)
+
+
+class AttentionCausal(Attention):
+    name, label = "attention_causal", "attention_fwd_f16_b4_h32_s4096_d128_causal"
+    causal = True
+    work = Attention.work / 2                    # the usual convention: masked half not counted
+    cpu_sample_desc = "fp32 causal softmax(QK^T*scale + mask)V on 2 of the 128 (batch, head) pairs"
+
+
+REGISTRY = {w.name: w for w in (Softmax, VAdd, GemmF16, GemmI8, GemmI8Dequant, Attention, AttentionCausal)}
+
+
+# ---------------------------------------------------------------------------------------------------
+# measurement
+# ---------------------------------------------------------------------------------------------------
+class Dist:
+    """torch.distributed plumbing for the multi-rank run (one rank per GPU under torchrun)."""
+
+    def __init__(self, n_gpus: int):
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        if n_gpus > 1 and self.world != n_gpus:
+            raise SystemExit(f"--gpus {n_gpus} needs torchrun with {n_gpus} ranks (WORLD_SIZE={self.world})")
+        self.enabled = self.world > 1
+
+    def init(self, backend: str) -> None:
+        if self.enabled:
+            import torch.distributed as dist
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group(backend, rank=self.rank, world_size=self.world)
+
+    def barrier(self) -> None:
+        if self.enabled:
+            import torch.distributed as dist
+            dist.barrier()
+
+    def max_over_ranks(self, value: float, device) -> float:
+        if not self.enabled:
+            return value
+        import torch.distributed as dist
+        t = torch.tensor([value], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def shutdown(self) -> None:
+        if self.enabled:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+def time_device(w: Workload, lib, steps: int, warmup: int, dist: Dist, dev) -> float:
+    """Milliseconds per launch: `steps` back-to-back launches between two CUDA events on the launching
+    (torch current) stream, barrier + synchronize on both sides, max over ranks."""
+    from pyasc_b200 import capi
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for _ in range(max(warmup, 3)):
+        rc = w.launch(lib, stream)
+        if rc != 0:
+            raise RuntimeError(f"{w.name}: C-ABI call returned {rc} ({capi.status_string(rc)}: {capi.last_cuda_error()})")
+    capi.check_device_status(stream)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(steps):
+        w.launch(lib, stream)
+    stop.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = start.elapsed_time(stop) / steps
+    capi.check_device_status(stream)
+    return dist.max_over_ranks(ms, dev)
+
+
+def time_e2e(w: Workload, steps: int, dist: Dist, dev) -> float:
+    """Seconds per step through the public asc2 surface with pinned host tensors (the launcher copies
+    in, launches, copies out and synchronises before returning)."""
+    w.e2e_step()                                   # warm-up: tracing, plan cache, device buffer pool
+    w.e2e_step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        w.e2e_step()
+    torch.cuda.synchronize()
+    sec = (time.perf_counter() - t0) / steps
+    dist.barrier()
+    return dist.max_over_ranks(sec, dev)
+
+
+def time_cpu(w: Workload, steps: int, warmup: int) -> Dict[str, Any]:
+    for _ in range(warmup):
+        w.cpu_sample()
+    best = float("inf")
+    work = 0.0
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        work = w.cpu_sample()
+        best = min(best, time.perf_counter() - t0)
+    return {"value": round(w.throughput(work, best), 4), "unit": w.unit, "cores": torch.get_num_threads(),
+            "kind": "reference", "sample": w.cpu_sample_desc, "seconds_per_sample": round(best, 4),
+            "host_cpus": os.cpu_count()}
+
+
+def time_allgather(w: Workload, dist: Dist) -> Optional[float]:
+    """Milliseconds for the NCCL all-gather that reassembles this workload's output on every rank."""
+    if not dist.enabled:
+        return None
+    import torch.distributed as tdist
+    local = next(t for t in (getattr(w, "out", None), getattr(w, "c", None), getattr(w, "deq", None),
+                             getattr(w, "acc", None), getattr(w, "o", None)) if t is not None)
+    flat = local.reshape(-1)
+    full = torch.empty(flat.numel() * dist.world, dtype=flat.dtype, device=flat.device)
+    tdist.all_gather_into_tensor(full, flat)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    start.record()
+    for _ in range(3):
+        tdist.all_gather_into_tensor(full, flat)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = dist.max_over_ranks(start.elapsed_time(stop) / 3, flat.device)
+    del full
+    return ms
+
+
+def run_ours(args) -> Dict[str, Any]:
+    dist = Dist(args.gpus)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the CUDA platform has no CPU fallback")
+    torch.cuda.set_device(dist.local_rank)
+    dev = torch.device("cuda", dist.local_rank)
+    dist.init("nccl")
+    import pyasc_b200  # noqa: F401
+    import asc
+    from pyasc_b200 import capi
+    lib = capi.load()
+    asc.runtime.config.set_platform("CUDA", device_id=dist.local_rank)
+    peaks = load_peaks()
+    names = args.workloads
+    sampler = ClockSampler(dist.local_rank)
+    results: Dict[str, Dict[str, Any]] = {}
+    launches_before = capi.launch_count()
+    timed_launches = 0
+    sampler.start()
+    for name in names:
+        w: Workload = REGISTRY[name]()
+        w.setup_device(dev)
+        n0 = capi.launch_count()
+        ms = time_device(w, lib, args.steps, args.warmup, dist, dev)
+        timed_launches += args.steps
+        per_gpu = w.throughput(w.work, ms * 1e-3)
+        peak = w.peak(peaks)
+        res: Dict[str, Any] = {
+            "workload": w.label, "value": round(per_gpu * dist.world, 2), "unit": w.unit, "ms_per_step": round(ms, 5),
+            "dtype": w.dtype,
+            "roofline": {"bound": w.bound, "achieved": round(per_gpu, 2), "peak": round(peak, 1),
+                         "unit": w.unit, "frac": round(per_gpu / peak, 4), "traffic": None,
+                         "peak_source": peaks["source"] + (" (2 x bf16 burst)" if name.startswith("gemm_i8") else
+                                                           " (bf16 burst)" if w.bound == "tensor" else " (copy)")},
+        }
+        ag = time_allgather(w, dist)
+        if ag is not None:
+            res["allgather_ms"] = round(ag, 4)
+        if not args.no_e2e:
+            w.setup_host()
+            e2e_steps = max(1, min(args.steps, args.e2e_steps))
+            sec = time_e2e(w, e2e_steps, dist, dev)
+            timed_launches += e2e_steps
+            res["e2e"] = {"value": round(w.throughput(w.work, sec) * dist.world, 3), "unit": w.unit,
+                          "h2d_bytes_per_step": w.h2d_bytes, "d2h_bytes_per_step": w.d2h_bytes,
+                          "ms_per_step": round(sec * 1e3, 3), "steps": e2e_steps}
+        res["launches"] = capi.launch_count() - n0
+        if dist.rank == 0 and dist.world == 1 and not args.no_cpu:
+            res["cpu_baseline"] = time_cpu(w, 3, 1)
+        results[name] = res
+        del w
+        torch.cuda.empty_cache()
+        from asc.lib import runtime as rt
+        rt.release_pool()
+    clocks = sampler.stop()
+    total_launches = capi.launch_count() - launches_before
+    dist.shutdown()
+    head = results[HEADLINE] if HEADLINE in results else results[names[0]]
+    traffic = load_traffic()
+    for name, res in results.items():
+        if name in traffic:
+            res["roofline"]["traffic"] = traffic[name]
+    line = {
+        "metric": "HBM GB/s (fp32 row softmax, whole job); per-kernel HBM GB/s and tensor TFLOP/s under 'workloads'",
+        "value": head["value"], "unit": head["unit"], "n_gpus": dist.world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": head["dtype"], "data": "synthetic (seeded, shapes and distributions of the named configs)",
+        "config": {"workload": head["workload"], "l2": "inputs larger than L2 (126 MB)", "timing": "CUDA events, max over ranks",
+                   "sharding": "every rank runs the full single-GPU workload on its own shard; no data-path collective"},
+        "roofline": head["roofline"], "e2e": head.get("e2e"), "cpu_baseline": head.get("cpu_baseline"),
+        "gpu_launches": total_launches, "gpu_launches_timed": timed_launches, "clocks": clocks, "workloads": results,
+    }
+    return line if dist.rank == 0 else {}
+
+
+def load_traffic() -> Dict[str, float]:
+    """DRAM bytes per launch from the committed ncu summaries (profiles/dram_traffic.json)."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if not os.path.exists(path):
+        return {}
+    with open(path) as f:
+        return {k: v for k, v in json.load(f).items() if isinstance(v, (int, float))}
+
+
+def run_reference(args) -> Dict[str, Any]:
+    """The reference's CPU computation of the path (its tests' torch expressions), all host threads."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return {}
+    results = {}
+    for name in args.workloads:
+        w: Workload = REGISTRY[name]()
+        steps = args.steps if name == HEADLINE else min(args.steps, 3)
+        results[name] = time_cpu(w, max(1, steps), max(1, min(args.warmup, 2)))
+        results[name]["workload"] = w.label
+        del w
+    head_name = HEADLINE if HEADLINE in results else args.workloads[0]
+    head = results[head_name]
+    w = REGISTRY[head_name]
+    return {
+        "impl": "reference",
+        "metric": "HBM GB/s (fp32 row softmax, whole job); per-kernel HBM GB/s and tensor TFLOP/s under 'workloads'",
+        "value": head["value"], "unit": head["unit"], "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(head["seconds_per_sample"] * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": w.dtype, "data": "synthetic (seeded, shapes and distributions of the named configs)",
+        "config": {"workload": w.label, "note": "CPU arm: torch expressions of the reference's tests on host cores"},
+        "cpu_baseline": head,
+        "e2e": {"value": head["value"], "unit": head["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "workloads": results,
+    }
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workloads", type=lambda s: s.split(","), default=ALL_WORKLOADS,
+                    help="comma-separated subset of: " + ",".join(ALL_WORKLOADS))
+    ap.add_argument("--e2e-steps", type=int, default=5, help="timed end-to-end steps per workload (<= --steps)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    unknown = [n for n in args.workloads if n not in REGISTRY]
+    if unknown:
+        raise SystemExit(f"unknown workloads: {unknown}")
+    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if line:
+        print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

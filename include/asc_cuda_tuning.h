@@ -17,8 +17,8 @@ extern "C" {
 int32_t asc_cuda_vadd_f32_variant(const float* x, const float* y, float* out, int64_t n, int32_t variant,
                                   void* stream);
 
-/* variant: bits 0-7 CTA shape for 2048 < cols <= 4096 (0: 256 threads x 4 vectors, 1: 128 x 8,
- * 2: 512 x 2, 0xff: the shared-memory staged kernel), bits 8-15 CTAs per SM (0 = default). */
+/* variant: bits 0-7 CTA shape for 2048 < cols <= 4096 (0: 512 threads x 2 vectors, 1: 128 x 8,
+ * 3: 256 x 4, 0xff: the shared-memory staged kernel), bits 8-15 CTAs per SM (0 = default). */
 int32_t asc_cuda_softmax_f32_variant(const float* x, float* out, int64_t rows, int64_t cols, int64_t ld,
                                      int32_t variant, void* stream);
 

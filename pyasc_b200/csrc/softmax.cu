@@ -137,6 +137,17 @@ int32_t launch_reg(const float* x, float* out, int64_t rows, int64_t cols, int64
   int sms = 0;
   int32_t rc = aschost::sm_count(&sms);
   if (rc != ASC_OK) return rc;
+  if (ctas_per_sm <= 0) {
+    // two full waves of resident CTAs: whole waves keep every SM busy to the end, the second wave
+    // evens out rows that finish at different times
+    static int occupancy = 0;
+    if (occupancy == 0) {
+      ASC_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occupancy, softmax_rows_reg_kernel<kThreads, kVec>,
+                                                                 kThreads, 0));
+      if (occupancy < 1) occupancy = 1;
+    }
+    ctas_per_sm = 2 * occupancy;
+  }
   int64_t grid = static_cast<int64_t>(sms) * ctas_per_sm;
   if (grid > rows) grid = rows;
   softmax_rows_reg_kernel<kThreads, kVec><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
@@ -155,15 +166,15 @@ int32_t launch_softmax(const float* x, float* out, int64_t rows, int64_t cols, i
   const int per_sm = (variant >> 8) & 0xff;
   const int shape = variant & 0xff;
   if (vec_ok && cols <= 8192 && shape != 0xff) {
-    if (cols <= 512) return launch_reg<128, 1>(x, out, rows, cols, ld, per_sm ? per_sm : 12, stream);
-    if (cols <= 1024) return launch_reg<128, 2>(x, out, rows, cols, ld, per_sm ? per_sm : 12, stream);
-    if (cols <= 2048) return launch_reg<128, 4>(x, out, rows, cols, ld, per_sm ? per_sm : 8, stream);
+    if (cols <= 512) return launch_reg<128, 1>(x, out, rows, cols, ld, per_sm, stream);
+    if (cols <= 1024) return launch_reg<128, 2>(x, out, rows, cols, ld, per_sm, stream);
+    if (cols <= 2048) return launch_reg<128, 4>(x, out, rows, cols, ld, per_sm, stream);
     if (cols <= 4096) {
-      if (shape == 1) return launch_reg<128, 8>(x, out, rows, cols, ld, per_sm ? per_sm : 6, stream);
-      if (shape == 2) return launch_reg<512, 2>(x, out, rows, cols, ld, per_sm ? per_sm : 3, stream);
-      return launch_reg<256, 4>(x, out, rows, cols, ld, per_sm ? per_sm : 6, stream);
+      if (shape == 1) return launch_reg<128, 8>(x, out, rows, cols, ld, per_sm, stream);
+      if (shape == 3) return launch_reg<256, 4>(x, out, rows, cols, ld, per_sm, stream);
+      return launch_reg<512, 2>(x, out, rows, cols, ld, per_sm, stream);
     }
-    return launch_reg<256, 8>(x, out, rows, cols, ld, per_sm ? per_sm : 4, stream);
+    return launch_reg<256, 8>(x, out, rows, cols, ld, per_sm, stream);
   }
   int sms = 0;
   int32_t rc = aschost::sm_count(&sms);
@@ -203,7 +214,7 @@ int32_t asc_cuda_softmax_f32(const float* x, float* out, int64_t rows, int64_t c
   return launch_softmax(x, out, rows, cols, ld, 0, static_cast<cudaStream_t>(stream));
 }
 
-// variant: bits 0-7 CTA shape selector for 2048 < cols <= 4096 (0: 256x4, 1: 128x8, 2: 512x2,
+// variant: bits 0-7 CTA shape selector for 2048 < cols <= 4096 (0: 512x2, 1: 128x8, 3: 256x4,
 // 0xff: force the generic staged kernel); bits 8-15 CTAs per SM (0: default).
 int32_t asc_cuda_softmax_f32_variant(const float* x, float* out, int64_t rows, int64_t cols, int64_t ld,
                                      int32_t variant, void* stream) {
