@@ -29,6 +29,10 @@ int32_t asc_cuda_gemm_debug(const void* A, const void* B, void* C, int64_t M, in
                             uint32_t a_kstep, uint32_t b_lbo, uint32_t b_sbo, uint32_t b_kstep, int32_t max_ctas,
                             void* stream);
 
+/* GEMM kernel selection: 0 choose per problem (default), 1 always the single-CTA 128 x 256 kernel,
+ * 2 the CTA-pair 256 x 256 kernel whenever M > 128.  Process-wide. */
+int32_t asc_cuda_gemm_set_mode(int32_t mode);
+
 #ifdef __cplusplus
 }
 #endif

@@ -62,6 +62,7 @@ TUNING_PROTOTYPES: Dict[str, Sequence] = {
     "asc_cuda_softmax_f32_variant": (P, P, c_int64, c_int64, c_int64, c_int32, P),
     "asc_cuda_gemm_debug": (P, P, P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32,
                             c_uint32, c_uint32, c_uint32, c_uint32, c_uint32, c_int32, P),
+    "asc_cuda_gemm_set_mode": (c_int32, ),
 }
 
 

@@ -53,6 +53,8 @@ struct GemmParams {
   uint32_t* status;
   // bring-up overrides of the shared-memory descriptor fields (0 = use the built-in value)
   uint32_t dbg_a_sbo, dbg_a_kstep, dbg_b_lbo, dbg_b_sbo, dbg_b_kstep;
+  uint32_t dbg_flags;   // bit0: issue no MMAs, bit1: issue no loads (timing experiments; results are garbage)
+  uint32_t dbg_stages;  // use only this many ring stages (0 = all)
 };
 
 struct SharedCtl {
@@ -198,6 +200,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int64_t num_n = (p.N + kBlockN - 1) / kBlockN;
   const int64_t num_tiles = num_m * num_n;
   const int64_t num_kb = (p.K + kBlockK - 1) / kBlockK;
+  const uint32_t n_stages = (p.dbg_stages > 0 && p.dbg_stages < kStages) ? p.dbg_stages : kStages;
 
   if (threadIdx.x == 0) {
     ctl.abort_flag = 0;
@@ -239,14 +242,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           const uint32_t sa = smem_base + stage * kStageBytes;
           const uint32_t sb = sa + kSmemA;
           const int32_t k0 = static_cast<int32_t>(kb * kBlockK);
-          mbar_arrive_expect_tx(full, kStageBytes);
-          tma_load_2d(sa, &tmap_a, full, k0, m0);
+          if (p.dbg_flags & 2) {
+            mbar_arrive(full);
+          } else {
+            mbar_arrive_expect_tx(full, kStageBytes);
+            tma_load_2d(sa, &tmap_a, full, k0, m0);
 #pragma unroll
-          for (int j = 0; j < kNBlocks; ++j)
-            tma_load_2d(sb + j * kBBlockBytes, &tmap_b, full, n0 + j * kNBlockCols, k0);
+            for (int j = 0; j < kNBlocks; ++j)
+              tma_load_2d(sb + j * kBBlockBytes, &tmap_b, full, n0 + j * kNBlockCols, k0);
+          }
         }
         __syncwarp();
-        if (++stage == kStages) {
+        if (++stage == n_stages) {
           stage = 0;
           phase ^= 1;
         }
@@ -282,6 +289,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             const uint64_t ad = adesc + static_cast<uint64_t>((k * a_kstep) >> 4);
             const uint64_t bd = bdesc + static_cast<uint64_t>((k * b_kstep) >> 4);
             const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+            if (p.dbg_flags & 1) continue;
             if (kElemBytes == 2) {
               umma_f16_ss(d_tmem, ad, bd, idesc, accumulate);
             } else {
@@ -292,7 +300,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           if (kb == num_kb - 1) umma_commit(smem_u32(&ctl.tmem_full[acc]));
         }
         __syncwarp();
-        if (++stage == kStages) {
+        if (++stage == n_stages) {
           stage = 0;
           phase ^= 1;
         }
@@ -337,6 +345,204 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2): two CTAs of a cluster compute one 256 x 256 tile.  Each CTA
+// stages its own 128 rows of A and its own 128 columns of B, so every SM reads and fills half as
+// much shared memory per MMA as in the single-CTA kernel; the even CTA issues the 256 x 256 x 32-byte
+// MMAs for both, each CTA keeps its 128 x 256 half of the accumulator in its own tensor memory and
+// runs its own epilogue.
+// ----------------------------------------------------------------------------------------------
+constexpr int kPairStages = 6;
+constexpr int kPairHalfN = kBlockN / 2;                          // columns of B staged per CTA
+constexpr uint32_t kPairSmemB = kPairHalfN * kKBytes;            // 16 KiB
+constexpr uint32_t kPairStageBytes = kSmemA + kPairSmemB;        // 32 KiB per CTA and stage
+constexpr uint32_t kPairSmem = kPairStages * kPairStageBytes + 1024;
+
+struct PairCtl {
+  uint64_t full[kPairStages];    // used in the even CTA: both CTAs' loads of a stage have landed
+  uint64_t empty[kPairStages];   // per CTA: the MMAs reading this stage have retired
+  uint64_t tmem_full[2];         // per CTA: accumulator ready for the epilogue
+  uint64_t tmem_empty[2];        // used in the even CTA: both epilogues have drained the accumulator
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+template <int kElemBytes, int kMode>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+    gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                             const GemmParams p, const uint32_t idesc) {
+  constexpr int kBlockK = kKBytes / kElemBytes;
+  constexpr int kUmmaK = 32 / kElemBytes;
+  constexpr int kNBlockCols = 128 / kElemBytes;            // columns per 128-byte block: 64 or 128
+  constexpr int kNBlocks = kPairHalfN / kNBlockCols;       // 2 or 1 column blocks per CTA
+  constexpr uint32_t kBBlockBytes = kBlockK * 128;
+  constexpr uint32_t kBKStep = kUmmaK * 128;
+  constexpr int kPairM = 2 * kBlockM;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ PairCtl ctl;
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();       // 0: issues the MMAs, 1: peer
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  volatile uint32_t* abort_flag = &ctl.abort_flag;
+
+  const int64_t num_m = (p.M + kPairM - 1) / kPairM;
+  const int64_t num_n = (p.N + kBlockN - 1) / kBlockN;
+  const int64_t num_tiles = num_m * num_n;
+  const int64_t num_kb = (p.K + kBlockK - 1) / kBlockK;
+  const int64_t pair = blockIdx.x >> 1;
+  const int64_t num_pairs = gridDim.x >> 1;
+  const uint32_t n_stages = (p.dbg_stages > 0 && p.dbg_stages < kPairStages) ? p.dbg_stages : kPairStages;
+
+  if (threadIdx.x == 0) {
+    ctl.abort_flag = 0;
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(smem_u32(&ctl.full[s]), 1);    // the even CTA's producer announces both CTAs' bytes
+      mbar_init(smem_u32(&ctl.empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&ctl.tmem_full[a]), 1);
+      mbar_init(smem_u32(&ctl.tmem_empty[a]), 8);   // 4 epilogue warps in each CTA
+    }
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(&ctl.tmem_base), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();            // the peer's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = ctl.tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      int64_t m_blk, n_blk;
+      tile_coords(tile, num_m, num_n, m_blk, n_blk);
+      const int32_t m0 = static_cast<int32_t>(m_blk * kPairM + rank * kBlockM);
+      const int32_t n0 = static_cast<int32_t>(n_blk * kBlockN + rank * kPairHalfN);
+      for (int64_t kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&ctl.empty[stage]), phase ^ 1, abort_flag, p.status, ASC_DEV_TIMEOUT_EMPTY);
+        if (!ok) break;
+        if (lane == 0) {
+          const uint32_t full0 = mapa_shared(smem_u32(&ctl.full[stage]), 0);   // the even CTA's barrier
+          const uint32_t sa = smem_base + stage * kPairStageBytes;
+          const uint32_t sb = sa + kSmemA;
+          const int32_t k0 = static_cast<int32_t>(kb * kBlockK);
+          if (p.dbg_flags & 2) {
+            if (rank == 0) mbar_arrive(smem_u32(&ctl.full[stage]));
+          } else {
+            // The even CTA announces the bytes of both CTAs' loads on its own barrier; the peer only
+            // issues its copies, whose completion bytes are routed to that barrier by the hardware.
+            if (rank == 0) mbar_arrive_expect_tx(smem_u32(&ctl.full[stage]), 2 * kPairStageBytes);
+            tma_load_2d_pair(sa, &tmap_a, full0, k0, m0);
+#pragma unroll
+            for (int j = 0; j < kNBlocks; ++j)
+              tma_load_2d_pair(sb + j * kBBlockBytes, &tmap_b, full0, n0 + j * kNBlockCols, k0);
+          }
+        }
+        __syncwarp();
+        if (++stage == n_stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1 && rank == 0) {
+    // --------------------------- MMA issuer (even CTA only) ---------------------------
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    int64_t local = 0;
+    for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+      const uint32_t acc = static_cast<uint32_t>(local & 1);
+      const uint32_t acc_phase = static_cast<uint32_t>((local >> 1) & 1);
+      ok = mbar_wait(smem_u32(&ctl.tmem_empty[acc]), acc_phase ^ 1, abort_flag, p.status,
+                     ASC_DEV_TIMEOUT_TMEM_EMPTY);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * kBlockN;
+      for (int64_t kb = 0; kb < num_kb; ++kb) {
+        ok = mbar_wait(smem_u32(&ctl.full[stage]), phase, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = smem_base + stage * kPairStageBytes;
+          const uint32_t sb = sa + kSmemA;
+          const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(sb, kBBlockBytes, 1024);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const uint64_t ad = adesc + static_cast<uint64_t>((k * 32) >> 4);
+            const uint64_t bd = bdesc + static_cast<uint64_t>((k * kBKStep) >> 4);
+            const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+            if (p.dbg_flags & 1) continue;
+            if (kElemBytes == 2) {
+              umma_f16_ss_pair(d_tmem, ad, bd, idesc, accumulate);
+            } else {
+              umma_i8_ss_pair(d_tmem, ad, bd, idesc, accumulate);
+            }
+          }
+          umma_commit_pair(smem_u32(&ctl.empty[stage]), 3);                 // frees the stage in both CTAs
+          if (kb == num_kb - 1) umma_commit_pair(smem_u32(&ctl.tmem_full[acc]), 3);
+        }
+        __syncwarp();
+        if (++stage == n_stages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp >= 2) {
+    // ------------------------------ epilogue (both CTAs) ------------------------------
+    const uint32_t quarter = warp & 3;
+    const uint32_t empty0 = mapa_shared(smem_u32(&ctl.tmem_empty[0]), 0);
+    const uint32_t empty1 = mapa_shared(smem_u32(&ctl.tmem_empty[1]), 0);
+    bool ok = true;
+    int64_t local = 0;
+    for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+      int64_t m_blk, n_blk;
+      tile_coords(tile, num_m, num_n, m_blk, n_blk);
+      const uint32_t acc = static_cast<uint32_t>(local & 1);
+      const uint32_t acc_phase = static_cast<uint32_t>((local >> 1) & 1);
+      ok = mbar_wait(smem_u32(&ctl.tmem_full[acc]), acc_phase, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      const int64_t row = m_blk * kPairM + rank * kBlockM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * kBlockN;
+#pragma unroll 1
+      for (int c = 0; c < kBlockN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, r);
+        tmem_ld_wait();
+        epilogue_store_chunk<kMode>(p, r, row, n_blk * kBlockN + c * 32);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc ? empty1 : empty0);
+    }
+  }
+
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync();            // neither CTA leaves while the other may still signal it or read its memory
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 
@@ -428,6 +634,91 @@ int32_t launch_gemm(const void* A, const void* B, int64_t lda, int64_t ldb, CUte
   return ASC_OK;
 }
 
+// 0: choose per problem, 1: always the single-CTA kernel, 2: the CTA-pair kernel whenever it applies
+static int g_gemm_mode = 0;
+static uint32_t g_dbg_flags = 0, g_dbg_stages = 0;
+
+template <int kElemBytes, int kMode>
+int32_t launch_gemm_pair(const void* A, const void* B, int64_t lda, int64_t ldb, CUtensorMapDataType dt,
+                         uint32_t idesc_pair, GemmParams p, int32_t max_ctas, cudaStream_t stream) {
+  constexpr int kBlockK = kKBytes / kElemBytes;
+  constexpr int kNBlockCols = 128 / kElemBytes;
+  CUtensorMap tmap_a, tmap_b;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(lda) * kElemBytes};
+    const uint32_t box[2] = {kBlockK, kBlockM};
+    int32_t rc = aschost::encode_tmap(&tmap_a, dt, 2, A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (rc != ASC_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.K)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(ldb) * kElemBytes};
+    const uint32_t box[2] = {kNBlockCols, kBlockK};
+    int32_t rc = aschost::encode_tmap(&tmap_b, dt, 2, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (rc != ASC_OK) return rc;
+  }
+  int32_t rc = aschost::device_status_word(&p.status);
+  if (rc != ASC_OK) return rc;
+  int sms = 0;
+  rc = aschost::sm_count(&sms);
+  if (rc != ASC_OK) return rc;
+  auto kernel = gemm_tcgen05_pair_kernel<kElemBytes, kMode>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  ASC_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    ASC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem));
+    attr_set[dev] = true;
+  }
+  const int64_t num_tiles = ((p.M + 2 * kBlockM - 1) / (2 * kBlockM)) * ((p.N + kBlockN - 1) / kBlockN);
+  // A persistent grid must be fully resident: ask how many 2-CTA clusters fit at once (SMs that have
+  // no partner inside their GPC cannot host one), otherwise the surplus clusters run as a second wave.
+  static int max_clusters[64] = {0};
+  if (dev >= 0 && dev < 64 && max_clusters[dev] == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(sms - sms % 2));
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = kPairSmem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    ASC_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+    max_clusters[dev] = n > 0 ? n : 1;
+  }
+  int64_t pairs = (dev >= 0 && dev < 64) ? max_clusters[dev] : sms / 2;
+  if (pairs > sms / 2) pairs = sms / 2;
+  if (max_ctas > 0 && pairs > max_ctas / 2) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  if (pairs > num_tiles) pairs = num_tiles;
+  kernel<<<static_cast<unsigned>(2 * pairs), kGemmThreads, kPairSmem, stream>>>(tmap_a, tmap_b, p, idesc_pair);
+  aschost::count_launch();
+  ASC_CUDA_TRY(cudaGetLastError());
+  return ASC_OK;
+}
+
+// Single-CTA kernel for small problems, CTA pairs once there are enough 256 x 256 tiles to fill the GPU.
+template <int kElemBytes, int kMode>
+int32_t dispatch_gemm(const void* A, const void* B, int64_t lda, int64_t ldb, CUtensorMapDataType dt, uint32_t c_fmt,
+                      uint32_t ab_fmt, GemmParams p, int32_t max_ctas, cudaStream_t stream) {
+  p.dbg_flags = g_dbg_flags;
+  p.dbg_stages = g_dbg_stages;
+  const int64_t pair_tiles = ((p.M + 2 * kBlockM - 1) / (2 * kBlockM)) * ((p.N + kBlockN - 1) / kBlockN);
+  const bool use_pair = g_gemm_mode == 2 ? p.M > kBlockM : (g_gemm_mode == 0 && pair_tiles >= 64);
+  if (use_pair) {
+    const uint32_t idesc = make_idesc(c_fmt, ab_fmt, ab_fmt, 0, 1, 2 * kBlockM, kBlockN);
+    return launch_gemm_pair<kElemBytes, kMode>(A, B, lda, ldb, dt, idesc, p, max_ctas, stream);
+  }
+  const uint32_t idesc = make_idesc(c_fmt, ab_fmt, ab_fmt, 0, 1, kBlockM, kBlockN);
+  return launch_gemm<kElemBytes, kMode>(A, B, lda, ldb, dt, idesc, p, max_ctas, stream);
+}
+
 int32_t check_gemm_args(const void* A, const void* B, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
                         int64_t ldc, int elem_bytes) {
   if (A == nullptr || B == nullptr) return ASC_ERR_INVALID_ARG;
@@ -461,14 +752,13 @@ int32_t asc_cuda_gemm_f16(const void* A, const void* B, void* C, int64_t M, int6
   p.accumulate = (flags >> 1) & 1;
   const int out_bytes = out_dtype == 2 ? 4 : 2;
   p.vec_ok = aschost::aligned16(C) && ((ldc * out_bytes) % 16 == 0);
-  const uint32_t idesc = make_idesc(/*c_fmt F32*/ 1, in_dtype, in_dtype, /*a K-major*/ 0, /*b MN-major*/ 1, kBlockM,
-                                    kBlockN);
+  // fp32 accumulator, A K-major, B MN-major (row-major [K, N] read as stored)
   const CUtensorMapDataType dt = in_dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (out_dtype) {
-    case 0: return launch_gemm<2, EPI_F16>(A, B, lda, ldb, dt, idesc, p, 0, s);
-    case 1: return launch_gemm<2, EPI_BF16>(A, B, lda, ldb, dt, idesc, p, 0, s);
-    default: return launch_gemm<2, EPI_F32>(A, B, lda, ldb, dt, idesc, p, 0, s);
+    case 0: return dispatch_gemm<2, EPI_F16>(A, B, lda, ldb, dt, 1, in_dtype, p, 0, s);
+    case 1: return dispatch_gemm<2, EPI_BF16>(A, B, lda, ldb, dt, 1, in_dtype, p, 0, s);
+    default: return dispatch_gemm<2, EPI_F32>(A, B, lda, ldb, dt, 1, in_dtype, p, 0, s);
   }
 }
 
@@ -506,9 +796,9 @@ int32_t asc_cuda_gemm_i8(const int8_t* A, const int8_t* B, int32_t* acc, void* d
   p.ldc = ldc;
   p.vec_ok = (acc == nullptr || (aschost::aligned16(acc) && (ldc * 4) % 16 == 0)) &&
              (deq == nullptr || (aschost::aligned16(deq) && (ldc * 2) % 16 == 0));
-  const uint32_t idesc = make_idesc(/*c_fmt S32*/ 2, /*S8*/ 1, 1, 0, 1, kBlockM, kBlockN);
-  return launch_gemm<1, EPI_I8>(A, B, lda, ldb, CU_TENSOR_MAP_DATA_TYPE_UINT8, idesc, p, 0,
-                                static_cast<cudaStream_t>(stream));
+  // int32 accumulator, signed 8-bit operands
+  return dispatch_gemm<1, EPI_I8>(A, B, lda, ldb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, 1, p, 0,
+                                  static_cast<cudaStream_t>(stream));
 }
 
 // Bring-up hook: same GEMM with descriptor-field overrides and a CTA cap.
@@ -534,18 +824,26 @@ int32_t asc_cuda_gemm_debug(const void* A, const void* B, void* C, int64_t M, in
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (in_dtype == 2) {
     p.vec_ok = aschost::aligned16(C) && (ldc * 4) % 16 == 0;
-    const uint32_t idesc = make_idesc(2, 1, 1, 0, 1, kBlockM, kBlockN);
-    return launch_gemm<1, EPI_I8>(A, B, lda, ldb, CU_TENSOR_MAP_DATA_TYPE_UINT8, idesc, p, max_ctas, s);
+    return dispatch_gemm<1, EPI_I8>(A, B, lda, ldb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, 1, p, max_ctas, s);
   }
   const int out_bytes = out_dtype == 2 ? 4 : 2;
   p.vec_ok = aschost::aligned16(C) && ((ldc * out_bytes) % 16 == 0);
-  const uint32_t idesc = make_idesc(1, in_dtype, in_dtype, 0, 1, kBlockM, kBlockN);
   const CUtensorMapDataType dt = in_dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   switch (out_dtype) {
-    case 0: return launch_gemm<2, EPI_F16>(A, B, lda, ldb, dt, idesc, p, max_ctas, s);
-    case 1: return launch_gemm<2, EPI_BF16>(A, B, lda, ldb, dt, idesc, p, max_ctas, s);
-    default: return launch_gemm<2, EPI_F32>(A, B, lda, ldb, dt, idesc, p, max_ctas, s);
+    case 0: return dispatch_gemm<2, EPI_F16>(A, B, lda, ldb, dt, 1, in_dtype, p, max_ctas, s);
+    case 1: return dispatch_gemm<2, EPI_BF16>(A, B, lda, ldb, dt, 1, in_dtype, p, max_ctas, s);
+    default: return dispatch_gemm<2, EPI_F32>(A, B, lda, ldb, dt, 1, in_dtype, p, max_ctas, s);
   }
+}
+
+// Tuning hook: 0 choose per problem, 1 always single-CTA tiles, 2 CTA pairs whenever M > 128.
+int32_t asc_cuda_gemm_set_mode(int32_t mode) {
+  // bits 0-3 kernel choice, bits 8-9 timing-experiment flags, bits 16-19 ring stages to use
+  if ((mode & 0xf) > 2) return ASC_ERR_INVALID_ARG;
+  g_gemm_mode = mode & 0xf;
+  g_dbg_flags = (mode >> 8) & 3;
+  g_dbg_stages = (mode >> 16) & 0xf;
+  return ASC_OK;
 }
 
 }  // extern "C"
