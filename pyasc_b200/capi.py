@@ -73,11 +73,7 @@ def load(build_if_missing: bool = True) -> ctypes.CDLL:
         return _lib
     path = _build.lib_path()
     if build_if_missing and not _build.is_current():
-        try:
-            path = _build.build()
-        except Exception:
-            if not path.exists():
-                raise
+        path = _build.build()   # a failed build raises: a stale library is never used silently
     if not path.exists():
         raise RuntimeError(f"{path} is missing: run `python -m pyasc_b200.build` (needs nvcc); "
                            "there is no CPU fallback for the CUDA platform")

@@ -60,6 +60,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <bool kBf16>
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   if (kBf16) {
@@ -116,11 +122,11 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, AttnCtl& ctl, 
     }
     float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      mx0 = fmaxf(mx0, __uint_as_float(s[0][i]));
-      mx1 = fmaxf(mx1, __uint_as_float(s[1][i]));
-      mx2 = fmaxf(mx2, __uint_as_float(s[2][i]));
-      mx3 = fmaxf(mx3, __uint_as_float(s[3][i]));
+    for (int i = 0; i < 32; i += 2) {
+      mx0 = max3(mx0, __uint_as_float(s[0][i]), __uint_as_float(s[0][i + 1]));
+      mx1 = max3(mx1, __uint_as_float(s[1][i]), __uint_as_float(s[1][i + 1]));
+      mx2 = max3(mx2, __uint_as_float(s[2][i]), __uint_as_float(s[2][i + 1]));
+      mx3 = max3(mx3, __uint_as_float(s[3][i]), __uint_as_float(s[3][i + 1]));
     }
     const float row_max = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
 
@@ -156,8 +162,11 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, AttnCtl& ctl, 
       uint32_t pk[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
+        // one MUFU ex2 per score: measured faster than the packed fp16 ex2 (same special-function
+        // rate, plus unpacking for the row sum)
         const float e0 = ex2_approx(fmaf(__uint_as_float(s[c][2 * i]), sl2, neg_m));
         const float e1 = ex2_approx(fmaf(__uint_as_float(s[c][2 * i + 1]), sl2, neg_m));
+        pk[i] = pack2<kBf16>(e0, e1);
         if (i & 1) {
           l2 += e0;
           l3 += e1;
@@ -165,7 +174,6 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, AttnCtl& ctl, 
           l0 += e0;
           l1 += e1;
         }
-        pk[i] = pack2<kBf16>(e0, e1);
       }
       tmem_st_32x32b_x16(t_s + c * 16, pk);
     }
