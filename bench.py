@@ -594,7 +594,17 @@ def main() -> None:
     unknown = [n for n in args.workloads if n not in REGISTRY]
     if unknown:
         raise SystemExit(f"unknown workloads: {unknown}")
-    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    # Libraries (NCCL's version banner, for one) write to stdout; the contract is ONE JSON line there.
+    # Everything else goes to stderr: stdout is parked on a duplicate descriptor until the line is ready.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    finally:
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
+        os.close(real_stdout)
     if line:
         print(json.dumps(line), flush=True)
 
