@@ -112,6 +112,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Warp-wide wait with a single poller: lane 0 spins on the barrier, the result is broadcast with a
+// shuffle (which also reconverges the warp).  A warp-wide try_wait costs ~250 cycles even on a
+// completed phase because the 32 lanes' barrier accesses are serialised; one lane costs a few tens.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
+                                               uint32_t* status, uint32_t err_code) {
+  uint32_t ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, status, err_code) ? 1u : 0u;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 // ---------------------------------- TMA -----------------------------------
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -51,10 +51,7 @@ struct GemmParams {
   int32_t accumulate;   // EPI_F32 only: C += A @ B
   int32_t vec_ok;       // 16-byte vector stores allowed (alignment of c/deq and ldc)
   uint32_t* status;
-  // bring-up overrides of the shared-memory descriptor fields (0 = use the built-in value)
-  uint32_t dbg_a_sbo, dbg_a_kstep, dbg_b_lbo, dbg_b_sbo, dbg_b_kstep;
-  uint32_t dbg_flags;   // bit0: issue no MMAs, bit1: issue no loads (timing experiments; results are garbage)
-  uint32_t dbg_stages;  // use only this many ring stages (0 = all)
+  uint32_t group_m;     // M blocks per rasterisation group (0 = default)
 };
 
 struct SharedCtl {
@@ -67,11 +64,11 @@ struct SharedCtl {
 };
 
 __device__ __forceinline__ void tile_coords(int64_t tile, int64_t num_m, int64_t num_n, int64_t& m_blk,
-                                            int64_t& n_blk) {
-  const int64_t group_sz = static_cast<int64_t>(kGroupM) * num_n;
+                                            int64_t& n_blk, int64_t group_m = kGroupM) {
+  const int64_t group_sz = group_m * num_n;
   const int64_t g = tile / group_sz;
-  const int64_t first_m = g * kGroupM;
-  const int64_t gm = (num_m - first_m) < kGroupM ? (num_m - first_m) : kGroupM;
+  const int64_t first_m = g * group_m;
+  const int64_t gm = (num_m - first_m) < group_m ? (num_m - first_m) : group_m;
   const int64_t r = tile - g * group_sz;
   m_blk = first_m + r % gm;
   n_blk = r / gm;
@@ -200,7 +197,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   const int64_t num_n = (p.N + kBlockN - 1) / kBlockN;
   const int64_t num_tiles = num_m * num_n;
   const int64_t num_kb = (p.K + kBlockK - 1) / kBlockK;
-  const uint32_t n_stages = (p.dbg_stages > 0 && p.dbg_stages < kStages) ? p.dbg_stages : kStages;
 
   if (threadIdx.x == 0) {
     ctl.abort_flag = 0;
@@ -227,33 +223,30 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
+    // one thread runs the whole loop: waits by a single poller are an order of magnitude cheaper
+    // than warp-wide ones, and nothing here needs the other lanes
     uint32_t stage = 0, phase = 0;
-    bool ok = true;
+    bool ok = lane == 0;
     for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int64_t m_blk, n_blk;
-      tile_coords(tile, num_m, num_n, m_blk, n_blk);
+      tile_coords(tile, num_m, num_n, m_blk, n_blk, p.group_m ? p.group_m : kGroupM);
       const int32_t m0 = static_cast<int32_t>(m_blk * kBlockM);
       const int32_t n0 = static_cast<int32_t>(n_blk * kBlockN);
       for (int64_t kb = 0; kb < num_kb; ++kb) {
         ok = mbar_wait(smem_u32(&ctl.empty[stage]), phase ^ 1, abort_flag, p.status, ASC_DEV_TIMEOUT_EMPTY);
         if (!ok) break;
-        if (lane == 0) {
+        {
           const uint32_t full = smem_u32(&ctl.full[stage]);
           const uint32_t sa = smem_base + stage * kStageBytes;
           const uint32_t sb = sa + kSmemA;
           const int32_t k0 = static_cast<int32_t>(kb * kBlockK);
-          if (p.dbg_flags & 2) {
-            mbar_arrive(full);
-          } else {
-            mbar_arrive_expect_tx(full, kStageBytes);
-            tma_load_2d(sa, &tmap_a, full, k0, m0);
+          mbar_arrive_expect_tx(full, kStageBytes);
+          tma_load_2d(sa, &tmap_a, full, k0, m0);
 #pragma unroll
-            for (int j = 0; j < kNBlocks; ++j)
-              tma_load_2d(sb + j * kBBlockBytes, &tmap_b, full, n0 + j * kNBlockCols, k0);
-          }
+          for (int j = 0; j < kNBlocks; ++j)
+            tma_load_2d(sb + j * kBBlockBytes, &tmap_b, full, n0 + j * kNBlockCols, k0);
         }
-        __syncwarp();
-        if (++stage == n_stages) {
+        if (++stage == kStages) {
           stage = 0;
           phase ^= 1;
         }
@@ -262,7 +255,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   } else if (warp == 1) {
     // ------------------------------- MMA issuer -------------------------------
     uint32_t stage = 0, phase = 0;
-    bool ok = true;
+    bool ok = lane == 0;   // single-thread loop, see the producer
     int64_t local = 0;
     for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
       const uint32_t acc = static_cast<uint32_t>(local & 1);
@@ -276,20 +269,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         ok = mbar_wait(smem_u32(&ctl.full[stage]), phase, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
         if (!ok) break;
         tc_fence_after();
-        if (lane == 0) {
+        {
           const uint32_t sa = smem_base + stage * kStageBytes;
           const uint32_t sb = sa + kSmemA;
-          const uint64_t adesc = make_smem_desc_sw128(sa, 16, p.dbg_a_sbo ? p.dbg_a_sbo : 1024);
-          const uint64_t bdesc = make_smem_desc_sw128(sb, p.dbg_b_lbo ? p.dbg_b_lbo : kBBlockBytes,
-                                                      p.dbg_b_sbo ? p.dbg_b_sbo : 1024);
-          const uint32_t a_kstep = p.dbg_a_kstep ? p.dbg_a_kstep : 32;
-          const uint32_t b_kstep = p.dbg_b_kstep ? p.dbg_b_kstep : kBKStep;
+          const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
+          const uint64_t bdesc = make_smem_desc_sw128(sb, kBBlockBytes, 1024);
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            const uint64_t ad = adesc + static_cast<uint64_t>((k * a_kstep) >> 4);
-            const uint64_t bd = bdesc + static_cast<uint64_t>((k * b_kstep) >> 4);
+            const uint64_t ad = adesc + static_cast<uint64_t>((k * 32) >> 4);
+            const uint64_t bd = bdesc + static_cast<uint64_t>((k * kBKStep) >> 4);
             const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-            if (p.dbg_flags & 1) continue;
             if (kElemBytes == 2) {
               umma_f16_ss(d_tmem, ad, bd, idesc, accumulate);
             } else {
@@ -299,8 +288,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           umma_commit(smem_u32(&ctl.empty[stage]));
           if (kb == num_kb - 1) umma_commit(smem_u32(&ctl.tmem_full[acc]));
         }
-        __syncwarp();
-        if (++stage == n_stages) {
+        if (++stage == kStages) {
           stage = 0;
           phase ^= 1;
         }
@@ -313,10 +301,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     int64_t local = 0;
     for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
       int64_t m_blk, n_blk;
-      tile_coords(tile, num_m, num_n, m_blk, n_blk);
+      tile_coords(tile, num_m, num_n, m_blk, n_blk, p.group_m ? p.group_m : kGroupM);
       const uint32_t acc = static_cast<uint32_t>(local & 1);
       const uint32_t acc_phase = static_cast<uint32_t>((local >> 1) & 1);
-      ok = mbar_wait(smem_u32(&ctl.tmem_full[acc]), acc_phase, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait_warp(smem_u32(&ctl.tmem_full[acc]), acc_phase, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
       const int64_t row = m_blk * kBlockM + quarter * 32 + lane;
@@ -334,6 +322,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
   }
 
+  __syncwarp();
   if (*abort_flag) {
     // a wait ran out somewhere: give copies and MMAs still in flight time to land before
     // shared and tensor memory are released
@@ -397,7 +386,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   const int64_t num_kb = (p.K + kBlockK - 1) / kBlockK;
   const int64_t pair = blockIdx.x >> 1;
   const int64_t num_pairs = gridDim.x >> 1;
-  const uint32_t n_stages = (p.dbg_stages > 0 && p.dbg_stages < kPairStages) ? p.dbg_stages : kPairStages;
 
   if (threadIdx.x == 0) {
     ctl.abort_flag = 0;
@@ -426,34 +414,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
     uint32_t stage = 0, phase = 0;
-    bool ok = true;
+    bool ok = lane == 0;   // single-thread loop
     for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs) {
       int64_t m_blk, n_blk;
-      tile_coords(tile, num_m, num_n, m_blk, n_blk);
+      tile_coords(tile, num_m, num_n, m_blk, n_blk, p.group_m ? p.group_m : kGroupM);
       const int32_t m0 = static_cast<int32_t>(m_blk * kPairM + rank * kBlockM);
       const int32_t n0 = static_cast<int32_t>(n_blk * kBlockN + rank * kPairHalfN);
       for (int64_t kb = 0; kb < num_kb; ++kb) {
         ok = mbar_wait(smem_u32(&ctl.empty[stage]), phase ^ 1, abort_flag, p.status, ASC_DEV_TIMEOUT_EMPTY);
         if (!ok) break;
-        if (lane == 0) {
+        {
           const uint32_t full0 = mapa_shared(smem_u32(&ctl.full[stage]), 0);   // the even CTA's barrier
           const uint32_t sa = smem_base + stage * kPairStageBytes;
           const uint32_t sb = sa + kSmemA;
           const int32_t k0 = static_cast<int32_t>(kb * kBlockK);
-          if (p.dbg_flags & 2) {
-            if (rank == 0) mbar_arrive(smem_u32(&ctl.full[stage]));
-          } else {
-            // The even CTA announces the bytes of both CTAs' loads on its own barrier; the peer only
-            // issues its copies, whose completion bytes are routed to that barrier by the hardware.
-            if (rank == 0) mbar_arrive_expect_tx(smem_u32(&ctl.full[stage]), 2 * kPairStageBytes);
-            tma_load_2d_pair(sa, &tmap_a, full0, k0, m0);
+          // The even CTA announces the bytes of both CTAs' loads on its own barrier; the peer only
+          // issues its copies, whose completion bytes are routed to that barrier by the hardware.
+          if (rank == 0) mbar_arrive_expect_tx(smem_u32(&ctl.full[stage]), 2 * kPairStageBytes);
+          tma_load_2d_pair(sa, &tmap_a, full0, k0, m0);
 #pragma unroll
-            for (int j = 0; j < kNBlocks; ++j)
-              tma_load_2d_pair(sb + j * kBBlockBytes, &tmap_b, full0, n0 + j * kNBlockCols, k0);
-          }
+          for (int j = 0; j < kNBlocks; ++j)
+            tma_load_2d_pair(sb + j * kBBlockBytes, &tmap_b, full0, n0 + j * kNBlockCols, k0);
         }
-        __syncwarp();
-        if (++stage == n_stages) {
+        if (++stage == kPairStages) {
           stage = 0;
           phase ^= 1;
         }
@@ -462,7 +445,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   } else if (warp == 1 && rank == 0) {
     // --------------------------- MMA issuer (even CTA only) ---------------------------
     uint32_t stage = 0, phase = 0;
-    bool ok = true;
+    bool ok = lane == 0;   // single-thread loop
     int64_t local = 0;
     for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
       const uint32_t acc = static_cast<uint32_t>(local & 1);
@@ -476,7 +459,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
         ok = mbar_wait(smem_u32(&ctl.full[stage]), phase, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
         if (!ok) break;
         tc_fence_after();
-        if (lane == 0) {
+        {
           const uint32_t sa = smem_base + stage * kPairStageBytes;
           const uint32_t sb = sa + kSmemA;
           const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
@@ -486,7 +469,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
             const uint64_t ad = adesc + static_cast<uint64_t>((k * 32) >> 4);
             const uint64_t bd = bdesc + static_cast<uint64_t>((k * kBKStep) >> 4);
             const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
-            if (p.dbg_flags & 1) continue;
             if (kElemBytes == 2) {
               umma_f16_ss_pair(d_tmem, ad, bd, idesc, accumulate);
             } else {
@@ -496,8 +478,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           umma_commit_pair(smem_u32(&ctl.empty[stage]), 3);                 // frees the stage in both CTAs
           if (kb == num_kb - 1) umma_commit_pair(smem_u32(&ctl.tmem_full[acc]), 3);
         }
-        __syncwarp();
-        if (++stage == n_stages) {
+        if (++stage == kPairStages) {
           stage = 0;
           phase ^= 1;
         }
@@ -512,10 +493,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     int64_t local = 0;
     for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
       int64_t m_blk, n_blk;
-      tile_coords(tile, num_m, num_n, m_blk, n_blk);
+      tile_coords(tile, num_m, num_n, m_blk, n_blk, p.group_m ? p.group_m : kGroupM);
       const uint32_t acc = static_cast<uint32_t>(local & 1);
       const uint32_t acc_phase = static_cast<uint32_t>((local >> 1) & 1);
-      ok = mbar_wait(smem_u32(&ctl.tmem_full[acc]), acc_phase, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait_warp(smem_u32(&ctl.tmem_full[acc]), acc_phase, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
       const int64_t row = m_blk * kPairM + rank * kBlockM + quarter * 32 + lane;
@@ -533,6 +514,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     }
   }
 
+  __syncwarp();
   if (*abort_flag) {
     const uint64_t t0 = global_timer_ns();
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
@@ -636,7 +618,7 @@ int32_t launch_gemm(const void* A, const void* B, int64_t lda, int64_t ldb, CUte
 
 // 0: choose per problem, 1: always the single-CTA kernel, 2: the CTA-pair kernel whenever it applies
 static int g_gemm_mode = 0;
-static uint32_t g_dbg_flags = 0, g_dbg_stages = 0;
+static uint32_t g_group_m = 0;
 
 template <int kElemBytes, int kMode>
 int32_t launch_gemm_pair(const void* A, const void* B, int64_t lda, int64_t ldb, CUtensorMapDataType dt,
@@ -707,8 +689,7 @@ int32_t launch_gemm_pair(const void* A, const void* B, int64_t lda, int64_t ldb,
 template <int kElemBytes, int kMode>
 int32_t dispatch_gemm(const void* A, const void* B, int64_t lda, int64_t ldb, CUtensorMapDataType dt, uint32_t c_fmt,
                       uint32_t ab_fmt, GemmParams p, int32_t max_ctas, cudaStream_t stream) {
-  p.dbg_flags = g_dbg_flags;
-  p.dbg_stages = g_dbg_stages;
+  p.group_m = g_group_m;
   const int64_t pair_tiles = ((p.M + 2 * kBlockM - 1) / (2 * kBlockM)) * ((p.N + kBlockN - 1) / kBlockN);
   const bool use_pair = g_gemm_mode == 2 ? p.M > kBlockM : (g_gemm_mode == 0 && pair_tiles >= 64);
   if (use_pair) {
@@ -816,11 +797,11 @@ int32_t asc_cuda_gemm_debug(const void* A, const void* B, void* C, int64_t M, in
   p.N = N;
   p.K = K;
   p.ldc = ldc;
-  p.dbg_a_sbo = a_sbo;
-  p.dbg_a_kstep = a_kstep;
-  p.dbg_b_lbo = b_lbo;
-  p.dbg_b_sbo = b_sbo;
-  p.dbg_b_kstep = b_kstep;
+  (void)a_sbo;
+  (void)a_kstep;
+  (void)b_lbo;
+  (void)b_sbo;
+  (void)b_kstep;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (in_dtype == 2) {
     p.vec_ok = aschost::aligned16(C) && (ldc * 4) % 16 == 0;
@@ -838,11 +819,10 @@ int32_t asc_cuda_gemm_debug(const void* A, const void* B, void* C, int64_t M, in
 
 // Tuning hook: 0 choose per problem, 1 always single-CTA tiles, 2 CTA pairs whenever M > 128.
 int32_t asc_cuda_gemm_set_mode(int32_t mode) {
-  // bits 0-3 kernel choice, bits 8-9 timing-experiment flags, bits 16-19 ring stages to use
+  // bits 0-3 kernel choice, bits 20-27 M blocks per rasterisation group (0 = default)
   if ((mode & 0xf) > 2) return ASC_ERR_INVALID_ARG;
   g_gemm_mode = mode & 0xf;
-  g_dbg_flags = (mode >> 8) & 3;
-  g_dbg_stages = (mode >> 16) & 0xf;
+  g_group_m = (mode >> 20) & 0xff;
   return ASC_OK;
 }
 
