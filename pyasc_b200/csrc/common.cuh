@@ -75,15 +75,29 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+// kHintNs > 0: the waiting thread is suspended in hardware until the phase completes or the hint
+// expires, instead of re-issuing the poll; that leaves issue slots and power to the working warps
+// (measured: +7 % on the GEMMs, -4 % on attention, whose softmax warps must wake as fast as possible).
+template <int kHintNs = 0>
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
+  if (kHintNs > 0) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(kHintNs)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+  }
   return ok != 0;
 }
 
@@ -93,13 +107,14 @@ constexpr uint64_t kWaitLimitNs = 400ull * 1000ull * 1000ull;
 
 // Bounded wait.  `abort_flag` lives in shared memory and is raised by whichever
 // thread of the CTA times out first; `status` is the kernel's global status word.
+template <int kHintNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* status, uint32_t err_code) {
-  if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait<kHintNs>(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 0xff) == 0) {
+    if (mbar_try_wait<kHintNs>(bar, parity)) return true;
+    if ((it & (kHintNs > 0 ? 0x3 : 0xff)) == 0) {
       if (*abort_flag) return false;
       uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
@@ -115,10 +130,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // Warp-wide wait with a single poller: lane 0 spins on the barrier, the result is broadcast with a
 // shuffle (which also reconverges the warp).  A warp-wide try_wait costs ~250 cycles even on a
 // completed phase because the 32 lanes' barrier accesses are serialised; one lane costs a few tens.
+template <int kHintNs = 0>
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                                uint32_t* status, uint32_t err_code) {
   uint32_t ok = 1;
-  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, status, err_code) ? 1u : 0u;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait<kHintNs>(bar, parity, abort_flag, status, err_code) ? 1u : 0u;
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 

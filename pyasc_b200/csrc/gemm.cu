@@ -31,7 +31,14 @@ constexpr int kKBytes = 128;  // bytes of K per stage and per swizzle span
 constexpr int kStages = 4;
 constexpr int kGemmThreads = 192;
 constexpr int kTmemCols = 512;
-constexpr int kGroupM = 16;  // tile rasterisation: M blocks per L2 reuse group
+#ifndef ASC_GEMM_GROUP_M
+#define ASC_GEMM_GROUP_M 16
+#endif
+#ifndef ASC_GEMM_HINT_NS
+#define ASC_GEMM_HINT_NS 1000
+#endif
+constexpr int kGroupM = ASC_GEMM_GROUP_M;  // tile rasterisation: M blocks per L2 reuse group
+constexpr int kWaitHintNs = ASC_GEMM_HINT_NS;  // mbarrier waits sleep in hardware instead of spinning
 
 constexpr uint32_t kSmemA = kBlockM * kKBytes;                // 16 KiB per stage
 constexpr uint32_t kSmemB = kBlockN * kKBytes;                // 32 KiB per stage
@@ -233,7 +240,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int32_t m0 = static_cast<int32_t>(m_blk * kBlockM);
       const int32_t n0 = static_cast<int32_t>(n_blk * kBlockN);
       for (int64_t kb = 0; kb < num_kb; ++kb) {
-        ok = mbar_wait(smem_u32(&ctl.empty[stage]), phase ^ 1, abort_flag, p.status, ASC_DEV_TIMEOUT_EMPTY);
+        ok = mbar_wait<kWaitHintNs>(smem_u32(&ctl.empty[stage]), phase ^ 1, abort_flag, p.status, ASC_DEV_TIMEOUT_EMPTY);
         if (!ok) break;
         {
           const uint32_t full = smem_u32(&ctl.full[stage]);
@@ -260,13 +267,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
       const uint32_t acc = static_cast<uint32_t>(local & 1);
       const uint32_t acc_phase = static_cast<uint32_t>((local >> 1) & 1);
-      ok = mbar_wait(smem_u32(&ctl.tmem_empty[acc]), acc_phase ^ 1, abort_flag, p.status,
+      ok = mbar_wait<kWaitHintNs>(smem_u32(&ctl.tmem_empty[acc]), acc_phase ^ 1, abort_flag, p.status,
                      ASC_DEV_TIMEOUT_TMEM_EMPTY);
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * kBlockN;
       for (int64_t kb = 0; kb < num_kb; ++kb) {
-        ok = mbar_wait(smem_u32(&ctl.full[stage]), phase, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
+        ok = mbar_wait<kWaitHintNs>(smem_u32(&ctl.full[stage]), phase, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
         if (!ok) break;
         tc_fence_after();
         {
@@ -304,7 +311,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       tile_coords(tile, num_m, num_n, m_blk, n_blk, p.group_m ? p.group_m : kGroupM);
       const uint32_t acc = static_cast<uint32_t>(local & 1);
       const uint32_t acc_phase = static_cast<uint32_t>((local >> 1) & 1);
-      ok = mbar_wait_warp(smem_u32(&ctl.tmem_full[acc]), acc_phase, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait_warp<kWaitHintNs>(smem_u32(&ctl.tmem_full[acc]), acc_phase, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
       const int64_t row = m_blk * kBlockM + quarter * 32 + lane;
@@ -421,7 +428,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       const int32_t m0 = static_cast<int32_t>(m_blk * kPairM + rank * kBlockM);
       const int32_t n0 = static_cast<int32_t>(n_blk * kBlockN + rank * kPairHalfN);
       for (int64_t kb = 0; kb < num_kb; ++kb) {
-        ok = mbar_wait(smem_u32(&ctl.empty[stage]), phase ^ 1, abort_flag, p.status, ASC_DEV_TIMEOUT_EMPTY);
+        ok = mbar_wait<kWaitHintNs>(smem_u32(&ctl.empty[stage]), phase ^ 1, abort_flag, p.status, ASC_DEV_TIMEOUT_EMPTY);
         if (!ok) break;
         {
           const uint32_t full0 = mapa_shared(smem_u32(&ctl.full[stage]), 0);   // the even CTA's barrier
@@ -450,13 +457,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
     for (int64_t tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
       const uint32_t acc = static_cast<uint32_t>(local & 1);
       const uint32_t acc_phase = static_cast<uint32_t>((local >> 1) & 1);
-      ok = mbar_wait(smem_u32(&ctl.tmem_empty[acc]), acc_phase ^ 1, abort_flag, p.status,
+      ok = mbar_wait<kWaitHintNs>(smem_u32(&ctl.tmem_empty[acc]), acc_phase ^ 1, abort_flag, p.status,
                      ASC_DEV_TIMEOUT_TMEM_EMPTY);
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + acc * kBlockN;
       for (int64_t kb = 0; kb < num_kb; ++kb) {
-        ok = mbar_wait(smem_u32(&ctl.full[stage]), phase, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
+        ok = mbar_wait<kWaitHintNs>(smem_u32(&ctl.full[stage]), phase, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
         if (!ok) break;
         tc_fence_after();
         {
@@ -496,7 +503,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       tile_coords(tile, num_m, num_n, m_blk, n_blk, p.group_m ? p.group_m : kGroupM);
       const uint32_t acc = static_cast<uint32_t>(local & 1);
       const uint32_t acc_phase = static_cast<uint32_t>((local >> 1) & 1);
-      ok = mbar_wait_warp(smem_u32(&ctl.tmem_full[acc]), acc_phase, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL);
+      ok = mbar_wait_warp<kWaitHintNs>(smem_u32(&ctl.tmem_full[acc]), acc_phase, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
       const int64_t row = m_blk * kPairM + rank * kBlockM + quarter * 32 + lane;
