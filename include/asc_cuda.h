@@ -76,6 +76,12 @@ int32_t HostUnregisterWrapper(void* hostPtr);
  * python/asc/lib/profiling/profiler.py:59-129): CUDA events on the launching stream.
  * ---------------------------------------------------------------------------------------- */
 int32_t asc_cuda_event_create(void** ev);
+/* ordering-only event (no timestamps) and a stream-side wait on an event: the launcher uses them to
+ * overlap uploads, kernels and downloads of one launch on three streams.  No reference counterpart
+ * (the reference launcher copies, launches and copies back strictly in sequence,
+ * python/asc/runtime/launcher.py:176-195). */
+int32_t asc_cuda_event_create_notiming(void** ev);
+int32_t StreamWaitEventWrapper(void* stm, void* ev);
 int32_t asc_cuda_event_record(void* ev, void* stream);
 int32_t asc_cuda_event_synchronize(void* ev);
 int32_t asc_cuda_event_elapsed_ms(void* start, void* stop, float* ms);

@@ -59,6 +59,20 @@ class Step:
         return f"Step({self.fn_name}: {self.note})"
 
 
+class PipelineSpec:
+    """How a one-call plan that overwrites its outputs completely splits into independent chunks along
+    its unit axis (elements, softmax rows, GEMM rows of A and C, attention heads), so that the launcher
+    can overlap the upload of chunk i+1, the kernel of chunk i and the download of chunk i-1."""
+
+    def __init__(self, units: int, granule: int, streamed: Dict[int, int], resident: set,
+                 make_steps: Callable[[int, int], List["Step"]]):
+        self.units = units            # length of the unit axis
+        self.granule = granule        # chunk boundaries are multiples of this many units
+        self.streamed = streamed      # argument index -> bytes per unit (argument is sliced along the axis)
+        self.resident = resident      # argument indices every chunk needs whole (uploaded first)
+        self.make_steps = make_steps  # C-ABI calls for units [lo, hi)
+
+
 class Plan:
 
     def __init__(self, pattern: str):
@@ -68,6 +82,7 @@ class Plan:
         self.writes: set = set()      # ... and writes
         self.partial_writes: set = set()  # written arguments whose buffer is not overwritten completely
         self.temps: Dict[str, int] = {}  # temp-buffer key -> bytes
+        self.pipeline: Optional[PipelineSpec] = None
 
     def __repr__(self) -> str:
         return f"Plan({self.pattern}, steps={self.steps}, reads={sorted(self.reads)}, writes={sorted(self.writes)})"
@@ -292,11 +307,16 @@ def _match_elementwise(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     plan.writes.add(out_idx)
     if intervals != [(0, out_t.base.numel)]:
         plan.partial_writes.add(out_idx)
-    for lo, hi in intervals:
+    def make(lo: int, hi: int) -> List[Step]:
         def build(ptrs, stream, lo=lo, hi=hi):
             args = [_p(ptrs[i] + 4 * lo) for i in in_idx]
             return (*args, _p(ptrs[out_idx] + 4 * lo), ctypes.c_int64(hi - lo), stream)
-        plan.steps.append(Step(fn_name, build, f"[{lo}, {hi})"))
+        return [Step(fn_name, build, f"[{lo}, {hi})")]
+
+    for lo, hi in intervals:
+        plan.steps += make(lo, hi)
+    if not plan.partial_writes and len(intervals) == 1:
+        plan.pipeline = PipelineSpec(intervals[0][1], 1 << 16, {i: 4 for i in in_idx + [out_idx]}, set(), make)
     return plan
 
 
@@ -380,12 +400,17 @@ def _match_softmax(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     plan.writes.add(out_idx)
     if not (intervals == [(0, R)] and col0 == 0 and tile_cols == C and R * C == out_t.base.numel):
         plan.partial_writes.add(out_idx)
-    for lo, hi in intervals:
+    def make(lo: int, hi: int) -> List[Step]:
         def build(ptrs, stream, lo=lo, hi=hi):
             byte_off = 4 * (lo * C + col0)
             return (_p(ptrs[in_idx] + byte_off), _p(ptrs[out_idx] + byte_off), ctypes.c_int64(hi - lo),
                     ctypes.c_int64(tile_cols), ctypes.c_int64(C), stream)
-        plan.steps.append(Step("asc_cuda_softmax_f32", build, f"rows [{lo}, {hi}) x {tile_cols} cols"))
+        return [Step("asc_cuda_softmax_f32", build, f"rows [{lo}, {hi}) x {tile_cols} cols")]
+
+    for lo, hi in intervals:
+        plan.steps += make(lo, hi)
+    if not plan.partial_writes:
+        plan.pipeline = PipelineSpec(R, 1, {in_idx: 4 * C, out_idx: 4 * C}, set(), make)
     return plan
 
 
@@ -635,49 +660,63 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
     osz = out_t.dtype.sizeof()
     lda, ldb, ldc = a_cols, b_cols, c_cols
     flags = 1 if epi.relu else 0
-    for (r0, c0, a0, b0, k0, M, N, K) in calls:
+    sa_idx = sb_idx = None
+    if in_dtype == KT.int8:
+        if epi.relu:
+            raise _unsupported("ReLU on an int8 matmul")
+        if epi.row_scale is not None:
+            if out_t.dtype != KT.float16:
+                raise _unsupported("dequantised int8 matmul must be stored as float16")
+            sa_idx, sb_idx = epi.row_scale.tensor.base.index, epi.col_scale.tensor.base.index
+            plan.reads.update((sa_idx, sb_idx))
+    elif in_dtype == KT.float32 or in_dtype.name in _DTYPE_CODE_16:
+        if out_t.dtype.name not in _OUT_CODE:
+            raise _unsupported(f"matmul result type {out_t.dtype}")
+    else:
+        raise _unsupported(f"matmul on {in_dtype} operands")
+
+    def gemm_step(r0: int, c0: int, a0: int, b0: int, k0: int, M: int, N: int, K: int) -> Step:
         a_off, b_off, c_off = (a0 * lda + k0) * es, (k0 * ldb + b0) * es, (r0 * ldc + c0) * osz
         dims = (ctypes.c_int64(M), ctypes.c_int64(N), ctypes.c_int64(K), ctypes.c_int64(lda), ctypes.c_int64(ldb),
                 ctypes.c_int64(ldc))
         note = f"C[{r0}:{r0 + M}, {c0}:{c0 + N}] = A[{a0}:, {k0}:{k0 + K}] @ B[{k0}:, {b0}:]"
         if in_dtype == KT.int8:
-            if epi.relu:
-                raise _unsupported("ReLU on an int8 matmul")
-            if epi.row_scale is not None:
-                if out_t.dtype != KT.float16:
-                    raise _unsupported("dequantised int8 matmul must be stored as float16")
-                sa_idx, sb_idx = epi.row_scale.tensor.base.index, epi.col_scale.tensor.base.index
-                plan.reads.update((sa_idx, sb_idx))
-
-                def build(ptrs, stream, a_off=a_off, b_off=b_off, c_off=c_off, dims=dims, a0=a0, b0=b0,
-                          sa_idx=sa_idx, sb_idx=sb_idx):
+            if sa_idx is not None:
+                def build(ptrs, stream):
                     return (_p(ptrs[a_idx] + a_off), _p(ptrs[b_idx] + b_off), None, _p(ptrs[c_idx] + c_off),
                             _p(ptrs[sa_idx] + 4 * a0), _p(ptrs[sb_idx] + 4 * b0), *dims, stream)
             else:
-                def build(ptrs, stream, a_off=a_off, b_off=b_off, c_off=c_off, dims=dims):
+                def build(ptrs, stream):
                     return (_p(ptrs[a_idx] + a_off), _p(ptrs[b_idx] + b_off), _p(ptrs[c_idx] + c_off), None, None,
                             None, *dims, stream)
-            plan.steps.append(Step("asc_cuda_gemm_i8", build, note))
-        elif in_dtype == KT.float32:
-            if out_t.dtype.name not in _OUT_CODE:
-                raise _unsupported(f"matmul result type {out_t.dtype}")
-            oc = _OUT_CODE[out_t.dtype.name]
-
-            def build(ptrs, stream, a_off=a_off, b_off=b_off, c_off=c_off, dims=dims, oc=oc):
+            return Step("asc_cuda_gemm_i8", build, note)
+        oc = _OUT_CODE[out_t.dtype.name]
+        if in_dtype == KT.float32:
+            def build(ptrs, stream):
                 return (_p(ptrs[a_idx] + a_off), _p(ptrs[b_idx] + b_off), _p(ptrs[c_idx] + c_off), *dims,
                         ctypes.c_int32(oc), ctypes.c_int32(flags), stream)
-            plan.steps.append(Step("asc_cuda_gemm_f32", build, note))
-        elif in_dtype.name in _DTYPE_CODE_16:
-            if out_t.dtype.name not in _OUT_CODE:
-                raise _unsupported(f"matmul result type {out_t.dtype}")
-            ic, oc = _DTYPE_CODE_16[in_dtype.name], _OUT_CODE[out_t.dtype.name]
+            return Step("asc_cuda_gemm_f32", build, note)
+        ic = _DTYPE_CODE_16[in_dtype.name]
 
-            def build(ptrs, stream, a_off=a_off, b_off=b_off, c_off=c_off, dims=dims, ic=ic, oc=oc):
-                return (_p(ptrs[a_idx] + a_off), _p(ptrs[b_idx] + b_off), _p(ptrs[c_idx] + c_off), *dims,
-                        ctypes.c_int32(ic), ctypes.c_int32(oc), ctypes.c_int32(flags), stream)
-            plan.steps.append(Step("asc_cuda_gemm_f16", build, note))
-        else:
-            raise _unsupported(f"matmul on {in_dtype} operands")
+        def build(ptrs, stream):
+            return (_p(ptrs[a_idx] + a_off), _p(ptrs[b_idx] + b_off), _p(ptrs[c_idx] + c_off), *dims,
+                    ctypes.c_int32(ic), ctypes.c_int32(oc), ctypes.c_int32(flags), stream)
+        return Step("asc_cuda_gemm_f16", build, note)
+
+    for call in calls:
+        plan.steps.append(gemm_step(*call))
+    # one full-output call whose operands are plain global tensors: rows of A and C can be streamed
+    if (len(calls) == 1 and c_idx not in plan.partial_writes and calls[0][2] == 0 and calls[0][3] == 0 and
+            calls[0][4] == 0 and all(isinstance(i, int) for i in (a_idx, b_idx, c_idx)) and
+            len({a_idx, b_idx, c_idx}) == 3 and in_dtype != KT.float32):
+        _, _, _, _, _, M, N, K = calls[0]
+        streamed = {a_idx: lda * es, c_idx: ldc * osz}
+        resident = {b_idx}
+        if sa_idx is not None:
+            streamed[sa_idx] = 4
+            resident.add(sb_idx)
+        plan.pipeline = PipelineSpec(M, 256, streamed, resident,
+                                     lambda lo, hi: [gemm_step(lo, 0, lo, 0, 0, hi - lo, N, K)])
     return True
 
 
@@ -769,11 +808,20 @@ def _match_attention(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         plan.partial_writes.add(idx[3])
     heads = rows // S
 
-    def build(ptrs, stream):
-        return (_p(ptrs[idx[0]]), _p(ptrs[idx[1]]), _p(ptrs[idx[2]]), _p(ptrs[idx[3]]), ctypes.c_int32(heads),
-                ctypes.c_int32(1), ctypes.c_int32(S), ctypes.c_int32(D), ctypes.c_float(scale),
-                ctypes.c_int32(int(causal)), ctypes.c_int32(_DTYPE_CODE_16[dt.name]), stream)
-    plan.steps.append(Step("asc_cuda_attn_fwd_f16", build, f"{heads} heads x {S} x {D}, causal={causal}"))
+    head_bytes = S * D * 2
+
+    def make(lo: int, hi: int) -> List[Step]:
+        def build(ptrs, stream, lo=lo, hi=hi):
+            off = lo * head_bytes
+            return (_p(ptrs[idx[0]] + off), _p(ptrs[idx[1]] + off), _p(ptrs[idx[2]] + off), _p(ptrs[idx[3]] + off),
+                    ctypes.c_int32(hi - lo), ctypes.c_int32(1), ctypes.c_int32(S), ctypes.c_int32(D),
+                    ctypes.c_float(scale), ctypes.c_int32(int(causal)), ctypes.c_int32(_DTYPE_CODE_16[dt.name]),
+                    stream)
+        return [Step("asc_cuda_attn_fwd_f16", build, f"{hi - lo} heads x {S} x {D}, causal={causal}")]
+
+    plan.steps += make(0, heads)
+    if not plan.partial_writes and len(set(idx)) == 4:
+        plan.pipeline = PipelineSpec(heads, 1, {i: head_bytes for i in idx}, set(), make)
     return plan
 
 
@@ -813,6 +861,8 @@ def build_plan(trace: KernelTrace) -> Plan:
                 raise _unsupported("several stores that each need temporary buffers")
             total.temps[k] = v
     total.pattern = "+".join(names)
+    if len(stores) == 1 and not total.temps:
+        total.pipeline = plan.pipeline
     total.reads = {i for i in total.reads if isinstance(i, int)}
     total.writes = {i for i in total.writes if isinstance(i, int)}
     total.partial_writes = {i for i in total.partial_writes if isinstance(i, int)}

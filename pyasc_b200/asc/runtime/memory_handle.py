@@ -39,6 +39,13 @@ class _HostMirror(MemoryHandle):
     def _host_ptr(self) -> int:
         raise NotImplementedError
 
+    def host_ptr(self) -> int:
+        return self._host_ptr()
+
+    def is_pinned(self) -> bool:
+        """True when the host buffer is page-locked, i.e. asynchronous copies really are asynchronous."""
+        return False
+
     def copy_to_device(self, stream=None) -> int:
         self.handle = rt.copy_data_to_device(ctypes.c_void_p(self._host_ptr()), self.nbytes, stream)
         return int(self.handle.value)
@@ -93,6 +100,12 @@ class TorchCpuTensorHandle(_HostMirror):
 
     def _host_ptr(self) -> int:
         return self.tensor.data_ptr()
+
+    def is_pinned(self) -> bool:
+        try:
+            return bool(self.tensor.is_pinned())
+        except RuntimeError:   # no CUDA context available to ask
+            return False
 
 
 class TorchCudaTensorArgument(MemoryHandle):

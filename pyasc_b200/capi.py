@@ -38,6 +38,8 @@ PROTOTYPES: Dict[str, Sequence] = {
     "HostRegisterWrapper": (P, c_uint64),
     "HostUnregisterWrapper": (P,),
     "asc_cuda_event_create": (P,),
+    "asc_cuda_event_create_notiming": (P,),
+    "StreamWaitEventWrapper": (P, P),
     "asc_cuda_event_record": (P, P),
     "asc_cuda_event_synchronize": (P,),
     "asc_cuda_event_elapsed_ms": (P, P, P),

@@ -307,6 +307,20 @@ int32_t asc_cuda_event_record(void* ev, void* stream) {
   return ASC_OK;
 }
 
+int32_t StreamWaitEventWrapper(void* stm, void* ev) {
+  if (ev == nullptr) return ASC_ERR_INVALID_ARG;
+  ASC_CUDA_TRY(cudaStreamWaitEvent(static_cast<cudaStream_t>(stm), static_cast<cudaEvent_t>(ev), 0));
+  return ASC_OK;
+}
+
+int32_t asc_cuda_event_create_notiming(void** ev) {
+  if (ev == nullptr) return ASC_ERR_INVALID_ARG;
+  cudaEvent_t e = nullptr;
+  ASC_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  *ev = e;
+  return ASC_OK;
+}
+
 int32_t asc_cuda_event_synchronize(void* ev) {
   if (ev == nullptr) return ASC_ERR_INVALID_ARG;
   ASC_CUDA_TRY(cudaEventSynchronize(static_cast<cudaEvent_t>(ev)));

@@ -198,3 +198,59 @@ def test_user_stream_and_profiler():
             T.vadd_launch(xh, yh, oh, core_num=16, tile_size=4096)
     assert task_time_median(prof.last_result.tasks, skip=1) > 0
     assert rt.launch_count() > 0
+
+
+# ------------------------------------------------------------------------- chunked (pipelined) launches
+def _pinned(*tensors):
+    return [t.pin_memory() for t in tensors]
+
+
+def test_pipelined_launch_matches_plain_launch(monkeypatch):
+    """Page-locked host arguments of >= 16 MiB take the three-stream chunked path; results must be
+    identical to the one-shot path and to the oracle."""
+    from asc.runtime import launcher
+    calls = []
+    real = launcher.Launcher._run_pipelined
+    monkeypatch.setattr(launcher.Launcher, "_run_pipelined", lambda self, plan, handles: (calls.append(plan.pattern),
+                                                                                          real(self, plan, handles))[1])
+    # softmax: 4096 x 4096 fp32
+    x = G.softmax_input(4096, 4096)
+    (xp, ) = _pinned(x)
+    out = torch.empty_like(x).pin_memory()
+    T.softmax_launch(xp, out)
+    G.assert_softmax_close(out, G.softmax(x))
+    plain = torch.empty_like(x)
+    T.softmax_launch(x, plain)                                # pageable memory: one-shot path
+    assert torch.equal(out, plain)
+    # vector add with a ragged size
+    n = (1 << 23) + 12345
+    a, b = G.vadd_inputs(n)
+    ap, bp = _pinned(a, b)
+    o = torch.empty(n).pin_memory()
+    T.vadd_launch(ap, bp, o, core_num=64, tile_size=1 << 14)
+    G.assert_exact(o, a + b)
+    # fp16 GEMM 4096 x 2048 x 2048 and int8 GEMM with dequantisation
+    ga, gb = G.gemm_f16_inputs(4096, 2048, 2048)
+    gap, gbp = _pinned(ga, gb)
+    gc = torch.empty(4096, 2048, dtype=torch.float16).pin_memory()
+    T.matmul_fp16_launch(gap, gbp, gc)
+    gplain = torch.empty(4096, 2048, dtype=torch.float16)
+    T.matmul_fp16_launch(ga, gb, gplain)
+    assert torch.equal(gc, gplain)
+    rows = torch.arange(0, 4096, 97)
+    G.assert_half_close(gc[rows], G.gemm_f16(ga[rows], gb))
+    ia, ib, sa, sb = G.gemm_i8_inputs(4096, 2048, 1024)
+    iap, ibp, sap, sbp = _pinned(ia, ib, sa, sb)
+    dq = torch.empty(4096, 2048, dtype=torch.float16).pin_memory()
+    T.matmul_int8_dequant_launch(iap, ibp, sap, sbp, dq)
+    G.assert_exact(dq[rows], G.dequant(G.gemm_i8(ia[rows], ib), sa[rows], sb))
+    # attention 2 x 8 x 1024 x 128
+    q, k, v = G.attention_inputs(2, 8, 1024)
+    qp, kp, vp = _pinned(q, k, v)
+    ao = torch.empty_like(q).pin_memory()
+    T.attention_launch(qp, kp, vp, ao, causal=True)
+    aplain = torch.empty_like(q)
+    T.attention_launch(q, k, v, aplain, causal=True)
+    assert torch.equal(ao, aplain)
+    G.assert_half_close(ao[:, :2], G.attention(q[:, :2], k[:, :2], v[:, :2], True))
+    assert calls == ["softmax", "elementwise:asc_cuda_vadd_f32", "matmul", "matmul", "attention"], calls
