@@ -138,15 +138,15 @@ int32_t launch_reg(const float* x, float* out, int64_t rows, int64_t cols, int64
   int32_t rc = aschost::sm_count(&sms);
   if (rc != ASC_OK) return rc;
   if (ctas_per_sm <= 0) {
-    // two full waves of resident CTAs: whole waves keep every SM busy to the end, the second wave
-    // evens out rows that finish at different times
+    // four full waves of resident CTAs: whole waves keep every SM busy to the end, and several of
+    // them even out rows that finish at different times (measured: 6.37 vs 6.22 TB/s with two)
     static int occupancy = 0;
     if (occupancy == 0) {
       ASC_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occupancy, softmax_rows_reg_kernel<kThreads, kVec>,
                                                                  kThreads, 0));
       if (occupancy < 1) occupancy = 1;
     }
-    ctas_per_sm = 2 * occupancy;
+    ctas_per_sm = 4 * occupancy;
   }
   int64_t grid = static_cast<int64_t>(sms) * ctas_per_sm;
   if (grid > rows) grid = rows;
