@@ -116,6 +116,29 @@ int32_t asc_cuda_vadd_f32(const float* x, const float* y, float* out, int64_t n,
  * matching NumPy.  Replaces python/test/asc2/kernels/test_vmuladd.py:16-31. */
 int32_t asc_cuda_vmuladd_f32(const float* x, const float* y, const float* z, float* out, int64_t n, void* stream);
 
+/* out[i] = f(in_0[i], ..., in_{k-1}[i]) for i in [0, n): any expression of the asc2 elementwise ops
+ * over same-shaped operands, evaluated in one pass over memory.  The expression is a postfix program
+ * of n_ops (<= 48) opcodes over an 8-deep stack of 32-bit words (fp32 values, or int32 for the
+ * integer opcodes); args[j] is the input index of a LOAD or the 32-bit word a CONST pushes.  Opcodes: 0 LOAD, 1 CONST, 2 ADD, 3 SUB, 4 MUL, 5 DIV, 6 MAX, 7 MIN, 8 NEG,
+ * 9 ABS, 10 RELU, 11 EXP, 12 EXP2, 13 LOG, 14 LOG2, 15 SQRT, 16 RSQRT, 17 SIN, 18 COS, 19 TAN,
+ * 20 SINH, 21 COSH, 22 TANH, 23 ERF, 24 FLOOR, 25 CEIL, 26 EQ, 27 NE, 28 GT, 29 GE, 30 LT, 31 LE
+ * (comparisons push 1.0 / 0.0), 32 WHERE (cond, a, b -> cond != 0 ? a : b), 33 ROUND_F16,
+ * 34 ROUND_BF16 (round the top of the stack through that type, so that a chain of 16-bit ops rounds
+ * like a per-op evaluation); on int32 stack words 35 IADD, 36 ISUB, 37 IMUL, 38 IMAX, 39 IMIN,
+ * 40 ISHL, 41 ISHR (arithmetic), 42 IEQ, 43 INE, 44 IGT, 45 IGE, 46 ILT, 47 ILE, 48 INEG, 49 IABS,
+ * 50 IRELU, 51 CVT_I2F, 52 CVT_F2I (truncating), 53 WRAP_I16 (sign-extend the low half); with the
+ * operands swapped (rhs op lhs) 54 RSUB, 55 RDIV, 56 IRSUB, 57 IRSHL, 58 IRSHR.  A binary opcode
+ * with bit 8 set (| 0x100) takes args[j] as its left operand instead of a stack entry.
+ * Element types: 0 fp32, 1 fp16, 2 bf16, 3 int32, 4 int16; at most 6 inputs.
+ * The program is validated on the host (status 1 for a malformed one, 6 for a stack deeper than 8).
+ * Replaces the per-op vector calls the reference lowers such kernels to
+ * (python/asc/language/tile/binary_ops.py, unary_ops.py, indexing_ops.py:where;
+ * lib/Conversion/LowerToAsc/LowerArithBinary.cpp, LowerMath.cpp), e.g. the kernels of
+ * python/test/asc2/kernels/test_leaky_relu.py:16-27 and test_gelu.py:16-34. */
+int32_t asc_cuda_eltwise_program(const int32_t* ops, const int32_t* args, int32_t n_ops, const void* const* inputs,
+                                 const int32_t* input_types, int32_t n_inputs, void* out, int32_t out_type,
+                                 int64_t n, void* stream);
+
 /* Row softmax over the last dimension of a contiguous [rows, cols] fp32 matrix with max
  * subtraction.  `ld` is the row pitch in elements (>= cols).  Replaces both asc2 softmax forms:
  * the manual reduce_max/exp/reduce_sum kernel (python/test/asc2/kernels/test_softmax.py:16-27;

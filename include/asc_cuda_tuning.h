@@ -34,6 +34,10 @@ int32_t asc_cuda_gemm_debug(const void* A, const void* B, void* C, int64_t M, in
  * 2 the CTA-pair 256 x 256 kernel whenever M > 128.  Process-wide. */
 int32_t asc_cuda_gemm_set_mode(int32_t mode);
 
+/* Elements each thread evaluates per opcode dispatch in asc_cuda_eltwise_program's aligned path:
+ * 4, 8 (default) or 16.  Process-wide. */
+int32_t asc_cuda_eltwise_set_lanes(int32_t lanes);
+
 #ifdef __cplusplus
 }
 #endif

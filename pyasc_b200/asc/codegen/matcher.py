@@ -11,7 +11,7 @@ of each tensor the blocks would have touched together.  For that it
 2. checks that the touched tiles form contiguous ranges / full tile grids and merges them;
 3. emits :class:`Step` objects, each one C-ABI call with concrete sizes and byte offsets.
 
-A kernel that fits no pattern raises ``NotImplementedError``: there is no interpreter, Triton or CPU
+A kernel that fits no pattern raises ``NotImplementedError``: there is no host-side interpreter, Triton or CPU
 fallback behind this module.
 """
 from __future__ import annotations
@@ -279,7 +279,7 @@ def _match_elementwise(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     if fn_name is None:
         return None
     if value.dtype != KT.float32 or out_t.dtype != KT.float32 or any(v.tensor.dtype != KT.float32 for v in operands):
-        raise _unsupported(f"elementwise add / multiply-add on {value.dtype} tiles (float32 only)")
+        return None  # the generic elementwise program handles the other types
     window = _flat_window(out_t, offsets, value.shape)
     if window is None:
         raise _unsupported("elementwise kernel whose tiles are not contiguous ranges of the tensor")
@@ -317,6 +317,232 @@ def _match_elementwise(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         plan.steps += make(lo, hi)
     if not plan.partial_writes and len(intervals) == 1:
         plan.pipeline = PipelineSpec(intervals[0][1], 1 << 16, {i: 4 for i in in_idx + [out_idx]}, set(), make)
+    return plan
+
+
+# --------------------------------------------------------------------------------------------------
+# Pattern: any elementwise expression over same-offset loads -> one postfix program, one pass
+# --------------------------------------------------------------------------------------------------
+_OP_LOAD, _OP_CONST, _OP_WHERE, _OP_ROUND_F16, _OP_ROUND_BF16 = 0, 1, 32, 33, 34
+_BINARY_CODE = {"add": 2, "sub": 3, "mul": 4, "div": 5, "max": 6, "min": 7}
+_UNARY_CODE = {"neg": 8, "abs": 9, "relu": 10, "exp": 11, "exp2": 12, "log": 13, "log2": 14, "sqrt": 15, "rsqrt": 16,
+               "sin": 17, "cos": 18, "tan": 19, "sinh": 20, "cosh": 21, "tanh": 22, "erf": 23, "floor": 24, "ceil": 25}
+_COMPARE_CODE = {"eq": 26, "ne": 27, "gt": 28, "ge": 29, "lt": 30, "le": 31}
+_INT_BINARY_CODE = {"add": 35, "sub": 36, "mul": 37, "max": 38, "min": 39, "shl": 40, "shr": 41}
+_INT_COMPARE_CODE = {"eq": 42, "ne": 43, "gt": 44, "ge": 45, "lt": 46, "le": 47}
+_INT_UNARY_CODE = {"neg": 48, "abs": 49, "relu": 50}
+_OP_CVT_I2F, _OP_CVT_F2I, _OP_WRAP_I16 = 51, 52, 53
+_ELT_TYPE = {"float32": 0, "float16": 1, "bfloat16": 2, "int32": 3, "int16": 4}
+_ROUND_CODE = {"float16": _OP_ROUND_F16, "bfloat16": _OP_ROUND_BF16, "int16": _OP_WRAP_I16}
+ELT_MAX_OPS, ELT_MAX_INPUTS, ELT_MAX_STACK = 48, 6, 8
+
+
+def _round_const(value: float, dtype: DataType) -> float:
+    """A scalar operand takes the tile's type (python/asc/language/tile/utils.py:73-94)."""
+    if dtype.name == "float16":
+        return float(np.float16(value))
+    if dtype.name == "bfloat16":
+        bits = np.array([value], dtype=np.float32).view(np.uint32).astype(np.uint64)
+        bits = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) << 16  # round to nearest even
+        return float(bits.astype(np.uint32).view(np.float32)[0])
+    return float(np.float32(value))
+
+
+_OP_IMM = 0x100
+# opcode whose operands are swapped: _SWAPPED[op](b, a) == op(a, b)
+_SWAPPED = {2: 2, 4: 4, 6: 6, 7: 7, 3: 54, 5: 55, 26: 26, 27: 27, 28: 30, 30: 28, 29: 31, 31: 29,
+            35: 35, 37: 37, 38: 38, 39: 39, 36: 56, 40: 57, 41: 58, 42: 42, 43: 43, 44: 46, 46: 44, 45: 47, 47: 45}
+
+
+class _Frag:
+    """Postfix code that leaves one value on the stack; ``need`` is the stack depth it uses.  A
+    constant is kept as its 32-bit word until its consumer decides between an immediate operand and a
+    CONST push."""
+
+    __slots__ = ("code", "need", "word")
+
+    def __init__(self, code: List[Tuple[int, int]], need: int, word: Optional[int] = None):
+        self.code, self.need, self.word = code, need, word
+
+    def pushed(self) -> "_Frag":
+        return _Frag([(_OP_CONST, self.word)], 1) if self.word is not None else self
+
+
+class _EltProgram:
+    """Compiles the expression tree of a stored tile into a postfix program.  Scalar operands become
+    immediates; of two tile operands the one needing the deeper stack is evaluated first (with the
+    swapped opcode when that reverses the order), which keeps most expressions at depth 2."""
+
+    def __init__(self, shape, offsets, out_t: Tensor):
+        self.shape, self.offsets, self.out_t = shape, offsets, out_t
+        self.inputs: List[Tensor] = []
+        self.ops: List[int] = []
+        self.args: List[int] = []
+        self.max_depth = 0
+
+    @staticmethod
+    def _word(value: Any, dtype: DataType) -> int:
+        """``value`` as a scalar of ``dtype``: a scalar operand takes the tile's type."""
+        if dtype.is_float():
+            return int(np.array([_round_const(float(value), dtype)], dtype=np.float32).view(np.int32)[0])
+        if float(value) != int(value):
+            raise _unsupported(f"scalar {value} combined with a tile of {dtype}")
+        wrapped = np.array([int(value)], dtype=np.int64).astype(np.int16 if dtype.name == "int16" else np.int32)
+        return int(wrapped[0])
+
+    @staticmethod
+    def _rounded(frag: _Frag, dtype: DataType) -> _Frag:
+        if dtype.name in _ROUND_CODE:
+            return _Frag(frag.code + [(_ROUND_CODE[dtype.name], 0)], frag.need)
+        return frag
+
+    def _binary(self, code: int, lhs: _Frag, rhs: _Frag) -> _Frag:
+        if rhs.word is not None and lhs.word is None:
+            return _Frag(lhs.code + [(_SWAPPED[code] | _OP_IMM, rhs.word)], lhs.need)
+        if lhs.word is not None and rhs.word is None:
+            return _Frag(rhs.code + [(code | _OP_IMM, lhs.word)], rhs.need)
+        lhs, rhs = lhs.pushed(), rhs.pushed()
+        if rhs.need > lhs.need:
+            return _Frag(rhs.code + lhs.code + [(_SWAPPED[code], 0)], max(rhs.need, lhs.need + 1))
+        return _Frag(lhs.code + rhs.code + [(code, 0)], max(lhs.need, rhs.need + 1))
+
+    def gen(self, v: Any, scalar_dtype: Optional[DataType] = None) -> Optional[_Frag]:
+        """Code for ``v``, or None when ``v`` is not expressible."""
+        if isinstance(v, PlainValue):
+            if not v.is_const:
+                return None
+            return _Frag([], 0, self._word(v.value, scalar_dtype or v.dtype))
+        if isinstance(v, (bool, int, float)):
+            return _Frag([], 0, self._word(v, scalar_dtype or (KT.float32 if isinstance(v, float) else KT.int32)))
+        if not isinstance(v, Tile) or v.shape != self.shape:
+            return None
+        node = v.node
+        if node.kind == "load":
+            view = resolve_view(v)
+            if view is None or not _same_offsets(view.offsets, self.offsets) or not _is_zero_pad(view):
+                return None
+            if view.tensor.static_shape() != self.out_t.static_shape() or view.tensor.dtype.name not in _ELT_TYPE:
+                return None
+            for k, t in enumerate(self.inputs):
+                if t.base.index == view.tensor.base.index:
+                    return _Frag([(_OP_LOAD, k)], 1) if t.dtype == view.tensor.dtype else None
+            self.inputs.append(view.tensor)
+            return _Frag([(_OP_LOAD, len(self.inputs) - 1)], 1)
+        if node.kind == "full":
+            return self.gen(node.attrs["value"], v.dtype)
+        if v.dtype.name not in _ELT_TYPE and node.kind != "compare":
+            return None
+        if node.kind == "binary":
+            code = (_BINARY_CODE if v.dtype.is_float() else _INT_BINARY_CODE).get(node.attrs["op"])
+            lhs, rhs = self.gen(node.args[0], v.dtype), self.gen(node.args[1], v.dtype)
+            if code is None or lhs is None or rhs is None:
+                return None
+            return self._rounded(self._binary(code, lhs, rhs), v.dtype)
+        if node.kind == "compare":
+            dt = node.args[0].dtype
+            if dt.name not in _ELT_TYPE:
+                return None
+            lhs, rhs = self.gen(node.args[0], dt), self.gen(node.args[1], dt)
+            if lhs is None or rhs is None:
+                return None
+            return self._binary((_COMPARE_CODE if dt.is_float() else _INT_COMPARE_CODE)[node.attrs["mode"]], lhs, rhs)
+        if node.kind == "where":
+            parts = [self.gen(node.args[0]), self.gen(node.args[1], v.dtype), self.gen(node.args[2], v.dtype)]
+            if any(p is None for p in parts) or parts[0].word is not None:
+                return None
+            c, a, b = (p.pushed() for p in parts)
+            return _Frag(c.code + a.code + b.code + [(_OP_WHERE, 0)], max(c.need, a.need + 1, b.need + 2))
+        if node.kind == "unary":
+            code = (_UNARY_CODE if v.dtype.is_float() else _INT_UNARY_CODE).get(node.attrs["op"])
+            src = self.gen(node.args[0])
+            if code is None or src is None:
+                return None
+            src = src.pushed()
+            return self._rounded(_Frag(src.code + [(code, 0)], src.need), v.dtype)
+        if node.kind == "cast":
+            src_t = node.args[0]
+            src = self.gen(src_t) if src_t.dtype.name in _ELT_TYPE else None
+            if src is None:
+                return None
+            src = src.pushed()
+            if src_t.dtype.is_float() != v.dtype.is_float():
+                src = _Frag(src.code + [(_OP_CVT_F2I if src_t.dtype.is_float() else _OP_CVT_I2F, 0)], src.need)
+            return self._rounded(src, v.dtype)
+        return None
+
+    def compile(self, v: Any) -> bool:
+        frag = self.gen(v)
+        if frag is None:
+            return False
+        frag = frag.pushed()
+        self.ops = [c[0] for c in frag.code]
+        self.args = [c[1] for c in frag.code]
+        self.max_depth = frag.need
+        return True
+
+
+def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
+    value, out_t = eff.args
+    offsets = eff.attrs["offsets"]
+    if not isinstance(value, Tile) or out_t.dtype.name not in _ELT_TYPE or value.dtype != out_t.dtype:
+        return None
+    prog = _EltProgram(value.shape, offsets, out_t)
+    if not prog.compile(value) or not prog.inputs:
+        return None
+    if len(prog.ops) > ELT_MAX_OPS or len(prog.inputs) > ELT_MAX_INPUTS or prog.max_depth > ELT_MAX_STACK:
+        raise _unsupported(f"elementwise expression with {len(prog.ops)} operations, {len(prog.inputs)} inputs and a "
+                           f"stack of {prog.max_depth} (limits: {ELT_MAX_OPS}, {ELT_MAX_INPUTS}, {ELT_MAX_STACK})")
+    window = _flat_window(out_t, offsets, value.shape)
+    if window is None:
+        raise _unsupported("elementwise kernel whose tiles are not contiguous ranges of the tensor")
+    _check_fits(out_t)
+    for t in prog.inputs:
+        _check_fits(t)
+    flat_off, tile_elems = window
+    numel = 1
+    for d in out_t.static_shape():
+        numel *= d
+    env = enumerate_instances(trace.core_num, eff.loops)
+    n = env_count(env)
+    starts = eval_int(flat_off, env, n)
+    if starts.size and starts.min() < 0:
+        raise RuntimeError("Negative tile offset in kernel")
+    ends = np.minimum(starts + tile_elems, numel)
+    intervals = merge_intervals(starts, ends)
+    if len(intervals) > MAX_CALLS:
+        raise _unsupported("elementwise kernel touching more than 4096 disjoint ranges")
+
+    plan = Plan("elementwise:program")
+    out_idx = out_t.base.index
+    in_idx = [t.base.index for t in prog.inputs]
+    in_size = [t.dtype.bitwidth // 8 for t in prog.inputs]
+    out_size = out_t.dtype.bitwidth // 8
+    if out_idx in in_idx:
+        raise _unsupported("elementwise kernel that stores into a tensor it also loads")
+    plan.reads.update(in_idx)
+    plan.writes.add(out_idx)
+    if intervals != [(0, out_t.base.numel)]:
+        plan.partial_writes.add(out_idx)
+    n_ops, n_in = len(prog.ops), len(prog.inputs)
+    ops_arr = (ctypes.c_int32 * n_ops)(*prog.ops)
+    args_arr = (ctypes.c_int32 * n_ops)(*prog.args)
+    types_arr = (ctypes.c_int32 * n_in)(*[_ELT_TYPE[t.dtype.name] for t in prog.inputs])
+    out_type = _ELT_TYPE[out_t.dtype.name]
+
+    def make(lo: int, hi: int) -> List[Step]:
+        def build(ptrs, stream, lo=lo, hi=hi):
+            # the library copies the program and the pointer table before it returns
+            ins = (ctypes.c_void_p * n_in)(*[ptrs[i] + sz * lo for i, sz in zip(in_idx, in_size)])
+            return (ops_arr, args_arr, ctypes.c_int32(n_ops), ins, types_arr, ctypes.c_int32(n_in),
+                    _p(ptrs[out_idx] + out_size * lo), ctypes.c_int32(out_type), ctypes.c_int64(hi - lo), stream)
+        return [Step("asc_cuda_eltwise_program", build, f"{n_ops} ops over [{lo}, {hi})")]
+
+    for lo, hi in intervals:
+        plan.steps += make(lo, hi)
+    if not plan.partial_writes and len(intervals) == 1:
+        streamed = {i: sz for i, sz in zip(in_idx, in_size)}
+        streamed[out_idx] = out_size
+        plan.pipeline = PipelineSpec(intervals[0][1], 1 << 16, streamed, set(), make)
     return plan
 
 
@@ -828,7 +1054,7 @@ def _match_attention(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
 # --------------------------------------------------------------------------------------------------
 # Entry point
 # --------------------------------------------------------------------------------------------------
-_MATCHERS = (_match_attention, _match_softmax, _match_elementwise, _match_matmul)
+_MATCHERS = (_match_attention, _match_softmax, _match_elementwise, _match_matmul, _match_eltwise_program)
 
 
 def build_plan(trace: KernelTrace) -> Plan:

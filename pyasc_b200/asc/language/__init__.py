@@ -4,12 +4,12 @@ from .core.constexpr import ConstExpr, require_constexpr
 from .core.dtype import (DataType, KnownTypes, bfloat16, bool_, float16, float32, float64, half, int8, int16,
                          int32, int64, uint8, uint16, uint32, uint64)
 from .core.ir_value import GlobalAddress, PlainValue
-from .core.utils import ceildiv
+from .core.utils import ceildiv, number
 from .tile.range import static_range
 from .tile.ops import block_idx as get_block_idx, block_num as get_block_num
 
 __all__ = [
     "ConstExpr", "require_constexpr", "DataType", "KnownTypes", "bfloat16", "bool_", "float16", "float32", "float64",
     "half", "int8", "int16", "int32", "int64", "uint8", "uint16", "uint32", "uint64", "GlobalAddress", "PlainValue",
-    "ceildiv", "static_range", "get_block_idx", "get_block_num",
+    "ceildiv", "number", "static_range", "get_block_idx", "get_block_num",
 ]

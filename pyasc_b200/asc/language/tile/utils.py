@@ -32,24 +32,39 @@ def check_data_alignment(shape: Tuple[int, ...], dtype: DataType) -> None:
                            f"got {shape[-1]} x {dtype_size} bytes")
 
 
+def _scalar_dtype(v: Any) -> DataType:
+    if isinstance(v, (Tile, PlainValue)):
+        return v.dtype
+    if isinstance(v, bool):
+        return KT.bool_
+    if isinstance(v, int):
+        return KT.int32
+    if isinstance(v, float):
+        return KT.float32
+    raise RuntimeError(f"Cannot infer a dtype for {type(v).__name__}")
+
+
 def infer_dtype(lhs: Any, rhs: Any) -> DataType:
-    """Tile dtype wins over a scalar; between tiles of one kind the wider wins
-    (reference: utils.py:73-94)."""
+    """Common dtype of two operands: a tile's dtype wins over a scalar's; between two tiles or two
+    scalars of one kind the wider wins, and float wins over int of the same width
+    (reference: python/asc/language/tile/utils.py:73-94)."""
+    a, b = _scalar_dtype(lhs), _scalar_dtype(rhs)
+    if a == b:
+        return a
+    if a.is_unsigned() or b.is_unsigned():
+        raise NotImplementedError(f"Unsigned dtype operands not supported, got {a} and {b}")
     lt, rt = isinstance(lhs, Tile), isinstance(rhs, Tile)
+    if lt and not rt:
+        return a
+    if rt and not lt:
+        return b
+    if a.is_float() == b.is_float() and a.bitwidth != b.bitwidth:
+        return a if a.bitwidth > b.bitwidth else b
+    if a.bitwidth == b.bitwidth:
+        return a if a.is_float() else b
     if lt and rt:
-        a, b = lhs.dtype, rhs.dtype
-        if a == b:
-            return a
-        if a.is_unsigned() or b.is_unsigned():
-            raise RuntimeError(f"Unsigned tile types are not supported in binary operations: {a}, {b}")
-        if a.is_float() != b.is_float():
-            return a if a.is_float() else b
-        return a if a.bitwidth >= b.bitwidth else b
-    if lt:
-        return lhs.dtype
-    if rt:
-        return rhs.dtype
-    raise RuntimeError("At least one operand must be a tile")
+        return a if a.is_float() else b   # mixed kinds and widths between tiles: the float one
+    raise RuntimeError(f"Unable to infer common dtype between {a} and {b}")
 
 
 def infer_shape(lhs: Any, rhs: Any) -> Tuple[int, ...]:

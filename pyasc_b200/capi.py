@@ -50,6 +50,7 @@ PROTOTYPES: Dict[str, Sequence] = {
     "asc_cuda_launch_count": (P,),
     "asc_cuda_vadd_f32": (P, P, P, c_int64, P),
     "asc_cuda_vmuladd_f32": (P, P, P, P, c_int64, P),
+    "asc_cuda_eltwise_program": (P, P, c_int32, P, P, c_int32, P, c_int32, c_int64, P),
     "asc_cuda_softmax_f32": (P, P, c_int64, c_int64, c_int64, P),
     "asc_cuda_gemm_f16": (P, P, P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32,
                           c_int32, P),
@@ -65,6 +66,7 @@ TUNING_PROTOTYPES: Dict[str, Sequence] = {
     "asc_cuda_gemm_debug": (P, P, P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32,
                             c_uint32, c_uint32, c_uint32, c_uint32, c_uint32, c_int32, P),
     "asc_cuda_gemm_set_mode": (c_int32, ),
+    "asc_cuda_eltwise_set_lanes": (c_int32, ),
 }
 
 

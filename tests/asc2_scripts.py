@@ -119,3 +119,85 @@ def mn_tiles_per_block(m, n, core_num, m_tile, n_tile, n_tiles_per_block):
     m_tiles_per_block = per_core // n_tiles_per_block
     assert m_tiles % m_tiles_per_block == 0
     return m_tiles_per_block
+
+
+# ---- elementwise kernels (python/test/asc2/kernels/test_{leaky_relu,gelu}.py and
+# ---- python/test/asc2/operations/test_{binary_ops,unary_ops,where}.py)
+@asc2.jit(always_compile=True)
+def leaky_relu(x_ptr: asc.GlobalAddress, alpha: float, out_ptr: asc.GlobalAddress, size: int,
+               tile_size: asc.ConstExpr[int], tile_per_block: asc.ConstExpr[int]):
+    x_gm = asc2.tensor(x_ptr, [size])
+    out_gm = asc2.tensor(out_ptr, [size])
+    base_offset = asc2.block_idx() * tile_size * tile_per_block
+    for i in range(tile_per_block, unroll_factor=2, parallel=True):
+        tile_offset = base_offset + i * tile_size
+        x = asc2.load(x_gm, [tile_size], offsets=[tile_offset])
+        out = asc2.where(x >= 0, x, x * alpha)
+        asc2.store(out, out_gm, offsets=[tile_offset])
+
+
+@asc2.jit(always_compile=True)
+def gelu(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, num_rows: asc.ConstExpr, num_columns: asc.ConstExpr,
+         tile_size: asc.ConstExpr, approximate: asc.ConstExpr):
+    x_gm = asc2.tensor(x_ptr, [num_rows, num_columns])
+    out_gm = asc2.tensor(out_ptr, [num_rows, num_columns])
+    for i in range(asc2.block_idx(), num_rows, asc2.block_num(), parallel=True):
+        row = asc2.load(x_gm, [1, tile_size], offsets=[i, 0])
+        if approximate:
+            pi = 3.141592653589793238462643383279502884
+            k1 = 2 * asc2.sqrt(2 / pi)
+            k2 = 2 * asc2.sqrt(2 / pi) * 0.044715
+            param = row * (row * row * k2 + k1)
+            out = row - row / (asc2.exp(param) + 1)
+        else:
+            k = asc2.sqrt(0.5)
+            out = row * (asc2.erf(row * k) + 1) * 0.5
+        asc2.store(out, out_gm, offsets=[i, 0])
+
+
+VV, VS, SV = "VV", "VS", "SV"
+
+
+@asc2.jit(always_compile=True)
+def binary_op(x_ptr, y_ptr, z_ptr, block_length: asc.ConstExpr, fmt: asc.ConstExpr, op: asc.ConstExpr) -> None:
+    if fmt == VV:
+        xt = asc2.load(asc2.tensor(x_ptr, [32]), [block_length], offsets=[0])
+        yt = asc2.load(asc2.tensor(y_ptr, [32]), [block_length], offsets=[0])
+    elif fmt == VS:
+        xt = asc2.load(asc2.tensor(x_ptr, [32]), [block_length], offsets=[0])
+        yt = y_ptr
+    elif fmt == SV:
+        xt = x_ptr
+        yt = asc2.load(asc2.tensor(y_ptr, [32]), [block_length], offsets=[0])
+    zt = op(xt, yt)
+    asc2.store(zt, asc2.tensor(z_ptr, [32]), offsets=[0])
+
+
+@asc2.jit(always_compile=True)
+def unary_op(x_ptr: asc.GlobalAddress, z_ptr: asc.GlobalAddress, block_length: asc.ConstExpr, op: asc.ConstExpr) -> None:
+    xt = asc2.load(asc2.tensor(x_ptr, [32]), [block_length], offsets=[0])
+    zt = op(xt)
+    asc2.store(zt, asc2.tensor(z_ptr, [32]), offsets=[0])
+
+
+WHERE_SIZE = 32
+
+
+@asc2.jit(always_compile=True)
+def where_op(x_ptr: asc.GlobalAddress, y_ptr: asc.GlobalAddress, z_ptr: asc.GlobalAddress, op: asc.ConstExpr):
+    x = asc2.tensor(x_ptr, [WHERE_SIZE])
+    y = asc2.tensor(y_ptr, [WHERE_SIZE])
+    z = asc2.tensor(z_ptr, [WHERE_SIZE])
+    xt = asc2.load(x, [WHERE_SIZE], offsets=[0])
+    yt = asc2.load(y, [WHERE_SIZE], offsets=[0])
+    zt = asc2.where(op(xt, yt), xt, yt)
+    asc2.store(zt, z, offsets=[0])
+
+
+@asc2.jit(always_compile=True)
+def where_scalar_op(x_ptr: asc.GlobalAddress, scalar, z_ptr: asc.GlobalAddress, op: asc.ConstExpr):
+    x = asc2.tensor(x_ptr, [WHERE_SIZE])
+    z = asc2.tensor(z_ptr, [WHERE_SIZE])
+    xt = asc2.load(x, [WHERE_SIZE], offsets=[0])
+    zt = asc2.where(op(xt, scalar), asc.number(0.0, x_ptr.dtype), asc.number(1.0, x_ptr.dtype))
+    asc2.store(zt, z, offsets=[0])

@@ -1,0 +1,137 @@
+"""Inputs, launches and torch goldens of the elementwise kernels, shared by the CPU tests (compiled
+program evaluated by the CPU oracle) and the GPU tests (the same launches run on the device).  Cases
+and value distributions follow python/test/asc2/operations/test_{binary_ops,unary_ops,where}.py and
+python/test/asc2/kernels/test_{leaky_relu,gelu}.py."""
+import math
+
+import torch
+
+import asc
+import asc2
+
+import asc2_scripts as K
+
+BINARY_OPS = [
+    (asc2.add, torch.add, [K.VV, K.VS, K.SV], [torch.bfloat16, torch.float32, torch.int32]),
+    (asc2.div, torch.div, [K.VV, K.VS, K.SV], [torch.float32]),
+    (asc2.mul, torch.mul, [K.VV, K.VS, K.SV], [torch.bfloat16, torch.float32, torch.int32]),
+    (asc2.sub, torch.sub, [K.VV, K.VS, K.SV], [torch.bfloat16, torch.float32, torch.int32]),
+    (asc2.left_shift, torch.bitwise_left_shift, [K.VS], [torch.int32]),
+    (asc2.right_shift, torch.bitwise_right_shift, [K.VS], [torch.int32]),
+    (asc2.maximum, torch.maximum, [K.VV, K.VS, K.SV], [torch.bfloat16, torch.float32, torch.int32]),
+    (asc2.minimum, torch.minimum, [K.VV, K.VS, K.SV], [torch.bfloat16, torch.float32, torch.int32]),
+]
+BINARY_CASES = [(a, t, f, d) for a, t, fmts, dtypes in BINARY_OPS for f in fmts for d in dtypes]
+
+UNARY_OPS = [
+    (asc2.abs, torch.abs), (asc2.ceil, torch.ceil), (asc2.cos, torch.cos), (asc2.cosh, torch.cosh),
+    (asc2.erf, torch.erf), (asc2.exp, torch.exp), (asc2.exp2, torch.exp2), (asc2.floor, torch.floor),
+    (asc2.log, torch.log), (asc2.negative, torch.neg), (asc2.relu, torch.relu), (asc2.rsqrt, torch.rsqrt),
+    (asc2.sin, torch.sin), (asc2.sinh, torch.sinh), (asc2.sqrt, torch.sqrt), (asc2.tan, torch.tan),
+    (asc2.tanh, torch.tanh),
+]
+
+COMPARE_OPS = [(asc2.equal, torch.eq), (asc2.not_equal, torch.ne), (asc2.greater, torch.gt),
+               (asc2.greater_equal, torch.ge), (asc2.less, torch.lt), (asc2.less_equal, torch.le)]
+WHERE_DTYPES = [torch.float16, torch.bfloat16, torch.float32, torch.int16, torch.int32]
+
+
+def ids(obj) -> str:
+    return obj.__name__ if callable(obj) else str(obj)
+
+
+def binary_case(asc_op, torch_op, fmt, dtype):
+    """Returns (launch, golden, runtime_args): ``launch()`` runs the kernel and returns the output
+    tensor; ``runtime_args`` are the kernel's run-time arguments in order."""
+    size = 32
+    gen = torch.Generator().manual_seed(2026)
+
+    def operand(is_vector: bool):
+        if not is_vector:
+            return torch.tensor(2, dtype=dtype)
+        if dtype.is_floating_point:
+            return torch.randn((size, ), dtype=dtype, generator=gen).clamp(1, 100)
+        return torch.randint(1, 100, (size, ), dtype=dtype, generator=gen)
+
+    x = operand(fmt in (K.VV, K.VS))
+    y = operand(fmt in (K.VV, K.SV))
+    z = torch.zeros(size, dtype=dtype)
+
+    def launch():
+        K.binary_op[1](x, y, z, size, fmt, asc_op)
+        return z
+
+    return launch, torch_op(x, y), [x, y, z]
+
+
+def unary_case(asc_op, torch_op):
+    gen = torch.Generator().manual_seed(2026)
+    x = torch.randn((32, ), dtype=torch.float32, generator=gen).clamp(1, 100)
+    z = torch.zeros(32, dtype=torch.float32)
+
+    def launch():
+        K.unary_op[1](x, z, 32, asc_op)
+        return z
+
+    return launch, torch_op(x), [x, z]
+
+
+def _where_tensor(dtype, gen):
+    if dtype.is_floating_point:
+        return torch.rand(K.WHERE_SIZE, dtype=dtype, generator=gen)
+    return torch.randint(-100, 100, (K.WHERE_SIZE, ), dtype=dtype, generator=gen)
+
+
+def where_case(asc_op, torch_op, dtype, scalar: bool):
+    gen = torch.Generator().manual_seed(2026)
+    x = _where_tensor(dtype, gen)
+    result = torch.zeros_like(x)
+    if scalar:
+        y = torch.tensor(0 if not dtype.is_floating_point else 0.5, dtype=dtype)
+        golden = torch.where(torch_op(x, y), torch.tensor(0, dtype=dtype), torch.tensor(1, dtype=dtype))
+
+        def launch():
+            K.where_scalar_op[1](x, y, result, asc_op)
+            return result
+    else:
+        y = _where_tensor(dtype, gen)
+        y[::5] = x[::5]          # make the equality branches non-trivial
+        golden = torch.where(torch_op(x, y), x, y)
+
+        def launch():
+            K.where_op[1](x, y, result, asc_op)
+            return result
+    return launch, golden, [x, y, result]
+
+
+def leaky_relu_case(size=8192, dtype=torch.bfloat16):
+    gen = torch.Generator().manual_seed(2026)
+    x = (torch.rand(size, generator=gen) * 10.0 - 5.0).to(dtype)
+    alpha = torch.tensor(0.1, dtype=dtype)
+    out = torch.empty_like(x)
+    core_num, tile_size = 16, 128
+    num_tiles = asc.ceildiv(size, tile_size)
+
+    def launch():
+        K.leaky_relu[core_num](x, alpha, out, size, tile_size, asc.ceildiv(num_tiles, core_num))
+        return out
+
+    return launch, torch.where(x >= 0, x, x * alpha), [x, alpha, out, size]
+
+
+def gelu_torch(x: torch.Tensor, approximate: bool):
+    if approximate:
+        return 0.5 * x * (1 + torch.tanh(math.sqrt(2 / math.pi) * (x + 0.044715 * torch.pow(x, 3))))
+    return 0.5 * x * (1 + torch.erf(x / math.sqrt(2)))
+
+
+def gelu_case(approximate: bool, rows=30, cols=1024):
+    gen = torch.Generator().manual_seed(2026)
+    x = torch.rand((rows, cols), dtype=torch.float32, generator=gen)
+    out = torch.empty_like(x)
+
+    def launch():
+        K.gelu[16](x, out, rows, cols, cols, approximate)
+        return out
+
+    return launch, gelu_torch(x, approximate), [x, out]

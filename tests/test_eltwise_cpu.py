@@ -1,0 +1,154 @@
+"""Elementwise asc2 kernels on CPU: the launcher's compiled postfix program, evaluated by the CPU
+oracle, must reproduce the torch goldens of the reference's tests
+(python/test/asc2/operations/test_{binary_ops,unary_ops,where}.py,
+python/test/asc2/kernels/test_{leaky_relu,gelu}.py).  ``DRY_RUN=1`` stops before the device launch."""
+import numpy as np
+import pytest
+import torch
+
+import asc
+import asc2
+
+import asc2_scripts as K
+import eltwise_cases as C
+from oracle import eltwise as E
+
+
+@pytest.fixture(autouse=True)
+def dry_run(monkeypatch):
+    monkeypatch.setenv("DRY_RUN", "1")
+
+
+def decode(step):
+    """(ops, args, runtime-argument index of each input, output index, out_type, n) of a program step."""
+    assert step.fn_name == "asc_cuda_eltwise_program"
+    ptrs = {i: (i + 1) << 32 for i in range(16)}
+    built = step.build(ptrs, None)
+    ops, args, n_ops, ins, types, n_in, out, out_type, n, _ = built
+    assert len(ops) == n_ops.value and len(ins) == n_in.value
+    in_idx = [(int(a) >> 32) - 1 for a in ins]
+    return list(ops), list(args), in_idx, list(types), (out.value >> 32) - 1, out_type.value, n.value
+
+
+def evaluate(jit_fn, runtime_args):
+    plan = jit_fn.last_plan
+    if plan.pattern == "elementwise:asc_cuda_vadd_f32":   # fp32 tile + tile keeps its dedicated kernel
+        assert plan.reads == {0, 1} and plan.writes == {2}
+        return runtime_args[0] + runtime_args[1]
+    assert plan.pattern == "elementwise:program" and len(plan.steps) == 1, plan
+    ops, args, in_idx, types, out_idx, out_type, n = decode(plan.steps[0])
+    inputs = [runtime_args[i].reshape(-1)[:n] for i in in_idx]
+    assert [E.TYPES[t] for t in types] == [t.dtype for t in inputs]
+    assert plan.reads == set(in_idx) and plan.writes == {out_idx}
+    return E.run_program(ops, args, inputs, out_type).reshape(runtime_args[out_idx].shape)
+
+
+def check(out, golden):
+    assert out.dtype == golden.dtype
+    if golden.dtype == torch.float32:
+        assert torch.allclose(out, golden, atol=1e-3)
+    else:
+        assert torch.equal(out, golden)
+
+
+@pytest.mark.parametrize("asc_op, torch_op, fmt, dtype", C.BINARY_CASES, ids=C.ids)
+def test_binary_programs(asc_op, torch_op, fmt, dtype):
+    launch, golden, rt_args = C.binary_case(asc_op, torch_op, fmt, dtype)
+    launch()
+    check(evaluate(K.binary_op, rt_args), golden)
+
+
+@pytest.mark.parametrize("asc_op, torch_op", C.UNARY_OPS, ids=C.ids)
+def test_unary_programs(asc_op, torch_op):
+    launch, golden, rt_args = C.unary_case(asc_op, torch_op)
+    launch()
+    check(evaluate(K.unary_op, rt_args), golden)
+
+
+@pytest.mark.parametrize("scalar", [False, True], ids=["tile", "scalar"])
+@pytest.mark.parametrize("dtype", C.WHERE_DTYPES, ids=str)
+@pytest.mark.parametrize("asc_op, torch_op", C.COMPARE_OPS, ids=C.ids)
+def test_where_programs(asc_op, torch_op, dtype, scalar):
+    launch, golden, rt_args = C.where_case(asc_op, torch_op, dtype, scalar)
+    launch()
+    out = evaluate(K.where_scalar_op if scalar else K.where_op, rt_args)
+    assert torch.equal(out, golden)
+
+
+def test_leaky_relu_program_is_exact_in_bf16():
+    launch, golden, rt_args = C.leaky_relu_case()
+    launch()
+    plan = K.leaky_relu.last_plan
+    # x >= 0 and x * alpha take their scalars as immediates: LOAD, LE|IMM, LOAD, LOAD, MUL|IMM, ROUND, WHERE
+    assert plan.steps[0].note == "7 ops over [0, 8192)" and plan.pipeline is not None
+    ops = decode(plan.steps[0])[0]
+    assert ops == [0, 31 | 0x100, 0, 0, 4 | 0x100, 34, 32]
+    assert torch.equal(evaluate(K.leaky_relu, rt_args), golden)
+
+
+@pytest.mark.parametrize("approximate", [True, False])
+def test_gelu_program(approximate):
+    launch, golden, rt_args = C.gelu_case(approximate)
+    launch()
+    torch.testing.assert_close(evaluate(K.gelu, rt_args), golden, rtol=1e-3, atol=1e-5)
+    # operand reordering keeps the whole expression within two stack levels
+    ops = decode(K.gelu.last_plan.steps[0])[0]
+    depth = peak = 0
+    for op in ops:
+        code, imm = op & 0xff, bool(op & 0x100)
+        depth += 1 if code <= 1 else 0 if imm or code in range(8, 26) or code in (33, 34) else -1
+        peak = max(peak, depth)
+    assert depth == 1 and peak == 2 and len(ops) == (13 if approximate else 7)
+
+
+def test_sixteen_bit_chain_rounds_after_every_op():
+    @asc2.jit
+    def chain(x_ptr: asc.GlobalAddress, y_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+        x = asc2.load(asc2.tensor(x_ptr, [n]), [n], offsets=[0])
+        y = asc2.load(asc2.tensor(y_ptr, [n]), [n], offsets=[0])
+        asc2.store(asc2.exp(x * y + 0.3) - y, asc2.tensor(out_ptr, [n]), offsets=[0])
+    gen = torch.Generator().manual_seed(7)
+    x = torch.rand(256, generator=gen).to(torch.float16)
+    y = torch.rand(256, generator=gen).to(torch.float16)
+    out = torch.empty_like(x)
+    chain[1](x, y, out, 256)
+    golden = torch.exp(x * y + torch.tensor(0.3, dtype=torch.float16)) - y     # every op rounds to fp16
+    assert torch.equal(evaluate(chain, [x, y, out]), golden)
+
+
+def test_cast_between_float_and_int():
+    @asc2.jit
+    def to_int(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+        x = asc2.load(asc2.tensor(x_ptr, [n]), [n], offsets=[0])
+        asc2.store((x * 3.5).to(asc.int32), asc2.tensor(out_ptr, [n]), offsets=[0])
+    x = torch.linspace(-40, 40, 64)
+    out = torch.empty(64, dtype=torch.int32)
+    to_int[1](x, out, 64)
+    assert torch.equal(evaluate(to_int, [x, out]), (x * 3.5).to(torch.int32))
+
+
+def test_program_limits_and_rejections():
+    @asc2.jit
+    def deep(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+        x = asc2.load(asc2.tensor(x_ptr, [n]), [n], offsets=[0])
+        v = x
+        for _ in asc.static_range(60):
+            v = v * 1.5 + x
+        asc2.store(v, asc2.tensor(out_ptr, [n]), offsets=[0])
+    x = torch.zeros(64)
+    with pytest.raises(NotImplementedError, match="limits"):
+        deep[1](x, torch.empty_like(x), 64)
+
+    @asc2.jit
+    def in_place(x_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+        x_gm = asc2.tensor(x_ptr, [n])
+        asc2.store(asc2.exp(asc2.load(x_gm, [n], offsets=[0])), x_gm, offsets=[0])
+    with pytest.raises(NotImplementedError, match="also loads"):
+        in_place[1](x, 64)
+
+    @asc2.jit
+    def shifted(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+        x = asc2.load(asc2.tensor(x_ptr, [2 * n]), [n], offsets=[n])
+        asc2.store(asc2.exp(x), asc2.tensor(out_ptr, [2 * n]), offsets=[0])
+    with pytest.raises(NotImplementedError, match="no kernel for this pattern"):
+        shifted[1](torch.zeros(128), torch.zeros(128), 64)

@@ -1,0 +1,177 @@
+"""The generic elementwise kernel on the GPU: the reference's operation and kernel tests run through
+the asc2 surface (python/test/asc2/operations/test_{binary_ops,unary_ops,where}.py,
+python/test/asc2/kernels/test_{leaky_relu,gelu}.py: same shapes, distributions, goldens, tolerances),
+and the C-ABI entry point itself against the CPU oracle's evaluation of the same program at sizes
+beyond L2.  Bit-exact for arithmetic, comparisons, selects and roundings; transcendental functions
+within atol 1e-3 of torch's CPU result as in the reference's tests."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import asc.runtime.config as config
+
+import asc2_scripts as K
+import eltwise_cases as C
+from oracle import eltwise as E
+from pyasc_b200 import capi
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def select_platform(backend, platform, device_id):
+    config.set_platform(backend, platform, device_id)
+
+
+def check(out, golden):
+    assert out.dtype == golden.dtype
+    if golden.dtype == torch.float32:
+        assert torch.allclose(out, golden, atol=1e-3)
+    else:
+        assert torch.equal(out, golden)
+
+
+# ------------------------------------------------------------------------------- asc2 surface
+@pytest.mark.parametrize("asc_op, torch_op, fmt, dtype", C.BINARY_CASES, ids=C.ids)
+def test_binary_operations(asc_op, torch_op, fmt, dtype):
+    launch, golden, _ = C.binary_case(asc_op, torch_op, fmt, dtype)
+    check(launch(), golden)
+
+
+@pytest.mark.parametrize("asc_op, torch_op", C.UNARY_OPS, ids=C.ids)
+def test_unary_operations(asc_op, torch_op):
+    launch, golden, _ = C.unary_case(asc_op, torch_op)
+    check(launch(), golden)
+
+
+@pytest.mark.parametrize("scalar", [False, True], ids=["tile", "scalar"])
+@pytest.mark.parametrize("dtype", C.WHERE_DTYPES, ids=str)
+@pytest.mark.parametrize("asc_op, torch_op", C.COMPARE_OPS, ids=C.ids)
+def test_where_ops(asc_op, torch_op, dtype, scalar):
+    launch, golden, _ = C.where_case(asc_op, torch_op, dtype, scalar)
+    torch.testing.assert_close(launch(), golden, rtol=0, atol=0)
+
+
+def test_leaky_relu():
+    launch, golden, _ = C.leaky_relu_case()
+    torch.testing.assert_close(launch(), golden)
+    assert torch.equal(launch(), golden)          # one rounded multiply and a select: exact in bf16
+
+
+@pytest.mark.parametrize("approximate", [True, False])
+def test_gelu(approximate):
+    launch, golden, _ = C.gelu_case(approximate)
+    torch.testing.assert_close(launch(), golden, rtol=1e-3, atol=1e-5)
+
+
+def test_gelu_pinned_pipelined_matches_plain():
+    """64 MiB of page-locked input takes the chunked three-stream launch path."""
+    gen = torch.Generator().manual_seed(11)
+    x = torch.rand((16384, 1024), dtype=torch.float32, generator=gen)
+    plain = torch.empty_like(x)
+    K.gelu[16](x, plain, 16384, 1024, 1024, False)
+    xp, outp = x.pin_memory(), torch.empty_like(x).pin_memory()
+    K.gelu[16](xp, outp, 16384, 1024, 1024, False)
+    assert torch.equal(outp, plain)
+    torch.testing.assert_close(plain, C.gelu_torch(x, False), rtol=1e-3, atol=1e-5)
+
+
+# ------------------------------------------------------------------------------- C ABI
+@pytest.fixture(scope="module")
+def lib():
+    torch.cuda.set_device(0)
+    return capi.load()
+
+
+def call(lib, ops, args, inputs, out, out_type, n, expect=0):
+    ops_a = (ctypes.c_int32 * len(ops))(*ops)
+    args_a = (ctypes.c_int32 * len(ops))(*args)
+    ins = (ctypes.c_void_p * max(1, len(inputs)))(*[t.data_ptr() for t in inputs])
+    code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2, torch.int32: 3, torch.int16: 4}
+    types = (ctypes.c_int32 * max(1, len(inputs)))(*[code[t.dtype] for t in inputs])
+    rc = lib.asc_cuda_eltwise_program(ops_a, args_a, len(ops), ins, types, len(inputs),
+                                      ctypes.c_void_p(out.data_ptr()), out_type, n, None)
+    assert rc == expect, f"returned {rc}: {capi.status_string(rc)} {capi.last_cuda_error()}"
+    if rc == 0:
+        capi.check_device_status(None)
+
+
+def fbits(v):
+    return int(np.array([v], dtype=np.float32).view(np.int32)[0])
+
+
+# x * y + 0.25 - max(x, y), every op rounded through the tensor type
+def _arith_program(round_op):
+    r = [(round_op, 0)] if round_op else []
+    prog = [(0, 0), (0, 1), (4, 0)] + r + [(1, fbits(0.25)), (2, 0)] + r + [(0, 0), (0, 1), (6, 0)] + r + [(3, 0)] + r
+    return [p[0] for p in prog], [p[1] for p in prog]
+
+
+@pytest.mark.parametrize("dtype, round_op, out_type", [(torch.float32, None, 0), (torch.float16, 33, 1),
+                                                       (torch.bfloat16, 34, 2)], ids=str)
+@pytest.mark.parametrize("n, offset", [(1, 0), (5, 0), (4099, 0), (4099, 1), ((1 << 25) + 3, 0), ((1 << 22) + 1, 3)])
+def test_program_arithmetic_bit_exact(lib, dtype, round_op, out_type, n, offset):
+    """Sizes around the group-of-four path and its tail, beyond L2 (2 x 128 MiB fp32 in, 128 MiB out),
+    and bases that are not aligned to four elements (scalar path)."""
+    gen = torch.Generator().manual_seed(n + offset)
+    x = (torch.rand(n + offset, generator=gen) * 8 - 4).to(dtype)
+    y = (torch.rand(n + offset, generator=gen) * 8 - 4).to(dtype)
+    xd, yd = x.cuda(), y.cuda()
+    out = torch.zeros(n + offset + 1, dtype=dtype, device="cuda")
+    ops, args = _arith_program(round_op)
+    call(lib, ops, args, [xd[offset:], yd[offset:]], out[offset:], out_type, n)
+    want = E.run_program(ops, args, [x[offset:], y[offset:]], out_type)
+    got = out.cpu()
+    assert torch.equal(got[offset:offset + n], want)
+    assert got[offset + n] == 0 and bool((got[:offset] == 0).all())        # nothing written outside [0, n)
+
+
+def test_program_integer_ops_wrap_like_torch(lib):
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randint(-2**31, 2**31 - 1, (100003, ), dtype=torch.int64, generator=gen).to(torch.int32)
+    y = torch.randint(-2**31, 2**31 - 1, (100003, ), dtype=torch.int64, generator=gen).to(torch.int32)
+    # (x + y) * 3 - min(x, y), then >> 2, then where(x > y, that, -that)
+    prog = [(0, 0), (0, 1), (35, 0), (1, 3), (37, 0), (0, 0), (0, 1), (39, 0), (36, 0), (1, 2), (41, 0)]
+    body_ops, body_args = [p[0] for p in prog], [p[1] for p in prog]
+    ops = [0, 0, 44] + body_ops + body_ops + [48, 32]
+    args = [0, 1, 0] + body_args + body_args + [0, 0]
+    out = torch.zeros(100003, dtype=torch.int32, device="cuda")
+    call(lib, ops, args, [x.cuda(), y.cuda()], out, 3, 100003)
+    assert torch.equal(out.cpu(), E.run_program(ops, args, [x, y], 3))
+    # int16: wrap after the multiply
+    a = torch.randint(-2**15, 2**15 - 1, (4100, ), dtype=torch.int32, generator=gen).to(torch.int16)
+    ops16, args16 = [0, 1, 37, 53], [0, 7, 0, 0]
+    out16 = torch.zeros(4100, dtype=torch.int16, device="cuda")
+    call(lib, ops16, args16, [a.cuda()], out16, 4, 4100)
+    assert torch.equal(out16.cpu(), a * 7)
+
+
+def test_program_transcendentals_close_to_cpu(lib):
+    gen = torch.Generator().manual_seed(5)
+    x = torch.rand(1 << 20, generator=gen) * 4 + 0.5
+    xd = x.cuda()
+    out = torch.empty_like(xd)
+    for op in range(11, 24):
+        call(lib, [0, op], [0, 0], [xd], out, 0, x.numel())
+        want = E.run_program([0, op], [0, 0], [x], 0)
+        torch.testing.assert_close(out.cpu(), want, rtol=2e-6, atol=1e-6, msg=lambda m: f"opcode {op}: {m}")
+
+
+def test_program_rejects_malformed_programs(lib):
+    x = torch.zeros(16, device="cuda")
+    out = torch.zeros(16, device="cuda")
+    call(lib, [0, 2], [0, 0], [x], out, 0, 16, expect=1)                     # ADD with one operand
+    call(lib, [0, 0], [0, 0], [x], out, 0, 16, expect=1)                     # two values left
+    call(lib, [0], [1], [x], out, 0, 16, expect=1)                           # LOAD of a missing input
+    call(lib, [0, 99], [0, 0], [x], out, 0, 16, expect=1)                    # unknown opcode
+    call(lib, [0] * 9 + [2] * 8, [0] * 17, [x], out, 0, 16, expect=6)        # stack deeper than 8
+    call(lib, [0] * 8 + [2] * 7, [0] * 15, [x], out, 0, 16)                  # exactly 8 is fine
+    assert torch.equal(out.cpu(), torch.zeros(16))
+    call(lib, [0], [0], [x], out, 0, 0)                                      # n == 0: nothing to do
+    half = torch.zeros(17, dtype=torch.float16, device="cuda")
+    bad = ctypes.c_void_p(half.data_ptr() + 1)
+    ops_a, args_a = (ctypes.c_int32 * 1)(0), (ctypes.c_int32 * 1)(0)
+    ins, types = (ctypes.c_void_p * 1)(bad), (ctypes.c_int32 * 1)(1)
+    assert lib.asc_cuda_eltwise_program(ops_a, args_a, 1, ins, types, 1, ctypes.c_void_p(out.data_ptr()), 0, 8, None) == 2

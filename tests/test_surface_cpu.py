@@ -143,13 +143,13 @@ def test_workload_scripts_match_at_full_size():
 
 def test_unsupported_pattern_raises_not_implemented():
     @asc2.jit
-    def sin_kernel(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, size: int, tile: asc.ConstExpr[int]):
-        x_gm, out_gm = asc2.tensor(x_ptr, [size]), asc2.tensor(out_ptr, [size])
-        off = asc2.block_idx() * tile
-        asc2.store(asc2.sin(asc2.load(x_gm, [tile], offsets=[off])), out_gm, offsets=[off])
-    x = np.zeros(256, np.float32)
+    def column_sums(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: asc.ConstExpr[int],
+                    cols: asc.ConstExpr[int]):
+        x = asc2.load(asc2.tensor(x_ptr, [rows, cols]), [rows, cols], offsets=[0, 0])
+        asc2.store(asc2.reduce_sum(x, 0), asc2.tensor(out_ptr, [cols]), offsets=[0])
+    x = np.zeros((16, 64), np.float32)
     with pytest.raises(NotImplementedError, match="no kernel for this pattern"):
-        sin_kernel[2](x, x.copy(), 256, 128)
+        column_sums[1](x, np.zeros(64, np.float32), 16, 64)
 
 
 # ----------------------------------------------------------------------------- reference error behaviour
