@@ -43,7 +43,8 @@ if ROOT not in sys.path:
 import torch  # noqa: E402
 
 HEADLINE = "softmax"
-ALL_WORKLOADS = ["softmax", "vadd", "gemm_f16", "gemm_i8", "gemm_i8_dequant", "attention", "attention_causal"]
+ALL_WORKLOADS = ["softmax", "vadd", "gemm_f16", "gemm_i8", "gemm_i8_dequant", "attention", "attention_causal",
+                 "gelu", "gelu_tanh", "leaky_relu_bf16"]
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -349,7 +350,111 @@ class AttentionCausal(Attention):
     cpu_sample_desc = "fp32 causal softmax(QK^T*scale + mask)V on 2 of the 128 (batch, head) pairs"
 
 
-REGISTRY = {w.name: w for w in (Softmax, VAdd, GemmF16, GemmI8, GemmI8Dequant, Attention, AttentionCausal)}
+class _Elementwise(Workload):
+    """An asc2 elementwise kernel: the device leg launches the C-ABI call the launcher plans for it (the
+    plan is built once, with the launch itself suppressed), the end-to-end leg goes through the kernel
+    launch a user writes."""
+
+    def plan_step(self, launch_fn, kernel, ptr_args):
+        prev = os.environ.get("DRY_RUN")
+        os.environ["DRY_RUN"] = "1"
+        try:
+            launch_fn()
+        finally:
+            if prev is None:
+                del os.environ["DRY_RUN"]
+            else:
+                os.environ["DRY_RUN"] = prev
+        plan = kernel.last_plan
+        assert plan.pattern == "elementwise:program" and len(plan.steps) == 1, plan
+        self.step = plan.steps[0]
+        self.ptrs = {i: t.data_ptr() for i, t in ptr_args.items()}
+
+    def launch(self, lib, stream):
+        return getattr(lib, self.step.fn_name)(*self.step.build(self.ptrs, stream))
+
+
+class Gelu(_Elementwise):
+    name, label, dtype = "gelu", "gelu_erf_f32_16384x4096", "f32"
+    approximate = False
+    R, C = 16384, 4096
+    work = 2.0 * 4 * R * C
+    h2d_bytes, d2h_bytes = 4 * R * C, 4 * R * C
+    CPU_R = 4096
+    cpu_sample_desc = "0.5*x*(1+erf(x/sqrt(2))) in torch on 4096 of the 16384 rows"
+
+    def setup_device(self, dev):
+        from pyasc_b200 import tutorials as T
+        g = torch.Generator(device=dev).manual_seed(2026)
+        self.x = torch.rand((self.R, self.C), device=dev, generator=g) * 6 - 3
+        self.out = torch.empty_like(self.x)
+        self.plan_step(lambda: T.gelu_launch(self.x, self.out, self.approximate, core_num=148), T.gelu_kernel,
+                       {0: self.x, 1: self.out})
+
+    def setup_host(self):
+        g = torch.Generator().manual_seed(2026)
+        self.hx = (torch.rand((self.R, self.C), generator=g) * 6 - 3).pin_memory()
+        self.hout = torch.empty_like(self.hx).pin_memory()
+
+    def e2e_step(self):
+        from pyasc_b200 import tutorials as T
+        T.gelu_launch(self.hx, self.hout, self.approximate, core_num=148)
+
+    def cpu_sample(self):
+        import math
+        if not hasattr(self, "cx"):
+            self.cx = torch.rand((self.CPU_R, self.C), generator=torch.Generator().manual_seed(2026)) * 6 - 3
+        x = self.cx
+        if self.approximate:
+            _ = 0.5 * x * (1 + torch.tanh(math.sqrt(2 / math.pi) * (x + 0.044715 * torch.pow(x, 3))))
+        else:
+            _ = 0.5 * x * (1 + torch.erf(x / math.sqrt(2)))
+        return 2.0 * 4 * self.CPU_R * self.C
+
+
+class GeluTanh(Gelu):
+    name, label = "gelu_tanh", "gelu_tanh_f32_16384x4096"
+    approximate = True
+    cpu_sample_desc = "the tanh-form GELU expression in torch on 4096 of the 16384 rows"
+
+
+class LeakyReluBF16(_Elementwise):
+    name, label, dtype = "leaky_relu_bf16", "leaky_relu_bf16_2^28", "bf16"
+    N = 1 << 28
+    work = 2.0 * 2 * N
+    h2d_bytes, d2h_bytes = 2 * N, 2 * N
+    CPU_N = 1 << 26
+    cpu_sample_desc = "torch.where(x >= 0, x, x * alpha) on 2^26 of the 2^28 bf16 elements"
+
+    def setup_device(self, dev):
+        from pyasc_b200 import tutorials as T
+        g = torch.Generator(device=dev).manual_seed(2026)
+        self.x = (torch.rand(self.N, device=dev, generator=g) * 10 - 5).to(torch.bfloat16)
+        self.out = torch.empty_like(self.x)
+        self.alpha = torch.tensor(0.1, dtype=torch.bfloat16)
+        self.plan_step(lambda: T.leaky_relu_launch(self.x, self.alpha, self.out, core_num=148, tile_size=1 << 16),
+                       T.leaky_relu_kernel, {0: self.x, 2: self.out})
+
+    def setup_host(self):
+        g = torch.Generator().manual_seed(2026)
+        self.hx = (torch.rand(self.N, generator=g) * 10 - 5).to(torch.bfloat16).pin_memory()
+        self.hout = torch.empty_like(self.hx).pin_memory()
+        self.alpha = torch.tensor(0.1, dtype=torch.bfloat16)
+
+    def e2e_step(self):
+        from pyasc_b200 import tutorials as T
+        T.leaky_relu_launch(self.hx, self.alpha, self.hout, core_num=148, tile_size=1 << 16)
+
+    def cpu_sample(self):
+        if not hasattr(self, "cx"):
+            g = torch.Generator().manual_seed(2026)
+            self.cx = (torch.rand(self.CPU_N, generator=g) * 10 - 5).to(torch.bfloat16)
+        _ = torch.where(self.cx >= 0, self.cx, self.cx * torch.tensor(0.1, dtype=torch.bfloat16))
+        return 2.0 * 2 * self.CPU_N
+
+
+REGISTRY = {w.name: w for w in (Softmax, VAdd, GemmF16, GemmI8, GemmI8Dequant, Attention, AttentionCausal, Gelu, GeluTanh,
+                                LeakyReluBF16)}
 
 
 # ---------------------------------------------------------------------------------------------------

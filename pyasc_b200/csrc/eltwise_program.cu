@@ -129,11 +129,11 @@ __device__ __forceinline__ void store_quad(void* p, int type, int64_t i, const f
 
 // A thread's kV lanes: kV == 1 is the element at i; otherwise kV / 4 quads, the first at i and the
 // others kQuadStride elements apart (so that a warp's accesses stay contiguous inside a CTA tile).
-template <int kV>
+template <int kV, bool kLoadedOnce = false>
 __device__ __forceinline__ void load_group(const void* p, int typeword, int64_t i, float (&v)[kV]) {
   const int type = typeword & 0xff;
   if constexpr (kV >= 4) {
-    const bool reused = (typeword & kReusedInput) != 0;
+    const bool reused = !kLoadedOnce && (typeword & kReusedInput) != 0;
 #pragma unroll
     for (int q = 0; q < kV / 4; ++q) load_quad(p, type, reused, i + q * kQuadStride, &v[4 * q]);
   } else {
@@ -163,6 +163,77 @@ __device__ __forceinline__ void store_group(void* p, int type, int64_t i, const 
   }
 }
 
+// ---- the meaning of every opcode, in one place (both executors below inline these with a constant op) ----
+__device__ __forceinline__ float apply_binary(int op, float a, float b) {
+  const int x = __float_as_int(a), y = __float_as_int(b);
+  const unsigned ux = static_cast<unsigned>(x), uy = static_cast<unsigned>(y);
+  switch (op) {
+    case OP_ADD: return __fadd_rn(a, b);
+    case OP_SUB: return __fsub_rn(a, b);
+    case OP_MUL: return __fmul_rn(a, b);
+    case OP_DIV: return __fdiv_rn(a, b);
+    case OP_MAX: return fmaxf(a, b);
+    case OP_MIN: return fminf(a, b);
+    case OP_EQ: return a == b ? 1.f : 0.f;
+    case OP_NE: return a != b ? 1.f : 0.f;
+    case OP_GT: return a > b ? 1.f : 0.f;
+    case OP_GE: return a >= b ? 1.f : 0.f;
+    case OP_LT: return a < b ? 1.f : 0.f;
+    case OP_LE: return a <= b ? 1.f : 0.f;
+    case OP_IADD: return __int_as_float(static_cast<int>(ux + uy));
+    case OP_ISUB: return __int_as_float(static_cast<int>(ux - uy));
+    case OP_IMUL: return __int_as_float(static_cast<int>(ux * uy));
+    case OP_IMAX: return __int_as_float(max(x, y));
+    case OP_IMIN: return __int_as_float(min(x, y));
+    case OP_ISHL: return __int_as_float(static_cast<int>(ux << (y & 31)));
+    case OP_ISHR: return __int_as_float(x >> (y & 31));
+    case OP_IEQ: return x == y ? 1.f : 0.f;
+    case OP_INE: return x != y ? 1.f : 0.f;
+    case OP_IGT: return x > y ? 1.f : 0.f;
+    case OP_IGE: return x >= y ? 1.f : 0.f;
+    case OP_ILT: return x < y ? 1.f : 0.f;
+    case OP_ILE: return x <= y ? 1.f : 0.f;
+    case OP_RSUB: return __fsub_rn(b, a);
+    case OP_RDIV: return __fdiv_rn(b, a);
+    case OP_IRSUB: return __int_as_float(static_cast<int>(uy - ux));
+    case OP_IRSHL: return __int_as_float(static_cast<int>(uy << (x & 31)));
+    default: return __int_as_float(y >> (x & 31));  // OP_IRSHR
+  }
+}
+
+__device__ __forceinline__ float apply_unary(int op, float a) {
+  const int x = __float_as_int(a);
+  switch (op) {
+    case OP_NEG: return -a;
+    case OP_ABS: return fabsf(a);
+    case OP_RELU: return fmaxf(a, 0.f);
+    case OP_EXP: return expf(a);
+    case OP_EXP2: return exp2f(a);
+    case OP_LOG: return logf(a);
+    case OP_LOG2: return log2f(a);
+    case OP_SQRT: return sqrtf(a);
+    case OP_RSQRT: return rsqrtf(a);
+    case OP_SIN: return sinf(a);
+    case OP_COS: return cosf(a);
+    case OP_TAN: return tanf(a);
+    case OP_SINH: return sinhf(a);
+    case OP_COSH: return coshf(a);
+    case OP_TANH: return tanhf(a);
+    case OP_ERF: return erff(a);
+    case OP_FLOOR: return floorf(a);
+    case OP_CEIL: return ceilf(a);
+    case OP_ROUND_F16: return __half2float(__float2half_rn(a));
+    case OP_ROUND_BF16: return __bfloat162float(__float2bfloat16_rn(a));
+    case OP_INEG: return __int_as_float(static_cast<int>(0u - static_cast<unsigned>(x)));
+    case OP_IABS: return __int_as_float(abs(x));
+    case OP_IRELU: return __int_as_float(max(x, 0));
+    case OP_CVT_I2F: return __int2float_rn(x);
+    case OP_CVT_F2I: return __int_as_float(__float2int_rz(a));
+    default: return __int_as_float(static_cast<int>(static_cast<int16_t>(x & 0xffff)));  // OP_WRAP_I16
+  }
+}
+
+// ---- executor 1: the interpreter, for any valid program ----
 // The top of the operand stack is a register group; the entries below it live in shared memory, one
 // kV-wide slot per thread and stack level (conflict-free 128-bit accesses), indexed by the
 // warp-uniform depth.  That keeps the register count low enough for high occupancy, which is what
@@ -194,180 +265,241 @@ struct StackSlots {
   }
 };
 
-// Evaluates the program for kV consecutive elements at once: one opcode dispatch (a single jump
-// through the switch table) serves kV lanes.  The host validated opcodes, operand indices and depth.
-template <int kV>
-__device__ __forceinline__ void run_program(const EltProgram& prog, int64_t i, const StackSlots<kV> slots) {
-  float top[kV];
-  int depth = 0;  // entries on the stack, the top included
+struct Interpreter {
+  // One opcode dispatch (a single jump through the switch table) serves kV lanes.  The host validated
+  // opcodes, operand indices and stack depth.
+  template <int kV>
+  __device__ __forceinline__ static void run(const EltProgram& prog, int64_t i, float* stack_mem) {
+    const StackSlots<kV> slots{stack_mem + threadIdx.x * (kV >= 4 ? 4 : 1)};
+    float top[kV];
+    int depth = 0;  // entries on the stack, the top included
 #define ASC_LANES _Pragma("unroll") for (int e = 0; e < kV; ++e)
-#define ASC_BIN(CODE, EXPR)                                  \
-  case CODE: {                                               \
-    float lhs[kV];                                           \
-    if (imm) {                                               \
-      ASC_LANES lhs[e] = __int_as_float(prog.arg[k]);        \
-    } else {                                                 \
-      slots.get(depth - 2, lhs);                             \
-      --depth;                                               \
-    }                                                        \
-    ASC_LANES {                                              \
-      const float a = lhs[e], b = top[e];                    \
-      const int x = __float_as_int(a), y = __float_as_int(b); \
-      (void)a; (void)b; (void)x; (void)y;                    \
-      top[e] = (EXPR);                                       \
-    }                                                        \
+#define ASC_BIN(CODE)                                                   \
+  case CODE: {                                                          \
+    float lhs[kV];                                                      \
+    if (imm) {                                                          \
+      ASC_LANES lhs[e] = __int_as_float(prog.arg[k]);                   \
+    } else {                                                            \
+      slots.get(depth - 2, lhs);                                        \
+      --depth;                                                          \
+    }                                                                   \
+    ASC_LANES top[e] = apply_binary(CODE, lhs[e], top[e]);              \
   } break;
-#define ASC_UN(CODE, EXPR)                \
-  case CODE:                              \
-    ASC_LANES {                           \
-      const float a = top[e];             \
-      const int x = __float_as_int(a);    \
-      (void)x;                            \
-      top[e] = (EXPR);                    \
-    }                                     \
+#define ASC_UN(CODE) \
+  case CODE:         \
+    ASC_LANES top[e] = apply_unary(CODE, top[e]); \
     break;
 #pragma unroll 1
-  for (int k = 0; k < prog.n_ops; ++k) {
-    const int op = prog.op[k] & 0xff;
-    const bool imm = (prog.op[k] & OP_IMM) != 0;
-    switch (op) {
-      case OP_LOAD:
-        if (depth > 0) slots.put(depth - 1, top);
-        ++depth;
-        load_group<kV>(prog.in[prog.arg[k]], prog.in_type[prog.arg[k]], i, top);
-        break;
-      case OP_CONST:
-        if (depth > 0) slots.put(depth - 1, top);
-        ++depth;
-        ASC_LANES top[e] = __int_as_float(prog.arg[k]);
-        break;
-      case OP_WHERE: {
-        float a[kV], c[kV];
-        slots.get(depth - 2, a);
-        slots.get(depth - 3, c);
-        depth -= 2;
-        ASC_LANES top[e] = c[e] != 0.f ? a[e] : top[e];
-      } break;
-      ASC_BIN(OP_ADD, __fadd_rn(a, b))
-      ASC_BIN(OP_SUB, __fsub_rn(a, b))
-      ASC_BIN(OP_MUL, __fmul_rn(a, b))
-      ASC_BIN(OP_DIV, __fdiv_rn(a, b))
-      ASC_BIN(OP_MAX, fmaxf(a, b))
-      ASC_BIN(OP_MIN, fminf(a, b))
-      ASC_BIN(OP_EQ, a == b ? 1.f : 0.f)
-      ASC_BIN(OP_NE, a != b ? 1.f : 0.f)
-      ASC_BIN(OP_GT, a > b ? 1.f : 0.f)
-      ASC_BIN(OP_GE, a >= b ? 1.f : 0.f)
-      ASC_BIN(OP_LT, a < b ? 1.f : 0.f)
-      ASC_BIN(OP_LE, a <= b ? 1.f : 0.f)
-      ASC_BIN(OP_IADD, __int_as_float(static_cast<int>(static_cast<unsigned>(x) + static_cast<unsigned>(y))))
-      ASC_BIN(OP_ISUB, __int_as_float(static_cast<int>(static_cast<unsigned>(x) - static_cast<unsigned>(y))))
-      ASC_BIN(OP_IMUL, __int_as_float(static_cast<int>(static_cast<unsigned>(x) * static_cast<unsigned>(y))))
-      ASC_BIN(OP_IMAX, __int_as_float(max(x, y)))
-      ASC_BIN(OP_IMIN, __int_as_float(min(x, y)))
-      ASC_BIN(OP_ISHL, __int_as_float(static_cast<int>(static_cast<unsigned>(x) << (y & 31))))
-      ASC_BIN(OP_ISHR, __int_as_float(x >> (y & 31)))
-      ASC_BIN(OP_IEQ, x == y ? 1.f : 0.f)
-      ASC_BIN(OP_INE, x != y ? 1.f : 0.f)
-      ASC_BIN(OP_IGT, x > y ? 1.f : 0.f)
-      ASC_BIN(OP_IGE, x >= y ? 1.f : 0.f)
-      ASC_BIN(OP_ILT, x < y ? 1.f : 0.f)
-      ASC_BIN(OP_ILE, x <= y ? 1.f : 0.f)
-      ASC_BIN(OP_RSUB, __fsub_rn(b, a))
-      ASC_BIN(OP_RDIV, __fdiv_rn(b, a))
-      ASC_BIN(OP_IRSUB, __int_as_float(static_cast<int>(static_cast<unsigned>(y) - static_cast<unsigned>(x))))
-      ASC_BIN(OP_IRSHL, __int_as_float(static_cast<int>(static_cast<unsigned>(y) << (x & 31))))
-      ASC_BIN(OP_IRSHR, __int_as_float(y >> (x & 31)))
-      ASC_UN(OP_NEG, -a)
-      ASC_UN(OP_ABS, fabsf(a))
-      ASC_UN(OP_RELU, fmaxf(a, 0.f))
-      ASC_UN(OP_EXP, expf(a))
-      ASC_UN(OP_EXP2, exp2f(a))
-      ASC_UN(OP_LOG, logf(a))
-      ASC_UN(OP_LOG2, log2f(a))
-      ASC_UN(OP_SQRT, sqrtf(a))
-      ASC_UN(OP_RSQRT, rsqrtf(a))
-      ASC_UN(OP_SIN, sinf(a))
-      ASC_UN(OP_COS, cosf(a))
-      ASC_UN(OP_TAN, tanf(a))
-      ASC_UN(OP_SINH, sinhf(a))
-      ASC_UN(OP_COSH, coshf(a))
-      ASC_UN(OP_TANH, tanhf(a))
-      ASC_UN(OP_ERF, erff(a))
-      ASC_UN(OP_FLOOR, floorf(a))
-      ASC_UN(OP_CEIL, ceilf(a))
-      ASC_UN(OP_ROUND_F16, __half2float(__float2half_rn(a)))
-      ASC_UN(OP_ROUND_BF16, __bfloat162float(__float2bfloat16_rn(a)))
-      ASC_UN(OP_INEG, __int_as_float(static_cast<int>(0u - static_cast<unsigned>(x))))
-      ASC_UN(OP_IABS, __int_as_float(abs(x)))
-      ASC_UN(OP_IRELU, __int_as_float(max(x, 0)))
-      ASC_UN(OP_CVT_I2F, __int2float_rn(x))
-      ASC_UN(OP_CVT_F2I, __int_as_float(__float2int_rz(a)))
-      ASC_UN(OP_WRAP_I16, __int_as_float(static_cast<int>(static_cast<int16_t>(x & 0xffff))))
-      default: break;
+    for (int k = 0; k < prog.n_ops; ++k) {
+      const int op = prog.op[k] & 0xff;
+      const bool imm = (prog.op[k] & OP_IMM) != 0;
+      switch (op) {
+        case OP_LOAD:
+          if (depth > 0) slots.put(depth - 1, top);
+          ++depth;
+          load_group<kV>(prog.in[prog.arg[k]], prog.in_type[prog.arg[k]], i, top);
+          break;
+        case OP_CONST:
+          if (depth > 0) slots.put(depth - 1, top);
+          ++depth;
+          ASC_LANES top[e] = __int_as_float(prog.arg[k]);
+          break;
+        case OP_WHERE: {
+          float a[kV], c[kV];
+          slots.get(depth - 2, a);
+          slots.get(depth - 3, c);
+          depth -= 2;
+          ASC_LANES top[e] = c[e] != 0.f ? a[e] : top[e];
+        } break;
+        ASC_BIN(OP_ADD) ASC_BIN(OP_SUB) ASC_BIN(OP_MUL) ASC_BIN(OP_DIV) ASC_BIN(OP_MAX) ASC_BIN(OP_MIN)
+        ASC_BIN(OP_EQ) ASC_BIN(OP_NE) ASC_BIN(OP_GT) ASC_BIN(OP_GE) ASC_BIN(OP_LT) ASC_BIN(OP_LE)
+        ASC_BIN(OP_IADD) ASC_BIN(OP_ISUB) ASC_BIN(OP_IMUL) ASC_BIN(OP_IMAX) ASC_BIN(OP_IMIN) ASC_BIN(OP_ISHL)
+        ASC_BIN(OP_ISHR) ASC_BIN(OP_IEQ) ASC_BIN(OP_INE) ASC_BIN(OP_IGT) ASC_BIN(OP_IGE) ASC_BIN(OP_ILT)
+        ASC_BIN(OP_ILE) ASC_BIN(OP_RSUB) ASC_BIN(OP_RDIV) ASC_BIN(OP_IRSUB) ASC_BIN(OP_IRSHL) ASC_BIN(OP_IRSHR)
+        ASC_UN(OP_NEG) ASC_UN(OP_ABS) ASC_UN(OP_RELU) ASC_UN(OP_EXP) ASC_UN(OP_EXP2) ASC_UN(OP_LOG) ASC_UN(OP_LOG2)
+        ASC_UN(OP_SQRT) ASC_UN(OP_RSQRT) ASC_UN(OP_SIN) ASC_UN(OP_COS) ASC_UN(OP_TAN) ASC_UN(OP_SINH)
+        ASC_UN(OP_COSH) ASC_UN(OP_TANH) ASC_UN(OP_ERF) ASC_UN(OP_FLOOR) ASC_UN(OP_CEIL) ASC_UN(OP_ROUND_F16)
+        ASC_UN(OP_ROUND_BF16) ASC_UN(OP_INEG) ASC_UN(OP_IABS) ASC_UN(OP_IRELU) ASC_UN(OP_CVT_I2F)
+        ASC_UN(OP_CVT_F2I) ASC_UN(OP_WRAP_I16)
+        default: break;
+      }
     }
-  }
 #undef ASC_UN
 #undef ASC_BIN
 #undef ASC_LANES
-  store_group<kV>(prog.out, prog.out_type, i, top);
-}
+    store_group<kV>(prog.out, prog.out_type, i, top);
+  }
+};
+
+// ---- executor 2: the same machine with the opcode sequence known at compile time ----
+// For the expressions the asc2 kernel tests and tutorials produce, the op sequence is a template
+// argument: every dispatch, stack index and opcode switch folds away and the stack lives in registers,
+// so the kernel is as good as one written by hand for that expression.  Immediates and pointers still
+// come from the launch's EltProgram.  A LOAD entry carries its input index in bits 16-23; each input is
+// read from memory once, up front, and a LOAD becomes a register copy.
+template <int... kWords>
+struct OpList {
+  static constexpr int n = sizeof...(kWords);
+  __host__ __device__ static constexpr int at(int k) {
+    constexpr int words[] = {kWords...};
+    return words[k];
+  }
+  __host__ __device__ static constexpr int inputs() {  // highest input index a LOAD names, plus one
+    constexpr int words[] = {kWords...};
+    int m = 0;
+    for (int k = 0; k < n; ++k)
+      if ((words[k] & 0xff) == OP_LOAD && ((words[k] >> 16) & 0xff) + 1 > m) m = ((words[k] >> 16) & 0xff) + 1;
+    return m;
+  }
+};
+__host__ __device__ constexpr int LD(int input) { return OP_LOAD | (input << 16); }
+
+template <class P, int kV, int K, int D>
+struct StaticStep {
+  __device__ __forceinline__ static void run(const EltProgram& prog, int64_t i, const float (&in)[P::inputs()][kV],
+                                             float (&st)[kStack][kV]) {
+    if constexpr (K == P::n) {
+      static_assert(D == 1, "a program leaves exactly one value");
+      store_group<kV>(prog.out, prog.out_type, i, st[0]);
+    } else {
+      constexpr int word = P::at(K);
+      constexpr int op = word & 0xff;
+      constexpr bool imm = (word & OP_IMM) != 0;
+      if constexpr (op == OP_LOAD) {
+        constexpr int input = (word >> 16) & 0xff;
+#pragma unroll
+        for (int e = 0; e < kV; ++e) st[D][e] = in[input][e];
+        StaticStep<P, kV, K + 1, D + 1>::run(prog, i, in, st);
+      } else if constexpr (op == OP_CONST) {
+#pragma unroll
+        for (int e = 0; e < kV; ++e) st[D][e] = __int_as_float(prog.arg[K]);
+        StaticStep<P, kV, K + 1, D + 1>::run(prog, i, in, st);
+      } else if constexpr (is_binary_op(op) && imm) {
+#pragma unroll
+        for (int e = 0; e < kV; ++e) st[D - 1][e] = apply_binary(op, __int_as_float(prog.arg[K]), st[D - 1][e]);
+        StaticStep<P, kV, K + 1, D>::run(prog, i, in, st);
+      } else if constexpr (is_binary_op(op)) {
+#pragma unroll
+        for (int e = 0; e < kV; ++e) st[D - 2][e] = apply_binary(op, st[D - 2][e], st[D - 1][e]);
+        StaticStep<P, kV, K + 1, D - 1>::run(prog, i, in, st);
+      } else if constexpr (op == OP_WHERE) {
+#pragma unroll
+        for (int e = 0; e < kV; ++e) st[D - 3][e] = st[D - 3][e] != 0.f ? st[D - 2][e] : st[D - 1][e];
+        StaticStep<P, kV, K + 1, D - 2>::run(prog, i, in, st);
+      } else {
+#pragma unroll
+        for (int e = 0; e < kV; ++e) st[D - 1][e] = apply_unary(op, st[D - 1][e]);
+        StaticStep<P, kV, K + 1, D>::run(prog, i, in, st);
+      }
+    }
+  }
+};
+
+template <class P>
+struct Compiled {
+  template <int kV>
+  __device__ __forceinline__ static void run(const EltProgram& prog, int64_t i, float*) {
+    float in[P::inputs()][kV];  // every input is read from memory exactly once
+#pragma unroll
+    for (int j = 0; j < P::inputs(); ++j) load_group<kV, true>(prog.in[j], prog.in_type[j], i, in[j]);
+    float st[kStack][kV];
+    StaticStep<P, kV, 0, 0>::run(prog, i, in, st);
+  }
+};
 
 // kLanes == 1: some pointer is not aligned to four elements, every element goes through the scalar
-// path.  Otherwise a CTA walks tiles of kThreads * kLanes elements (kLanes per thread and dispatch),
-// then the remaining quads, then the scalar tail.
-template <int kLanes>
+// path.  Otherwise a CTA walks tiles of kThreads * kLanes elements (kLanes per thread at a time), then
+// the remaining quads, then the scalar tail.
+template <class Exec, int kLanes>
 __global__ void __launch_bounds__(kThreads) eltwise_program_kernel(const __grid_constant__ EltProgram prog, int64_t n) {
-  extern __shared__ __align__(16) float stack_mem[];  // (max depth - 1) levels x kThreads x kLanes floats
+  extern __shared__ __align__(16) float stack_mem[];  // interpreter: (max depth - 1) levels x kThreads x kLanes floats
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kThreads;
   const int64_t tid = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
-  const StackSlots<1> scalar_slots{stack_mem + threadIdx.x};
   int64_t done = 0;
   if constexpr (kLanes >= 4) {
-    const StackSlots<4> quad_slots{stack_mem + threadIdx.x * 4};
     if constexpr (kLanes > 4) {
       constexpr int64_t kTile = static_cast<int64_t>(kThreads) * kLanes;
-      const StackSlots<kLanes> slots{stack_mem + threadIdx.x * 4};
       const int64_t tiles = n / kTile;
-      for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) run_program<kLanes>(prog, t * kTile + threadIdx.x * 4, slots);
+      for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x)
+        Exec::template run<kLanes>(prog, t * kTile + threadIdx.x * 4, stack_mem);
       done = tiles * kTile;
     }
     const int64_t quads = (n - done) >> 2;
-    for (int64_t g = tid; g < quads; g += stride) run_program<4>(prog, done + (g << 2), quad_slots);
+    for (int64_t g = tid; g < quads; g += stride) Exec::template run<4>(prog, done + (g << 2), stack_mem);
     done += quads << 2;
   }
-  for (int64_t i = done + tid; i < n; i += stride) run_program<1>(prog, i, scalar_slots);
+  for (int64_t i = done + tid; i < n; i += stride) Exec::template run<1>(prog, i, stack_mem);
 }
 
-int g_lanes = 8;  // elements per thread and dispatch on the aligned path (4, 8 or 16)
+int g_lanes = 8;            // interpreter: elements per thread and dispatch on the aligned path (4, 8 or 16)
+bool g_use_compiled = true;  // tuning hook can force the interpreter for every program
 
-template <int kLanes>
-int32_t launch_program(const EltProgram& prog, int64_t n, int max_depth, int sms, cudaStream_t stream) {
-  const size_t smem = static_cast<size_t>(max_depth > 1 ? max_depth - 1 : 1) * kThreads * (kLanes < 4 ? 4 : kLanes) * sizeof(float);
+template <class Exec, int kLanes>
+int32_t launch_program(const EltProgram& prog, int64_t n, size_t smem, int sms, cudaStream_t stream) {
   if (smem > 48 * 1024) {
     static bool attr_set[64] = {false};
     int dev = 0;
     ASC_CUDA_TRY(cudaGetDevice(&dev));
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-      ASC_CUDA_TRY(cudaFuncSetAttribute(eltwise_program_kernel<kLanes>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      ASC_CUDA_TRY(cudaFuncSetAttribute(eltwise_program_kernel<Exec, kLanes>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (kStack - 1) * kThreads * 16 * static_cast<int>(sizeof(float))));
       attr_set[dev] = true;
     }
   }
   int resident = 0;
-  ASC_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, eltwise_program_kernel<kLanes>, kThreads, smem));
+  ASC_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, eltwise_program_kernel<Exec, kLanes>, kThreads, smem));
   if (resident < 1) resident = 1;
   const int64_t per_cta = static_cast<int64_t>(kThreads) * kLanes;
   int64_t ctas = (n + per_cta - 1) / per_cta;
   const int64_t cap = static_cast<int64_t>(sms) * resident * 4;  // four waves of resident CTAs; CTAs stride beyond
   if (ctas > cap) ctas = cap;
-  eltwise_program_kernel<kLanes><<<static_cast<unsigned>(ctas), kThreads, smem, stream>>>(prog, n);
+  eltwise_program_kernel<Exec, kLanes><<<static_cast<unsigned>(ctas), kThreads, smem, stream>>>(prog, n);
   aschost::count_launch();
   ASC_CUDA_TRY(cudaGetLastError());
   return ASC_OK;
 }
 
+template <int kLanes>
+int32_t launch_interpreter(const EltProgram& prog, int64_t n, int max_depth, int sms, cudaStream_t stream) {
+  const size_t smem = static_cast<size_t>(max_depth > 1 ? max_depth - 1 : 1) * kThreads * (kLanes < 4 ? 4 : kLanes) * sizeof(float);
+  return launch_program<Interpreter, kLanes>(prog, n, smem, sms, stream);
+}
+
+// ---- the compiled programs: exactly what the launcher's expression compiler emits for these kernels ----
+constexpr int I = OP_IMM;
+// where(x >= 0, x, x * alpha): python/test/asc2/kernels/test_leaky_relu.py:16-27 (fp32 / fp16 / bf16 tiles)
+using LeakyReluF32 = OpList<LD(0), OP_LE | I, LD(0), LD(0), OP_MUL | I, OP_WHERE>;
+using LeakyReluF16 = OpList<LD(0), OP_LE | I, LD(0), LD(0), OP_MUL | I, OP_ROUND_F16, OP_WHERE>;
+using LeakyReluBF16 = OpList<LD(0), OP_LE | I, LD(0), LD(0), OP_MUL | I, OP_ROUND_BF16, OP_WHERE>;
+// x * (erf(x * k) + 1) * 0.5 and x - x / (exp(x * (x * x * k2 + k1)) + 1): test_gelu.py:16-34 (fp32)
+using GeluErf = OpList<LD(0), LD(0), OP_MUL | I, OP_ERF, OP_ADD | I, OP_MUL, OP_MUL | I>;
+using GeluTanh = OpList<LD(0), LD(0), OP_MUL, OP_MUL | I, OP_ADD | I, LD(0), OP_MUL, OP_EXP, OP_ADD | I, LD(0), OP_RDIV,
+                        LD(0), OP_RSUB>;
+
 int elem_size(int type) { return (type == T_F16 || type == T_BF16 || type == T_I16) ? 2 : 4; }
+
+template <class P>
+bool matches(const int32_t* ops, const int32_t* args, int n_ops) {
+  if (n_ops != P::n) return false;
+  for (int k = 0; k < n_ops; ++k) {
+    const int word = P::at(k);
+    if ((word & 0xffff) != ops[k]) return false;
+    if ((word & 0xff) == OP_LOAD && ((word >> 16) & 0xff) != args[k]) return false;
+  }
+  return true;
+}
+
+// launches the compiled form of the program when there is one (aligned pointers only); *launched tells
+template <class P>
+int32_t try_compiled(const EltProgram& prog, const int32_t* ops, const int32_t* args, int n_ops, int64_t n, int sms,
+                     cudaStream_t stream, bool* launched) {
+  if (*launched || !matches<P>(ops, args, n_ops)) return ASC_OK;
+  *launched = true;
+  // 16 bytes per access and thread want twice the lanes for 16-bit elements
+  if (elem_size(prog.out_type) == 2) return launch_program<Compiled<P>, 16>(prog, n, 0, sms, stream);
+  return launch_program<Compiled<P>, 8>(prog, n, 0, sms, stream);
+}
+
 
 }  // namespace
 
@@ -426,14 +558,26 @@ extern "C" int32_t asc_cuda_eltwise_program(const int32_t* ops, const int32_t* a
   bool vec = reinterpret_cast<uintptr_t>(out) % (4 * elem_size(out_type)) == 0;
   for (int i = 0; i < n_inputs; ++i) vec = vec && reinterpret_cast<uintptr_t>(inputs[i]) % (4 * elem_size(input_types[i])) == 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (!vec) return launch_program<1>(prog, n, max_depth, sms, st);
-  if (g_lanes == 4 || n < kThreads * 8) return launch_program<4>(prog, n, max_depth, sms, st);
-  if (g_lanes == 16) return launch_program<16>(prog, n, max_depth, sms, st);
-  return launch_program<8>(prog, n, max_depth, sms, st);
+  if (!vec) return launch_interpreter<1>(prog, n, max_depth, sms, st);
+  if (g_use_compiled) {
+    bool launched = false;
+    rc = try_compiled<LeakyReluF32>(prog, ops, args, n_ops, n, sms, st, &launched);
+    if (rc == ASC_OK) rc = try_compiled<LeakyReluF16>(prog, ops, args, n_ops, n, sms, st, &launched);
+    if (rc == ASC_OK) rc = try_compiled<LeakyReluBF16>(prog, ops, args, n_ops, n, sms, st, &launched);
+    if (rc == ASC_OK) rc = try_compiled<GeluErf>(prog, ops, args, n_ops, n, sms, st, &launched);
+    if (rc == ASC_OK) rc = try_compiled<GeluTanh>(prog, ops, args, n_ops, n, sms, st, &launched);
+    if (launched || rc != ASC_OK) return rc;
+  }
+  if (g_lanes == 4 || n < kThreads * 8) return launch_interpreter<4>(prog, n, max_depth, sms, st);
+  if (g_lanes == 16) return launch_interpreter<16>(prog, n, max_depth, sms, st);
+  return launch_interpreter<8>(prog, n, max_depth, sms, st);
 }
 
-// tuning hook: elements per thread and dispatch on the aligned path (4, 8 or 16; anything else: default)
+// tuning hook: bits 0-7 elements per thread and dispatch in the interpreter's aligned path (4, 8 or 16;
+// anything else: default 8); bit 8 set: never use a compiled program
 extern "C" int32_t asc_cuda_eltwise_set_lanes(int32_t lanes) {
-  g_lanes = (lanes == 4 || lanes == 16) ? lanes : 8;
+  const int l = lanes & 0xff;
+  g_lanes = (l == 4 || l == 16) ? l : 8;
+  g_use_compiled = (lanes & 0x100) == 0;
   return ASC_OK;
 }

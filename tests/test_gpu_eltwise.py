@@ -159,6 +159,72 @@ def test_program_transcendentals_close_to_cpu(lib):
         torch.testing.assert_close(out.cpu(), want, rtol=2e-6, atol=1e-6, msg=lambda m: f"opcode {op}: {m}")
 
 
+IMM = 0x100
+
+
+@pytest.mark.parametrize("name, dtype, out_type, ops, imms", [
+    ("leaky_relu", torch.float32, 0, [0, 31 | IMM, 0, 0, 4 | IMM, 32], {1: 0.0, 4: 0.1}),
+    ("leaky_relu", torch.float16, 1, [0, 31 | IMM, 0, 0, 4 | IMM, 33, 32], {1: 0.0, 4: 0.1}),
+    ("leaky_relu", torch.bfloat16, 2, [0, 31 | IMM, 0, 0, 4 | IMM, 34, 32], {1: 0.0, 4: 0.1}),
+    ("gelu_erf", torch.float32, 0, [0, 0, 4 | IMM, 23, 2 | IMM, 4, 4 | IMM], {2: 0.5 ** 0.5, 4: 1.0, 6: 0.5}),
+    ("gelu_tanh", torch.float32, 0, [0, 0, 4, 4 | IMM, 2 | IMM, 0, 4, 11, 2 | IMM, 0, 55, 0, 54],
+     {3: 0.0713548, 4: 1.5957691, 8: 1.0}),
+], ids=lambda v: str(v) if isinstance(v, (str, torch.dtype)) else "")
+def test_compiled_programs_equal_the_interpreter(lib, name, dtype, out_type, ops, imms):
+    """The programs that have a compile-time specialised kernel must give bit-identical results in both
+    executors (same per-op arithmetic), at a ragged size beyond L2, and agree with the CPU oracle."""
+    n = (1 << 25) + 1029
+    gen = torch.Generator().manual_seed(17)
+    x = (torch.rand(n, generator=gen) * 6 - 3).to(dtype)
+    xd = x.cuda()
+    args = [fbits(imms[k]) if k in imms else 0 for k in range(len(ops))]
+    if dtype != torch.float32:                       # scalars take the tile's type
+        args = [fbits(float(torch.tensor(imms[k]).to(dtype))) if k in imms else 0 for k in range(len(ops))]
+    compiled = torch.zeros(n, dtype=dtype, device="cuda")
+    interpreted = torch.zeros(n, dtype=dtype, device="cuda")
+    before = capi.launch_count()
+    call(lib, ops, args, [xd], compiled, out_type, n)
+    try:
+        lib.asc_cuda_eltwise_set_lanes(0x100)        # interpreter only
+        call(lib, ops, args, [xd], interpreted, out_type, n)
+    finally:
+        lib.asc_cuda_eltwise_set_lanes(0)
+    assert capi.launch_count() == before + 2
+    assert torch.equal(compiled, interpreted)
+    want = E.run_program(ops, args, [x], out_type)
+    if name == "leaky_relu":
+        assert torch.equal(compiled.cpu(), want)
+    else:
+        torch.testing.assert_close(compiled.cpu(), want, rtol=1e-5, atol=1e-6)
+
+
+def test_program_immediates_and_swapped_forms(lib):
+    gen = torch.Generator().manual_seed(23)
+    x = torch.rand(70001, generator=gen) * 4 - 2
+    y = torch.rand(70001, generator=gen) * 4 + 1
+    xd, yd = x.cuda(), y.cuda()
+    out = torch.empty_like(xd)
+    # (3 - x) / y  as  LOAD x, SUB|IMM 3, LOAD y, DIV ;  (x - 3) as RSUB|IMM ; y / x as [x, y] RDIV
+    for ops, args, want in [
+        ([0, 3 | IMM, 0, 5], [0, fbits(3.0), 1, 0], (3.0 - x) / y),
+        ([0, 54 | IMM], [0, fbits(3.0)], x - 3.0),
+        ([0, 0, 55], [0, 1, 0], y / x),
+        ([0, 0, 54], [0, 1, 0], y - x),
+        ([0, 30 | IMM], [0, fbits(0.5)], (0.5 < x).float()),
+    ]:
+        call(lib, ops, args, [xd, yd], out, 0, 70001)
+        assert torch.equal(out.cpu(), want), ops
+        assert torch.equal(E.run_program(ops, args, [x, y], 0), want), ops
+    xi = torch.randint(-1000, 1000, (70001, ), dtype=torch.int32, generator=gen)
+    oi = torch.zeros(70001, dtype=torch.int32, device="cuda")
+    for ops, args, want in [([0, 57 | IMM], [0, 3], xi << 3), ([0, 58 | IMM], [0, 2], xi >> 2),
+                            ([0, 56 | IMM], [0, 7], xi - 7), ([0, 36 | IMM], [0, 7], 7 - xi)]:
+        call(lib, ops, args, [xi.cuda()], oi, 3, 70001)
+        assert torch.equal(oi.cpu(), want), ops
+        assert torch.equal(E.run_program(ops, args, [xi], 3), want), ops
+    call(lib, [0, 11 | IMM], [0, 0], [xd], out, 0, 16, expect=1)             # immediate on a unary opcode
+
+
 def test_program_rejects_malformed_programs(lib):
     x = torch.zeros(16, device="cuda")
     out = torch.zeros(16, device="cuda")
