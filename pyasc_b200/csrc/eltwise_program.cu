@@ -127,6 +127,41 @@ __device__ __forceinline__ void store_quad(void* p, int type, int64_t i, const f
   }
 }
 
+// eight consecutive 16-bit elements starting at element index i (i % 8 == 0, base aligned to 16 bytes):
+// one 128-bit access.  Used when every operand of a compiled program is a 16-bit type.
+__device__ __forceinline__ void load_oct(const void* p, int type, int64_t i, float* v) {
+  const uint4 t = __ldcs(reinterpret_cast<const uint4*>(p) + (i >> 3));
+  const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    if (type == T_I16) {
+      v[2 * k] = __int_as_float(static_cast<int>(static_cast<int16_t>(w[k] & 0xffffu)));
+      v[2 * k + 1] = __int_as_float(static_cast<int>(static_cast<int16_t>(w[k] >> 16)));
+    } else if (type == T_F16) {
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+      v[2 * k] = a.x; v[2 * k + 1] = a.y;
+    } else {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]));
+      v[2 * k] = a.x; v[2 * k + 1] = a.y;
+    }
+  }
+}
+
+__device__ __forceinline__ void store_oct(void* p, int type, int64_t i, const float* v) {
+  uint32_t w[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    if (type == T_I16) {
+      w[k] = (static_cast<uint32_t>(__float_as_int(v[2 * k])) & 0xffffu) | (static_cast<uint32_t>(__float_as_int(v[2 * k + 1])) << 16);
+    } else if (type == T_F16) {
+      *reinterpret_cast<__half2*>(&w[k]) = __floats2half2_rn(v[2 * k], v[2 * k + 1]);
+    } else {
+      *reinterpret_cast<__nv_bfloat162*>(&w[k]) = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+    }
+  }
+  __stcs(reinterpret_cast<uint4*>(p) + (i >> 3), make_uint4(w[0], w[1], w[2], w[3]));
+}
+
 // A thread's kV lanes: kV == 1 is the element at i; otherwise kV / 4 quads, the first at i and the
 // others kQuadStride elements apart (so that a warp's accesses stay contiguous inside a CTA tile).
 template <int kV, bool kLoadedOnce = false>
@@ -266,6 +301,7 @@ struct StackSlots {
 };
 
 struct Interpreter {
+  static constexpr int kGroup = 4;  // consecutive elements per thread and memory access in a CTA tile
   // One opcode dispatch (a single jump through the switch table) serves kV lanes.  The host validated
   // opcodes, operand indices and stack depth.
   template <int kV>
@@ -354,13 +390,13 @@ struct OpList {
 };
 __host__ __device__ constexpr int LD(int input) { return OP_LOAD | (input << 16); }
 
-template <class P, int kV, int K, int D>
+template <class P, int kV, int K, int D, bool kStore>
 struct StaticStep {
   __device__ __forceinline__ static void run(const EltProgram& prog, int64_t i, const float (&in)[P::inputs()][kV],
                                              float (&st)[kStack][kV]) {
     if constexpr (K == P::n) {
       static_assert(D == 1, "a program leaves exactly one value");
-      store_group<kV>(prog.out, prog.out_type, i, st[0]);
+      if constexpr (kStore) store_group<kV>(prog.out, prog.out_type, i, st[0]);
     } else {
       constexpr int word = P::at(K);
       constexpr int op = word & 0xff;
@@ -369,41 +405,55 @@ struct StaticStep {
         constexpr int input = (word >> 16) & 0xff;
 #pragma unroll
         for (int e = 0; e < kV; ++e) st[D][e] = in[input][e];
-        StaticStep<P, kV, K + 1, D + 1>::run(prog, i, in, st);
+        StaticStep<P, kV, K + 1, D + 1, kStore>::run(prog, i, in, st);
       } else if constexpr (op == OP_CONST) {
 #pragma unroll
         for (int e = 0; e < kV; ++e) st[D][e] = __int_as_float(prog.arg[K]);
-        StaticStep<P, kV, K + 1, D + 1>::run(prog, i, in, st);
+        StaticStep<P, kV, K + 1, D + 1, kStore>::run(prog, i, in, st);
       } else if constexpr (is_binary_op(op) && imm) {
 #pragma unroll
         for (int e = 0; e < kV; ++e) st[D - 1][e] = apply_binary(op, __int_as_float(prog.arg[K]), st[D - 1][e]);
-        StaticStep<P, kV, K + 1, D>::run(prog, i, in, st);
+        StaticStep<P, kV, K + 1, D, kStore>::run(prog, i, in, st);
       } else if constexpr (is_binary_op(op)) {
 #pragma unroll
         for (int e = 0; e < kV; ++e) st[D - 2][e] = apply_binary(op, st[D - 2][e], st[D - 1][e]);
-        StaticStep<P, kV, K + 1, D - 1>::run(prog, i, in, st);
+        StaticStep<P, kV, K + 1, D - 1, kStore>::run(prog, i, in, st);
       } else if constexpr (op == OP_WHERE) {
 #pragma unroll
         for (int e = 0; e < kV; ++e) st[D - 3][e] = st[D - 3][e] != 0.f ? st[D - 2][e] : st[D - 1][e];
-        StaticStep<P, kV, K + 1, D - 2>::run(prog, i, in, st);
+        StaticStep<P, kV, K + 1, D - 2, kStore>::run(prog, i, in, st);
       } else {
 #pragma unroll
         for (int e = 0; e < kV; ++e) st[D - 1][e] = apply_unary(op, st[D - 1][e]);
-        StaticStep<P, kV, K + 1, D>::run(prog, i, in, st);
+        StaticStep<P, kV, K + 1, D, kStore>::run(prog, i, in, st);
       }
     }
   }
 };
 
-template <class P>
+// kOct: every operand is a 16-bit type with 16-byte aligned pointers; inside a CTA tile a thread then owns
+// groups of eight consecutive elements (one 128-bit access each) instead of quads.
+template <class P, bool kOct = false>
 struct Compiled {
+  static constexpr int kGroup = kOct ? 8 : 4;
   template <int kV>
   __device__ __forceinline__ static void run(const EltProgram& prog, int64_t i, float*) {
     float in[P::inputs()][kV];  // every input is read from memory exactly once
-#pragma unroll
-    for (int j = 0; j < P::inputs(); ++j) load_group<kV, true>(prog.in[j], prog.in_type[j], i, in[j]);
     float st[kStack][kV];
-    StaticStep<P, kV, 0, 0>::run(prog, i, in, st);
+    if constexpr (kOct && kV >= 8) {
+#pragma unroll
+      for (int j = 0; j < P::inputs(); ++j) {
+#pragma unroll
+        for (int o = 0; o < kV / 8; ++o) load_oct(prog.in[j], prog.in_type[j] & 0xff, i + o * (kThreads * 8), &in[j][8 * o]);
+      }
+      StaticStep<P, kV, 0, 0, false>::run(prog, i, in, st);
+#pragma unroll
+      for (int o = 0; o < kV / 8; ++o) store_oct(prog.out, prog.out_type, i + o * (kThreads * 8), &st[0][8 * o]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < P::inputs(); ++j) load_group<kV, true>(prog.in[j], prog.in_type[j], i, in[j]);
+      StaticStep<P, kV, 0, 0, true>::run(prog, i, in, st);
+    }
   }
 };
 
@@ -421,7 +471,7 @@ __global__ void __launch_bounds__(kThreads) eltwise_program_kernel(const __grid_
       constexpr int64_t kTile = static_cast<int64_t>(kThreads) * kLanes;
       const int64_t tiles = n / kTile;
       for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x)
-        Exec::template run<kLanes>(prog, t * kTile + threadIdx.x * 4, stack_mem);
+        Exec::template run<kLanes>(prog, t * kTile + threadIdx.x * Exec::kGroup, stack_mem);
       done = tiles * kTile;
     }
     const int64_t quads = (n - done) >> 2;
@@ -496,8 +546,11 @@ int32_t try_compiled(const EltProgram& prog, const int32_t* ops, const int32_t* 
   if (*launched || !matches<P>(ops, args, n_ops)) return ASC_OK;
   *launched = true;
   // 16 bytes per access and thread want twice the lanes for 16-bit elements
-  if (elem_size(prog.out_type) == 2) return launch_program<Compiled<P>, 16>(prog, n, 0, sms, stream);
-  return launch_program<Compiled<P>, 8>(prog, n, 0, sms, stream);
+  bool oct = elem_size(prog.out_type) == 2 && reinterpret_cast<uintptr_t>(prog.out) % 16 == 0;
+  for (int i = 0; i < prog.n_inputs; ++i)
+    oct = oct && elem_size(prog.in_type[i] & 0xff) == 2 && reinterpret_cast<uintptr_t>(prog.in[i]) % 16 == 0;
+  if (oct) return launch_program<Compiled<P, true>, 16>(prog, n, 0, sms, stream);
+  return launch_program<Compiled<P, false>, 8>(prog, n, 0, sms, stream);
 }
 
 
