@@ -44,7 +44,7 @@ import torch  # noqa: E402
 
 HEADLINE = "softmax"
 ALL_WORKLOADS = ["softmax", "vadd", "gemm_f16", "gemm_i8", "gemm_i8_dequant", "attention", "attention_causal",
-                 "gelu", "gelu_tanh", "leaky_relu_bf16", "silu_interpreted"]
+                 "gelu", "gelu_tanh", "leaky_relu_bf16", "silu_interpreted", "row_sum"]
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -458,6 +458,55 @@ class SiluInterpreted(Gelu):
         return 2.0 * 4 * self.CPU_R * self.C
 
 
+class RowSum(Workload):
+    """asc2.reduce_sum over the rows of [65536, 4096] fp32 (1 GiB read, 256 KiB written)."""
+    name, label, dtype = "row_sum", "row_sum_f32_65536x4096", "f32"
+    R, C = 65536, 4096
+    work = 4.0 * R * C + 4.0 * R
+    h2d_bytes, d2h_bytes = 4 * R * C, 4 * R
+    CPU_R = 16384
+    cpu_sample_desc = "x.sum(1) in torch on 16384 of the 65536 rows"
+
+    def setup_device(self, dev):
+        g = torch.Generator(device=dev).manual_seed(2026)
+        self.x = torch.randn((self.R, self.C), device=dev, generator=g)
+        self.out = torch.empty(self.R, device=dev)
+
+    def launch(self, lib, stream):
+        return lib.asc_cuda_reduce_f32(P(self.x), P(self.out), self.R, self.C, self.C, 1, 0, 1, stream)
+
+    @staticmethod
+    def kernel():
+        import pyasc_b200  # noqa: F401  (makes `asc` / `asc2` importable)
+        import asc
+        import asc2
+
+        @asc2.jit
+        def row_sum_kernel(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, num_rows: int,
+                           num_cols: asc.ConstExpr[int], rows_per_tile: asc.ConstExpr[int]):
+            x_gm = asc2.tensor(x_ptr, [num_rows, num_cols])
+            out_gm = asc2.tensor(out_ptr, [num_rows])
+            for i in range(asc2.block_idx() * rows_per_tile, num_rows, asc2.block_num() * rows_per_tile):
+                tile = asc2.load(x_gm, [rows_per_tile, num_cols], offsets=[i, 0])
+                asc2.store(asc2.reduce_sum(tile, 1), out_gm, offsets=[i])
+        return row_sum_kernel
+
+    def setup_host(self):
+        g = torch.Generator().manual_seed(2026)
+        self.hx = torch.randn((self.R, self.C), generator=g).pin_memory()
+        self.hout = torch.empty(self.R).pin_memory()
+        self.k = self.kernel()
+
+    def e2e_step(self):
+        self.k[148](self.hx, self.hout, self.R, self.C, 8)
+
+    def cpu_sample(self):
+        if not hasattr(self, "cx"):
+            self.cx = torch.randn((self.CPU_R, self.C), generator=torch.Generator().manual_seed(2026))
+        _ = self.cx.sum(1)
+        return 4.0 * self.CPU_R * self.C
+
+
 class LeakyReluBF16(_Elementwise):
     name, label, dtype = "leaky_relu_bf16", "leaky_relu_bf16_2^28", "bf16"
     N = 1 << 28
@@ -494,7 +543,7 @@ class LeakyReluBF16(_Elementwise):
 
 
 REGISTRY = {w.name: w for w in (Softmax, VAdd, GemmF16, GemmI8, GemmI8Dequant, Attention, AttentionCausal, Gelu, GeluTanh,
-                                LeakyReluBF16, SiluInterpreted)}
+                                LeakyReluBF16, SiluInterpreted, RowSum)}
 
 
 # ---------------------------------------------------------------------------------------------------

@@ -139,6 +139,16 @@ int32_t asc_cuda_eltwise_program(const int32_t* ops, const int32_t* args, int32_
                                  const int32_t* input_types, int32_t n_inputs, void* out, int32_t out_type,
                                  int64_t n, void* stream);
 
+/* Reduction of a row-major [rows, cols] fp32 window with row pitch `ld` (elements).  kind: 0 sum, 1 max,
+ * 2 min, 3 product.  axis 1: out[r] = reduce over the columns of row r; axis 0: out[c] = reduce over the
+ * rows of column c; axis -1: out[0 .. n_fill) all receive the reduction of the whole window (the window is
+ * an on-chip sized tile: at most 2^24 elements).  n_fill is ignored for axis 0 / 1.
+ * Replaces asc2.reduce_sum / reduce_max / reduce_min / reduce_prod on a loaded tile
+ * (python/asc/language/tile/reduction_ops.py; ReduceOp, lib/Conversion/LowerToAsc/LowerAscTile.cpp:428-459),
+ * as exercised by python/test/asc2/operations/test_reduce_ops.py:17-104. */
+int32_t asc_cuda_reduce_f32(const float* x, float* out, int64_t rows, int64_t cols, int64_t ld, int32_t axis,
+                            int32_t kind, int64_t n_fill, void* stream);
+
 /* Row softmax over the last dimension of a contiguous [rows, cols] fp32 matrix with max
  * subtraction.  `ld` is the row pitch in elements (>= cols).  Replaces both asc2 softmax forms:
  * the manual reduce_max/exp/reduce_sum kernel (python/test/asc2/kernels/test_softmax.py:16-27;

@@ -547,6 +547,109 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
 
 
 # --------------------------------------------------------------------------------------------------
+# Pattern: reduction of a loaded tile along one axis, or of the whole tile broadcast into the store
+# --------------------------------------------------------------------------------------------------
+_REDUCE_KIND = {"sum": 0, "max": 1, "min": 2, "prod": 3}
+
+
+def _match_reduce(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
+    value, out_t = eff.args
+    offsets = eff.attrs["offsets"]
+    if not isinstance(value, Tile):
+        return None
+    node = _node(value, "reduce")
+    n_fill = 0
+    if node is None:
+        full = _node(value, "full")
+        node = _tile_scalar_node(full.attrs["value"], "reduce") if full is not None else None
+        if node is None or node.attrs["dims"] != ():
+            return None
+        n_fill = value.size
+    src = node.args[0]
+    view = resolve_view(src) if _node(src, "load") or _node(src, "copy") else None
+    if view is None:
+        raise _unsupported("reduction of a tile that is not loaded from global memory")
+    if src.dtype != KT.float32 or out_t.dtype != KT.float32 or view.tensor.dtype != KT.float32:
+        raise _unsupported(f"reduction of {src.dtype} tiles (float32 only)")
+    if len(view.shape) > 2:
+        raise _unsupported("reduction of a tile of rank > 2")
+    _check_fits(out_t)
+    _check_fits(view.tensor)
+    x_rows, x_cols = _row_major_2d(view.tensor)
+    t_rows, t_cols = (1, view.shape[0]) if len(view.shape) == 1 else view.shape
+    dims = node.attrs["dims"]
+    if n_fill or len(view.shape) == 1:
+        if dims not in ((), (0, )):
+            raise _unsupported("reduction axis of a 1-D tile")
+        axis, n_out = -1, (n_fill or 1)
+    else:
+        if len(dims) != 1:
+            raise _unsupported("reduction over several axes at once")
+        axis = dims[0]
+        n_out = t_rows if axis == 1 else t_cols
+    if value.size != n_out:
+        return None
+    window = _flat_window(out_t, offsets, value.shape)
+    if window is None:
+        raise _unsupported("reduction whose result is not stored as one contiguous range")
+    out_off_expr, out_elems = window
+    assert out_elems == n_out
+    env = enumerate_instances(trace.core_num, eff.loops)
+    n = env_count(env)
+    zero = PlainValue.const(0)
+    x_offs = view.offsets if len(view.offsets) == 2 else (zero, view.offsets[0])
+    row0, col0 = eval_int(x_offs[0], env, n), eval_int(x_offs[1], env, n)
+    out0 = eval_int(out_off_expr, env, n)
+    if n and (row0.min() < 0 or col0.min() < 0 or out0.min() < 0):
+        raise RuntimeError("Negative tile offset in kernel")
+    if n and ((row0 + t_rows).max() > x_rows or (col0 + t_cols).max() > x_cols):
+        raise _unsupported("reduction of a tile that reaches past the end of its tensor")
+    if n and (out0 + n_out).max() > out_t.base.numel:
+        raise _unsupported("reduction whose result reaches past the end of its tensor")
+    if n > (1 << 20):
+        raise _unsupported(f"reduction kernel with {n} tiles; use larger tiles")
+    calls = sorted(set(zip(row0.tolist(), col0.tolist(), out0.tolist())))
+    # full-row tiles reduced along the row: consecutive tiles merge into one call over more rows
+    merged: List[Tuple[int, int, int, int]] = []      # (row0, col0, out0, rows)
+    for r0, c0, o0 in calls:
+        if merged and axis == 1 and t_cols == x_cols:
+            pr, pc, po, prow = merged[-1]
+            if r0 == pr + prow and o0 == po + prow:
+                merged[-1] = (pr, pc, po, prow + t_rows)
+                continue
+        merged.append((r0, c0, o0, t_rows))
+    if len(merged) > MAX_CALLS:
+        raise _unsupported("reduction kernel that needs more than 4096 separate calls")
+    plan = Plan(f"reduce:{node.attrs['kind']}")
+    x_idx, out_idx = view.tensor.base.index, out_t.base.index
+    if x_idx == out_idx:
+        raise _unsupported("reduction that stores into the tensor it loads")
+    plan.reads.add(x_idx)
+    plan.writes.add(out_idx)
+    covered = merge_intervals(np.array([m[2] for m in merged]), np.array([m[2] + (m[3] if axis == 1 else n_out) for m in merged]))
+    if covered != [(0, out_t.base.numel)]:
+        plan.partial_writes.add(out_idx)
+    kind = _REDUCE_KIND[node.attrs["kind"]]
+
+    def make_step(r0: int, c0: int, o0: int, rows: int) -> Step:
+        def build(ptrs, stream):
+            return (_p(ptrs[x_idx] + 4 * (r0 * x_cols + c0)), _p(ptrs[out_idx] + 4 * o0), ctypes.c_int64(rows),
+                    ctypes.c_int64(t_cols), ctypes.c_int64(x_cols), ctypes.c_int32(axis), ctypes.c_int32(kind),
+                    ctypes.c_int64(n_fill or 1), stream)
+        return Step("asc_cuda_reduce_f32", build, f"{node.attrs['kind']} axis {axis} of [{rows}, {t_cols}] at "
+                                                   f"({r0}, {c0}) -> [{o0}, +{rows if axis == 1 else n_out})")
+
+    for r0, c0, o0, rows in merged:
+        plan.steps.append(make_step(r0, c0, o0, rows))
+    if len(merged) == 1 and axis == 1 and merged[0][:3] == (0, 0, 0) and t_cols == x_cols and not plan.partial_writes \
+            and merged[0][3] * x_cols == view.tensor.base.numel:
+        # whole rows of the whole tensor: chunks of rows can be uploaded, reduced and downloaded independently
+        plan.pipeline = PipelineSpec(merged[0][3], 64, {x_idx: 4 * x_cols, out_idx: 4}, set(),
+                                     lambda lo, hi: [make_step(lo, 0, lo, hi - lo)])
+    return plan
+
+
+# --------------------------------------------------------------------------------------------------
 # Pattern: row softmax (manual reduce_max / exp / reduce_sum form, and asc2.softmax)
 # --------------------------------------------------------------------------------------------------
 def _softmax_source(value: Tile) -> Optional[Tile]:
@@ -1054,13 +1157,24 @@ def _match_attention(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
 # --------------------------------------------------------------------------------------------------
 # Entry point
 # --------------------------------------------------------------------------------------------------
-_MATCHERS = (_match_attention, _match_softmax, _match_elementwise, _match_matmul, _match_eltwise_program)
+_MATCHERS = (_match_attention, _match_softmax, _match_elementwise, _match_matmul, _match_eltwise_program,
+             _match_reduce)
+
+
+def _is_identity_store(eff: Effect) -> bool:
+    value, out_t = eff.args
+    view = resolve_view(value) if _node(value, "load") else None
+    return (view is not None and view.tensor.base.index == out_t.base.index and view.shape == value.shape
+            and view.tensor.static_shape() == out_t.static_shape() and _same_offsets(view.offsets, eff.attrs["offsets"]))
 
 
 def build_plan(trace: KernelTrace) -> Plan:
     """The C-ABI calls that reproduce the traced kernel's effect on global memory."""
-    stores = [e for e in trace.effects if e.kind == "store"]
-    others = [e for e in trace.effects if e.kind not in ("store", "matmul_acc")]
+    def is_store(e: Effect) -> bool:
+        # a one-element tile is stored through the scalar form of asc2.store; it is a tile store all the same
+        return e.kind == "store" or (e.kind == "store_scalar" and isinstance(e.args[0], Tile))
+    stores = [e for e in trace.effects if is_store(e)]
+    others = [e for e in trace.effects if not is_store(e) and e.kind != "matmul_acc"]
     if others:
         raise _unsupported(f"'{others[0].kind}' side effect")
     if not stores:
@@ -1068,6 +1182,8 @@ def build_plan(trace: KernelTrace) -> Plan:
     total = Plan("")
     names = []
     for eff in stores:
+        if _is_identity_store(eff):
+            continue        # a tile stored back to where it was loaded from changes nothing
         plan = None
         for matcher in _MATCHERS:
             plan = matcher(trace, eff)
@@ -1086,8 +1202,10 @@ def build_plan(trace: KernelTrace) -> Plan:
             if k in total.temps:
                 raise _unsupported("several stores that each need temporary buffers")
             total.temps[k] = v
+    if not names:
+        raise _unsupported("kernel whose only stores write tiles back unchanged")
     total.pattern = "+".join(names)
-    if len(stores) == 1 and not total.temps:
+    if len(names) == 1 and not total.temps:
         total.pipeline = plan.pipeline
     total.reads = {i for i in total.reads if isinstance(i, int)}
     total.writes = {i for i in total.writes if isinstance(i, int)}

@@ -201,3 +201,68 @@ def where_scalar_op(x_ptr: asc.GlobalAddress, scalar, z_ptr: asc.GlobalAddress, 
     xt = asc2.load(x, [WHERE_SIZE], offsets=[0])
     zt = asc2.where(op(xt, scalar), asc.number(0.0, x_ptr.dtype), asc.number(1.0, x_ptr.dtype))
     asc2.store(zt, z, offsets=[0])
+
+
+# ---- reductions and the softmax op (python/test/asc2/operations/test_{reduce_ops,softmax}.py)
+@asc2.jit(always_compile=True)
+def reduce_axis(input_ptr: asc.GlobalAddress, output_ptr: asc.GlobalAddress, reduce_dim: asc.ConstExpr,
+                input_shape: asc.ConstExpr, input_offsets: asc.ConstExpr, output_shape: asc.ConstExpr,
+                output_offsets: asc.ConstExpr, op: asc.ConstExpr, keep_dims: asc.ConstExpr) -> None:
+    g_input = asc2.tensor(input_ptr, input_shape)
+    g_output = asc2.tensor(output_ptr, output_shape)
+    input = asc2.load(g_input, input_shape, offsets=input_offsets)
+    output = op(input, reduce_dim, keep_dims=keep_dims)
+    asc2.store(output, g_output, offsets=output_offsets)
+
+
+@asc2.jit(always_compile=True)
+def reduce_all(input_ptr: asc.GlobalAddress, output_ptr: asc.GlobalAddress, input_shape: asc.ConstExpr,
+               input_offsets: asc.ConstExpr, output_shape: asc.ConstExpr, output_offsets: asc.ConstExpr,
+               op: asc.ConstExpr) -> None:
+    g_input = asc2.tensor(input_ptr, input_shape)
+    g_output = asc2.tensor(output_ptr, output_shape)
+    input = asc2.load(g_input, input_shape, offsets=input_offsets)
+    scalar = op(input)
+    output = asc2.full(output_shape, scalar, dtype=input.dtype)
+    asc2.store(output, g_output, offsets=output_offsets)
+
+
+@asc2.jit(always_compile=True)
+def reduce_tile(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, size: int, tile_size: asc.ConstExpr[int]):
+    x_gm = asc2.tensor(x_ptr, [size])
+    out_gm = asc2.tensor(out_ptr, [1])
+    tile = asc2.load(x_gm, [tile_size], offsets=[0])
+    max_val = asc2.reduce_max(tile)
+    result = asc2.full([1], max_val, dtype=tile.dtype)
+    asc2.store(result, out_gm, offsets=[0])
+
+
+@asc2.jit(always_compile=True)
+def row_sums(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, num_rows: int, num_cols: asc.ConstExpr[int],
+             rows_per_tile: asc.ConstExpr[int]):
+    """Each block walks row tiles and stores their row sums: the tiles merge into one call."""
+    x_gm = asc2.tensor(x_ptr, [num_rows, num_cols])
+    out_gm = asc2.tensor(out_ptr, [num_rows])
+    for i in range(asc2.block_idx() * rows_per_tile, num_rows, asc2.block_num() * rows_per_tile):
+        tile = asc2.load(x_gm, [rows_per_tile, num_cols], offsets=[i, 0])
+        asc2.store(asc2.reduce_sum(tile, 1), out_gm, offsets=[i])
+
+
+@asc2.jit(always_compile=True)
+def softmax_1d(dst_ptr, src_ptr, length: asc.ConstExpr) -> None:
+    dst = asc2.tensor(dst_ptr, [length])
+    src = asc2.tensor(src_ptr, [length])
+    src_tile = asc2.load(src, shape=[length], offsets=[0])
+    dst_tile = asc2.softmax(src_tile)
+    asc2.store(dst_tile, dst, offsets=[0])
+    asc2.store(src_tile, src, offsets=[0])
+
+
+@asc2.jit(always_compile=True)
+def softmax_2d(dst_ptr, src_ptr, shape: asc.ConstExpr) -> None:
+    dst = asc2.tensor(dst_ptr, shape)
+    src = asc2.tensor(src_ptr, shape)
+    src_tile = asc2.load(src, shape=shape, offsets=[0, 0])
+    dst_tile = asc2.softmax(src_tile)
+    asc2.store(dst_tile, dst, offsets=[0, 0])
+    asc2.store(src_tile, src, offsets=[0, 0])

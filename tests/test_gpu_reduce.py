@@ -1,0 +1,164 @@
+"""Reductions on the GPU: the reference's operation tests through the asc2 surface
+(python/test/asc2/operations/test_reduce_ops.py:17-104, test_softmax.py: same shapes, distributions and
+torch goldens) and the C-ABI entry point at sizes beyond L2.  max / min are bit-exact; sums and products
+are compared with torch's CPU result within the rounding of a different summation order."""
+import ctypes
+
+import pytest
+import torch
+
+import asc.runtime.config as config
+import asc2
+
+import asc2_scripts as K
+from pyasc_b200 import capi
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def select_platform(backend, platform, device_id):
+    config.set_platform(backend, platform, device_id)
+
+
+REDUCE_CASES = [
+    (asc2.reduce_prod, torch.prod, False, 0), (asc2.reduce_prod, torch.prod, False, 1),
+    (asc2.reduce_min, torch.amin, False, 0), (asc2.reduce_min, torch.amin, False, 1),
+    (asc2.reduce_sum, torch.sum, False, 0), (asc2.reduce_sum, torch.sum, False, 1),
+    (asc2.reduce_max, torch.amax, False, 0), (asc2.reduce_max, torch.amax, False, 1),
+    (asc2.reduce_prod, torch.prod, True, 0), (asc2.reduce_sum, torch.sum, True, 0),
+]
+
+
+@pytest.mark.parametrize("op, torch_op, keep_dims, dim", REDUCE_CASES, ids=lambda v: getattr(v, "__name__", str(v)))
+def test_reduce(op, torch_op, keep_dims, dim):
+    shape = [64, 32]
+    gen = torch.Generator().manual_seed(2026)
+    x = torch.randn(shape, generator=gen) * 2.0
+    output_shape = list(shape)
+    if keep_dims:
+        output_shape[dim] = 1
+    else:
+        del output_shape[dim]
+    output = torch.zeros(output_shape)
+    K.reduce_axis[1](x, output, dim, shape, [0, 0], output_shape, [0] * len(output_shape), op, keep_dims)
+    expected = torch_op(x, dim, keepdim=keep_dims)
+    if op in (asc2.reduce_max, asc2.reduce_min):
+        assert torch.equal(output, expected)
+    else:
+        # a product of 32 or 64 factors accumulates one rounding per factor in either order
+        torch.testing.assert_close(output, expected, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("op, torch_op", [(asc2.reduce_sum, torch.sum), (asc2.reduce_max, torch.amax),
+                                          (asc2.reduce_min, torch.amin), (asc2.reduce_prod, torch.prod)],
+                         ids=lambda v: getattr(v, "__name__", str(v)))
+def test_reduce_all(op, torch_op):
+    gen = torch.Generator().manual_seed(7)
+    x = torch.randn([32, 32], generator=gen) * (1.05 if op is asc2.reduce_prod else 2.0)
+    out = torch.zeros(32)
+    K.reduce_all[1](x, out, [32, 32], [0, 0], [32], [0], op)
+    expected = torch.ones(32) * torch_op(x).item()
+    torch.testing.assert_close(out, expected, rtol=2e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("tile_size", [1, 7, 17])
+def test_reduce_partial_tile(tile_size):
+    torch.manual_seed(0)
+    x = torch.rand(32, dtype=torch.float32) * -10.0
+    x[tile_size:] = 1000.0
+    out = torch.empty(1, dtype=torch.float32)
+    K.reduce_tile[1](x, out, 32, tile_size=tile_size)
+    torch.testing.assert_close(out, torch.amax(x[:tile_size]).unsqueeze(0), rtol=0, atol=0)
+
+
+def test_row_sums_over_all_blocks():
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn(4096, 1024, generator=gen)
+    out = torch.full((4096, ), -1.0)
+    K.row_sums[16](x, out, 4096, 1024, 8)
+    torch.testing.assert_close(out, x.sum(1), rtol=1e-5, atol=1e-4)
+    torch.testing.assert_close(out, x.double().sum(1).float(), rtol=1e-5, atol=1e-4)
+
+
+@pytest.mark.parametrize("shape", [[1, 8], [4, 256]])
+def test_softmax_2d_op(shape):
+    src = torch.rand(shape, dtype=torch.float32)
+    keep = src.clone()
+    dst = torch.zeros_like(src)
+    K.softmax_2d[1](dst, src, shape)
+    torch.testing.assert_close(dst, torch.softmax(keep, dim=1))
+    assert torch.equal(src, keep)                      # the tile stored back to the source is unchanged
+
+
+@pytest.mark.parametrize("length", [8, 1024])
+def test_softmax_1d_op(length):
+    src = torch.rand(length, dtype=torch.float32)
+    dst = torch.zeros_like(src)
+    K.softmax_1d[1](dst, src, length)
+    torch.testing.assert_close(dst, torch.softmax(src, dim=0))
+
+
+# ------------------------------------------------------------------------------- C ABI
+@pytest.fixture(scope="module")
+def lib():
+    torch.cuda.set_device(0)
+    return capi.load()
+
+
+def call(lib, x, out, rows, cols, ld, axis, kind, n_fill=1, expect=0):
+    rc = lib.asc_cuda_reduce_f32(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()), rows, cols, ld, axis,
+                                 kind, n_fill, None)
+    assert rc == expect, f"returned {rc}: {capi.status_string(rc)} {capi.last_cuda_error()}"
+    if rc == 0:
+        capi.check_device_status(None)
+
+
+@pytest.mark.parametrize("rows, cols", [(1, 1), (3, 5), (1000, 33), (257, 4096), (65536, 1024), (37, 100003)])
+def test_capi_row_and_column_reductions(lib, rows, cols):
+    """Includes a 256 MiB window (beyond L2), rows long enough for the CTA-per-row kernel and ragged sizes."""
+    gen = torch.Generator(device="cuda").manual_seed(rows * 31 + cols)
+    x = torch.randn(rows, cols + 3, device="cuda", generator=gen)      # pitch != cols
+    win = x[:, :cols]
+    for axis, n_out in ((1, rows), (0, cols)):
+        out = torch.full((n_out + 1, ), 7.0, device="cuda")
+        call(lib, x, out, rows, cols, cols + 3, axis, 1)
+        assert torch.equal(out[:n_out], win.amax(dim=axis)) and out[n_out] == 7.0
+        call(lib, x, out, rows, cols, cols + 3, axis, 2)
+        assert torch.equal(out[:n_out], win.amin(dim=axis))
+        call(lib, x, out, rows, cols, cols + 3, axis, 0)
+        ref = win.double().sum(dim=axis)
+        scale = win.abs().double().sum(dim=axis).clamp_min(1e-30)
+        assert float(((out[:n_out].double() - ref).abs() / scale).max()) < 2e-6     # error relative to sum |x|
+    small = (torch.rand(rows, min(cols, 64), device="cuda", generator=gen) * 0.2 + 0.9).contiguous()
+    out = torch.empty(rows, device="cuda")
+    call(lib, small, out, rows, small.shape[1], small.shape[1], 1, 3)
+    torch.testing.assert_close(out, small.double().prod(dim=1).float(), rtol=1e-5, atol=0)
+
+
+def test_capi_full_reduction_and_rejections(lib):
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(512, 1000, device="cuda", generator=gen)
+    out = torch.zeros(40, device="cuda")
+    call(lib, x, out, 512, 1000, 1000, -1, 1, n_fill=33)
+    assert torch.equal(out[:33], x.max().expand(33)) and bool((out[33:] == 0).all())
+    call(lib, x, out, 512, 1000, 1000, -1, 0, n_fill=1)
+    assert abs(float(out[0]) - float(x.double().sum())) < 1e-2
+    call(lib, x, out, 0, 1000, 1000, 1, 0)                              # nothing to write
+    call(lib, x, out, 512, 1000, 999, 1, 0, expect=1)                   # pitch smaller than the row
+    call(lib, x, out, 512, 1000, 1000, 2, 0, expect=1)                  # no such axis
+    call(lib, x, out, 512, 1000, 1000, 1, 4, expect=1)                  # no such kind
+    call(lib, x, out, 1 << 13, 1 << 12, 1 << 12, -1, 0, expect=6)       # a full reduction is for tile-sized windows
+
+
+def test_row_sums_pinned_pipelined_matches_plain():
+    """64 MiB of page-locked input takes the chunked three-stream launch path."""
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(16384, 1024, generator=gen)
+    plain = torch.empty(16384)
+    K.row_sums[16](x, plain, 16384, 1024, 8)
+    xp, outp = x.pin_memory(), torch.empty(16384).pin_memory()
+    K.row_sums[16](xp, outp, 16384, 1024, 8)
+    assert K.row_sums.last_plan.pipeline is not None
+    assert torch.equal(outp, plain)
+    torch.testing.assert_close(plain, x.sum(1), rtol=1e-5, atol=1e-4)

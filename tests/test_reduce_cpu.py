@@ -1,0 +1,78 @@
+"""Reduction and softmax-op kernels on CPU: the plans the launcher builds for the reference's operation
+tests (python/test/asc2/operations/test_reduce_ops.py, test_softmax.py).  ``DRY_RUN=1`` stops before
+the device launch."""
+import pytest
+import torch
+
+import asc2
+
+import asc2_scripts as K
+
+
+@pytest.fixture(autouse=True)
+def dry_run(monkeypatch):
+    monkeypatch.setenv("DRY_RUN", "1")
+
+
+def step_of(jit_fn):
+    plan = jit_fn.last_plan
+    assert len(plan.steps) == 1, plan
+    return plan, plan.steps[0]
+
+
+@pytest.mark.parametrize("dim, keep_dims, note", [
+    (0, False, "axis 0 of [64, 32] at (0, 0) -> [0, +32)"),
+    (1, False, "axis 1 of [64, 32] at (0, 0) -> [0, +64)"),
+    (0, True, "axis 0 of [64, 32] at (0, 0) -> [0, +32)"),
+])
+def test_axis_reduction_plans(dim, keep_dims, note):
+    x = torch.zeros(64, 32)
+    out_shape = [64, 32]
+    if keep_dims:
+        out_shape[dim] = 1
+    else:
+        del out_shape[dim]
+    K.reduce_axis[1](x, torch.zeros(out_shape), dim, [64, 32], [0, 0], out_shape, [0] * len(out_shape), asc2.reduce_min,
+                     keep_dims)
+    plan, step = step_of(K.reduce_axis)
+    assert plan.pattern == "reduce:min" and step.fn_name == "asc_cuda_reduce_f32" and step.note == "min " + note
+    assert plan.reads == {0} and plan.writes == {1} and not plan.partial_writes
+
+
+def test_full_reduction_fills_the_stored_tile():
+    x = torch.zeros(64, 32)
+    K.reduce_all[1](x, torch.zeros(32), [64, 32], [0, 0], [32], [0], asc2.reduce_sum)
+    assert step_of(K.reduce_all)[1].note == "sum axis -1 of [64, 32] at (0, 0) -> [0, +32)"
+    for tile in (1, 7, 17):
+        K.reduce_tile[1](torch.zeros(32), torch.empty(1), 32, tile_size=tile)
+        assert step_of(K.reduce_tile)[1].note == f"max axis -1 of [1, {tile}] at (0, 0) -> [0, +1)"
+
+
+def test_row_tiles_of_all_blocks_merge_into_one_call():
+    x = torch.zeros(4096, 1024)
+    K.row_sums[16](x, torch.empty(4096), 4096, 1024, 8)
+    plan, step = step_of(K.row_sums)
+    assert step.note == "sum axis 1 of [4096, 1024] at (0, 0) -> [0, +4096)" and not plan.partial_writes
+    # keep_dims along the last axis would make a [rows, 1] tile, which the surface rejects like the reference
+    with pytest.raises(RuntimeError, match="aligned by 32 bytes"):
+        K.reduce_axis[1](x, torch.zeros(4096, 1), 1, [4096, 1024], [0, 0], [4096, 1], [0, 0], asc2.reduce_sum, True)
+
+
+def test_reduction_rejections():
+    x = torch.zeros(64, 32)
+    with pytest.raises(NotImplementedError, match="past the end"):
+        K.reduce_axis[1](x, torch.zeros(32), 0, [64, 32], [32, 0], [32], [0], asc2.reduce_sum, False)
+    with pytest.raises(NotImplementedError, match="float32 only"):
+        K.reduce_axis[1](x.half(), torch.zeros(32, dtype=torch.float16), 0, [64, 32], [0, 0], [32], [0], asc2.reduce_sum,
+                         False)
+
+
+def test_softmax_op_plans_and_identity_store():
+    s = torch.zeros(4, 256)
+    K.softmax_2d[1](torch.zeros_like(s), s, [4, 256])
+    plan, step = step_of(K.softmax_2d)        # the store of the unchanged source tile adds no call
+    assert step.fn_name == "asc_cuda_softmax_f32" and step.note == "rows [0, 4) x 256 cols"
+    assert plan.reads == {1} and plan.writes == {0}
+    v = torch.zeros(1024)
+    K.softmax_1d[1](torch.zeros_like(v), v, 1024)
+    assert step_of(K.softmax_1d)[1].note == "rows [0, 1) x 1024 cols"

@@ -143,13 +143,19 @@ def test_workload_scripts_match_at_full_size():
 
 def test_unsupported_pattern_raises_not_implemented():
     @asc2.jit
-    def column_sums(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: asc.ConstExpr[int],
-                    cols: asc.ConstExpr[int]):
-        x = asc2.load(asc2.tensor(x_ptr, [rows, cols]), [rows, cols], offsets=[0, 0])
-        asc2.store(asc2.reduce_sum(x, 0), asc2.tensor(out_ptr, [cols]), offsets=[0])
-    x = np.zeros((16, 64), np.float32)
+    def scatter_add(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+        x = asc2.load(asc2.tensor(x_ptr, [n]), [n], offsets=[0])
+        asc2.atomic_add(x, asc2.tensor(out_ptr, [n]), [0])
+    x = np.zeros(64, np.float32)
     with pytest.raises(NotImplementedError, match="no kernel for this pattern"):
-        column_sums[1](x, np.zeros(64, np.float32), 16, 64)
+        scatter_add[1](x, x.copy(), 64)
+
+    @asc2.jit
+    def shifted_copy(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+        x = asc2.load(asc2.tensor(x_ptr, [2 * n]), [n], offsets=[n])
+        asc2.store(asc2.exp(x), asc2.tensor(out_ptr, [2 * n]), offsets=[0])
+    with pytest.raises(NotImplementedError, match="no kernel for this pattern"):
+        shifted_copy[1](np.zeros(128, np.float32), np.zeros(128, np.float32), 64)
 
 
 # ----------------------------------------------------------------------------- reference error behaviour
