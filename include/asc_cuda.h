@@ -139,6 +139,16 @@ int32_t asc_cuda_eltwise_program(const int32_t* ops, const int32_t* args, int32_
                                  const int32_t* input_types, int32_t n_inputs, void* out, int32_t out_type,
                                  int64_t n, void* stream);
 
+/* The same over a [rows, cols] window of row-major tensors that all have a row pitch of `ld` elements
+ * (every pointer addresses the window's first element): what a 2-D tile that does not span whole rows
+ * touches (asc2.load / asc2.store with 2-D offsets, python/asc/language/tile/memory_ops.py; exercised by
+ * python/test/asc2/operations/test_memory_ops.py:10-59).  A window with ld != cols is limited to 2^32
+ * elements. */
+int32_t asc_cuda_eltwise_program_2d(const int32_t* ops, const int32_t* args, int32_t n_ops,
+                                    const void* const* inputs, const int32_t* input_types, int32_t n_inputs,
+                                    void* out, int32_t out_type, int64_t rows, int64_t cols, int64_t ld,
+                                    void* stream);
+
 /* Reduction of a row-major [rows, cols] fp32 window with row pitch `ld` (elements).  kind: 0 sum, 1 max,
  * 2 min, 3 product.  axis 1: out[r] = reduce over the columns of row r; axis 0: out[c] = reduce over the
  * rows of column c; axis -1: out[0 .. n_fill) all receive the reduction of the whole window (the window is

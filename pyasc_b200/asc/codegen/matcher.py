@@ -280,9 +280,9 @@ def _match_elementwise(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         return None
     if value.dtype != KT.float32 or out_t.dtype != KT.float32 or any(v.tensor.dtype != KT.float32 for v in operands):
         return None  # the generic elementwise program handles the other types
-    window = _flat_window(out_t, offsets, value.shape)
+    window = _flat_window(out_t, offsets, value.shape) if eff.kind == "store" else None
     if window is None:
-        raise _unsupported("elementwise kernel whose tiles are not contiguous ranges of the tensor")
+        return None   # 2-D tiles that do not span whole rows: the program kernel handles windows
     _check_fits(out_t)
     for v in operands:
         _check_fits(v.tensor)
@@ -373,8 +373,9 @@ class _EltProgram:
     immediates; of two tile operands the one needing the deeper stack is evaluated first (with the
     swapped opcode when that reverses the order), which keeps most expressions at depth 2."""
 
-    def __init__(self, shape, offsets, out_t: Tensor):
+    def __init__(self, shape, offsets, out_t: Tensor, scalar_store: bool = False):
         self.shape, self.offsets, self.out_t = shape, offsets, out_t
+        self.scalar_store = scalar_store
         self.inputs: List[Tensor] = []
         self.ops: List[int] = []
         self.args: List[int] = []
@@ -406,12 +407,37 @@ class _EltProgram:
             return _Frag(rhs.code + lhs.code + [(_SWAPPED[code], 0)], max(rhs.need, lhs.need + 1))
         return _Frag(lhs.code + rhs.code + [(code, 0)], max(lhs.need, rhs.need + 1))
 
+    def _load(self, tensor: Tensor) -> Optional[_Frag]:
+        for k, t in enumerate(self.inputs):
+            if t.base.index == tensor.base.index:
+                return _Frag([(_OP_LOAD, k)], 1) if t.dtype == tensor.dtype else None
+        self.inputs.append(tensor)
+        return _Frag([(_OP_LOAD, len(self.inputs) - 1)], 1)
+
     def gen(self, v: Any, scalar_dtype: Optional[DataType] = None) -> Optional[_Frag]:
         """Code for ``v``, or None when ``v`` is not expressible."""
         if isinstance(v, PlainValue):
-            if not v.is_const:
+            if v.is_const:
+                return _Frag([], 0, self._word(v.value, scalar_dtype or v.dtype))
+            if not self.scalar_store:
                 return None
-            return _Frag([], 0, self._word(v.value, scalar_dtype or v.dtype))
+            # a one-element store: scalars loaded from the stored position and arithmetic on them
+            if v.op == "tile_scalar":
+                node = v.args[0]
+                if node.kind != "load_scalar":
+                    return None
+                tensor = node.args[0]
+                if tensor.static_shape() != self.out_t.static_shape() or tensor.dtype.name not in _ELT_TYPE \
+                        or not _same_offsets(node.attrs["offsets"], self.offsets):
+                    return None
+                return self._load(tensor)
+            code = (_BINARY_CODE if v.dtype.is_float() else _INT_BINARY_CODE).get(v.op)
+            if code is None or v.dtype.name not in _ELT_TYPE or len(v.args) != 2:
+                return None
+            lhs, rhs = self.gen(v.args[0], v.dtype), self.gen(v.args[1], v.dtype)
+            if lhs is None or rhs is None:
+                return None
+            return self._rounded(self._binary(code, lhs, rhs), v.dtype)
         if isinstance(v, (bool, int, float)):
             return _Frag([], 0, self._word(v, scalar_dtype or (KT.float32 if isinstance(v, float) else KT.int32)))
         if not isinstance(v, Tile) or v.shape != self.shape:
@@ -423,11 +449,7 @@ class _EltProgram:
                 return None
             if view.tensor.static_shape() != self.out_t.static_shape() or view.tensor.dtype.name not in _ELT_TYPE:
                 return None
-            for k, t in enumerate(self.inputs):
-                if t.base.index == view.tensor.base.index:
-                    return _Frag([(_OP_LOAD, k)], 1) if t.dtype == view.tensor.dtype else None
-            self.inputs.append(view.tensor)
-            return _Frag([(_OP_LOAD, len(self.inputs) - 1)], 1)
+            return self._load(view.tensor)
         if node.kind == "full":
             return self.gen(node.attrs["value"], v.dtype)
         if v.dtype.name not in _ELT_TYPE and node.kind != "compare":
@@ -481,35 +503,69 @@ class _EltProgram:
         return True
 
 
+def _tile_windows(tshape: Tuple[int, ...], offsets: Sequence[PlainValue], shape: Tuple[int, ...],
+                  env: Dict[str, np.ndarray], n: int):
+    """For 2-D tiles of a 2-D tensor: the distinct (row0, col0, rows, cols) windows the instances store, clipped
+    to the tensor (stores are clipped, LowerAscTileDataTransfer.cpp:254-261), and whether together they are
+    exactly the regular tile grid of the whole tensor."""
+    row0, col0 = eval_int(offsets[0], env, n), eval_int(offsets[1], env, n)
+    if n and (row0.min() < 0 or col0.min() < 0):
+        raise RuntimeError("Negative tile offset in kernel")
+    keep = (row0 < tshape[0]) & (col0 < tshape[1])
+    origins = sorted(set(zip(row0[keep].tolist(), col0[keep].tolist())))
+    windows = [(r, c, min(shape[0], tshape[0] - r), min(shape[1], tshape[1] - c)) for r, c in origins]
+    grid = {(r, c) for r in range(0, tshape[0], shape[0]) for c in range(0, tshape[1], shape[1])} \
+        if tshape[0] * tshape[1] <= (1 << 24) * shape[0] * shape[1] else None
+    return windows, grid is not None and set(origins) == grid
+
+
 def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     value, out_t = eff.args
     offsets = eff.attrs["offsets"]
-    if not isinstance(value, Tile) or out_t.dtype.name not in _ELT_TYPE or value.dtype != out_t.dtype:
+    scalar_store = eff.kind == "store_scalar"
+    if not isinstance(value, (Tile, PlainValue)) or out_t.dtype.name not in _ELT_TYPE or value.dtype != out_t.dtype:
         return None
-    prog = _EltProgram(value.shape, offsets, out_t)
+    tshape = out_t.static_shape()
+    prog = _EltProgram((1, ) if scalar_store else value.shape, offsets, out_t, scalar_store)
     if not prog.compile(value) or not prog.inputs:
         return None
     if len(prog.ops) > ELT_MAX_OPS or len(prog.inputs) > ELT_MAX_INPUTS or prog.max_depth > ELT_MAX_STACK:
         raise _unsupported(f"elementwise expression with {len(prog.ops)} operations, {len(prog.inputs)} inputs and a "
                            f"stack of {prog.max_depth} (limits: {ELT_MAX_OPS}, {ELT_MAX_INPUTS}, {ELT_MAX_STACK})")
-    window = _flat_window(out_t, offsets, value.shape)
-    if window is None:
-        raise _unsupported("elementwise kernel whose tiles are not contiguous ranges of the tensor")
     _check_fits(out_t)
     for t in prog.inputs:
         _check_fits(t)
-    flat_off, tile_elems = window
     numel = 1
-    for d in out_t.static_shape():
+    for d in tshape:
         numel *= d
     env = enumerate_instances(trace.core_num, eff.loops)
     n = env_count(env)
-    starts = eval_int(flat_off, env, n)
-    if starts.size and starts.min() < 0:
-        raise RuntimeError("Negative tile offset in kernel")
-    ends = np.minimum(starts + tile_elems, numel)
-    intervals = merge_intervals(starts, ends)
-    if len(intervals) > MAX_CALLS:
+    windows: List[Tuple[int, int, int, int]] = []     # 2-D mode: (row0, col0, rows, cols)
+    if scalar_store:
+        if len(offsets) != len(tshape):
+            raise RuntimeError("number of 'offsets' must match the rank of the tensor")
+        flat_off = PlainValue.const(0)
+        stride = 1
+        for d in range(len(tshape) - 1, -1, -1):
+            flat_off = flat_off + offsets[d] * stride
+            stride *= tshape[d]
+        window = (flat_off, 1)
+    else:
+        window = _flat_window(out_t, offsets, value.shape)
+    if window is not None:
+        flat_off, tile_elems = window
+        starts = eval_int(flat_off, env, n)
+        if starts.size and starts.min() < 0:
+            raise RuntimeError("Negative tile offset in kernel")
+        intervals = merge_intervals(starts, np.minimum(starts + tile_elems, numel))
+    elif len(tshape) == 2 and len(value.shape) == 2:
+        windows, whole = _tile_windows(tshape, offsets, value.shape, env, n)
+        intervals = [(0, numel)] if whole else []
+        if whole:
+            windows = []
+    else:
+        raise _unsupported("elementwise kernel whose tiles are neither contiguous ranges nor 2-D windows of a matrix")
+    if len(intervals) + len(windows) > MAX_CALLS:
         raise _unsupported("elementwise kernel touching more than 4096 disjoint ranges")
 
     plan = Plan("elementwise:program")
@@ -537,8 +593,22 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
                     _p(ptrs[out_idx] + out_size * lo), ctypes.c_int32(out_type), ctypes.c_int64(hi - lo), stream)
         return [Step("asc_cuda_eltwise_program", build, f"{n_ops} ops over [{lo}, {hi})")]
 
+    def make_2d(r0: int, c0: int, rows: int, cols: int) -> Step:
+        first = r0 * tshape[1] + c0
+
+        def build(ptrs, stream):
+            ins = (ctypes.c_void_p * n_in)(*[ptrs[i] + sz * first for i, sz in zip(in_idx, in_size)])
+            return (ops_arr, args_arr, ctypes.c_int32(n_ops), ins, types_arr, ctypes.c_int32(n_in),
+                    _p(ptrs[out_idx] + out_size * first), ctypes.c_int32(out_type), ctypes.c_int64(rows),
+                    ctypes.c_int64(cols), ctypes.c_int64(tshape[1]), stream)
+        return Step("asc_cuda_eltwise_program_2d", build, f"{n_ops} ops over [{rows}, {cols}] at ({r0}, {c0})")
+
     for lo, hi in intervals:
         plan.steps += make(lo, hi)
+    for w in windows:
+        plan.steps.append(make_2d(*w))
+    if not plan.steps:
+        raise _unsupported("elementwise kernel whose tiles all lie outside the tensor")
     if not plan.partial_writes and len(intervals) == 1:
         streamed = {i: sz for i, sz in zip(in_idx, in_size)}
         streamed[out_idx] = out_size
@@ -1171,8 +1241,8 @@ def _is_identity_store(eff: Effect) -> bool:
 def build_plan(trace: KernelTrace) -> Plan:
     """The C-ABI calls that reproduce the traced kernel's effect on global memory."""
     def is_store(e: Effect) -> bool:
-        # a one-element tile is stored through the scalar form of asc2.store; it is a tile store all the same
-        return e.kind == "store" or (e.kind == "store_scalar" and isinstance(e.args[0], Tile))
+        # scalars and one-element tiles go through the scalar form of asc2.store: a store of one element
+        return e.kind in ("store", "store_scalar")
     stores = [e for e in trace.effects if is_store(e)]
     others = [e for e in trace.effects if not is_store(e) and e.kind != "matmul_acc"]
     if others:
@@ -1185,7 +1255,8 @@ def build_plan(trace: KernelTrace) -> Plan:
         if _is_identity_store(eff):
             continue        # a tile stored back to where it was loaded from changes nothing
         plan = None
-        for matcher in _MATCHERS:
+        scalar_value = not isinstance(eff.args[0], Tile)
+        for matcher in ((_match_eltwise_program, ) if scalar_value else _MATCHERS):
             plan = matcher(trace, eff)
             if plan is not None:
                 break

@@ -63,7 +63,17 @@ struct EltProgram {
   int32_t in_type[kMaxInputs];
   void* out;
   int32_t out_type;
+  // 2-D window: element i of the window is row i / cols, column i % cols of tensors with a row pitch of ld
+  // elements.  cols == 0: the operands are flat arrays (element i is at index i).
+  uint32_t cols, ld;
 };
+
+__device__ __forceinline__ int64_t element_offset(const EltProgram& prog, int64_t i) {
+  if (prog.cols == 0) return i;
+  const uint32_t u = static_cast<uint32_t>(i);
+  const uint32_t r = u / prog.cols;
+  return static_cast<int64_t>(r) * prog.ld + (u - r * prog.cols);
+}
 
 constexpr int kThreads = 256;
 constexpr int kReusedInput = 0x100;  // flag in EltProgram::in_type: the program loads this input more than once
@@ -165,13 +175,15 @@ __device__ __forceinline__ void store_oct(void* p, int type, int64_t i, const fl
 // A thread's kV lanes: kV == 1 is the element at i; otherwise kV / 4 quads, the first at i and the
 // others kQuadStride elements apart (so that a warp's accesses stay contiguous inside a CTA tile).
 template <int kV, bool kLoadedOnce = false>
-__device__ __forceinline__ void load_group(const void* p, int typeword, int64_t i, float (&v)[kV]) {
+__device__ __forceinline__ void load_group(const EltProgram& prog, const void* p, int typeword, int64_t i,
+                                           float (&v)[kV]) {
   const int type = typeword & 0xff;
   if constexpr (kV >= 4) {
     const bool reused = !kLoadedOnce && (typeword & kReusedInput) != 0;
 #pragma unroll
-    for (int q = 0; q < kV / 4; ++q) load_quad(p, type, reused, i + q * kQuadStride, &v[4 * q]);
+    for (int q = 0; q < kV / 4; ++q) load_quad(p, type, reused, element_offset(prog, i + q * kQuadStride), &v[4 * q]);
   } else {
+    i = element_offset(prog, i);
     switch (type) {
       case T_F16: v[0] = __half2float(reinterpret_cast<const __half*>(p)[i]); break;
       case T_BF16: v[0] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]); break;
@@ -183,11 +195,12 @@ __device__ __forceinline__ void load_group(const void* p, int typeword, int64_t 
 }
 
 template <int kV>
-__device__ __forceinline__ void store_group(void* p, int type, int64_t i, const float (&v)[kV]) {
+__device__ __forceinline__ void store_group(const EltProgram& prog, void* p, int type, int64_t i, const float (&v)[kV]) {
   if constexpr (kV >= 4) {
 #pragma unroll
-    for (int q = 0; q < kV / 4; ++q) store_quad(p, type, i + q * kQuadStride, &v[4 * q]);
+    for (int q = 0; q < kV / 4; ++q) store_quad(p, type, element_offset(prog, i + q * kQuadStride), &v[4 * q]);
   } else {
+    i = element_offset(prog, i);
     switch (type) {
       case T_F16: reinterpret_cast<__half*>(p)[i] = __float2half_rn(v[0]); break;
       case T_BF16: reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v[0]); break;
@@ -333,7 +346,7 @@ struct Interpreter {
         case OP_LOAD:
           if (depth > 0) slots.put(depth - 1, top);
           ++depth;
-          load_group<kV>(prog.in[prog.arg[k]], prog.in_type[prog.arg[k]], i, top);
+          load_group<kV>(prog, prog.in[prog.arg[k]], prog.in_type[prog.arg[k]], i, top);
           break;
         case OP_CONST:
           if (depth > 0) slots.put(depth - 1, top);
@@ -363,7 +376,7 @@ struct Interpreter {
 #undef ASC_UN
 #undef ASC_BIN
 #undef ASC_LANES
-    store_group<kV>(prog.out, prog.out_type, i, top);
+    store_group<kV>(prog, prog.out, prog.out_type, i, top);
   }
 };
 
@@ -396,7 +409,7 @@ struct StaticStep {
                                              float (&st)[kStack][kV]) {
     if constexpr (K == P::n) {
       static_assert(D == 1, "a program leaves exactly one value");
-      if constexpr (kStore) store_group<kV>(prog.out, prog.out_type, i, st[0]);
+      if constexpr (kStore) store_group<kV>(prog, prog.out, prog.out_type, i, st[0]);
     } else {
       constexpr int word = P::at(K);
       constexpr int op = word & 0xff;
@@ -451,7 +464,7 @@ struct Compiled {
       for (int o = 0; o < kV / 8; ++o) store_oct(prog.out, prog.out_type, i + o * (kThreads * 8), &st[0][8 * o]);
     } else {
 #pragma unroll
-      for (int j = 0; j < P::inputs(); ++j) load_group<kV, true>(prog.in[j], prog.in_type[j], i, in[j]);
+      for (int j = 0; j < P::inputs(); ++j) load_group<kV, true>(prog, prog.in[j], prog.in_type[j], i, in[j]);
       StaticStep<P, kV, 0, 0, true>::run(prog, i, in, st);
     }
   }
@@ -556,9 +569,14 @@ int32_t try_compiled(const EltProgram& prog, const int32_t* ops, const int32_t* 
 
 }  // namespace
 
-extern "C" int32_t asc_cuda_eltwise_program(const int32_t* ops, const int32_t* args, int32_t n_ops,
-                                            const void* const* inputs, const int32_t* input_types, int32_t n_inputs,
-                                            void* out, int32_t out_type, int64_t n, void* stream) {
+extern "C" int32_t asc_cuda_eltwise_program_2d(const int32_t* ops, const int32_t* args, int32_t n_ops,
+                                               const void* const* inputs, const int32_t* input_types, int32_t n_inputs,
+                                               void* out, int32_t out_type, int64_t rows, int64_t cols, int64_t ld,
+                                               void* stream) {
+  if (rows < 0 || cols < 0 || ld < cols) return ASC_ERR_INVALID_ARG;
+  const bool strided = rows > 1 && ld != cols;
+  if (strided && (rows * cols >= (int64_t{1} << 32) || ld >= (int64_t{1} << 32))) return ASC_ERR_TOO_LARGE;
+  const int64_t n = rows * cols;
   if (n < 0 || n_ops <= 0 || n_ops > kMaxOps || n_inputs < 0 || n_inputs > kMaxInputs) return ASC_ERR_INVALID_ARG;
   if (ops == nullptr || args == nullptr || out == nullptr || (n_inputs > 0 && (inputs == nullptr || input_types == nullptr)))
     return ASC_ERR_INVALID_ARG;
@@ -605,14 +623,17 @@ extern "C" int32_t asc_cuda_eltwise_program(const int32_t* ops, const int32_t* a
   if (reinterpret_cast<uintptr_t>(out) % elem_size(out_type) != 0) return ASC_ERR_MISALIGNED;
   prog.out = out;
   prog.out_type = out_type;
+  prog.cols = strided ? static_cast<uint32_t>(cols) : 0u;
+  prog.ld = strided ? static_cast<uint32_t>(ld) : 0u;
   int sms = 0;
   int32_t rc = aschost::sm_count(&sms);
   if (rc != ASC_OK) return rc;
   bool vec = reinterpret_cast<uintptr_t>(out) % (4 * elem_size(out_type)) == 0;
   for (int i = 0; i < n_inputs; ++i) vec = vec && reinterpret_cast<uintptr_t>(inputs[i]) % (4 * elem_size(input_types[i])) == 0;
+  if (strided) vec = vec && cols % 4 == 0 && ld % 4 == 0;   // a quad must not straddle two rows
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!vec) return launch_interpreter<1>(prog, n, max_depth, sms, st);
-  if (g_use_compiled) {
+  if (g_use_compiled && !strided) {
     bool launched = false;
     rc = try_compiled<LeakyReluF32>(prog, ops, args, n_ops, n, sms, st, &launched);
     if (rc == ASC_OK) rc = try_compiled<LeakyReluF16>(prog, ops, args, n_ops, n, sms, st, &launched);
@@ -624,6 +645,12 @@ extern "C" int32_t asc_cuda_eltwise_program(const int32_t* ops, const int32_t* a
   if (g_lanes == 4 || n < kThreads * 8) return launch_interpreter<4>(prog, n, max_depth, sms, st);
   if (g_lanes == 16) return launch_interpreter<16>(prog, n, max_depth, sms, st);
   return launch_interpreter<8>(prog, n, max_depth, sms, st);
+}
+
+extern "C" int32_t asc_cuda_eltwise_program(const int32_t* ops, const int32_t* args, int32_t n_ops,
+                                            const void* const* inputs, const int32_t* input_types, int32_t n_inputs,
+                                            void* out, int32_t out_type, int64_t n, void* stream) {
+  return asc_cuda_eltwise_program_2d(ops, args, n_ops, inputs, input_types, n_inputs, out, out_type, 1, n, n, stream);
 }
 
 // tuning hook: bits 0-7 elements per thread and dispatch in the interpreter's aligned path (4, 8 or 16;

@@ -266,3 +266,60 @@ def softmax_2d(dst_ptr, src_ptr, shape: asc.ConstExpr) -> None:
     dst_tile = asc2.softmax(src_tile)
     asc2.store(dst_tile, dst, offsets=[0, 0])
     asc2.store(src_tile, src, offsets=[0, 0])
+
+
+# ---- loads and stores of tiles anywhere in a tensor (python/test/asc2/operations/test_memory_ops.py)
+@asc2.jit(always_compile=True)
+def add_static(x_ptr, y_ptr, z_ptr, tensor_shape: asc.ConstExpr, tile_shape: asc.ConstExpr, tile_id: asc.ConstExpr,
+               offsets: asc.ConstExpr) -> None:
+    xt = asc2.load(asc2.tensor(x_ptr, tensor_shape), tile_shape, tile_id=tile_id, offsets=offsets)
+    yt = asc2.load(asc2.tensor(y_ptr, tensor_shape), tile_shape, tile_id=tile_id, offsets=offsets)
+    zt = xt + yt
+    asc2.store(zt, asc2.tensor(z_ptr, tensor_shape), tile_id=tile_id, offsets=offsets)
+
+
+@asc2.jit(always_compile=True)
+def add_dynamic_1d(x_ptr, y_ptr, z_ptr, ts0, tile_shape: asc.ConstExpr, tile_id: asc.ConstExpr,
+                   offsets: asc.ConstExpr) -> None:
+    xt = asc2.load(asc2.tensor(x_ptr, [ts0]), tile_shape, tile_id=tile_id, offsets=offsets)
+    yt = asc2.load(asc2.tensor(y_ptr, [ts0]), tile_shape, tile_id=tile_id, offsets=offsets)
+    zt = xt + yt
+    asc2.store(zt, asc2.tensor(z_ptr, [ts0]), tile_id=tile_id, offsets=offsets)
+
+
+@asc2.jit(always_compile=True)
+def add_dynamic_2d(x_ptr, y_ptr, z_ptr, ts0, ts1, tile_shape: asc.ConstExpr, tile_id: asc.ConstExpr,
+                   offsets: asc.ConstExpr) -> None:
+    xt = asc2.load(asc2.tensor(x_ptr, [ts0, ts1]), tile_shape, tile_id=tile_id, offsets=offsets)
+    yt = asc2.load(asc2.tensor(y_ptr, [ts0, ts1]), tile_shape, tile_id=tile_id, offsets=offsets)
+    zt = xt + yt
+    asc2.store(zt, asc2.tensor(z_ptr, [ts0, ts1]), tile_id=tile_id, offsets=offsets)
+
+
+@asc2.jit(always_compile=True)
+def add_scalar(x_ptr, y_ptr, z_ptr, tensor_shape: asc.ConstExpr, offsets: asc.ConstExpr) -> None:
+    xt = asc2.load(asc2.tensor(x_ptr, tensor_shape), offsets=offsets)
+    yt = asc2.load(asc2.tensor(y_ptr, tensor_shape), offsets=offsets)
+    zt = xt + yt
+    asc2.store(zt, asc2.tensor(z_ptr, tensor_shape), offsets=offsets)
+
+
+@asc2.jit(always_compile=True)
+def copy_1elem(x_ptr, y_ptr, tensor_shape: asc.ConstExpr, offsets: asc.ConstExpr):
+    x = asc2.tensor(x_ptr, tensor_shape)
+    s = asc2.load(x, offsets=offsets)
+    y = asc2.tensor(y_ptr, tensor_shape)
+    asc2.store(asc2.full([1], s), y, offsets=offsets)
+
+
+@asc2.jit(always_compile=True)
+def scale_2d_tiles(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: int, cols: int, alpha: float,
+                   tile_r: asc.ConstExpr[int], tile_c: asc.ConstExpr[int]):
+    """Blocks walk the 2-D tile grid of a matrix (tile_id addressing); edge tiles are ragged."""
+    x_gm = asc2.tensor(x_ptr, [rows, cols])
+    out_gm = asc2.tensor(out_ptr, [rows, cols])
+    tiles_c = asc.ceildiv(cols, tile_c)
+    num_tiles = asc.ceildiv(rows, tile_r) * tiles_c
+    for t in range(asc2.block_idx(), num_tiles, asc2.block_num()):
+        tile = asc2.load(x_gm, [tile_r, tile_c], tile_id=[t // tiles_c, t % tiles_c])
+        asc2.store(asc2.tanh(tile * alpha), out_gm, tile_id=[t // tiles_c, t % tiles_c])

@@ -135,3 +135,56 @@ def gelu_case(approximate: bool, rows=30, cols=1024):
         return out
 
     return launch, gelu_torch(x, approximate), [x, out]
+
+
+# (dim, tensor_shape, tile_shape, tile_id, offsets, is_static): python/test/asc2/operations/test_memory_ops.py:10-59
+MEMORY_CASES = [
+    (1, [64], [16], [0], None, True), (1, [64], [16], [3], None, True),
+    (2, [128, 128], [32, 32], [0, 0], None, True), (2, [128, 128], [32, 32], [3, 3], None, True),
+    (2, [1024, 512], [128, 64], [1, 2], None, True), (1, [37], [8], [3], None, True),
+    (2, [123, 456], [13, 16], [2, 5], None, True),
+    (1, [64], [16], None, [0], True), (1, [64], [16], None, [48], True),
+    (2, [128, 128], [32, 32], None, [0, 0], True), (2, [128, 128], [32, 32], None, [96, 64], True),
+    (2, [1024, 512], [128, 64], None, [256, 128], True), (1, [53], [16], None, [22], True),
+    (2, [257, 511], [19, 24], None, [40, 64], True),
+    (1, [32], [8], [1], None, False), (1, [32], [8], [3], None, False),
+    (2, [16, 2048], [4, 512], [0, 3], None, False), (2, [16, 2048], [8, 256], [1, 7], None, False),
+    (2, [512, 512], [64, 64], [4, 4], None, False), (1, [99], [16], [5], None, False),
+    (2, [1000, 1000], [33, 40], [1, 1], None, False),
+    (1, [32], [8], None, [16], False), (1, [32], [8], None, [24], False),
+    (2, [16, 2048], [4, 512], None, [8, 1024], False), (2, [16, 2048], [12, 1024], None, [4, 0], False),
+    (2, [512, 512], [64, 64], None, [128, 256], False), (1, [77], [24], None, [48], False),
+    (2, [150, 300], [21, 40], None, [10, 20], False),
+    (1, [32], None, None, [0], True), (2, [32, 32], None, None, [0, 0], True),
+    (1, [1024], None, None, [0], True), (2, [512, 512], None, None, [0, 0], True),
+]
+
+
+def memory_case(dim, tensor_shape, tile_shape, tile_id, offsets, is_static):
+    """Returns (launch, expected): z = x + y inside the addressed tile (or element), zero elsewhere."""
+    gen = torch.Generator().manual_seed(2026)
+    x, y = [torch.randn(tensor_shape, generator=gen) for _ in range(2)]
+    z = torch.zeros(tensor_shape, dtype=torch.float32)
+
+    def launch():
+        if is_static:
+            if tile_shape is None:
+                K.add_scalar[1](x, y, z, tensor_shape, offsets)
+            else:
+                K.add_static[1](x, y, z, tensor_shape, tile_shape, tile_id, offsets)
+        elif dim == 1:
+            K.add_dynamic_1d[1](x, y, z, tensor_shape[0], tile_shape, tile_id, offsets)
+        else:
+            K.add_dynamic_2d[1](x, y, z, tensor_shape[0], tensor_shape[1], tile_shape, tile_id, offsets)
+        return z
+
+    actual = [i * s for i, s in zip(tile_id, tile_shape)] if tile_id is not None else offsets
+    if tile_shape is not None:
+        slices = tuple(slice(off, off + size) for off, size in zip(actual, tile_shape))
+    else:
+        slices = tuple(actual)
+    expected = torch.zeros_like(z)
+    expected[slices] = x[slices] + y[slices]
+    kernel = K.add_scalar if tile_shape is None else K.add_static if is_static else \
+        K.add_dynamic_1d if dim == 1 else K.add_dynamic_2d
+    return launch, expected, kernel

@@ -1,0 +1,97 @@
+"""Tile loads and stores anywhere in a tensor, on the GPU: the reference's memory-operation tests
+(python/test/asc2/operations/test_memory_ops.py: same shapes, tile ids / offsets, goldens) and the 2-D
+window entry point at sizes beyond L2.  Additions are bit-exact; untouched elements must stay untouched."""
+import ctypes
+
+import pytest
+import torch
+
+import asc.runtime.config as config
+
+import asc2_scripts as K
+import eltwise_cases as C
+from oracle import eltwise as E
+from pyasc_b200 import capi
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def select_platform(backend, platform, device_id):
+    config.set_platform(backend, platform, device_id)
+
+
+@pytest.mark.parametrize("case", C.MEMORY_CASES, ids=str)
+def test_load_store(case):
+    launch, expected, _ = C.memory_case(*case)
+    z = launch()
+    torch.testing.assert_close(z, expected, atol=1e-3, rtol=1e-3)
+    assert torch.equal(z, expected)
+
+
+@pytest.mark.parametrize("tensor_shape, offsets", [((16, ), (0, )), ((16, ), (7, )), ((16, 16), (0, 0)), ((16, 16), (7, 7))],
+                         ids=str)
+def test_store_1elem_tile(tensor_shape, offsets):
+    x = torch.randn(tensor_shape, dtype=torch.float32)
+    y = torch.zeros_like(x)
+    K.copy_1elem[1](x, y, tensor_shape, offsets)
+    expected = torch.zeros_like(x)
+    expected[offsets] = x[offsets]
+    assert torch.equal(y, expected)
+
+
+@pytest.mark.parametrize("rows, cols, tile_r, tile_c, cores", [(1000, 1000, 64, 128, 16), (130, 70, 32, 32, 3),
+                                                               (4096, 4096, 128, 256, 148)])
+def test_2d_tile_grid_kernel(rows, cols, tile_r, tile_c, cores):
+    gen = torch.Generator().manual_seed(rows + cols)
+    x = torch.randn(rows, cols, generator=gen)
+    out = torch.full_like(x, -7.0)
+    K.scale_2d_tiles[cores](x, out, rows, cols, 0.5, tile_r, tile_c)
+    torch.testing.assert_close(out, torch.tanh(x * 0.5), rtol=2e-6, atol=1e-6)
+
+
+# ------------------------------------------------------------------------------- C ABI
+@pytest.fixture(scope="module")
+def lib():
+    torch.cuda.set_device(0)
+    return capi.load()
+
+
+@pytest.mark.parametrize("dtype, out_type, round_op", [(torch.float32, 0, None), (torch.bfloat16, 2, 34)], ids=str)
+@pytest.mark.parametrize("R, C_, r0, c0, rows, cols", [
+    (64, 64, 3, 5, 7, 9),                    # odd origin and size: scalar path
+    (512, 1024, 128, 256, 128, 512),         # aligned: quads
+    (8192, 8192, 4096, 1024, 4096, 6144),    # 96 MiB fp32 window inside a 256 MiB matrix
+    (300, 1000, 0, 0, 300, 1000),            # the whole matrix (ld == cols: flat)
+], ids=str)
+def test_window_program_bit_exact_and_confined(lib, dtype, out_type, round_op, R, C_, r0, c0, rows, cols):
+    gen = torch.Generator(device="cuda").manual_seed(R + c0)
+    x = (torch.rand(R, C_, device="cuda", generator=gen) * 4 - 2).to(dtype)
+    y = (torch.rand(R, C_, device="cuda", generator=gen) * 4 - 2).to(dtype)
+    out = torch.full((R, C_), 3.0, device="cuda", dtype=dtype)
+    ops = [0, 0, 4] + ([round_op] if round_op else []) + [2 | 0x100] + ([round_op] if round_op else [])
+    args = [0, 1, 0] + ([0] if round_op else []) + [int(torch.tensor(0.25).view(torch.int32))] + ([0] if round_op else [])
+    es = x.element_size()
+    first = (r0 * C_ + c0) * es
+    ops_a, args_a = (ctypes.c_int32 * len(ops))(*ops), (ctypes.c_int32 * len(ops))(*args)
+    ins = (ctypes.c_void_p * 2)(x.data_ptr() + first, y.data_ptr() + first)
+    types = (ctypes.c_int32 * 2)(out_type, out_type)
+    rc = lib.asc_cuda_eltwise_program_2d(ops_a, args_a, len(ops), ins, types, 2, ctypes.c_void_p(out.data_ptr() + first),
+                                         out_type, rows, cols, C_, None)
+    assert rc == 0, capi.status_string(rc)
+    capi.check_device_status(None)
+    want = torch.full((R, C_), 3.0, dtype=dtype)
+    xw, yw = x[r0:r0 + rows, c0:c0 + cols].cpu().reshape(-1), y[r0:r0 + rows, c0:c0 + cols].cpu().reshape(-1)
+    want[r0:r0 + rows, c0:c0 + cols] = E.run_program(ops, args, [xw, yw], out_type).reshape(rows, cols)
+    assert torch.equal(out.cpu(), want)
+
+
+def test_window_program_rejections(lib):
+    x = torch.zeros(16, 16, device="cuda")
+    ops_a, args_a = (ctypes.c_int32 * 1)(0), (ctypes.c_int32 * 1)(0)
+    ins, types = (ctypes.c_void_p * 1)(x.data_ptr()), (ctypes.c_int32 * 1)(0)
+    out = ctypes.c_void_p(x.data_ptr())
+    assert lib.asc_cuda_eltwise_program_2d(ops_a, args_a, 1, ins, types, 1, out, 0, 4, 8, 4, None) == 1   # pitch < cols
+    assert lib.asc_cuda_eltwise_program_2d(ops_a, args_a, 1, ins, types, 1, out, 0, -1, 8, 8, None) == 1
+    assert lib.asc_cuda_eltwise_program_2d(ops_a, args_a, 1, ins, types, 1, out, 0, 1 << 20, 1 << 12, 1 << 13, None) == 6
+    assert lib.asc_cuda_eltwise_program_2d(ops_a, args_a, 1, ins, types, 1, out, 0, 0, 8, 16, None) == 0  # empty
