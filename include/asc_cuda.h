@@ -139,14 +139,16 @@ int32_t asc_cuda_eltwise_program(const int32_t* ops, const int32_t* args, int32_
                                  const int32_t* input_types, int32_t n_inputs, void* out, int32_t out_type,
                                  int64_t n, void* stream);
 
-/* The same over a [rows, cols] window of row-major tensors that all have a row pitch of `ld` elements
- * (every pointer addresses the window's first element): what a 2-D tile that does not span whole rows
- * touches (asc2.load / asc2.store with 2-D offsets, python/asc/language/tile/memory_ops.py; exercised by
- * python/test/asc2/operations/test_memory_ops.py:10-59).  A window with ld != cols is limited to 2^32
- * elements. */
+/* The same over a [rows, cols] window in which every operand has its own row pitch: lds holds the pitch
+ * (in elements) of each input, then of the output; every pointer addresses its operand's first element of
+ * the window.  An input pitch of 0 repeats one row for every row of the window (asc2.broadcast_to of a
+ * [1, cols] tile).  lds == NULL means that all pitches equal cols, i.e. one contiguous range.  This is what
+ * 2-D tiles that do not span whole rows touch (asc2.load / asc2.store with 2-D offsets,
+ * python/asc/language/tile/memory_ops.py; python/test/asc2/operations/test_memory_ops.py:10-59,
+ * test_shape_ops.py:17-18).  A window that is not one contiguous range is limited to 2^32 elements. */
 int32_t asc_cuda_eltwise_program_2d(const int32_t* ops, const int32_t* args, int32_t n_ops,
                                     const void* const* inputs, const int32_t* input_types, int32_t n_inputs,
-                                    void* out, int32_t out_type, int64_t rows, int64_t cols, int64_t ld,
+                                    void* out, int32_t out_type, int64_t rows, int64_t cols, const int64_t* lds,
                                     void* stream);
 
 /* Reduction of a row-major [rows, cols] fp32 window with row pitch `ld` (elements).  kind: 0 sum, 1 max,

@@ -23,12 +23,10 @@ int32_t asc_cuda_softmax_f32_variant(const float* x, float* out, int64_t rows, i
                                      int32_t variant, void* stream);
 
 /* GEMM with a cap on the number of CTAs.  in_dtype: 0 fp16, 1 bf16, 2 int8 (int32 output);
- * out_dtype as asc_cuda_gemm_f16 (ignored for int8); max_ctas 0 = one per SM.  The five uint32
- * arguments were descriptor-field overrides during bring-up and are ignored. */
-int32_t asc_cuda_gemm_debug(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
-                            int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype, uint32_t a_sbo,
-                            uint32_t a_kstep, uint32_t b_lbo, uint32_t b_sbo, uint32_t b_kstep, int32_t max_ctas,
-                            void* stream);
+ * out_dtype as asc_cuda_gemm_f16 (ignored for int8); max_ctas 0 = one per SM. */
+int32_t asc_cuda_gemm_capped(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                             int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype, int32_t max_ctas,
+                             void* stream);
 
 /* GEMM kernel selection: 0 choose per problem (default), 1 always the single-CTA 128 x 256 kernel,
  * 2 the CTA-pair 256 x 256 kernel whenever M > 128.  Process-wide. */

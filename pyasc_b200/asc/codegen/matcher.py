@@ -368,18 +368,44 @@ class _Frag:
         return _Frag([(_OP_CONST, self.word)], 1) if self.word is not None else self
 
 
+class _Operand:
+    """One LOAD source of a program: the tile of ``shape`` loaded from ``tensor`` at ``offsets``.  ``bcast``: the
+    tile is a single row that every row of the result repeats; ``scalar``: one element (a scalar load)."""
+
+    __slots__ = ("tensor", "offsets", "shape", "bcast", "scalar")
+
+    def __init__(self, tensor: Tensor, offsets: Sequence[PlainValue], shape: Tuple[int, ...], bcast: bool = False,
+                 scalar: bool = False):
+        self.tensor, self.offsets, self.shape, self.bcast, self.scalar = tensor, tuple(offsets), tuple(shape), bcast, scalar
+
+    def same(self, o: "_Operand") -> bool:
+        return (self.tensor.base.index == o.tensor.base.index and self.tensor.dtype == o.tensor.dtype
+                and self.tensor.static_shape() == o.tensor.static_shape() and self.shape == o.shape
+                and self.bcast == o.bcast and self.scalar == o.scalar and _same_offsets(self.offsets, o.offsets))
+
+    def addressed_like(self, out_t: Tensor, offsets: Sequence[PlainValue], shape: Tuple[int, ...]) -> bool:
+        """Same tile of a same-shaped tensor as the store: element i of the operand is element i of the result."""
+        return (not self.bcast and self.tensor.static_shape() == out_t.static_shape() and self.shape == tuple(shape)
+                and _same_offsets(self.offsets, offsets))
+
+
 class _EltProgram:
     """Compiles the expression tree of a stored tile into a postfix program.  Scalar operands become
     immediates; of two tile operands the one needing the deeper stack is evaluated first (with the
     swapped opcode when that reverses the order), which keeps most expressions at depth 2."""
 
     def __init__(self, shape, offsets, out_t: Tensor, scalar_store: bool = False):
-        self.shape, self.offsets, self.out_t = shape, offsets, out_t
+        self.shape, self.offsets, self.out_t = tuple(shape), offsets, out_t
         self.scalar_store = scalar_store
-        self.inputs: List[Tensor] = []
+        self.operands: List[_Operand] = []
+        self.reshaped = False       # a reshape was seen: element order is the flat (row-major) order
         self.ops: List[int] = []
         self.args: List[int] = []
         self.max_depth = 0
+
+    @property
+    def inputs(self) -> List[Tensor]:
+        return [o.tensor for o in self.operands]
 
     @staticmethod
     def _word(value: Any, dtype: DataType) -> int:
@@ -407,12 +433,20 @@ class _EltProgram:
             return _Frag(rhs.code + lhs.code + [(_SWAPPED[code], 0)], max(rhs.need, lhs.need + 1))
         return _Frag(lhs.code + rhs.code + [(code, 0)], max(lhs.need, rhs.need + 1))
 
-    def _load(self, tensor: Tensor) -> Optional[_Frag]:
-        for k, t in enumerate(self.inputs):
-            if t.base.index == tensor.base.index:
-                return _Frag([(_OP_LOAD, k)], 1) if t.dtype == tensor.dtype else None
-        self.inputs.append(tensor)
-        return _Frag([(_OP_LOAD, len(self.inputs) - 1)], 1)
+    def _load(self, operand: _Operand) -> Optional[_Frag]:
+        if operand.tensor.dtype.name not in _ELT_TYPE:
+            return None
+        for k, o in enumerate(self.operands):
+            if o.same(operand):
+                return _Frag([(_OP_LOAD, k)], 1)
+        self.operands.append(operand)
+        return _Frag([(_OP_LOAD, len(self.operands) - 1)], 1)
+
+    def _view_operand(self, tile: Tile, bcast: bool = False) -> Optional[_Frag]:
+        view = resolve_view(tile) if tile.node.kind in ("load", "copy") else None
+        if view is None or not _is_zero_pad(view):
+            return None
+        return self._load(_Operand(view.tensor, view.offsets, view.shape, bcast))
 
     def gen(self, v: Any, scalar_dtype: Optional[DataType] = None) -> Optional[_Frag]:
         """Code for ``v``, or None when ``v`` is not expressible."""
@@ -426,11 +460,7 @@ class _EltProgram:
                 node = v.args[0]
                 if node.kind != "load_scalar":
                     return None
-                tensor = node.args[0]
-                if tensor.static_shape() != self.out_t.static_shape() or tensor.dtype.name not in _ELT_TYPE \
-                        or not _same_offsets(node.attrs["offsets"], self.offsets):
-                    return None
-                return self._load(tensor)
+                return self._load(_Operand(node.args[0], node.attrs["offsets"], (1, ), scalar=True))
             code = (_BINARY_CODE if v.dtype.is_float() else _INT_BINARY_CODE).get(v.op)
             if code is None or v.dtype.name not in _ELT_TYPE or len(v.args) != 2:
                 return None
@@ -440,18 +470,33 @@ class _EltProgram:
             return self._rounded(self._binary(code, lhs, rhs), v.dtype)
         if isinstance(v, (bool, int, float)):
             return _Frag([], 0, self._word(v, scalar_dtype or (KT.float32 if isinstance(v, float) else KT.int32)))
-        if not isinstance(v, Tile) or v.shape != self.shape:
+        if not isinstance(v, Tile):
             return None
         node = v.node
-        if node.kind == "load":
-            view = resolve_view(v)
-            if view is None or not _same_offsets(view.offsets, self.offsets) or not _is_zero_pad(view):
-                return None
-            if view.tensor.static_shape() != self.out_t.static_shape() or view.tensor.dtype.name not in _ELT_TYPE:
-                return None
-            return self._load(view.tensor)
         if node.kind == "full":
             return self.gen(node.attrs["value"], v.dtype)
+        if v.shape != self.shape:
+            return None
+        if node.kind in ("load", "copy"):
+            return self._view_operand(v)
+        if node.kind == "reshape":
+            # row-major element order is kept, so elementwise code commutes with the reshape
+            src = node.args[0]
+            outer, self.shape = self.shape, src.shape
+            try:
+                frag = self.gen(src, scalar_dtype)
+            finally:
+                self.shape = outer
+            self.reshaped = True
+            return frag
+        if node.kind == "broadcast":
+            src = node.args[0]
+            if _node(src, "full") is not None:
+                return self.gen(src.node.attrs["value"], v.dtype)
+            # a single row repeated along the leading dimension
+            if len(self.shape) == 2 and src.size == self.shape[1] and src.shape[-1] == self.shape[1]:
+                return self._view_operand(src, bcast=True)
+            return None
         if v.dtype.name not in _ELT_TYPE and node.kind != "compare":
             return None
         if node.kind == "binary":
@@ -519,6 +564,145 @@ def _tile_windows(tshape: Tuple[int, ...], offsets: Sequence[PlainValue], shape:
     return windows, grid is not None and set(origins) == grid
 
 
+def _flat_scalar_offset(tshape: Tuple[int, ...], offsets: Sequence[PlainValue]) -> PlainValue:
+    if len(offsets) != len(tshape):
+        raise RuntimeError("number of 'offsets' must match the rank of the tensor")
+    flat, stride = PlainValue.const(0), 1
+    for d in range(len(tshape) - 1, -1, -1):
+        flat = flat + offsets[d] * stride
+        stride *= tshape[d]
+    return flat
+
+
+class _Geometry:
+    """Where a tile lies in its tensor for every instance: the flat index of its first element and either one
+    contiguous range of ``numel`` elements (``pitch`` None) or ``rows`` x ``cols`` with a row pitch."""
+
+    def __init__(self, tensor: Tensor, offsets: Sequence[PlainValue], shape: Tuple[int, ...], scalar: bool,
+                 env: Dict[str, np.ndarray], n: int):
+        tshape = tensor.static_shape()
+        numel = 1
+        for d in tshape:
+            numel *= d
+        self.pitch: Optional[int] = None
+        self.rows, self.cols = 1, 1
+        if scalar:
+            self.start = eval_int(_flat_scalar_offset(tshape, offsets), env, n)
+            self.numel, ends = 1, None
+        else:
+            window = _flat_window(tensor, offsets, shape)
+            if window is not None:
+                self.start = eval_int(window[0], env, n)
+                self.numel = window[1]
+            elif len(tshape) == 2 and len(shape) == 2:
+                r0, c0 = eval_int(offsets[0], env, n), eval_int(offsets[1], env, n)
+                if n and (r0.min() < 0 or c0.min() < 0):
+                    raise RuntimeError("Negative tile offset in kernel")
+                if n and ((r0 + shape[0]).max() > tshape[0] or (c0 + shape[1]).max() > tshape[1]):
+                    raise _unsupported("tile that reaches past the end of its tensor in a kernel whose operands are "
+                                       "addressed differently from its result")
+                self.start = r0 * tshape[1] + c0
+                self.rows, self.cols, self.pitch = shape[0], shape[1], tshape[1]
+                self.numel = shape[0] * shape[1]
+            else:
+                raise _unsupported("tile that is neither a contiguous range nor a 2-D window of a matrix")
+        if n and self.start.min() < 0:
+            raise RuntimeError("Negative tile offset in kernel")
+        if self.pitch is None and n and (self.start + self.numel).max() > numel:
+            raise _unsupported("tile that reaches past the end of its tensor in a kernel whose operands are addressed "
+                               "differently from its result")
+
+
+def _program_arrays(prog: "_EltProgram", out_t: Tensor):
+    n_ops, n_in = len(prog.ops), len(prog.operands)
+    return (n_ops, n_in, (ctypes.c_int32 * n_ops)(*prog.ops), (ctypes.c_int32 * n_ops)(*prog.args),
+            (ctypes.c_int32 * max(1, n_in))(*[_ELT_TYPE[t.dtype.name] for t in prog.inputs]), _ELT_TYPE[out_t.dtype.name])
+
+
+def _check_program_limits(prog: "_EltProgram") -> None:
+    if len(prog.ops) > ELT_MAX_OPS or len(prog.operands) > ELT_MAX_INPUTS or prog.max_depth > ELT_MAX_STACK:
+        raise _unsupported(f"elementwise expression with {len(prog.ops)} operations, {len(prog.operands)} inputs and a "
+                           f"stack of {prog.max_depth} (limits: {ELT_MAX_OPS}, {ELT_MAX_INPUTS}, {ELT_MAX_STACK})")
+
+
+def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", out_t: Tensor,
+                          offsets: Sequence[PlainValue], out_shape: Tuple[int, ...], scalar_store: bool,
+                          in_place_operand: Optional[int], dedupe: bool) -> Plan:
+    """Operands addressed differently from the result (other tensor shapes or offsets, reshapes, a broadcast row,
+    an accumulation into a fixed window): one call per (block, iteration) instance, in program order."""
+    env = enumerate_instances(trace.core_num, eff.loops)
+    n = env_count(env)
+    if n > MAX_CALLS:
+        raise _unsupported("elementwise kernel with differently addressed operands and more than 4096 tiles")
+    out_g = _Geometry(out_t, offsets, out_shape, scalar_store, env, n)
+    geoms = [_Geometry(o.tensor, o.offsets, o.shape, o.scalar, env, n) for o in prog.operands]
+    # the window every call walks: rows x cols
+    rows, cols = (out_g.rows, out_g.cols) if out_g.pitch is not None else (1, out_g.numel)
+    for o, g in zip(prog.operands, geoms):
+        if o.bcast and out_g.pitch is None:
+            if out_g.numel % g.numel:
+                raise _unsupported("broadcast of a row whose length does not divide the stored tile")
+            rows, cols = out_g.numel // g.numel, g.numel
+    if prog.reshaped and (out_g.pitch is not None or any(g.pitch is not None for g in geoms)):
+        raise _unsupported("reshape of a tile that is not a contiguous range of its tensor")
+    lds: List[int] = []
+    for o, g in zip(prog.operands, geoms):
+        if o.bcast:
+            if g.numel != cols:
+                raise _unsupported("broadcast of a tile that is not one row of the result")
+            lds.append(0)
+        elif g.pitch is not None:
+            if (g.rows, g.cols) != (rows, cols):
+                raise _unsupported("operand window of a different shape than the stored tile")
+            lds.append(g.pitch)
+        else:
+            if g.numel != rows * cols:
+                raise _unsupported("operand tile with a different number of elements than the stored tile")
+            lds.append(cols)
+    lds.append(out_g.pitch if out_g.pitch is not None else cols)
+    out_idx = out_t.base.index
+    in_idx = [o.tensor.base.index for o in prog.operands]
+    in_size = [o.tensor.dtype.bitwidth // 8 for o in prog.operands]
+    out_size = out_t.dtype.bitwidth // 8
+    for k, (i, g) in enumerate(zip(in_idx, geoms)):
+        if i == out_idx and not (k == in_place_operand and lds[k] == lds[-1] and np.array_equal(g.start, out_g.start)):
+            raise _unsupported("elementwise kernel that stores into a tensor it also loads at other positions")
+    plan = Plan("elementwise:program")
+    plan.reads.update(in_idx)
+    plan.writes.add(out_idx)
+    plan.partial_writes.add(out_idx)
+    n_ops, n_in, ops_arr, args_arr, types_arr, out_type = _program_arrays(prog, out_t)
+    lds_arr = (ctypes.c_int64 * len(lds))(*lds)
+    calls: List[Tuple[Tuple[int, ...], int]] = []      # (first element of every operand and of the result, rows)
+    all_starts = [tuple(int(g.start[j]) for g in geoms) + (int(out_g.start[j]), ) for j in range(n)]
+    if dedupe:
+        # stores are idempotent and independent: drop repeats, and let windows that continue each other row
+        # after row (every operand advancing by its own pitch, a broadcast row staying put) become one call
+        for starts in sorted(set(all_starts), key=lambda st: st[-1]):
+            if calls and cols > 0:
+                prev, prev_rows = calls[-1]
+                if all(st == p0 + prev_rows * ld for st, p0, ld in zip(starts, prev, lds)):
+                    calls[-1] = (prev, prev_rows + rows)
+                    continue
+            calls.append((starts, rows))
+    else:
+        calls = [(starts, rows) for starts in all_starts]
+    for starts, call_rows in calls:
+        def build(ptrs, stream, starts=starts, call_rows=call_rows):
+            ins = (ctypes.c_void_p * max(1, n_in))(*[ptrs[i] + sz * st for i, sz, st in zip(in_idx, in_size, starts)])
+            return (ops_arr, args_arr, ctypes.c_int32(n_ops), ins, types_arr, ctypes.c_int32(n_in),
+                    _p(ptrs[out_idx] + out_size * starts[-1]), ctypes.c_int32(out_type), ctypes.c_int64(call_rows),
+                    ctypes.c_int64(cols), lds_arr, stream)
+        plan.steps.append(Step("asc_cuda_eltwise_program_2d", build,
+                               f"{n_ops} ops over [{call_rows}, {cols}] pitches {lds} from {list(starts[:-1])} to {starts[-1]}"))
+    covered = sum(r for _, r in calls) * cols
+    if dedupe and len(calls) == 1 and lds[-1] == cols and calls[0][0][-1] == 0 and covered == out_t.base.numel:
+        plan.partial_writes.discard(out_idx)
+    if not plan.steps:
+        raise _unsupported("elementwise kernel without any tile")
+    return plan
+
+
 def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     value, out_t = eff.args
     offsets = eff.attrs["offsets"]
@@ -526,15 +710,21 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     if not isinstance(value, (Tile, PlainValue)) or out_t.dtype.name not in _ELT_TYPE or value.dtype != out_t.dtype:
         return None
     tshape = out_t.static_shape()
-    prog = _EltProgram((1, ) if scalar_store else value.shape, offsets, out_t, scalar_store)
-    if not prog.compile(value) or not prog.inputs:
+    out_shape = (1, ) if scalar_store else value.shape
+    prog = _EltProgram(out_shape, offsets, out_t, scalar_store)
+    if not prog.compile(value):
         return None
-    if len(prog.ops) > ELT_MAX_OPS or len(prog.inputs) > ELT_MAX_INPUTS or prog.max_depth > ELT_MAX_STACK:
-        raise _unsupported(f"elementwise expression with {len(prog.ops)} operations, {len(prog.inputs)} inputs and a "
-                           f"stack of {prog.max_depth} (limits: {ELT_MAX_OPS}, {ELT_MAX_INPUTS}, {ELT_MAX_STACK})")
+    _check_program_limits(prog)
     _check_fits(out_t)
     for t in prog.inputs:
         _check_fits(t)
+    if scalar_store:
+        aligned = all(o.scalar and o.tensor.static_shape() == tshape and _same_offsets(o.offsets, offsets)
+                      for o in prog.operands)
+    else:
+        aligned = not prog.reshaped and all(o.addressed_like(out_t, offsets, out_shape) for o in prog.operands)
+    if not aligned or not prog.operands:
+        return _plan_general_program(trace, eff, prog, out_t, offsets, out_shape, scalar_store, None, dedupe=True)
     numel = 1
     for d in tshape:
         numel *= d
@@ -542,14 +732,7 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     n = env_count(env)
     windows: List[Tuple[int, int, int, int]] = []     # 2-D mode: (row0, col0, rows, cols)
     if scalar_store:
-        if len(offsets) != len(tshape):
-            raise RuntimeError("number of 'offsets' must match the rank of the tensor")
-        flat_off = PlainValue.const(0)
-        stride = 1
-        for d in range(len(tshape) - 1, -1, -1):
-            flat_off = flat_off + offsets[d] * stride
-            stride *= tshape[d]
-        window = (flat_off, 1)
+        window = (_flat_scalar_offset(tshape, offsets), 1)
     else:
         window = _flat_window(out_t, offsets, value.shape)
     if window is not None:
@@ -579,11 +762,7 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     plan.writes.add(out_idx)
     if intervals != [(0, out_t.base.numel)]:
         plan.partial_writes.add(out_idx)
-    n_ops, n_in = len(prog.ops), len(prog.inputs)
-    ops_arr = (ctypes.c_int32 * n_ops)(*prog.ops)
-    args_arr = (ctypes.c_int32 * n_ops)(*prog.args)
-    types_arr = (ctypes.c_int32 * n_in)(*[_ELT_TYPE[t.dtype.name] for t in prog.inputs])
-    out_type = _ELT_TYPE[out_t.dtype.name]
+    n_ops, n_in, ops_arr, args_arr, types_arr, out_type = _program_arrays(prog, out_t)
 
     def make(lo: int, hi: int) -> List[Step]:
         def build(ptrs, stream, lo=lo, hi=hi):
@@ -593,6 +772,8 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
                     _p(ptrs[out_idx] + out_size * lo), ctypes.c_int32(out_type), ctypes.c_int64(hi - lo), stream)
         return [Step("asc_cuda_eltwise_program", build, f"{n_ops} ops over [{lo}, {hi})")]
 
+    lds_arr = (ctypes.c_int64 * (n_in + 1))(*([tshape[-1]] * (n_in + 1)))
+
     def make_2d(r0: int, c0: int, rows: int, cols: int) -> Step:
         first = r0 * tshape[1] + c0
 
@@ -600,7 +781,7 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
             ins = (ctypes.c_void_p * n_in)(*[ptrs[i] + sz * first for i, sz in zip(in_idx, in_size)])
             return (ops_arr, args_arr, ctypes.c_int32(n_ops), ins, types_arr, ctypes.c_int32(n_in),
                     _p(ptrs[out_idx] + out_size * first), ctypes.c_int32(out_type), ctypes.c_int64(rows),
-                    ctypes.c_int64(cols), ctypes.c_int64(tshape[1]), stream)
+                    ctypes.c_int64(cols), lds_arr, stream)
         return Step("asc_cuda_eltwise_program_2d", build, f"{n_ops} ops over [{rows}, {cols}] at ({r0}, {c0})")
 
     for lo, hi in intervals:
@@ -613,6 +794,36 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         streamed = {i: sz for i, sz in zip(in_idx, in_size)}
         streamed[out_idx] = out_size
         plan.pipeline = PipelineSpec(intervals[0][1], 1 << 16, streamed, set(), make)
+    return plan
+
+
+# --------------------------------------------------------------------------------------------------
+# Pattern: atomic accumulation of a tile into a window of a tensor (add / max / min)
+# --------------------------------------------------------------------------------------------------
+def _match_atomic(trace: KernelTrace, eff: Effect) -> Plan:
+    """``asc2.atomic_add/max/min(tile, tensor, offsets)``: tensor[window] = op(tensor[window], tile).  The blocks'
+    accumulations are applied one after the other on the launch stream, in block order, so the result is the
+    one any serial order of the reference's atomics gives (exactly for max / min and integers, within fp
+    rounding for floating-point sums)."""
+    value, out_t = eff.args
+    offsets = eff.attrs["offsets"]
+    if not isinstance(value, Tile) or out_t.dtype.name not in _ELT_TYPE or value.dtype != out_t.dtype:
+        raise _unsupported(f"atomic_{eff.attrs['kind']} of a {getattr(value, 'dtype', type(value).__name__)} tile into a "
+                           f"{out_t.dtype} tensor")
+    prog = _EltProgram(value.shape, offsets, out_t)
+    current = prog._load(_Operand(out_t, offsets, value.shape))
+    update = prog.gen(value)
+    if current is None or update is None:
+        raise _unsupported("atomic operation on a tile that is not an elementwise expression of loaded tiles")
+    table = _BINARY_CODE if out_t.dtype.is_float() else _INT_BINARY_CODE
+    frag = prog._rounded(prog._binary(table[eff.attrs["kind"]], current, update), out_t.dtype).pushed()
+    prog.ops, prog.args, prog.max_depth = [c[0] for c in frag.code], [c[1] for c in frag.code], frag.need
+    _check_program_limits(prog)
+    _check_fits(out_t)
+    for t in prog.inputs:
+        _check_fits(t)
+    plan = _plan_general_program(trace, eff, prog, out_t, offsets, value.shape, False, 0, dedupe=False)
+    plan.pattern = f"atomic:{eff.attrs['kind']}"
     return plan
 
 
@@ -1243,8 +1454,8 @@ def build_plan(trace: KernelTrace) -> Plan:
     def is_store(e: Effect) -> bool:
         # scalars and one-element tiles go through the scalar form of asc2.store: a store of one element
         return e.kind in ("store", "store_scalar")
-    stores = [e for e in trace.effects if is_store(e)]
-    others = [e for e in trace.effects if not is_store(e) and e.kind != "matmul_acc"]
+    stores = [e for e in trace.effects if is_store(e) or e.kind == "atomic"]
+    others = [e for e in trace.effects if not is_store(e) and e.kind not in ("matmul_acc", "atomic")]
     if others:
         raise _unsupported(f"'{others[0].kind}' side effect")
     if not stores:
@@ -1252,11 +1463,12 @@ def build_plan(trace: KernelTrace) -> Plan:
     total = Plan("")
     names = []
     for eff in stores:
-        if _is_identity_store(eff):
+        if eff.kind != "atomic" and _is_identity_store(eff):
             continue        # a tile stored back to where it was loaded from changes nothing
         plan = None
         scalar_value = not isinstance(eff.args[0], Tile)
-        for matcher in ((_match_eltwise_program, ) if scalar_value else _MATCHERS):
+        for matcher in ((_match_atomic, ) if eff.kind == "atomic" else (_match_eltwise_program, ) if scalar_value
+                        else _MATCHERS):
             plan = matcher(trace, eff)
             if plan is not None:
                 break

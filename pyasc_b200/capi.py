@@ -51,7 +51,7 @@ PROTOTYPES: Dict[str, Sequence] = {
     "asc_cuda_vadd_f32": (P, P, P, c_int64, P),
     "asc_cuda_vmuladd_f32": (P, P, P, P, c_int64, P),
     "asc_cuda_eltwise_program": (P, P, c_int32, P, P, c_int32, P, c_int32, c_int64, P),
-    "asc_cuda_eltwise_program_2d": (P, P, c_int32, P, P, c_int32, P, c_int32, c_int64, c_int64, c_int64, P),
+    "asc_cuda_eltwise_program_2d": (P, P, c_int32, P, P, c_int32, P, c_int32, c_int64, c_int64, P, P),
     "asc_cuda_reduce_f32": (P, P, c_int64, c_int64, c_int64, c_int32, c_int32, c_int64, P),
     "asc_cuda_softmax_f32": (P, P, c_int64, c_int64, c_int64, P),
     "asc_cuda_gemm_f16": (P, P, P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32,
@@ -65,8 +65,7 @@ PROTOTYPES: Dict[str, Sequence] = {
 TUNING_PROTOTYPES: Dict[str, Sequence] = {
     "asc_cuda_vadd_f32_variant": (P, P, P, c_int64, c_int32, P),
     "asc_cuda_softmax_f32_variant": (P, P, c_int64, c_int64, c_int64, c_int32, P),
-    "asc_cuda_gemm_debug": (P, P, P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32,
-                            c_uint32, c_uint32, c_uint32, c_uint32, c_uint32, c_int32, P),
+    "asc_cuda_gemm_capped": (P, P, P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32, c_int32, P),
     "asc_cuda_gemm_set_mode": (c_int32, ),
     "asc_cuda_eltwise_set_lanes": (c_int32, ),
 }

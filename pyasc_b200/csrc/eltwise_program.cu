@@ -63,16 +63,18 @@ struct EltProgram {
   int32_t in_type[kMaxInputs];
   void* out;
   int32_t out_type;
-  // 2-D window: element i of the window is row i / cols, column i % cols of tensors with a row pitch of ld
-  // elements.  cols == 0: the operands are flat arrays (element i is at index i).
-  uint32_t cols, ld;
+  // 2-D window: element i of the window is row i / cols, column i % cols; operand k (the inputs, then the
+  // output) has a row pitch of ld[k] elements, 0 meaning that every row of the window reads the same row
+  // (a broadcast).  cols == 0: the operands are flat arrays (element i is at index i).
+  uint32_t cols;
+  uint32_t ld[kMaxInputs + 1];
 };
 
-__device__ __forceinline__ int64_t element_offset(const EltProgram& prog, int64_t i) {
+__device__ __forceinline__ int64_t element_offset(const EltProgram& prog, int operand, int64_t i) {
   if (prog.cols == 0) return i;
   const uint32_t u = static_cast<uint32_t>(i);
   const uint32_t r = u / prog.cols;
-  return static_cast<int64_t>(r) * prog.ld + (u - r * prog.cols);
+  return static_cast<int64_t>(r) * prog.ld[operand] + (u - r * prog.cols);
 }
 
 constexpr int kThreads = 256;
@@ -175,15 +177,17 @@ __device__ __forceinline__ void store_oct(void* p, int type, int64_t i, const fl
 // A thread's kV lanes: kV == 1 is the element at i; otherwise kV / 4 quads, the first at i and the
 // others kQuadStride elements apart (so that a warp's accesses stay contiguous inside a CTA tile).
 template <int kV, bool kLoadedOnce = false>
-__device__ __forceinline__ void load_group(const EltProgram& prog, const void* p, int typeword, int64_t i,
-                                           float (&v)[kV]) {
+__device__ __forceinline__ void load_group(const EltProgram& prog, int input, int64_t i, float (&v)[kV]) {
+  const void* p = prog.in[input];
+  const int typeword = prog.in_type[input];
   const int type = typeword & 0xff;
   if constexpr (kV >= 4) {
     const bool reused = !kLoadedOnce && (typeword & kReusedInput) != 0;
 #pragma unroll
-    for (int q = 0; q < kV / 4; ++q) load_quad(p, type, reused, element_offset(prog, i + q * kQuadStride), &v[4 * q]);
+    for (int q = 0; q < kV / 4; ++q)
+      load_quad(p, type, reused, element_offset(prog, input, i + q * kQuadStride), &v[4 * q]);
   } else {
-    i = element_offset(prog, i);
+    i = element_offset(prog, input, i);
     switch (type) {
       case T_F16: v[0] = __half2float(reinterpret_cast<const __half*>(p)[i]); break;
       case T_BF16: v[0] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]); break;
@@ -195,12 +199,14 @@ __device__ __forceinline__ void load_group(const EltProgram& prog, const void* p
 }
 
 template <int kV>
-__device__ __forceinline__ void store_group(const EltProgram& prog, void* p, int type, int64_t i, const float (&v)[kV]) {
+__device__ __forceinline__ void store_group(const EltProgram& prog, int64_t i, const float (&v)[kV]) {
+  void* p = prog.out;
+  const int type = prog.out_type;
   if constexpr (kV >= 4) {
 #pragma unroll
-    for (int q = 0; q < kV / 4; ++q) store_quad(p, type, element_offset(prog, i + q * kQuadStride), &v[4 * q]);
+    for (int q = 0; q < kV / 4; ++q) store_quad(p, type, element_offset(prog, prog.n_inputs, i + q * kQuadStride), &v[4 * q]);
   } else {
-    i = element_offset(prog, i);
+    i = element_offset(prog, prog.n_inputs, i);
     switch (type) {
       case T_F16: reinterpret_cast<__half*>(p)[i] = __float2half_rn(v[0]); break;
       case T_BF16: reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v[0]); break;
@@ -346,7 +352,7 @@ struct Interpreter {
         case OP_LOAD:
           if (depth > 0) slots.put(depth - 1, top);
           ++depth;
-          load_group<kV>(prog, prog.in[prog.arg[k]], prog.in_type[prog.arg[k]], i, top);
+          load_group<kV>(prog, prog.arg[k], i, top);
           break;
         case OP_CONST:
           if (depth > 0) slots.put(depth - 1, top);
@@ -376,7 +382,7 @@ struct Interpreter {
 #undef ASC_UN
 #undef ASC_BIN
 #undef ASC_LANES
-    store_group<kV>(prog, prog.out, prog.out_type, i, top);
+    store_group<kV>(prog, i, top);
   }
 };
 
@@ -409,7 +415,7 @@ struct StaticStep {
                                              float (&st)[kStack][kV]) {
     if constexpr (K == P::n) {
       static_assert(D == 1, "a program leaves exactly one value");
-      if constexpr (kStore) store_group<kV>(prog, prog.out, prog.out_type, i, st[0]);
+      if constexpr (kStore) store_group<kV>(prog, i, st[0]);
     } else {
       constexpr int word = P::at(K);
       constexpr int op = word & 0xff;
@@ -464,7 +470,7 @@ struct Compiled {
       for (int o = 0; o < kV / 8; ++o) store_oct(prog.out, prog.out_type, i + o * (kThreads * 8), &st[0][8 * o]);
     } else {
 #pragma unroll
-      for (int j = 0; j < P::inputs(); ++j) load_group<kV, true>(prog, prog.in[j], prog.in_type[j], i, in[j]);
+      for (int j = 0; j < P::inputs(); ++j) load_group<kV, true>(prog, j, i, in[j]);
       StaticStep<P, kV, 0, 0, true>::run(prog, i, in, st);
     }
   }
@@ -571,11 +577,20 @@ int32_t try_compiled(const EltProgram& prog, const int32_t* ops, const int32_t* 
 
 extern "C" int32_t asc_cuda_eltwise_program_2d(const int32_t* ops, const int32_t* args, int32_t n_ops,
                                                const void* const* inputs, const int32_t* input_types, int32_t n_inputs,
-                                               void* out, int32_t out_type, int64_t rows, int64_t cols, int64_t ld,
-                                               void* stream) {
-  if (rows < 0 || cols < 0 || ld < cols) return ASC_ERR_INVALID_ARG;
-  const bool strided = rows > 1 && ld != cols;
-  if (strided && (rows * cols >= (int64_t{1} << 32) || ld >= (int64_t{1} << 32))) return ASC_ERR_TOO_LARGE;
+                                               void* out, int32_t out_type, int64_t rows, int64_t cols,
+                                               const int64_t* lds, void* stream) {
+  if (rows < 0 || cols < 0 || n_inputs < 0 || n_inputs > kMaxInputs) return ASC_ERR_INVALID_ARG;
+  // lds: row pitch of every input, then of the output; NULL: all pitches equal cols (one contiguous range)
+  bool strided = false;
+  if (lds != nullptr && rows > 1) {
+    for (int k = 0; k <= n_inputs; ++k) {
+      const bool broadcast = lds[k] == 0 && k < n_inputs;
+      if (!broadcast && lds[k] < cols) return ASC_ERR_INVALID_ARG;
+      if (lds[k] >= (int64_t{1} << 32)) return ASC_ERR_TOO_LARGE;
+      strided = strided || lds[k] != cols;
+    }
+  }
+  if (strided && rows * cols >= (int64_t{1} << 32)) return ASC_ERR_TOO_LARGE;
   const int64_t n = rows * cols;
   if (n < 0 || n_ops <= 0 || n_ops > kMaxOps || n_inputs < 0 || n_inputs > kMaxInputs) return ASC_ERR_INVALID_ARG;
   if (ops == nullptr || args == nullptr || out == nullptr || (n_inputs > 0 && (inputs == nullptr || input_types == nullptr)))
@@ -624,13 +639,16 @@ extern "C" int32_t asc_cuda_eltwise_program_2d(const int32_t* ops, const int32_t
   prog.out = out;
   prog.out_type = out_type;
   prog.cols = strided ? static_cast<uint32_t>(cols) : 0u;
-  prog.ld = strided ? static_cast<uint32_t>(ld) : 0u;
+  for (int k = 0; k <= n_inputs; ++k) prog.ld[k] = strided ? static_cast<uint32_t>(lds[k]) : 0u;
   int sms = 0;
   int32_t rc = aschost::sm_count(&sms);
   if (rc != ASC_OK) return rc;
   bool vec = reinterpret_cast<uintptr_t>(out) % (4 * elem_size(out_type)) == 0;
   for (int i = 0; i < n_inputs; ++i) vec = vec && reinterpret_cast<uintptr_t>(inputs[i]) % (4 * elem_size(input_types[i])) == 0;
-  if (strided) vec = vec && cols % 4 == 0 && ld % 4 == 0;   // a quad must not straddle two rows
+  if (strided) {
+    vec = vec && cols % 4 == 0;   // a quad must not straddle two rows
+    for (int k = 0; k <= n_inputs; ++k) vec = vec && lds[k] % 4 == 0;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (!vec) return launch_interpreter<1>(prog, n, max_depth, sms, st);
   if (g_use_compiled && !strided) {
@@ -650,7 +668,8 @@ extern "C" int32_t asc_cuda_eltwise_program_2d(const int32_t* ops, const int32_t
 extern "C" int32_t asc_cuda_eltwise_program(const int32_t* ops, const int32_t* args, int32_t n_ops,
                                             const void* const* inputs, const int32_t* input_types, int32_t n_inputs,
                                             void* out, int32_t out_type, int64_t n, void* stream) {
-  return asc_cuda_eltwise_program_2d(ops, args, n_ops, inputs, input_types, n_inputs, out, out_type, 1, n, n, stream);
+  return asc_cuda_eltwise_program_2d(ops, args, n_ops, inputs, input_types, n_inputs, out, out_type, 1, n, nullptr,
+                                     stream);
 }
 
 // tuning hook: bits 0-7 elements per thread and dispatch in the interpreter's aligned path (4, 8 or 16;

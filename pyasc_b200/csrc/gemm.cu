@@ -789,12 +789,11 @@ int32_t asc_cuda_gemm_i8(const int8_t* A, const int8_t* B, int32_t* acc, void* d
                                   static_cast<cudaStream_t>(stream));
 }
 
-// Bring-up hook: same GEMM with descriptor-field overrides and a CTA cap.
+// Tuning hook: the same GEMM with a cap on the number of CTAs (how throughput scales with the SMs used).
 // in_dtype: 0 fp16, 1 bf16, 2 int8 (int32 output); out_dtype as asc_cuda_gemm_f16 (ignored for int8).
-int32_t asc_cuda_gemm_debug(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
-                            int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype, uint32_t a_sbo,
-                            uint32_t a_kstep, uint32_t b_lbo, uint32_t b_sbo, uint32_t b_kstep, int32_t max_ctas,
-                            void* stream) {
+int32_t asc_cuda_gemm_capped(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                             int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype, int32_t max_ctas,
+                             void* stream) {
   if (C == nullptr) return ASC_ERR_INVALID_ARG;
   int32_t rc = check_gemm_args(A, B, M, N, K, lda, ldb, ldc, in_dtype == 2 ? 1 : 2);
   if (rc != ASC_OK) return rc;
@@ -804,11 +803,6 @@ int32_t asc_cuda_gemm_debug(const void* A, const void* B, void* C, int64_t M, in
   p.N = N;
   p.K = K;
   p.ldc = ldc;
-  (void)a_sbo;
-  (void)a_kstep;
-  (void)b_lbo;
-  (void)b_sbo;
-  (void)b_kstep;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (in_dtype == 2) {
     p.vec_ok = aschost::aligned16(C) && (ldc * 4) % 16 == 0;

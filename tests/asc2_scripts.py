@@ -323,3 +323,40 @@ def scale_2d_tiles(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: i
     for t in range(asc2.block_idx(), num_tiles, asc2.block_num()):
         tile = asc2.load(x_gm, [tile_r, tile_c], tile_id=[t // tiles_c, t % tiles_c])
         asc2.store(asc2.tanh(tile * alpha), out_gm, tile_id=[t // tiles_c, t % tiles_c])
+
+
+# ---- shape operations and atomics (python/test/asc2/operations/test_{shape_ops,atomic_ops}.py)
+@asc2.jit(always_compile=True)
+def shape_op(x_ptr, z_ptr, input_shape: asc.ConstExpr, output_shape: asc.ConstExpr, in_offsets: asc.ConstExpr,
+             out_offsets: asc.ConstExpr, op: asc.ConstExpr, op_param: asc.ConstExpr) -> None:
+    xt = asc2.load(asc2.tensor(x_ptr, input_shape), input_shape, offsets=in_offsets)
+    zt = op(xt, *op_param)
+    asc2.store(zt, asc2.tensor(z_ptr, output_shape), offsets=out_offsets)
+
+
+@asc2.jit(always_compile=True)
+def broadcast_dup(out_ptr, shape: asc.ConstExpr, offsets: asc.ConstExpr):
+    out_tensor = asc2.tensor(out_ptr, shape)
+    out = asc2.full([1], 777, out_tensor.dtype).broadcast_to(*out_tensor.shape)
+    asc2.store(out, out_tensor, offsets=offsets)
+
+
+@asc2.jit(always_compile=True)
+def atomic_op(x_ptr: asc.GlobalAddress, z_ptr: asc.GlobalAddress, tensor_shape: asc.ConstExpr, tile_length: asc.ConstExpr,
+              op: asc.ConstExpr):
+    offset_x = asc.get_block_idx() * tile_length
+    xt = asc2.load(asc2.tensor(x_ptr, tensor_shape), [tile_length], offsets=[offset_x])
+    xt += asc2.full_like(xt, 10)
+    op(xt, asc2.tensor(z_ptr, [tile_length]), offsets=[0])
+
+
+@asc2.jit(always_compile=True)
+def add_row_bias(x_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: int,
+                 cols: asc.ConstExpr[int], rows_per_tile: asc.ConstExpr[int]):
+    """out = relu(x + bias) with one bias row broadcast over the rows of every tile."""
+    x_gm = asc2.tensor(x_ptr, [rows, cols])
+    out_gm = asc2.tensor(out_ptr, [rows, cols])
+    bias = asc2.load(asc2.tensor(b_ptr, [1, cols]), [1, cols], offsets=[0, 0])
+    for i in range(asc2.block_idx() * rows_per_tile, rows, asc2.block_num() * rows_per_tile):
+        x = asc2.load(x_gm, [rows_per_tile, cols], offsets=[i, 0])
+        asc2.store(asc2.relu(x + asc2.broadcast_to(bias, rows_per_tile, cols)), out_gm, offsets=[i, 0])

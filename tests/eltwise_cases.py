@@ -188,3 +188,64 @@ def memory_case(dim, tensor_shape, tile_shape, tile_id, offsets, is_static):
     kernel = K.add_scalar if tile_shape is None else K.add_static if is_static else \
         K.add_dynamic_1d if dim == 1 else K.add_dynamic_2d
     return launch, expected, kernel
+
+
+# (asc2 op, torch op, op arguments, input shape): python/test/asc2/operations/test_shape_ops.py:10-18
+SHAPE_OPS = [
+    (asc2.broadcast_to, torch.broadcast_to, [4, 32], [1, 32]), (asc2.broadcast_to, torch.broadcast_to, [50, 32], [1, 32]),
+    (asc2.reshape, torch.reshape, [64], [2, 32]), (asc2.reshape, torch.reshape, [4, 16], [64]),
+    (asc2.ravel, torch.ravel, [], [2, 32]), (asc2.expand_dims, torch.unsqueeze, [0], [32]),
+    (asc2.squeeze, torch.squeeze, [0], [1, 32]),
+]
+SHAPE_CASES = [(a, t, args, shape, d) for a, t, args, shape in SHAPE_OPS for d in (torch.float16, torch.float32, torch.int32)]
+
+
+def shape_case(asc_op, torch_op, args, shape, dtype):
+    gen = torch.Generator().manual_seed(2026)
+
+    def create_input(tensor_shape):
+        if dtype.is_floating_point:
+            return torch.randn(tuple(tensor_shape), dtype=dtype, generator=gen).clamp(1, 100)
+        return torch.randint(1, 100, tuple(tensor_shape), dtype=dtype, generator=gen)
+
+    x = create_input(shape)
+    if asc_op in (asc2.expand_dims, asc2.squeeze):
+        ref_z = torch_op(x, dim=args[0])
+    elif not args:
+        ref_z = torch_op(x)
+    else:
+        ref_z = torch_op(x, args)
+    z = create_input(ref_z.shape)
+
+    def launch():
+        K.shape_op[1](x, z, tuple(x.shape), tuple(ref_z.shape), (0, ) * x.dim(), (0, ) * ref_z.dim(), asc_op, args)
+        return z
+
+    return launch, ref_z.contiguous()
+
+
+ATOMIC_CASES = [(a, t, d) for a, t in ((asc2.atomic_add, torch.add), (asc2.atomic_max, torch.maximum),
+                                       (asc2.atomic_min, torch.minimum))
+                for d in (torch.float32, torch.float16, torch.int32)]
+
+
+def atomic_case(asc_op, torch_op, dtype, cores=4, size=128):
+    gen = torch.Generator().manual_seed(2026)
+
+    def create_input(shape):
+        if dtype == torch.float32:
+            return torch.randn(tuple(shape), dtype=dtype, generator=gen).clamp(1, 100)
+        return torch.randint(1, 100, tuple(shape), generator=gen).to(dtype)
+
+    tile_length = size // cores
+    x = create_input([size])
+    z = create_input([tile_length])
+    expected = z.clone()
+    for i in range(cores):
+        expected = torch_op(expected, x[i * tile_length:(i + 1) * tile_length] + 10)
+
+    def launch():
+        K.atomic_op[cores](x, z, [size], tile_length, asc_op)
+        return z
+
+    return launch, expected

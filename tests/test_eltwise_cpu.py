@@ -150,5 +150,11 @@ def test_program_limits_and_rejections():
     def shifted(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
         x = asc2.load(asc2.tensor(x_ptr, [2 * n]), [n], offsets=[n])
         asc2.store(asc2.exp(x), asc2.tensor(out_ptr, [2 * n]), offsets=[0])
-    with pytest.raises(NotImplementedError, match="no kernel for this pattern"):
-        shifted[1](torch.zeros(128), torch.zeros(128), 64)
+    shifted[1](torch.zeros(128), torch.zeros(128), 64)       # operands addressed differently: one call per tile
+    assert [st.note for st in shifted.last_plan.steps] == ["2 ops over [1, 64] pitches [64, 64] from [64] to 0"]
+    with pytest.raises(NotImplementedError, match="also loads at other positions"):
+        @asc2.jit
+        def shift_in_place(x_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+            x_gm = asc2.tensor(x_ptr, [2 * n])
+            asc2.store(asc2.exp(asc2.load(x_gm, [n], offsets=[n])), x_gm, offsets=[0])
+        shift_in_place[1](torch.zeros(128), 64)

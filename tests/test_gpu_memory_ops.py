@@ -76,8 +76,9 @@ def test_window_program_bit_exact_and_confined(lib, dtype, out_type, round_op, R
     ops_a, args_a = (ctypes.c_int32 * len(ops))(*ops), (ctypes.c_int32 * len(ops))(*args)
     ins = (ctypes.c_void_p * 2)(x.data_ptr() + first, y.data_ptr() + first)
     types = (ctypes.c_int32 * 2)(out_type, out_type)
+    lds = (ctypes.c_int64 * 3)(C_, C_, C_)
     rc = lib.asc_cuda_eltwise_program_2d(ops_a, args_a, len(ops), ins, types, 2, ctypes.c_void_p(out.data_ptr() + first),
-                                         out_type, rows, cols, C_, None)
+                                         out_type, rows, cols, lds, None)
     assert rc == 0, capi.status_string(rc)
     capi.check_device_status(None)
     want = torch.full((R, C_), 3.0, dtype=dtype)
@@ -86,12 +87,37 @@ def test_window_program_bit_exact_and_confined(lib, dtype, out_type, round_op, R
     assert torch.equal(out.cpu(), want)
 
 
+def test_broadcast_row_and_mixed_pitches(lib):
+    """out[r, c] = x[r, c] * b[c] + y[r, c]: x from a wider matrix, y contiguous, b one row (pitch 0)."""
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    rows, cols = 3000, 1024
+    x = torch.randn(rows, cols + 64, device="cuda", generator=gen)
+    y = torch.randn(rows, cols, device="cuda", generator=gen)
+    b = torch.randn(cols, device="cuda", generator=gen)
+    out = torch.full((rows, cols + 8), 5.0, device="cuda")
+    ops, args = [0, 0, 4, 0, 2], [0, 1, 0, 2, 0]
+    ops_a, args_a = (ctypes.c_int32 * 5)(*ops), (ctypes.c_int32 * 5)(*args)
+    ins = (ctypes.c_void_p * 3)(x.data_ptr(), b.data_ptr(), y.data_ptr())
+    types = (ctypes.c_int32 * 3)(0, 0, 0)
+    lds = (ctypes.c_int64 * 4)(cols + 64, 0, cols, cols + 8)
+    rc = lib.asc_cuda_eltwise_program_2d(ops_a, args_a, 5, ins, types, 3, ctypes.c_void_p(out.data_ptr()), 0, rows, cols,
+                                         lds, None)
+    assert rc == 0, capi.status_string(rc)
+    capi.check_device_status(None)
+    assert torch.equal(out[:, :cols], x[:, :cols] * b + y) and bool((out[:, cols:] == 5.0).all())
+
+
 def test_window_program_rejections(lib):
     x = torch.zeros(16, 16, device="cuda")
     ops_a, args_a = (ctypes.c_int32 * 1)(0), (ctypes.c_int32 * 1)(0)
     ins, types = (ctypes.c_void_p * 1)(x.data_ptr()), (ctypes.c_int32 * 1)(0)
     out = ctypes.c_void_p(x.data_ptr())
-    assert lib.asc_cuda_eltwise_program_2d(ops_a, args_a, 1, ins, types, 1, out, 0, 4, 8, 4, None) == 1   # pitch < cols
-    assert lib.asc_cuda_eltwise_program_2d(ops_a, args_a, 1, ins, types, 1, out, 0, -1, 8, 8, None) == 1
-    assert lib.asc_cuda_eltwise_program_2d(ops_a, args_a, 1, ins, types, 1, out, 0, 1 << 20, 1 << 12, 1 << 13, None) == 6
-    assert lib.asc_cuda_eltwise_program_2d(ops_a, args_a, 1, ins, types, 1, out, 0, 0, 8, 16, None) == 0  # empty
+
+    def call(rows, cols, pitches):
+        lds = (ctypes.c_int64 * 2)(*pitches)
+        return lib.asc_cuda_eltwise_program_2d(ops_a, args_a, 1, ins, types, 1, out, 0, rows, cols, lds, None)
+    assert call(4, 8, (4, 8)) == 1                       # an input pitch smaller than the row (and not 0)
+    assert call(4, 8, (8, 0)) == 1                       # the output cannot be a broadcast row
+    assert call(-1, 8, (8, 8)) == 1
+    assert call(1 << 20, 1 << 12, (1 << 13, 1 << 13)) == 6
+    assert call(0, 8, (16, 16)) == 0                     # empty

@@ -143,19 +143,22 @@ def test_workload_scripts_match_at_full_size():
 
 def test_unsupported_pattern_raises_not_implemented():
     @asc2.jit
-    def scatter_add(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
-        x = asc2.load(asc2.tensor(x_ptr, [n]), [n], offsets=[0])
-        asc2.atomic_add(x, asc2.tensor(out_ptr, [n]), [0])
-    x = np.zeros(64, np.float32)
+    def norm(x_ptr: asc.GlobalAddress, g_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+        x = asc2.load(asc2.tensor(x_ptr, [1, n]), [1, n], offsets=[0, 0])
+        g = asc2.load(asc2.tensor(g_ptr, [1, n]), [1, n], offsets=[0, 0])
+        asc2.store(asc2.rms_norm(x, g, 1e-6), asc2.tensor(out_ptr, [1, n]), offsets=[0, 0])
+    x = np.zeros((1, 64), np.float32)
     with pytest.raises(NotImplementedError, match="no kernel for this pattern"):
-        scatter_add[1](x, x.copy(), 64)
+        norm[1](x, x.copy(), x.copy(), 64)
 
     @asc2.jit
-    def shifted_copy(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
-        x = asc2.load(asc2.tensor(x_ptr, [2 * n]), [n], offsets=[n])
-        asc2.store(asc2.exp(x), asc2.tensor(out_ptr, [2 * n]), offsets=[0])
+    def centred(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, r: asc.ConstExpr[int], c: asc.ConstExpr[int]):
+        x = asc2.load(asc2.tensor(x_ptr, [r, c]), [r, c], offsets=[0, 0])
+        asc2.store(x - asc2.reduce_max(x, 1, keep_dims=False).reshape(r, 1).broadcast_to(r, c),
+                   asc2.tensor(out_ptr, [r, c]), offsets=[0, 0])
+    y = np.zeros((16, 64), np.float32)
     with pytest.raises(NotImplementedError, match="no kernel for this pattern"):
-        shifted_copy[1](np.zeros(128, np.float32), np.zeros(128, np.float32), 64)
+        centred[1](y, y.copy(), 16, 64)
 
 
 # ----------------------------------------------------------------------------- reference error behaviour
