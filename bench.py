@@ -609,6 +609,25 @@ def time_device(w: Workload, lib, steps: int, warmup: int, dist: Dist, dev) -> f
     return dist.max_over_ranks(ms, dev)
 
 
+NOMINAL = {"hbm": 8000.0, "tensor": 2250.0}     # B200 datasheet: 8 TB/s HBM3e, 2.25 PFLOP/s dense fp16/bf16
+
+
+def time_sustained(w: Workload, lib, seconds: float, ms_per_launch: float) -> Dict[str, Any]:
+    """Throughput over a loop of at least `seconds` of back-to-back launches (the power cap pulls the clock
+    down within about a second, so a tensor-bound kernel settles below its burst rate)."""
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    n = max(8, int(seconds * 1e3 / max(ms_per_launch, 1e-3)))
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(n):
+        w.launch(lib, stream)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / n
+    return {"launches": n, "ms_per_step": round(ms, 5), "value": round(w.throughput(w.work, ms * 1e-3), 2)}
+
+
 def time_e2e(w: Workload, steps: int, dist: Dist, dev) -> float:
     """Seconds per step through the public asc2 surface with pinned host tensors (the launcher copies
     in, launches, copies out and synchronises before returning)."""
@@ -697,9 +716,20 @@ def run_ours(args) -> Dict[str, Any]:
                          "peak_source": peaks["source"] + (" (2 x bf16 burst)" if name.startswith("gemm_i8") else
                                                            " (bf16 burst)" if w.bound == "tensor" else " (copy)")},
         }
+        res["roofline"]["nominal_peak"] = NOMINAL[w.bound] * (2 if name.startswith("gemm_i8") else 1)
+        res["roofline"]["frac_of_nominal"] = round(per_gpu / res["roofline"]["nominal_peak"], 4)
+        if w.bound == "tensor" and args.sustained_seconds > 0:
+            timed_launches_before = capi.launch_count()
+            sus = time_sustained(w, lib, args.sustained_seconds, ms)
+            timed_launches += capi.launch_count() - timed_launches_before
+            sus_peak = float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])) * (2 if name.startswith("gemm_i8") else 1)
+            sus.update({"unit": w.unit, "peak": round(sus_peak, 1), "frac": round(sus["value"] / sus_peak, 4),
+                        "peak_source": peaks["source"] + " (bf16 sustained" + (", x 2)" if name.startswith("gemm_i8") else ")")})
+            res["sustained"] = sus
         ag = time_allgather(w, dist)
         if ag is not None:
             res["allgather_ms"] = round(ag, 4)
+            res["compute_plus_allgather_ms"] = round(ms + ag, 4)
         if not args.no_e2e:
             w.setup_host()
             e2e_steps = max(1, min(args.steps, args.e2e_steps))
@@ -779,6 +809,8 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0,
+                    help="length of the extra sustained loop for tensor-bound workloads (0: skip)")
     ap.add_argument("--workloads", type=lambda s: s.split(","), default=ALL_WORKLOADS,
                     help="comma-separated subset of: " + ",".join(ALL_WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=5, help="timed end-to-end steps per workload (<= --steps)")

@@ -32,8 +32,9 @@ int32_t asc_cuda_gemm_capped(const void* A, const void* B, void* C, int64_t M, i
  * 2 the CTA-pair 256 x 256 kernel whenever M > 128.  Process-wide. */
 int32_t asc_cuda_gemm_set_mode(int32_t mode);
 
-/* Elements each thread evaluates per opcode dispatch in asc_cuda_eltwise_program's aligned path:
- * 4, 8 (default) or 16.  Process-wide. */
+/* bits 0-7: elements each thread evaluates per opcode dispatch in asc_cuda_eltwise_program's aligned path
+ * (4, 8 or 16; anything else: chosen by program length); bit 8: run every program in the interpreter, also
+ * those with a compile-time specialised kernel.  Process-wide. */
 int32_t asc_cuda_eltwise_set_lanes(int32_t lanes);
 
 #ifdef __cplusplus
