@@ -1,7 +1,7 @@
 """Generates the committed golden fixtures under tests/golden/ with the reference's own CPU
 expressions (torch / NumPy, see oracle/golden.py for the file:line of each).
 
-Run from the repository root:  python tests/golden/make_golden.py
+Run from the repository root:  python tests/golden/make_golden.py   (--only-elementwise: just elementwise_reduce.npz)
 The reference package itself cannot be imported (its compiled MLIR extension and the CANN toolkit are
 absent), so the fixtures come from the torch/NumPy calls its tests make, on the seeds its tests use.
 """
@@ -16,8 +16,31 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 from oracle import golden as G  # noqa: E402
 
 
+def elementwise_and_reduce() -> None:
+    """GELU (both forms), bf16 leaky ReLU and the tile reductions, with the torch expressions of
+    python/test/asc2/kernels/test_gelu.py:46-50, test_leaky_relu.py:41-46 and
+    python/test/asc2/operations/test_reduce_ops.py:62-83."""
+    import math
+    g = G.gen()
+    x = torch.rand((8, 1024), generator=g)
+    erf = 0.5 * x * (1 + torch.erf(x / math.sqrt(2)))
+    tanh = 0.5 * x * (1 + torch.tanh(math.sqrt(2 / math.pi) * (x + 0.044715 * torch.pow(x, 3))))
+    xl = (torch.rand(8192, generator=g) * 10.0 - 5.0).to(torch.bfloat16)
+    alpha = torch.tensor(0.1, dtype=torch.bfloat16)
+    leaky = torch.where(xl >= 0, xl, xl * alpha)
+    xr = torch.randn([64, 32], generator=g) * 2.0
+    np.savez_compressed(os.path.join(HERE, "elementwise_reduce.npz"), gelu_x=x.numpy(), gelu_erf=erf.numpy(),
+                        gelu_tanh=tanh.numpy(), leaky_x=xl.view(torch.int16).numpy(), leaky_alpha=np.float32(alpha.item()),
+                        leaky_out=leaky.view(torch.int16).numpy(), reduce_x=xr.numpy(), sum0=xr.sum(0).numpy(),
+                        sum1=xr.sum(1).numpy(), max0=xr.amax(0).numpy(), min1=xr.amin(1).numpy(),
+                        prod0=xr.prod(0).numpy())
+
+
 def main() -> None:
     torch.set_num_threads(1)  # fixed summation order for the fp32 reductions
+    if "--only-elementwise" in sys.argv:
+        elementwise_and_reduce()
+        return
     # vector add, NumPy form of python/test/asc2/kernels/test_vadd.py:41-48
     rng = np.random.default_rng(seed=2026)
     x = rng.random(8192, dtype=np.float32) * 10
@@ -51,6 +74,7 @@ def main() -> None:
     q, k, v = G.attention_inputs(1, 2, 256)
     np.savez_compressed(os.path.join(HERE, "attention.npz"), q=q.numpy(), k=k.numpy(), v=v.numpy(),
                         o=G.attention(q, k, v, False).numpy(), o_causal=G.attention(q, k, v, True).numpy())
+    elementwise_and_reduce()
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

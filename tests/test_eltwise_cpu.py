@@ -158,3 +158,20 @@ def test_program_limits_and_rejections():
             x_gm = asc2.tensor(x_ptr, [2 * n])
             asc2.store(asc2.exp(asc2.load(x_gm, [n], offsets=[n])), x_gm, offsets=[0])
         shift_in_place[1](torch.zeros(128), 64)
+
+
+def test_golden_fixture_through_compiled_programs(golden_dir):
+    """The committed fixture (tests/golden/make_golden.py) against the programs the launcher compiles,
+    evaluated by the CPU oracle."""
+    import os
+    d = np.load(os.path.join(golden_dir, "elementwise_reduce.npz"))
+    x = torch.from_numpy(d["gelu_x"])
+    out = torch.empty_like(x)
+    for approximate, key in ((False, "gelu_erf"), (True, "gelu_tanh")):
+        K.gelu[16](x, out, 8, 1024, 1024, approximate)
+        torch.testing.assert_close(evaluate(K.gelu, [x, out]), torch.from_numpy(d[key]), rtol=1e-3, atol=1e-5)
+    xl = torch.from_numpy(d["leaky_x"]).view(torch.bfloat16)
+    alpha = torch.tensor(float(d["leaky_alpha"]), dtype=torch.bfloat16)
+    ol = torch.empty_like(xl)
+    K.leaky_relu[16](xl, alpha, ol, 8192, 128, 4)
+    assert torch.equal(evaluate(K.leaky_relu, [xl, alpha, ol, 8192]), torch.from_numpy(d["leaky_out"]).view(torch.bfloat16))

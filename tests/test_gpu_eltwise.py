@@ -241,3 +241,17 @@ def test_program_rejects_malformed_programs(lib):
     ops_a, args_a = (ctypes.c_int32 * 1)(0), (ctypes.c_int32 * 1)(0)
     ins, types = (ctypes.c_void_p * 1)(bad), (ctypes.c_int32 * 1)(1)
     assert lib.asc_cuda_eltwise_program(ops_a, args_a, 1, ins, types, 1, ctypes.c_void_p(out.data_ptr()), 0, 8, None) == 2
+
+
+def test_golden_fixture(golden_dir):
+    import os
+    d = np.load(os.path.join(golden_dir, "elementwise_reduce.npz"))
+    x = torch.from_numpy(d["gelu_x"])
+    out = torch.empty_like(x)
+    for approximate, key in ((False, "gelu_erf"), (True, "gelu_tanh")):
+        K.gelu[16](x, out, 8, 1024, 1024, approximate)
+        torch.testing.assert_close(out, torch.from_numpy(d[key]), rtol=1e-3, atol=1e-5)
+    xl = torch.from_numpy(d["leaky_x"]).view(torch.bfloat16)
+    ol = torch.empty_like(xl)
+    K.leaky_relu[16](xl, torch.tensor(float(d["leaky_alpha"]), dtype=torch.bfloat16), ol, 8192, 128, 4)
+    assert torch.equal(ol, torch.from_numpy(d["leaky_out"]).view(torch.bfloat16))

@@ -162,3 +162,20 @@ def test_row_sums_pinned_pipelined_matches_plain():
     assert K.row_sums.last_plan.pipeline is not None
     assert torch.equal(outp, plain)
     torch.testing.assert_close(plain, x.sum(1), rtol=1e-5, atol=1e-4)
+
+
+def test_golden_fixture(golden_dir):
+    import os
+    import numpy as np
+    d = np.load(os.path.join(golden_dir, "elementwise_reduce.npz"))
+    x = torch.from_numpy(d["reduce_x"])
+    for op, dim, key, exact in ((asc2.reduce_sum, 0, "sum0", False), (asc2.reduce_sum, 1, "sum1", False),
+                                (asc2.reduce_max, 0, "max0", True), (asc2.reduce_min, 1, "min1", True),
+                                (asc2.reduce_prod, 0, "prod0", False)):
+        want = torch.from_numpy(d[key])
+        out = torch.zeros_like(want)
+        K.reduce_axis[1](x, out, dim, [64, 32], [0, 0], list(want.shape), [0], op, False)
+        if exact:
+            assert torch.equal(out, want)
+        else:
+            torch.testing.assert_close(out, want, rtol=1e-5, atol=1e-5)
