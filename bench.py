@@ -159,6 +159,9 @@ class Softmax(Workload):
     def launch(self, lib, stream):
         return lib.asc_cuda_softmax_f32(P(self.x), P(self.out), self.R, self.C, self.C, stream)
 
+    def launch_range(self, lib, stream, lo, hi):      # rows [lo, hi) of this rank's shard
+        return lib.asc_cuda_softmax_f32(P(self.x[lo:hi]), P(self.out[lo:hi]), hi - lo, self.C, self.C, stream)
+
     def setup_host(self):
         from oracle import golden as G
         self.hx = G.softmax_input(self.R, self.C).pin_memory()
@@ -193,6 +196,9 @@ class VAdd(Workload):
 
     def launch(self, lib, stream):
         return lib.asc_cuda_vadd_f32(P(self.x), P(self.y), P(self.out), self.N, stream)
+
+    def launch_range(self, lib, stream, lo, hi):      # elements [lo, hi) of this rank's shard
+        return lib.asc_cuda_vadd_f32(P(self.x[lo:hi]), P(self.y[lo:hi]), P(self.out[lo:hi]), hi - lo, stream)
 
     def setup_host(self):
         g = torch.Generator().manual_seed(2026)
@@ -681,6 +687,35 @@ def time_allgather(w: Workload, dist: Dist) -> Optional[float]:
     return ms
 
 
+def time_overlapped_gather(w: Workload, lib, dist: Dist, chunks: int = 4) -> Optional[float]:
+    """Milliseconds for the shard's kernel in `chunks` pieces with each piece's all-gather started as soon as
+    the piece is enqueued (pyasc_b200.sharding.compute_and_gather): kernel and NCCL traffic overlap."""
+    if not dist.enabled or not hasattr(w, "launch_range"):
+        return None
+    from pyasc_b200 import sharding
+    local = w.out
+    full = torch.empty((local.shape[0] * dist.world, ) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def compute(lo, hi):
+        rc = w.launch_range(lib, stream, lo, hi)
+        if rc != 0:
+            raise RuntimeError(f"{w.name}: chunk launch returned {rc}")
+
+    sharding.compute_and_gather(compute, local, full, dist.world, chunks)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    start.record()
+    for _ in range(3):
+        sharding.compute_and_gather(compute, local, full, dist.world, chunks)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = dist.max_over_ranks(start.elapsed_time(stop) / 3, local.device)
+    del full
+    return ms
+
+
 def run_ours(args) -> Dict[str, Any]:
     dist = Dist(args.gpus)
     if not torch.cuda.is_available():
@@ -730,6 +765,9 @@ def run_ours(args) -> Dict[str, Any]:
         if ag is not None:
             res["allgather_ms"] = round(ag, 4)
             res["compute_plus_allgather_ms"] = round(ms + ag, 4)
+            ov = time_overlapped_gather(w, lib, dist)
+            if ov is not None:
+                res["overlapped_compute_and_allgather_ms"] = round(ov, 4)
         if not args.no_e2e:
             w.setup_host()
             e2e_steps = max(1, min(args.steps, args.e2e_steps))

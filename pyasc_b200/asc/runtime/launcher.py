@@ -27,7 +27,7 @@ from .options import LaunchOptions
 
 
 PIPELINE_MIN_BYTES = 16 << 20     # below this a launch is latency-bound and is not chunked
-PIPELINE_MAX_CHUNKS = 8
+PIPELINE_MAX_CHUNKS = int(os.environ.get("ASC_CUDA_PIPELINE_CHUNKS", "8"))
 
 _pipe_streams: Dict[int, Tuple[ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]] = {}
 _event_pool: List[ctypes.c_void_p] = []

@@ -10,7 +10,7 @@ every rank.  Kernels read local HBM only.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Optional, Tuple
+from typing import Callable, List, Optional, Tuple
 
 import torch
 
@@ -78,3 +78,42 @@ def all_gather_units(local: torch.Tensor, units: int, world_size: int, granule: 
     pieces = [torch.empty_like(padded) for _ in range(world_size)]
     dist.all_gather(pieces, padded, group=group)
     return torch.cat([p[:h - l] for p, (l, h) in zip(pieces, ranges)], dim=0)
+
+
+def cyclic_chunks(units_per_rank: int, n_chunks: int) -> List[Tuple[int, int]]:
+    """Local ``[lo, hi)`` pieces a rank's shard is produced in (equal on every rank)."""
+    if units_per_rank < 0 or n_chunks <= 0:
+        raise ValueError("bad chunking request")
+    step = -(-max(units_per_rank, 1) // min(n_chunks, max(1, units_per_rank)))
+    return [(lo, min(units_per_rank, lo + step)) for lo in range(0, units_per_rank, step)]
+
+
+def cyclic_global_range(lo: int, hi: int, rank: int, world_size: int) -> Tuple[int, int]:
+    """Where local units ``[lo, hi)`` of ``rank`` sit in the gathered output: piece by piece the ranks'
+    contributions lie side by side (a block-cyclic distribution), so each piece of every rank lands in one
+    contiguous range that a single all-gather fills."""
+    return world_size * lo + rank * (hi - lo), world_size * lo + (rank + 1) * (hi - lo)
+
+
+def compute_and_gather(compute: Callable[[int, int], None], local: torch.Tensor, full: torch.Tensor, world_size: int,
+                       n_chunks: int, group: Optional["torch.distributed.ProcessGroup"] = None) -> None:
+    """Overlap the output all-gather with the computation that produces it.
+
+    Every rank produces an equally sized shard ``local`` (``[units_per_rank, ...]``, a buffer ``compute``
+    fills) in ``n_chunks`` pieces: ``compute(lo, hi)`` enqueues the kernel for local units ``[lo, hi)`` on the
+    current stream, and as soon as a piece is enqueued its all-gather is started asynchronously, so the
+    collective of piece i runs while piece i + 1 is computed.  Units are independent, so the gathered
+    ``full`` (``[world_size * units_per_rank, ...]``) is laid out block-cyclically: piece by piece, rank after
+    rank (``cyclic_global_range``); that keeps every collective a plain contiguous all-gather.  Returns when
+    all of ``full`` is in place."""
+    import torch.distributed as dist
+    per = local.shape[0]
+    if full.shape[0] != per * world_size or tuple(full.shape[1:]) != tuple(local.shape[1:]):
+        raise ValueError(f"full output {tuple(full.shape)} is not {world_size} shards of {tuple(local.shape)}")
+    works = []
+    for lo, hi in cyclic_chunks(per, n_chunks):
+        compute(lo, hi)
+        works.append(dist.all_gather_into_tensor(full[world_size * lo:world_size * hi], local[lo:hi], group=group,
+                                                 async_op=True))
+    for w in works:
+        w.wait()

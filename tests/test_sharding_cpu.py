@@ -56,3 +56,43 @@ def _worker(rank: int, world: int, port: int, units: int, gran: int):
 @pytest.mark.parametrize("units, gran", [(64, 1), (1000, 4), (130, 128)])
 def test_all_gather_over_gloo(units, gran):
     mp.spawn(_worker, args=(2, _free_port(), units, gran), nprocs=2, join=True)
+
+
+def _overlap_worker(rank: int, world: int, port: int, per: int, chunks: int):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # global unit g holds the value g; every rank "computes" (x * 2) the units the cyclic layout gives it
+        local = torch.zeros(per, 2)
+        full = torch.full((world * per, 2), -1.0)
+        calls = []
+
+        def compute(lo, hi):
+            calls.append((lo, hi))
+            g0, g1 = sharding.cyclic_global_range(lo, hi, rank, world)
+            local[lo:hi] = torch.arange(g0, g1, dtype=torch.float32)[:, None].expand(-1, 2) * 2
+
+        sharding.compute_and_gather(compute, local, full, world, chunks)
+        want = torch.arange(world * per, dtype=torch.float32)[:, None].expand(-1, 2) * 2
+        assert torch.equal(full, want), f"rank {rank}"
+        assert calls == sharding.cyclic_chunks(per, chunks)
+        assert calls[0][0] == 0 and calls[-1][1] == per and all(a[1] == b[0] for a, b in zip(calls, calls[1:]))
+        with pytest.raises(ValueError):
+            sharding.compute_and_gather(compute, local, full[:-1], world, chunks)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("per, chunks", [(64, 4), (10, 3), (5, 8)])
+def test_compute_and_gather_overlapped_over_gloo(per, chunks):
+    mp.spawn(_overlap_worker, args=(2, _free_port(), per, chunks), nprocs=2, join=True)
+
+
+def test_cyclic_layout_covers_every_unit_once():
+    for per, chunks, world in [(64, 4, 2), (10, 3, 4), (5, 8, 8), (1, 1, 3)]:
+        seen = []
+        for r in range(world):
+            for lo, hi in sharding.cyclic_chunks(per, chunks):
+                g0, g1 = sharding.cyclic_global_range(lo, hi, r, world)
+                seen += list(range(g0, g1))
+        assert sorted(seen) == list(range(per * world))
