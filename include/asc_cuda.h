@@ -167,6 +167,9 @@ int32_t asc_cuda_reduce_f32(const float* x, float* out, int64_t rows, int64_t co
  * LowerAscTile.cpp:428-459, LowerMath.cpp:95) and asc2.softmax
  * (python/asc/language/tile/unary_ops.py:215-223 -> SoftMaxOp, LowerAscTile.cpp:155-188). */
 int32_t asc_cuda_softmax_f32(const float* x, float* out, int64_t rows, int64_t cols, int64_t ld, void* stream);
+/* The same for fp16 rows (asc2.softmax accepts float16 tiles, python/asc/language/tile/unary_ops.py:217;
+ * python/test/asc2/operations/test_softmax.py:35-58): fp32 arithmetic, one rounding at the store. */
+int32_t asc_cuda_softmax_f16(const void* x, void* out, int64_t rows, int64_t cols, int64_t ld, void* stream);
 
 /* C[M,N] = epilogue(A[M,K] @ B[K,N]), row-major operands, fp32 accumulation on tcgen05 tensor
  * cores.  in_dtype: 0 fp16, 1 bf16.  out_dtype: 0 fp16, 1 bf16, 2 fp32.

@@ -976,8 +976,10 @@ def _match_softmax(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         raise _unsupported("softmax of a tile that is not loaded directly from global memory")
     if not _same_offsets(view.offsets, eff.attrs["offsets"]) or view.shape != value.shape:
         raise _unsupported("softmax stored at a different position than it was loaded from")
-    if value.dtype != KT.float32 or out_t.dtype != KT.float32 or view.tensor.dtype != KT.float32:
-        raise _unsupported(f"softmax on {value.dtype} tiles (float32 only)")
+    if value.dtype not in (KT.float32, KT.float16) or out_t.dtype != value.dtype or view.tensor.dtype != value.dtype:
+        raise _unsupported(f"softmax on {value.dtype} tiles (float32 and float16 only)")
+    esize = value.dtype.bitwidth // 8
+    fn_name = "asc_cuda_softmax_f32" if value.dtype == KT.float32 else "asc_cuda_softmax_f16"
     if view.tensor.static_shape() != out_t.static_shape():
         raise _unsupported("softmax between tensors of different shapes")
     _check_fits(out_t)
@@ -1012,15 +1014,15 @@ def _match_softmax(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         plan.partial_writes.add(out_idx)
     def make(lo: int, hi: int) -> List[Step]:
         def build(ptrs, stream, lo=lo, hi=hi):
-            byte_off = 4 * (lo * C + col0)
+            byte_off = esize * (lo * C + col0)
             return (_p(ptrs[in_idx] + byte_off), _p(ptrs[out_idx] + byte_off), ctypes.c_int64(hi - lo),
                     ctypes.c_int64(tile_cols), ctypes.c_int64(C), stream)
-        return [Step("asc_cuda_softmax_f32", build, f"rows [{lo}, {hi}) x {tile_cols} cols")]
+        return [Step(fn_name, build, f"rows [{lo}, {hi}) x {tile_cols} cols")]
 
     for lo, hi in intervals:
         plan.steps += make(lo, hi)
     if not plan.partial_writes:
-        plan.pipeline = PipelineSpec(R, 1, {in_idx: 4 * C, out_idx: 4 * C}, set(), make)
+        plan.pipeline = PipelineSpec(R, 1, {in_idx: esize * C, out_idx: esize * C}, set(), make)
     return plan
 
 

@@ -8,6 +8,7 @@
 // staged in shared memory instead (one global read, one global write); rows too long for shared
 // memory are re-read from global memory.
 #include <cfloat>
+#include <cuda_fp16.h>
 
 #include "../../include/asc_cuda.h"
 #include "host_common.h"
@@ -97,38 +98,76 @@ __global__ void __launch_bounds__(kThreads)
   }
 }
 
-// Any cols / alignment.  kStage: the row is kept in dynamic shared memory between the passes.
-template <bool kStage>
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+// Any cols / alignment, fp32 or fp16 elements (arithmetic in fp32, one rounding at the store).
+// kStage: the row is kept as fp32 in dynamic shared memory between the passes.
+template <bool kStage, typename T>
 __global__ void __launch_bounds__(256)
-    softmax_rows_generic_kernel(const float* __restrict__ x, float* __restrict__ out, int64_t rows, int64_t cols,
-                                int64_t ld) {
+    softmax_rows_generic_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t rows, int64_t cols, int64_t ld) {
   extern __shared__ float row_buf[];
   __shared__ float red_a[8];
   __shared__ float red_b[8];
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float* xr = x + row * ld;
-    float* orow = out + row * ld;
+    const T* xr = x + row * ld;
+    T* orow = out + row * ld;
     float m = -FLT_MAX;
     for (int64_t c = threadIdx.x; c < cols; c += 256) {
-      const float t = xr[c];
+      const float t = to_f32(xr[c]);
       if (kStage) row_buf[c] = t;
       m = fmaxf(m, t);
     }
     m = cta_reduce<8, true>(m, red_a);
     float s = 0.f;
     for (int64_t c = threadIdx.x; c < cols; c += 256) {
-      const float e = expf((kStage ? row_buf[c] : xr[c]) - m);
+      const float e = expf((kStage ? row_buf[c] : to_f32(xr[c])) - m);
       if (kStage) row_buf[c] = e;
       s += e;
     }
     s = cta_reduce<8, false>(s, red_b);
     const float inv = __frcp_rn(s);
     for (int64_t c = threadIdx.x; c < cols; c += 256) {
-      const float e = kStage ? row_buf[c] : expf(xr[c] - m);
-      orow[c] = e * inv;
+      const float e = kStage ? row_buf[c] : expf(to_f32(xr[c]) - m);
+      orow[c] = from_f32<T>(e * inv);
     }
     __syncthreads();  // red_a / red_b / row_buf are reused by the next row
   }
+}
+
+template <typename T>
+int32_t launch_generic(const T* x, T* out, int64_t rows, int64_t cols, int64_t ld, cudaStream_t stream) {
+  int sms = 0;
+  int32_t rc = aschost::sm_count(&sms);
+  if (rc != ASC_OK) return rc;
+  const size_t row_bytes = static_cast<size_t>(cols) * sizeof(float);
+  constexpr size_t kMaxStage = 200 * 1024;
+  if (row_bytes <= kMaxStage) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    ASC_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+      ASC_CUDA_TRY(cudaFuncSetAttribute(softmax_rows_generic_kernel<true, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(kMaxStage)));
+      attr_set[dev] = true;
+    }
+    int64_t per = static_cast<int64_t>((220 * 1024) / (row_bytes + 1024));
+    if (per < 1) per = 1;
+    if (per > 8) per = 8;
+    int64_t grid = static_cast<int64_t>(sms) * per;
+    if (grid > rows) grid = rows;
+    softmax_rows_generic_kernel<true, T><<<static_cast<unsigned>(grid), 256, row_bytes, stream>>>(x, out, rows, cols, ld);
+  } else {
+    int64_t grid = static_cast<int64_t>(sms) * 8;
+    if (grid > rows) grid = rows;
+    softmax_rows_generic_kernel<false, T><<<static_cast<unsigned>(grid), 256, 0, stream>>>(x, out, rows, cols, ld);
+  }
+  aschost::count_launch();
+  ASC_CUDA_TRY(cudaGetLastError());
+  return ASC_OK;
 }
 
 template <int kThreads, int kVec>
@@ -176,34 +215,7 @@ int32_t launch_softmax(const float* x, float* out, int64_t rows, int64_t cols, i
     }
     return launch_reg<256, 8>(x, out, rows, cols, ld, per_sm, stream);
   }
-  int sms = 0;
-  int32_t rc = aschost::sm_count(&sms);
-  if (rc != ASC_OK) return rc;
-  const size_t row_bytes = static_cast<size_t>(cols) * sizeof(float);
-  constexpr size_t kMaxStage = 200 * 1024;
-  if (row_bytes <= kMaxStage) {
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    ASC_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-      ASC_CUDA_TRY(cudaFuncSetAttribute(softmax_rows_generic_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(kMaxStage)));
-      attr_set[dev] = true;
-    }
-    int64_t per = static_cast<int64_t>((220 * 1024) / (row_bytes + 1024));
-    if (per < 1) per = 1;
-    if (per > 8) per = 8;
-    int64_t grid = static_cast<int64_t>(sms) * per;
-    if (grid > rows) grid = rows;
-    softmax_rows_generic_kernel<true><<<static_cast<unsigned>(grid), 256, row_bytes, stream>>>(x, out, rows, cols, ld);
-  } else {
-    int64_t grid = static_cast<int64_t>(sms) * 8;
-    if (grid > rows) grid = rows;
-    softmax_rows_generic_kernel<false><<<static_cast<unsigned>(grid), 256, 0, stream>>>(x, out, rows, cols, ld);
-  }
-  aschost::count_launch();
-  ASC_CUDA_TRY(cudaGetLastError());
-  return ASC_OK;
+  return launch_generic<float>(x, out, rows, cols, ld, stream);
 }
 
 }  // namespace
@@ -212,6 +224,16 @@ extern "C" {
 
 int32_t asc_cuda_softmax_f32(const float* x, float* out, int64_t rows, int64_t cols, int64_t ld, void* stream) {
   return launch_softmax(x, out, rows, cols, ld, 0, static_cast<cudaStream_t>(stream));
+}
+
+// fp16 rows (asc2.softmax accepts fp16 tiles, python/asc/language/tile/unary_ops.py:217): fp32 arithmetic, the
+// result rounded once.  Not a tuned path.
+int32_t asc_cuda_softmax_f16(const void* x, void* out, int64_t rows, int64_t cols, int64_t ld, void* stream) {
+  if (rows < 0 || cols < 0 || ld < cols) return ASC_ERR_INVALID_ARG;
+  if (rows == 0 || cols == 0) return ASC_OK;
+  if (x == nullptr || out == nullptr) return ASC_ERR_INVALID_ARG;
+  return launch_generic<__half>(static_cast<const __half*>(x), static_cast<__half*>(out), rows, cols, ld,
+                                static_cast<cudaStream_t>(stream));
 }
 
 // variant: bits 0-7 CTA shape selector for 2048 < cols <= 4096 (0: 512x2, 1: 128x8, 3: 256x4,

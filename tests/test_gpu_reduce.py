@@ -81,9 +81,10 @@ def test_row_sums_over_all_blocks():
     torch.testing.assert_close(out, x.double().sum(1).float(), rtol=1e-5, atol=1e-4)
 
 
-@pytest.mark.parametrize("shape", [[1, 8], [4, 256]])
-def test_softmax_2d_op(shape):
-    src = torch.rand(shape, dtype=torch.float32)
+@pytest.mark.parametrize("dtype, shape", [(torch.float16, [1, 16]), (torch.float16, [4, 1024]), (torch.float32, [1, 8]),
+                                          (torch.float32, [4, 256])])
+def test_softmax_2d_op(dtype, shape):
+    src = torch.rand(shape, dtype=dtype)
     keep = src.clone()
     dst = torch.zeros_like(src)
     K.softmax_2d[1](dst, src, shape)
@@ -91,9 +92,10 @@ def test_softmax_2d_op(shape):
     assert torch.equal(src, keep)                      # the tile stored back to the source is unchanged
 
 
-@pytest.mark.parametrize("length", [8, 1024])
-def test_softmax_1d_op(length):
-    src = torch.rand(length, dtype=torch.float32)
+@pytest.mark.parametrize("dtype, length", [(torch.float16, 16), (torch.float16, 1024), (torch.float32, 8),
+                                           (torch.float32, 1024)])
+def test_softmax_1d_op(dtype, length):
+    src = torch.rand(length, dtype=dtype)
     dst = torch.zeros_like(src)
     K.softmax_1d[1](dst, src, length)
     torch.testing.assert_close(dst, torch.softmax(src, dim=0))
@@ -179,3 +181,17 @@ def test_golden_fixture(golden_dir):
             assert torch.equal(out, want)
         else:
             torch.testing.assert_close(out, want, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("rows, cols", [(3, 7), (257, 4096), (8, 60000), (4, 70001)])
+def test_capi_softmax_f16(lib, rows, cols):
+    """fp16 rows: registers-free generic path, rows staged in shared memory and rows too long for it."""
+    gen = torch.Generator(device="cuda").manual_seed(rows + cols)
+    x = (torch.randn(rows, cols + 1, device="cuda", generator=gen) * 3).half()
+    out = torch.full_like(x, 9.0)
+    rc = lib.asc_cuda_softmax_f16(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()), rows, cols, cols + 1, None)
+    assert rc == 0, capi.status_string(rc)
+    capi.check_device_status(None)
+    want = torch.softmax(x[:, :cols].float(), dim=1).half()
+    torch.testing.assert_close(out[:, :cols], want, rtol=1e-3, atol=1e-6)
+    assert bool((out[:, cols] == 9.0).all())
