@@ -255,3 +255,84 @@ def test_golden_fixture(golden_dir):
     ol = torch.empty_like(xl)
     K.leaky_relu[16](xl, torch.tensor(float(d["leaky_alpha"]), dtype=torch.bfloat16), ol, 8192, 128, 4)
     assert torch.equal(ol, torch.from_numpy(d["leaky_out"]).view(torch.bfloat16))
+
+
+# ------------------------------------------------------------------------------- random programs
+def _random_program(rng, n_inputs, round_op):
+    """A random valid postfix program over fp32 stack words: arithmetic, comparisons, selects, immediates and
+    swapped forms, every result rounded through `round_op` when the tensors are 16-bit."""
+    binary = [2, 3, 4, 6, 7, 54]
+    unary = [8, 9, 10, 24, 25]
+    compare = [26, 27, 28, 29, 30, 31]
+    code = []
+
+    def rounded():
+        if round_op:
+            code.append((round_op, 0))
+
+    def const():
+        return fbits(float(np.float32(rng.uniform(-2, 2)))) if not round_op else \
+            fbits(float(torch.tensor(rng.uniform(-2, 2)).to(torch.float16 if round_op == 33 else torch.bfloat16)))
+
+    def gen(depth):
+        kind = rng.integers(0, 6) if depth > 0 else 0
+        if kind == 0:
+            code.append((0, int(rng.integers(0, n_inputs))))
+        elif kind == 1:
+            gen(depth - 1)
+            code.append((int(rng.choice(unary)), 0))
+            rounded()
+        elif kind == 2:
+            gen(depth - 1)
+            gen(depth - 1)
+            code.append((int(rng.choice(binary)), 0))
+            rounded()
+        elif kind == 3:
+            gen(depth - 1)
+            code.append((int(rng.choice(binary)) | IMM, const()))
+            rounded()
+        elif kind == 4:
+            gen(depth - 1)
+            gen(depth - 1)
+            code.append((int(rng.choice(compare)), 0))
+            gen(depth - 1)
+            gen(depth - 1)
+            code.append((32, 0))
+        else:
+            gen(depth - 1)
+            code.append((int(rng.choice(compare)) | IMM, const()))
+            gen(depth - 1)
+            code.append((1, const()))
+            code.append((32, 0))
+    gen(3)
+    return [c[0] for c in code], [c[1] for c in code]
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_programs_bit_exact_in_every_executor_width(lib, seed):
+    rng = np.random.default_rng(seed)
+    dtype, out_type, round_op = [(torch.float32, 0, None), (torch.float16, 1, 33), (torch.bfloat16, 2, 34)][seed % 3]
+    n_inputs = int(rng.integers(1, 4))
+    ops, args = _random_program(rng, n_inputs, round_op)
+    depth = peak = 0
+    for op in ops:
+        code, imm = op & 0xff, bool(op & IMM)
+        depth += 1 if code <= 1 else -2 if code == 32 else 0 if imm or code in (8, 9, 10, 24, 25, 33, 34) else -1
+        peak = max(peak, depth)
+    if len(ops) > 48 or peak > 8:
+        pytest.skip("program beyond the documented limits")
+    n = int(rng.choice([1, 37, 4096, 70001, (1 << 20) + 5]))
+    gen = torch.Generator().manual_seed(seed)
+    inputs = [(torch.rand(n, generator=gen) * 8 - 4).to(dtype) for _ in range(n_inputs)]
+    dev = [t.cuda() for t in inputs]
+    want = E.run_program(ops, args, inputs, out_type)
+    try:
+        for lanes in (4, 8, 16):
+            lib.asc_cuda_eltwise_set_lanes(lanes)
+            out = torch.zeros(n + 1, dtype=dtype, device="cuda")
+            call(lib, ops, args, dev, out, out_type, n)
+            got = out.cpu()
+            assert torch.equal(got[:n], want), f"lanes {lanes}: {ops}"
+            assert got[n] == 0
+    finally:
+        lib.asc_cuda_eltwise_set_lanes(0)
