@@ -1,7 +1,11 @@
 // Flash-attention forward (fp16 / bf16, head size 128) for sm_100a.
 //
-// One CTA owns 256 consecutive query rows of one (batch, head): two 128-row query tiles that
-// ping-pong on the tensor core so that the softmax of one tile overlaps the MMAs of the other.
+// Persistent kernel: one CTA per SM walks a static list of work items.  An item is 256 consecutive query
+// rows of one (batch, head): two 128-row query tiles that ping-pong on the tensor core so that the
+// softmax of one tile overlaps the MMAs of the other.  The producer and MMA warps run ahead into the next
+// item (its Q load and first Q K^T) while the softmax warps still write out the previous one, and with a
+// causal mask every unit of the list pairs a heavy query block with a light one of the same head, so all
+// units cost the same and a round-robin over the CTAs is balanced.
 //   warps 0-3   softmax warpgroup of query tile 0: one thread per query row.  Reads the 128 scores
 //   warps 4-7   (same for tile 1)  of its row from tensor memory (tcgen05.ld), keeps the running
 //               max / sum in fp32, writes P as 16-bit values back into the same tensor-memory
@@ -36,6 +40,11 @@ constexpr uint32_t kAttnSmem = 6 * kTileBytes + 1024;
 constexpr uint32_t kColS = 0;    // S_t at columns [128 t, 128 t + 128); P_t aliases its first 64 columns
 constexpr uint32_t kColO = 256;  // O_t at columns [256 + 128 t, ...)
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units
+// Register split after launch (setmaxnreg): the 8 softmax warps grow, the other 4 shrink.  An increase can
+// only take registers a decrease in the same CTA has released, otherwise it waits forever, so the split must
+// fit the launch allocation of 168 registers x 384 threads (what __launch_bounds__(384, 1) compiles to).
+constexpr int kLaunchRegs = 168, kSoftmaxRegs = 208, kOtherRegs = 88;
+static_assert(8 * kSoftmaxRegs + 4 * kOtherRegs <= 12 * kLaunchRegs, "register split exceeds the launch allocation");
 
 struct AttnParams {
   void* o;
@@ -43,11 +52,27 @@ struct AttnParams {
   float scale_log2;  // softmax scale * log2(e)
   int32_t causal;
   int32_t pairs;     // 256-row query blocks per head
+  int32_t units;     // work units: (head, query block) non-causal; (head, heavy + light query block) causal
+  int32_t half;      // causal: units per head = ceil(pairs / 2)
   uint32_t* status;
 };
 
+// The items of work unit `u`, in order: sub 0 and, with a causal mask, sub 1.  Returns false when the unit
+// has no such item.  Heads are the slow axis so that the CTAs running at any time share K and V through L2.
+__device__ __forceinline__ bool unit_item(const AttnParams& p, int u, int sub, int& bh, int& pair) {
+  if (!p.causal) {
+    bh = u / p.pairs;
+    pair = p.pairs - 1 - u % p.pairs;
+    return sub == 0;
+  }
+  bh = u / p.half;
+  const int q = u % p.half;
+  pair = sub == 0 ? p.pairs - 1 - q : q;      // the heavy block first, then its light partner
+  return sub == 0 || (sub == 1 && q != p.pairs - 1 - q);
+}
+
 struct AttnCtl {
-  uint64_t q_full[2];
+  uint64_t q_full[2], q_empty[2];
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
   uint64_t s_full[2], p_full[2], o_full[2];
   uint32_t tmem_base;
@@ -106,8 +131,8 @@ __device__ __forceinline__ int kv_tiles_for(int qt, int S, int causal) {
 // Softmax warpgroup of one query tile.
 // ----------------------------------------------------------------------------------------------
 template <bool kBf16>
-__device__ __forceinline__ void softmax_role(const AttnParams& p, AttnCtl& ctl, uint32_t tmem_base, int t, int bh,
-                                             int qt, int n_kv) {
+__device__ __forceinline__ bool softmax_role(const AttnParams& p, AttnCtl& ctl, uint32_t tmem_base, int t, int bh,
+                                             int qt, int n_kv, uint32_t& s_it, uint32_t& o_it) {
   volatile uint32_t* abort_flag = &ctl.abort_flag;
   const uint32_t lane_row = threadIdx.x & 127;  // row inside the tile == TMEM lane
   const uint32_t lane_base = ((threadIdx.x >> 5) & 3) * 32;
@@ -120,7 +145,8 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, AttnCtl& ctl, 
   float l = 0.f;      // running sum of exp2((s - m_ref) * sl2)
 
   for (int j = 0; j < n_kv; ++j) {
-    if (!mbar_wait(smem_u32(&ctl.s_full[t]), j & 1, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL)) return;
+    if (!mbar_wait(smem_u32(&ctl.s_full[t]), s_it & 1, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL)) return false;
+    ++s_it;
     tc_fence_after();
     uint32_t s[4][32];
 #pragma unroll
@@ -204,10 +230,11 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, AttnCtl& ctl, 
     tc_fence_before();
     mbar_arrive(smem_u32(&ctl.p_full[t]));
   }
-  if (n_kv == 0) return;
+  if (n_kv == 0) return true;
 
   // ------------------------------ epilogue: O / l -> 16-bit -> global ------------------------------
-  if (!mbar_wait(smem_u32(&ctl.o_full[t]), 0, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL)) return;
+  if (!mbar_wait(smem_u32(&ctl.o_full[t]), o_it & 1, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL)) return false;
+  ++o_it;
   tc_fence_after();
   const float inv = 1.f / l;
   uint16_t* dst = reinterpret_cast<uint16_t*>(p.o) + (static_cast<int64_t>(bh) * p.S + q_row) * kHeadDim;
@@ -226,6 +253,10 @@ __device__ __forceinline__ void softmax_role(const AttnParams& p, AttnCtl& ctl, 
         reinterpret_cast<uint4*>(dst + c * 32)[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
     }
   }
+  // O_t has been read: the first P V of the next item may overwrite it.  That MMA is issued only after this
+  // thread's next p_full arrival, which follows in program order.
+  tc_fence_before();
+  return true;
 }
 
 // ----------------------------------------------------------------------------------------------
@@ -244,15 +275,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   volatile uint32_t* abort_flag = &ctl.abort_flag;
 
-  // Heads are the slow grid axis so that the CTAs resident at any time share K and V through L2;
-  // within a head the heaviest (causal: last) query block goes first.
-  const int bh = static_cast<int>(blockIdx.x) / p.pairs;
-  const int pair = p.pairs - 1 - static_cast<int>(blockIdx.x) % p.pairs;
-  const int qt0 = 2 * pair;
-  const int n0 = kv_tiles_for(qt0, p.S, p.causal);
-  const int n1 = kv_tiles_for(qt0 + 1, p.S, p.causal);
-  const int n_max = n0 > n1 ? n0 : n1;
-
   if (threadIdx.x == 0) {
     ctl.abort_flag = 0;
     prefetch_tmap(&tmap_q);
@@ -260,6 +282,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     prefetch_tmap(&tmap_v);
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&ctl.q_full[i]), 1);
+      mbar_init(smem_u32(&ctl.q_empty[i]), 1);
       mbar_init(smem_u32(&ctl.k_full[i]), 1);
       mbar_init(smem_u32(&ctl.k_empty[i]), 1);
       mbar_init(smem_u32(&ctl.v_full[i]), 1);
@@ -279,45 +302,76 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = ctl.tmem_base;
 
+  // Every role walks the same list of items, so the running use counts of the barriers (which give stage and
+  // phase) advance identically in all of them.
   if (warp < 8) {
-    setmaxnreg_inc<224>();
+    setmaxnreg_inc<kSoftmaxRegs>();
     const int t = static_cast<int>(warp >> 2);
-    softmax_role<kBf16>(p, ctl, tmem_base, t, bh, qt0 + t, t == 0 ? n0 : n1);
+    uint32_t s_it = 0, o_it = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+      for (int sub = 0; sub < 2 && ok; ++sub) {
+        int bh, pair;
+        if (!unit_item(p, u, sub, bh, pair)) continue;
+        const int qt = 2 * pair + t;
+        ok = softmax_role<kBf16>(p, ctl, tmem_base, t, bh, qt, kv_tiles_for(qt, p.S, p.causal), s_it, o_it);
+      }
+    }
   } else {
-    setmaxnreg_dec<56>();
+    setmaxnreg_dec<kOtherRegs>();
     if (warp == 8) {
       // ------------------------------ TMA producer ------------------------------
       bool ok = true;
-      for (int t = 0; t < 2; ++t) {
-        if ((t == 0 ? n0 : n1) > 0 && lane == 0) {
-          const uint32_t bar = smem_u32(&ctl.q_full[t]);
-          const uint32_t dst = smem_base + kSmemQ + t * kTileBytes;
-          mbar_arrive_expect_tx(bar, kTileBytes);
-          tma_load_3d(dst, &tmap_q, bar, 0, (qt0 + t) * kTileQ, bh);
-          tma_load_3d(dst + kHalfTile, &tmap_q, bar, 64, (qt0 + t) * kTileQ, bh);
+      uint32_t q_it[2] = {0, 0}, k_it = 0, v_it = 0;
+      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+        for (int sub = 0; sub < 2 && ok; ++sub) {
+          int bh, pair;
+          if (!unit_item(p, u, sub, bh, pair)) continue;
+          const int qt0 = 2 * pair;
+          const int n0 = kv_tiles_for(qt0, p.S, p.causal), n1 = kv_tiles_for(qt0 + 1, p.S, p.causal);
+          const int n_max = n0 > n1 ? n0 : n1;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (!ok || (t == 0 ? n0 : n1) == 0) continue;
+            // the previous item's Q K^T of this tile have retired
+            ok = mbar_wait(smem_u32(&ctl.q_empty[t]), (q_it[t] & 1) ^ 1, abort_flag, p.status, ASC_DEV_TIMEOUT_EMPTY);
+            if (!ok) continue;
+            ++q_it[t];
+            if (lane == 0) {
+              const uint32_t bar = smem_u32(&ctl.q_full[t]);
+              const uint32_t dst = smem_base + kSmemQ + t * kTileBytes;
+              mbar_arrive_expect_tx(bar, kTileBytes);
+              tma_load_3d(dst, &tmap_q, bar, 0, (qt0 + t) * kTileQ, bh);
+              tma_load_3d(dst + kHalfTile, &tmap_q, bar, 64, (qt0 + t) * kTileQ, bh);
+            }
+            __syncwarp();
+          }
+          for (int j = 0; j < n_max && ok; ++j) {
+            const uint32_t kst = k_it & 1, kph = (k_it >> 1) & 1;
+            ok = mbar_wait(smem_u32(&ctl.k_empty[kst]), kph ^ 1, abort_flag, p.status, ASC_DEV_TIMEOUT_EMPTY);
+            if (!ok) break;
+            ++k_it;
+            if (lane == 0) {
+              const uint32_t bar = smem_u32(&ctl.k_full[kst]);
+              const uint32_t dst = smem_base + kSmemK + kst * kTileBytes;
+              mbar_arrive_expect_tx(bar, kTileBytes);
+              tma_load_3d(dst, &tmap_k, bar, 0, j * kTileKV, bh);
+              tma_load_3d(dst + kHalfTile, &tmap_k, bar, 64, j * kTileKV, bh);
+            }
+            const uint32_t vst = v_it & 1, vph = (v_it >> 1) & 1;
+            ok = mbar_wait(smem_u32(&ctl.v_empty[vst]), vph ^ 1, abort_flag, p.status, ASC_DEV_TIMEOUT_EMPTY);
+            if (!ok) break;
+            ++v_it;
+            if (lane == 0) {
+              const uint32_t bar = smem_u32(&ctl.v_full[vst]);
+              const uint32_t dst = smem_base + kSmemV + vst * kTileBytes;
+              mbar_arrive_expect_tx(bar, kTileBytes);
+              tma_load_3d(dst, &tmap_v, bar, 0, j * kTileKV, bh);
+              tma_load_3d(dst + kHalfTile, &tmap_v, bar, 64, j * kTileKV, bh);
+            }
+            __syncwarp();
+          }
         }
-      }
-      for (int j = 0; j < n_max && ok; ++j) {
-        const uint32_t st = j & 1, ph = (j >> 1) & 1;
-        ok = mbar_wait(smem_u32(&ctl.k_empty[st]), ph ^ 1, abort_flag, p.status, ASC_DEV_TIMEOUT_EMPTY);
-        if (!ok) break;
-        if (lane == 0) {
-          const uint32_t bar = smem_u32(&ctl.k_full[st]);
-          const uint32_t dst = smem_base + kSmemK + st * kTileBytes;
-          mbar_arrive_expect_tx(bar, kTileBytes);
-          tma_load_3d(dst, &tmap_k, bar, 0, j * kTileKV, bh);
-          tma_load_3d(dst + kHalfTile, &tmap_k, bar, 64, j * kTileKV, bh);
-        }
-        ok = mbar_wait(smem_u32(&ctl.v_empty[st]), ph ^ 1, abort_flag, p.status, ASC_DEV_TIMEOUT_EMPTY);
-        if (!ok) break;
-        if (lane == 0) {
-          const uint32_t bar = smem_u32(&ctl.v_full[st]);
-          const uint32_t dst = smem_base + kSmemV + st * kTileBytes;
-          mbar_arrive_expect_tx(bar, kTileBytes);
-          tma_load_3d(dst, &tmap_v, bar, 0, j * kTileKV, bh);
-          tma_load_3d(dst + kHalfTile, &tmap_v, bar, 64, j * kTileKV, bh);
-        }
-        __syncwarp();
       }
     } else if (warp == 9) {
       // ------------------------------- MMA issuer -------------------------------
@@ -344,52 +398,74 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
                       (accumulate || ks > 0) ? 1u : 0u);
         }
       };
-      bool ok = n_max > 0;
-      if (ok) ok = mbar_wait(smem_u32(&ctl.k_full[0]), 0, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
-      for (int t = 0; t < 2 && ok; ++t) {
-        if ((t == 0 ? n0 : n1) == 0) continue;
-        ok = mbar_wait(smem_u32(&ctl.q_full[t]), 0, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
-        if (!ok) break;
-        tc_fence_after();
-        if (lane == 0) {
-          issue_qk(t, 0);
-          umma_commit(smem_u32(&ctl.s_full[t]));
-        }
-        __syncwarp();
-      }
-      if (ok && lane == 0) umma_commit(smem_u32(&ctl.k_empty[0]));
-      __syncwarp();
-      for (int j = 0; j < n_max && ok; ++j) {
-        const uint32_t st = j & 1, ph = (j >> 1) & 1;
-        const uint32_t st_n = (j + 1) & 1, ph_n = ((j + 1) >> 1) & 1;
-        ok = mbar_wait(smem_u32(&ctl.v_full[st]), ph, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
-        if (!ok) break;
-        if (j + 1 < n_max) {
-          ok = mbar_wait(smem_u32(&ctl.k_full[st_n]), ph_n, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
-          if (!ok) break;
-        }
-        for (int t = 0; t < 2 && ok; ++t) {
-          const int nt = t == 0 ? n0 : n1;
-          if (j >= nt) continue;
-          ok = mbar_wait(smem_u32(&ctl.p_full[t]), j & 1, abort_flag, p.status, ASC_DEV_TIMEOUT_OTHER);
-          if (!ok) break;
-          tc_fence_after();
-          if (lane == 0) {
-            issue_pv(t, st, j > 0 ? 1u : 0u);
-            if (j + 1 < nt) {
-              issue_qk(t, st_n);
+      bool ok = true;
+      uint32_t q_it[2] = {0, 0}, p_it[2] = {0, 0}, k_it = 0, v_it = 0;
+      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+        for (int sub = 0; sub < 2 && ok; ++sub) {
+          int bh, pair;
+          if (!unit_item(p, u, sub, bh, pair)) continue;
+          const int qt0 = 2 * pair;
+          const int n0 = kv_tiles_for(qt0, p.S, p.causal), n1 = kv_tiles_for(qt0 + 1, p.S, p.causal);
+          const int n_max = n0 > n1 ? n0 : n1;
+          if (n_max == 0) continue;
+          // first scores of both tiles
+          uint32_t kst = k_it & 1, kph = (k_it >> 1) & 1;
+          ok = mbar_wait(smem_u32(&ctl.k_full[kst]), kph, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (!ok || (t == 0 ? n0 : n1) == 0) continue;
+            ok = mbar_wait(smem_u32(&ctl.q_full[t]), q_it[t] & 1, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
+            if (!ok) continue;
+            ++q_it[t];
+            tc_fence_after();
+            if (lane == 0) {
+              issue_qk(t, kst);
               umma_commit(smem_u32(&ctl.s_full[t]));
-            } else {
-              umma_commit(smem_u32(&ctl.o_full[t]));
             }
+            __syncwarp();
           }
+          if (ok && lane == 0) umma_commit(smem_u32(&ctl.k_empty[kst]));
           __syncwarp();
+          ++k_it;
+          for (int j = 0; j < n_max && ok; ++j) {
+            const uint32_t vst = v_it & 1, vph = (v_it >> 1) & 1;
+            ok = mbar_wait(smem_u32(&ctl.v_full[vst]), vph, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
+            if (!ok) break;
+            kst = k_it & 1;
+            kph = (k_it >> 1) & 1;
+            if (j + 1 < n_max) {
+              ok = mbar_wait(smem_u32(&ctl.k_full[kst]), kph, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
+              if (!ok) break;
+            }
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+              const int nt = t == 0 ? n0 : n1;
+              if (!ok || j >= nt) continue;
+              ok = mbar_wait(smem_u32(&ctl.p_full[t]), p_it[t] & 1, abort_flag, p.status, ASC_DEV_TIMEOUT_OTHER);
+              if (!ok) continue;
+              ++p_it[t];
+              tc_fence_after();
+              if (lane == 0) {
+                issue_pv(t, vst, j > 0 ? 1u : 0u);
+                if (j + 1 < nt) {
+                  issue_qk(t, kst);
+                  umma_commit(smem_u32(&ctl.s_full[t]));
+                } else {
+                  umma_commit(smem_u32(&ctl.o_full[t]));
+                  umma_commit(smem_u32(&ctl.q_empty[t]));   // every Q K^T of this item's tile has retired
+                }
+              }
+              __syncwarp();
+            }
+            if (ok && lane == 0) {
+              umma_commit(smem_u32(&ctl.v_empty[vst]));
+              if (j + 1 < n_max) umma_commit(smem_u32(&ctl.k_empty[kst]));
+            }
+            __syncwarp();
+            ++v_it;
+            if (j + 1 < n_max) ++k_it;
+          }
         }
-        if (ok && lane == 0) {
-          umma_commit(smem_u32(&ctl.v_empty[st]));
-          if (j + 1 < n_max) umma_commit(smem_u32(&ctl.k_empty[st_n]));
-        }
-        __syncwarp();
       }
     }
   }
@@ -432,8 +508,13 @@ int32_t launch_attn(const void* q, const void* k, const void* v, AttnParams p, c
   const uint32_t fmt = kBf16 ? 1u : 0u;
   const uint32_t idesc_qk = make_idesc(1, fmt, fmt, 0, 0, kTileQ, kTileKV);
   const uint32_t idesc_pv = make_idesc(1, fmt, fmt, 0, 1, kTileQ, kHeadDim);
-  const int64_t grid = static_cast<int64_t>(p.BH) * p.pairs;
-  if (grid > 0x7fffffff) return ASC_ERR_TOO_LARGE;
+  int sms = 0;
+  if ((rc = aschost::sm_count(&sms)) != ASC_OK) return rc;
+  p.half = (p.pairs + 1) / 2;
+  const int64_t units = static_cast<int64_t>(p.BH) * (p.causal ? p.half : p.pairs);
+  if (units > 0x7fffffff) return ASC_ERR_TOO_LARGE;
+  p.units = static_cast<int32_t>(units);
+  const int64_t grid = units < sms ? units : sms;     // one persistent CTA per SM (shared memory allows one)
   kernel<<<static_cast<unsigned>(grid), kAttnThreads, kAttnSmem, stream>>>(tq, tk, tv, p, idesc_qk, idesc_pv);
   aschost::count_launch();
   ASC_CUDA_TRY(cudaGetLastError());
