@@ -375,28 +375,30 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       }
     } else if (warp == 9) {
       // ------------------------------- MMA issuer -------------------------------
+      // Descriptors are built once: only the start address changes between MMAs, and shared-memory
+      // addresses >> 4 fit the 14-bit address field with room to spare, so adding to the low bits cannot carry.
+      const uint64_t q_desc0 = make_smem_desc_sw128(smem_base + kSmemQ, 16, 1024);
+      const uint64_t k_desc0 = make_smem_desc_sw128(smem_base + kSmemK, 16, 1024);
+      const uint64_t v_desc0 = make_smem_desc_sw128(smem_base + kSmemV, kHalfTile, 1024);
       // S_t = Q_t K_j^T : 8 MMAs of 128 x 128 x 16, both operands K-major (two 64-column halves).
       auto issue_qk = [&](int t, uint32_t k_stage) {
-        const uint32_t qa = smem_base + kSmemQ + t * kTileBytes;
-        const uint32_t kb = smem_base + kSmemK + k_stage * kTileBytes;
+        const uint64_t qd = q_desc0 + static_cast<uint64_t>(t) * (kTileBytes >> 4);
+        const uint64_t kd = k_desc0 + static_cast<uint64_t>(k_stage) * (kTileBytes >> 4);
         const uint32_t d = tmem_base + kColS + t * 128;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t off = (ks >> 2) * kHalfTile + (ks & 3) * 32;
-          umma_f16_ss(d, make_smem_desc_sw128(qa + off, 16, 1024), make_smem_desc_sw128(kb + off, 16, 1024),
-                      idesc_qk, ks > 0 ? 1u : 0u);
+          const uint32_t off = ((ks >> 2) * kHalfTile + (ks & 3) * 32) >> 4;
+          umma_f16_ss(d, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
         }
       };
       // O_t (+)= P_t V_j : P from tensor memory (8 columns per 16 keys), V MN-major as stored.
       auto issue_pv = [&](int t, uint32_t v_stage, uint32_t accumulate) {
-        const uint32_t vb = smem_base + kSmemV + v_stage * kTileBytes;
+        const uint64_t vd = v_desc0 + static_cast<uint64_t>(v_stage) * (kTileBytes >> 4);
         const uint32_t d = tmem_base + kColO + t * 128;
         const uint32_t a = tmem_base + kColS + t * 128;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          umma_f16_ts(d, a + ks * 8, make_smem_desc_sw128(vb + ks * 2048, kHalfTile, 1024), idesc_pv,
-                      (accumulate || ks > 0) ? 1u : 0u);
-        }
+        for (int ks = 0; ks < 8; ++ks)
+          umma_f16_ts(d, a + ks * 8, vd + ((ks * 2048) >> 4), idesc_pv, (accumulate || ks > 0) ? 1u : 0u);
       };
       bool ok = true;
       uint32_t q_it[2] = {0, 0}, p_it[2] = {0, 0}, k_it = 0, v_it = 0;
