@@ -40,9 +40,11 @@ constexpr uint32_t kAttnSmem = 6 * kTileBytes + 1024;
 constexpr uint32_t kColS = 0;    // S_t at columns [128 t, 128 t + 128); P_t aliases its first 64 columns
 constexpr uint32_t kColO = 256;  // O_t at columns [256 + 128 t, ...)
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units
-// Register split after launch (setmaxnreg): the 8 softmax warps grow, the other 4 shrink.  An increase can
-// only take registers a decrease in the same CTA has released, otherwise it waits forever, so the split must
-// fit the launch allocation of 168 registers x 384 threads (what __launch_bounds__(384, 1) compiles to).
+// Register split after launch (setmaxnreg): the 8 softmax warps grow, the other 4 shrink.  setmaxnreg is a
+// warpgroup-wide instruction: the four warps of a warpgroup (0-3, 4-7, 8-11) must all execute the same one.
+// An increase can only take registers a decrease in the same CTA has released, otherwise it waits forever,
+// so the split must fit the launch allocation of 168 registers x 384 threads (what __launch_bounds__(384, 1)
+// compiles to; check "Used 168 registers" in the ptxas output after changing the kernel).
 constexpr int kLaunchRegs = 168, kSoftmaxRegs = 208, kOtherRegs = 88;
 static_assert(8 * kSoftmaxRegs + 4 * kOtherRegs <= 12 * kLaunchRegs, "register split exceeds the launch allocation");
 
