@@ -506,6 +506,11 @@ int32_t launch_attn(const void* q, const void* k, const void* v, AttnParams p, c
   int dev = 0;
   ASC_CUDA_TRY(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    // the register split inside the kernel must fit what the kernel is launched with, or its first
+    // setmaxnreg increase would wait forever: refuse to launch a build where it does not
+    cudaFuncAttributes fa{};
+    ASC_CUDA_TRY(cudaFuncGetAttributes(&fa, kernel));
+    if (12 * fa.numRegs < 8 * kSoftmaxRegs + 4 * kOtherRegs) return ASC_ERR_UNSUPPORTED;
     ASC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
     attr_set[dev] = true;
   }
