@@ -44,7 +44,7 @@ import torch  # noqa: E402
 
 HEADLINE = "softmax"
 ALL_WORKLOADS = ["softmax", "vadd", "gemm_f16", "gemm_i8", "gemm_i8_dequant", "attention", "attention_causal",
-                 "gelu", "gelu_tanh", "leaky_relu_bf16", "silu_interpreted", "row_sum"]
+                 "gelu", "gelu_tanh", "leaky_relu_bf16", "mish_interpreted", "row_sum"]
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -424,10 +424,10 @@ class GeluTanh(Gelu):
     cpu_sample_desc = "the tanh-form GELU expression in torch on 4096 of the 16384 rows"
 
 
-class SiluInterpreted(Gelu):
-    """x / (exp(-x) + 1): an expression without a compiled instance, so the interpreter runs it."""
-    name, label = "silu_interpreted", "silu_f32_16384x4096_interpreter"
-    cpu_sample_desc = "x / (exp(-x) + 1) in torch on 4096 of the 16384 rows"
+class MishInterpreted(Gelu):
+    """x * tanh(log(exp(x) + 1)): an expression without a compiled instance, so the interpreter runs it."""
+    name, label = "mish_interpreted", "mish_f32_16384x4096_interpreter"
+    cpu_sample_desc = "x * tanh(log(exp(x) + 1)) in torch on 4096 of the 16384 rows"
 
     @staticmethod
     def kernel():
@@ -436,14 +436,14 @@ class SiluInterpreted(Gelu):
         import asc2
 
         @asc2.jit
-        def silu_kernel(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, num_rows: asc.ConstExpr,
+        def mish_kernel(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, num_rows: asc.ConstExpr,
                         num_columns: asc.ConstExpr):
             x_gm = asc2.tensor(x_ptr, [num_rows, num_columns])
             out_gm = asc2.tensor(out_ptr, [num_rows, num_columns])
             for i in range(asc2.block_idx(), num_rows, asc2.block_num()):
                 row = asc2.load(x_gm, [1, num_columns], offsets=[i, 0])
-                asc2.store(row / (asc2.exp(-row) + 1), out_gm, offsets=[i, 0])
-        return silu_kernel
+                asc2.store(row * asc2.tanh(asc2.log(asc2.exp(row) + 1)), out_gm, offsets=[i, 0])
+        return mish_kernel
 
     def setup_device(self, dev):
         g = torch.Generator(device=dev).manual_seed(2026)
@@ -460,7 +460,7 @@ class SiluInterpreted(Gelu):
     def cpu_sample(self):
         if not hasattr(self, "cx"):
             self.cx = torch.rand((self.CPU_R, self.C), generator=torch.Generator().manual_seed(2026)) * 6 - 3
-        _ = self.cx / (torch.exp(-self.cx) + 1)
+        _ = self.cx * torch.tanh(torch.log(torch.exp(self.cx) + 1))
         return 2.0 * 4 * self.CPU_R * self.C
 
 
@@ -549,7 +549,7 @@ class LeakyReluBF16(_Elementwise):
 
 
 REGISTRY = {w.name: w for w in (Softmax, VAdd, GemmF16, GemmI8, GemmI8Dequant, Attention, AttentionCausal, Gelu, GeluTanh,
-                                LeakyReluBF16, SiluInterpreted, RowSum)}
+                                LeakyReluBF16, MishInterpreted, RowSum)}
 
 
 # ---------------------------------------------------------------------------------------------------

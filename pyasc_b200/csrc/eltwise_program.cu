@@ -547,6 +547,10 @@ using GeluTanh = OpList<LD(0), LD(0), OP_MUL, OP_MUL | I, OP_ADD | I, LD(0), OP_
 
 int elem_size(int type) { return (type == T_F16 || type == T_BF16 || type == T_I16) ? 2 : 4; }
 
+// 1 / (1 + exp(-x)) and x / (exp(-x) + 1): the usual spellings of sigmoid and SiLU
+using Sigmoid = OpList<LD(0), OP_NEG, OP_EXP, OP_ADD | I, OP_DIV | I>;
+using Silu = OpList<LD(0), LD(0), OP_NEG, OP_EXP, OP_ADD | I, OP_DIV>;
+
 template <class P>
 bool matches(const int32_t* ops, const int32_t* args, int n_ops) {
   if (n_ops != P::n) return false;
@@ -658,6 +662,8 @@ extern "C" int32_t asc_cuda_eltwise_program_2d(const int32_t* ops, const int32_t
     if (rc == ASC_OK) rc = try_compiled<LeakyReluBF16>(prog, ops, args, n_ops, n, sms, st, &launched);
     if (rc == ASC_OK) rc = try_compiled<GeluErf>(prog, ops, args, n_ops, n, sms, st, &launched);
     if (rc == ASC_OK) rc = try_compiled<GeluTanh>(prog, ops, args, n_ops, n, sms, st, &launched);
+    if (rc == ASC_OK) rc = try_compiled<Sigmoid>(prog, ops, args, n_ops, n, sms, st, &launched);
+    if (rc == ASC_OK) rc = try_compiled<Silu>(prog, ops, args, n_ops, n, sms, st, &launched);
     if (launched || rc != ASC_OK) return rc;
   }
   // more elements per dispatch amortise the dispatch of long programs (measured: 7 ops 4.2 vs 3.8 TB/s, 13 ops

@@ -175,3 +175,24 @@ def test_golden_fixture_through_compiled_programs(golden_dir):
     ol = torch.empty_like(xl)
     K.leaky_relu[16](xl, alpha, ol, 8192, 128, 4)
     assert torch.equal(evaluate(K.leaky_relu, [xl, alpha, ol, 8192]), torch.from_numpy(d["leaky_out"]).view(torch.bfloat16))
+
+
+def test_sigmoid_and_silu_compile_to_the_specialised_programs():
+    """The library has compile-time instances for exactly these opcode sequences."""
+    @asc2.jit
+    def sigmoid(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+        x = asc2.load(asc2.tensor(x_ptr, [n]), [n], offsets=[0])
+        asc2.store(1 / (1 + asc2.exp(-x)), asc2.tensor(out_ptr, [n]), offsets=[0])
+
+    @asc2.jit
+    def silu(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+        x = asc2.load(asc2.tensor(x_ptr, [n]), [n], offsets=[0])
+        asc2.store(x / (asc2.exp(-x) + 1), asc2.tensor(out_ptr, [n]), offsets=[0])
+    x = torch.linspace(-6, 6, 256)
+    out = torch.empty_like(x)
+    sigmoid[1](x, out, 256)
+    assert decode(sigmoid.last_plan.steps[0])[0] == [0, 8, 11, 2 | 0x100, 5 | 0x100]
+    torch.testing.assert_close(evaluate(sigmoid, [x, out]), torch.sigmoid(x), rtol=1e-6, atol=1e-7)
+    silu[1](x, out, 256)
+    assert decode(silu.last_plan.steps[0])[0] == [0, 0, 8, 11, 2 | 0x100, 5]
+    torch.testing.assert_close(evaluate(silu, [x, out]), torch.nn.functional.silu(x), rtol=1e-6, atol=1e-6)

@@ -169,6 +169,8 @@ IMM = 0x100
     ("gelu_erf", torch.float32, 0, [0, 0, 4 | IMM, 23, 2 | IMM, 4, 4 | IMM], {2: 0.5 ** 0.5, 4: 1.0, 6: 0.5}),
     ("gelu_tanh", torch.float32, 0, [0, 0, 4, 4 | IMM, 2 | IMM, 0, 4, 11, 2 | IMM, 0, 55, 0, 54],
      {3: 0.0713548, 4: 1.5957691, 8: 1.0}),
+    ("sigmoid", torch.float32, 0, [0, 8, 11, 2 | IMM, 5 | IMM], {3: 1.0, 4: 1.0}),
+    ("silu", torch.float32, 0, [0, 0, 8, 11, 2 | IMM, 5], {4: 1.0}),
 ], ids=lambda v: str(v) if isinstance(v, (str, torch.dtype)) else "")
 def test_compiled_programs_equal_the_interpreter(lib, name, dtype, out_type, ops, imms):
     """The programs that have a compile-time specialised kernel must give bit-identical results in both
