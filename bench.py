@@ -44,7 +44,7 @@ import torch  # noqa: E402
 
 HEADLINE = "softmax"
 ALL_WORKLOADS = ["softmax", "vadd", "gemm_f16", "gemm_i8", "gemm_i8_dequant", "attention", "attention_causal",
-                 "gelu", "gelu_tanh", "leaky_relu_bf16", "mish_interpreted", "row_sum"]
+                 "gelu", "gelu_tanh", "leaky_relu_bf16", "mish_interpreted", "row_sum", "rms_norm"]
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -513,6 +513,62 @@ class RowSum(Workload):
         return 4.0 * self.CPU_R * self.C
 
 
+class RmsNorm(Workload):
+    """asc2.rms_norm over the rows of [16384, 4096] fp32 (256 MiB read, 256 MiB written, gamma resident)."""
+    name, label, dtype = "rms_norm", "rms_norm_f32_16384x4096", "f32"
+    R, C = 16384, 4096
+    EPS = 1e-5
+    work = 2.0 * 4 * R * C
+    h2d_bytes, d2h_bytes = 4 * R * C + 4 * C, 4 * R * C
+    CPU_R = 4096
+    cpu_sample_desc = "x * rsqrt(mean(x^2, 1) + eps) * gamma in torch on 4096 of the 16384 rows"
+
+    def setup_device(self, dev):
+        g = torch.Generator(device=dev).manual_seed(2026)
+        self.x = torch.randn((self.R, self.C), device=dev, generator=g)
+        self.gamma = torch.rand((1, self.C), device=dev, generator=g) + 0.5
+        self.out = torch.empty_like(self.x)
+
+    def launch(self, lib, stream):
+        return lib.asc_cuda_rms_norm_f32(P(self.x), P(self.gamma), P(self.out), self.R, self.C, self.C, self.EPS, stream)
+
+    @staticmethod
+    def kernel():
+        import pyasc_b200  # noqa: F401  (makes `asc` / `asc2` importable)
+        import asc
+        import asc2
+
+        @asc2.jit
+        def rms_norm_kernel(x_ptr: asc.GlobalAddress, gamma_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress,
+                            num_rows: int, num_cols: asc.ConstExpr[int], rows_per_tile: asc.ConstExpr[int],
+                            epsilon: float):
+            x_gm = asc2.tensor(x_ptr, [num_rows, num_cols])
+            out_gm = asc2.tensor(out_ptr, [num_rows, num_cols])
+            gamma = asc2.load(asc2.tensor(gamma_ptr, [1, num_cols]), [1, num_cols], offsets=[0, 0])
+            for i in range(asc2.block_idx() * rows_per_tile, num_rows, asc2.block_num() * rows_per_tile):
+                tile = asc2.load(x_gm, [rows_per_tile, num_cols], offsets=[i, 0])
+                asc2.store(asc2.rms_norm(tile, gamma, epsilon), out_gm, offsets=[i, 0])
+        return rms_norm_kernel
+
+    def setup_host(self):
+        g = torch.Generator().manual_seed(2026)
+        self.hx = torch.randn((self.R, self.C), generator=g).pin_memory()
+        self.hgamma = (torch.rand((1, self.C), generator=g) + 0.5).pin_memory()
+        self.hout = torch.empty_like(self.hx).pin_memory()
+        self.k = self.kernel()
+
+    def e2e_step(self):
+        self.k[148](self.hx, self.hgamma, self.hout, self.R, self.C, 4, self.EPS)
+
+    def cpu_sample(self):
+        if not hasattr(self, "cx"):
+            g = torch.Generator().manual_seed(2026)
+            self.cx = torch.randn((self.CPU_R, self.C), generator=g)
+            self.cg = torch.rand((1, self.C), generator=g) + 0.5
+        _ = self.cx * torch.rsqrt(self.cx.pow(2).mean(1, keepdim=True) + self.EPS) * self.cg
+        return 2.0 * 4 * self.CPU_R * self.C
+
+
 class LeakyReluBF16(_Elementwise):
     name, label, dtype = "leaky_relu_bf16", "leaky_relu_bf16_2^28", "bf16"
     N = 1 << 28
@@ -549,7 +605,7 @@ class LeakyReluBF16(_Elementwise):
 
 
 REGISTRY = {w.name: w for w in (Softmax, VAdd, GemmF16, GemmI8, GemmI8Dequant, Attention, AttentionCausal, Gelu, GeluTanh,
-                                LeakyReluBF16, MishInterpreted, RowSum)}
+                                LeakyReluBF16, MishInterpreted, RowSum, RmsNorm)}
 
 
 # ---------------------------------------------------------------------------------------------------

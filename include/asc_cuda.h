@@ -171,6 +171,14 @@ int32_t asc_cuda_softmax_f32(const float* x, float* out, int64_t rows, int64_t c
  * python/test/asc2/operations/test_softmax.py:35-58): fp32 arithmetic, one rounding at the store. */
 int32_t asc_cuda_softmax_f16(const void* x, void* out, int64_t rows, int64_t cols, int64_t ld, void* stream);
 
+/* RMS normalisation over the last dimension of a row-major fp32 window [rows, cols] with row pitch ld:
+ *   out[r, c] = x[r, c] / sqrt(mean_c(x[r, :]^2) + eps) * gamma[c]
+ * Replaces asc2.rms_norm (python/asc/language/tile/unary_ops.py:225-237), which the reference lowers to the
+ * Ascend C RmsNorm routine with a generated tiling (lib/Conversion/LowerToAsc/LowerAscTile.cpp:190-289).
+ * x and out may alias; gamma holds cols floats.  Empty windows return ASC_OK without a launch. */
+int32_t asc_cuda_rms_norm_f32(const float* x, const float* gamma, float* out, int64_t rows, int64_t cols, int64_t ld,
+                              float eps, void* stream);
+
 /* C[M,N] = epilogue(A[M,K] @ B[K,N]), row-major operands, fp32 accumulation on tcgen05 tensor
  * cores.  in_dtype: 0 fp16, 1 bf16.  out_dtype: 0 fp16, 1 bf16, 2 fp32.
  * flags: bit0 ReLU before the cast; bit1 accumulate into C (C += A@B, fp32 out only).

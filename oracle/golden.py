@@ -91,6 +91,14 @@ def softmax(x: torch.Tensor) -> torch.Tensor:
     return torch.softmax(x, dim=-1)
 
 
+def rms_norm(x: torch.Tensor, gamma: torch.Tensor, eps: float) -> torch.Tensor:
+    """x / sqrt(mean(x^2, last dim) + eps) * gamma in fp32: the formula of the Ascend C RmsNorm routine that
+    asc2.rms_norm lowers to (python/asc/language/tile/unary_ops.py:225-237; the tiling's
+    ``reciprocalOfHLength`` = 1 / row length, lib/Conversion/LowerToAsc/LowerAscTile.cpp:223)."""
+    x = x.float()
+    return x * torch.rsqrt(x.pow(2).mean(dim=-1, keepdim=True) + eps) * gamma.float().reshape(-1)
+
+
 def gemm_f32acc(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     """python/test/asc2/kernels/test_matmul_tiled.py:49 — fp32 product of the up-cast operands."""
     return a.to(torch.float32) @ b.to(torch.float32)

@@ -1027,6 +1027,96 @@ def _match_softmax(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
 
 
 # --------------------------------------------------------------------------------------------------
+# Pattern: RMS normalisation of whole rows
+# --------------------------------------------------------------------------------------------------
+def _match_rms_norm(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
+    """``store(rms_norm(load(x rows), load(gamma), eps))`` at the rows it was loaded from -> one fused row
+    kernel per contiguous row range (python/asc/language/tile/unary_ops.py:225-237; the reference lowers to
+    the Ascend C RmsNorm routine, lib/Conversion/LowerToAsc/LowerAscTile.cpp:190-289)."""
+    value, out_t = eff.args
+    node = _node(value, "rms_norm") if isinstance(value, Tile) else None
+    if node is None:
+        return None
+    src, gamma, eps = node.args
+    if value.dtype != KT.float32 or out_t.dtype != KT.float32 or gamma.dtype != KT.float32:
+        raise _unsupported(f"rms_norm on {value.dtype} tiles (float32 only)")
+    view = resolve_view(src) if _node(src, "load") else None
+    gview = resolve_view(gamma) if _node(gamma, "load") else None
+    if view is None or gview is None:
+        raise _unsupported("rms_norm of tiles that are not loaded directly from global memory")
+    if not eps.is_const:
+        raise _unsupported("rms_norm with an epsilon that varies between blocks or iterations")
+    if not _same_offsets(view.offsets, eff.attrs["offsets"]) or view.shape != value.shape:
+        raise _unsupported("rms_norm stored at a different position than it was loaded from")
+    if view.tensor.static_shape() != out_t.static_shape() or view.tensor.dtype != KT.float32:
+        raise _unsupported("rms_norm between tensors of different shapes or types")
+    _check_fits(out_t)
+    _check_fits(view.tensor)
+    _check_fits(gview.tensor)
+    R, C = _row_major_2d(out_t)
+    tile_rows = 1 if len(value.shape) == 1 else value.shape[0]
+    tile_cols = value.shape[-1]
+    g_elems = 1
+    for d in gamma.shape:
+        g_elems *= d
+    if gamma.shape[-1] != tile_cols or g_elems != tile_cols:
+        raise _unsupported("rms_norm with a gamma tile that is not one row of the input's width")
+    if tile_cols != C:
+        # the mean runs over the tile's row; a window of a wider row would need a second pitch
+        raise _unsupported("rms_norm of tiles narrower or wider than the tensor row")
+    env = enumerate_instances(trace.core_num, eff.loops)
+    n = env_count(env)
+    row_off = PlainValue.const(0) if len(value.shape) == 1 else view.offsets[0]
+    col_off = view.offsets[-1]
+    r0 = eval_int(row_off, env, n)
+    c0 = eval_int(col_off, env, n)
+    if len(value.shape) == 1:       # a 1-D tensor of C elements is one row
+        r0 = c0 // max(C, 1)
+        c0 = c0 % max(C, 1)
+    if n and (r0.min() < 0 or c0.min() < 0):
+        raise RuntimeError("Negative tile offset in kernel")
+    if n and c0.max() != 0:
+        raise _unsupported("rms_norm tiles that do not start at the beginning of a row")
+    g_off = np.zeros(n, dtype=np.int64)
+    g_cols = gview.tensor.static_shape()[-1]
+    for d, off in enumerate(gview.offsets):
+        o = eval_int(off, env, n)
+        if d < len(gview.offsets) - 1:
+            o = o * g_cols       # gamma held as a [1, C] (or [k, C]) tensor
+            if len(gview.offsets) > 2:
+                raise _unsupported("rms_norm with gamma loaded from a tensor of rank above 2")
+        g_off += o
+    if n and (g_off.min() < 0 or not np.all(g_off == g_off[0])):
+        raise _unsupported("rms_norm with gamma loaded from varying positions")
+    gamma_off = int(g_off[0]) if n else 0
+    if gamma_off + tile_cols > gview.tensor.base.numel:
+        raise _unsupported("rms_norm with a gamma tile reaching past its tensor (zero padding)")
+    intervals = merge_intervals(r0, np.minimum(r0 + tile_rows, R))
+    if len(intervals) > MAX_CALLS:
+        raise _unsupported("rms_norm kernel touching more than 4096 disjoint row ranges")
+    plan = Plan("rms_norm")
+    in_idx, out_idx, g_idx = view.tensor.base.index, out_t.base.index, gview.tensor.base.index
+    plan.reads.update((in_idx, g_idx))
+    plan.writes.add(out_idx)
+    if not (intervals == [(0, R)] and R * C == out_t.base.numel):
+        plan.partial_writes.add(out_idx)
+    epsilon = float(eps.value)
+
+    def make(lo: int, hi: int) -> List[Step]:
+        def build(ptrs, stream, lo=lo, hi=hi):
+            byte_off = 4 * lo * C
+            return (_p(ptrs[in_idx] + byte_off), _p(ptrs[g_idx] + 4 * gamma_off), _p(ptrs[out_idx] + byte_off),
+                    ctypes.c_int64(hi - lo), ctypes.c_int64(C), ctypes.c_int64(C), ctypes.c_float(epsilon), stream)
+        return [Step("asc_cuda_rms_norm_f32", build, f"rows [{lo}, {hi}) x {C} cols")]
+
+    for lo, hi in intervals:
+        plan.steps += make(lo, hi)
+    if not plan.partial_writes and g_idx not in (in_idx, out_idx):
+        plan.pipeline = PipelineSpec(R, 1, {in_idx: 4 * C, out_idx: 4 * C}, {g_idx}, make)
+    return plan
+
+
+# --------------------------------------------------------------------------------------------------
 # Pattern: matmul (+ K loop with matmul_acc) with a fused store epilogue
 # --------------------------------------------------------------------------------------------------
 class _Epilogue:
@@ -1440,7 +1530,7 @@ def _match_attention(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
 # --------------------------------------------------------------------------------------------------
 # Entry point
 # --------------------------------------------------------------------------------------------------
-_MATCHERS = (_match_attention, _match_softmax, _match_elementwise, _match_matmul, _match_eltwise_program,
+_MATCHERS = (_match_attention, _match_softmax, _match_rms_norm, _match_elementwise, _match_matmul, _match_eltwise_program,
              _match_reduce)
 
 

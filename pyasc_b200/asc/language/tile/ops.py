@@ -221,6 +221,10 @@ def softmax(input: Tile) -> Tile:
 def rms_norm(input: Tile, gamma: Tile, epsilon: Any) -> Tile:
     if not isinstance(input, Tile) or not isinstance(gamma, Tile):
         raise RuntimeError("'rms_norm' expects tiles")
+    if input.dtype not in (KT.float32, KT.float16) or gamma.dtype != input.dtype:
+        raise RuntimeError(f"'rms_norm' supports float32 and float16 tiles of one type, got {input.dtype} and {gamma.dtype}")
+    if len(input.shape) > 2:
+        raise RuntimeError("'rms_norm' supports 1-D and 2-D tiles")
     return Tile(input.shape, input.dtype, trace.current().node("rms_norm", input, gamma, _scalar(epsilon)))
 
 

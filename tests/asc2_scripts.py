@@ -360,3 +360,23 @@ def add_row_bias(x_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, out_ptr: as
     for i in range(asc2.block_idx() * rows_per_tile, rows, asc2.block_num() * rows_per_tile):
         x = asc2.load(x_gm, [rows_per_tile, cols], offsets=[i, 0])
         asc2.store(asc2.relu(x + asc2.broadcast_to(bias, rows_per_tile, cols)), out_gm, offsets=[i, 0])
+
+
+# ---- RMS normalisation (asc2.rms_norm, python/asc/language/tile/unary_ops.py:225-237)
+@asc2.jit
+def rms_norm_rows(x_ptr: asc.GlobalAddress, gamma_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, num_rows: int,
+                  num_cols: asc.ConstExpr[int], block_size: asc.ConstExpr[int], epsilon: float):
+    x_gm = asc2.tensor(x_ptr, [num_rows, num_cols])
+    out_gm = asc2.tensor(out_ptr, [num_rows, num_cols])
+    gamma = asc2.load(asc2.tensor(gamma_ptr, [1, num_cols]), [1, num_cols], offsets=[0, 0])
+    for r0 in asc2.range(asc2.block_idx() * block_size, num_rows, asc2.block_num() * block_size):
+        x = asc2.load(x_gm, [block_size, num_cols], offsets=[r0, 0])
+        asc2.store(asc2.rms_norm(x, gamma, epsilon), out_gm, offsets=[r0, 0])
+
+
+@asc2.jit
+def rms_norm_1d(x_ptr: asc.GlobalAddress, gamma_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress,
+                length: asc.ConstExpr[int]):
+    x = asc2.load(asc2.tensor(x_ptr, [length]), [length], offsets=[0])
+    gamma = asc2.load(asc2.tensor(gamma_ptr, [length]), [length], offsets=[0])
+    asc2.store(asc2.rms_norm(x, gamma, 1e-6), asc2.tensor(out_ptr, [length]), offsets=[0])

@@ -11,6 +11,7 @@ import asc.runtime.config as config
 import asc2
 
 import asc2_scripts as K
+from oracle import golden
 from pyasc_b200 import capi
 
 pytestmark = pytest.mark.gpu
@@ -195,3 +196,60 @@ def test_capi_softmax_f16(lib, rows, cols):
     want = torch.softmax(x[:, :cols].float(), dim=1).half()
     torch.testing.assert_close(out[:, :cols], want, rtol=1e-3, atol=1e-6)
     assert bool((out[:, cols] == 9.0).all())
+
+
+# ------------------------------------------------------------------------------- RMS normalisation
+@pytest.mark.parametrize("rows, cols, block, blocks", [(64, 256, 8, 4), (4096, 1024, 8, 16), (96, 8192, 1, 3),
+                                                       (24, 8, 8, 1)])
+def test_rms_norm_rows_kernel(rows, cols, block, blocks):
+    gen = torch.Generator().manual_seed(rows + cols)
+    x = torch.randn(rows, cols, generator=gen) * 3
+    gamma = torch.rand(1, cols, generator=gen) + 0.5
+    out = torch.zeros_like(x)
+    K.rms_norm_rows[blocks](x, gamma, out, rows, cols, block, 1e-5)
+    torch.testing.assert_close(out, golden.rms_norm(x, gamma, 1e-5), rtol=1e-5, atol=1e-6)
+
+
+def test_rms_norm_1d_and_device_tensors():
+    x = torch.randn(1024)
+    gamma = torch.rand(1024)
+    out = torch.zeros(1024)
+    K.rms_norm_1d[1](x, gamma, out, 1024)
+    torch.testing.assert_close(out, golden.rms_norm(x, gamma, 1e-6), rtol=1e-5, atol=1e-6)
+    xd, gd = torch.randn(512, 2048, device="cuda"), torch.rand(1, 2048, device="cuda")
+    od = torch.empty_like(xd)
+    K.rms_norm_rows[8](xd, gd, od, 512, 2048, 4, 1e-6)
+    torch.testing.assert_close(od.cpu(), golden.rms_norm(xd.cpu(), gd.cpu(), 1e-6), rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("rows, cols, pad", [(1, 1, 0), (7, 33, 3), (300, 1000, 0), (129, 4096, 4), (33, 8192, 0),
+                                             (5, 20000, 0), (9, 16384, 8), (32768, 2048, 0)])
+def test_capi_rms_norm(lib, rows, cols, pad):
+    """Every register depth of the vector kernel, the two-read kernel (long, ragged or unaligned rows), pitched
+    rows, and a 256 MiB matrix (beyond L2); in place as well."""
+    gen = torch.Generator(device="cuda").manual_seed(rows * 7 + cols)
+    ld = cols + pad
+    buf = torch.randn(rows, ld, device="cuda", generator=gen) * 2
+    gamma = torch.rand(cols, device="cuda", generator=gen) + 0.25
+    out = torch.full((rows, ld), -7.0, device="cuda")
+    x = buf[:, :cols]
+    rc = lib.asc_cuda_rms_norm_f32(ctypes.c_void_p(buf.data_ptr()), ctypes.c_void_p(gamma.data_ptr()),
+                                   ctypes.c_void_p(out.data_ptr()), rows, cols, ld, 1e-5, None)
+    assert rc == 0, capi.status_string(rc)
+    capi.check_device_status(None)
+    ref = golden.rms_norm(x.double(), gamma.double(), 1e-5) if rows * cols < (1 << 22) else golden.rms_norm(x, gamma, 1e-5)
+    torch.testing.assert_close(out[:, :cols], ref.float(), rtol=1e-5, atol=1e-6)
+    assert pad == 0 or bool((out[:, cols:] == -7.0).all())          # the pitch padding is untouched
+    keep = buf.clone()
+    rc = lib.asc_cuda_rms_norm_f32(ctypes.c_void_p(buf.data_ptr()), ctypes.c_void_p(gamma.data_ptr()),
+                                   ctypes.c_void_p(buf.data_ptr()), rows, cols, ld, 1e-5, None)
+    assert rc == 0
+    assert torch.equal(buf[:, :cols], out[:, :cols]) and torch.equal(buf[:, cols:], keep[:, cols:])
+
+
+def test_capi_rms_norm_rejects_bad_arguments(lib):
+    x = torch.zeros(4, 8, device="cuda")
+    p = ctypes.c_void_p(x.data_ptr())
+    assert lib.asc_cuda_rms_norm_f32(p, p, p, 4, 8, 4, 1e-5, None) == 1     # invalid argument: pitch < cols
+    assert lib.asc_cuda_rms_norm_f32(p, None, p, 4, 8, 8, 1e-5, None) == 1
+    assert lib.asc_cuda_rms_norm_f32(None, None, None, 0, 8, 8, 1e-5, None) == 0                   # empty

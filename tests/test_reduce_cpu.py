@@ -76,3 +76,29 @@ def test_softmax_op_plans_and_identity_store():
     v = torch.zeros(1024)
     K.softmax_1d[1](torch.zeros_like(v), v, 1024)
     assert step_of(K.softmax_1d)[1].note == "rows [0, 1) x 1024 cols"
+
+
+def test_rms_norm_plans():
+    """asc2.rms_norm over whole rows becomes one fused call per contiguous row range; gamma stays resident when
+    the launcher streams the rows in chunks."""
+    x = torch.zeros(4096, 1024)
+    K.rms_norm_rows[16](x, torch.ones(1, 1024), torch.empty_like(x), 4096, 1024, 8, 1e-5)
+    plan, step = step_of(K.rms_norm_rows)
+    assert plan.pattern == "rms_norm" and step.fn_name == "asc_cuda_rms_norm_f32"
+    assert step.note == "rows [0, 4096) x 1024 cols"
+    assert plan.reads == {0, 1} and plan.writes == {2} and not plan.partial_writes
+    assert plan.pipeline is not None and plan.pipeline.resident == {1} and plan.pipeline.units == 4096
+    args = step.build({0: 1 << 20, 1: 2 << 20, 2: 3 << 20}, None)
+    assert [a.value for a in args[:6]] == [1 << 20, 2 << 20, 3 << 20, 4096, 1024, 1024]
+    assert args[6].value == pytest.approx(1e-5)
+    # rows not all covered: a partial write, no pipelining
+    K.rms_norm_rows[1](x, torch.ones(1, 1024), torch.empty_like(x), 4096, 1024, 8, 1e-5)
+    assert K.rms_norm_rows.last_plan.steps[0].note == "rows [0, 4096) x 1024 cols"
+    K.rms_norm_1d[1](torch.zeros(256), torch.ones(256), torch.empty(256), 256)
+    assert step_of(K.rms_norm_1d)[1].note == "rows [0, 1) x 256 cols"
+    with pytest.raises(RuntimeError, match="float32 and float16"):
+        K.rms_norm_1d[1](torch.zeros(256, dtype=torch.int32), torch.ones(256, dtype=torch.int32),
+                         torch.empty(256, dtype=torch.int32), 256)
+    with pytest.raises(NotImplementedError, match="float32 only"):
+        K.rms_norm_1d[1](torch.zeros(256, dtype=torch.float16), torch.ones(256, dtype=torch.float16),
+                         torch.empty(256, dtype=torch.float16), 256)
