@@ -1541,12 +1541,36 @@ def _is_identity_store(eff: Effect) -> bool:
             and view.tensor.static_shape() == out_t.static_shape() and _same_offsets(view.offsets, eff.attrs["offsets"]))
 
 
+def _split_concat_store(eff: Effect) -> List[Effect]:
+    """A store of ``concat(a, b, ...)`` (python/asc/language/tile/creation_ops.py:56-72: tiles joined along the
+    first dimension) writes each part at its row offset inside the stored window, so it is planned as one store
+    per part; nested concats unfold the same way."""
+    value, out_t = eff.args
+    if not isinstance(value, Tile) or value.node.kind != "concat":
+        return [eff]
+    parts = []
+    row = 0
+    offsets = eff.attrs["offsets"]
+    for part in value.node.args:
+        attrs = dict(eff.attrs)
+        attrs["offsets"] = (offsets[0] + row, ) + tuple(offsets[1:])
+        kind = "store_scalar" if part.size == 1 else "store"
+        parts += _split_concat_store(Effect(kind, (part, out_t), attrs, eff.loops))
+        row += part.shape[0]
+    return parts
+
+
 def build_plan(trace: KernelTrace) -> Plan:
     """The C-ABI calls that reproduce the traced kernel's effect on global memory."""
     def is_store(e: Effect) -> bool:
         # scalars and one-element tiles go through the scalar form of asc2.store: a store of one element
         return e.kind in ("store", "store_scalar")
-    stores = [e for e in trace.effects if is_store(e) or e.kind == "atomic"]
+    stores = []
+    for e in trace.effects:
+        if e.kind == "store":
+            stores += _split_concat_store(e)
+        elif is_store(e) or e.kind == "atomic":
+            stores.append(e)
     others = [e for e in trace.effects if not is_store(e) and e.kind not in ("matmul_acc", "atomic")]
     if others:
         raise _unsupported(f"'{others[0].kind}' side effect")

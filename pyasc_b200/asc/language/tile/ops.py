@@ -304,10 +304,12 @@ def zeros_acc(shape, dtype: DataType) -> Tile:
 
 def concat(*inputs: Tile) -> Tile:
     if not inputs or not all(isinstance(t, Tile) for t in inputs):
-        raise RuntimeError("'concat' expects tiles")
+        raise RuntimeError("All input arguments must be tiles")
     first = inputs[0]
-    if any(t.dtype != first.dtype or t.shape[1:] != first.shape[1:] for t in inputs):
-        raise RuntimeError("'concat' expects tiles of one dtype that differ in the first dim only")
+    if any(t.shape[1:] != first.shape[1:] for t in inputs):
+        raise RuntimeError("All tiles must have the same shape except their first dimension")
+    if any(t.dtype != first.dtype for t in inputs):
+        raise RuntimeError("All tiles must have the same dtype")
     shape = (sum(t.shape[0] for t in inputs), ) + first.shape[1:]
     return Tile(shape, first.dtype, trace.current().node("concat", *inputs))
 

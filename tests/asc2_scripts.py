@@ -380,3 +380,24 @@ def rms_norm_1d(x_ptr: asc.GlobalAddress, gamma_ptr: asc.GlobalAddress, out_ptr:
     x = asc2.load(asc2.tensor(x_ptr, [length]), [length], offsets=[0])
     gamma = asc2.load(asc2.tensor(gamma_ptr, [length]), [length], offsets=[0])
     asc2.store(asc2.rms_norm(x, gamma, 1e-6), asc2.tensor(out_ptr, [length]), offsets=[0])
+
+
+# ---- concat (asc2.concat, python/asc/language/tile/creation_ops.py:56-72): tiles joined along the first dimension
+@asc2.jit
+def concat_rows(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows_a: asc.ConstExpr[int],
+                rows_b: asc.ConstExpr[int], cols: asc.ConstExpr[int], blocks_rows: asc.ConstExpr[int]):
+    """Every block joins ``blocks_rows`` rows of a (doubled) with the matching rows of b and stores them as one tile."""
+    a_gm = asc2.tensor(a_ptr, [rows_a, cols])
+    b_gm = asc2.tensor(b_ptr, [rows_b, cols])
+    out_gm = asc2.tensor(out_ptr, [rows_a + rows_b, cols])
+    i = asc2.block_idx() * blocks_rows
+    a = asc2.load(a_gm, [blocks_rows, cols], offsets=[i, 0])
+    b = asc2.load(b_gm, [blocks_rows, cols], offsets=[i, 0])
+    asc2.store(asc2.concat(a * 2, b), out_gm, offsets=[2 * i, 0])
+
+
+@asc2.jit
+def concat_1d(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+    a = asc2.load(asc2.tensor(a_ptr, [n]), [n], offsets=[0])
+    b = asc2.load(asc2.tensor(b_ptr, [n]), [n], offsets=[0])
+    asc2.store(asc2.concat(a, asc2.concat(b, a + b)), asc2.tensor(out_ptr, [3 * n]), offsets=[0])

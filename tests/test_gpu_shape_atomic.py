@@ -56,3 +56,17 @@ def test_bias_row_broadcast(rows, cols, rows_per_tile, cores):
     out = torch.full_like(x, -3.0)
     K.add_row_bias[cores](x, b, out, rows, cols, rows_per_tile)
     assert torch.equal(out, torch.relu(x + b))
+
+
+def test_concat_rows_and_nested_concat():
+    """asc2.concat joins tiles along the first dimension; the stored parts land at their row offsets."""
+    gen = torch.Generator().manual_seed(11)
+    a, b = torch.randn(32, 64, generator=gen), torch.randn(32, 64, generator=gen)
+    out = torch.full((64, 64), -1.0)
+    K.concat_rows[4](a, b, out, 32, 32, 64, 8)
+    ref = torch.cat([torch.cat([2 * a[i:i + 8], b[i:i + 8]]) for i in range(0, 32, 8)])
+    assert torch.equal(out, ref)
+    x, y = torch.randn(64, generator=gen), torch.randn(64, generator=gen)
+    flat = torch.zeros(192)
+    K.concat_1d[1](x, y, flat, 64)
+    assert torch.equal(flat, torch.cat([x, y, x + y]))

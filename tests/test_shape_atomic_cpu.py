@@ -4,6 +4,7 @@ before the device launch."""
 import pytest
 import torch
 
+import asc
 import asc2
 
 import asc2_scripts as K
@@ -53,3 +54,20 @@ def test_bias_row_broadcast_merges_row_tiles():
     plan = K.add_row_bias.last_plan
     assert [s.note for s in plan.steps] == ["4 ops over [4096, 1024] pitches [1024, 0, 1024] from [0, 0] to 0"]
     assert plan.reads == {0, 1} and plan.writes == {2} and not plan.partial_writes
+
+
+def test_concat_store_unfolds_into_one_store_per_part():
+    a, b = torch.zeros(32, 64), torch.zeros(32, 64)
+    K.concat_rows[4](a, b, torch.zeros(64, 64), 32, 32, 64, 8)
+    plan = K.concat_rows.last_plan
+    assert plan.reads == {0, 1} and plan.writes == {2} and plan.partial_writes == {2}
+    assert len(plan.steps) == 8 and {s.fn_name for s in plan.steps} <= {"asc_cuda_eltwise_program",
+                                                                         "asc_cuda_eltwise_program_2d"}
+    K.concat_1d[1](torch.zeros(64), torch.zeros(64), torch.zeros(192), 64)
+    assert len(K.concat_1d.last_plan.steps) == 3
+    with pytest.raises(RuntimeError, match="same shape except their first dimension"):
+        @asc2.jit
+        def bad(x_ptr: asc.GlobalAddress):
+            x_gm = asc2.tensor(x_ptr, [8, 16])
+            asc2.concat(asc2.load(x_gm, [4, 16], offsets=[0, 0]), asc2.load(x_gm, [4, 8], offsets=[0, 0]))
+        bad[1](torch.zeros(8, 16))

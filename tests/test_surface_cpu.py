@@ -143,12 +143,13 @@ def test_workload_scripts_match_at_full_size():
 
 def test_unsupported_pattern_raises_not_implemented():
     @asc2.jit
-    def joined(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
-        x = asc2.load(asc2.tensor(x_ptr, [1, n]), [1, n], offsets=[0, 0])
-        asc2.store(asc2.concat(x, x), asc2.tensor(out_ptr, [2, n]), offsets=[0, 0])
-    x = np.zeros((1, 64), np.float32)
+    def sum_of_squares(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, r: asc.ConstExpr[int],
+                       c: asc.ConstExpr[int]):
+        x = asc2.load(asc2.tensor(x_ptr, [r, c]), [r, c], offsets=[0, 0])
+        asc2.store(asc2.reduce_sum(x * x, 1), asc2.tensor(out_ptr, [r]), offsets=[0])
+    x = np.zeros((16, 64), np.float32)
     with pytest.raises(NotImplementedError, match="no kernel for this pattern"):
-        joined[1](x, np.zeros((2, 64), np.float32), 64)
+        sum_of_squares[1](x, np.zeros(16, np.float32), 16, 64)
 
     @asc2.jit
     def centred(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, r: asc.ConstExpr[int], c: asc.ConstExpr[int]):
