@@ -178,6 +178,10 @@ int32_t asc_cuda_softmax_f16(const void* x, void* out, int64_t rows, int64_t col
  * x and out may alias; gamma holds cols floats.  Empty windows return ASC_OK without a launch. */
 int32_t asc_cuda_rms_norm_f32(const float* x, const float* gamma, float* out, int64_t rows, int64_t cols, int64_t ld,
                               float eps, void* stream);
+/* The same for fp16 rows and gamma (asc2.rms_norm accepts float16 tiles, unary_ops.py:227): the row is widened to
+ * fp32, the sum of squares and the scaling are fp32, one rounding at the store. */
+int32_t asc_cuda_rms_norm_f16(const void* x, const void* gamma, void* out, int64_t rows, int64_t cols, int64_t ld,
+                              float eps, void* stream);
 
 /* C[M,N] = epilogue(A[M,K] @ B[K,N]), row-major operands, fp32 accumulation on tcgen05 tensor
  * cores.  in_dtype: 0 fp16, 1 bf16.  out_dtype: 0 fp16, 1 bf16, 2 fp32.

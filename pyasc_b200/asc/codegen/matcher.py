@@ -1038,8 +1038,11 @@ def _match_rms_norm(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     if node is None:
         return None
     src, gamma, eps = node.args
-    if value.dtype != KT.float32 or out_t.dtype != KT.float32 or gamma.dtype != KT.float32:
-        raise _unsupported(f"rms_norm on {value.dtype} tiles (float32 only)")
+    dtype = value.dtype
+    if dtype not in (KT.float32, KT.float16) or out_t.dtype != dtype or gamma.dtype != dtype:
+        raise _unsupported(f"rms_norm on {dtype} tiles (float32 and float16, one type throughout)")
+    esize = dtype.bitwidth // 8
+    fn_name = "asc_cuda_rms_norm_f32" if dtype == KT.float32 else "asc_cuda_rms_norm_f16"
     view = resolve_view(src) if _node(src, "load") else None
     gview = resolve_view(gamma) if _node(gamma, "load") else None
     if view is None or gview is None:
@@ -1048,7 +1051,7 @@ def _match_rms_norm(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         raise _unsupported("rms_norm with an epsilon that varies between blocks or iterations")
     if not _same_offsets(view.offsets, eff.attrs["offsets"]) or view.shape != value.shape:
         raise _unsupported("rms_norm stored at a different position than it was loaded from")
-    if view.tensor.static_shape() != out_t.static_shape() or view.tensor.dtype != KT.float32:
+    if view.tensor.static_shape() != out_t.static_shape() or view.tensor.dtype != dtype or gview.tensor.dtype != dtype:
         raise _unsupported("rms_norm between tensors of different shapes or types")
     _check_fits(out_t)
     _check_fits(view.tensor)
@@ -1104,15 +1107,15 @@ def _match_rms_norm(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
 
     def make(lo: int, hi: int) -> List[Step]:
         def build(ptrs, stream, lo=lo, hi=hi):
-            byte_off = 4 * lo * C
-            return (_p(ptrs[in_idx] + byte_off), _p(ptrs[g_idx] + 4 * gamma_off), _p(ptrs[out_idx] + byte_off),
+            byte_off = esize * lo * C
+            return (_p(ptrs[in_idx] + byte_off), _p(ptrs[g_idx] + esize * gamma_off), _p(ptrs[out_idx] + byte_off),
                     ctypes.c_int64(hi - lo), ctypes.c_int64(C), ctypes.c_int64(C), ctypes.c_float(epsilon), stream)
-        return [Step("asc_cuda_rms_norm_f32", build, f"rows [{lo}, {hi}) x {C} cols")]
+        return [Step(fn_name, build, f"rows [{lo}, {hi}) x {C} cols")]
 
     for lo, hi in intervals:
         plan.steps += make(lo, hi)
     if not plan.partial_writes and g_idx not in (in_idx, out_idx):
-        plan.pipeline = PipelineSpec(R, 1, {in_idx: 4 * C, out_idx: 4 * C}, {g_idx}, make)
+        plan.pipeline = PipelineSpec(R, 1, {in_idx: esize * C, out_idx: esize * C}, {g_idx}, make)
     return plan
 
 

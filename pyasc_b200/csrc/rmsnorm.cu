@@ -4,8 +4,10 @@
 //
 // HBM-bound: 8 bytes per element (one read, one write); gamma is re-read by every row and stays in L2 / L1.
 // One CTA owns a row at a time and keeps it in registers between the single read and the single write
-// (128-bit accesses), the sum of squares is reduced with warp shuffles and a shared-memory exchange.  Rows
+// (128-bit accesses; fp16 rows are widened to fp32), the sum of squares is reduced with warp shuffles and a shared-memory exchange.  Rows
 // too long for registers, or not 16-byte aligned, are read twice by a plain kernel.
+#include <cuda_fp16.h>
+
 #include "../../include/asc_cuda.h"
 #include "host_common.h"
 
@@ -23,83 +25,145 @@ __device__ __forceinline__ float cta_sum(float v, float* red) {
   return r;
 }
 
-// cols % 4 == 0, cols <= 256 * kVec * 4, rows and gamma 16-byte aligned
-template <int kVec>
-__global__ void __launch_bounds__(256) rms_rows_reg_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
-                                                           float* __restrict__ out, int64_t rows, int cols4, int64_t ld4,
+// One 16-byte vector of a row: 4 floats or 8 halves, widened to fp32 registers.
+template <typename T>
+struct RowVec;
+template <>
+struct RowVec<float> {
+  static constexpr int kElems = 4;
+  __device__ static void load(const float* p, float (&v)[4], bool streaming) {
+    const float4 t = streaming ? __ldcs(reinterpret_cast<const float4*>(p)) : __ldg(reinterpret_cast<const float4*>(p));
+    v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+  }
+  __device__ static void store(float* p, const float (&v)[4]) {
+    __stcs(reinterpret_cast<float4*>(p), make_float4(v[0], v[1], v[2], v[3]));
+  }
+  __device__ static float widen(float x) { return x; }
+  __device__ static float narrow(float x) { return x; }
+};
+template <>
+struct RowVec<__half> {
+  static constexpr int kElems = 8;
+  __device__ static void load(const __half* p, float (&v)[8], bool streaming) {
+    const uint4 t = streaming ? __ldcs(reinterpret_cast<const uint4*>(p)) : __ldg(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      v[2 * i] = f.x, v[2 * i + 1] = f.y;
+    }
+  }
+  __device__ static void store(__half* p, const float (&v)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    __stcs(reinterpret_cast<uint4*>(p), make_uint4(w[0], w[1], w[2], w[3]));
+  }
+  __device__ static float widen(__half x) { return __half2float(x); }
+  __device__ static __half narrow(float x) { return __float2half_rn(x); }
+};
+
+// whole 16-byte vectors only: cols a multiple of kElems and at most 256 * kVec * kElems, rows and gamma 16-byte aligned
+template <typename T, int kVec>
+__global__ void __launch_bounds__(256) rms_rows_reg_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
+                                                           T* __restrict__ out, int64_t rows, int cols_v, int64_t ld,
                                                            float eps, float inv_cols) {
+  constexpr int kE = RowVec<T>::kElems;
   __shared__ float red[8];
-  const float4* x4 = reinterpret_cast<const float4*>(x);
-  const float4* g4 = reinterpret_cast<const float4*>(gamma);
-  float4* o4 = reinterpret_cast<float4*>(out);
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    float4 v[kVec];
+    float v[kVec][kE];
     float ss = 0.f;
 #pragma unroll
     for (int u = 0; u < kVec; ++u) {
       const int c = threadIdx.x + u * 256;
-      v[u] = (c < cols4) ? __ldcs(x4 + row * ld4 + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-      ss += (v[u].x * v[u].x + v[u].y * v[u].y) + (v[u].z * v[u].z + v[u].w * v[u].w);
+      if (c < cols_v) {
+        RowVec<T>::load(x + row * ld + static_cast<int64_t>(c) * kE, v[u], true);
+      } else {
+#pragma unroll
+        for (int e = 0; e < kE; ++e) v[u][e] = 0.f;
+      }
+      float part = 0.f;
+#pragma unroll
+      for (int e = 0; e < kE; ++e) part = fmaf(v[u][e], v[u][e], part);
+      ss += part;
     }
     const float scale = 1.f / sqrtf(cta_sum(ss, red) * inv_cols + eps);
 #pragma unroll
     for (int u = 0; u < kVec; ++u) {
       const int c = threadIdx.x + u * 256;
-      if (c < cols4) {
-        const float4 g = __ldg(g4 + c);
-        __stcs(o4 + row * ld4 + c,
-               make_float4(v[u].x * scale * g.x, v[u].y * scale * g.y, v[u].z * scale * g.z, v[u].w * scale * g.w));
+      if (c < cols_v) {
+        float g[kE];
+        RowVec<T>::load(gamma + static_cast<int64_t>(c) * kE, g, false);
+#pragma unroll
+        for (int e = 0; e < kE; ++e) v[u][e] = v[u][e] * scale * g[e];
+        RowVec<T>::store(out + row * ld + static_cast<int64_t>(c) * kE, v[u]);
       }
     }
   }
 }
 
 // any cols / alignment: the row is read twice
-__global__ void __launch_bounds__(256) rms_rows_generic_kernel(const float* __restrict__ x, const float* __restrict__ gamma,
-                                                               float* __restrict__ out, int64_t rows, int64_t cols,
+template <typename T>
+__global__ void __launch_bounds__(256) rms_rows_generic_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
+                                                               T* __restrict__ out, int64_t rows, int64_t cols,
                                                                int64_t ld, float eps, float inv_cols) {
   __shared__ float red[8];
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float* xr = x + row * ld;
+    const T* xr = x + row * ld;
     float ss = 0.f;
-    for (int64_t c = threadIdx.x; c < cols; c += 256) ss += xr[c] * xr[c];
+    for (int64_t c = threadIdx.x; c < cols; c += 256) {
+      const float t = RowVec<T>::widen(xr[c]);
+      ss = fmaf(t, t, ss);
+    }
     const float scale = 1.f / sqrtf(cta_sum(ss, red) * inv_cols + eps);
-    for (int64_t c = threadIdx.x; c < cols; c += 256) out[row * ld + c] = xr[c] * scale * gamma[c];
+    for (int64_t c = threadIdx.x; c < cols; c += 256)
+      out[row * ld + c] = RowVec<T>::narrow(RowVec<T>::widen(xr[c]) * scale * RowVec<T>::widen(gamma[c]));
   }
 }
 
-template <int kVec>
-void launch_reg(const float* x, const float* gamma, float* out, int64_t rows, int64_t cols, int64_t ld, float eps,
-                int64_t grid, cudaStream_t stream) {
-  rms_rows_reg_kernel<kVec><<<static_cast<unsigned>(grid), 256, 0, stream>>>(x, gamma, out, rows, static_cast<int>(cols / 4),
-                                                                             ld / 4, eps, 1.f / static_cast<float>(cols));
-}
-
-}  // namespace
-
-extern "C" int32_t asc_cuda_rms_norm_f32(const float* x, const float* gamma, float* out, int64_t rows, int64_t cols,
-                                         int64_t ld, float eps, void* stream) {
+template <typename T>
+int32_t launch_rms(const T* x, const T* gamma, T* out, int64_t rows, int64_t cols, int64_t ld, float eps,
+                   cudaStream_t s) {
   if (rows < 0 || cols < 0 || ld < cols) return ASC_ERR_INVALID_ARG;
   if (rows == 0 || cols == 0) return ASC_OK;
   if (x == nullptr || gamma == nullptr || out == nullptr) return ASC_ERR_INVALID_ARG;
   int sms = 0;
   int32_t rc = aschost::sm_count(&sms);
   if (rc != ASC_OK) return rc;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  constexpr int kE = RowVec<T>::kElems;
   int64_t grid = static_cast<int64_t>(sms) * 16;   // whole waves of resident CTAs; CTAs stride over the rows
   if (grid > rows) grid = rows;
-  const bool vec = cols % 4 == 0 && ld % 4 == 0 && aschost::aligned16(x) && aschost::aligned16(gamma) &&
+  const unsigned g = static_cast<unsigned>(grid);
+  const float inv_cols = 1.f / static_cast<float>(cols);
+  const bool vec = cols % kE == 0 && ld % kE == 0 && aschost::aligned16(x) && aschost::aligned16(gamma) &&
                    aschost::aligned16(out);
-  if (vec && cols <= 8192) {
-    if (cols <= 1024) launch_reg<1>(x, gamma, out, rows, cols, ld, eps, grid, s);
-    else if (cols <= 2048) launch_reg<2>(x, gamma, out, rows, cols, ld, eps, grid, s);
-    else if (cols <= 4096) launch_reg<4>(x, gamma, out, rows, cols, ld, eps, grid, s);
-    else launch_reg<8>(x, gamma, out, rows, cols, ld, eps, grid, s);
+  const int64_t cols_v = cols / kE;
+  if (vec && cols_v <= 256 * 8 / (kE / 4)) {     // at most 32 fp32 registers of row per thread
+    const int cv = static_cast<int>(cols_v);
+    if (cols_v <= 256) rms_rows_reg_kernel<T, 1><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
+    else if (cols_v <= 512) rms_rows_reg_kernel<T, 2><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
+    else if (cols_v <= 1024) rms_rows_reg_kernel<T, 4><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
+    else rms_rows_reg_kernel<T, 8><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
   } else {
-    rms_rows_generic_kernel<<<static_cast<unsigned>(grid), 256, 0, s>>>(x, gamma, out, rows, cols, ld, eps,
-                                                                        1.f / static_cast<float>(cols));
+    rms_rows_generic_kernel<T><<<g, 256, 0, s>>>(x, gamma, out, rows, cols, ld, eps, inv_cols);
   }
   aschost::count_launch();
   ASC_CUDA_TRY(cudaGetLastError());
   return ASC_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t asc_cuda_rms_norm_f32(const float* x, const float* gamma, float* out, int64_t rows, int64_t cols,
+                                         int64_t ld, float eps, void* stream) {
+  return launch_rms<float>(x, gamma, out, rows, cols, ld, eps, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int32_t asc_cuda_rms_norm_f16(const void* x, const void* gamma, void* out, int64_t rows, int64_t cols,
+                                         int64_t ld, float eps, void* stream) {
+  return launch_rms<__half>(static_cast<const __half*>(x), static_cast<const __half*>(gamma), static_cast<__half*>(out),
+                            rows, cols, ld, eps, static_cast<cudaStream_t>(stream));
 }

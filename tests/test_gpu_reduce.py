@@ -247,6 +247,32 @@ def test_capi_rms_norm(lib, rows, cols, pad):
     assert torch.equal(buf[:, :cols], out[:, :cols]) and torch.equal(buf[:, cols:], keep[:, cols:])
 
 
+@pytest.mark.parametrize("rows, cols, pad", [(3, 8, 0), (65, 1000, 0), (40, 4096, 8), (17, 8192, 0), (9, 16384, 0),
+                                             (11, 1001, 1), (65536, 2048, 0)])
+def test_capi_rms_norm_f16(lib, rows, cols, pad):
+    """fp16 rows: every register depth, the two-read kernel (long or odd rows), pitched rows, 256 MiB beyond L2."""
+    gen = torch.Generator(device="cuda").manual_seed(rows * 5 + cols)
+    ld = cols + pad
+    buf = (torch.randn(rows, ld, device="cuda", generator=gen) * 2).half()
+    gamma = (torch.rand(cols, device="cuda", generator=gen) + 0.25).half()
+    out = torch.full((rows, ld), -7.0, device="cuda", dtype=torch.float16)
+    rc = lib.asc_cuda_rms_norm_f16(ctypes.c_void_p(buf.data_ptr()), ctypes.c_void_p(gamma.data_ptr()),
+                                   ctypes.c_void_p(out.data_ptr()), rows, cols, ld, 1e-5, None)
+    assert rc == 0, capi.status_string(rc)
+    capi.check_device_status(None)
+    ref = golden.rms_norm(buf[:, :cols], gamma, 1e-5).half()      # fp32 arithmetic, one rounding at the end
+    torch.testing.assert_close(out[:, :cols], ref, rtol=1e-3, atol=1e-3)
+    assert pad == 0 or bool((out[:, cols:] == -7.0).all())
+
+
+def test_rms_norm_f16_through_asc2():
+    x = (torch.randn(64, 512) * 3).half()
+    gamma = (torch.rand(1, 512) + 0.5).half()
+    out = torch.zeros_like(x)
+    K.rms_norm_rows[4](x, gamma, out, 64, 512, 8, 1e-5)
+    torch.testing.assert_close(out, golden.rms_norm(x, gamma, 1e-5).half(), rtol=1e-3, atol=1e-3)
+
+
 def test_capi_rms_norm_rejects_bad_arguments(lib):
     x = torch.zeros(4, 8, device="cuda")
     p = ctypes.c_void_p(x.data_ptr())

@@ -99,6 +99,6 @@ def test_rms_norm_plans():
     with pytest.raises(RuntimeError, match="float32 and float16"):
         K.rms_norm_1d[1](torch.zeros(256, dtype=torch.int32), torch.ones(256, dtype=torch.int32),
                          torch.empty(256, dtype=torch.int32), 256)
-    with pytest.raises(NotImplementedError, match="float32 only"):
-        K.rms_norm_1d[1](torch.zeros(256, dtype=torch.float16), torch.ones(256, dtype=torch.float16),
-                         torch.empty(256, dtype=torch.float16), 256)
+    K.rms_norm_1d[1](torch.zeros(256, dtype=torch.float16), torch.ones(256, dtype=torch.float16),
+                     torch.empty(256, dtype=torch.float16), 256)
+    assert step_of(K.rms_norm_1d)[1].fn_name == "asc_cuda_rms_norm_f16"
