@@ -151,6 +151,21 @@ int32_t asc_cuda_eltwise_program_2d(const int32_t* ops, const int32_t* args, int
                                     void* out, int32_t out_type, int64_t rows, int64_t cols, const int64_t* lds,
                                     void* stream);
 
+/* A program over the rows of a [rows, cols] window (cols <= 8192) in which four more opcodes reduce the top of
+ * the stack over the row: ROW_SUM 59, ROW_MAX 60, ROW_MIN 61, ROW_PROD 62 (fp32).  Every element of the row
+ * then sees the reduced value as an ordinary operand, so an expression that mixes elementwise arithmetic with
+ * reductions of its own intermediate tiles along the last dimension (x - max(x), exp(..) / sum(exp(..)), a
+ * variance) is one pass: a row never leaves the SM between its load and its store.  lds as for the 2-D
+ * elementwise call (NULL: all pitches equal cols).  row_result != 0: the program's value is uniform along the
+ * row and one element per row is stored, at out[r * lds[n_inputs]] (pitch 1 when lds is NULL).
+ * Replaces the chains of vector calls and ReduceOp calls the reference lowers such kernels to
+ * (python/asc/language/tile/reduction_ops.py, shape_ops.py:30-75; lib/Conversion/LowerToAsc/LowerAscTile.cpp:
+ * 329-378 BroadcastOp, 428-459 ReduceOp; the manual softmax of python/test/asc2/kernels/test_softmax.py:16-27 is
+ * the reference's own example of the shape). */
+int32_t asc_cuda_row_program(const int32_t* ops, const int32_t* args, int32_t n_ops, const void* const* inputs,
+                             const int32_t* input_types, int32_t n_inputs, void* out, int32_t out_type, int64_t rows,
+                             int64_t cols, const int64_t* lds, int32_t row_result, void* stream);
+
 /* Reduction of a row-major [rows, cols] fp32 window with row pitch `ld` (elements).  kind: 0 sum, 1 max,
  * 2 min, 3 product.  axis 1: out[r] = reduce over the columns of row r; axis 0: out[c] = reduce over the
  * rows of column c; axis -1: out[0 .. n_fill) all receive the reduction of the whole window (the window is

@@ -25,6 +25,8 @@ _I_BINARY = {35: torch.add, 36: torch.sub, 37: torch.mul, 38: torch.maximum, 39:
 _I_UNARY = {48: torch.neg, 49: torch.abs, 50: torch.relu}
 _F_SWAPPED = {54: torch.sub, 55: torch.div}
 _I_SWAPPED = {56: torch.sub, 57: torch.bitwise_left_shift, 58: torch.bitwise_right_shift}
+_ROW = {59: lambda t: t.sum(-1, keepdim=True), 60: lambda t: t.amax(-1, keepdim=True),
+        61: lambda t: t.amin(-1, keepdim=True), 62: lambda t: t.prod(-1, keepdim=True)}
 IMM = 0x100
 TYPES = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16, 3: torch.int32, 4: torch.int16}
 
@@ -88,10 +90,14 @@ def run_program(ops: Sequence[int], args: Sequence[int], inputs: List[torch.Tens
             stack.append(torch.trunc(as_float(stack.pop())).to(torch.int32))
         elif op == 53:
             stack.append(as_int(stack.pop()).to(torch.int16).to(torch.int32))
+        elif op in _ROW:
+            # row programs (asc_cuda_row_program): the reduction over the last dimension replaces every element
+            t = as_float(stack.pop()).expand(shape)
+            stack.append(_ROW[op](t.double()).to(torch.float32).expand(shape))
         else:
             raise ValueError(f"unknown opcode {op}")
     assert len(stack) == 1, "malformed program"
     top = stack[0]
     dtype = TYPES[out_type]
     top = (as_float if dtype.is_floating_point else as_int)(top)
-    return top.to(dtype)
+    return top.expand(shape).to(dtype)

@@ -335,6 +335,8 @@ _OP_CVT_I2F, _OP_CVT_F2I, _OP_WRAP_I16 = 51, 52, 53
 _ELT_TYPE = {"float32": 0, "float16": 1, "bfloat16": 2, "int32": 3, "int16": 4}
 _ROUND_CODE = {"float16": _OP_ROUND_F16, "bfloat16": _OP_ROUND_BF16, "int16": _OP_WRAP_I16}
 ELT_MAX_OPS, ELT_MAX_INPUTS, ELT_MAX_STACK = 48, 6, 8
+_ROW_CODE = {"sum": 59, "max": 60, "min": 61, "prod": 62}     # row programs: reduce the top of the stack over the row
+ROW_MAX_COLS = 8192
 
 
 def _round_const(value: float, dtype: DataType) -> float:
@@ -399,6 +401,8 @@ class _EltProgram:
         self.scalar_store = scalar_store
         self.operands: List[_Operand] = []
         self.reshaped = False       # a reshape was seen: element order is the flat (row-major) order
+        self.row_ops = False        # the program reduces over rows: it runs as a row program
+        self.full_shape: Optional[Tuple[int, ...]] = None   # set while code for a per-row value is generated
         self.ops: List[int] = []
         self.args: List[int] = []
         self.max_depth = 0
@@ -453,7 +457,10 @@ class _EltProgram:
         if isinstance(v, PlainValue):
             if v.is_const:
                 return _Frag([], 0, self._word(v.value, scalar_dtype or v.dtype))
-            if not self.scalar_store:
+            if v.op == "tile_scalar" and v.args[0].kind == "reduce" and not self.scalar_store:
+                # the reduction of a whole one-row tile: a row reduction whose value every element sees
+                return self._row_reduction(v.args[0], v.dtype)
+            if v.op in ("sym", "tile_scalar") and not self.scalar_store:
                 return None
             # a one-element store: scalars loaded from the stored position and arithmetic on them
             if v.op == "tile_scalar":
@@ -475,6 +482,8 @@ class _EltProgram:
         node = v.node
         if node.kind == "full":
             return self.gen(node.attrs["value"], v.dtype)
+        if node.kind == "reduce" and self.full_shape is not None:
+            return self._row_reduction(node, v.dtype)
         if v.shape != self.shape:
             return None
         if node.kind in ("load", "copy"):
@@ -487,15 +496,22 @@ class _EltProgram:
                 frag = self.gen(src, scalar_dtype)
             finally:
                 self.shape = outer
-            self.reshaped = True
+            if self.full_shape is None:
+                self.reshaped = True      # (a per-row value has one element per row whatever its shape)
             return frag
         if node.kind == "broadcast":
             src = node.args[0]
             if _node(src, "full") is not None:
                 return self.gen(src.node.attrs["value"], v.dtype)
             # a single row repeated along the leading dimension
-            if len(self.shape) == 2 and src.size == self.shape[1] and src.shape[-1] == self.shape[1]:
+            if len(self.shape) == 2 and src.size == self.shape[1] and src.shape[-1] == self.shape[1] \
+                    and src.node.kind in ("load", "copy"):
                 return self._view_operand(src, bcast=True)
+            # one value per row repeated along the row: an expression over reductions of tiles of this shape
+            # along their last dimension (every element of the row evaluates it, the values agree)
+            if len(self.shape) == 2 and self.full_shape is None and src.size == self.shape[0] \
+                    and src.shape in ((self.shape[0], ), (self.shape[0], 1)):
+                return self._per_row(src, self.shape)
             return None
         if v.dtype.name not in _ELT_TYPE and node.kind != "compare":
             return None
@@ -536,6 +552,43 @@ class _EltProgram:
                 src = _Frag(src.code + [(_OP_CVT_F2I if src_t.dtype.is_float() else _OP_CVT_I2F, 0)], src.need)
             return self._rounded(src, v.dtype)
         return None
+
+    def _per_row(self, v: Tile, full_shape: Tuple[int, ...]) -> Optional[_Frag]:
+        """Code for a tile that holds one value per row of ``full_shape``."""
+        outer, self.shape, self.full_shape = self.shape, v.shape, tuple(full_shape)
+        try:
+            return self.gen(v)
+        finally:
+            self.shape, self.full_shape = outer, None
+
+    def _row_reduction(self, node: Node, dtype: DataType) -> Optional[_Frag]:
+        """``reduce_*`` along the last dimension of a computed tile: the tile's code, then a ROW opcode."""
+        src = node.args[0]
+        if dtype != KT.float32 or src.dtype != KT.float32 or node.attrs["kind"] not in _ROW_CODE:
+            return None
+        dims = node.attrs["dims"]
+        if self.full_shape is not None:
+            # per-row mode: the reduced tile has the full shape and loses its last dimension
+            if src.shape != self.full_shape or dims != (len(src.shape) - 1, ):
+                return None
+            outer, outer_full, self.shape, self.full_shape = self.shape, self.full_shape, src.shape, None
+            try:
+                inner = self.gen(src)
+            finally:
+                self.shape, self.full_shape = outer, outer_full
+        else:
+            # the scalar reduction of a tile that is a single row of the stored shape
+            rows = 1
+            for d in self.shape[:-1]:
+                rows *= d
+            if dims != () or rows != 1 or src.shape != self.shape:
+                return None
+            inner = self.gen(src)
+        if inner is None:
+            return None
+        inner = inner.pushed()
+        self.row_ops = True
+        return _Frag(inner.code + [(_ROW_CODE[node.attrs["kind"]], 0)], inner.need)
 
     def compile(self, v: Any) -> bool:
         frag = self.gen(v)
@@ -627,7 +680,8 @@ def _check_program_limits(prog: "_EltProgram") -> None:
 
 def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", out_t: Tensor,
                           offsets: Sequence[PlainValue], out_shape: Tuple[int, ...], scalar_store: bool,
-                          in_place_operand: Optional[int], dedupe: bool) -> Plan:
+                          in_place_operand: Optional[int], dedupe: bool,
+                          row_shape: Optional[Tuple[int, int]] = None, row_result: bool = False) -> Plan:
     """Operands addressed differently from the result (other tensor shapes or offsets, reshapes, a broadcast row,
     an accumulation into a fixed window): one call per (block, iteration) instance, in program order."""
     env = enumerate_instances(trace.core_num, eff.loops)
@@ -643,6 +697,19 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
             if out_g.numel % g.numel:
                 raise _unsupported("broadcast of a row whose length does not divide the stored tile")
             rows, cols = out_g.numel // g.numel, g.numel
+    if row_shape is not None:
+        # a row program walks the rows of the tile as the kernel wrote it: reductions run along them
+        rows, cols = row_shape
+        kv = 1
+        while kv * 256 < cols:
+            kv *= 2
+        if cols > ROW_MAX_COLS or max(1, prog.max_depth - 1) * kv * 1024 > 200 * 1024:
+            raise _unsupported(f"row reductions inside an expression over rows of {cols} elements with a stack of "
+                               f"{prog.max_depth} (the row and its intermediate values must fit one SM)")
+        if out_g.pitch is not None and (out_g.rows, out_g.cols) != (rows, 1 if row_result else cols):
+            raise _unsupported("row program stored into a window of a different shape")
+        if out_g.pitch is None and out_g.numel != (rows if row_result else rows * cols):
+            raise _unsupported("row program stored into a range of a different size")
     if prog.reshaped and (out_g.pitch is not None or any(g.pitch is not None for g in geoms)):
         raise _unsupported("reshape of a tile that is not a contiguous range of its tensor")
     lds: List[int] = []
@@ -659,7 +726,7 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
             if g.numel != rows * cols:
                 raise _unsupported("operand tile with a different number of elements than the stored tile")
             lds.append(cols)
-    lds.append(out_g.pitch if out_g.pitch is not None else cols)
+    lds.append(out_g.pitch if out_g.pitch is not None else (1 if row_result else cols))
     out_idx = out_t.base.index
     in_idx = [o.tensor.base.index for o in prog.operands]
     in_size = [o.tensor.dtype.bitwidth // 8 for o in prog.operands]
@@ -667,12 +734,14 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
     for k, (i, g) in enumerate(zip(in_idx, geoms)):
         if i == out_idx and not (k == in_place_operand and lds[k] == lds[-1] and np.array_equal(g.start, out_g.start)):
             raise _unsupported("elementwise kernel that stores into a tensor it also loads at other positions")
-    plan = Plan("elementwise:program")
+    plan = Plan("row:program" if row_shape is not None else "elementwise:program")
     plan.reads.update(in_idx)
     plan.writes.add(out_idx)
     plan.partial_writes.add(out_idx)
     n_ops, n_in, ops_arr, args_arr, types_arr, out_type = _program_arrays(prog, out_t)
     lds_arr = (ctypes.c_int64 * len(lds))(*lds)
+    fn_name = "asc_cuda_row_program" if row_shape is not None else "asc_cuda_eltwise_program_2d"
+    tail_args = (ctypes.c_int32(1 if row_result else 0), ) if row_shape is not None else ()
     calls: List[Tuple[Tuple[int, ...], int]] = []      # (first element of every operand and of the result, rows)
     all_starts = [tuple(int(g.start[j]) for g in geoms) + (int(out_g.start[j]), ) for j in range(n)]
     if dedupe:
@@ -692,11 +761,12 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
             ins = (ctypes.c_void_p * max(1, n_in))(*[ptrs[i] + sz * st for i, sz, st in zip(in_idx, in_size, starts)])
             return (ops_arr, args_arr, ctypes.c_int32(n_ops), ins, types_arr, ctypes.c_int32(n_in),
                     _p(ptrs[out_idx] + out_size * starts[-1]), ctypes.c_int32(out_type), ctypes.c_int64(call_rows),
-                    ctypes.c_int64(cols), lds_arr, stream)
-        plan.steps.append(Step("asc_cuda_eltwise_program_2d", build,
+                    ctypes.c_int64(cols), lds_arr) + tail_args + (stream, )
+        plan.steps.append(Step(fn_name, build,
                                f"{n_ops} ops over [{call_rows}, {cols}] pitches {lds} from {list(starts[:-1])} to {starts[-1]}"))
-    covered = sum(r for _, r in calls) * cols
-    if dedupe and len(calls) == 1 and lds[-1] == cols and calls[0][0][-1] == 0 and covered == out_t.base.numel:
+    out_cols = 1 if row_result else cols
+    covered = sum(r for _, r in calls) * out_cols
+    if dedupe and len(calls) == 1 and lds[-1] == out_cols and calls[0][0][-1] == 0 and covered == out_t.base.numel:
         plan.partial_writes.discard(out_idx)
     if not plan.steps:
         raise _unsupported("elementwise kernel without any tile")
@@ -723,6 +793,12 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
                       for o in prog.operands)
     else:
         aligned = not prog.reshaped and all(o.addressed_like(out_t, offsets, out_shape) for o in prog.operands)
+    if prog.row_ops:
+        rows = 1
+        for d in out_shape[:-1]:
+            rows *= d
+        return _plan_general_program(trace, eff, prog, out_t, offsets, out_shape, False, None, dedupe=True,
+                                     row_shape=(rows, out_shape[-1]))
     if not aligned or not prog.operands:
         return _plan_general_program(trace, eff, prog, out_t, offsets, out_shape, scalar_store, None, dedupe=True)
     numel = 1
@@ -825,6 +901,61 @@ def _match_atomic(trace: KernelTrace, eff: Effect) -> Plan:
     plan = _plan_general_program(trace, eff, prog, out_t, offsets, value.shape, False, 0, dedupe=False)
     plan.pattern = f"atomic:{eff.attrs['kind']}"
     return plan
+
+
+# --------------------------------------------------------------------------------------------------
+# Pattern: one value per row, computed from reductions of elementwise expressions along the row
+# --------------------------------------------------------------------------------------------------
+def _find_row_reduction(v: Any, depth: int = 0) -> Optional[Node]:
+    """The first reduction along the last dimension of a 2-D tile in the expression tree of ``v``."""
+    if depth > 64:
+        return None
+    if isinstance(v, PlainValue):
+        args = v.args if v.op not in ("const", "sym") else ()
+    elif isinstance(v, Tile):
+        node = v.node
+        if node.kind == "reduce" and len(node.args[0].shape) == 2 and node.attrs["dims"] == (1, ):
+            return node
+        args = node.args
+    elif isinstance(v, Node):
+        args = v.args
+    else:
+        return None
+    for a in args:
+        found = _find_row_reduction(a, depth + 1)
+        if found is not None:
+            return found
+    return None
+
+
+def _match_row_result(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
+    """``store(f(reduce(g(tiles), 1), ...), vector)``: a [rows] (or [rows, 1]) tile whose elements are functions of
+    row reductions of computed tiles, e.g. ``reduce_sum(x * x, 1)``.  One row program, one stored element per row."""
+    value, out_t = eff.args
+    if not isinstance(value, Tile) or eff.kind != "store" or out_t.dtype != KT.float32 or value.dtype != KT.float32:
+        return None
+    direct = _node(value, "reduce")
+    if direct is not None and direct.args[0].node.kind in ("load", "copy"):
+        return None                        # a reduction of a loaded tile has its own kernel
+    red = _find_row_reduction(value)
+    if red is None:
+        return None
+    full_shape = red.args[0].shape
+    if value.shape not in ((full_shape[0], ), (full_shape[0], 1)):
+        return None
+    offsets = eff.attrs["offsets"]
+    prog = _EltProgram(value.shape, offsets, out_t)
+    frag = prog._per_row(value, full_shape)
+    if frag is None or not prog.row_ops:
+        return None
+    frag = frag.pushed()
+    prog.ops, prog.args, prog.max_depth = [c[0] for c in frag.code], [c[1] for c in frag.code], frag.need
+    _check_program_limits(prog)
+    _check_fits(out_t)
+    for t in prog.inputs:
+        _check_fits(t)
+    return _plan_general_program(trace, eff, prog, out_t, offsets, value.shape, False, None, dedupe=True,
+                                 row_shape=(full_shape[0], full_shape[1]), row_result=True)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -1534,7 +1665,7 @@ def _match_attention(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
 # Entry point
 # --------------------------------------------------------------------------------------------------
 _MATCHERS = (_match_attention, _match_softmax, _match_rms_norm, _match_elementwise, _match_matmul, _match_eltwise_program,
-             _match_reduce)
+             _match_row_result, _match_reduce)
 
 
 def _is_identity_store(eff: Effect) -> bool:

@@ -37,13 +37,18 @@ enum EltOp : int32_t {
   OP_WRAP_I16 = 53,                  // sign-extend the low 16 bits (int16 arithmetic wraps)
   // operands swapped: f(lhs, rhs) = rhs op lhs
   OP_RSUB = 54, OP_RDIV = 55, OP_IRSUB = 56, OP_IRSHL = 57, OP_IRSHR = 58,
-  OP_COUNT = 59,
+  // row programs only: replace the top of the stack by its reduction over the row (fp32 words), so that
+  // every element of the row sees the reduced value
+  OP_ROW_SUM = 59, OP_ROW_MAX = 60, OP_ROW_MIN = 61, OP_ROW_PROD = 62,
+  OP_COUNT = 63,
   // flag on a binary opcode: the left operand is the 32-bit word in arg instead of a stack entry, so a
   // scalar operand costs neither a push nor a pop (with the swapped forms either side can be the scalar)
   OP_IMM = 0x100,
 };
 
 enum EltType : int32_t { T_F32 = 0, T_F16 = 1, T_BF16 = 2, T_I32 = 3, T_I16 = 4, T_COUNT = 5 };
+
+__host__ __device__ constexpr bool is_row_op(int op) { return op >= OP_ROW_SUM && op <= OP_ROW_PROD; }
 
 __host__ __device__ constexpr bool is_binary_op(int op) {
   return (op >= OP_ADD && op <= OP_MIN) || (op >= OP_EQ && op <= OP_LE) || (op >= OP_IADD && op <= OP_ILE) ||
@@ -577,40 +582,182 @@ int32_t try_compiled(const EltProgram& prog, const int32_t* ops, const int32_t* 
 }
 
 
-}  // namespace
+// ---- executor 3: programs with row reductions ----
+// One CTA evaluates one row of the window at a time; thread t owns columns t, t + 256, ... (kV of them), so
+// the loads and stores of consecutive threads are consecutive.  The top of the stack is in registers, lower
+// levels in shared memory ([level][lane][thread]: conflict-free).  A ROW_* opcode reduces the thread's lanes,
+// then the CTA (shuffles + one exchange through shared memory), and every lane of the top takes the result:
+// the reduced value is from then on an ordinary operand, which is how `x - max(x)`, `x / sum(x)` or a
+// variance are one pass over the row.  No scratch memory: a row never leaves the SM between its load and
+// its store.
+__device__ __forceinline__ float load_elem(const void* p, int type, int64_t i) {
+  switch (type) {
+    case T_F16: return __half2float(reinterpret_cast<const __half*>(p)[i]);
+    case T_BF16: return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+    case T_I32: return __int_as_float(reinterpret_cast<const int32_t*>(p)[i]);
+    case T_I16: return __int_as_float(static_cast<int>(reinterpret_cast<const int16_t*>(p)[i]));
+    default: return reinterpret_cast<const float*>(p)[i];
+  }
+}
+__device__ __forceinline__ void store_elem(void* p, int type, int64_t i, float v) {
+  switch (type) {
+    case T_F16: reinterpret_cast<__half*>(p)[i] = __float2half_rn(v); break;
+    case T_BF16: reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v); break;
+    case T_I32: reinterpret_cast<int32_t*>(p)[i] = __float_as_int(v); break;
+    case T_I16: reinterpret_cast<int16_t*>(p)[i] = static_cast<int16_t>(__float_as_int(v)); break;
+    default: reinterpret_cast<float*>(p)[i] = v; break;
+  }
+}
 
-extern "C" int32_t asc_cuda_eltwise_program_2d(const int32_t* ops, const int32_t* args, int32_t n_ops,
-                                               const void* const* inputs, const int32_t* input_types, int32_t n_inputs,
-                                               void* out, int32_t out_type, int64_t rows, int64_t cols,
-                                               const int64_t* lds, void* stream) {
-  if (rows < 0 || cols < 0 || n_inputs < 0 || n_inputs > kMaxInputs) return ASC_ERR_INVALID_ARG;
-  // lds: row pitch of every input, then of the output; NULL: all pitches equal cols (one contiguous range)
-  bool strided = false;
-  if (lds != nullptr && rows > 1) {
-    for (int k = 0; k <= n_inputs; ++k) {
-      const bool broadcast = lds[k] == 0 && k < n_inputs;
-      if (!broadcast && lds[k] < cols) return ASC_ERR_INVALID_ARG;
-      if (lds[k] >= (int64_t{1} << 32)) return ASC_ERR_TOO_LARGE;
-      strided = strided || lds[k] != cols;
+__device__ __forceinline__ float row_identity(int op) {
+  return op == OP_ROW_SUM ? 0.f : op == OP_ROW_PROD ? 1.f : op == OP_ROW_MAX ? -INFINITY : INFINITY;
+}
+__device__ __forceinline__ float row_combine(int op, float a, float b) {
+  return op == OP_ROW_SUM ? __fadd_rn(a, b) : op == OP_ROW_PROD ? __fmul_rn(a, b) : op == OP_ROW_MAX ? fmaxf(a, b) : fminf(a, b);
+}
+
+template <int kV>
+__global__ void __launch_bounds__(kThreads) row_program_kernel(const __grid_constant__ EltProgram prog, uint32_t rows,
+                                                               int row_result) {
+  extern __shared__ float stack_mem[];
+  __shared__ float red[kThreads / 32];
+  float* const slots = stack_mem + threadIdx.x;
+  const uint32_t cols = prog.cols;
+#define ASC_LANES _Pragma("unroll") for (int e = 0; e < kV; ++e)
+#define ASC_PUT(LEVEL) ASC_LANES slots[((LEVEL) * kV + e) * kThreads] = top[e];
+#define ASC_GET(LEVEL, DST) ASC_LANES DST[e] = slots[((LEVEL) * kV + e) * kThreads];
+#define ASC_BIN(CODE)                                      \
+  case CODE: {                                             \
+    float lhs[kV];                                         \
+    if (imm) {                                             \
+      ASC_LANES lhs[e] = __int_as_float(prog.arg[k]);      \
+    } else {                                               \
+      ASC_GET(depth - 2, lhs)                              \
+      --depth;                                             \
+    }                                                      \
+    ASC_LANES top[e] = apply_binary(CODE, lhs[e], top[e]); \
+  } break;
+#define ASC_UN(CODE)                              \
+  case CODE:                                      \
+    ASC_LANES top[e] = apply_unary(CODE, top[e]); \
+    break;
+#define ASC_ROW(CODE)                                                                              \
+  case CODE: {                                                                                     \
+    float v = row_identity(CODE);                                                                  \
+    ASC_LANES if (threadIdx.x + e * kThreads < cols) v = row_combine(CODE, v, top[e]);             \
+    _Pragma("unroll") for (int o = 16; o > 0; o >>= 1) v = row_combine(CODE, v, __shfl_xor_sync(0xffffffffu, v, o)); \
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;                                        \
+    __syncthreads();                                                                               \
+    v = red[0];                                                                                    \
+    _Pragma("unroll") for (int w = 1; w < kThreads / 32; ++w) v = row_combine(CODE, v, red[w]);    \
+    __syncthreads();                                                                               \
+    ASC_LANES top[e] = v;                                                                          \
+  } break;
+  for (uint32_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    float top[kV];
+    int depth = 0;
+#pragma unroll 1
+    for (int k = 0; k < prog.n_ops; ++k) {
+      const int op = prog.op[k] & 0xff;
+      const bool imm = (prog.op[k] & OP_IMM) != 0;
+      switch (op) {
+        case OP_LOAD: {
+          if (depth > 0) { ASC_PUT(depth - 1) }
+          ++depth;
+          const int input = prog.arg[k];
+          const void* p = prog.in[input];
+          const int type = prog.in_type[input] & 0xff;
+          const int64_t base = static_cast<int64_t>(r) * prog.ld[input];
+          ASC_LANES {
+            const uint32_t c = threadIdx.x + e * kThreads;
+            top[e] = c < cols ? load_elem(p, type, base + c) : 0.f;
+          }
+        } break;
+        case OP_CONST:
+          if (depth > 0) { ASC_PUT(depth - 1) }
+          ++depth;
+          ASC_LANES top[e] = __int_as_float(prog.arg[k]);
+          break;
+        case OP_WHERE: {
+          float a[kV], c[kV];
+          ASC_GET(depth - 2, a)
+          ASC_GET(depth - 3, c)
+          depth -= 2;
+          ASC_LANES top[e] = c[e] != 0.f ? a[e] : top[e];
+        } break;
+        ASC_BIN(OP_ADD) ASC_BIN(OP_SUB) ASC_BIN(OP_MUL) ASC_BIN(OP_DIV) ASC_BIN(OP_MAX) ASC_BIN(OP_MIN)
+        ASC_BIN(OP_EQ) ASC_BIN(OP_NE) ASC_BIN(OP_GT) ASC_BIN(OP_GE) ASC_BIN(OP_LT) ASC_BIN(OP_LE)
+        ASC_BIN(OP_IADD) ASC_BIN(OP_ISUB) ASC_BIN(OP_IMUL) ASC_BIN(OP_IMAX) ASC_BIN(OP_IMIN) ASC_BIN(OP_ISHL)
+        ASC_BIN(OP_ISHR) ASC_BIN(OP_IEQ) ASC_BIN(OP_INE) ASC_BIN(OP_IGT) ASC_BIN(OP_IGE) ASC_BIN(OP_ILT)
+        ASC_BIN(OP_ILE) ASC_BIN(OP_RSUB) ASC_BIN(OP_RDIV) ASC_BIN(OP_IRSUB) ASC_BIN(OP_IRSHL) ASC_BIN(OP_IRSHR)
+        ASC_UN(OP_NEG) ASC_UN(OP_ABS) ASC_UN(OP_RELU) ASC_UN(OP_EXP) ASC_UN(OP_EXP2) ASC_UN(OP_LOG) ASC_UN(OP_LOG2)
+        ASC_UN(OP_SQRT) ASC_UN(OP_RSQRT) ASC_UN(OP_SIN) ASC_UN(OP_COS) ASC_UN(OP_TAN) ASC_UN(OP_SINH)
+        ASC_UN(OP_COSH) ASC_UN(OP_TANH) ASC_UN(OP_ERF) ASC_UN(OP_FLOOR) ASC_UN(OP_CEIL) ASC_UN(OP_ROUND_F16)
+        ASC_UN(OP_ROUND_BF16) ASC_UN(OP_INEG) ASC_UN(OP_IABS) ASC_UN(OP_IRELU) ASC_UN(OP_CVT_I2F)
+        ASC_UN(OP_CVT_F2I) ASC_UN(OP_WRAP_I16)
+        ASC_ROW(OP_ROW_SUM) ASC_ROW(OP_ROW_MAX) ASC_ROW(OP_ROW_MIN) ASC_ROW(OP_ROW_PROD)
+        default: break;
+      }
+    }
+    const int64_t out_base = static_cast<int64_t>(r) * prog.ld[prog.n_inputs];
+    if (row_result) {
+      // the program ends in a value that is the same for the whole row: one element per row is stored
+      if (threadIdx.x == 0) store_elem(prog.out, prog.out_type, out_base, top[0]);
+    } else {
+      ASC_LANES {
+        const uint32_t c = threadIdx.x + e * kThreads;
+        if (c < cols) store_elem(prog.out, prog.out_type, out_base + c, top[e]);
+      }
     }
   }
-  if (strided && rows * cols >= (int64_t{1} << 32)) return ASC_ERR_TOO_LARGE;
-  const int64_t n = rows * cols;
-  if (n < 0 || n_ops <= 0 || n_ops > kMaxOps || n_inputs < 0 || n_inputs > kMaxInputs) return ASC_ERR_INVALID_ARG;
-  if (ops == nullptr || args == nullptr || out == nullptr || (n_inputs > 0 && (inputs == nullptr || input_types == nullptr)))
-    return ASC_ERR_INVALID_ARG;
-  if (out_type < 0 || out_type >= T_COUNT) return ASC_ERR_INVALID_ARG;
-  if (n == 0) return ASC_OK;
-  EltProgram prog{};
+#undef ASC_ROW
+#undef ASC_UN
+#undef ASC_BIN
+#undef ASC_GET
+#undef ASC_PUT
+#undef ASC_LANES
+}
+
+template <int kV>
+int32_t launch_row_program(const EltProgram& prog, int64_t rows, int max_depth, int row_result, int sms,
+                           cudaStream_t stream) {
+  const size_t smem = static_cast<size_t>(max_depth > 1 ? max_depth - 1 : 1) * kV * kThreads * sizeof(float);
+  if (smem > 200 * 1024) return ASC_ERR_TOO_LARGE;
+  if (smem > 48 * 1024) {
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    ASC_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+      ASC_CUDA_TRY(cudaFuncSetAttribute(row_program_kernel<kV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+  }
+  int resident = 0;
+  ASC_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, row_program_kernel<kV>, kThreads, smem));
+  if (resident < 1) resident = 1;
+  int64_t ctas = static_cast<int64_t>(sms) * resident * 4;   // four waves of resident CTAs; CTAs stride over the rows
+  if (ctas > rows) ctas = rows;
+  row_program_kernel<kV><<<static_cast<unsigned>(ctas), kThreads, smem, stream>>>(prog, static_cast<uint32_t>(rows),
+                                                                                   row_result);
+  aschost::count_launch();
+  ASC_CUDA_TRY(cudaGetLastError());
+  return ASC_OK;
+}
+
+// Validates a program on the host (opcodes, operand indices, stack depth) and copies it, with the input
+// pointers and types, into the launch argument.  Row reductions are legal only where the caller says so.
+int32_t fill_program(const int32_t* ops, const int32_t* args, int n_ops, const void* const* inputs,
+                     const int32_t* input_types, int n_inputs, bool row_ops_allowed, EltProgram& prog, int& max_depth) {
   prog.n_ops = n_ops;
   prog.n_inputs = n_inputs;
-  // validate the program on the host: opcodes, operand indices and stack depth
-  int depth = 0, max_depth = 0;
+  int depth = 0;
+  max_depth = 0;
   for (int k = 0; k < n_ops; ++k) {
     const int op = ops[k] & 0xff;
     const bool imm = (ops[k] & OP_IMM) != 0;
     if (ops[k] < 0 || (ops[k] & ~(0xff | OP_IMM)) != 0 || op >= OP_COUNT) return ASC_ERR_INVALID_ARG;
     if (imm && !is_binary_op(op)) return ASC_ERR_INVALID_ARG;
+    if (is_row_op(op) && !row_ops_allowed) return ASC_ERR_INVALID_ARG;
     if (op == OP_LOAD) {
       if (args[k] < 0 || args[k] >= n_inputs) return ASC_ERR_INVALID_ARG;
       ++depth;
@@ -639,13 +786,44 @@ extern "C" int32_t asc_cuda_eltwise_program_2d(const int32_t* ops, const int32_t
     for (int k = 0; k < n_ops; ++k) loads += (prog.op[k] == OP_LOAD && prog.arg[k] == i) ? 1 : 0;
     prog.in_type[i] = input_types[i] | (loads > 1 ? kReusedInput : 0);
   }
+  return ASC_OK;
+}
+
+}  // namespace
+
+extern "C" int32_t asc_cuda_eltwise_program_2d(const int32_t* ops, const int32_t* args, int32_t n_ops,
+                                               const void* const* inputs, const int32_t* input_types, int32_t n_inputs,
+                                               void* out, int32_t out_type, int64_t rows, int64_t cols,
+                                               const int64_t* lds, void* stream) {
+  if (rows < 0 || cols < 0 || n_inputs < 0 || n_inputs > kMaxInputs) return ASC_ERR_INVALID_ARG;
+  // lds: row pitch of every input, then of the output; NULL: all pitches equal cols (one contiguous range)
+  bool strided = false;
+  if (lds != nullptr && rows > 1) {
+    for (int k = 0; k <= n_inputs; ++k) {
+      const bool broadcast = lds[k] == 0 && k < n_inputs;
+      if (!broadcast && lds[k] < cols) return ASC_ERR_INVALID_ARG;
+      if (lds[k] >= (int64_t{1} << 32)) return ASC_ERR_TOO_LARGE;
+      strided = strided || lds[k] != cols;
+    }
+  }
+  if (strided && rows * cols >= (int64_t{1} << 32)) return ASC_ERR_TOO_LARGE;
+  const int64_t n = rows * cols;
+  if (n < 0 || n_ops <= 0 || n_ops > kMaxOps || n_inputs < 0 || n_inputs > kMaxInputs) return ASC_ERR_INVALID_ARG;
+  if (ops == nullptr || args == nullptr || out == nullptr || (n_inputs > 0 && (inputs == nullptr || input_types == nullptr)))
+    return ASC_ERR_INVALID_ARG;
+  if (out_type < 0 || out_type >= T_COUNT) return ASC_ERR_INVALID_ARG;
+  if (n == 0) return ASC_OK;
+  EltProgram prog{};
+  int max_depth = 0;
+  int32_t rc = fill_program(ops, args, n_ops, inputs, input_types, n_inputs, false, prog, max_depth);
+  if (rc != ASC_OK) return rc;
   if (reinterpret_cast<uintptr_t>(out) % elem_size(out_type) != 0) return ASC_ERR_MISALIGNED;
   prog.out = out;
   prog.out_type = out_type;
   prog.cols = strided ? static_cast<uint32_t>(cols) : 0u;
   for (int k = 0; k <= n_inputs; ++k) prog.ld[k] = strided ? static_cast<uint32_t>(lds[k]) : 0u;
   int sms = 0;
-  int32_t rc = aschost::sm_count(&sms);
+  rc = aschost::sm_count(&sms);
   if (rc != ASC_OK) return rc;
   bool vec = reinterpret_cast<uintptr_t>(out) % (4 * elem_size(out_type)) == 0;
   for (int i = 0; i < n_inputs; ++i) vec = vec && reinterpret_cast<uintptr_t>(inputs[i]) % (4 * elem_size(input_types[i])) == 0;
@@ -688,4 +866,50 @@ extern "C" int32_t asc_cuda_eltwise_set_lanes(int32_t lanes) {
   g_lanes = (l == 4 || l == 8 || l == 16) ? l : 0;
   g_use_compiled = (lanes & 0x100) == 0;
   return ASC_OK;
+}
+
+// A program over the rows of a [rows, cols] window in which ROW_SUM / ROW_MAX / ROW_MIN / ROW_PROD reduce the
+// top of the stack over the row.  lds as for the 2-D elementwise call (0: an input row every window row reads);
+// row_result != 0: the program's value is uniform along the row and one element per row is stored, at
+// out[r * lds[n_inputs]].
+extern "C" int32_t asc_cuda_row_program(const int32_t* ops, const int32_t* args, int32_t n_ops,
+                                        const void* const* inputs, const int32_t* input_types, int32_t n_inputs,
+                                        void* out, int32_t out_type, int64_t rows, int64_t cols, const int64_t* lds,
+                                        int32_t row_result, void* stream) {
+  if (rows < 0 || cols < 0 || n_inputs < 0 || n_inputs > kMaxInputs || n_ops <= 0 || n_ops > kMaxOps)
+    return ASC_ERR_INVALID_ARG;
+  if (ops == nullptr || args == nullptr || out == nullptr || (n_inputs > 0 && (inputs == nullptr || input_types == nullptr)))
+    return ASC_ERR_INVALID_ARG;
+  if (out_type < 0 || out_type >= T_COUNT) return ASC_ERR_INVALID_ARG;
+  if (rows >= (int64_t{1} << 32)) return ASC_ERR_TOO_LARGE;
+  if (cols > 32 * kThreads) return ASC_ERR_TOO_LARGE;     // a thread holds at most 32 elements of the row
+  EltProgram prog{};
+  int max_depth = 0;
+  int32_t rc = fill_program(ops, args, n_ops, inputs, input_types, n_inputs, true, prog, max_depth);
+  if (rc != ASC_OK) return rc;
+  if (reinterpret_cast<uintptr_t>(out) % elem_size(out_type) != 0) return ASC_ERR_MISALIGNED;
+  for (int k = 0; k <= n_inputs; ++k) {
+    const bool is_out = k == n_inputs;
+    int64_t ld = lds != nullptr ? lds[k] : (is_out && row_result ? 1 : cols);
+    const int64_t least = is_out ? (row_result ? 1 : cols) : 0;       // an input pitch of 0 is a broadcast row
+    if (ld < least || (!is_out && ld != 0 && ld < cols)) return ASC_ERR_INVALID_ARG;
+    if (ld >= (int64_t{1} << 32)) return ASC_ERR_TOO_LARGE;
+    prog.ld[k] = static_cast<uint32_t>(ld);
+  }
+  if (rows == 0 || cols == 0) return ASC_OK;
+  prog.out = out;
+  prog.out_type = out_type;
+  prog.cols = static_cast<uint32_t>(cols);
+  int sms = 0;
+  rc = aschost::sm_count(&sms);
+  if (rc != ASC_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t per_thread = (cols + kThreads - 1) / kThreads;
+  const int rr = row_result != 0 ? 1 : 0;
+  if (per_thread <= 1) return launch_row_program<1>(prog, rows, max_depth, rr, sms, st);
+  if (per_thread <= 2) return launch_row_program<2>(prog, rows, max_depth, rr, sms, st);
+  if (per_thread <= 4) return launch_row_program<4>(prog, rows, max_depth, rr, sms, st);
+  if (per_thread <= 8) return launch_row_program<8>(prog, rows, max_depth, rr, sms, st);
+  if (per_thread <= 16) return launch_row_program<16>(prog, rows, max_depth, rr, sms, st);
+  return launch_row_program<32>(prog, rows, max_depth, rr, sms, st);
 }

@@ -401,3 +401,41 @@ def concat_1d(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, out_ptr: asc.G
     a = asc2.load(asc2.tensor(a_ptr, [n]), [n], offsets=[0])
     b = asc2.load(asc2.tensor(b_ptr, [n]), [n], offsets=[0])
     asc2.store(asc2.concat(a, asc2.concat(b, a + b)), asc2.tensor(out_ptr, [3 * n]), offsets=[0])
+
+
+# ---- expressions that reduce their own intermediate tiles along the row (row programs)
+@asc2.jit
+def layer_norm_rows(x_ptr: asc.GlobalAddress, gamma_ptr: asc.GlobalAddress, beta_ptr: asc.GlobalAddress,
+                    out_ptr: asc.GlobalAddress, num_rows: int, num_cols: asc.ConstExpr[int],
+                    block_size: asc.ConstExpr[int], epsilon: float):
+    x_gm = asc2.tensor(x_ptr, [num_rows, num_cols])
+    out_gm = asc2.tensor(out_ptr, [num_rows, num_cols])
+    gamma = asc2.load(asc2.tensor(gamma_ptr, [1, num_cols]), [1, num_cols], offsets=[0, 0])
+    beta = asc2.load(asc2.tensor(beta_ptr, [1, num_cols]), [1, num_cols], offsets=[0, 0])
+    for r0 in asc2.range(asc2.block_idx() * block_size, num_rows, asc2.block_num() * block_size):
+        x = asc2.load(x_gm, [block_size, num_cols], offsets=[r0, 0])
+        mean = (asc2.reduce_sum(x, 1) / num_cols).reshape(block_size, 1).broadcast_to(block_size, num_cols)
+        xc = x - mean
+        var = (asc2.reduce_sum(xc * xc, 1, keep_dims=True) / num_cols).broadcast_to(block_size, num_cols)
+        y = xc * asc2.rsqrt(var + epsilon)
+        asc2.store(y * gamma.broadcast_to(block_size, num_cols) + beta.broadcast_to(block_size, num_cols), out_gm,
+                   offsets=[r0, 0])
+
+
+@asc2.jit
+def l1_normalize_rows(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, num_rows: int, num_cols: asc.ConstExpr[int]):
+    x_gm = asc2.tensor(x_ptr, [num_rows, num_cols])
+    out_gm = asc2.tensor(out_ptr, [num_rows, num_cols])
+    for i in asc2.range(asc2.block_idx(), num_rows, asc2.block_num()):
+        row = asc2.load(x_gm, [1, num_cols], offsets=[i, 0])
+        asc2.store(row / (asc2.reduce_sum(asc2.abs(row)) + 1e-6), out_gm, offsets=[i, 0])
+
+
+@asc2.jit
+def row_sum_of_squares(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, num_rows: int, num_cols: asc.ConstExpr[int],
+                       block_size: asc.ConstExpr[int]):
+    x_gm = asc2.tensor(x_ptr, [num_rows, num_cols])
+    out_gm = asc2.tensor(out_ptr, [num_rows])
+    for r0 in asc2.range(asc2.block_idx() * block_size, num_rows, asc2.block_num() * block_size):
+        x = asc2.load(x_gm, [block_size, num_cols], offsets=[r0, 0])
+        asc2.store(asc2.sqrt(asc2.reduce_sum(x * x, 1)) * 0.5 + asc2.reduce_max(asc2.abs(x), 1), out_gm, offsets=[r0])

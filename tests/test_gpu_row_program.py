@@ -1,0 +1,120 @@
+"""Row programs on the GPU: asc2 kernels that reduce their own intermediate tiles along the row, against torch,
+and the C-ABI entry point against the CPU oracle's evaluation of the same program."""
+import ctypes
+
+import pytest
+import torch
+
+import asc.runtime.config as config
+import asc2
+
+import asc2_scripts as K
+from oracle import eltwise as E
+from pyasc_b200 import capi
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def platform():
+    config.set_platform(config.Backend.CUDA, config.Platform.B200, 0)
+
+
+@pytest.mark.parametrize("rows, cols, block, blocks", [(64, 512, 8, 4), (256, 4096, 4, 16), (32, 8, 8, 2),
+                                                       (48, 1000, 2, 3)])
+def test_layer_norm(rows, cols, block, blocks):
+    gen = torch.Generator().manual_seed(rows + cols)
+    x = torch.randn(rows, cols, generator=gen) * 2 + 1
+    gamma, beta = torch.rand(1, cols, generator=gen) + 0.5, torch.randn(1, cols, generator=gen)
+    out = torch.zeros_like(x)
+    K.layer_norm_rows[blocks](x, gamma, beta, out, rows, cols, block, 1e-5)
+    ref = torch.nn.functional.layer_norm(x, (cols, ), gamma[0], beta[0], 1e-5)
+    torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-5)
+
+
+def test_l1_normalize_and_row_results():
+    gen = torch.Generator().manual_seed(9)
+    x = torch.randn(96, 2048, generator=gen)
+    out = torch.zeros_like(x)
+    K.l1_normalize_rows[8](x, out, 96, 2048)
+    torch.testing.assert_close(out, x / (x.abs().sum(1, keepdim=True) + 1e-6), rtol=1e-5, atol=1e-7)
+    xd = torch.randn(512, 384, device="cuda")
+    res = torch.zeros(512, device="cuda")
+    K.row_sum_of_squares[16](xd, res, 512, 384, 8)
+    torch.testing.assert_close(res, xd.pow(2).sum(1).sqrt() * 0.5 + xd.abs().amax(1), rtol=1e-5, atol=1e-6)
+
+
+# ------------------------------------------------------------------------------- C ABI
+@pytest.fixture(scope="module")
+def lib():
+    torch.cuda.set_device(0)
+    return capi.load()
+
+
+def f32_word(v: float) -> int:
+    return int(torch.tensor([v], dtype=torch.float32).view(torch.int32)[0])
+
+
+# LOAD x, ROW_MAX, LOAD x, RSUB (x - max), EXP, the same five again, ROW_SUM, DIV, LOAD y, MUL:
+# exp(x - max) / sum(exp(x - max)) * y
+SOFTMAX_TIMES_Y = ([0, 60, 0, 54, 11, 0, 60, 0, 54, 11, 59, 5, 0, 4],
+                   [0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 1, 0])
+
+
+def run_row_program(lib, ops, args, inputs, out, rows, cols, lds, row_result, expect=0):
+    n_in = len(inputs)
+    ops_arr = (ctypes.c_int32 * len(ops))(*ops)
+    args_arr = (ctypes.c_int32 * len(ops))(*args)
+    ins = (ctypes.c_void_p * max(1, n_in))(*[t.data_ptr() for t in inputs])
+    types = (ctypes.c_int32 * max(1, n_in))(*[{torch.float32: 0, torch.float16: 1}[t.dtype] for t in inputs])
+    lds_arr = (ctypes.c_int64 * len(lds))(*lds) if lds is not None else None
+    rc = lib.asc_cuda_row_program(ops_arr, args_arr, len(ops), ins, types, n_in, ctypes.c_void_p(out.data_ptr()),
+                                  {torch.float32: 0, torch.float16: 1}[out.dtype], rows, cols, lds_arr, row_result, None)
+    assert rc == expect, f"returned {rc}: {capi.status_string(rc)} {capi.last_cuda_error()}"
+    if rc == 0:
+        capi.check_device_status(None)
+
+
+@pytest.mark.parametrize("rows, cols, pad", [(1, 1, 0), (5, 33, 0), (300, 256, 0), (129, 1000, 24), (64, 4096, 0),
+                                             (33, 8192, 0), (16384, 4096, 0)])
+def test_capi_row_program_against_oracle(lib, rows, cols, pad):
+    """Every lane count of the kernel (1 to 32 elements per thread), ragged rows, pitched operands, a broadcast
+    row, and a 256 MiB window (beyond L2)."""
+    gen = torch.Generator(device="cuda").manual_seed(rows * 3 + cols)
+    ld = cols + pad
+    xbuf = torch.randn(rows, ld, device="cuda", generator=gen)
+    y = torch.rand(cols, device="cuda", generator=gen) + 0.5
+    out = torch.full((rows, ld), -3.0, device="cuda")
+    ops, args = SOFTMAX_TIMES_Y
+    run_row_program(lib, ops, args, [xbuf, y], out, rows, cols, [ld, 0, ld], 0)
+    x = xbuf[:, :cols]
+    if rows * cols <= (1 << 22):
+        ref = E.run_program(ops, args, [x.cpu(), y.cpu().expand(rows, cols)], 0)
+        torch.testing.assert_close(out[:, :cols].cpu(), ref, rtol=2e-5, atol=1e-7)
+    torch.testing.assert_close(out[:, :cols], torch.softmax(x, 1) * y, rtol=2e-5, atol=1e-7)
+    assert pad == 0 or bool((out[:, cols:] == -3.0).all())
+
+
+def test_capi_row_result_and_fp16_operands(lib):
+    x = torch.randn(1000, 777, device="cuda").half()
+    out = torch.zeros(1000, device="cuda")
+    # LOAD 0, LOAD 0, MUL, ROW_SUM: sum of squares of fp16 rows, one fp32 value per row
+    run_row_program(lib, [0, 0, 4, 59], [0, 0, 0, 0], [x], out, 1000, 777, None, 1)
+    torch.testing.assert_close(out, x.float().pow(2).sum(1), rtol=1e-5, atol=1e-5)
+    # ROW_MIN / ROW_PROD with an immediate: min(x) * prod(1 + 0 * x) == min(x)
+    out2 = torch.zeros(1000, device="cuda")
+    run_row_program(lib, [0, 61, 0, 4 | 0x100, 2 | 0x100, 62, 4], [0, 0, 0, f32_word(0.0), f32_word(1.0), 0, 0], [x], out2,
+                    1000, 777, None, 1)
+    torch.testing.assert_close(out2, x.float().amin(1), rtol=0, atol=0)
+
+
+def test_capi_row_program_rejections(lib):
+    x = torch.zeros(4, 16, device="cuda")
+    out = torch.zeros(4, 16, device="cuda")
+    run_row_program(lib, [0, 59], [0, 0], [x], out, 4, 8193 * 4, None, 0, expect=6)       # row too long for one SM
+    run_row_program(lib, [0, 59], [0, 0], [x], out, 4, 16, [8, 16], 0, expect=1)          # pitch below the row length
+    run_row_program(lib, [0, 63], [0, 0], [x], out, 4, 16, None, 0, expect=1)             # no such opcode
+    # the elementwise entry point refuses row opcodes
+    ops_arr, args_arr = (ctypes.c_int32 * 2)(0, 59), (ctypes.c_int32 * 2)(0, 0)
+    ins, types = (ctypes.c_void_p * 1)(x.data_ptr()), (ctypes.c_int32 * 1)(0)
+    assert lib.asc_cuda_eltwise_program(ops_arr, args_arr, 2, ins, types, 1, ctypes.c_void_p(out.data_ptr()), 0, 64, None) == 1

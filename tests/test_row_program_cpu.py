@@ -1,0 +1,82 @@
+"""Kernels that reduce their own intermediate tiles along the row (layer norm, normalisations, norms of computed
+tiles) on CPU: the launcher compiles them into one row program; evaluated by the CPU oracle it must reproduce
+the torch expression.  ``DRY_RUN=1`` stops before the device launch."""
+import pytest
+import torch
+
+import asc
+import asc2
+
+import asc2_scripts as K
+from oracle import eltwise as E
+
+
+@pytest.fixture(autouse=True)
+def dry_run(monkeypatch):
+    monkeypatch.setenv("DRY_RUN", "1")
+
+
+def decode(step):
+    assert step.fn_name == "asc_cuda_row_program"
+    ptrs = {i: (i + 1) << 40 for i in range(16)}
+    ops, args, n_ops, ins, types, n_in, out, out_type, rows, cols, lds, row_result, _ = step.build(ptrs, None)
+    assert len(ops) == n_ops.value
+    operands = [((int(a) >> 40) - 1, int(a) & ((1 << 40) - 1)) for a in list(ins)[:n_in.value]]
+    return (list(ops), list(args), operands, list(types), ((out.value >> 40) - 1, out.value & ((1 << 40) - 1)),
+            out_type.value, rows.value, cols.value, list(lds), row_result.value)
+
+
+def evaluate(step, runtime_args):
+    """The step's effect on its output argument, computed by the oracle from flat views of the arguments."""
+    ops, args, operands, types, (out_idx, out_off), out_type, rows, cols, lds, row_result = decode(step)
+    inputs = []
+    for (idx, byte_off), ld in zip(operands, lds):
+        flat = runtime_args[idx].reshape(-1)
+        first = byte_off // flat.element_size()
+        if ld == 0:
+            inputs.append(flat[first:first + cols].expand(rows, cols))
+        else:
+            inputs.append(torch.as_strided(flat, (rows, cols), (ld, 1), first))
+    res = E.run_program(ops, args, inputs, out_type)
+    return res[:, 0] if row_result else res
+
+
+def test_layer_norm_is_one_row_program():
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn(64, 512, generator=gen) * 2 + 1
+    gamma, beta = torch.rand(1, 512, generator=gen) + 0.5, torch.randn(1, 512, generator=gen)
+    K.layer_norm_rows[4](x, gamma, beta, torch.empty_like(x), 64, 512, 8, 1e-5)
+    plan = K.layer_norm_rows.last_plan
+    assert plan.pattern == "row:program" and len(plan.steps) == 1 and not plan.partial_writes
+    assert plan.reads == {0, 1, 2} and plan.writes == {3}
+    *_, rows, cols, lds, row_result = decode(plan.steps[0])
+    assert (rows, cols, lds, row_result) == (64, 512, [512, 0, 0, 512], 0)
+    out = evaluate(plan.steps[0], [x, gamma, beta, None])
+    ref = torch.nn.functional.layer_norm(x, (512, ), gamma[0], beta[0], 1e-5)
+    torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-5)
+
+
+def test_scalar_reduction_of_a_one_row_tile():
+    x = torch.randn(48, 256, generator=torch.Generator().manual_seed(4))
+    K.l1_normalize_rows[8](x, torch.empty_like(x), 48, 256)
+    plan = K.l1_normalize_rows.last_plan
+    assert plan.pattern == "row:program" and len(plan.steps) == 1
+    out = evaluate(plan.steps[0], [x, None])
+    torch.testing.assert_close(out, x / (x.abs().sum(1, keepdim=True) + 1e-6), rtol=1e-5, atol=1e-6)
+
+
+def test_per_row_results_of_computed_tiles():
+    x = torch.randn(64, 384, generator=torch.Generator().manual_seed(5))
+    K.row_sum_of_squares[4](x, torch.empty(64), 64, 384, 8)
+    plan = K.row_sum_of_squares.last_plan
+    assert plan.pattern == "row:program" and len(plan.steps) == 1 and not plan.partial_writes
+    *_, rows, cols, lds, row_result = decode(plan.steps[0])
+    assert (rows, cols, lds, row_result) == (64, 384, [384, 1], 1)
+    out = evaluate(plan.steps[0], [x, None])
+    torch.testing.assert_close(out, x.pow(2).sum(1).sqrt() * 0.5 + x.abs().amax(1), rtol=1e-5, atol=1e-6)
+
+
+def test_rows_too_long_for_one_sm_are_refused():
+    x = torch.zeros(2, 16384)
+    with pytest.raises(NotImplementedError, match="must fit one SM"):
+        K.l1_normalize_rows[2](x, torch.empty_like(x), 2, 16384)

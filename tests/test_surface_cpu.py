@@ -143,22 +143,22 @@ def test_workload_scripts_match_at_full_size():
 
 def test_unsupported_pattern_raises_not_implemented():
     @asc2.jit
-    def sum_of_squares(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, r: asc.ConstExpr[int],
-                       c: asc.ConstExpr[int]):
+    def column_sums_of_squares(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, r: asc.ConstExpr[int],
+                               c: asc.ConstExpr[int]):
         x = asc2.load(asc2.tensor(x_ptr, [r, c]), [r, c], offsets=[0, 0])
-        asc2.store(asc2.reduce_sum(x * x, 1), asc2.tensor(out_ptr, [r]), offsets=[0])
+        asc2.store(asc2.reduce_sum(x * x, 0), asc2.tensor(out_ptr, [c]), offsets=[0])
     x = np.zeros((16, 64), np.float32)
     with pytest.raises(NotImplementedError, match="no kernel for this pattern"):
-        sum_of_squares[1](x, np.zeros(16, np.float32), 16, 64)
+        column_sums_of_squares[1](x, np.zeros(64, np.float32), 16, 64)
 
     @asc2.jit
-    def centred(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, r: asc.ConstExpr[int], c: asc.ConstExpr[int]):
-        x = asc2.load(asc2.tensor(x_ptr, [r, c]), [r, c], offsets=[0, 0])
-        asc2.store(x - asc2.reduce_max(x, 1, keep_dims=False).reshape(r, 1).broadcast_to(r, c),
-                   asc2.tensor(out_ptr, [r, c]), offsets=[0, 0])
-    y = np.zeros((16, 64), np.float32)
-    with pytest.raises(NotImplementedError, match="no kernel for this pattern"):
-        centred[1](y, y.copy(), 16, 64)
+    def masked(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+        x = asc2.load(asc2.tensor(x_ptr, [n]), [n], offsets=[0])
+        with asc2.mask(count=8, other=0):
+            y = x + 1
+        asc2.store(y, asc2.tensor(out_ptr, [n]), offsets=[0])
+    with pytest.raises(NotImplementedError, match="mask"):
+        masked[1](np.zeros(64, np.float32), np.zeros(64, np.float32), 64)
 
 
 # ----------------------------------------------------------------------------- reference error behaviour
