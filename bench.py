@@ -44,7 +44,7 @@ import torch  # noqa: E402
 
 HEADLINE = "softmax"
 ALL_WORKLOADS = ["softmax", "vadd", "gemm_f16", "gemm_i8", "gemm_i8_dequant", "attention", "attention_causal",
-                 "gelu", "gelu_tanh", "leaky_relu_bf16", "mish_interpreted", "row_sum", "rms_norm"]
+                 "gelu", "gelu_tanh", "leaky_relu_bf16", "mish_interpreted", "row_sum", "rms_norm", "layer_norm"]
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -372,7 +372,7 @@ class _Elementwise(Workload):
             else:
                 os.environ["DRY_RUN"] = prev
         plan = kernel.last_plan
-        assert plan.pattern == "elementwise:program" and len(plan.steps) == 1, plan
+        assert plan.pattern in ("elementwise:program", "row:program") and len(plan.steps) == 1, plan
         self.step = plan.steps[0]
         self.ptrs = {i: t.data_ptr() for i, t in ptr_args.items()}
 
@@ -569,6 +569,72 @@ class RmsNorm(Workload):
         return 2.0 * 4 * self.CPU_R * self.C
 
 
+class LayerNorm(_Elementwise):
+    """Layer norm written with asc2 reductions and broadcasts (mean, centred variance, scale and shift): one row
+    program over [16384, 4096] fp32 (256 MiB read, 256 MiB written; gamma and beta resident)."""
+    name, label, dtype = "layer_norm", "layer_norm_f32_16384x4096_row_program", "f32"
+    R, C = 16384, 4096
+    EPS = 1e-5
+    work = 2.0 * 4 * R * C
+    h2d_bytes, d2h_bytes = 4 * R * C + 8 * C, 4 * R * C
+    CPU_R = 4096
+    cpu_sample_desc = "torch.nn.functional.layer_norm on 4096 of the 16384 rows"
+
+    @staticmethod
+    def kernel():
+        import pyasc_b200  # noqa: F401  (makes `asc` / `asc2` importable)
+        import asc
+        import asc2
+
+        @asc2.jit
+        def layer_norm_kernel(x_ptr: asc.GlobalAddress, gamma_ptr: asc.GlobalAddress, beta_ptr: asc.GlobalAddress,
+                              out_ptr: asc.GlobalAddress, num_rows: int, num_cols: asc.ConstExpr[int],
+                              rows_per_tile: asc.ConstExpr[int], epsilon: float):
+            x_gm = asc2.tensor(x_ptr, [num_rows, num_cols])
+            out_gm = asc2.tensor(out_ptr, [num_rows, num_cols])
+            gamma = asc2.load(asc2.tensor(gamma_ptr, [1, num_cols]), [1, num_cols], offsets=[0, 0])
+            beta = asc2.load(asc2.tensor(beta_ptr, [1, num_cols]), [1, num_cols], offsets=[0, 0])
+            for i in range(asc2.block_idx() * rows_per_tile, num_rows, asc2.block_num() * rows_per_tile):
+                x = asc2.load(x_gm, [rows_per_tile, num_cols], offsets=[i, 0])
+                mean = (asc2.reduce_sum(x, 1, keep_dims=True) / num_cols).broadcast_to(rows_per_tile, num_cols)
+                xc = x - mean
+                var = (asc2.reduce_sum(xc * xc, 1, keep_dims=True) / num_cols).broadcast_to(rows_per_tile, num_cols)
+                y = xc * asc2.rsqrt(var + epsilon)
+                asc2.store(y * gamma.broadcast_to(rows_per_tile, num_cols) + beta.broadcast_to(rows_per_tile, num_cols),
+                           out_gm, offsets=[i, 0])
+        return layer_norm_kernel
+
+    def setup_device(self, dev):
+        g = torch.Generator(device=dev).manual_seed(2026)
+        self.x = torch.randn((self.R, self.C), device=dev, generator=g)
+        self.gamma = torch.rand((1, self.C), device=dev, generator=g) + 0.5
+        self.beta = torch.randn((1, self.C), device=dev, generator=g)
+        self.out = torch.empty_like(self.x)
+        self.k = self.kernel()
+        self.plan_step(lambda: self.k[148](self.x, self.gamma, self.beta, self.out, self.R, self.C, 4, self.EPS), self.k,
+                       {0: self.x, 1: self.gamma, 2: self.beta, 3: self.out})
+
+    def setup_host(self):
+        g = torch.Generator().manual_seed(2026)
+        self.hx = torch.randn((self.R, self.C), generator=g).pin_memory()
+        self.hgamma = (torch.rand((1, self.C), generator=g) + 0.5).pin_memory()
+        self.hbeta = torch.randn((1, self.C), generator=g).pin_memory()
+        self.hout = torch.empty_like(self.hx).pin_memory()
+        if not hasattr(self, "k"):
+            self.k = self.kernel()
+
+    def e2e_step(self):
+        self.k[148](self.hx, self.hgamma, self.hbeta, self.hout, self.R, self.C, 4, self.EPS)
+
+    def cpu_sample(self):
+        if not hasattr(self, "cx"):
+            g = torch.Generator().manual_seed(2026)
+            self.cx = torch.randn((self.CPU_R, self.C), generator=g)
+            self.cg, self.cb = torch.rand(self.C, generator=g) + 0.5, torch.randn(self.C, generator=g)
+        _ = torch.nn.functional.layer_norm(self.cx, (self.C, ), self.cg, self.cb, self.EPS)
+        return 2.0 * 4 * self.CPU_R * self.C
+
+
 class LeakyReluBF16(_Elementwise):
     name, label, dtype = "leaky_relu_bf16", "leaky_relu_bf16_2^28", "bf16"
     N = 1 << 28
@@ -605,7 +671,7 @@ class LeakyReluBF16(_Elementwise):
 
 
 REGISTRY = {w.name: w for w in (Softmax, VAdd, GemmF16, GemmI8, GemmI8Dequant, Attention, AttentionCausal, Gelu, GeluTanh,
-                                LeakyReluBF16, MishInterpreted, RowSum, RmsNorm)}
+                                LeakyReluBF16, MishInterpreted, RowSum, RmsNorm, LayerNorm)}
 
 
 # ---------------------------------------------------------------------------------------------------

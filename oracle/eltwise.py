@@ -37,6 +37,7 @@ def run_program(ops: Sequence[int], args: Sequence[int], inputs: List[torch.Tens
     the word is untyped."""
     shape = inputs[0].shape
     stack: list = []
+    tmp: dict = {}
 
     def as_float(v):
         return v if isinstance(v, torch.Tensor) else torch.tensor([v], dtype=torch.int32).view(torch.float32).expand(shape)
@@ -90,6 +91,10 @@ def run_program(ops: Sequence[int], args: Sequence[int], inputs: List[torch.Tens
             stack.append(torch.trunc(as_float(stack.pop())).to(torch.int32))
         elif op == 53:
             stack.append(as_int(stack.pop()).to(torch.int16).to(torch.int32))
+        elif op == 63:                        # TEE: copy the top into temporary slot arg
+            tmp[int(arg)] = stack[-1]
+        elif op == 64:                        # TMP: push temporary slot arg
+            stack.append(tmp[int(arg)])
         elif op in _ROW:
             # row programs (asc_cuda_row_program): the reduction over the last dimension replaces every element
             t = as_float(stack.pop()).expand(shape)

@@ -337,6 +337,9 @@ _ROUND_CODE = {"float16": _OP_ROUND_F16, "bfloat16": _OP_ROUND_BF16, "int16": _O
 ELT_MAX_OPS, ELT_MAX_INPUTS, ELT_MAX_STACK = 48, 6, 8
 _ROW_CODE = {"sum": 59, "max": 60, "min": 61, "prod": 62}     # row programs: reduce the top of the stack over the row
 ROW_MAX_COLS = 8192
+ROW_MAX_TMP = 4
+_OP_TEE, _OP_TMP = 63, 64     # row programs: copy the top into / push temporary slot arg
+_MARK_BEGIN, _MARK_END = -1, -2   # pseudo-ops around the code of one traced value (arg: its identity)
 
 
 def _round_const(value: float, dtype: DataType) -> float:
@@ -402,6 +405,7 @@ class _EltProgram:
         self.operands: List[_Operand] = []
         self.reshaped = False       # a reshape was seen: element order is the flat (row-major) order
         self.row_ops = False        # the program reduces over rows: it runs as a row program
+        self.n_tmp = 0              # temporary slots the finished program uses
         self.full_shape: Optional[Tuple[int, ...]] = None   # set while code for a per-row value is generated
         self.ops: List[int] = []
         self.args: List[int] = []
@@ -453,7 +457,20 @@ class _EltProgram:
         return self._load(_Operand(view.tensor, view.offsets, view.shape, bcast))
 
     def gen(self, v: Any, scalar_dtype: Optional[DataType] = None) -> Optional[_Frag]:
-        """Code for ``v``, or None when ``v`` is not expressible."""
+        """Code for ``v``, or None when ``v`` is not expressible.  The code of every traced value is bracketed by
+        markers that name the value, so that ``_finish`` can see which values an expression uses more than once."""
+        frag = self._gen(v, scalar_dtype)
+        if frag is None or frag.word is not None or len(frag.code) < 2:
+            return frag
+        if isinstance(v, Tile):
+            key = id(v.node)
+        elif isinstance(v, PlainValue) and not v.is_const:
+            key = id(v.args[0]) if v.op == "tile_scalar" else id(v)
+        else:
+            return frag
+        return _Frag([(_MARK_BEGIN, key)] + frag.code + [(_MARK_END, key)], frag.need)
+
+    def _gen(self, v: Any, scalar_dtype: Optional[DataType] = None) -> Optional[_Frag]:
         if isinstance(v, PlainValue):
             if v.is_const:
                 return _Frag([], 0, self._word(v.value, scalar_dtype or v.dtype))
@@ -590,14 +607,53 @@ class _EltProgram:
         self.row_ops = True
         return _Frag(inner.code + [(_ROW_CODE[node.attrs["kind"]], 0)], inner.need)
 
+    def _finish(self, frag: _Frag) -> None:
+        """The final program.  In a row program a value that occurs again is computed once: its first occurrence
+        is followed by TEE into a temporary slot, every later one is replaced by TMP (the code of a traced value
+        does not depend on where it is used).  Elsewhere the markers just drop out."""
+        code = frag.pushed().code
+        ends = {}
+        stack: List[int] = []
+        uses: Dict[int, int] = {}
+        parent: Dict[int, Optional[int]] = {}     # the value whose code encloses a value's first occurrence
+        for i, (op, arg) in enumerate(code):
+            if op == _MARK_BEGIN:
+                uses[arg] = uses.get(arg, 0) + 1
+                parent.setdefault(arg, code[stack[-1]][1] if stack else None)
+                stack.append(i)
+            elif op == _MARK_END:
+                ends[stack.pop()] = i
+
+        def shared(key: int) -> bool:
+            # used again on its own, not merely as a part of an enclosing value that is used again
+            return uses[key] > (uses[parent[key]] if parent[key] is not None else 1)
+        out: List[Tuple[int, int]] = []
+        slots: Dict[int, int] = {}
+        i = 0
+        while i < len(code):
+            op, arg = code[i]
+            if op == _MARK_BEGIN:
+                if self.row_ops and arg in slots:
+                    out.append((_OP_TMP, slots[arg]))
+                    i = ends[i] + 1
+                    continue
+            elif op == _MARK_END:
+                if self.row_ops and shared(arg) and arg not in slots and len(slots) < ROW_MAX_TMP:
+                    slots[arg] = len(slots)
+                    out.append((_OP_TEE, slots[arg]))
+            else:
+                out.append((op, arg))
+            i += 1
+        self.ops = [c[0] for c in out]
+        self.args = [c[1] for c in out]
+        self.max_depth = frag.pushed().need
+        self.n_tmp = len(slots)
+
     def compile(self, v: Any) -> bool:
         frag = self.gen(v)
         if frag is None:
             return False
-        frag = frag.pushed()
-        self.ops = [c[0] for c in frag.code]
-        self.args = [c[1] for c in frag.code]
-        self.max_depth = frag.need
+        self._finish(frag)
         return True
 
 
@@ -703,7 +759,7 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
         kv = 1
         while kv * 256 < cols:
             kv *= 2
-        if cols > ROW_MAX_COLS or max(1, prog.max_depth - 1) * kv * 1024 > 200 * 1024:
+        if cols > ROW_MAX_COLS or (max(1, prog.max_depth - 1) + prog.n_tmp) * kv * 1024 > 200 * 1024:
             raise _unsupported(f"row reductions inside an expression over rows of {cols} elements with a stack of "
                                f"{prog.max_depth} (the row and its intermediate values must fit one SM)")
         if out_g.pitch is not None and (out_g.rows, out_g.cols) != (rows, 1 if row_result else cols):
@@ -756,20 +812,35 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
             calls.append((starts, rows))
     else:
         calls = [(starts, rows) for starts in all_starts]
-    for starts, call_rows in calls:
-        def build(ptrs, stream, starts=starts, call_rows=call_rows):
+    def make_step(starts: Tuple[int, ...], call_rows: int) -> Step:
+        def build(ptrs, stream):
             ins = (ctypes.c_void_p * max(1, n_in))(*[ptrs[i] + sz * st for i, sz, st in zip(in_idx, in_size, starts)])
             return (ops_arr, args_arr, ctypes.c_int32(n_ops), ins, types_arr, ctypes.c_int32(n_in),
                     _p(ptrs[out_idx] + out_size * starts[-1]), ctypes.c_int32(out_type), ctypes.c_int64(call_rows),
                     ctypes.c_int64(cols), lds_arr) + tail_args + (stream, )
-        plan.steps.append(Step(fn_name, build,
-                               f"{n_ops} ops over [{call_rows}, {cols}] pitches {lds} from {list(starts[:-1])} to {starts[-1]}"))
+        return Step(fn_name, build,
+                    f"{n_ops} ops over [{call_rows}, {cols}] pitches {lds} from {list(starts[:-1])} to {starts[-1]}")
+
+    for starts, call_rows in calls:
+        plan.steps.append(make_step(starts, call_rows))
     out_cols = 1 if row_result else cols
     covered = sum(r for _, r in calls) * out_cols
     if dedupe and len(calls) == 1 and lds[-1] == out_cols and calls[0][0][-1] == 0 and covered == out_t.base.numel:
         plan.partial_writes.discard(out_idx)
     if not plan.steps:
         raise _unsupported("elementwise kernel without any tile")
+    if row_shape is not None and not plan.partial_writes and len(calls) == 1:
+        # whole rows of whole tensors: chunks of rows can be uploaded, computed and downloaded independently;
+        # a broadcast row is needed by every chunk
+        starts0, total_rows = calls[0]
+        whole = all(st == 0 and (ld == 0 or ld * total_rows == o.tensor.base.numel)
+                    for st, ld, o in zip(starts0, lds, prog.operands))
+        if whole and len(set(in_idx)) == len(in_idx) and out_idx not in in_idx:
+            streamed = {i: sz * ld for i, sz, ld in zip(in_idx, in_size, lds) if ld != 0}
+            streamed[out_idx] = out_size * lds[-1]
+            resident = {i for i, ld in zip(in_idx, lds) if ld == 0}
+            plan.pipeline = PipelineSpec(total_rows, 1, streamed, resident,
+                                         lambda lo, hi: [make_step(tuple(lo * ld for ld in lds), hi - lo)])
     return plan
 
 
@@ -892,8 +963,7 @@ def _match_atomic(trace: KernelTrace, eff: Effect) -> Plan:
     if current is None or update is None:
         raise _unsupported("atomic operation on a tile that is not an elementwise expression of loaded tiles")
     table = _BINARY_CODE if out_t.dtype.is_float() else _INT_BINARY_CODE
-    frag = prog._rounded(prog._binary(table[eff.attrs["kind"]], current, update), out_t.dtype).pushed()
-    prog.ops, prog.args, prog.max_depth = [c[0] for c in frag.code], [c[1] for c in frag.code], frag.need
+    prog._finish(prog._rounded(prog._binary(table[eff.attrs["kind"]], current, update), out_t.dtype))
     _check_program_limits(prog)
     _check_fits(out_t)
     for t in prog.inputs:
@@ -948,8 +1018,7 @@ def _match_row_result(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     frag = prog._per_row(value, full_shape)
     if frag is None or not prog.row_ops:
         return None
-    frag = frag.pushed()
-    prog.ops, prog.args, prog.max_depth = [c[0] for c in frag.code], [c[1] for c in frag.code], frag.need
+    prog._finish(frag)
     _check_program_limits(prog)
     _check_fits(out_t)
     for t in prog.inputs:

@@ -40,7 +40,10 @@ enum EltOp : int32_t {
   // row programs only: replace the top of the stack by its reduction over the row (fp32 words), so that
   // every element of the row sees the reduced value
   OP_ROW_SUM = 59, OP_ROW_MAX = 60, OP_ROW_MIN = 61, OP_ROW_PROD = 62,
-  OP_COUNT = 63,
+  // row programs only: a value the expression uses more than once is computed once.  TEE copies the top of
+  // the stack into temporary slot arg (the stack is unchanged), TMP pushes slot arg.
+  OP_TEE = 63, OP_TMP = 64,
+  OP_COUNT = 65,
   // flag on a binary opcode: the left operand is the 32-bit word in arg instead of a stack entry, so a
   // scalar operand costs neither a push nor a pop (with the swapped forms either side can be the scalar)
   OP_IMM = 0x100,
@@ -49,6 +52,7 @@ enum EltOp : int32_t {
 enum EltType : int32_t { T_F32 = 0, T_F16 = 1, T_BF16 = 2, T_I32 = 3, T_I16 = 4, T_COUNT = 5 };
 
 __host__ __device__ constexpr bool is_row_op(int op) { return op >= OP_ROW_SUM && op <= OP_ROW_PROD; }
+constexpr int kMaxTmp = 4;   // temporary slots of a row program
 
 __host__ __device__ constexpr bool is_binary_op(int op) {
   return (op >= OP_ADD && op <= OP_MIN) || (op >= OP_EQ && op <= OP_LE) || (op >= OP_IADD && op <= OP_ILE) ||
@@ -618,7 +622,7 @@ __device__ __forceinline__ float row_combine(int op, float a, float b) {
 
 template <int kV>
 __global__ void __launch_bounds__(kThreads) row_program_kernel(const __grid_constant__ EltProgram prog, uint32_t rows,
-                                                               int row_result) {
+                                                               int row_result, int tmp_level) {
   extern __shared__ float stack_mem[];
   __shared__ float red[kThreads / 32];
   float* const slots = stack_mem + threadIdx.x;
@@ -696,6 +700,14 @@ __global__ void __launch_bounds__(kThreads) row_program_kernel(const __grid_cons
         ASC_UN(OP_ROUND_BF16) ASC_UN(OP_INEG) ASC_UN(OP_IABS) ASC_UN(OP_IRELU) ASC_UN(OP_CVT_I2F)
         ASC_UN(OP_CVT_F2I) ASC_UN(OP_WRAP_I16)
         ASC_ROW(OP_ROW_SUM) ASC_ROW(OP_ROW_MAX) ASC_ROW(OP_ROW_MIN) ASC_ROW(OP_ROW_PROD)
+        case OP_TEE: {   // temporaries lie above the stack levels in shared memory
+          ASC_PUT(tmp_level + prog.arg[k])
+        } break;
+        case OP_TMP:
+          if (depth > 0) { ASC_PUT(depth - 1) }
+          ++depth;
+          ASC_GET(tmp_level + prog.arg[k], top)
+          break;
         default: break;
       }
     }
@@ -719,9 +731,10 @@ __global__ void __launch_bounds__(kThreads) row_program_kernel(const __grid_cons
 }
 
 template <int kV>
-int32_t launch_row_program(const EltProgram& prog, int64_t rows, int max_depth, int row_result, int sms,
+int32_t launch_row_program(const EltProgram& prog, int64_t rows, int max_depth, int n_tmp, int row_result, int sms,
                            cudaStream_t stream) {
-  const size_t smem = static_cast<size_t>(max_depth > 1 ? max_depth - 1 : 1) * kV * kThreads * sizeof(float);
+  const int tmp_level = max_depth > 1 ? max_depth - 1 : 1;
+  const size_t smem = static_cast<size_t>(tmp_level + n_tmp) * kV * kThreads * sizeof(float);
   if (smem > 200 * 1024) return ASC_ERR_TOO_LARGE;
   if (smem > 48 * 1024) {
     static bool attr_set[64] = {false};
@@ -738,7 +751,7 @@ int32_t launch_row_program(const EltProgram& prog, int64_t rows, int max_depth, 
   int64_t ctas = static_cast<int64_t>(sms) * resident * 4;   // four waves of resident CTAs; CTAs stride over the rows
   if (ctas > rows) ctas = rows;
   row_program_kernel<kV><<<static_cast<unsigned>(ctas), kThreads, smem, stream>>>(prog, static_cast<uint32_t>(rows),
-                                                                                   row_result);
+                                                                                   row_result, tmp_level);
   aschost::count_launch();
   ASC_CUDA_TRY(cudaGetLastError());
   return ASC_OK;
@@ -747,18 +760,29 @@ int32_t launch_row_program(const EltProgram& prog, int64_t rows, int max_depth, 
 // Validates a program on the host (opcodes, operand indices, stack depth) and copies it, with the input
 // pointers and types, into the launch argument.  Row reductions are legal only where the caller says so.
 int32_t fill_program(const int32_t* ops, const int32_t* args, int n_ops, const void* const* inputs,
-                     const int32_t* input_types, int n_inputs, bool row_ops_allowed, EltProgram& prog, int& max_depth) {
+                     const int32_t* input_types, int n_inputs, bool row_ops_allowed, EltProgram& prog, int& max_depth,
+                     int* n_tmp = nullptr) {
   prog.n_ops = n_ops;
   prog.n_inputs = n_inputs;
   int depth = 0;
   max_depth = 0;
+  uint32_t tmp_set = 0;   // slots a TEE has written so far
   for (int k = 0; k < n_ops; ++k) {
     const int op = ops[k] & 0xff;
     const bool imm = (ops[k] & OP_IMM) != 0;
     if (ops[k] < 0 || (ops[k] & ~(0xff | OP_IMM)) != 0 || op >= OP_COUNT) return ASC_ERR_INVALID_ARG;
     if (imm && !is_binary_op(op)) return ASC_ERR_INVALID_ARG;
-    if (is_row_op(op) && !row_ops_allowed) return ASC_ERR_INVALID_ARG;
-    if (op == OP_LOAD) {
+    if ((is_row_op(op) || op == OP_TEE || op == OP_TMP) && !row_ops_allowed) return ASC_ERR_INVALID_ARG;
+    if (op == OP_TEE || op == OP_TMP) {
+      if (args[k] < 0 || args[k] >= kMaxTmp) return ASC_ERR_INVALID_ARG;
+      if (op == OP_TEE) {
+        if (depth < 1) return ASC_ERR_INVALID_ARG;
+        tmp_set |= 1u << args[k];
+      } else {
+        if (((tmp_set >> args[k]) & 1u) == 0) return ASC_ERR_INVALID_ARG;   // read before any write
+        ++depth;
+      }
+    } else if (op == OP_LOAD) {
       if (args[k] < 0 || args[k] >= n_inputs) return ASC_ERR_INVALID_ARG;
       ++depth;
     } else if (op == OP_CONST) {
@@ -778,6 +802,11 @@ int32_t fill_program(const int32_t* ops, const int32_t* args, int n_ops, const v
     prog.arg[k] = args[k];
   }
   if (depth != 1) return ASC_ERR_INVALID_ARG;
+  if (n_tmp != nullptr) {
+    *n_tmp = 0;
+    for (int t = 0; t < kMaxTmp; ++t)
+      if ((tmp_set >> t) & 1u) *n_tmp = t + 1;
+  }
   for (int i = 0; i < n_inputs; ++i) {
     if (inputs[i] == nullptr || input_types[i] < 0 || input_types[i] >= T_COUNT) return ASC_ERR_INVALID_ARG;
     if (reinterpret_cast<uintptr_t>(inputs[i]) % elem_size(input_types[i]) != 0) return ASC_ERR_MISALIGNED;
@@ -885,7 +914,8 @@ extern "C" int32_t asc_cuda_row_program(const int32_t* ops, const int32_t* args,
   if (cols > 32 * kThreads) return ASC_ERR_TOO_LARGE;     // a thread holds at most 32 elements of the row
   EltProgram prog{};
   int max_depth = 0;
-  int32_t rc = fill_program(ops, args, n_ops, inputs, input_types, n_inputs, true, prog, max_depth);
+  int n_tmp = 0;
+  int32_t rc = fill_program(ops, args, n_ops, inputs, input_types, n_inputs, true, prog, max_depth, &n_tmp);
   if (rc != ASC_OK) return rc;
   if (reinterpret_cast<uintptr_t>(out) % elem_size(out_type) != 0) return ASC_ERR_MISALIGNED;
   for (int k = 0; k <= n_inputs; ++k) {
@@ -906,10 +936,10 @@ extern "C" int32_t asc_cuda_row_program(const int32_t* ops, const int32_t* args,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t per_thread = (cols + kThreads - 1) / kThreads;
   const int rr = row_result != 0 ? 1 : 0;
-  if (per_thread <= 1) return launch_row_program<1>(prog, rows, max_depth, rr, sms, st);
-  if (per_thread <= 2) return launch_row_program<2>(prog, rows, max_depth, rr, sms, st);
-  if (per_thread <= 4) return launch_row_program<4>(prog, rows, max_depth, rr, sms, st);
-  if (per_thread <= 8) return launch_row_program<8>(prog, rows, max_depth, rr, sms, st);
-  if (per_thread <= 16) return launch_row_program<16>(prog, rows, max_depth, rr, sms, st);
-  return launch_row_program<32>(prog, rows, max_depth, rr, sms, st);
+  if (per_thread <= 1) return launch_row_program<1>(prog, rows, max_depth, n_tmp, rr, sms, st);
+  if (per_thread <= 2) return launch_row_program<2>(prog, rows, max_depth, n_tmp, rr, sms, st);
+  if (per_thread <= 4) return launch_row_program<4>(prog, rows, max_depth, n_tmp, rr, sms, st);
+  if (per_thread <= 8) return launch_row_program<8>(prog, rows, max_depth, n_tmp, rr, sms, st);
+  if (per_thread <= 16) return launch_row_program<16>(prog, rows, max_depth, n_tmp, rr, sms, st);
+  return launch_row_program<32>(prog, rows, max_depth, n_tmp, rr, sms, st);
 }

@@ -108,12 +108,27 @@ def test_capi_row_result_and_fp16_operands(lib):
     torch.testing.assert_close(out2, x.float().amin(1), rtol=0, atol=0)
 
 
+def test_capi_temporaries(lib):
+    """TEE / TMP: (x - mean) computed once and used three times, as the launcher compiles a layer norm."""
+    x = torch.randn(77, 3000, device="cuda") * 3 + 2
+    out = torch.zeros_like(x)
+    inv_c = f32_word(1.0 / 3000)
+    # LOAD x, LOAD x, ROW_SUM, * 1/C, SUB, TEE 0, TMP 0, MUL, ROW_SUM, * 1/C, + eps, RSQRT, TMP 0, MUL
+    ops = [0, 0, 59, 4 | 0x100, 3, 63, 64, 4, 59, 4 | 0x100, 2 | 0x100, 16, 64, 4]
+    args = [0, 0, 0, inv_c, 0, 0, 0, 0, 0, inv_c, f32_word(1e-5), 0, 0, 0]
+    run_row_program(lib, ops, args, [x], out, 77, 3000, None, 0)
+    torch.testing.assert_close(out, torch.nn.functional.layer_norm(x, (3000, ), eps=1e-5), rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(out.cpu(), E.run_program(ops, args, [x.cpu()], 0), rtol=1e-4, atol=1e-5)
+
+
 def test_capi_row_program_rejections(lib):
     x = torch.zeros(4, 16, device="cuda")
     out = torch.zeros(4, 16, device="cuda")
     run_row_program(lib, [0, 59], [0, 0], [x], out, 4, 8193 * 4, None, 0, expect=6)       # row too long for one SM
     run_row_program(lib, [0, 59], [0, 0], [x], out, 4, 16, [8, 16], 0, expect=1)          # pitch below the row length
-    run_row_program(lib, [0, 63], [0, 0], [x], out, 4, 16, None, 0, expect=1)             # no such opcode
+    run_row_program(lib, [0, 65], [0, 0], [x], out, 4, 16, None, 0, expect=1)             # no such opcode
+    run_row_program(lib, [0, 64, 2], [0, 0, 0], [x], out, 4, 16, None, 0, expect=1)       # temporary read before written
+    run_row_program(lib, [0, 63], [0, 4], [x], out, 4, 16, None, 0, expect=1)             # no such temporary slot
     # the elementwise entry point refuses row opcodes
     ops_arr, args_arr = (ctypes.c_int32 * 2)(0, 59), (ctypes.c_int32 * 2)(0, 0)
     ins, types = (ctypes.c_void_p * 1)(x.data_ptr()), (ctypes.c_int32 * 1)(0)

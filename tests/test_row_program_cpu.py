@@ -51,6 +51,14 @@ def test_layer_norm_is_one_row_program():
     assert plan.reads == {0, 1, 2} and plan.writes == {3}
     *_, rows, cols, lds, row_result = decode(plan.steps[0])
     assert (rows, cols, lds, row_result) == (64, 512, [512, 0, 0, 512], 0)
+    # whole rows of whole tensors: the launcher may stream chunks of rows; gamma and beta stay resident
+    pipe = plan.pipeline
+    assert pipe is not None and pipe.units == 64 and pipe.resident == {1, 2} and pipe.streamed == {0: 2048, 3: 2048}
+    chunk = pipe.make_steps(16, 48)
+    assert len(chunk) == 1 and decode(chunk[0])[2][0] == (0, 16 * 2048) and decode(chunk[0])[6] == 32
+    ops = decode(plan.steps[0])[0]
+    # the centred row is used three times and computed once: two row reductions, one temporary
+    assert sum(1 for o in ops if o in (59, 60, 61, 62)) == 2 and ops.count(63) == 1 and ops.count(64) == 2
     out = evaluate(plan.steps[0], [x, gamma, beta, None])
     ref = torch.nn.functional.layer_norm(x, (512, ), gamma[0], beta[0], 1e-5)
     torch.testing.assert_close(out, ref, rtol=1e-4, atol=1e-5)
