@@ -1,7 +1,8 @@
 """Generates the committed golden fixtures under tests/golden/ with the reference's own CPU
 expressions (torch / NumPy, see oracle/golden.py for the file:line of each).
 
-Run from the repository root:  python tests/golden/make_golden.py   (--only-elementwise: just elementwise_reduce.npz)
+Run from the repository root:  python tests/golden/make_golden.py   (--only-elementwise: just elementwise_reduce.npz;
+--only-normalisation: just normalisation.npz)
 The reference package itself cannot be imported (its compiled MLIR extension and the CANN toolkit are
 absent), so the fixtures come from the torch/NumPy calls its tests make, on the seeds its tests use.
 """
@@ -36,10 +37,27 @@ def elementwise_and_reduce() -> None:
                         prod0=xr.prod(0).numpy())
 
 
+def normalisation() -> None:
+    """RMS norm (the formula of the Ascend C RmsNorm routine asc2.rms_norm lowers to,
+    python/asc/language/tile/unary_ops.py:225-237) and a layer norm, computed in float64 and rounded once."""
+    g = torch.Generator().manual_seed(G.SEED + 1)
+    x = torch.randn((8, 512), generator=g) * 3 + 0.5
+    gamma = torch.rand(512, generator=g) + 0.5
+    beta = torch.randn(512, generator=g)
+    xd, gd, bd = x.double(), gamma.double(), beta.double()
+    rms = xd / torch.sqrt(xd.pow(2).mean(1, keepdim=True) + 1e-5) * gd
+    ln = (xd - xd.mean(1, keepdim=True)) / torch.sqrt(xd.var(1, unbiased=False, keepdim=True) + 1e-5) * gd + bd
+    np.savez_compressed(os.path.join(HERE, "normalisation.npz"), x=x.numpy(), gamma=gamma.numpy(), beta=beta.numpy(),
+                        eps=np.float32(1e-5), rms_norm=rms.float().numpy(), layer_norm=ln.float().numpy())
+
+
 def main() -> None:
     torch.set_num_threads(1)  # fixed summation order for the fp32 reductions
     if "--only-elementwise" in sys.argv:
         elementwise_and_reduce()
+        return
+    if "--only-normalisation" in sys.argv:
+        normalisation()
         return
     # vector add, NumPy form of python/test/asc2/kernels/test_vadd.py:41-48
     rng = np.random.default_rng(seed=2026)
@@ -75,6 +93,7 @@ def main() -> None:
     np.savez_compressed(os.path.join(HERE, "attention.npz"), q=q.numpy(), k=k.numpy(), v=v.numpy(),
                         o=G.attention(q, k, v, False).numpy(), o_causal=G.attention(q, k, v, True).numpy())
     elementwise_and_reduce()
+    normalisation()
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)))

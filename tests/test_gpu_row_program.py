@@ -133,3 +133,17 @@ def test_capi_row_program_rejections(lib):
     ops_arr, args_arr = (ctypes.c_int32 * 2)(0, 59), (ctypes.c_int32 * 2)(0, 0)
     ins, types = (ctypes.c_void_p * 1)(x.data_ptr()), (ctypes.c_int32 * 1)(0)
     assert lib.asc_cuda_eltwise_program(ops_arr, args_arr, 2, ins, types, 1, ctypes.c_void_p(out.data_ptr()), 0, 64, None) == 1
+
+
+def test_golden_fixture_normalisations(golden_dir):
+    import os
+    import numpy as np
+    d = np.load(os.path.join(golden_dir, "normalisation.npz"))
+    x, gamma, beta = (torch.from_numpy(d[k]) for k in ("x", "gamma", "beta"))
+    eps = float(d["eps"])
+    out = torch.zeros_like(x)
+    K.rms_norm_rows[2](x, gamma.reshape(1, -1), out, 8, 512, 4, eps)
+    torch.testing.assert_close(out, torch.from_numpy(d["rms_norm"]), rtol=1e-5, atol=1e-6)
+    out = torch.zeros_like(x)
+    K.layer_norm_rows[2](x, gamma.reshape(1, -1), beta.reshape(1, -1), out, 8, 512, 4, eps)
+    torch.testing.assert_close(out, torch.from_numpy(d["layer_norm"]), rtol=1e-5, atol=2e-6)

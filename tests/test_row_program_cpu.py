@@ -88,3 +88,17 @@ def test_rows_too_long_for_one_sm_are_refused():
     x = torch.zeros(2, 16384)
     with pytest.raises(NotImplementedError, match="must fit one SM"):
         K.l1_normalize_rows[2](x, torch.empty_like(x), 2, 16384)
+
+
+def test_golden_fixture_normalisations(golden_dir):
+    """The committed float64-derived vectors pin the oracle's rms_norm and the compiled layer-norm program."""
+    import os
+    import numpy as np
+    from oracle import golden
+    d = np.load(os.path.join(golden_dir, "normalisation.npz"))
+    x, gamma, beta = (torch.from_numpy(d[k]) for k in ("x", "gamma", "beta"))
+    eps = float(d["eps"])
+    torch.testing.assert_close(golden.rms_norm(x, gamma, eps), torch.from_numpy(d["rms_norm"]), rtol=1e-5, atol=1e-6)
+    K.layer_norm_rows[2](x, gamma.reshape(1, -1), beta.reshape(1, -1), torch.empty_like(x), 8, 512, 4, eps)
+    out = evaluate(K.layer_norm_rows.last_plan.steps[0], [x, gamma.reshape(1, -1), beta.reshape(1, -1), None])
+    torch.testing.assert_close(out, torch.from_numpy(d["layer_norm"]), rtol=1e-5, atol=2e-6)
