@@ -620,6 +620,50 @@ __device__ __forceinline__ float row_combine(int op, float a, float b) {
   return op == OP_ROW_SUM ? __fadd_rn(a, b) : op == OP_ROW_PROD ? __fmul_rn(a, b) : op == OP_ROW_MAX ? fmaxf(a, b) : fminf(a, b);
 }
 
+__device__ __forceinline__ int16_t word_to_i16(float v) { return static_cast<int16_t>(__float_as_int(v)); }
+
+// The lanes of one thread for one operand: element c = thread + e * 256 of row `base`.  The element type is
+// resolved once per operand, and a row that fills every lane skips the bounds checks.
+template <int kV>
+__device__ __forceinline__ void row_load(const void* p, int type, int64_t base, uint32_t cols, bool full, float (&v)[kV]) {
+#define ASC_ROW_LOAD(T, CONV)                                                         \
+  {                                                                                   \
+    const T* q = reinterpret_cast<const T*>(p) + base + threadIdx.x;                  \
+    if (full) {                                                                       \
+      _Pragma("unroll") for (int e = 0; e < kV; ++e) v[e] = CONV(q[e * kThreads]);    \
+    } else {                                                                          \
+      _Pragma("unroll") for (int e = 0; e < kV; ++e)                                  \
+        v[e] = threadIdx.x + e * kThreads < cols ? CONV(q[e * kThreads]) : 0.f;       \
+    }                                                                                 \
+  }
+  switch (type) {
+    case T_F16: ASC_ROW_LOAD(__half, __half2float) break;
+    case T_BF16: ASC_ROW_LOAD(__nv_bfloat16, __bfloat162float) break;
+    case T_I32: ASC_ROW_LOAD(int32_t, __int_as_float) break;
+    case T_I16: ASC_ROW_LOAD(int16_t, __int_as_float) break;
+    default: ASC_ROW_LOAD(float, ) break;
+  }
+#undef ASC_ROW_LOAD
+}
+
+template <int kV>
+__device__ __forceinline__ void row_store(void* p, int type, int64_t base, uint32_t cols, bool full, const float (&v)[kV]) {
+#define ASC_ROW_STORE(T, CONV)                                                          \
+  {                                                                                     \
+    T* q = reinterpret_cast<T*>(p) + base + threadIdx.x;                                \
+    _Pragma("unroll") for (int e = 0; e < kV; ++e)                                      \
+      if (full || threadIdx.x + e * kThreads < cols) q[e * kThreads] = CONV(v[e]);      \
+  }
+  switch (type) {
+    case T_F16: ASC_ROW_STORE(__half, __float2half_rn) break;
+    case T_BF16: ASC_ROW_STORE(__nv_bfloat16, __float2bfloat16_rn) break;
+    case T_I32: ASC_ROW_STORE(int32_t, __float_as_int) break;
+    case T_I16: ASC_ROW_STORE(int16_t, word_to_i16) break;
+    default: ASC_ROW_STORE(float, ) break;
+  }
+#undef ASC_ROW_STORE
+}
+
 template <int kV>
 __global__ void __launch_bounds__(kThreads) row_program_kernel(const __grid_constant__ EltProgram prog, uint32_t rows,
                                                                int row_result, int tmp_level) {
@@ -627,28 +671,65 @@ __global__ void __launch_bounds__(kThreads) row_program_kernel(const __grid_cons
   __shared__ float red[kThreads / 32];
   float* const slots = stack_mem + threadIdx.x;
   const uint32_t cols = prog.cols;
+  const bool full = cols == kV * kThreads;
+  // The two upper stack entries (`top`, and `nos` below it) are registers; only entries below them live in
+  // shared memory: entry d (0 = bottom) of a stack of `depth` entries is at level d for d < depth - 2.  The
+  // expression compiler orders operands so that most programs never go deeper than two.
 #define ASC_LANES _Pragma("unroll") for (int e = 0; e < kV; ++e)
-#define ASC_PUT(LEVEL) ASC_LANES slots[((LEVEL) * kV + e) * kThreads] = top[e];
+#define ASC_PUT(LEVEL, SRC) ASC_LANES slots[((LEVEL) * kV + e) * kThreads] = SRC[e];
 #define ASC_GET(LEVEL, DST) ASC_LANES DST[e] = slots[((LEVEL) * kV + e) * kThreads];
-#define ASC_BIN(CODE)                                      \
-  case CODE: {                                             \
-    float lhs[kV];                                         \
-    if (imm) {                                             \
-      ASC_LANES lhs[e] = __int_as_float(prog.arg[k]);      \
-    } else {                                               \
-      ASC_GET(depth - 2, lhs)                              \
-      --depth;                                             \
-    }                                                      \
-    ASC_LANES top[e] = apply_binary(CODE, lhs[e], top[e]); \
+  // top_u / nos_u: every lane of the entry holds the same value (a constant, a row reduction, or a function of
+  // those).  Unary operations and operations with an immediate then run once instead of once per lane, which
+  // is what keeps `sum / n` and `rsqrt(var + eps)` (IEEE division, square root) off the per-element path.
+#define ASC_PUSH(UNIFORM)                          \
+  {                                                \
+    if (depth >= 2) { ASC_PUT(depth - 2, nos) }    \
+    if (depth >= 1) {                              \
+      ASC_LANES nos[e] = top[e];                   \
+      nos_u = top_u;                               \
+    }                                              \
+    top_u = UNIFORM;                               \
+    ++depth;                                       \
+  }
+#define ASC_REFILL()                              \
+  if (depth >= 2) {                               \
+    ASC_GET(depth - 2, nos)                       \
+    nos_u = false;                                \
+  }
+#define ASC_BIN(CODE)                                               \
+  case CODE: {                                                      \
+    if (imm) {                                                      \
+      const float w = __int_as_float(prog.arg[k]);                  \
+      if (top_u) {                                                  \
+        const float t = apply_binary(CODE, w, top[0]);              \
+        ASC_LANES top[e] = t;                                       \
+      } else {                                                      \
+        ASC_LANES top[e] = apply_binary(CODE, w, top[e]);           \
+      }                                                             \
+    } else {                                                        \
+      ASC_LANES top[e] = apply_binary(CODE, nos[e], top[e]);        \
+      top_u = top_u && nos_u;                                       \
+      --depth;                                                      \
+      ASC_REFILL()                                                  \
+    }                                                               \
   } break;
-#define ASC_UN(CODE)                              \
-  case CODE:                                      \
-    ASC_LANES top[e] = apply_unary(CODE, top[e]); \
+#define ASC_UN(CODE)                                \
+  case CODE:                                        \
+    if (top_u) {                                    \
+      const float t = apply_unary(CODE, top[0]);    \
+      ASC_LANES top[e] = t;                         \
+    } else {                                        \
+      ASC_LANES top[e] = apply_unary(CODE, top[e]); \
+    }                                               \
     break;
 #define ASC_ROW(CODE)                                                                              \
   case CODE: {                                                                                     \
     float v = row_identity(CODE);                                                                  \
-    ASC_LANES if (threadIdx.x + e * kThreads < cols) v = row_combine(CODE, v, top[e]);             \
+    if (full) {                                                                                    \
+      ASC_LANES v = row_combine(CODE, v, top[e]);                                                  \
+    } else {                                                                                       \
+      ASC_LANES if (threadIdx.x + e * kThreads < cols) v = row_combine(CODE, v, top[e]);           \
+    }                                                                                              \
     _Pragma("unroll") for (int o = 16; o > 0; o >>= 1) v = row_combine(CODE, v, __shfl_xor_sync(0xffffffffu, v, o)); \
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;                                        \
     __syncthreads();                                                                               \
@@ -656,9 +737,11 @@ __global__ void __launch_bounds__(kThreads) row_program_kernel(const __grid_cons
     _Pragma("unroll") for (int w = 1; w < kThreads / 32; ++w) v = row_combine(CODE, v, red[w]);    \
     __syncthreads();                                                                               \
     ASC_LANES top[e] = v;                                                                          \
+    top_u = true;                                                                                  \
   } break;
   for (uint32_t r = blockIdx.x; r < rows; r += gridDim.x) {
-    float top[kV];
+    float top[kV], nos[kV];
+    bool top_u = false, nos_u = false;
     int depth = 0;
 #pragma unroll 1
     for (int k = 0; k < prog.n_ops; ++k) {
@@ -666,28 +749,21 @@ __global__ void __launch_bounds__(kThreads) row_program_kernel(const __grid_cons
       const bool imm = (prog.op[k] & OP_IMM) != 0;
       switch (op) {
         case OP_LOAD: {
-          if (depth > 0) { ASC_PUT(depth - 1) }
-          ++depth;
+          ASC_PUSH(false)
           const int input = prog.arg[k];
-          const void* p = prog.in[input];
-          const int type = prog.in_type[input] & 0xff;
-          const int64_t base = static_cast<int64_t>(r) * prog.ld[input];
-          ASC_LANES {
-            const uint32_t c = threadIdx.x + e * kThreads;
-            top[e] = c < cols ? load_elem(p, type, base + c) : 0.f;
-          }
+          row_load<kV>(prog.in[input], prog.in_type[input] & 0xff, static_cast<int64_t>(r) * prog.ld[input], cols, full, top);
         } break;
         case OP_CONST:
-          if (depth > 0) { ASC_PUT(depth - 1) }
-          ++depth;
+          ASC_PUSH(true)
           ASC_LANES top[e] = __int_as_float(prog.arg[k]);
           break;
         case OP_WHERE: {
-          float a[kV], c[kV];
-          ASC_GET(depth - 2, a)
+          float c[kV];
           ASC_GET(depth - 3, c)
+          ASC_LANES top[e] = c[e] != 0.f ? nos[e] : top[e];
+          top_u = false;
           depth -= 2;
-          ASC_LANES top[e] = c[e] != 0.f ? a[e] : top[e];
+          ASC_REFILL()
         } break;
         ASC_BIN(OP_ADD) ASC_BIN(OP_SUB) ASC_BIN(OP_MUL) ASC_BIN(OP_DIV) ASC_BIN(OP_MAX) ASC_BIN(OP_MIN)
         ASC_BIN(OP_EQ) ASC_BIN(OP_NE) ASC_BIN(OP_GT) ASC_BIN(OP_GE) ASC_BIN(OP_LT) ASC_BIN(OP_LE)
@@ -701,11 +777,10 @@ __global__ void __launch_bounds__(kThreads) row_program_kernel(const __grid_cons
         ASC_UN(OP_CVT_F2I) ASC_UN(OP_WRAP_I16)
         ASC_ROW(OP_ROW_SUM) ASC_ROW(OP_ROW_MAX) ASC_ROW(OP_ROW_MIN) ASC_ROW(OP_ROW_PROD)
         case OP_TEE: {   // temporaries lie above the stack levels in shared memory
-          ASC_PUT(tmp_level + prog.arg[k])
+          ASC_PUT(tmp_level + prog.arg[k], top)
         } break;
         case OP_TMP:
-          if (depth > 0) { ASC_PUT(depth - 1) }
-          ++depth;
+          ASC_PUSH(false)
           ASC_GET(tmp_level + prog.arg[k], top)
           break;
         default: break;
@@ -716,15 +791,14 @@ __global__ void __launch_bounds__(kThreads) row_program_kernel(const __grid_cons
       // the program ends in a value that is the same for the whole row: one element per row is stored
       if (threadIdx.x == 0) store_elem(prog.out, prog.out_type, out_base, top[0]);
     } else {
-      ASC_LANES {
-        const uint32_t c = threadIdx.x + e * kThreads;
-        if (c < cols) store_elem(prog.out, prog.out_type, out_base + c, top[e]);
-      }
+      row_store<kV>(prog.out, prog.out_type, out_base, cols, full, top);
     }
   }
 #undef ASC_ROW
 #undef ASC_UN
 #undef ASC_BIN
+#undef ASC_REFILL
+#undef ASC_PUSH
 #undef ASC_GET
 #undef ASC_PUT
 #undef ASC_LANES
@@ -733,7 +807,7 @@ __global__ void __launch_bounds__(kThreads) row_program_kernel(const __grid_cons
 template <int kV>
 int32_t launch_row_program(const EltProgram& prog, int64_t rows, int max_depth, int n_tmp, int row_result, int sms,
                            cudaStream_t stream) {
-  const int tmp_level = max_depth > 1 ? max_depth - 1 : 1;
+  const int tmp_level = max_depth > 2 ? max_depth - 2 : 1;   // the two upper stack entries are registers
   const size_t smem = static_cast<size_t>(tmp_level + n_tmp) * kV * kThreads * sizeof(float);
   if (smem > 200 * 1024) return ASC_ERR_TOO_LARGE;
   if (smem > 48 * 1024) {

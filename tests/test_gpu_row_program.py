@@ -121,6 +121,22 @@ def test_capi_temporaries(lib):
     torch.testing.assert_close(out.cpu(), E.run_program(ops, args, [x.cpu()], 0), rtol=1e-4, atol=1e-5)
 
 
+def test_capi_row_uniform_values(lib):
+    """Values that are the same for the whole row (constants, reductions and functions of them) take a
+    once-per-row path in the kernel; mixed with per-element operands and a select they must still be exact."""
+    x = torch.randn(40, 1500, device="cuda")
+    out = torch.zeros_like(x)
+    # LOAD x, 0 > x (immediate), CONST 2, SQRT, LOAD x, ROW_MAX, ADD -> u = sqrt(2) + max(x), TEE 0, LOAD x, MUL,
+    # TMP 0, WHERE: x < 0 ? x * u : u
+    ops = [0, 28 | 0x100, 1, 15, 0, 60, 2, 63, 0, 4, 64, 32]
+    args = [0, f32_word(0.0), f32_word(2.0), 0, 0, 0, 0, 0, 0, 0, 0, 0]
+    run_row_program(lib, ops, args, [x], out, 40, 1500, None, 0)
+    ref = E.run_program(ops, args, [x.cpu()], 0)
+    u = torch.sqrt(torch.tensor(2.0)) + x.cpu().amax(1, keepdim=True)
+    torch.testing.assert_close(ref, torch.where(x.cpu() < 0, x.cpu() * u, u.expand_as(x.cpu())), rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(out.cpu(), ref, rtol=1e-6, atol=1e-6)
+
+
 def test_capi_row_program_rejections(lib):
     x = torch.zeros(4, 16, device="cuda")
     out = torch.zeros(4, 16, device="cuda")
