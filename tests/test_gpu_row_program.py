@@ -2,6 +2,7 @@
 and the C-ABI entry point against the CPU oracle's evaluation of the same program."""
 import ctypes
 
+import numpy as np
 import pytest
 import torch
 
@@ -163,3 +164,76 @@ def test_golden_fixture_normalisations(golden_dir):
     out = torch.zeros_like(x)
     K.layer_norm_rows[2](x, gamma.reshape(1, -1), beta.reshape(1, -1), out, 8, 512, 4, eps)
     torch.testing.assert_close(out, torch.from_numpy(d["layer_norm"]), rtol=1e-5, atol=2e-6)
+
+
+# ------------------------------------------------------------------------------- random programs
+def _random_row_program(rng, n_inputs):
+    """A random valid row program over fp32 words: arithmetic, comparisons, selects and immediates as in the
+    elementwise fuzz, plus row maxima / minima of subexpressions and temporaries (all exact operations, so the
+    device must agree with the oracle bit for bit)."""
+    binary = [2, 3, 4, 6, 7, 54]
+    unary = [8, 9, 10, 24, 25]
+    compare = [26, 27, 28, 29, 30, 31]
+    code = []
+    slots = []
+
+    def const():
+        return f32_word(float(np.float32(rng.uniform(-2, 2))))
+
+    def gen(depth):
+        kind = int(rng.integers(0, 9)) if depth > 0 else 0
+        if kind == 0:
+            code.append((0, int(rng.integers(0, n_inputs))))
+        elif kind == 1:
+            gen(depth - 1)
+            code.append((int(rng.choice(unary)), 0))
+        elif kind == 2:
+            gen(depth - 1)
+            gen(depth - 1)
+            code.append((int(rng.choice(binary)), 0))
+        elif kind == 3:
+            gen(depth - 1)
+            code.append((int(rng.choice(binary)) | 0x100, const()))
+        elif kind == 4:
+            gen(depth - 1)
+            gen(depth - 1)
+            code.append((int(rng.choice(compare)), 0))
+            gen(depth - 1)
+            gen(depth - 1)
+            code.append((32, 0))
+        elif kind in (5, 6):
+            gen(depth - 1)
+            code.append((int(rng.choice([60, 61])), 0))          # ROW_MAX / ROW_MIN
+        elif kind == 7 and len(slots) < 4:
+            gen(depth - 1)
+            slots.append(len(slots))
+            code.append((63, slots[-1]))                          # TEE
+        elif kind == 8 and slots:
+            code.append((64, int(rng.choice(slots))))             # TMP
+        else:
+            code.append((1, const()))
+    gen(4)
+    return [c[0] for c in code], [c[1] for c in code]
+
+
+@pytest.mark.parametrize("seed", range(32))
+def test_random_row_programs_bit_exact(lib, seed):
+    import numpy as np
+    rng = np.random.default_rng(1000 + seed)
+    n_inputs = int(rng.integers(1, 4))
+    ops, args = _random_row_program(rng, n_inputs)
+    depth = peak = 0
+    for op in ops:
+        code, imm = op & 0xff, bool(op & 0x100)
+        depth += 1 if code in (0, 1, 64) else -2 if code == 32 else 0 if imm or code in (8, 9, 10, 24, 25, 60, 61, 63) else -1
+        peak = max(peak, depth)
+    if len(ops) > 48 or peak > 8:
+        pytest.skip("program beyond the documented limits")
+    rows = int(rng.choice([1, 3, 70]))
+    cols = int(rng.choice([1, 37, 256, 1000, 4096, 5000]))
+    gen = torch.Generator().manual_seed(seed)
+    inputs = [torch.rand(rows, cols, generator=gen) * 8 - 4 for _ in range(n_inputs)]
+    want = E.run_program(ops, args, inputs, 0)
+    out = torch.zeros(rows, cols, device="cuda")
+    run_row_program(lib, ops, args, [t.cuda() for t in inputs], out, rows, cols, None, 0)
+    assert torch.equal(out.cpu(), want), f"{ops} {args}"
