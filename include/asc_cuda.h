@@ -158,6 +158,8 @@ int32_t asc_cuda_eltwise_program_2d(const int32_t* ops, const int32_t* args, int
  * variance) is one pass: a row never leaves the SM between its load and its store.  lds as for the 2-D
  * elementwise call (NULL: all pitches equal cols).  row_result != 0: the program's value is uniform along the
  * row and one element per row is stored, at out[r * lds[n_inputs]] (pitch 1 when lds is NULL).
+ * An input type with bit 0x200 set marks an input that holds one element per row (a column: element r at
+ * inputs[k][r * lds[k]], pitch 1 when lds is NULL), which every element of the row reads.
  * Replaces the chains of vector calls and ReduceOp calls the reference lowers such kernels to
  * (python/asc/language/tile/reduction_ops.py, shape_ops.py:30-75; lib/Conversion/LowerToAsc/LowerAscTile.cpp:
  * 329-378 BroadcastOp, 428-459 ReduceOp; the manual softmax of python/test/asc2/kernels/test_softmax.py:16-27 is

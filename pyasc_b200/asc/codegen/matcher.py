@@ -338,6 +338,7 @@ ELT_MAX_OPS, ELT_MAX_INPUTS, ELT_MAX_STACK = 48, 6, 8
 _ROW_CODE = {"sum": 59, "max": 60, "min": 61, "prod": 62}     # row programs: reduce the top of the stack over the row
 ROW_MAX_COLS = 8192
 ROW_MAX_TMP = 4
+_ROW_SCALAR_INPUT = 0x200    # flag on an input type: one element per row (address = row * pitch)
 _OP_TEE, _OP_TMP = 63, 64     # row programs: copy the top into / push temporary slot arg
 _MARK_BEGIN, _MARK_END = -1, -2   # pseudo-ops around the code of one traced value (arg: its identity)
 
@@ -377,16 +378,18 @@ class _Operand:
     """One LOAD source of a program: the tile of ``shape`` loaded from ``tensor`` at ``offsets``.  ``bcast``: the
     tile is a single row that every row of the result repeats; ``scalar``: one element (a scalar load)."""
 
-    __slots__ = ("tensor", "offsets", "shape", "bcast", "scalar")
+    __slots__ = ("tensor", "offsets", "shape", "bcast", "scalar", "per_row")
 
     def __init__(self, tensor: Tensor, offsets: Sequence[PlainValue], shape: Tuple[int, ...], bcast: bool = False,
-                 scalar: bool = False):
+                 scalar: bool = False, per_row: bool = False):
         self.tensor, self.offsets, self.shape, self.bcast, self.scalar = tensor, tuple(offsets), tuple(shape), bcast, scalar
+        self.per_row = per_row      # one element per row of the result, repeated along the row (row programs)
 
     def same(self, o: "_Operand") -> bool:
         return (self.tensor.base.index == o.tensor.base.index and self.tensor.dtype == o.tensor.dtype
                 and self.tensor.static_shape() == o.tensor.static_shape() and self.shape == o.shape
-                and self.bcast == o.bcast and self.scalar == o.scalar and _same_offsets(self.offsets, o.offsets))
+                and self.bcast == o.bcast and self.scalar == o.scalar and self.per_row == o.per_row
+                and _same_offsets(self.offsets, o.offsets))
 
     def addressed_like(self, out_t: Tensor, offsets: Sequence[PlainValue], shape: Tuple[int, ...]) -> bool:
         """Same tile of a same-shaped tensor as the store: element i of the operand is element i of the result."""
@@ -504,6 +507,13 @@ class _EltProgram:
         if v.shape != self.shape:
             return None
         if node.kind in ("load", "copy"):
+            if self.full_shape is not None:
+                # a loaded column: one element per row of the result; only a row program can address it
+                view = resolve_view(v)
+                if view is None or not _is_zero_pad(view):
+                    return None
+                self.row_ops = True
+                return self._load(_Operand(view.tensor, view.offsets, view.shape, per_row=True))
             return self._view_operand(v)
         if node.kind == "reshape":
             # row-major element order is kept, so elementwise code commutes with the reshape
@@ -725,7 +735,8 @@ class _Geometry:
 def _program_arrays(prog: "_EltProgram", out_t: Tensor):
     n_ops, n_in = len(prog.ops), len(prog.operands)
     return (n_ops, n_in, (ctypes.c_int32 * n_ops)(*prog.ops), (ctypes.c_int32 * n_ops)(*prog.args),
-            (ctypes.c_int32 * max(1, n_in))(*[_ELT_TYPE[t.dtype.name] for t in prog.inputs]), _ELT_TYPE[out_t.dtype.name])
+            (ctypes.c_int32 * max(1, n_in))(*[_ELT_TYPE[o.tensor.dtype.name] | (_ROW_SCALAR_INPUT if o.per_row else 0)
+                                              for o in prog.operands]), _ELT_TYPE[out_t.dtype.name])
 
 
 def _check_program_limits(prog: "_EltProgram") -> None:
@@ -770,7 +781,14 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
         raise _unsupported("reshape of a tile that is not a contiguous range of its tensor")
     lds: List[int] = []
     for o, g in zip(prog.operands, geoms):
-        if o.bcast:
+        if o.per_row:
+            if g.pitch is None and g.numel == rows:
+                lds.append(1)                     # a contiguous [rows] vector
+            elif g.pitch is not None and (g.rows, g.cols) == (rows, 1):
+                lds.append(g.pitch)               # a column of a matrix
+            else:
+                raise _unsupported("column operand that does not hold one element per row of the result")
+        elif o.bcast:
             if g.numel != cols:
                 raise _unsupported("broadcast of a tile that is not one row of the result")
             lds.append(0)
@@ -1025,6 +1043,60 @@ def _match_row_result(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         _check_fits(t)
     return _plan_general_program(trace, eff, prog, out_t, offsets, value.shape, False, None, dedupe=True,
                                  row_shape=(full_shape[0], full_shape[1]), row_result=True)
+
+
+def _find_scalar_reduction(v: Any, depth: int = 0) -> Optional[Node]:
+    """The first whole-tile reduction in the expression tree of the scalar ``v``."""
+    if depth > 64 or not isinstance(v, PlainValue) or v.op in ("const", "sym"):
+        return None
+    if v.op == "tile_scalar":
+        node = v.args[0]
+        return node if node.kind == "reduce" and node.attrs["dims"] == () else None
+    for a in v.args:
+        found = _find_scalar_reduction(a, depth + 1)
+        if found is not None:
+            return found
+    return None
+
+
+def _match_row_scalar(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
+    """``store(f(reduce(g(row))), tensor, offsets)``: one element computed from whole-tile reductions of an
+    elementwise expression over a one-row tile (also wrapped in ``asc2.full([1], ...)``, the reference's idiom for
+    storing a scalar).  A row program over that row with one stored element."""
+    value, out_t = eff.args
+    if eff.kind != "store_scalar" or out_t.dtype != KT.float32:
+        return None
+    v = value
+    if isinstance(v, Tile):
+        full = _node(v, "full")
+        if full is None:
+            return None
+        v = full.attrs["value"]
+    if not isinstance(v, PlainValue) or v.is_const or v.dtype != KT.float32:
+        return None
+    red = _find_scalar_reduction(v)
+    if red is None:
+        return None
+    src = red.args[0]
+    rows = 1
+    for d in src.shape[:-1]:
+        rows *= d
+    if rows != 1:
+        return None
+    if v.op == "tile_scalar" and v.args[0] is red and src.node.kind in ("load", "copy"):
+        return None                        # a reduction of a loaded tile has its own kernel
+    offsets = eff.attrs["offsets"]
+    prog = _EltProgram(src.shape, offsets, out_t)
+    frag = prog.gen(v, KT.float32)
+    if frag is None or not prog.row_ops:
+        return None
+    prog._finish(frag)
+    _check_program_limits(prog)
+    _check_fits(out_t)
+    for t in prog.inputs:
+        _check_fits(t)
+    return _plan_general_program(trace, eff, prog, out_t, offsets, (1, ), True, None, dedupe=True,
+                                 row_shape=(1, src.shape[-1]), row_result=True)
 
 
 # --------------------------------------------------------------------------------------------------
@@ -1734,7 +1806,7 @@ def _match_attention(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
 # Entry point
 # --------------------------------------------------------------------------------------------------
 _MATCHERS = (_match_attention, _match_softmax, _match_rms_norm, _match_elementwise, _match_matmul, _match_eltwise_program,
-             _match_row_result, _match_reduce)
+             _match_row_result, _match_row_scalar, _match_reduce)
 
 
 def _is_identity_store(eff: Effect) -> bool:
@@ -1786,7 +1858,7 @@ def build_plan(trace: KernelTrace) -> Plan:
             continue        # a tile stored back to where it was loaded from changes nothing
         plan = None
         scalar_value = not isinstance(eff.args[0], Tile)
-        for matcher in ((_match_atomic, ) if eff.kind == "atomic" else (_match_eltwise_program, ) if scalar_value
+        for matcher in ((_match_atomic, ) if eff.kind == "atomic" else (_match_eltwise_program, _match_row_scalar) if scalar_value
                         else _MATCHERS):
             plan = matcher(trace, eff)
             if plan is not None:

@@ -88,6 +88,7 @@ __device__ __forceinline__ int64_t element_offset(const EltProgram& prog, int op
 
 constexpr int kThreads = 256;
 constexpr int kReusedInput = 0x100;  // flag in EltProgram::in_type: the program loads this input more than once
+constexpr int kRowScalarInput = 0x200;  // row programs, flag in the caller's input type: one element per row, at row * pitch
 constexpr int kQuadStride = kThreads * 4;  // elements between the quads one thread owns inside a CTA tile
 
 // four consecutive elements starting at element index i (i % 4 == 0, base aligned to four elements:
@@ -749,9 +750,15 @@ __global__ void __launch_bounds__(kThreads) row_program_kernel(const __grid_cons
       const bool imm = (prog.op[k] & OP_IMM) != 0;
       switch (op) {
         case OP_LOAD: {
-          ASC_PUSH(false)
           const int input = prog.arg[k];
-          row_load<kV>(prog.in[input], prog.in_type[input] & 0xff, static_cast<int64_t>(r) * prog.ld[input], cols, full, top);
+          if (prog.in_type[input] & kRowScalarInput) {
+            ASC_PUSH(true)
+            const float v = load_elem(prog.in[input], prog.in_type[input] & 0xff, static_cast<int64_t>(r) * prog.ld[input]);
+            ASC_LANES top[e] = v;
+          } else {
+            ASC_PUSH(false)
+            row_load<kV>(prog.in[input], prog.in_type[input] & 0xff, static_cast<int64_t>(r) * prog.ld[input], cols, full, top);
+          }
         } break;
         case OP_CONST:
           ASC_PUSH(true)
@@ -882,12 +889,14 @@ int32_t fill_program(const int32_t* ops, const int32_t* args, int n_ops, const v
       if ((tmp_set >> t) & 1u) *n_tmp = t + 1;
   }
   for (int i = 0; i < n_inputs; ++i) {
-    if (inputs[i] == nullptr || input_types[i] < 0 || input_types[i] >= T_COUNT) return ASC_ERR_INVALID_ARG;
-    if (reinterpret_cast<uintptr_t>(inputs[i]) % elem_size(input_types[i]) != 0) return ASC_ERR_MISALIGNED;
+    const int row_scalar = row_ops_allowed ? (input_types[i] & kRowScalarInput) : 0;
+    const int type = input_types[i] & ~row_scalar;
+    if (inputs[i] == nullptr || type < 0 || type >= T_COUNT) return ASC_ERR_INVALID_ARG;
+    if (reinterpret_cast<uintptr_t>(inputs[i]) % elem_size(type) != 0) return ASC_ERR_MISALIGNED;
     prog.in[i] = inputs[i];
     int loads = 0;
     for (int k = 0; k < n_ops; ++k) loads += (prog.op[k] == OP_LOAD && prog.arg[k] == i) ? 1 : 0;
-    prog.in_type[i] = input_types[i] | (loads > 1 ? kReusedInput : 0);
+    prog.in_type[i] = type | row_scalar | (loads > 1 ? kReusedInput : 0);
   }
   return ASC_OK;
 }
@@ -996,7 +1005,9 @@ extern "C" int32_t asc_cuda_row_program(const int32_t* ops, const int32_t* args,
     const bool is_out = k == n_inputs;
     int64_t ld = lds != nullptr ? lds[k] : (is_out && row_result ? 1 : cols);
     const int64_t least = is_out ? (row_result ? 1 : cols) : 0;       // an input pitch of 0 is a broadcast row
-    if (ld < least || (!is_out && ld != 0 && ld < cols)) return ASC_ERR_INVALID_ARG;
+    const bool row_scalar = !is_out && (input_types[k] & kRowScalarInput) != 0;   // one element per row: any pitch
+    if (lds == nullptr && row_scalar) ld = 1;
+    if (ld < least || (!is_out && !row_scalar && ld != 0 && ld < cols)) return ASC_ERR_INVALID_ARG;
     if (ld >= (int64_t{1} << 32)) return ASC_ERR_TOO_LARGE;
     prog.ld[k] = static_cast<uint32_t>(ld);
   }

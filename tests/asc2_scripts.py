@@ -439,3 +439,29 @@ def row_sum_of_squares(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, num
     for r0 in asc2.range(asc2.block_idx() * block_size, num_rows, asc2.block_num() * block_size):
         x = asc2.load(x_gm, [block_size, num_cols], offsets=[r0, 0])
         asc2.store(asc2.sqrt(asc2.reduce_sum(x * x, 1)) * 0.5 + asc2.reduce_max(asc2.abs(x), 1), out_gm, offsets=[r0])
+
+
+@asc2.jit
+def row_norms_scalar(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, num_rows: int, num_cols: asc.ConstExpr[int]):
+    """One scalar per row, stored the way the reference stores scalars: through a one-element tile."""
+    x_gm = asc2.tensor(x_ptr, [num_rows, num_cols])
+    out_gm = asc2.tensor(out_ptr, [num_rows])
+    for i in asc2.range(asc2.block_idx(), num_rows, asc2.block_num()):
+        row = asc2.load(x_gm, [1, num_cols], offsets=[i, 0])
+        energy = asc2.reduce_sum(row * row) / num_cols + asc2.reduce_max(asc2.abs(row))
+        asc2.store(asc2.full([1], energy, dtype=row.dtype), out_gm, offsets=[i])
+
+
+@asc2.jit
+def scale_rows(x_ptr: asc.GlobalAddress, scale_ptr: asc.GlobalAddress, bias_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress,
+               num_rows: int, num_cols: asc.ConstExpr[int], block_size: asc.ConstExpr[int]):
+    """out[r, c] = x[r, c] * scale[r] + bias[r]: loaded [rows] vectors, each element repeated along its row."""
+    x_gm = asc2.tensor(x_ptr, [num_rows, num_cols])
+    out_gm = asc2.tensor(out_ptr, [num_rows, num_cols])
+    scale_gm = asc2.tensor(scale_ptr, [num_rows])
+    bias_gm = asc2.tensor(bias_ptr, [num_rows])
+    for r0 in asc2.range(asc2.block_idx() * block_size, num_rows, asc2.block_num() * block_size):
+        x = asc2.load(x_gm, [block_size, num_cols], offsets=[r0, 0])
+        scale = asc2.load(scale_gm, [block_size], offsets=[r0]).reshape(block_size, 1).broadcast_to(block_size, num_cols)
+        bias = asc2.expand_dims(asc2.load(bias_gm, [block_size], offsets=[r0]), 1).broadcast_to(block_size, num_cols)
+        asc2.store(x * scale + bias, out_gm, offsets=[r0, 0])

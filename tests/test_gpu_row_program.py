@@ -45,6 +45,21 @@ def test_l1_normalize_and_row_results():
     torch.testing.assert_close(res, xd.pow(2).sum(1).sqrt() * 0.5 + xd.abs().amax(1), rtol=1e-5, atol=1e-6)
 
 
+def test_scalar_store_of_reductions_of_a_computed_row():
+    x = torch.randn(200, 1024, generator=torch.Generator().manual_seed(12))
+    out = torch.zeros(200)
+    K.row_norms_scalar[8](x, out, 200, 1024)
+    torch.testing.assert_close(out, x.pow(2).sum(1) / 1024 + x.abs().amax(1), rtol=1e-5, atol=1e-6)
+
+
+def test_loaded_columns_repeat_along_the_row():
+    gen = torch.Generator().manual_seed(13)
+    x, scale, bias = torch.randn(96, 640, generator=gen), torch.randn(96, generator=gen), torch.randn(96, generator=gen)
+    out = torch.zeros_like(x)
+    K.scale_rows[4](x, scale, bias, out, 96, 640, 8)
+    assert torch.equal(out, x * scale[:, None] + bias[:, None])
+
+
 # ------------------------------------------------------------------------------- C ABI
 @pytest.fixture(scope="module")
 def lib():
@@ -62,12 +77,13 @@ SOFTMAX_TIMES_Y = ([0, 60, 0, 54, 11, 0, 60, 0, 54, 11, 59, 5, 0, 4],
                    [0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 1, 0])
 
 
-def run_row_program(lib, ops, args, inputs, out, rows, cols, lds, row_result, expect=0):
+def run_row_program(lib, ops, args, inputs, out, rows, cols, lds, row_result, expect=0, flags=None):
     n_in = len(inputs)
     ops_arr = (ctypes.c_int32 * len(ops))(*ops)
     args_arr = (ctypes.c_int32 * len(ops))(*args)
     ins = (ctypes.c_void_p * max(1, n_in))(*[t.data_ptr() for t in inputs])
-    types = (ctypes.c_int32 * max(1, n_in))(*[{torch.float32: 0, torch.float16: 1}[t.dtype] for t in inputs])
+    types = (ctypes.c_int32 * max(1, n_in))(*[{torch.float32: 0, torch.float16: 1}[t.dtype] | (flags[i] if flags else 0)
+                                              for i, t in enumerate(inputs)])
     lds_arr = (ctypes.c_int64 * len(lds))(*lds) if lds is not None else None
     rc = lib.asc_cuda_row_program(ops_arr, args_arr, len(ops), ins, types, n_in, ctypes.c_void_p(out.data_ptr()),
                                   {torch.float32: 0, torch.float16: 1}[out.dtype], rows, cols, lds_arr, row_result, None)
@@ -136,6 +152,21 @@ def test_capi_row_uniform_values(lib):
     u = torch.sqrt(torch.tensor(2.0)) + x.cpu().amax(1, keepdim=True)
     torch.testing.assert_close(ref, torch.where(x.cpu() < 0, x.cpu() * u, u.expand_as(x.cpu())), rtol=1e-6, atol=1e-6)
     torch.testing.assert_close(out.cpu(), ref, rtol=1e-6, atol=1e-6)
+
+
+def test_capi_one_element_per_row_inputs(lib):
+    """Input type bit 0x200: a column of a matrix (pitch 8) and a contiguous vector, each read once per row."""
+    x = torch.randn(300, 777, device="cuda")
+    m = torch.randn(300, 8, device="cuda")
+    v = torch.randn(300, device="cuda")
+    out = torch.zeros_like(x)
+    # LOAD x, LOAD column, MUL, LOAD vector, ADD
+    run_row_program(lib, [0, 0, 4, 0, 2], [0, 1, 0, 2, 0], [x, m, v], out, 300, 777, [777, 8, 1, 777], 0, flags=[0, 0x200, 0x200])
+    assert torch.equal(out, x * m[:, :1] + v[:, None])
+    # the elementwise entry point does not know the flag
+    ops_arr, args_arr = (ctypes.c_int32 * 1)(0), (ctypes.c_int32 * 1)(0)
+    ins, types = (ctypes.c_void_p * 1)(x.data_ptr()), (ctypes.c_int32 * 1)(0x200)
+    assert lib.asc_cuda_eltwise_program(ops_arr, args_arr, 1, ins, types, 1, ctypes.c_void_p(out.data_ptr()), 0, 64, None) == 1
 
 
 def test_capi_row_program_rejections(lib):

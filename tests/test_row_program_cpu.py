@@ -30,10 +30,12 @@ def evaluate(step, runtime_args):
     """The step's effect on its output argument, computed by the oracle from flat views of the arguments."""
     ops, args, operands, types, (out_idx, out_off), out_type, rows, cols, lds, row_result = decode(step)
     inputs = []
-    for (idx, byte_off), ld in zip(operands, lds):
+    for (idx, byte_off), ld, type_word in zip(operands, lds, types):
         flat = runtime_args[idx].reshape(-1)
         first = byte_off // flat.element_size()
-        if ld == 0:
+        if type_word & 0x200:       # one element per row
+            inputs.append(torch.as_strided(flat, (rows, 1), (ld, 1), first).expand(rows, cols))
+        elif ld == 0:
             inputs.append(flat[first:first + cols].expand(rows, cols))
         else:
             inputs.append(torch.as_strided(flat, (rows, cols), (ld, 1), first))
@@ -82,6 +84,29 @@ def test_per_row_results_of_computed_tiles():
     assert (rows, cols, lds, row_result) == (64, 384, [384, 1], 1)
     out = evaluate(plan.steps[0], [x, None])
     torch.testing.assert_close(out, x.pow(2).sum(1).sqrt() * 0.5 + x.abs().amax(1), rtol=1e-5, atol=1e-6)
+
+
+def test_scalar_store_of_reductions_of_a_computed_row():
+    x = torch.randn(64, 512, generator=torch.Generator().manual_seed(6))
+    K.row_norms_scalar[8](x, torch.empty(64), 64, 512)
+    plan = K.row_norms_scalar.last_plan
+    assert plan.pattern == "row:program" and len(plan.steps) == 1 and not plan.partial_writes
+    *_, rows, cols, lds, row_result = decode(plan.steps[0])
+    assert (rows, cols, lds, row_result) == (64, 512, [512, 1], 1)
+    out = evaluate(plan.steps[0], [x, None])
+    torch.testing.assert_close(out, x.pow(2).sum(1) / 512 + x.abs().amax(1), rtol=1e-5, atol=1e-6)
+
+
+def test_loaded_columns_repeat_along_the_row():
+    gen = torch.Generator().manual_seed(8)
+    x, scale, bias = torch.randn(64, 256, generator=gen), torch.randn(64, generator=gen), torch.randn(64, generator=gen)
+    K.scale_rows[4](x, scale, bias, torch.empty_like(x), 64, 256, 8)
+    plan = K.scale_rows.last_plan
+    assert plan.pattern == "row:program" and len(plan.steps) == 1 and not plan.partial_writes
+    ops, args, operands, types, _, _, rows, cols, lds, row_result = decode(plan.steps[0])
+    assert (rows, cols, lds, row_result) == (64, 256, [256, 1, 1, 256], 0) and types[:3] == [0, 0x200, 0x200]
+    out = evaluate(plan.steps[0], [x, scale, bias, None])
+    assert torch.equal(out, x * scale[:, None] + bias[:, None])
 
 
 def test_rows_too_long_for_one_sm_are_refused():
