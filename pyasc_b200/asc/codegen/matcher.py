@@ -978,7 +978,7 @@ def _match_atomic(trace: KernelTrace, eff: Effect) -> Plan:
     prog = _EltProgram(value.shape, offsets, out_t)
     current = prog._load(_Operand(out_t, offsets, value.shape))
     update = prog.gen(value)
-    if current is None or update is None:
+    if current is None or update is None or prog.row_ops:
         raise _unsupported("atomic operation on a tile that is not an elementwise expression of loaded tiles")
     table = _BINARY_CODE if out_t.dtype.is_float() else _INT_BINARY_CODE
     prog._finish(prog._rounded(prog._binary(table[eff.attrs["kind"]], current, update), out_t.dtype))
