@@ -11,8 +11,10 @@
 //               tcgen05.commit releases the stage and, after the last K block, publishes the
 //               accumulator.
 //   warps 2-5   epilogue: tcgen05.ld their 32-lane quarter of the accumulator, apply the
-//               epilogue and store 16-byte vectors; the other accumulator is being filled
-//               meanwhile, so the epilogue of tile i overlaps the main loop of tile i+1.
+//               epilogue and store 16-byte vectors (in the CTA-pair kernel 16-bit outputs pass
+//               through shared memory so that stores cover whole 128-byte lines); the other
+//               accumulator is being filled meanwhile, so the epilogue of tile i overlaps the
+//               main loop of tile i+1.
 // B is never transposed in memory: the MN-major shared-memory descriptor lets the tensor core
 // read it as stored.  All waits are bounded (see common.cuh).
 #include <cuda_fp16.h>
@@ -344,6 +346,52 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
   }
 }
 
+// 16-bit outputs, a chunk that lies wholly inside C: the warp's 32 rows x 64 columns (128 bytes per row) pass
+// through shared memory so that every store instruction writes four whole 128-byte lines instead of 16 bytes
+// in each of 32 rows.  16-byte pieces are XOR-swizzled by the row, so both the row-per-thread writes and the
+// line-per-8-threads reads are free of bank conflicts.
+__device__ __forceinline__ void staged_store_64cols(uint32_t stage_smem, const uint32_t (&packed)[32], uint16_t* c,
+                                                     int64_t ldc, int64_t row0, int64_t col0, uint32_t lane) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const uint32_t addr = stage_smem + lane * 128 + ((j ^ (lane & 7)) << 4);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * j]), "r"(packed[4 * j + 1]),
+                 "r"(packed[4 * j + 2]), "r"(packed[4 * j + 3])
+                 : "memory");
+  }
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t r = 4 * i + (lane >> 3), piece = lane & 7;
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(stage_smem + r * 128 + ((piece ^ (r & 7)) << 4))
+                 : "memory");
+    *reinterpret_cast<uint4*>(c + (row0 + r) * ldc + col0 + piece * 8) = v;
+  }
+  __syncwarp();
+}
+
+template <int kMode>
+__device__ __forceinline__ void pack16(const GemmParams& p, const uint32_t (&r)[32], uint32_t* packed) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    float a = __uint_as_float(r[2 * i]), b = __uint_as_float(r[2 * i + 1]);
+    if (p.relu) {
+      a = fmaxf(a, 0.f);
+      b = fmaxf(b, 0.f);
+    }
+    if (kMode == EPI_F16) {
+      __half2 h = __floats2half2_rn(a, b);
+      packed[i] = *reinterpret_cast<uint32_t*>(&h);
+    } else {
+      __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+      packed[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------------------------
 // CTA-pair variant (cta_group::2): two CTAs of a cluster compute one 256 x 256 tile.  Each CTA
 // stages its own 128 rows of A and its own 128 columns of B, so every SM reads and fills half as
@@ -355,7 +403,9 @@ constexpr int kPairStages = 6;
 constexpr int kPairHalfN = kBlockN / 2;                          // columns of B staged per CTA
 constexpr uint32_t kPairSmemB = kPairHalfN * kKBytes;            // 16 KiB
 constexpr uint32_t kPairStageBytes = kSmemA + kPairSmemB;        // 32 KiB per CTA and stage
-constexpr uint32_t kPairSmem = kPairStages * kPairStageBytes + 1024;
+constexpr uint32_t kPairStageRing = kPairStages * kPairStageBytes;
+constexpr uint32_t kEpiStageBytes = 32 * 128;                    // one epilogue warp: 32 rows of 128 output bytes
+constexpr uint32_t kPairSmem = kPairStageRing + 4 * kEpiStageBytes + 1024;
 
 struct PairCtl {
   uint64_t full[kPairStages];    // used in the even CTA: both CTAs' loads of a stage have landed
@@ -506,14 +556,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       ok = mbar_wait_warp<kWaitHintNs>(smem_u32(&ctl.tmem_full[acc]), acc_phase, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL);
       if (!ok) break;
       tc_fence_after();
-      const int64_t row = m_blk * kPairM + rank * kBlockM + quarter * 32 + lane;
+      const int64_t row0 = m_blk * kPairM + rank * kBlockM + quarter * 32;
+      const int64_t row = row0 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * kBlockN;
+      if ((kMode == EPI_F16 || kMode == EPI_BF16) && p.vec_ok && row0 + 32 <= p.M &&
+          (n_blk + 1) * kBlockN <= p.N) {
+        const uint32_t stage_smem = smem_base + kPairStageRing + quarter * kEpiStageBytes;
 #pragma unroll 1
-      for (int c = 0; c < kBlockN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, r);
-        tmem_ld_wait();
-        epilogue_store_chunk<kMode>(p, r, row, n_blk * kBlockN + c * 32);
+        for (int c = 0; c < kBlockN / 64; ++c) {
+          uint32_t r0[32], r1[32], packed[32];
+          tmem_ld_32x32b_x32(taddr + c * 64, r0);
+          tmem_ld_32x32b_x32(taddr + c * 64 + 32, r1);
+          tmem_ld_wait();
+          pack16<kMode>(p, r0, packed);
+          pack16<kMode>(p, r1, packed + 16);
+          staged_store_64cols(stage_smem, packed, reinterpret_cast<uint16_t*>(p.c), p.ldc, row0, n_blk * kBlockN + c * 64,
+                              lane);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < kBlockN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          epilogue_store_chunk<kMode>(p, r, row, n_blk * kBlockN + c * 32);
+        }
       }
       tc_fence_before();
       __syncwarp();
