@@ -409,6 +409,7 @@ class _EltProgram:
         self.reshaped = False       # a reshape was seen: element order is the flat (row-major) order
         self.row_ops = False        # the program reduces over rows: it runs as a row program
         self.n_tmp = 0              # temporary slots the finished program uses
+        self.visits = 0             # values visited while generating code
         self.full_shape: Optional[Tuple[int, ...]] = None   # set while code for a per-row value is generated
         self.ops: List[int] = []
         self.args: List[int] = []
@@ -462,6 +463,11 @@ class _EltProgram:
     def gen(self, v: Any, scalar_dtype: Optional[DataType] = None) -> Optional[_Frag]:
         """Code for ``v``, or None when ``v`` is not expressible.  The code of every traced value is bracketed by
         markers that name the value, so that ``_finish`` can see which values an expression uses more than once."""
+        self.visits += 1
+        if self.visits > 8 * ELT_MAX_OPS * ELT_MAX_OPS:
+            # an expression graph that shares subexpressions unfolds into a tree here; one that unfolds into far
+            # more nodes than a program may hold is refused before the unfolding takes exponential time
+            raise _unsupported(f"elementwise expression that unfolds into more than {self.visits - 1} operations")
         frag = self._gen(v, scalar_dtype)
         if frag is None or frag.word is not None or len(frag.code) < 2:
             return frag
@@ -994,10 +1000,12 @@ def _match_atomic(trace: KernelTrace, eff: Effect) -> Plan:
 # --------------------------------------------------------------------------------------------------
 # Pattern: one value per row, computed from reductions of elementwise expressions along the row
 # --------------------------------------------------------------------------------------------------
-def _find_row_reduction(v: Any, depth: int = 0) -> Optional[Node]:
-    """The first reduction along the last dimension of a 2-D tile in the expression tree of ``v``."""
-    if depth > 64:
+def _find_row_reduction(v: Any, depth: int = 0, seen: Optional[set] = None) -> Optional[Node]:
+    """The first reduction along the last dimension of a 2-D tile in the expression graph of ``v``."""
+    seen = set() if seen is None else seen
+    if depth > 64 or id(v) in seen:
         return None
+    seen.add(id(v))
     if isinstance(v, PlainValue):
         args = v.args if v.op not in ("const", "sym") else ()
     elif isinstance(v, Tile):
@@ -1010,7 +1018,7 @@ def _find_row_reduction(v: Any, depth: int = 0) -> Optional[Node]:
     else:
         return None
     for a in args:
-        found = _find_row_reduction(a, depth + 1)
+        found = _find_row_reduction(a, depth + 1, seen)
         if found is not None:
             return found
     return None
@@ -1816,6 +1824,30 @@ def _is_identity_store(eff: Effect) -> bool:
             and view.tensor.static_shape() == out_t.static_shape() and _same_offsets(view.offsets, eff.attrs["offsets"]))
 
 
+def _value_from_deeper_loop(value: Any, loops: Tuple[Loop, ...]) -> bool:
+    """True when the stored value (or a value it is computed from) was produced inside a loop that does not
+    enclose the store: a tile carried from one iteration to the next, or out of its loop.  A loop body is traced
+    once, so such a value stands for a single iteration; only the matmul patterns, which read a sum over the
+    loop out of it, may accept one."""
+    seen = set()
+    stack = [value]
+    while stack:
+        v = stack.pop()
+        if id(v) in seen:
+            continue
+        seen.add(id(v))
+        if isinstance(v, Tile):
+            v = v.node
+        if isinstance(v, Node):
+            if len(v.loops) > len(loops) or any(a is not b for a, b in zip(v.loops, loops)):
+                return True
+            stack.extend(v.args)
+            stack.extend(a for a in v.attrs.values() if isinstance(a, (Tile, PlainValue)))
+        elif isinstance(v, PlainValue) and v.op not in ("const", "sym"):
+            stack.extend(v.args)
+    return False
+
+
 def _split_concat_store(eff: Effect) -> List[Effect]:
     """A store of ``concat(a, b, ...)`` (python/asc/language/tile/creation_ops.py:56-72: tiles joined along the
     first dimension) writes each part at its row offset inside the stored window, so it is planned as one store
@@ -1858,11 +1890,19 @@ def build_plan(trace: KernelTrace) -> Plan:
             continue        # a tile stored back to where it was loaded from changes nothing
         plan = None
         scalar_value = not isinstance(eff.args[0], Tile)
-        for matcher in ((_match_atomic, ) if eff.kind == "atomic" else (_match_eltwise_program, _match_row_scalar) if scalar_value
-                        else _MATCHERS):
+        matchers = (_match_atomic, ) if eff.kind == "atomic" else (_match_eltwise_program, _match_row_scalar) if scalar_value \
+            else _MATCHERS
+        carried = _value_from_deeper_loop(eff.args[0], eff.loops)
+        if carried:
+            # only the matmul patterns read a loop-carried value as a sum over the loop
+            matchers = tuple(m for m in matchers if m in (_match_matmul, _match_attention))
+        for matcher in matchers:
             plan = matcher(trace, eff)
             if plan is not None:
                 break
+        if plan is None and carried:
+            raise _unsupported(f"tile carried across iterations of a loop (or out of it) in kernel '{trace.fn_name}'; "
+                               "only matmul accumulation over a loop is recognised")
         if plan is None:
             value = eff.args[0]
             kind = value.node.kind if isinstance(value, Tile) else type(value).__name__

@@ -196,3 +196,29 @@ def test_sigmoid_and_silu_compile_to_the_specialised_programs():
     silu[1](x, out, 256)
     assert decode(silu.last_plan.steps[0])[0] == [0, 0, 8, 11, 2 | 0x100, 5]
     torch.testing.assert_close(evaluate(silu, [x, out]), torch.nn.functional.silu(x), rtol=1e-6, atol=1e-6)
+
+
+def test_expression_graph_that_explodes_as_a_tree_is_refused_quickly():
+    """y = y + y forty times: 2^40 leaves as a tree; the compiler must refuse it instead of unfolding it."""
+    @asc2.jit
+    def doubling(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+        y = asc2.load(asc2.tensor(x_ptr, [n]), [n], offsets=[0])
+        for _ in asc.static_range(40):
+            y = y * 2 + y
+        asc2.store(y, asc2.tensor(out_ptr, [n]), offsets=[0])
+    with pytest.raises(NotImplementedError, match="unfolds into more than"):
+        doubling[1](torch.zeros(64), torch.zeros(64), 64)
+
+
+def test_tile_carried_across_loop_iterations_is_refused():
+    """A loop body is traced once, so a tile that one iteration hands to the next cannot be represented: the
+    launcher must say so instead of computing a single iteration."""
+    @asc2.jit
+    def running_sum(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int], reps: int):
+        x_gm = asc2.tensor(x_ptr, [reps * n])
+        acc = asc2.zeros([n], dtype=asc.float32)
+        for i in range(reps):
+            acc = acc + asc2.load(x_gm, [n], offsets=[i * n])
+        asc2.store(acc, asc2.tensor(out_ptr, [n]), offsets=[0])
+    with pytest.raises(NotImplementedError, match="carried across iterations"):
+        running_sum[1](torch.zeros(256), torch.zeros(64), 64, 4)
