@@ -1848,6 +1848,28 @@ def _value_from_deeper_loop(value: Any, loops: Tuple[Loop, ...]) -> bool:
     return False
 
 
+def _loads_of(value: Any) -> List[Node]:
+    """The load nodes the value is computed from."""
+    found: List[Node] = []
+    seen = set()
+    stack = [value]
+    while stack:
+        v = stack.pop()
+        if id(v) in seen:
+            continue
+        seen.add(id(v))
+        if isinstance(v, Tile):
+            v = v.node
+        if isinstance(v, Node):
+            if v.kind in ("load", "load_scalar"):
+                found.append(v)
+            stack.extend(v.args)
+            stack.extend(a for a in v.attrs.values() if isinstance(a, (Tile, PlainValue)))
+        elif isinstance(v, PlainValue) and v.op not in ("const", "sym"):
+            stack.extend(v.args)
+    return found
+
+
 def _split_concat_store(eff: Effect) -> List[Effect]:
     """A store of ``concat(a, b, ...)`` (python/asc/language/tile/creation_ops.py:56-72: tiles joined along the
     first dimension) writes each part at its row offset inside the stored window, so it is planned as one store
@@ -1862,7 +1884,9 @@ def _split_concat_store(eff: Effect) -> List[Effect]:
         attrs = dict(eff.attrs)
         attrs["offsets"] = (offsets[0] + row, ) + tuple(offsets[1:])
         kind = "store_scalar" if part.size == 1 else "store"
-        parts += _split_concat_store(Effect(kind, (part, out_t), attrs, eff.loops))
+        piece = Effect(kind, (part, out_t), attrs, eff.loops)
+        piece.uid = eff.uid            # the parts take the place of the store in program order
+        parts += _split_concat_store(piece)
         row += part.shape[0]
     return parts
 
@@ -1885,11 +1909,30 @@ def build_plan(trace: KernelTrace) -> Plan:
         raise _unsupported("kernel without a tile store")
     total = Plan("")
     names = []
+    written: Dict[int, int] = {}       # runtime-argument index -> uid of the first effect that writes it
+    windows: Dict[int, list] = {}      # runtime-argument index -> (offsets, shape, loop nest) of every store to it
     for eff in stores:
         if eff.kind != "atomic" and _is_identity_store(eff):
             continue        # a tile stored back to where it was loaded from changes nothing
         plan = None
         scalar_value = not isinstance(eff.args[0], Tile)
+        # The plan runs effect after effect, each over all blocks and iterations.  A tile that the kernel loaded
+        # *before* an earlier effect overwrote its tensor would be read after that write here: refuse.
+        for ld in _loads_of(eff.args[0]):
+            src = ld.args[0]
+            first_write = written.get(src.base.index) if isinstance(src, Tensor) else None
+            if first_write is not None and ld.uid < first_write:
+                raise _unsupported(f"kernel '{trace.fn_name}' uses a tile it loaded before an earlier store to the same "
+                                   "tensor")
+            if first_write is not None and (trace.core_num > 1 or eff.loops or ld.loops):
+                # data an earlier effect produced: every block and iteration must read exactly the window it wrote
+                # itself, otherwise "all of effect A, then all of effect B" differs from the kernel's own order
+                for w_offsets, w_shape, w_loops in windows.get(src.base.index, []):
+                    same = (ld.kind == "load" and tuple(ld.attrs["shape"]) == tuple(w_shape) and w_loops == ld.loops
+                            and _same_offsets(ld.attrs["offsets"], w_offsets))
+                    if not same:
+                        raise _unsupported(f"kernel '{trace.fn_name}' reads a tensor back at other positions than an "
+                                           "earlier store of the same kernel wrote")
         matchers = (_match_atomic, ) if eff.kind == "atomic" else (_match_eltwise_program, _match_row_scalar) if scalar_value \
             else _MATCHERS
         carried = _value_from_deeper_loop(eff.args[0], eff.loops)
@@ -1907,6 +1950,10 @@ def build_plan(trace: KernelTrace) -> Plan:
             value = eff.args[0]
             kind = value.node.kind if isinstance(value, Tile) else type(value).__name__
             raise _unsupported(f"store of a tile produced by '{kind}' in kernel '{trace.fn_name}'")
+        written.setdefault(eff.args[1].base.index, eff.uid)
+        stored = eff.args[0]
+        windows.setdefault(eff.args[1].base.index, []).append(
+            (eff.attrs["offsets"], stored.shape if isinstance(stored, Tile) else (1, ), eff.loops))
         names.append(plan.pattern)
         total.steps += plan.steps
         total.reads |= plan.reads

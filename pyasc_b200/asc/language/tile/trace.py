@@ -60,13 +60,14 @@ class Node:
 class Effect:
     """A side effect in program order: ``store``, ``matmul_acc`` or ``atomic``."""
 
-    __slots__ = ("kind", "args", "attrs", "loops")
+    __slots__ = ("kind", "args", "attrs", "loops", "uid")
 
     def __init__(self, kind: str, args: Tuple[Any, ...], attrs: dict, loops: Tuple[Loop, ...]):
         self.kind = kind
         self.args = args
         self.attrs = attrs
         self.loops = loops
+        self.uid = next(Node._ids)    # one counter with the nodes: program order of operations and effects
 
     def __repr__(self) -> str:
         return f"Effect({self.kind}, {self.attrs}, loops={list(self.loops)})"

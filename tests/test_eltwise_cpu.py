@@ -222,3 +222,46 @@ def test_tile_carried_across_loop_iterations_is_refused():
         asc2.store(acc, asc2.tensor(out_ptr, [n]), offsets=[0])
     with pytest.raises(NotImplementedError, match="carried across iterations"):
         running_sum[1](torch.zeros(256), torch.zeros(64), 64, 4)
+
+
+def test_tile_loaded_before_an_overwrite_of_its_tensor_is_refused():
+    """Effects run one after the other over all blocks, so a tile loaded before a store to its tensor and used
+    after it would see the new contents: the launcher must refuse; loading again after the store is fine."""
+    @asc2.jit
+    def stale(x_ptr: asc.GlobalAddress, z_ptr: asc.GlobalAddress, y_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+        x_gm, z_gm, y_gm = (asc2.tensor(p, [n]) for p in (x_ptr, z_ptr, y_ptr))
+        old = asc2.load(x_gm, [n], offsets=[0])
+        asc2.store(asc2.load(z_gm, [n], offsets=[0]) * 2, x_gm, offsets=[0])
+        asc2.store(old + 1, y_gm, offsets=[0])
+    with pytest.raises(NotImplementedError, match="loaded before an earlier store"):
+        stale[1](torch.zeros(64), torch.zeros(64), torch.zeros(64), 64)
+
+    @asc2.jit
+    def fresh(x_ptr: asc.GlobalAddress, z_ptr: asc.GlobalAddress, y_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+        x_gm, z_gm, y_gm = (asc2.tensor(p, [n]) for p in (x_ptr, z_ptr, y_ptr))
+        asc2.store(asc2.load(z_gm, [n], offsets=[0]) * 2, x_gm, offsets=[0])
+        asc2.store(asc2.load(x_gm, [n], offsets=[0]) + 1, y_gm, offsets=[0])
+    fresh[1](torch.zeros(64), torch.zeros(64), torch.zeros(64), 64)
+    assert len(fresh.last_plan.steps) == 2
+
+
+def test_reading_back_another_blocks_output_is_refused():
+    @asc2.jit
+    def neighbour(z_ptr: asc.GlobalAddress, x_ptr: asc.GlobalAddress, y_ptr: asc.GlobalAddress, n: asc.ConstExpr[int],
+                  total: asc.ConstExpr[int]):
+        z_gm, x_gm, y_gm = (asc2.tensor(p, [total]) for p in (z_ptr, x_ptr, y_ptr))
+        i = asc2.block_idx() * n
+        asc2.store(asc2.load(z_gm, [n], offsets=[i]) * 2, x_gm, offsets=[i])
+        asc2.store(asc2.load(x_gm, [n], offsets=[0]) + 1, y_gm, offsets=[i])      # block 0's output, read by all
+    with pytest.raises(NotImplementedError, match="reads a tensor back at other positions"):
+        neighbour[4](torch.zeros(256), torch.zeros(256), torch.zeros(256), 64, 256)
+
+    @asc2.jit
+    def own(z_ptr: asc.GlobalAddress, x_ptr: asc.GlobalAddress, y_ptr: asc.GlobalAddress, n: asc.ConstExpr[int],
+            total: asc.ConstExpr[int]):
+        z_gm, x_gm, y_gm = (asc2.tensor(p, [total]) for p in (z_ptr, x_ptr, y_ptr))
+        i = asc2.block_idx() * n
+        asc2.store(asc2.load(z_gm, [n], offsets=[i]) * 2, x_gm, offsets=[i])
+        asc2.store(asc2.load(x_gm, [n], offsets=[i]) + 1, y_gm, offsets=[i])      # each block reads what it wrote
+    own[4](torch.zeros(256), torch.zeros(256), torch.zeros(256), 64, 256)
+    assert len(own.last_plan.steps) == 2
