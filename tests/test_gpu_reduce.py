@@ -184,18 +184,22 @@ def test_golden_fixture(golden_dir):
             torch.testing.assert_close(out, want, rtol=1e-5, atol=1e-5)
 
 
-@pytest.mark.parametrize("rows, cols", [(3, 7), (257, 4096), (8, 60000), (4, 70001)])
+@pytest.mark.parametrize("rows, cols", [(3, 7), (257, 4096), (8, 60000), (4, 70001), (1000, 8), (513, 1000), (300, 2048),
+                                        (77, 8192), (33, 16384), (65536, 2048)])
 def test_capi_softmax_f16(lib, rows, cols):
-    """fp16 rows: registers-free generic path, rows staged in shared memory and rows too long for it."""
+    """fp16 rows: every depth of the register kernel (whole 16-byte vectors up to 16384 columns, 256 MiB beyond L2
+    included) and the generic path for odd lengths, odd pitches and longer rows (rows staged in shared memory and
+    rows too long for it)."""
     gen = torch.Generator(device="cuda").manual_seed(rows + cols)
-    x = (torch.randn(rows, cols + 1, device="cuda", generator=gen) * 3).half()
+    pad = 8 if cols % 8 == 0 and rows != 257 else 1      # a pitch of whole vectors keeps the register kernel
+    x = (torch.randn(rows, cols + pad, device="cuda", generator=gen) * 3).half()
     out = torch.full_like(x, 9.0)
-    rc = lib.asc_cuda_softmax_f16(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()), rows, cols, cols + 1, None)
+    rc = lib.asc_cuda_softmax_f16(ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(out.data_ptr()), rows, cols, cols + pad, None)
     assert rc == 0, capi.status_string(rc)
     capi.check_device_status(None)
     want = torch.softmax(x[:, :cols].float(), dim=1).half()
     torch.testing.assert_close(out[:, :cols], want, rtol=1e-3, atol=1e-6)
-    assert bool((out[:, cols] == 9.0).all())
+    assert bool((out[:, cols:] == 9.0).all())
 
 
 # ------------------------------------------------------------------------------- RMS normalisation
