@@ -13,6 +13,7 @@
 
 namespace {
 
+template <int kWarps>
 __device__ __forceinline__ float cta_sum(float v, float* red) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -20,7 +21,7 @@ __device__ __forceinline__ float cta_sum(float v, float* red) {
   __syncthreads();
   float r = red[0];
 #pragma unroll
-  for (int w = 1; w < 8; ++w) r += red[w];
+  for (int w = 1; w < kWarps; ++w) r += red[w];
   __syncthreads();  // red is reused by the next row
   return r;
 }
@@ -66,19 +67,20 @@ struct RowVec<__half> {
   __device__ static __half narrow(float x) { return __float2half_rn(x); }
 };
 
-// whole 16-byte vectors only: cols a multiple of kElems and at most 256 * kVec * kElems, rows and gamma 16-byte aligned
-template <typename T, int kVec>
-__global__ void __launch_bounds__(256) rms_rows_reg_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
+// whole 16-byte vectors only: cols a multiple of kElems and at most kT * kVec * kElems, rows and gamma 16-byte
+// aligned; kT threads per CTA (short rows take 128 so that no warp idles through the barriers)
+template <typename T, int kVec, int kT>
+__global__ void __launch_bounds__(kT) rms_rows_reg_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
                                                            T* __restrict__ out, int64_t rows, int cols_v, int64_t ld,
                                                            float eps, float inv_cols) {
   constexpr int kE = RowVec<T>::kElems;
-  __shared__ float red[8];
+  __shared__ float red[kT / 32];
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     float v[kVec][kE];
     float ss = 0.f;
 #pragma unroll
     for (int u = 0; u < kVec; ++u) {
-      const int c = threadIdx.x + u * 256;
+      const int c = threadIdx.x + u * kT;
       if (c < cols_v) {
         RowVec<T>::load(x + row * ld + static_cast<int64_t>(c) * kE, v[u], true);
       } else {
@@ -90,10 +92,10 @@ __global__ void __launch_bounds__(256) rms_rows_reg_kernel(const T* __restrict__
       for (int e = 0; e < kE; ++e) part = fmaf(v[u][e], v[u][e], part);
       ss += part;
     }
-    const float scale = 1.f / sqrtf(cta_sum(ss, red) * inv_cols + eps);
+    const float scale = 1.f / sqrtf(cta_sum<kT / 32>(ss, red) * inv_cols + eps);
 #pragma unroll
     for (int u = 0; u < kVec; ++u) {
-      const int c = threadIdx.x + u * 256;
+      const int c = threadIdx.x + u * kT;
       if (c < cols_v) {
         float g[kE];
         RowVec<T>::load(gamma + static_cast<int64_t>(c) * kE, g, false);
@@ -118,7 +120,7 @@ __global__ void __launch_bounds__(256) rms_rows_generic_kernel(const T* __restri
       const float t = RowVec<T>::widen(xr[c]);
       ss = fmaf(t, t, ss);
     }
-    const float scale = 1.f / sqrtf(cta_sum(ss, red) * inv_cols + eps);
+    const float scale = 1.f / sqrtf(cta_sum<8>(ss, red) * inv_cols + eps);
     for (int64_t c = threadIdx.x; c < cols; c += 256)
       out[row * ld + c] = RowVec<T>::narrow(RowVec<T>::widen(xr[c]) * scale * RowVec<T>::widen(gamma[c]));
   }
@@ -143,10 +145,14 @@ int32_t launch_rms(const T* x, const T* gamma, T* out, int64_t rows, int64_t col
   const int64_t cols_v = cols / kE;
   if (vec && cols_v <= 256 * 8 / (kE / 4)) {     // at most 32 fp32 registers of row per thread
     const int cv = static_cast<int>(cols_v);
-    if (cols_v <= 256) rms_rows_reg_kernel<T, 1><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
-    else if (cols_v <= 512) rms_rows_reg_kernel<T, 2><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
-    else if (cols_v <= 1024) rms_rows_reg_kernel<T, 4><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
-    else rms_rows_reg_kernel<T, 8><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
+    if (cols_v <= 128) {
+      int64_t g128 = static_cast<int64_t>(sms) * 32;
+      if (g128 > rows) g128 = rows;
+      rms_rows_reg_kernel<T, 1, 128><<<static_cast<unsigned>(g128), 128, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
+    } else if (cols_v <= 256) rms_rows_reg_kernel<T, 1, 256><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
+    else if (cols_v <= 512) rms_rows_reg_kernel<T, 2, 256><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
+    else if (cols_v <= 1024) rms_rows_reg_kernel<T, 4, 256><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
+    else rms_rows_reg_kernel<T, 8, 256><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
   } else {
     rms_rows_generic_kernel<T><<<g, 256, 0, s>>>(x, gamma, out, rows, cols, ld, eps, inv_cols);
   }
