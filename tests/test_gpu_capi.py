@@ -102,7 +102,8 @@ def test_softmax_fixtures(lib, golden_dir):
 
 
 @pytest.mark.parametrize("rows, cols", [(1, 1), (7, 4), (33, 100), (17, 516), (64, 1024), (9, 2052), (5, 4100),
-                                        (3, 8192), (2, 10000), (2, 70000), (300, 4096)])
+                                        (3, 8192), (2, 10000), (2, 70000), (300, 4096), (70, 1536), (45, 3072), (31, 2560),
+                                        (29, 5120), (23, 6144)])
 def test_softmax_shapes(lib, rows, cols):
     x = G.softmax_input(rows, cols, seed=rows * 131 + cols)
     xd = dev(x)

@@ -185,7 +185,7 @@ def test_golden_fixture(golden_dir):
 
 
 @pytest.mark.parametrize("rows, cols", [(3, 7), (257, 4096), (8, 60000), (4, 70001), (1000, 8), (513, 1000), (300, 2048),
-                                        (77, 8192), (33, 16384), (65536, 2048)])
+                                        (77, 8192), (33, 16384), (65536, 2048), (50, 3072), (40, 5120), (20, 12288)])
 def test_capi_softmax_f16(lib, rows, cols):
     """fp16 rows: every depth of the register kernel (whole 16-byte vectors up to 16384 columns, 256 MiB beyond L2
     included) and the generic path for odd lengths, odd pitches and longer rows (rows staged in shared memory and
