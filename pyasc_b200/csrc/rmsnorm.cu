@@ -149,10 +149,16 @@ int32_t launch_rms(const T* x, const T* gamma, T* out, int64_t rows, int64_t col
       int64_t g128 = static_cast<int64_t>(sms) * 32;
       if (g128 > rows) g128 = rows;
       rms_rows_reg_kernel<T, 1, 128><<<static_cast<unsigned>(g128), 128, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
-    } else if (cols_v <= 256) rms_rows_reg_kernel<T, 1, 256><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
-    else if (cols_v <= 512) rms_rows_reg_kernel<T, 2, 256><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
-    else if (cols_v <= 1024) rms_rows_reg_kernel<T, 4, 256><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
-    else rms_rows_reg_kernel<T, 8, 256><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols);
+    } else {
+      // the smallest register tile that holds the row: idle vector slots cost issue slots and bytes in flight
+#define ASC_RMS_CASE(V) \
+  case V: rms_rows_reg_kernel<T, V, 256><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols); break;
+      switch ((cv + 255) / 256) {
+        ASC_RMS_CASE(1) ASC_RMS_CASE(2) ASC_RMS_CASE(3) ASC_RMS_CASE(4) ASC_RMS_CASE(5) ASC_RMS_CASE(6) ASC_RMS_CASE(7)
+        default: rms_rows_reg_kernel<T, 8, 256><<<g, 256, 0, s>>>(x, gamma, out, rows, cv, ld, eps, inv_cols); break;
+      }
+#undef ASC_RMS_CASE
+    }
   } else {
     rms_rows_generic_kernel<T><<<g, 256, 0, s>>>(x, gamma, out, rows, cols, ld, eps, inv_cols);
   }

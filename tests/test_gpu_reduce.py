@@ -227,7 +227,8 @@ def test_rms_norm_1d_and_device_tensors():
 
 
 @pytest.mark.parametrize("rows, cols, pad", [(1, 1, 0), (7, 33, 3), (300, 1000, 0), (129, 4096, 4), (33, 8192, 0),
-                                             (5, 20000, 0), (9, 16384, 8), (32768, 2048, 0)])
+                                             (5, 20000, 0), (9, 16384, 8), (32768, 2048, 0), (50, 3072, 0), (40, 5120, 0),
+                                             (30, 6144, 8), (21, 7168, 0), (60, 1280, 0)])
 def test_capi_rms_norm(lib, rows, cols, pad):
     """Every register depth of the vector kernel, the two-read kernel (long, ragged or unaligned rows), pitched
     rows, and a 256 MiB matrix (beyond L2); in place as well."""
@@ -252,7 +253,7 @@ def test_capi_rms_norm(lib, rows, cols, pad):
 
 
 @pytest.mark.parametrize("rows, cols, pad", [(3, 8, 0), (65, 1000, 0), (40, 4096, 8), (17, 8192, 0), (9, 16384, 0),
-                                             (11, 1001, 1), (65536, 2048, 0)])
+                                             (11, 1001, 1), (65536, 2048, 0), (50, 3072, 0), (40, 5120, 8), (30, 6144, 0)])
 def test_capi_rms_norm_f16(lib, rows, cols, pad):
     """fp16 rows: every register depth, the two-read kernel (long or odd rows), pitched rows, 256 MiB beyond L2."""
     gen = torch.Generator(device="cuda").manual_seed(rows * 5 + cols)
