@@ -160,6 +160,11 @@ int32_t asc_cuda_eltwise_program_2d(const int32_t* ops, const int32_t* args, int
  * row and one element per row is stored, at out[r * lds[n_inputs]] (pitch 1 when lds is NULL).
  * An input type with bit 0x200 set marks an input that holds one element per row (a column: element r at
  * inputs[k][r * lds[k]], pitch 1 when lds is NULL), which every element of the row reads.
+ * Two more opcodes let a program compute a shared sub-expression once: TEE 63 copies the top of the stack into
+ * temporary slot args[j] (0..3) without popping it, TMP 64 pushes that slot; a slot must be written before it is
+ * read (status 1 otherwise).  The two upper stack entries live in registers, deeper entries and the temporary
+ * slots in shared memory: a program whose (stack depth - 2, at least 1, + slots used) x ceil(cols / 256 to a power
+ * of two) KiB exceeds 200 KiB returns status 6, as does cols > 8192.
  * Replaces the chains of vector calls and ReduceOp calls the reference lowers such kernels to
  * (python/asc/language/tile/reduction_ops.py, shape_ops.py:30-75; lib/Conversion/LowerToAsc/LowerAscTile.cpp:
  * 329-378 BroadcastOp, 428-459 ReduceOp; the manual softmax of python/test/asc2/kernels/test_softmax.py:16-27 is
@@ -229,7 +234,8 @@ int32_t asc_cuda_gemm_i8(const int8_t* A, const int8_t* B, int32_t* acc, void* d
 
 /* O = softmax(scale * Q K^T [+ causal mask]) V for contiguous [B, H, S, D] tensors, fp32
  * online-softmax accumulation.  dtype: 0 fp16, 1 bf16.  D must be 128 (the only head size of the
- * workload this library targets) and S a multiple of 8.  causal != 0 masks key j > query i.
+ * workload this library targets; anything else returns status 3); S is any positive length (rows past S
+ * read as zero and are never written).  Pointers 16-byte aligned.  causal != 0 masks key j > query i.
  * No counterpart in the reference (it has no attention kernel); defined by the torch expression
  * softmax((Q.float() @ K.float().transpose(-1,-2)) * scale + mask, -1) @ V.float(). */
 int32_t asc_cuda_attn_fwd_f16(const void* q, const void* k, const void* v, void* o, int32_t B, int32_t H,

@@ -824,6 +824,18 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
     tail_args = (ctypes.c_int32(1 if row_result else 0), ) if row_shape is not None else ()
     calls: List[Tuple[Tuple[int, ...], int]] = []      # (first element of every operand and of the result, rows)
     all_starts = [tuple(int(g.start[j]) for g in geoms) + (int(out_g.start[j]), ) for j in range(n)]
+    if dedupe and len(set(all_starts)) > 1:
+        # Instances that differ in where they read from but write overlapping elements do not commute: the last
+        # writer (in block order, then iteration order) must win, so such a kernel keeps one call per instance in
+        # that order.  Instances with equal addresses throughout are repeats of one another.
+        uniq = sorted(set(all_starts))
+        u = np.array(uniq, dtype=np.int64)
+        width = out_t.static_shape()[-1] if out_t.static_shape() else 1
+        rect = _flat_rects(width, u[:, -1], out_g.numel, out_g.rows, out_g.cols, out_g.pitch)
+        clash = _rects_overlap(rect, rect)
+        np.fill_diagonal(clash, False)
+        if clash.any():
+            dedupe = False
     if dedupe:
         # stores are idempotent and independent: drop repeats, and let windows that continue each other row
         # after row (every operand advancing by its own pitch, a broadcast row staying put) become one call
@@ -1170,6 +1182,9 @@ def _match_reduce(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     if n > (1 << 20):
         raise _unsupported(f"reduction kernel with {n} tiles; use larger tiles")
     calls = sorted(set(zip(row0.tolist(), col0.tolist(), out0.tolist())))
+    by_out = sorted(c[2] for c in calls)
+    if any(b < a + n_out for a, b in zip(by_out, by_out[1:])):
+        raise _unsupported("reductions of different tiles stored into overlapping ranges (the last writer would win)")
     # full-row tiles reduced along the row: consecutive tiles merge into one call over more rows
     merged: List[Tuple[int, int, int, int]] = []      # (row0, col0, out0, rows)
     for r0, c0, o0 in calls:
@@ -1635,6 +1650,14 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
                           int(k_eff[i])))
         if len(calls) > MAX_CALLS:
             raise _unsupported("matmul kernel whose tiles do not form a grid and exceed 4096 calls")
+        if calls:
+            c = np.array(calls, dtype=np.int64)
+            rect = np.stack([c[:, 0], c[:, 0] + c[:, 5], c[:, 1], c[:, 1] + c[:, 6]], axis=1)
+            clash = _rects_overlap(rect, rect)
+            np.fill_diagonal(clash, False)
+            if clash.any():
+                raise _unsupported("matmul tiles computed from different operands that overlap in the output "
+                                   "(the last writer would win)")
 
     a_idx, b_idx, c_idx = a_w.tensor.base.index, b_w.tensor.base.index, out_t.base.index
     plan.writes.add(c_idx)
@@ -1811,6 +1834,106 @@ def _match_attention(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
 
 
 # --------------------------------------------------------------------------------------------------
+# Write-after-write order: footprints of stores and the order the plan applies them in
+# --------------------------------------------------------------------------------------------------
+def _rects_overlap(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """Pairwise overlap of two sets of rectangles ``[row_lo, row_hi, col_lo, col_hi)``: a bool matrix [len(a), len(b)]."""
+    return ((a[:, None, 0] < b[None, :, 1]) & (b[None, :, 0] < a[:, None, 1]) &
+            (a[:, None, 2] < b[None, :, 3]) & (b[None, :, 2] < a[:, None, 3]))
+
+
+def _flat_rects(width: int, start: np.ndarray, numel: int, rows: int = 1, cols: int = 0,
+                pitch: Optional[int] = None) -> np.ndarray:
+    """Rectangles over a tensor seen as rows of ``width`` elements for windows that begin at flat index ``start``:
+    ``rows`` x ``cols`` with a row pitch, or one contiguous range of ``numel`` elements.  A range that spans several
+    rows is widened to whole rows (conservative)."""
+    width = max(1, width)
+    r0, c0 = start // width, start % width
+    if pitch is not None:
+        return np.stack([r0, r0 + rows, c0, c0 + cols], axis=1)
+    one_row = c0 + numel <= width
+    r1 = np.where(one_row, r0 + 1, -((-(start + numel)) // width))
+    return np.stack([r0, r1, np.where(one_row, c0, 0), np.where(one_row, c0 + numel, width)], axis=1)
+
+
+MAX_ORDER_PAIRS = 1 << 24    # instance pairs the write-order checks compare exactly
+
+
+def _store_footprint(trace: KernelTrace, eff: Effect):
+    """``(env, rects)`` of a store or atomic effect: the symbol bindings of its instances and the rectangle of the
+    output tensor (rows of its last dimension) each instance writes, clipped to the tensor."""
+    value, out_t = eff.args
+    offsets = eff.attrs["offsets"]
+    tshape = out_t.static_shape()
+    width = tshape[-1] if tshape else 1
+    env = enumerate_instances(trace.core_num, eff.loops)
+    n = env_count(env)
+    shape = value.shape if isinstance(value, Tile) and eff.kind != "store_scalar" else None
+    if shape is None:
+        start = eval_int(_flat_scalar_offset(tshape, offsets), env, n)
+        return env, _flat_rects(width, start, 1)
+    window = _flat_window(out_t, offsets, shape)
+    if window is not None:
+        start = eval_int(window[0], env, n)
+        total = 1
+        for d in tshape:
+            total *= d
+        rects = _flat_rects(width, start, window[1])
+        rects[:, 1] = np.minimum(rects[:, 1], -(-total // max(1, width)))
+        return env, rects
+    if len(tshape) == 2 and len(shape) == 2:
+        r0, c0 = eval_int(offsets[0], env, n), eval_int(offsets[1], env, n)
+        return env, np.stack([r0, np.minimum(r0 + shape[0], tshape[0]), c0, np.minimum(c0 + shape[1], tshape[1])], axis=1)
+    return env, None
+
+
+def _check_effect_order(trace: KernelTrace, first: Effect, second: Effect, cache: Dict[int, Any]) -> None:
+    """The plan applies ``first`` over all blocks and iterations, then ``second``.  Inside one block the kernel
+    instead interleaves them iteration by iteration: if an instance of ``first`` that runs *after* an instance of
+    ``second`` (a later iteration of a loop both are in) writes elements that instance also writes, the kernel
+    leaves ``first``'s data there and the plan would leave ``second``'s.  Such kernels are refused."""
+    if first.kind == "atomic" and second.kind == "atomic" and first.attrs.get("kind") == second.attrs.get("kind"):
+        return                      # accumulations of one kind commute
+    shared = 0
+    while shared < min(len(first.loops), len(second.loops)) and first.loops[shared] is second.loops[shared]:
+        shared += 1
+    if shared == 0:
+        return                      # `first` is complete in every block before `second` starts
+    for e in (first, second):
+        if id(e) not in cache:
+            cache[id(e)] = _store_footprint(trace, e)
+    (env_a, ra), (env_b, rb) = cache[id(first)], cache[id(second)]
+    refuse = _unsupported(f"kernel '{trace.fn_name}' overwrites, in a later loop iteration, elements that another store "
+                          "of an earlier iteration wrote after it in program order")
+    if ra is None or rb is None or ra.shape[0] * rb.shape[0] > MAX_ORDER_PAIRS:
+        # too many instances to compare pair by pair: any overlap of the two footprints is refused
+        if ra is None or rb is None:
+            raise refuse
+        width = max(int(ra[:, 3].max(initial=1)), int(rb[:, 3].max(initial=1)))
+        ia = merge_intervals(ra[:, 0] * width + ra[:, 2], (ra[:, 1] - 1) * width + ra[:, 3])
+        ib = merge_intervals(rb[:, 0] * width + rb[:, 2], (rb[:, 1] - 1) * width + rb[:, 3])
+        j = 0
+        for lo, hi in ia:
+            while j < len(ib) and ib[j][1] <= lo:
+                j += 1
+            if j < len(ib) and ib[j][0] < hi:
+                raise refuse
+        return
+    names = ["block_idx"] + [l.name for l in first.loops[:shared]]
+    later = np.zeros((ra.shape[0], rb.shape[0]), dtype=bool)      # `first`'s instance runs after `second`'s
+    equal = np.ones_like(later)
+    for k, name in enumerate(names):
+        a, b = env_a[name][:, None], env_b[name][None, :]
+        if k == 0:
+            equal &= a == b         # only instances of one block are ordered
+            continue
+        later |= equal & (a > b)
+        equal &= a == b
+    if np.any(later & _rects_overlap(ra, rb)):
+        raise refuse
+
+
+# --------------------------------------------------------------------------------------------------
 # Entry point
 # --------------------------------------------------------------------------------------------------
 _MATCHERS = (_match_attention, _match_softmax, _match_rms_norm, _match_elementwise, _match_matmul, _match_eltwise_program,
@@ -1911,6 +2034,8 @@ def build_plan(trace: KernelTrace) -> Plan:
     names = []
     written: Dict[int, int] = {}       # runtime-argument index -> uid of the first effect that writes it
     windows: Dict[int, list] = {}      # runtime-argument index -> (offsets, shape, loop nest) of every store to it
+    writers: Dict[int, List[Effect]] = {}   # runtime-argument index -> the planned effects that write it, in order
+    footprints: Dict[int, Any] = {}    # id(effect) -> its instances and the rectangles they write (computed on demand)
     for eff in stores:
         if eff.kind != "atomic" and _is_identity_store(eff):
             continue        # a tile stored back to where it was loaded from changes nothing
@@ -1950,6 +2075,9 @@ def build_plan(trace: KernelTrace) -> Plan:
             value = eff.args[0]
             kind = value.node.kind if isinstance(value, Tile) else type(value).__name__
             raise _unsupported(f"store of a tile produced by '{kind}' in kernel '{trace.fn_name}'")
+        for earlier in writers.get(eff.args[1].base.index, []):
+            _check_effect_order(trace, earlier, eff, footprints)
+        writers.setdefault(eff.args[1].base.index, []).append(eff)
         written.setdefault(eff.args[1].base.index, eff.uid)
         stored = eff.args[0]
         windows.setdefault(eff.args[1].base.index, []).append(

@@ -13,13 +13,21 @@ from __future__ import annotations
 
 import atexit
 import ctypes
-from typing import Dict, List, Optional
+from typing import Callable, Dict, List, Optional
 
 from . import state, support
 
 _pool: Dict[int, List[int]] = {}
 _POOL_LIMIT_BYTES = 8 << 30
 _pool_bytes = 0
+# callables(device_id) run by reset_device before the device's streams are destroyed, so that modules holding
+# streams or events of that device (the launcher's copy/compute pipeline) can drop them
+_reset_hooks: List[Callable[[int], None]] = []
+
+
+def on_device_reset(hook: Callable[[int], None]) -> None:
+    if hook not in _reset_hooks:
+        _reset_hooks.append(hook)
 
 
 def _lazy_init(need_device: bool = True, need_stream: bool = True) -> None:
@@ -139,6 +147,8 @@ def reset_device(device_id: Optional[int] = None) -> None:
     if dev is None:
         return
     release_pool()
+    for hook in _reset_hooks:
+        hook(dev)
     state.lib.call("DeviceResetWrapper", ctypes.c_int32(dev))
     state.streams[dev] = None
     if dev == state.device_id:

@@ -29,20 +29,34 @@ from .options import LaunchOptions
 PIPELINE_MIN_BYTES = 16 << 20     # below this a launch is latency-bound and is not chunked
 PIPELINE_MAX_CHUNKS = int(os.environ.get("ASC_CUDA_PIPELINE_CHUNKS", "8"))
 
+# per device: the three pipeline streams and a pool of events created on that device
 _pipe_streams: Dict[int, Tuple[ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]] = {}
-_event_pool: List[ctypes.c_void_p] = []
+_event_pool: Dict[int, List[ctypes.c_void_p]] = {}
+
+
+def _forget_device(dev: int) -> None:
+    """``reset_device`` destroys every stream the runtime created on ``dev``: drop the handles kept here and
+    destroy the device's pooled events, so the next pipelined launch makes fresh ones."""
+    _pipe_streams.pop(dev, None)
+    for ev in _event_pool.pop(dev, []):
+        try:
+            rt.state.lib.call("asc_cuda_event_destroy", ev)
+        except RuntimeError:
+            pass
 
 
 def _pipeline_streams() -> Tuple[ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]:
     dev = rt.current_device()
     if dev not in _pipe_streams:
+        rt.on_device_reset(_forget_device)
         _pipe_streams[dev] = (rt.create_stream(), rt.create_stream(), rt.create_stream())
     return _pipe_streams[dev]
 
 
 def _new_event() -> ctypes.c_void_p:
-    if _event_pool:
-        return _event_pool.pop()
+    pool = _event_pool.setdefault(rt.current_device(), [])
+    if pool:
+        return pool.pop()
     ev = ctypes.c_void_p()
     rt.state.lib.call("asc_cuda_event_create_notiming", ctypes.c_void_p(ctypes.addressof(ev)))
     return ev
@@ -160,6 +174,7 @@ class Launcher:
         bounds = [(lo, min(lo + per, spec.units)) for lo in range(0, spec.units, per)]
         ptrs: Dict[Any, int] = {}
         events: List[ctypes.c_void_p] = []
+        dev = rt.current_device()
         try:
             for index, handle in handles.items():
                 ptrs[index] = handle.device_alloc_only()
@@ -197,6 +212,6 @@ class Launcher:
                     rt.synchronize(stream)
                 except RuntimeError:
                     pass
-            _event_pool.extend(events)
+            _event_pool.setdefault(dev, []).extend(events)
             for handle in handles.values():
                 handle.release_memory()

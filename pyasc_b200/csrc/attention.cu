@@ -502,17 +502,17 @@ int32_t launch_attn(const void* q, const void* k, const void* v, AttnParams p, c
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) != ASC_OK) return rc;
   if ((rc = aschost::device_status_word(&p.status)) != ASC_OK) return rc;
   auto kernel = attn_fwd_tcgen05_kernel<kBf16>;
-  static bool attr_set[64] = {false};
+  static aschost::PerDevice attr_set;
   int dev = 0;
   ASC_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+  if (!attr_set.get(dev)) {
     // the register split inside the kernel must fit what the kernel is launched with, or its first
     // setmaxnreg increase would wait forever: refuse to launch a build where it does not
     cudaFuncAttributes fa{};
     ASC_CUDA_TRY(cudaFuncGetAttributes(&fa, kernel));
     if (12 * fa.numRegs < 8 * kSoftmaxRegs + 4 * kOtherRegs) return ASC_ERR_UNSUPPORTED;
     ASC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-    attr_set[dev] = true;
+    attr_set.set(dev, 1);
   }
   const uint32_t fmt = kBf16 ? 1u : 0u;
   const uint32_t idesc_qk = make_idesc(1, fmt, fmt, 0, 0, kTileQ, kTileKV);

@@ -58,6 +58,19 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// max / min that return NaN when either operand is NaN, as torch.maximum / minimum / relu / amax do
+// (fmaxf / fminf return the other operand instead).
+__device__ __forceinline__ float max_nan(float a, float b) {
+  float d;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+  return d;
+}
+__device__ __forceinline__ float min_nan(float a, float b) {
+  float d;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+  return d;
+}
+
 // ------------------------------- mbarrier ---------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

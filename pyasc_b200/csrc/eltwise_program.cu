@@ -236,8 +236,8 @@ __device__ __forceinline__ float apply_binary(int op, float a, float b) {
     case OP_SUB: return __fsub_rn(a, b);
     case OP_MUL: return __fmul_rn(a, b);
     case OP_DIV: return __fdiv_rn(a, b);
-    case OP_MAX: return fmaxf(a, b);
-    case OP_MIN: return fminf(a, b);
+    case OP_MAX: return ascdev::max_nan(a, b);
+    case OP_MIN: return ascdev::min_nan(a, b);
     case OP_EQ: return a == b ? 1.f : 0.f;
     case OP_NE: return a != b ? 1.f : 0.f;
     case OP_GT: return a > b ? 1.f : 0.f;
@@ -270,7 +270,7 @@ __device__ __forceinline__ float apply_unary(int op, float a) {
   switch (op) {
     case OP_NEG: return -a;
     case OP_ABS: return fabsf(a);
-    case OP_RELU: return fmaxf(a, 0.f);
+    case OP_RELU: return ascdev::max_nan(a, 0.f);
     case OP_EXP: return expf(a);
     case OP_EXP2: return exp2f(a);
     case OP_LOG: return logf(a);
@@ -510,19 +510,19 @@ __global__ void __launch_bounds__(kThreads) eltwise_program_kernel(const __grid_
   for (int64_t i = done + tid; i < n; i += stride) Exec::template run<1>(prog, i, stack_mem);
 }
 
-int g_lanes = 0;            // interpreter: elements per thread and dispatch on the aligned path (4, 8, 16; 0: by program length)
-bool g_use_compiled = true;  // tuning hook can force the interpreter for every program
+std::atomic<int> g_lanes{0};            // interpreter: elements per thread and dispatch on the aligned path (4, 8, 16; 0: by program length)
+std::atomic<bool> g_use_compiled{true};  // tuning hook can force the interpreter for every program
 
 template <class Exec, int kLanes>
 int32_t launch_program(const EltProgram& prog, int64_t n, size_t smem, int sms, cudaStream_t stream) {
   if (smem > 48 * 1024) {
-    static bool attr_set[64] = {false};
+    static aschost::PerDevice attr_set;
     int dev = 0;
     ASC_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (!attr_set.get(dev)) {
       ASC_CUDA_TRY(cudaFuncSetAttribute(eltwise_program_kernel<Exec, kLanes>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         (kStack - 1) * kThreads * 16 * static_cast<int>(sizeof(float))));
-      attr_set[dev] = true;
+      attr_set.set(dev, 1);
     }
   }
   int resident = 0;
@@ -618,7 +618,7 @@ __device__ __forceinline__ float row_identity(int op) {
   return op == OP_ROW_SUM ? 0.f : op == OP_ROW_PROD ? 1.f : op == OP_ROW_MAX ? -INFINITY : INFINITY;
 }
 __device__ __forceinline__ float row_combine(int op, float a, float b) {
-  return op == OP_ROW_SUM ? __fadd_rn(a, b) : op == OP_ROW_PROD ? __fmul_rn(a, b) : op == OP_ROW_MAX ? fmaxf(a, b) : fminf(a, b);
+  return op == OP_ROW_SUM ? __fadd_rn(a, b) : op == OP_ROW_PROD ? __fmul_rn(a, b) : op == OP_ROW_MAX ? ascdev::max_nan(a, b) : ascdev::min_nan(a, b);
 }
 
 __device__ __forceinline__ int16_t word_to_i16(float v) { return static_cast<int16_t>(__float_as_int(v)); }
@@ -818,12 +818,12 @@ int32_t launch_row_program(const EltProgram& prog, int64_t rows, int max_depth, 
   const size_t smem = static_cast<size_t>(tmp_level + n_tmp) * kV * kThreads * sizeof(float);
   if (smem > 200 * 1024) return ASC_ERR_TOO_LARGE;
   if (smem > 48 * 1024) {
-    static bool attr_set[64] = {false};
+    static aschost::PerDevice attr_set;
     int dev = 0;
     ASC_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    if (!attr_set.get(dev)) {
       ASC_CUDA_TRY(cudaFuncSetAttribute(row_program_kernel<kV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-      if (dev >= 0 && dev < 64) attr_set[dev] = true;
+      attr_set.set(dev, 1);
     }
   }
   int resident = 0;
@@ -958,7 +958,8 @@ extern "C" int32_t asc_cuda_eltwise_program_2d(const int32_t* ops, const int32_t
   }
   // more elements per dispatch amortise the dispatch of long programs (measured: 7 ops 4.2 vs 3.8 TB/s, 13 ops
   // 2.9 vs 2.5 with 16 instead of 8); short ones are memory-bound either way and keep the smaller register set
-  const int lanes = g_lanes != 0 ? g_lanes : (n_ops >= 5 ? 16 : 8);
+  const int forced = g_lanes.load(std::memory_order_relaxed);
+  const int lanes = forced != 0 ? forced : (n_ops >= 5 ? 16 : 8);
   if (lanes == 4 || n < kThreads * 8) return launch_interpreter<4>(prog, n, max_depth, sms, st);
   if (lanes == 16 && n >= kThreads * 16) return launch_interpreter<16>(prog, n, max_depth, sms, st);
   return launch_interpreter<8>(prog, n, max_depth, sms, st);

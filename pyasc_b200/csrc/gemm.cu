@@ -674,12 +674,12 @@ int32_t launch_gemm(const void* A, const void* B, int64_t lda, int64_t ldb, CUte
   if (rc != ASC_OK) return rc;
 
   auto kernel = gemm_tcgen05_kernel<kElemBytes, kMode>;
-  static bool attr_set[64] = {false};
+  static aschost::PerDevice attr_set;
   int dev = 0;
   ASC_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+  if (!attr_set.get(dev)) {
     ASC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
-    attr_set[dev] = true;
+    attr_set.set(dev, 1);
   }
   const int64_t num_tiles = ((p.M + kBlockM - 1) / kBlockM) * ((p.N + kBlockN - 1) / kBlockN);
   int64_t grid = num_tiles < sms ? num_tiles : sms;
@@ -691,8 +691,8 @@ int32_t launch_gemm(const void* A, const void* B, int64_t lda, int64_t ldb, CUte
 }
 
 // 0: choose per problem, 1: always the single-CTA kernel, 2: the CTA-pair kernel whenever it applies
-static int g_gemm_mode = 0;
-static uint32_t g_group_m = 0;
+static std::atomic<int> g_gemm_mode{0};
+static std::atomic<uint32_t> g_group_m{0};
 
 template <int kElemBytes, int kMode>
 int32_t launch_gemm_pair(const void* A, const void* B, int64_t lda, int64_t ldb, CUtensorMapDataType dt,
@@ -722,18 +722,18 @@ int32_t launch_gemm_pair(const void* A, const void* B, int64_t lda, int64_t ldb,
   rc = aschost::sm_count(&sms);
   if (rc != ASC_OK) return rc;
   auto kernel = gemm_tcgen05_pair_kernel<kElemBytes, kMode>;
-  static bool attr_set[64] = {false};
+  static aschost::PerDevice attr_set;
   int dev = 0;
   ASC_CUDA_TRY(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+  if (!attr_set.get(dev)) {
     ASC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem));
-    attr_set[dev] = true;
+    attr_set.set(dev, 1);
   }
   const int64_t num_tiles = ((p.M + 2 * kBlockM - 1) / (2 * kBlockM)) * ((p.N + kBlockN - 1) / kBlockN);
   // A persistent grid must be fully resident: ask how many 2-CTA clusters fit at once (SMs that have
   // no partner inside their GPC cannot host one), otherwise the surplus clusters run as a second wave.
-  static int max_clusters[64] = {0};
-  if (dev >= 0 && dev < 64 && max_clusters[dev] == 0) {
+  static aschost::PerDevice max_clusters;
+  if (max_clusters.get(dev) == 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(sms - sms % 2));
     cfg.blockDim = dim3(kGemmThreads);
@@ -747,9 +747,9 @@ int32_t launch_gemm_pair(const void* A, const void* B, int64_t lda, int64_t ldb,
     cfg.numAttrs = 1;
     int n = 0;
     ASC_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
-    max_clusters[dev] = n > 0 ? n : 1;
+    max_clusters.set(dev, n > 0 ? n : 1);
   }
-  int64_t pairs = (dev >= 0 && dev < 64) ? max_clusters[dev] : sms / 2;
+  int64_t pairs = max_clusters.get(dev) > 0 ? max_clusters.get(dev) : sms / 2;
   if (pairs > sms / 2) pairs = sms / 2;
   if (max_ctas > 0 && pairs > max_ctas / 2) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   if (pairs > num_tiles) pairs = num_tiles;
@@ -763,9 +763,10 @@ int32_t launch_gemm_pair(const void* A, const void* B, int64_t lda, int64_t ldb,
 template <int kElemBytes, int kMode>
 int32_t dispatch_gemm(const void* A, const void* B, int64_t lda, int64_t ldb, CUtensorMapDataType dt, uint32_t c_fmt,
                       uint32_t ab_fmt, GemmParams p, int32_t max_ctas, cudaStream_t stream) {
-  p.group_m = g_group_m;
+  p.group_m = g_group_m.load(std::memory_order_relaxed);
+  const int mode = g_gemm_mode.load(std::memory_order_relaxed);
   const int64_t pair_tiles = ((p.M + 2 * kBlockM - 1) / (2 * kBlockM)) * ((p.N + kBlockN - 1) / kBlockN);
-  const bool use_pair = g_gemm_mode == 2 ? p.M > kBlockM : (g_gemm_mode == 0 && pair_tiles >= 64);
+  const bool use_pair = mode == 2 ? p.M > kBlockM : (mode == 0 && pair_tiles >= 64);
   if (use_pair) {
     const uint32_t idesc = make_idesc(c_fmt, ab_fmt, ab_fmt, 0, 1, 2 * kBlockM, kBlockN);
     return launch_gemm_pair<kElemBytes, kMode>(A, B, lda, ldb, dt, idesc, p, max_ctas, stream);

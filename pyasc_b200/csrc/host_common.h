@@ -39,6 +39,17 @@ int32_t encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, uint32_t rank, 
 extern std::atomic<uint64_t> g_launch_count;
 inline void count_launch() { g_launch_count.fetch_add(1, std::memory_order_relaxed); }
 
+// One small cached value per device (a "set-up done" flag, an occupancy figure) that several host threads
+// may read and write at once.  Zero means "not computed yet"; threads that race compute the same value.
+struct PerDevice {
+  static constexpr int kMax = 64;
+  std::atomic<int> v[kMax];
+  int get(int dev) const { return (dev >= 0 && dev < kMax) ? v[dev].load(std::memory_order_acquire) : 0; }
+  void set(int dev, int value) {
+    if (dev >= 0 && dev < kMax) v[dev].store(value, std::memory_order_release);
+  }
+};
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace aschost

@@ -24,8 +24,8 @@ template <int kKind>
 __device__ __forceinline__ float combine(float a, float b) {
   if (kKind == R_SUM) return __fadd_rn(a, b);
   if (kKind == R_PROD) return __fmul_rn(a, b);
-  if (kKind == R_MAX) return fmaxf(a, b);
-  return fminf(a, b);
+  if (kKind == R_MAX) return ascdev::max_nan(a, b);
+  return ascdev::min_nan(a, b);
 }
 template <int kKind>
 __device__ __forceinline__ float warp_combine(float v) {

@@ -32,7 +32,7 @@ int32_t record_driver_error(int code, const char* what) {
 
 static constexpr int kMaxDevices = 64;
 static uint32_t* g_status_ptr[kMaxDevices] = {nullptr};
-static int g_sm_count[kMaxDevices] = {0};
+static std::atomic<int> g_sm_count[kMaxDevices];
 static std::mutex g_mutex;
 static std::vector<cudaStream_t> g_streams[kMaxDevices];
 
@@ -56,26 +56,30 @@ int32_t sm_count(int* out) {
   int dev = 0;
   ASC_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return ASC_ERR_INVALID_ARG;
-  if (g_sm_count[dev] == 0) {
+  int cached = g_sm_count[dev].load(std::memory_order_acquire);
+  if (cached == 0) {
     int n = 0;
     ASC_CUDA_TRY(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
-    g_sm_count[dev] = n;
+    g_sm_count[dev].store(n, std::memory_order_release);
+    cached = n;
   }
-  *out = g_sm_count[dev];
+  *out = cached;
   return ASC_OK;
 }
 
-static PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
+static std::atomic<PFN_cuTensorMapEncodeTiled_v12000> g_encode{nullptr};
 
 int32_t encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, uint32_t rank, const void* base,
                     const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                     CUtensorMapSwizzle swizzle, CUtensorMapL2promotion promo) {
-  if (g_encode == nullptr) {
+  PFN_cuTensorMapEncodeTiled_v12000 encode = g_encode.load(std::memory_order_acquire);
+  if (encode == nullptr) {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
     ASC_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
     if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return record_driver_error(-1, "cuTensorMapEncodeTiled lookup");
-    g_encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+    g_encode.store(encode, std::memory_order_release);
   }
   cuuint64_t gdims[5];
   cuuint64_t gstrides[4];
@@ -87,7 +91,7 @@ int32_t encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, uint32_t rank, 
     estr[i] = 1;
     if (i + 1 < rank) gstrides[i] = strides_bytes[i];
   }
-  CUresult r = g_encode(out, dtype, rank, const_cast<void*>(base), gdims, gstrides, gbox, estr,
+  CUresult r = encode(out, dtype, rank, const_cast<void*>(base), gdims, gstrides, gbox, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return record_driver_error(static_cast<int>(r), "cuTensorMapEncodeTiled");
   return ASC_OK;

@@ -48,7 +48,11 @@ __global__ void __launch_bounds__(kThreads)
   __shared__ float red_sum[kWarps];
   const float4* x4 = reinterpret_cast<const float4*>(x);
   float4* o4 = reinterpret_cast<float4*>(out);
-  const float4 neg = make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+  // idle vector slots hold -inf: they never raise the maximum (which starts at -FLT_MAX) and exp(-inf - m) is 0
+  // for every finite m, so they add nothing to the sum -- a row that is all -inf then sums to 0 and comes out NaN,
+  // as it does in a row without idle slots and in torch.softmax
+  const float ninf = __int_as_float(0xff800000u);
+  const float4 neg = make_float4(ninf, ninf, ninf, ninf);
 
   int64_t row = blockIdx.x;
   if (row >= rows) return;
@@ -235,13 +239,13 @@ int32_t launch_generic(const T* x, T* out, int64_t rows, int64_t cols, int64_t l
   const size_t row_bytes = static_cast<size_t>(cols) * sizeof(float);
   constexpr size_t kMaxStage = 200 * 1024;
   if (row_bytes <= kMaxStage) {
-    static bool attr_set[64] = {false};
+    static aschost::PerDevice attr_set;
     int dev = 0;
     ASC_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (!attr_set.get(dev)) {
       ASC_CUDA_TRY(cudaFuncSetAttribute(softmax_rows_generic_kernel<true, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(kMaxStage)));
-      attr_set[dev] = true;
+      attr_set.set(dev, 1);
     }
     int64_t per = static_cast<int64_t>((220 * 1024) / (row_bytes + 1024));
     if (per < 1) per = 1;
@@ -268,11 +272,15 @@ int32_t launch_reg(const float* x, float* out, int64_t rows, int64_t cols, int64
   if (ctas_per_sm <= 0) {
     // four full waves of resident CTAs: whole waves keep every SM busy to the end, and several of
     // them even out rows that finish at different times (measured: 6.37 vs 6.22 TB/s with two)
-    static int occupancy = 0;
+    static aschost::PerDevice resident;
+    int dev = 0;
+    ASC_CUDA_TRY(cudaGetDevice(&dev));
+    int occupancy = resident.get(dev);
     if (occupancy == 0) {
       ASC_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occupancy, softmax_rows_reg_kernel<kThreads, kVec>,
                                                                  kThreads, 0));
       if (occupancy < 1) occupancy = 1;
+      resident.set(dev, occupancy);
     }
     ctas_per_sm = 4 * occupancy;
   }
@@ -290,11 +298,15 @@ int32_t launch_reg16(const __half* x, __half* out, int64_t rows, int64_t cols, i
   int sms = 0;
   int32_t rc = aschost::sm_count(&sms);
   if (rc != ASC_OK) return rc;
-  static int occupancy = 0;
+  static aschost::PerDevice resident;
+  int dev = 0;
+  ASC_CUDA_TRY(cudaGetDevice(&dev));
+  int occupancy = resident.get(dev);
   if (occupancy == 0) {
     ASC_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occupancy, softmax_rows_reg16_kernel<kThreads, kVec>,
                                                                kThreads, 0));
     if (occupancy < 1) occupancy = 1;
+    resident.set(dev, occupancy);
   }
   int64_t grid = static_cast<int64_t>(sms) * 4 * occupancy;   // four whole waves, as for fp32 rows
   if (grid > rows) grid = rows;

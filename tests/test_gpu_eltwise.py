@@ -148,6 +148,25 @@ def test_program_integer_ops_wrap_like_torch(lib):
     assert torch.equal(out16.cpu(), a * 7)
 
 
+def test_program_max_min_relu_propagate_nan(lib):
+    """torch.maximum / minimum / relu return NaN when an operand is NaN (fmaxf would return the other operand);
+    the same holds for a maximum reduced along the rows of a row program."""
+    gen = torch.Generator().manual_seed(9)
+    x = torch.randn(4099, generator=gen)
+    y = torch.randn(4099, generator=gen)
+    x[::7] = float("nan")
+    y[3::11] = float("nan")
+    xd, yd = x.cuda(), y.cuda()
+    out = torch.zeros_like(xd)
+    for ops, args, ins, cpu_ins in (([0, 0, 6], [0, 1, 0], [xd, yd], [x, y]), ([0, 0, 7], [0, 1, 0], [xd, yd], [x, y]),
+                                    ([0, 10], [0, 0], [xd], [x]), ([0, 6 | 0x100], [0, fbits(0.5)], [xd], [x])):
+        call(lib, ops, args, ins, out, 0, 4099)
+        want = E.run_program(ops, args, cpu_ins, 0)
+        got = out.cpu()
+        assert torch.equal(got.isnan(), want.isnan()) and bool(want.isnan().any())
+        assert torch.equal(got[~want.isnan()], want[~want.isnan()])
+
+
 def test_program_transcendentals_close_to_cpu(lib):
     gen = torch.Generator().manual_seed(5)
     x = torch.rand(1 << 20, generator=gen) * 4 + 0.5

@@ -139,6 +139,26 @@ def test_capi_row_and_column_reductions(lib, rows, cols):
     torch.testing.assert_close(out, small.double().prod(dim=1).float(), rtol=1e-5, atol=0)
 
 
+def test_capi_max_min_reductions_propagate_nan(lib):
+    """torch.amax / amin return NaN for a row or column that holds one; so do the kernels (all four of them:
+    a warp per row, a CTA per row, along columns, the whole window)."""
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    for rows, cols in ((37, 100), (5, 20000)):
+        x = torch.randn(rows, cols, device="cuda", generator=gen)
+        x[2, cols // 3] = float("nan")
+        for axis, n_out in ((1, rows), (0, cols)):
+            for kind, ref in ((1, x.amax(dim=axis)), (2, x.amin(dim=axis))):
+                out = torch.zeros(n_out, device="cuda")
+                call(lib, x, out, rows, cols, cols, axis, kind)
+                assert torch.equal(out.isnan(), ref.isnan()) and int(ref.isnan().sum()) == 1
+                assert torch.equal(out[~ref.isnan()], ref[~ref.isnan()])
+    x = torch.randn(64, 64, device="cuda", generator=gen)
+    x[10, 10] = float("nan")
+    out = torch.zeros(1, device="cuda")
+    call(lib, x, out, 64, 64, 64, -1, 1)
+    assert bool(out.isnan().all())
+
+
 def test_capi_full_reduction_and_rejections(lib):
     gen = torch.Generator(device="cuda").manual_seed(1)
     x = torch.randn(512, 1000, device="cuda", generator=gen)
