@@ -37,6 +37,12 @@ int32_t asc_cuda_gemm_set_mode(int32_t mode);
  * those with a compile-time specialised kernel.  Process-wide. */
 int32_t asc_cuda_eltwise_set_lanes(int32_t lanes);
 
+/* Self-test of the bounded device-side waits: launches one warp that waits on a barrier nobody arrives on, with a
+ * limit of 0.5 ms (the kernels' own waits use the same routine with 400 ms).  The wait gives up, writes code
+ * 0x500 to the device's status word and the kernel returns normally; *gave_up (device memory, may be NULL)
+ * receives 1.  The next asc_cuda_check_device_status on that stream then reports status 5 and clears the word. */
+int32_t asc_cuda_selftest_wait_runs_out(uint32_t* gave_up, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

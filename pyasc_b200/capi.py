@@ -72,6 +72,7 @@ TUNING_PROTOTYPES: Dict[str, Sequence] = {
     "asc_cuda_gemm_capped": (P, P, P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32, c_int32, P),
     "asc_cuda_gemm_set_mode": (c_int32, ),
     "asc_cuda_eltwise_set_lanes": (c_int32, ),
+    "asc_cuda_selftest_wait_runs_out": (P, P),
 }
 
 

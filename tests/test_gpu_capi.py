@@ -329,3 +329,28 @@ def test_attention_properties_full_size(lib):
     ones = torch.ones_like(vd)
     o = attn(lib, qd, kd, ones, False)
     torch.testing.assert_close(o.float(), ones.float(), atol=1e-3, rtol=0)
+
+
+# ----------------------------------------------------------------------------------------- bounded waits
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_device_usable(lib):
+    """The one error path a healthy kernel never takes: a device-side wait whose limit expires.  The self-test
+    kernel waits 0.5 ms on a barrier nobody arrives on, gives up and returns normally; the host then sees status 5
+    with device code 0x500, the status word is clear again afterwards, and the next ordinary launch succeeds."""
+    capi.check_device_status(None)                                     # starts clean
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert lib.asc_cuda_selftest_wait_runs_out(P(flag), None) == 0
+    code = ctypes.c_uint32(0)
+    rc = lib.asc_cuda_check_device_status(None, ctypes.addressof(code))
+    assert rc == 5 and code.value == 0x500
+    assert capi.status_string(rc) == "bounded device-side wait ran out"
+    assert int(flag.item()) == 1
+    rc = lib.asc_cuda_check_device_status(None, ctypes.addressof(code))
+    assert rc == 0 and code.value == 0                                 # reported once, then clear
+    with pytest.raises(RuntimeError, match="0x500"):
+        lib.asc_cuda_selftest_wait_runs_out(None, None)
+        capi.check_device_status(None)
+    x, y = G.vadd_inputs(4096)
+    xd, yd = dev(x), dev(y)
+    out = torch.empty_like(xd)
+    run(lib, "asc_cuda_vadd_f32", P(xd), P(yd), P(out), 4096)
+    G.assert_exact(out, G.vadd(x, y))

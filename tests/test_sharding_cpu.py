@@ -24,6 +24,17 @@ def test_shard_ranges_cover_and_align():
         sharding.shard_range(10, 2, 2)
 
 
+def test_rotated_shards_cover_the_problem_once_per_pass():
+    for units, world, gran in [(16384, 8, 1), (1 << 28, 4, 1 << 16), (8192, 2, 256), (128, 8, 1), (1000, 3, 4), (7, 1, 1)]:
+        per_rank = [sharding.rotated_shards(units, world, r, gran) for r in range(world)]
+        assert all(per_rank[r][0] == sharding.shard_range(units, world, r, gran) for r in range(world))
+        for step in range(world):
+            taken = sorted(per_rank[r][step] for r in range(world))
+            assert taken == sharding.all_shard_ranges(units, world, gran)          # each shard exactly once
+        if world > 1:
+            assert all(per_rank[r][i] != per_rank[r][(i + 1) % world] for r in range(world) for i in range(world))
+
+
 def test_partitions_name_the_replicated_operands():
     assert sharding.partition_for("gemm_f16", m=8192).replicated == ("B", )
     assert sharding.partition_for("gemm_i8", m=8192).replicated == ("B", "b_scale")
@@ -56,6 +67,27 @@ def _worker(rank: int, world: int, port: int, units: int, gran: int):
 @pytest.mark.parametrize("units, gran", [(64, 1), (1000, 4), (130, 128)])
 def test_all_gather_over_gloo(units, gran):
     mp.spawn(_worker, args=(2, _free_port(), units, gran), nprocs=2, join=True)
+
+
+def _in_place_worker(rank: int, world: int, port: int, units: int, gran: int):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        want = torch.arange(units * 5, dtype=torch.float32).reshape(units, 5) * 3
+        full = torch.full((units, 5), -1.0)
+        lo, hi = sharding.shard_range(units, world, rank, gran)
+        full[lo:hi] = want[lo:hi]                      # this rank's shard, written at its place
+        sharding.all_gather_in_place(full, units, world, gran)
+        assert torch.equal(full, want), f"rank {rank}"
+        with pytest.raises(ValueError):
+            sharding.all_gather_in_place(full[:, :3], units, world, gran)      # not contiguous
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("units, gran", [(64, 1), (1024, 256), (1000, 4), (130, 128)])
+def test_all_gather_in_place_over_gloo(units, gran):
+    mp.spawn(_in_place_worker, args=(2, _free_port(), units, gran), nprocs=2, join=True)
 
 
 def _overlap_worker(rank: int, world: int, port: int, per: int, chunks: int):
