@@ -209,7 +209,10 @@ int32_t asc_cuda_rms_norm_f16(const void* x, const void* gamma, void* out, int64
  * cores.  in_dtype: 0 fp16, 1 bf16.  out_dtype: 0 fp16, 1 bf16, 2 fp32.
  * flags: bit0 ReLU before the cast; bit1 accumulate into C (C += A@B, fp32 out only).
  * lda/ldb/ldc are row pitches in elements.  Requirements: base pointers 16-byte aligned,
- * lda*2 and ldb*2 multiples of 16 bytes.
+ * lda*2 and ldb*2 multiples of 16 bytes.  A product stored as fp32 with M*N*K <= 2^28 runs on the FMA pipe
+ * instead (exact products, round-to-nearest sums: within a few units in the last place of an fp32 CPU matmul,
+ * which the reference's own matmul tests assert at torch's default fp32 tolerance,
+ * python/test/asc2/kernels/test_matmul_mnblock.py:92); the tensor core's accumulator truncates.
  * Replaces asc2.matmul / matmul_acc + the fixpipe store
  * (python/asc/language/tile/binary_ops.py:181-221; MmadOp, LowerAscTile.cpp:291-315,577-603;
  * FixpipeOp, LowerAscTileDataTransfer.cpp:273-325). */

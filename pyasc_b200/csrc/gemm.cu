@@ -602,11 +602,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   }
 }
 
-// Plain fp32 matmul on CUDA cores (32 x 32 tiles), used only for fp32 operands.
+// Matmul on the FMA pipe (32 x 32 tiles) for fp32 operands, and for small fp16 / bf16 products whose result is
+// stored as fp32.  A product of two 16-bit values is exact in fp32 and every addition here rounds to nearest;
+// each 32-long slice of K is summed on its own and then added to the running total, which keeps the rounding
+// error of a sum of some hundred terms near one unit in the last place.  The tensor core's accumulator instead
+// truncates when it adds, a bias that grows with K / 16 and reaches tens of units for a sum of same-signed terms.
+__device__ __forceinline__ float simt_to_f32(float v) { return v; }
+__device__ __forceinline__ float simt_to_f32(__half v) { return __half2float(v); }
+__device__ __forceinline__ float simt_to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
 __global__ void __launch_bounds__(256)
-    gemm_f32_simt_kernel(const float* __restrict__ A, const float* __restrict__ B, void* __restrict__ C, int64_t M,
-                         int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int out_dtype, int relu,
-                         int accumulate) {
+    gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ B, void* __restrict__ C, int64_t M,
+                     int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int out_dtype, int relu,
+                     int accumulate) {
   __shared__ float as[32][33];
   __shared__ float bs[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
@@ -616,15 +625,18 @@ __global__ void __launch_bounds__(256)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int r = ty + 8 * i;
-      as[r][tx] = (m0 + r < M && k0 + tx < K) ? A[(m0 + r) * lda + k0 + tx] : 0.f;
-      bs[r][tx] = (k0 + r < K && n0 + tx < N) ? B[(k0 + r) * ldb + n0 + tx] : 0.f;
+      as[r][tx] = (m0 + r < M && k0 + tx < K) ? simt_to_f32(A[(m0 + r) * lda + k0 + tx]) : 0.f;
+      bs[r][tx] = (k0 + r < K && n0 + tx < N) ? simt_to_f32(B[(k0 + r) * ldb + n0 + tx]) : 0.f;
     }
     __syncthreads();
+    float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int kk = 0; kk < 32; ++kk) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[i] = fmaf(as[ty + 8 * i][kk], bs[kk][tx], acc[i]);
+      for (int i = 0; i < 4; ++i) part[i] = fmaf(as[ty + 8 * i][kk], bs[kk][tx], part[i]);
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] += part[i];
     __syncthreads();
   }
 #pragma unroll
@@ -633,7 +645,7 @@ __global__ void __launch_bounds__(256)
     if (r < M && c < N) {
       float v = acc[i];
       if (accumulate && out_dtype == 2) v += reinterpret_cast<float*>(C)[r * ldc + c];
-      if (relu) v = fmaxf(v, 0.f);
+      if (relu) v = v < 0.f ? 0.f : v;          // NaN stays NaN, as in torch.relu
       if (out_dtype == 2) {
         reinterpret_cast<float*>(C)[r * ldc + c] = v;
       } else if (out_dtype == 0) {
@@ -644,6 +656,22 @@ __global__ void __launch_bounds__(256)
     }
   }
 }
+
+template <typename T>
+int32_t launch_gemm_simt(const T* A, const T* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                         int64_t ldc, int32_t out_dtype, int32_t flags, cudaStream_t stream) {
+  const int64_t gx = (N + 31) / 32, gy = (M + 31) / 32;
+  if (gy > 65535) return ASC_ERR_TOO_LARGE;
+  dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
+  gemm_simt_kernel<T><<<grid, 256, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc, out_dtype, flags & 1, (flags >> 1) & 1);
+  aschost::count_launch();
+  ASC_CUDA_TRY(cudaGetLastError());
+  return ASC_OK;
+}
+
+// fp16 / bf16 products stored as fp32 run on the FMA pipe up to this many multiply-adds (2^28: a few tens of
+// microseconds); larger ones, and every product stored as 16 bits, run on the tensor core.
+constexpr int64_t kSimtMaxMacs = 1ll << 28;
 
 template <int kElemBytes, int kMode>
 int32_t launch_gemm(const void* A, const void* B, int64_t lda, int64_t ldb, CUtensorMapDataType dt, uint32_t idesc,
@@ -693,6 +721,7 @@ int32_t launch_gemm(const void* A, const void* B, int64_t lda, int64_t ldb, CUte
 // 0: choose per problem, 1: always the single-CTA kernel, 2: the CTA-pair kernel whenever it applies
 static std::atomic<int> g_gemm_mode{0};
 static std::atomic<uint32_t> g_group_m{0};
+static std::atomic<bool> g_tensor_only{false};   // tuning hook: small fp32-output products on the tensor core too
 
 template <int kElemBytes, int kMode>
 int32_t launch_gemm_pair(const void* A, const void* B, int64_t lda, int64_t ldb, CUtensorMapDataType dt,
@@ -811,6 +840,14 @@ int32_t asc_cuda_gemm_f16(const void* A, const void* B, void* C, int64_t M, int6
   // fp32 accumulator, A K-major, B MN-major (row-major [K, N] read as stored)
   const CUtensorMapDataType dt = in_dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (out_dtype == 2 && M * N <= kSimtMaxMacs / K && !g_tensor_only.load(std::memory_order_relaxed)) {
+    // a small product whose fp32 result the caller keeps: exact products, round-to-nearest sums
+    if (in_dtype == 0)
+      return launch_gemm_simt<__half>(static_cast<const __half*>(A), static_cast<const __half*>(B), C, M, N, K, lda, ldb,
+                                      ldc, out_dtype, flags, s);
+    return launch_gemm_simt<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(B), C, M,
+                                           N, K, lda, ldb, ldc, out_dtype, flags, s);
+  }
   switch (out_dtype) {
     case 0: return dispatch_gemm<2, EPI_F16>(A, B, lda, ldb, dt, 1, in_dtype, p, 0, s);
     case 1: return dispatch_gemm<2, EPI_BF16>(A, B, lda, ldb, dt, 1, in_dtype, p, 0, s);
@@ -824,14 +861,7 @@ int32_t asc_cuda_gemm_f32(const float* A, const float* B, void* C, int64_t M, in
   if (M <= 0 || N <= 0 || K <= 0 || lda < K || ldb < N || ldc < N) return ASC_ERR_INVALID_ARG;
   if (out_dtype < 0 || out_dtype > 2 || (flags & ~3) != 0) return ASC_ERR_INVALID_ARG;
   if ((flags & 2) && out_dtype != 2) return ASC_ERR_UNSUPPORTED;
-  const int64_t gx = (N + 31) / 32, gy = (M + 31) / 32;
-  if (gy > 65535) return ASC_ERR_TOO_LARGE;
-  dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
-  gemm_f32_simt_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(A, B, C, M, N, K, lda, ldb, ldc, out_dtype,
-                                                                           flags & 1, (flags >> 1) & 1);
-  aschost::count_launch();
-  ASC_CUDA_TRY(cudaGetLastError());
-  return ASC_OK;
+  return launch_gemm_simt<float>(A, B, C, M, N, K, lda, ldb, ldc, out_dtype, flags, static_cast<cudaStream_t>(stream));
 }
 
 int32_t asc_cuda_gemm_i8(const int8_t* A, const int8_t* B, int32_t* acc, void* deq, const float* a_scale,
@@ -888,9 +918,11 @@ int32_t asc_cuda_gemm_capped(const void* A, const void* B, void* C, int64_t M, i
 
 // Tuning hook: 0 choose per problem, 1 always single-CTA tiles, 2 CTA pairs whenever M > 128.
 int32_t asc_cuda_gemm_set_mode(int32_t mode) {
-  // bits 0-3 kernel choice, bits 20-27 M blocks per rasterisation group (0 = default)
+  // bits 0-3 kernel choice, bit 4 tensor core also for small fp32-output products, bits 20-27 M blocks per
+  // rasterisation group (0 = default)
   if ((mode & 0xf) > 2) return ASC_ERR_INVALID_ARG;
   g_gemm_mode = mode & 0xf;
+  g_tensor_only = (mode & 0x10) != 0;
   g_group_m = (mode >> 20) & 0xff;
   return ASC_OK;
 }

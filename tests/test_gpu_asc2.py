@@ -94,10 +94,9 @@ def test_matmul_mnblock(m, k, n, core_num, m_tile, n_tile, n_tiles_per_block):
     c = torch.zeros((m, n), dtype=torch.float32)
     mtpb = K.mn_tiles_per_block(m, n, core_num, m_tile, n_tile, n_tiles_per_block)
     K.matmul_mn_blocked[core_num](a, b, c, a.shape, b.shape, c.shape, m_tile, mtpb, n_tile, n_tiles_per_block)
-    # The reference asserts with torch's fp32 defaults (rtol 1.3e-6).  The tensor core keeps an fp32
-    # accumulator but does not round every partial sum to nearest, so sums of a few hundred positive
-    # products land within ~30 ulp of the CPU's; the workload's own bound for this GEMM is 2e-3.
-    torch.testing.assert_close(c, a.to(torch.float32) @ b.to(torch.float32), rtol=1e-5, atol=1e-4)
+    # torch's fp32 defaults (rtol 1.3e-6), as the reference asserts (python/test/asc2/kernels/test_matmul_mnblock.py:92):
+    # a product of this size stored as fp32 runs on the FMA pipe with exact products and round-to-nearest sums
+    torch.testing.assert_close(c, a.to(torch.float32) @ b.to(torch.float32))
 
 
 @pytest.mark.parametrize("m, k, n, dtype", [(64, 128, 128, torch.float32), (64, 128, 256, torch.float16),
@@ -273,6 +272,6 @@ def test_pipelined_launch_after_a_device_reset(backend, platform, device_id):
     config.set_platform(backend, platform, device_id)
     out2 = torch.empty_like(x).pin_memory()
     T.softmax_launch(xp, out2)
-    assert [s.value for s in launcher._pipe_streams[dev_id]] != [s.value for s in before] or True   # handles may be reused
+    assert dev_id in launcher._pipe_streams and before is not None
     assert torch.equal(out2, out)
     G.assert_softmax_close(out2, G.softmax(x))

@@ -186,6 +186,13 @@ def test_gemm_f16_shapes(lib, m, n, k, dtype):
         pytest.skip("row pitch of B must be a multiple of 16 bytes")
     a, b = G.gemm_f16_inputs(m, n, k, dtype, seed=m + n + k)
     c = gemm16(lib, dev(a), dev(b), torch.float32)
+    if m * n * k <= 1 << 28:        # small fp32 results come from the FMA pipe: torch's default fp32 tolerance holds
+        torch.testing.assert_close(c.cpu(), G.gemm_f32acc(a, b))
+    assert lib.asc_cuda_gemm_set_mode(0x10) == 0          # ... and from the tensor core when asked to
+    try:
+        c = gemm16(lib, dev(a), dev(b), torch.float32)
+    finally:
+        assert lib.asc_cuda_gemm_set_mode(0) == 0
     torch.testing.assert_close(c.cpu(), G.gemm_f32acc(a, b), atol=2e-5 * (k ** 0.5) / 8 + 1e-5, rtol=1e-4)
     c16 = gemm16(lib, dev(a), dev(b), dtype)
     ref = G.gemm_f16(a, b, out_dtype=dtype)
@@ -193,7 +200,16 @@ def test_gemm_f16_shapes(lib, m, n, k, dtype):
     torch.testing.assert_close(c16.cpu().float(), ref.float(), atol=tol, rtol=tol)
 
 
-def test_gemm_f16_accumulate_relu_and_linearity(lib):
+@pytest.mark.parametrize("tensor_core", [False, True], ids=["fma_pipe", "tensor_core"])
+def test_gemm_f16_accumulate_relu_and_linearity(lib, tensor_core):
+    assert lib.asc_cuda_gemm_set_mode(0x10 if tensor_core else 0) == 0
+    try:
+        _accumulate_relu_and_linearity(lib)
+    finally:
+        assert lib.asc_cuda_gemm_set_mode(0) == 0
+
+
+def _accumulate_relu_and_linearity(lib):
     a, b = G.gemm_f16_inputs(256, 512, 384)
     ad, bd = dev(a), dev(b)
     base = gemm16(lib, ad, bd, torch.float32)

@@ -2,13 +2,14 @@
 
 ``ASC2_REFERENCE_TESTS`` names a directory holding the reference project's ``python/test/asc2`` tree (its
 ``conftest.py``, ``kernels/`` and ``operations/``, exactly as the reference ships them).  The suite is run in a
-child pytest with this package's ``asc`` / ``asc2`` first on ``PYTHONPATH`` and the options the reference's
-conftest declares (python/test/asc2/conftest.py:27-33): ``--backend CUDA --platform B200``.  The reference's
-files are not part of this repository, so without the variable the test is skipped.
+child pytest with this package's ``asc`` / ``asc2`` first on ``PYTHONPATH`` and one option of the reference's
+conftest (python/test/asc2/conftest.py:27-33) changed from its default: ``--backend CUDA``.  ``--platform`` keeps
+the reference's default (an Ascend 950 part); ``set_platform`` on the CUDA back end takes the device it finds, and
+the tests the reference guards with ``require_c310`` (conftest.py:62-69: features of that Ascend generation, such
+as 1-D softmax and most operation tests) therefore run instead of being skipped.  The reference's files are not
+part of this repository, so without the variable the test is skipped.
 
-What has to hold: no test of the reference fails.  Tests the reference itself guards with ``require_c310``
-(python/test/asc2/conftest.py:62-69: features of one Ascend architecture generation) run here as well, because
-``platform_to_arch(B200)`` answers C310: nothing is skipped for the architecture.
+What has to hold: every test of the reference passes, none fails, none is skipped.
 """
 import os
 import re
@@ -26,7 +27,7 @@ def run_reference_suite(ref_dir: str, extra=()):
     env = dict(os.environ)
     env["PYTHONPATH"] = PKG_DIR + os.pathsep + env.get("PYTHONPATH", "")
     env.pop("DRY_RUN", None)
-    cmd = [sys.executable, "-m", "pytest", ref_dir, "--backend", "CUDA", "--platform", "B200", "--import-mode=importlib",
+    cmd = [sys.executable, "-m", "pytest", ref_dir, "--backend", "CUDA", "--import-mode=importlib",
            "-p", "no:cacheprovider", "-q", "-rfEs", "--no-header", *extra]
     # cwd outside this repository: its tests/conftest.py must not be picked up next to the reference's own
     proc = subprocess.run(cmd, env=env, cwd=ref_dir, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
@@ -49,6 +50,6 @@ def test_reference_asc2_suite_passes_unmodified():
         with open(report, "w") as f:
             f.write(proc.stdout)
     summary = "\n".join(proc.stdout.splitlines()[-60:])
-    assert counts["failed"] == 0 and counts["error"] == 0, summary
-    assert counts["passed"] >= 200, summary            # 10 kernel files + 8 operation files, parametrised
+    assert counts["failed"] == 0 and counts["error"] == 0 and counts["skipped"] == 0, summary
+    assert counts["passed"] >= 240, summary            # 10 kernel files + 8 operation files, parametrised
     assert proc.returncode == 0, summary
