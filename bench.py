@@ -765,7 +765,8 @@ class Dist:
         if self.enabled:
             import torch.distributed as dist
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-            dist.init_process_group(backend, rank=self.rank, world_size=self.world)
+            kwargs = {"device_id": torch.device("cuda", self.local_rank)} if backend == "nccl" else {}
+            dist.init_process_group(backend, rank=self.rank, world_size=self.world, **kwargs)
 
     def barrier(self) -> None:
         if self.enabled:

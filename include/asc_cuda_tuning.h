@@ -30,7 +30,8 @@ int32_t asc_cuda_gemm_capped(const void* A, const void* B, void* C, int64_t M, i
 
 /* GEMM kernel selection: 0 choose per problem (default), 1 always the single-CTA 128 x 256 kernel,
  * 2 the CTA-pair 256 x 256 kernel whenever M > 128.  Bit 4 (0x10): run small fp16 / bf16 products with an fp32
- * result on the tensor core as well (by default they take the FMA pipe, see asc_cuda_gemm_f16).  Process-wide. */
+ * result on the tensor core as well (by default they take the FMA pipe, see asc_cuda_gemm_f16).  Bit 5 (0x20): never
+ * split K over several CTAs per tile.  Process-wide. */
 int32_t asc_cuda_gemm_set_mode(int32_t mode);
 
 /* bits 0-7: elements each thread evaluates per opcode dispatch in asc_cuda_eltwise_program's aligned path

@@ -61,6 +61,10 @@ struct GemmParams {
   int32_t vec_ok;       // 16-byte vector stores allowed (alignment of c/deq and ldc)
   uint32_t* status;
   uint32_t group_m;     // M blocks per rasterisation group (0 = default)
+  // split-K kernel only: every 128 x 256 tile is computed by `split_k` CTAs, each over its own range of K
+  int32_t split_k;
+  uint32_t* arrivals;   // one counter per tile, zero at launch: slices whose partial tile is in the workspace
+  uint32_t* partials;   // [tiles][split_k][128][256] 32-bit accumulator words
 };
 
 struct SharedCtl {
@@ -602,6 +606,247 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
   }
 }
 
+// ----------------------------------------------------------------------------------------------
+// Split-K variant for problems with far fewer 128 x 256 tiles than SMs (a long K over a small C): `split_k`
+// CTAs share a tile, each runs the same TMA / tcgen05 main loop over its own contiguous range of K blocks and
+// writes its 128 x 256 accumulator to a workspace in global memory.  Once all slices of a tile have arrived
+// (a counter per tile; the grid is at most one CTA per SM, so all of them are running), every CTA sums a band of
+// rows of the tile over all slices, always in slice order, so the result does not depend on which CTA finished
+// first, applies the epilogue and stores the band.  The wait is bounded like every other wait in this library.
+// ----------------------------------------------------------------------------------------------
+constexpr uint32_t kTileWords = kBlockM * kBlockN;      // 32-bit words of one partial tile (128 KiB)
+
+template <int kMode>
+__device__ __forceinline__ void splitk_store_pair(const GemmParams& p, int64_t row, int64_t col, uint32_t w0, uint32_t w1) {
+  // two neighbouring columns of one output row; w0 / w1 are fp32 (or, for int8, int32) sums over all slices
+  if (row >= p.M || col >= p.N) return;
+  const bool two = col + 1 < p.N;
+  if (kMode == EPI_I8) {
+    if (p.c != nullptr) {
+      int32_t* dst = reinterpret_cast<int32_t*>(p.c) + row * p.ldc + col;
+      dst[0] = static_cast<int32_t>(w0);
+      if (two) dst[1] = static_cast<int32_t>(w1);
+    }
+    if (p.deq != nullptr) {
+      const float as = __ldg(p.a_scale + row);
+      __half* dst = reinterpret_cast<__half*>(p.deq) + row * p.ldc + col;
+      dst[0] = __float2half_rn(__fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(w0)), as), __ldg(p.b_scale + col)));
+      if (two)
+        dst[1] = __float2half_rn(__fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(w1)), as), __ldg(p.b_scale + col + 1)));
+    }
+    return;
+  }
+  float a = __uint_as_float(w0), b = __uint_as_float(w1);
+  if (kMode == EPI_F32) {
+    float* dst = reinterpret_cast<float*>(p.c) + row * p.ldc + col;
+    if (p.accumulate) {
+      a += dst[0];
+      if (two) b += dst[1];
+    }
+    if (p.relu) {
+      a = fmaxf(a, 0.f);
+      b = fmaxf(b, 0.f);
+    }
+    dst[0] = a;
+    if (two) dst[1] = b;
+    return;
+  }
+  if (p.relu) {
+    a = fmaxf(a, 0.f);
+    b = fmaxf(b, 0.f);
+  }
+  if (kMode == EPI_F16) {
+    __half* dst = reinterpret_cast<__half*>(p.c) + row * p.ldc + col;
+    dst[0] = __float2half_rn(a);
+    if (two) dst[1] = __float2half_rn(b);
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + row * p.ldc + col;
+    dst[0] = __float2bfloat16_rn(a);
+    if (two) dst[1] = __float2bfloat16_rn(b);
+  }
+}
+
+template <int kElemBytes, int kMode>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+    gemm_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                               const GemmParams p, const uint32_t idesc) {
+  constexpr int kBlockK = kKBytes / kElemBytes;
+  constexpr int kUmmaK = 32 / kElemBytes;
+  constexpr int kNBlockCols = 128 / kElemBytes;
+  constexpr int kNBlocks = kBlockN / kNBlockCols;
+  constexpr uint32_t kBBlockBytes = kBlockK * 128;
+  constexpr uint32_t kBKStep = kUmmaK * 128;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ SharedCtl ctl;
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  volatile uint32_t* abort_flag = &ctl.abort_flag;
+
+  const int64_t num_n = (p.N + kBlockN - 1) / kBlockN;
+  const int64_t num_kb = (p.K + kBlockK - 1) / kBlockK;
+  const int64_t tile = blockIdx.x / p.split_k;
+  const int64_t slice = blockIdx.x % p.split_k;
+  const int64_t m_blk = tile / num_n, n_blk = tile % num_n;
+  // K blocks of this slice: the first `num_kb % split_k` slices take one block more
+  const int64_t kb_each = num_kb / p.split_k, kb_more = num_kb % p.split_k;
+  const int64_t kb_lo = slice * kb_each + (slice < kb_more ? slice : kb_more);
+  const int64_t kb_hi = kb_lo + kb_each + (slice < kb_more ? 1 : 0);
+
+  if (threadIdx.x == 0) {
+    ctl.abort_flag = 0;
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(smem_u32(&ctl.full[s]), 1);
+      mbar_init(smem_u32(&ctl.empty[s]), 1);
+    }
+    mbar_init(smem_u32(&ctl.tmem_full[0]), 1);
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctl.tmem_base), kBlockN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl.tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    uint32_t stage = 0, phase = 0;
+    bool ok = lane == 0;
+    const int32_t m0 = static_cast<int32_t>(m_blk * kBlockM);
+    const int32_t n0 = static_cast<int32_t>(n_blk * kBlockN);
+    for (int64_t kb = kb_lo; kb < kb_hi && ok; ++kb) {
+      ok = mbar_wait<kWaitHintNs>(smem_u32(&ctl.empty[stage]), phase ^ 1, abort_flag, p.status, ASC_DEV_TIMEOUT_EMPTY);
+      if (!ok) break;
+      const uint32_t full = smem_u32(&ctl.full[stage]);
+      const uint32_t sa = smem_base + stage * kStageBytes;
+      const uint32_t sb = sa + kSmemA;
+      const int32_t k0 = static_cast<int32_t>(kb * kBlockK);
+      mbar_arrive_expect_tx(full, kStageBytes);
+      tma_load_2d(sa, &tmap_a, full, k0, m0);
+#pragma unroll
+      for (int j = 0; j < kNBlocks; ++j) tma_load_2d(sb + j * kBBlockBytes, &tmap_b, full, n0 + j * kNBlockCols, k0);
+      if (++stage == kStages) {
+        stage = 0;
+        phase ^= 1;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    uint32_t stage = 0, phase = 0;
+    bool ok = lane == 0;
+    for (int64_t kb = kb_lo; kb < kb_hi && ok; ++kb) {
+      ok = mbar_wait<kWaitHintNs>(smem_u32(&ctl.full[stage]), phase, abort_flag, p.status, ASC_DEV_TIMEOUT_FULL);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t sa = smem_base + stage * kStageBytes;
+      const uint32_t sb = sa + kSmemA;
+      const uint64_t adesc = make_smem_desc_sw128(sa, 16, 1024);
+      const uint64_t bdesc = make_smem_desc_sw128(sb, kBBlockBytes, 1024);
+#pragma unroll
+      for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+        const uint64_t ad = adesc + static_cast<uint64_t>((k * 32) >> 4);
+        const uint64_t bd = bdesc + static_cast<uint64_t>((k * kBKStep) >> 4);
+        const uint32_t accumulate = (kb > kb_lo || k > 0) ? 1u : 0u;
+        if (kElemBytes == 2) {
+          umma_f16_ss(tmem_base, ad, bd, idesc, accumulate);
+        } else {
+          umma_i8_ss(tmem_base, ad, bd, idesc, accumulate);
+        }
+      }
+      umma_commit(smem_u32(&ctl.empty[stage]));
+      if (kb == kb_hi - 1) umma_commit(smem_u32(&ctl.tmem_full[0]));
+      if (++stage == kStages) {
+        stage = 0;
+        phase ^= 1;
+      }
+    }
+  } else {
+    // ---------------- epilogue warps: publish the partial tile, then reduce a band of rows ----------------
+    const uint32_t quarter = warp & 3;
+    const uint32_t e = threadIdx.x - 64;                      // 0 .. 127 among the epilogue threads
+    uint32_t* mine = p.partials + (tile * p.split_k + slice) * static_cast<int64_t>(kTileWords);
+    bool ok = true;
+    if (kb_hi > kb_lo) {
+      ok = mbar_wait_warp<kWaitHintNs>(smem_u32(&ctl.tmem_full[0]), 0, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((quarter * 32u) << 16);
+        uint4* dst = reinterpret_cast<uint4*>(mine + (quarter * 32u + lane) * kBlockN);
+#pragma unroll 1
+        for (int c = 0; c < kBlockN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) dst[c * 8 + i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+        }
+        tc_fence_before();
+      }
+    } else {
+      // a slice without K blocks (more slices than blocks never happens by construction, kept for safety)
+      for (uint32_t i = e; i < kTileWords; i += 128) mine[i] = 0u;
+    }
+    __threadfence();
+    named_bar_sync(1, 128);
+    if (e == 0) {
+      if (ok && !*abort_flag) atomicAdd(p.arrivals + tile, 1u);
+      // wait for the other slices of this tile
+      const uint64_t t0 = global_timer_ns();
+      volatile uint32_t* arrived = p.arrivals + tile;
+      while (ok && *arrived < static_cast<uint32_t>(p.split_k)) {
+        __nanosleep(100);
+        if (*abort_flag || global_timer_ns() - t0 > kWaitLimitNs) {
+          *abort_flag = 1;
+          atomicCAS(p.status, 0u, static_cast<uint32_t>(ASC_DEV_TIMEOUT_OTHER));
+          ok = false;
+        }
+      }
+    }
+    named_bar_sync(1, 128);
+    __threadfence();
+    if (!*abort_flag) {
+      const int rows_each = (kBlockM + p.split_k - 1) / p.split_k;
+      const int r_lo = static_cast<int>(slice) * rows_each;
+      const int r_hi = r_lo + rows_each < kBlockM ? r_lo + rows_each : kBlockM;
+      const uint32_t* first = p.partials + tile * p.split_k * static_cast<int64_t>(kTileWords);
+      for (int r = r_lo; r < r_hi; ++r) {
+        const uint2* src = reinterpret_cast<const uint2*>(first + r * kBlockN) + e;
+        uint2 v = __ldcg(src);
+        for (int s2 = 1; s2 < p.split_k; ++s2) {
+          const uint2 w = __ldcg(src + s2 * (kTileWords / 2));
+          if (kMode == EPI_I8) {
+            v.x += w.x;
+            v.y += w.y;
+          } else {
+            v.x = __float_as_uint(__fadd_rn(__uint_as_float(v.x), __uint_as_float(w.x)));
+            v.y = __float_as_uint(__fadd_rn(__uint_as_float(v.y), __uint_as_float(w.y)));
+          }
+        }
+        splitk_store_pair<kMode>(p, m_blk * kBlockM + r, n_blk * kBlockN + 2 * e, v.x, v.y);
+      }
+    }
+  }
+
+  __syncwarp();
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kBlockN);
+  }
+}
+
 // Matmul on the FMA pipe (32 x 32 tiles) for fp32 operands, and for small fp16 / bf16 products whose result is
 // stored as fp32.  A product of two 16-bit values is exact in fp32 and every addition here rounds to nearest;
 // each 32-long slice of K is summed on its own and then added to the running total, which keeps the rounding
@@ -721,6 +966,7 @@ int32_t launch_gemm(const void* A, const void* B, int64_t lda, int64_t ldb, CUte
 // 0: choose per problem, 1: always the single-CTA kernel, 2: the CTA-pair kernel whenever it applies
 static std::atomic<int> g_gemm_mode{0};
 static std::atomic<uint32_t> g_group_m{0};
+static std::atomic<bool> g_no_split_k{false};   // tuning hook: never split K over several CTAs
 static std::atomic<bool> g_tensor_only{false};   // tuning hook: small fp32-output products on the tensor core too
 
 template <int kElemBytes, int kMode>
@@ -787,8 +1033,82 @@ int32_t launch_gemm_pair(const void* A, const void* B, int64_t lda, int64_t ldb,
   ASC_CUDA_TRY(cudaGetLastError());
   return ASC_OK;
 }
+// Workspace of the split-K kernel: a 1 KiB header of per-tile arrival counters, then the partial tiles.
+constexpr size_t kSplitHeaderBytes = 1024;
+constexpr int kSplitMaxTiles = static_cast<int>(kSplitHeaderBytes / sizeof(uint32_t));
+constexpr size_t kPartialTileBytes = static_cast<size_t>(kTileWords) * sizeof(uint32_t);
 
-// Single-CTA kernel for small problems, CTA pairs once there are enough 256 x 256 tiles to fill the GPU.
+// How many slices of K each 128 x 256 tile is cut into when `ctas` CTAs may run at once: as many as fill the GPU,
+// but at least four K blocks per slice (below that the pipeline fill and the reduction cost more than the
+// parallelism returns) and at most one slice per row band of 2 rows.  1 means: do not split.
+inline int split_k_slices(int64_t tiles, int64_t num_kb, int64_t ctas) {
+  if (tiles <= 0 || tiles > kSplitMaxTiles || tiles * 2 > ctas) return 1;
+  int64_t s = ctas / tiles;
+  if (s > num_kb / 4) s = num_kb / 4;
+  if (s > 64) s = 64;
+  return s < 2 ? 1 : static_cast<int>(s);
+}
+
+// Launches the split-K kernel.  `workspace` (kSplitHeaderBytes + tiles * split * 128 KiB, 256-byte aligned) is the
+// caller's when given; otherwise it is taken from the stream-ordered allocator for the duration of the kernel, so
+// that calls on different streams never share it.
+template <int kElemBytes, int kMode>
+int32_t launch_gemm_splitk(const void* A, const void* B, int64_t lda, int64_t ldb, CUtensorMapDataType dt,
+                           uint32_t idesc, GemmParams p, int split, void* workspace, cudaStream_t stream) {
+  constexpr int kBlockK = kKBytes / kElemBytes;
+  constexpr int kNBlockCols = 128 / kElemBytes;
+  CUtensorMap tmap_a, tmap_b;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.M)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(lda) * kElemBytes};
+    const uint32_t box[2] = {kBlockK, kBlockM};
+    int32_t rc = aschost::encode_tmap(&tmap_a, dt, 2, A, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (rc != ASC_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.K)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(ldb) * kElemBytes};
+    const uint32_t box[2] = {kNBlockCols, kBlockK};
+    int32_t rc = aschost::encode_tmap(&tmap_b, dt, 2, B, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (rc != ASC_OK) return rc;
+  }
+  int32_t rc = aschost::device_status_word(&p.status);
+  if (rc != ASC_OK) return rc;
+  auto kernel = gemm_tcgen05_splitk_kernel<kElemBytes, kMode>;
+  static aschost::PerDevice attr_set;
+  int dev = 0;
+  ASC_CUDA_TRY(cudaGetDevice(&dev));
+  if (!attr_set.get(dev)) {
+    ASC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
+    attr_set.set(dev, 1);
+  }
+  const int64_t tiles = ((p.M + kBlockM - 1) / kBlockM) * ((p.N + kBlockN - 1) / kBlockN);
+  if (tiles > kSplitMaxTiles || split < 1) return ASC_ERR_TOO_LARGE;
+  const size_t bytes = kSplitHeaderBytes + static_cast<size_t>(tiles) * split * kPartialTileBytes;
+  void* ws = workspace;
+  if (ws == nullptr && (rc = aschost::scratch_alloc(&ws, bytes, stream)) != ASC_OK) return rc;
+  p.split_k = split;
+  p.arrivals = static_cast<uint32_t*>(ws);
+  p.partials = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ws) + kSplitHeaderBytes);
+  // the counters start at zero for every launch; the partial tiles are overwritten before they are read
+  cudaError_t e = cudaMemsetAsync(ws, 0, kSplitHeaderBytes, stream);
+  if (e == cudaSuccess) {
+    kernel<<<static_cast<unsigned>(tiles * split), kGemmThreads, kGemmSmem, stream>>>(tmap_a, tmap_b, p, idesc);
+    aschost::count_launch();
+    e = cudaGetLastError();
+  }
+  if (workspace == nullptr) {
+    const int32_t rc2 = aschost::scratch_free(ws, stream);
+    if (e == cudaSuccess && rc2 != ASC_OK) return rc2;
+  }
+  ASC_CUDA_TRY(e);
+  return ASC_OK;
+}
+
+// Single-CTA kernel for small problems (K split over several CTAs per tile when the tiles alone would leave most
+// SMs idle), CTA pairs once there are enough 256 x 256 tiles to fill the GPU.
 template <int kElemBytes, int kMode>
 int32_t dispatch_gemm(const void* A, const void* B, int64_t lda, int64_t ldb, CUtensorMapDataType dt, uint32_t c_fmt,
                       uint32_t ab_fmt, GemmParams p, int32_t max_ctas, cudaStream_t stream) {
@@ -801,6 +1121,15 @@ int32_t dispatch_gemm(const void* A, const void* B, int64_t lda, int64_t ldb, CU
     return launch_gemm_pair<kElemBytes, kMode>(A, B, lda, ldb, dt, idesc, p, max_ctas, stream);
   }
   const uint32_t idesc = make_idesc(c_fmt, ab_fmt, ab_fmt, 0, 1, kBlockM, kBlockN);
+  if (mode == 0 && max_ctas == 0 && !g_no_split_k.load(std::memory_order_relaxed)) {
+    int sms = 0;
+    int32_t rc = aschost::sm_count(&sms);
+    if (rc != ASC_OK) return rc;
+    const int64_t tiles = ((p.M + kBlockM - 1) / kBlockM) * ((p.N + kBlockN - 1) / kBlockN);
+    const int64_t num_kb = (p.K * kElemBytes + kKBytes - 1) / kKBytes;
+    const int split = split_k_slices(tiles, num_kb, sms);
+    if (split > 1) return launch_gemm_splitk<kElemBytes, kMode>(A, B, lda, ldb, dt, idesc, p, split, nullptr, stream);
+  }
   return launch_gemm<kElemBytes, kMode>(A, B, lda, ldb, dt, idesc, p, max_ctas, stream);
 }
 
@@ -918,11 +1247,12 @@ int32_t asc_cuda_gemm_capped(const void* A, const void* B, void* C, int64_t M, i
 
 // Tuning hook: 0 choose per problem, 1 always single-CTA tiles, 2 CTA pairs whenever M > 128.
 int32_t asc_cuda_gemm_set_mode(int32_t mode) {
-  // bits 0-3 kernel choice, bit 4 tensor core also for small fp32-output products, bits 20-27 M blocks per
-  // rasterisation group (0 = default)
+  // bits 0-3 kernel choice, bit 4 tensor core also for small fp32-output products, bit 5 no split-K, bits 20-27 M
+  // blocks per rasterisation group (0 = default)
   if ((mode & 0xf) > 2) return ASC_ERR_INVALID_ARG;
   g_gemm_mode = mode & 0xf;
   g_tensor_only = (mode & 0x10) != 0;
+  g_no_split_k = (mode & 0x20) != 0;
   g_group_m = (mode >> 20) & 0xff;
   return ASC_OK;
 }

@@ -35,6 +35,13 @@ int32_t encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, uint32_t rank, 
                     const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                     CUtensorMapSwizzle swizzle, CUtensorMapL2promotion promo);
 
+// Stream-ordered scratch memory for kernels that need a workspace: taken from a memory pool this library owns
+// (one per device, created at first use; freed blocks stay in the pool instead of going back to the driver at
+// every synchronisation), allocated and released in stream order, so launches on different streams never share
+// a workspace.
+int32_t scratch_alloc(void** out, size_t bytes, cudaStream_t stream);
+int32_t scratch_free(void* ptr, cudaStream_t stream);
+
 // Kernels launched by this library since load.
 extern std::atomic<uint64_t> g_launch_count;
 inline void count_launch() { g_launch_count.fetch_add(1, std::memory_order_relaxed); }

@@ -67,6 +67,37 @@ int32_t sm_count(int* out) {
   return ASC_OK;
 }
 
+static cudaMemPool_t g_scratch_pool[kMaxDevices] = {nullptr};
+
+int32_t scratch_alloc(void** out, size_t bytes, cudaStream_t stream) {
+  int dev = 0;
+  ASC_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return ASC_ERR_INVALID_ARG;
+  cudaMemPool_t pool = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_scratch_pool[dev] == nullptr) {
+      cudaMemPoolProps props = {};
+      props.allocType = cudaMemAllocationTypePinned;
+      props.handleTypes = cudaMemHandleTypeNone;
+      props.location.type = cudaMemLocationTypeDevice;
+      props.location.id = dev;
+      ASC_CUDA_TRY(cudaMemPoolCreate(&pool, &props));
+      uint64_t keep = ~0ull;      // freed blocks stay in the pool
+      ASC_CUDA_TRY(cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep));
+      g_scratch_pool[dev] = pool;
+    }
+    pool = g_scratch_pool[dev];
+  }
+  ASC_CUDA_TRY(cudaMallocFromPoolAsync(out, bytes, pool, stream));
+  return ASC_OK;
+}
+
+int32_t scratch_free(void* ptr, cudaStream_t stream) {
+  ASC_CUDA_TRY(cudaFreeAsync(ptr, stream));
+  return ASC_OK;
+}
+
 static std::atomic<PFN_cuTensorMapEncodeTiled_v12000> g_encode{nullptr};
 
 int32_t encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, uint32_t rank, const void* base,

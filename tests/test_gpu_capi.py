@@ -225,6 +225,42 @@ def _accumulate_relu_and_linearity(lib):
     assert torch.equal(gemm16(lib, ad, eye, torch.float16), ad)
 
 
+@pytest.mark.parametrize("m, n, k", [(256, 256, 8192), (128, 256, 2048), (100, 520, 4104), (384, 768, 4096),
+                                     (1024, 1024, 16384), (64, 64, 65536)])
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.float32])
+def test_gemm_f16_split_k(lib, m, n, k, out_dtype):
+    """A long K over a C of a few tiles: K is split over several CTAs per tile and the partial tiles are summed
+    from a workspace.  Against the CPU oracle at the workload's tolerance, against the unsplit kernel, and
+    bit-identical from run to run (the slices are always summed in the same order)."""
+    a, b = G.gemm_f16_inputs(m, n, k, seed=k + m)
+    ad, bd = dev(a), dev(b)
+    assert lib.asc_cuda_gemm_set_mode(0x10) == 0           # fp32 results from the tensor core as well
+    try:
+        c = gemm16(lib, ad, bd, out_dtype, flags=1)
+        again = gemm16(lib, ad, bd, out_dtype, flags=1)
+        assert lib.asc_cuda_gemm_set_mode(0x30) == 0       # the same without split-K
+        whole = gemm16(lib, ad, bd, out_dtype, flags=1)
+    finally:
+        assert lib.asc_cuda_gemm_set_mode(0) == 0
+    assert torch.equal(c, again)
+    ref = G.gemm_f16(a, b, relu=True, out_dtype=out_dtype)
+    if out_dtype == torch.float16:
+        G.assert_half_close(c, ref)
+        G.assert_half_close(c, whole.cpu())
+    else:
+        torch.testing.assert_close(c.cpu(), ref, atol=2e-5 * (k ** 0.5) / 8 + 1e-5, rtol=1e-4)
+        torch.testing.assert_close(c, whole, atol=2e-5 * (k ** 0.5) / 8 + 1e-5, rtol=1e-4)
+    if out_dtype == torch.float32:                         # C += A @ B through the split-K epilogue
+        assert lib.asc_cuda_gemm_set_mode(0x10) == 0
+        try:
+            acc = c.clone()
+            gemm16(lib, ad, bd, torch.float32, flags=2, c=acc)
+            plain = gemm16(lib, ad, bd, torch.float32)
+        finally:
+            assert lib.asc_cuda_gemm_set_mode(0) == 0
+        assert torch.equal(acc, c + plain)
+
+
 def test_gemm_f16_full_size(lib):
     m = n = k = 8192
     a, b = G.gemm_f16_inputs(m, n, k)
@@ -266,6 +302,23 @@ def test_gemm_i8_shapes_bit_exact(lib, m, n, k):
     ref = G.gemm_i8(a, b)
     G.assert_exact(acc, ref)
     G.assert_exact(deq, G.dequant(ref, sa, sb))
+
+
+@pytest.mark.parametrize("m, n, k", [(256, 256, 8192), (130, 272, 16400), (512, 512, 32768)])
+def test_gemm_i8_split_k_bit_exact(lib, m, n, k):
+    """Integer partial sums add exactly, so the split-K result equals the unsplit one and the oracle bit for bit,
+    dequantised output included."""
+    a, b, sa, sb = G.gemm_i8_inputs(m, n, k, seed=k)
+    acc, deq = gemm8(lib, dev(a), dev(b), dev(sa), dev(sb))
+    ref = G.gemm_i8(a, b)
+    G.assert_exact(acc, ref)
+    G.assert_exact(deq, G.dequant(ref, sa, sb))
+    assert lib.asc_cuda_gemm_set_mode(0x20) == 0
+    try:
+        acc2, deq2 = gemm8(lib, dev(a), dev(b), dev(sa), dev(sb))
+    finally:
+        assert lib.asc_cuda_gemm_set_mode(0) == 0
+    assert torch.equal(acc, acc2) and torch.equal(deq, deq2)
 
 
 def test_gemm_i8_extreme_values(lib):
