@@ -429,6 +429,8 @@ class _Planned(Workload):
                 os.environ["DRY_RUN"] = prev
         plan = kernel.last_plan
         assert plan.pattern in patterns and len(plan.steps) == 1 and plan.pipeline is not None, plan
+        from pyasc_b200 import jit
+        jit.prepare(plan, wait=True)        # the kernel specialised for this expression: built (or found in the cache) now
         self.spec = plan.pipeline
         self.units, self.granule = self.spec.units, self.spec.granule
         self.ptrs = {i: t.data_ptr() for i, t in ptr_args.items()}
@@ -1087,7 +1089,8 @@ def run_ours(args) -> Dict[str, Any]:
                    "timing": "CUDA events around one replay of a CUDA graph holding the K launches, max over ranks"},
         "roofline": head["roofline"], "e2e": head.get("e2e"), "cpu_baseline": head.get("cpu_baseline"),
         "gpu_launches": total_launches + timed_launches, "gpu_launches_timed": timed_launches, "clocks": clocks,
-        "workloads": results, "summary": summarise(results),
+        "workloads": results, "native_so_jit": [os.path.relpath(b, ROOT) for b in jit_builds()],
+        "summary": summarise(results),
     }
     if args.summary_file and dist.rank == 0:
         with open(args.summary_file, "w") as f:
@@ -1095,6 +1098,15 @@ def run_ours(args) -> Dict[str, Any]:
                        ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained", "source")}, "clocks": clocks,
                        "summary": line["summary"]}, f, indent=1)
     return line if dist.rank == 0 else {}
+
+
+def jit_builds() -> List[str]:
+    """Libraries of kernels specialised at first use that this process built or loaded (pyasc_b200/jit.py)."""
+    from pyasc_b200 import jit
+    failed = jit.failures()
+    if failed:
+        print(f"[bench] {len(failed)} specialised kernels failed to build: {list(failed.values())[0][:400]}", file=sys.stderr)
+    return list(jit.builds)
 
 
 def load_traffic() -> Dict[str, float]:

@@ -173,6 +173,15 @@ int32_t asc_cuda_row_program(const int32_t* ops, const int32_t* args, int32_t n_
                              const int32_t* input_types, int32_t n_inputs, void* out, int32_t out_type, int64_t rows,
                              int64_t cols, const int64_t* lds, int32_t row_result, void* stream);
 
+/* Registers a kernel specialised for one program, so that asc_cuda_eltwise_program[_2d] (kind 0) or
+ * asc_cuda_row_program (kind 1000 + columns per thread: 1, 2, 4, ... 32) runs it instead of the interpreter whenever
+ * that program is submitted.  `words[k]` = ops[k] | (args[k] << 16 for a LOAD, TEE or TMP) | (1 << 24 for a LOAD of
+ * a one-element-per-row input); `fn` is the entry point `int asc_jit_run(const void* program, int64_t n_or_rows,
+ * int32_t flag, int32_t sms, void* stream)` of a shared library built from pyasc_b200/csrc/eltwise_program.cuh
+ * (pyasc_b200/jit.py generates, builds and caches such libraries at first use of an expression).  Plays the role of the
+ * reference's first-use build and cache of device code (python/asc/runtime/jit.py:158-202, cache.py:57-112). */
+int32_t asc_cuda_register_program(int32_t kind, const int32_t* words, int32_t n_words, void* fn);
+
 /* Reduction of a row-major [rows, cols] fp32 window with row pitch `ld` (elements).  kind: 0 sum, 1 max,
  * 2 min, 3 product.  axis 1: out[r] = reduce over the columns of row r; axis 0: out[c] = reduce over the
  * rows of column c; axis -1: out[0 .. n_fill) all receive the reduction of the whole window (the window is

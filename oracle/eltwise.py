@@ -28,6 +28,7 @@ _I_SWAPPED = {56: torch.sub, 57: torch.bitwise_left_shift, 58: torch.bitwise_rig
 _ROW = {59: lambda t: t.sum(-1, keepdim=True), 60: lambda t: t.amax(-1, keepdim=True),
         61: lambda t: t.amin(-1, keepdim=True), 62: lambda t: t.prod(-1, keepdim=True)}
 IMM = 0x100
+INDEX = 65                 # the element's row-major index inside the window, as int32
 TYPES = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16, 3: torch.int32, 4: torch.int16}
 
 
@@ -54,6 +55,8 @@ def run_program(ops: Sequence[int], args: Sequence[int], inputs: List[torch.Tens
             stack.append(t.to(torch.int32) if not t.dtype.is_floating_point else t.to(torch.float32))
         elif op == CONST:
             stack.append(int(arg))            # untyped 32-bit word
+        elif op == INDEX:
+            stack.append(torch.arange(inputs[0].numel(), dtype=torch.int32).reshape(shape))
         elif op in _F_BINARY:
             b, a = as_float(stack.pop()), as_float(stack.pop())
             stack.append(_F_BINARY[op](a, b))

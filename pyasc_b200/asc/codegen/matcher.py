@@ -54,6 +54,7 @@ class Step:
         self.fn_name = fn_name
         self.build = build
         self.note = note
+        self.program = None      # (kind, opcode-list words) of an elementwise / row program step, see pyasc_b200/jit.py
 
     def __repr__(self) -> str:
         return f"Step({self.fn_name}: {self.note})"
@@ -95,8 +96,21 @@ def _p(addr: int) -> ctypes.c_void_p:
 # --------------------------------------------------------------------------------------------------
 # Enumerating (block, iteration) instances of a loop nest
 # --------------------------------------------------------------------------------------------------
-def enumerate_instances(core_num: int, loops: Tuple[Loop, ...]) -> Dict[str, np.ndarray]:
-    """Symbol bindings, one array entry per (block, iteration...) combination of ``loops``."""
+def enumerate_instances(core_num: int, loops: Tuple[Loop, ...], guards: Tuple = ()) -> Dict[str, np.ndarray]:
+    """Symbol bindings, one array entry per (block, iteration...) combination of ``loops`` for which every guard
+    (an ``if`` condition on the block index or a loop variable, with the outcome the effect lies under) holds."""
+    if guards:
+        env = enumerate_instances(core_num, loops)
+        n = env_count(env)
+        keep = np.ones(n, dtype=bool)
+        for cond, outcome in guards:
+            try:
+                value = np.broadcast_to(np.asarray(cond.evaluate(env)), (n, )) != 0
+            except Exception as e:
+                raise _unsupported("'if' on a scalar that is not a function of the block index, loop variables and "
+                                   f"launch arguments ({e})") from None
+            keep &= value if outcome else ~value
+        return {name: arr[keep] for name, arr in env.items()}
     env: Dict[str, np.ndarray] = {"block_idx": np.arange(core_num, dtype=np.int64)}
     count = core_num
     for loop in loops:
@@ -290,7 +304,7 @@ def _match_elementwise(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     numel = 1
     for d in out_t.static_shape():
         numel *= d
-    env = enumerate_instances(trace.core_num, eff.loops)
+    env = enumerate_instances(trace.core_num, eff.loops, eff.guards)
     n = env_count(env)
     starts = eval_int(flat_off, env, n)
     if starts.size and starts.min() < 0:
@@ -340,6 +354,7 @@ ROW_MAX_COLS = 8192
 ROW_MAX_TMP = 4
 _ROW_SCALAR_INPUT = 0x200    # flag on an input type: one element per row (address = row * pitch)
 _OP_TEE, _OP_TMP = 63, 64     # row programs: copy the top into / push temporary slot arg
+_OP_INDEX = 65                # push the element's row-major index inside the call's window (int32)
 _MARK_BEGIN, _MARK_END = -1, -2   # pseudo-ops around the code of one traced value (arg: its identity)
 
 
@@ -408,6 +423,7 @@ class _EltProgram:
         self.operands: List[_Operand] = []
         self.reshaped = False       # a reshape was seen: element order is the flat (row-major) order
         self.row_ops = False        # the program reduces over rows: it runs as a row program
+        self.uses_index = False     # the program reads the element index inside the tile: one call per tile
         self.n_tmp = 0              # temporary slots the finished program uses
         self.visits = 0             # values visited while generating code
         self.full_shape: Optional[Tuple[int, ...]] = None   # set while code for a per-row value is generated
@@ -512,6 +528,11 @@ class _EltProgram:
             return self._row_reduction(node, v.dtype)
         if v.shape != self.shape:
             return None
+        if node.kind == "iota":
+            if self.full_shape is not None:
+                return None
+            self.uses_index = True
+            return _Frag([(_OP_INDEX, 0)], 1)
         if node.kind in ("load", "copy"):
             if self.full_shape is not None:
                 # a loaded column: one element per row of the result; only a row program can address it
@@ -745,6 +766,16 @@ def _program_arrays(prog: "_EltProgram", out_t: Tensor):
                                               for o in prog.operands]), _ELT_TYPE[out_t.dtype.name])
 
 
+def _program_key(prog: "_EltProgram", row_cols: Optional[int] = None):
+    """``(kind, words)`` under which the kernel specialised for this program is built and registered
+    (pyasc_b200/jit.py): the launcher asks for it before it runs a step that carries one."""
+    from pyasc_b200 import jit
+    if not prog.operands:
+        return None
+    words = jit.program_words(prog.ops, prog.args, [o.per_row for o in prog.operands])
+    return (jit.row_kind(row_cols) if row_cols is not None else 0, words)
+
+
 def _check_program_limits(prog: "_EltProgram") -> None:
     if len(prog.ops) > ELT_MAX_OPS or len(prog.operands) > ELT_MAX_INPUTS or prog.max_depth > ELT_MAX_STACK:
         raise _unsupported(f"elementwise expression with {len(prog.ops)} operations, {len(prog.operands)} inputs and a "
@@ -757,7 +788,7 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
                           row_shape: Optional[Tuple[int, int]] = None, row_result: bool = False) -> Plan:
     """Operands addressed differently from the result (other tensor shapes or offsets, reshapes, a broadcast row,
     an accumulation into a fixed window): one call per (block, iteration) instance, in program order."""
-    env = enumerate_instances(trace.core_num, eff.loops)
+    env = enumerate_instances(trace.core_num, eff.loops, eff.guards)
     n = env_count(env)
     if n > MAX_CALLS:
         raise _unsupported("elementwise kernel with differently addressed operands and more than 4096 tiles")
@@ -822,6 +853,7 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
     lds_arr = (ctypes.c_int64 * len(lds))(*lds)
     fn_name = "asc_cuda_row_program" if row_shape is not None else "asc_cuda_eltwise_program_2d"
     tail_args = (ctypes.c_int32(1 if row_result else 0), ) if row_shape is not None else ()
+    program_key = _program_key(prog, cols if row_shape is not None else None)
     calls: List[Tuple[Tuple[int, ...], int]] = []      # (first element of every operand and of the result, rows)
     all_starts = [tuple(int(g.start[j]) for g in geoms) + (int(out_g.start[j]), ) for j in range(n)]
     if dedupe and len(set(all_starts)) > 1:
@@ -840,7 +872,7 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
         # stores are idempotent and independent: drop repeats, and let windows that continue each other row
         # after row (every operand advancing by its own pitch, a broadcast row staying put) become one call
         for starts in sorted(set(all_starts), key=lambda st: st[-1]):
-            if calls and cols > 0:
+            if calls and cols > 0 and not prog.uses_index:      # (an element index restarts with every tile)
                 prev, prev_rows = calls[-1]
                 if all(st == p0 + prev_rows * ld for st, p0, ld in zip(starts, prev, lds)):
                     calls[-1] = (prev, prev_rows + rows)
@@ -854,8 +886,10 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
             return (ops_arr, args_arr, ctypes.c_int32(n_ops), ins, types_arr, ctypes.c_int32(n_in),
                     _p(ptrs[out_idx] + out_size * starts[-1]), ctypes.c_int32(out_type), ctypes.c_int64(call_rows),
                     ctypes.c_int64(cols), lds_arr) + tail_args + (stream, )
-        return Step(fn_name, build,
+        step = Step(fn_name, build,
                     f"{n_ops} ops over [{call_rows}, {cols}] pitches {lds} from {list(starts[:-1])} to {starts[-1]}")
+        step.program = program_key
+        return step
 
     for starts, call_rows in calls:
         plan.steps.append(make_step(starts, call_rows))
@@ -899,7 +933,8 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         aligned = all(o.scalar and o.tensor.static_shape() == tshape and _same_offsets(o.offsets, offsets)
                       for o in prog.operands)
     else:
-        aligned = not prog.reshaped and all(o.addressed_like(out_t, offsets, out_shape) for o in prog.operands)
+        aligned = not prog.reshaped and not prog.uses_index and \
+            all(o.addressed_like(out_t, offsets, out_shape) for o in prog.operands)
     if prog.row_ops:
         rows = 1
         for d in out_shape[:-1]:
@@ -911,7 +946,7 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     numel = 1
     for d in tshape:
         numel *= d
-    env = enumerate_instances(trace.core_num, eff.loops)
+    env = enumerate_instances(trace.core_num, eff.loops, eff.guards)
     n = env_count(env)
     windows: List[Tuple[int, int, int, int]] = []     # 2-D mode: (row0, col0, rows, cols)
     if scalar_store:
@@ -946,6 +981,7 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     if intervals != [(0, out_t.base.numel)]:
         plan.partial_writes.add(out_idx)
     n_ops, n_in, ops_arr, args_arr, types_arr, out_type = _program_arrays(prog, out_t)
+    program_key = _program_key(prog)
 
     def make(lo: int, hi: int) -> List[Step]:
         def build(ptrs, stream, lo=lo, hi=hi):
@@ -953,7 +989,9 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
             ins = (ctypes.c_void_p * n_in)(*[ptrs[i] + sz * lo for i, sz in zip(in_idx, in_size)])
             return (ops_arr, args_arr, ctypes.c_int32(n_ops), ins, types_arr, ctypes.c_int32(n_in),
                     _p(ptrs[out_idx] + out_size * lo), ctypes.c_int32(out_type), ctypes.c_int64(hi - lo), stream)
-        return [Step("asc_cuda_eltwise_program", build, f"{n_ops} ops over [{lo}, {hi})")]
+        step = Step("asc_cuda_eltwise_program", build, f"{n_ops} ops over [{lo}, {hi})")
+        step.program = program_key
+        return [step]
 
     lds_arr = (ctypes.c_int64 * (n_in + 1))(*([tshape[-1]] * (n_in + 1)))
 
@@ -965,7 +1003,9 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
             return (ops_arr, args_arr, ctypes.c_int32(n_ops), ins, types_arr, ctypes.c_int32(n_in),
                     _p(ptrs[out_idx] + out_size * first), ctypes.c_int32(out_type), ctypes.c_int64(rows),
                     ctypes.c_int64(cols), lds_arr, stream)
-        return Step("asc_cuda_eltwise_program_2d", build, f"{n_ops} ops over [{rows}, {cols}] at ({r0}, {c0})")
+        step = Step("asc_cuda_eltwise_program_2d", build, f"{n_ops} ops over [{rows}, {cols}] at ({r0}, {c0})")
+        step.program = program_key
+        return step
 
     for lo, hi in intervals:
         plan.steps += make(lo, hi)
@@ -1167,7 +1207,7 @@ def _match_reduce(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         raise _unsupported("reduction whose result is not stored as one contiguous range")
     out_off_expr, out_elems = window
     assert out_elems == n_out
-    env = enumerate_instances(trace.core_num, eff.loops)
+    env = enumerate_instances(trace.core_num, eff.loops, eff.guards)
     n = env_count(env)
     zero = PlainValue.const(0)
     x_offs = view.offsets if len(view.offsets) == 2 else (zero, view.offsets[0])
@@ -1286,7 +1326,7 @@ def _match_softmax(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         row_off, col_off = PlainValue.const(0), view.offsets[0]
     else:
         row_off, col_off = view.offsets
-    env = enumerate_instances(trace.core_num, eff.loops)
+    env = enumerate_instances(trace.core_num, eff.loops, eff.guards)
     n = env_count(env)
     r0 = eval_int(row_off, env, n)
     c0 = eval_int(col_off, env, n)
@@ -1362,7 +1402,7 @@ def _match_rms_norm(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     if tile_cols != C:
         # the mean runs over the tile's row; a window of a wider row would need a second pitch
         raise _unsupported("rms_norm of tiles narrower or wider than the tensor row")
-    env = enumerate_instances(trace.core_num, eff.loops)
+    env = enumerate_instances(trace.core_num, eff.loops, eff.guards)
     n = env_count(env)
     row_off = PlainValue.const(0) if len(value.shape) == 1 else view.offsets[0]
     col_off = view.offsets[-1]
@@ -1575,7 +1615,7 @@ def _merge_k_loop(a: _Window, b: _Window, red: Tuple[Loop, ...]) -> Tuple[_Windo
 
 
 def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offsets: Sequence[PlainValue],
-                       loops: Tuple[Loop, ...], plan: Plan) -> bool:
+                       loops: Tuple[Loop, ...], plan: Plan, guards: Tuple = ()) -> bool:
     """Append the steps computing ``value`` (a matmul with epilogue) into ``out_t`` at ``out_offsets``.
     Returns False when ``value`` is not a matmul expression."""
     if not isinstance(value, Tile) or len(value.shape) != 2:
@@ -1605,7 +1645,7 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
     b_rows, b_cols = b_w.tensor.static_shape()
     c_rows, c_cols = out_t.static_shape()
 
-    env = enumerate_instances(trace.core_num, loops)
+    env = enumerate_instances(trace.core_num, loops, guards)
     n = env_count(env)
     ro, co = eval_int(out_offsets[0], env, n), eval_int(out_offsets[1], env, n)
     ar, ak = eval_int(a_w.row, env, n), eval_int(a_w.col, env, n)
@@ -1731,7 +1771,7 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
 def _match_matmul(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     value, out_t = eff.args
     plan = Plan("matmul")
-    if not _plan_matmul_value(trace, value, out_t, eff.attrs["offsets"], eff.loops, plan):
+    if not _plan_matmul_value(trace, value, out_t, eff.attrs["offsets"], eff.loops, plan, eff.guards):
         return None
     return plan
 
@@ -1792,7 +1832,7 @@ def _match_attention(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         raise _unsupported("attention Q, K, V, O must have the same [rows, head_dim] shape")
     if qv.shape[1] != D or kv.shape != (S, D) or vv.shape != (S, D) or rows % S != 0 or S % tq != 0:
         raise _unsupported("attention tiles must span the head dimension, K/V tiles one whole sequence")
-    env = enumerate_instances(trace.core_num, eff.loops)
+    env = enumerate_instances(trace.core_num, eff.loops, eff.guards)
     n = env_count(env)
     row0 = eval_int(eff.attrs["offsets"][0], env, n)
     checks = [
@@ -1866,7 +1906,7 @@ def _store_footprint(trace: KernelTrace, eff: Effect):
     offsets = eff.attrs["offsets"]
     tshape = out_t.static_shape()
     width = tshape[-1] if tshape else 1
-    env = enumerate_instances(trace.core_num, eff.loops)
+    env = enumerate_instances(trace.core_num, eff.loops, eff.guards)
     n = env_count(env)
     shape = value.shape if isinstance(value, Tile) and eff.kind != "store_scalar" else None
     if shape is None:
@@ -2007,7 +2047,7 @@ def _split_concat_store(eff: Effect) -> List[Effect]:
         attrs = dict(eff.attrs)
         attrs["offsets"] = (offsets[0] + row, ) + tuple(offsets[1:])
         kind = "store_scalar" if part.size == 1 else "store"
-        piece = Effect(kind, (part, out_t), attrs, eff.loops)
+        piece = Effect(kind, (part, out_t), attrs, eff.loops, eff.guards)
         piece.uid = eff.uid            # the parts take the place of the store in program order
         parts += _split_concat_store(piece)
         row += part.shape[0]

@@ -64,8 +64,11 @@ def _pointer_proxy(name: str, value: Any, index: int) -> Optional[GlobalAddress]
     return None
 
 
+MAX_PATHS = 64      # paths through ``if``s on run-time scalars one kernel may have
+
+
 def trace_kernel(fn: Callable, runtime_args: Dict[str, Any], constexprs: Dict[str, ConstExpr], core_num: int,
-                 custom_builtins: Optional[Dict[str, Any]] = None) -> KernelTrace:
+                 custom_builtins: Optional[Dict[str, Any]] = None, unroll_limit: int = 0) -> KernelTrace:
     call_args: Dict[str, Any] = {}
     pointers: List[GlobalAddress] = []
     for index, (name, value) in enumerate(runtime_args.items()):
@@ -86,8 +89,23 @@ def trace_kernel(fn: Callable, runtime_args: Dict[str, Any], constexprs: Dict[st
     traced_fn = types.FunctionType(fn.__code__, scope, fn.__name__, fn.__defaults__, fn.__closure__)
     traced_fn.__kwdefaults__ = fn.__kwdefaults__
 
-    with TraceContext(fn.__name__, core_num) as ctx:
-        traced_fn(**call_args)
-        if ctx.loops:
-            raise CodegenError("Unbalanced loop nest at the end of kernel tracing")
-        return KernelTrace(fn.__name__, core_num, ctx.effects, pointers)
+    # One run per path through the kernel's ``if``s on run-time scalars (depth first).  A run that was forced down
+    # its first m branches shares everything before the m-th branch with the run it was forked from, so only the
+    # effects it recorded after that branch are new.
+    effects: List[Effect] = []
+    pending: List[tuple] = [()]
+    runs = 0
+    while pending:
+        forced = pending.pop()
+        runs += 1
+        if runs > MAX_PATHS:
+            raise NotImplementedError(f"kernel '{fn.__name__}' branches on run-time scalars along more than {MAX_PATHS} paths")
+        with TraceContext(fn.__name__, core_num, forced, unroll_limit) as ctx:
+            traced_fn(**call_args)
+            if ctx.loops:
+                raise CodegenError("Unbalanced loop nest at the end of kernel tracing")
+        effects += [e for e in ctx.effects if len(e.guards) >= len(forced)]
+        outcomes = tuple(o for _, o in ctx.taken)
+        for j in range(len(ctx.taken) - 1, len(forced) - 1, -1):
+            pending.append(outcomes[:j] + (not outcomes[j], ))
+    return KernelTrace(fn.__name__, core_num, effects, pointers)

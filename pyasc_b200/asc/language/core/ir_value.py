@@ -195,7 +195,12 @@ class PlainValue:
     def __bool__(self) -> bool:
         if self.is_const:
             return bool(self.value)
-        raise NotImplementedError("Branching on a run-time scalar is not supported by the CUDA platform tracer")
+        # a condition on the block index or a loop variable: the tracer follows one outcome per run and records it
+        # (the reference emits scf.if, python/asc/codegen/function_visitor.py:585-627)
+        from ..tile import trace
+        if trace.is_tracing():
+            return trace.current().branch(self)
+        raise NotImplementedError("Branching on a run-time scalar outside a kernel")
 
     def __index__(self) -> int:
         if self.is_const and not self.dtype.is_float():

@@ -4,6 +4,8 @@ prog_model}_ops.py).  Argument checks and result shapes/dtypes follow the refere
 appends one node to the active trace."""
 from __future__ import annotations
 
+import contextlib
+
 import math
 from typing import Any, Iterable, List, Optional, Tuple, Union
 
@@ -98,7 +100,7 @@ def _binary(op: str, lhs: Any, rhs: Any) -> Tile:
     shape = infer_shape(lhs, rhs)
     a = lhs if isinstance(lhs, Tile) else _scalar(lhs)
     b = rhs if isinstance(rhs, Tile) else _scalar(rhs)
-    return Tile(shape, dtype, trace.current().node("binary", a, b, op=op))
+    return _masked(Tile(shape, dtype, trace.current().node("binary", a, b, op=op)))
 
 
 def _compare(mode: str, lhs: Any, rhs: Any) -> Tile:
@@ -185,7 +187,7 @@ def _unary(op: str, input: Any, float_only: bool = True):
         raise RuntimeError(f"'{op}' expects a tile, got {type(input).__name__}")
     if float_only and not input.dtype.is_float():
         raise RuntimeError(f"'{op}' supports floating-point tiles only, got {input.dtype}")
-    return Tile(input.shape, input.dtype, trace.current().node("unary", input, op=op), input.location)
+    return _masked(Tile(input.shape, input.dtype, trace.current().node("unary", input, op=op), input.location))
 
 
 def cos(input): return _unary("cos", input)
@@ -373,8 +375,39 @@ def where(mask: Tile, src0: Any, src1: Any) -> Tile:
     return Tile(mask.shape, dtype, trace.current().node("where", mask, a, b))
 
 
+@contextlib.contextmanager
 def mask(*, count=None, bits=None, other=None):
-    raise NotImplementedError("asc2.mask is not supported by the CUDA platform")
+    """``with asc2.mask(count=n, other=v):`` -- the unary and binary tile operations inside compute only the first
+    ``n`` elements of their tile (row-major order); the remaining elements of each result hold ``v``
+    (python/asc/language/tile/indexing_ops.py:30-63; the reference's lowering fills the destination with ``other`` and
+    runs the vector instruction under a count mask, lib/Conversion/LowerToAsc/ExpandMask.cpp:36-67).  Without
+    ``other`` the reference leaves those elements undefined; here they hold the unmasked result.  The ``bits`` form
+    (a raw 128-bit lane mask of the Ascend vector unit) has no counterpart on this platform."""
+    if count is None and bits is None:
+        raise ValueError("One of 'count', 'bits' must be provided")
+    if count is None:
+        raise NotImplementedError("asc2.mask(bits=...) addresses the lanes of the Ascend vector unit and is not "
+                                  "supported by the CUDA platform; use count=")
+    ctx = trace.current()
+    entry = (_scalar(count), None if other is None else _scalar(other))
+    ctx.masks.append(entry)
+    try:
+        yield
+    finally:
+        ctx.masks.pop()
+
+
+def _masked(result: Tile) -> Tile:
+    """Applies the innermost active ``asc2.mask`` to the result of a unary or binary operation."""
+    ctx = trace.current()
+    if not ctx.masks:
+        return result
+    count, other = ctx.masks[-1]
+    if other is None:
+        return result
+    index = Tile(result.shape, KT.int32, ctx.node("iota"), result.location)
+    active = Tile(result.shape, KT.bool_, ctx.node("compare", index, count, mode="lt"))
+    return Tile(result.shape, result.dtype, ctx.node("where", active, result, other), result.location)
 
 
 def causal_mask(scores: Tile, q_offset: Any, kv_offset: Any) -> Tile:

@@ -45,6 +45,15 @@ class range:  # noqa: A001 - mirrors the reference's name
         start, stop = PlainValue.wrap(self.start), PlainValue.wrap(self.stop)
         if start.is_const and stop.is_const and step.is_const and start.value >= stop.value:
             return  # statically empty loop: the body is never traced
+        if ctx.unroll_limit > 0 and start.is_const and stop.is_const and step.is_const:
+            import builtins
+            values = builtins.range(int(start.value), int(stop.value), int(step.value))
+            if len(values) <= ctx.unroll_limit:
+                # unrolled trace: every iteration records its own operations, so a tile carried from one iteration
+                # to the next (the reference's scf.for iteration arguments) is an ordinary value
+                for i in values:
+                    yield PlainValue.const(i)
+                return
         loop = ctx.push_loop(self.start, self.stop, self.step, self.unroll_factor, self.parallel)
         try:
             yield loop.var

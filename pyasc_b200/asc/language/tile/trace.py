@@ -60,14 +60,18 @@ class Node:
 class Effect:
     """A side effect in program order: ``store``, ``matmul_acc`` or ``atomic``."""
 
-    __slots__ = ("kind", "args", "attrs", "loops", "uid")
+    __slots__ = ("kind", "args", "attrs", "loops", "uid", "guards")
 
-    def __init__(self, kind: str, args: Tuple[Any, ...], attrs: dict, loops: Tuple[Loop, ...]):
+    def __init__(self, kind: str, args: Tuple[Any, ...], attrs: dict, loops: Tuple[Loop, ...],
+                 guards: Tuple[Tuple[PlainValue, bool], ...] = ()):
         self.kind = kind
         self.args = args
         self.attrs = attrs
         self.loops = loops
         self.uid = next(Node._ids)    # one counter with the nodes: program order of operations and effects
+        # (condition, outcome) of every ``if`` on a run-time scalar this effect lies under: it happens only for the
+        # blocks and iterations in which each condition has that outcome
+        self.guards = guards
 
     def __repr__(self) -> str:
         return f"Effect({self.kind}, {self.attrs}, loops={list(self.loops)})"
@@ -75,7 +79,7 @@ class Effect:
 
 class TraceContext:
 
-    def __init__(self, fn_name: str, core_num: int):
+    def __init__(self, fn_name: str, core_num: int, forced: Tuple[bool, ...] = (), unroll_limit: int = 0):
         self.fn_name = fn_name
         self.core_num = core_num
         self.block_idx = PlainValue.sym("block_idx")
@@ -83,6 +87,19 @@ class TraceContext:
         self.effects: List[Effect] = []
         self.tensors: List[Any] = []
         self._loop_ids = itertools.count()
+        # ``if`` on a run-time scalar: the kernel is traced once per path.  `forced` holds the outcomes this run must
+        # take at its first branches (further ones default to True); `taken` records every (condition, outcome).
+        self.forced = tuple(forced)
+        self.taken: List[Tuple[PlainValue, bool]] = []
+        # loops with compile-time bounds and at most this many iterations are unrolled while tracing (0: never)
+        self.unroll_limit = unroll_limit
+        self.masks: List[Tuple[PlainValue, Optional[PlainValue]]] = []     # active ``asc2.mask`` contexts, innermost last
+
+    # -- branches ---------------------------------------------------------------------------------
+    def branch(self, cond: PlainValue) -> bool:
+        outcome = self.forced[len(self.taken)] if len(self.taken) < len(self.forced) else True
+        self.taken.append((cond, outcome))
+        return outcome
 
     # -- loops ------------------------------------------------------------------------------------
     def push_loop(self, start, stop, step, unroll_factor: int, parallel: bool) -> Loop:
@@ -103,7 +120,7 @@ class TraceContext:
         return Node(_kind, args, attrs, self.loop_nest())
 
     def effect(self, _kind: str, /, *args, **attrs) -> None:
-        self.effects.append(Effect(_kind, args, attrs, self.loop_nest()))
+        self.effects.append(Effect(_kind, args, attrs, self.loop_nest(), tuple(self.taken)))
 
     def __enter__(self) -> "TraceContext":
         global _current

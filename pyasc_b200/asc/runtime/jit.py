@@ -36,6 +36,9 @@ class PointerArgType:
         self.dtype = dtype
 
 
+UNROLL_LIMIT = 64      # iterations up to which a compile-time loop is unrolled when a tile is carried across it
+
+
 class JITFunction(Function[P, T]):
     launcher: Type[Launcher] = Launcher
 
@@ -145,7 +148,20 @@ class JITFunction(Function[P, T]):
             return self.kernel_cache[key]
         builtins = dict(codegen_options.custom_builtins) or {"range": asc2_range}
         trace = trace_kernel(self.fn, runtime_args, constexprs, self.launch_options.core_num, builtins)
-        plan = build_plan(trace)
+        try:
+            plan = build_plan(trace)
+        except NotImplementedError as first:
+            if "carried across iterations" not in str(first):
+                raise
+            # A tile flows from one loop iteration to the next (`acc = acc + tile`; the reference compiles it as
+            # scf.for iteration arguments, python/asc/codegen/function_visitor.py:509-547).  A loop body traced once
+            # cannot express that; with the kernel's short compile-time loops unrolled it is ordinary data flow.
+            trace = trace_kernel(self.fn, runtime_args, constexprs, self.launch_options.core_num, builtins,
+                                 unroll_limit=UNROLL_LIMIT)
+            try:
+                plan = build_plan(trace)
+            except NotImplementedError:
+                raise first from None
         if enable_cache:
             self.kernel_cache[key] = plan
         return plan

@@ -95,6 +95,8 @@ class Launcher:
             raise ValueError("Core number should be large than 0")
         if os.environ.get("DRY_RUN"):
             return
+        from pyasc_b200 import jit
+        jit.prepare(plan)           # expressions met for the first time get their specialised kernel built
         handles: Dict[int, MemoryHandle] = {}
         for index, arg in enumerate(user_args):
             if self.is_scalar(arg):

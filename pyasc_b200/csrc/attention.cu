@@ -87,24 +87,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-// 2^x on the FMA pipe (round to nearest integer with the 1.5 * 2^23 trick, degree-3 polynomial on the
-// fraction in [-0.5, 0.5], exponent patched in with an integer add): relative error 1e-4, below the
-// rounding of the 16-bit P it feeds.  Used for a share of the scores so that the special-function
-// unit (16 ex2 per clock and SM) stops being the longest stage of the softmax.
-__device__ __forceinline__ float exp2_poly(float x) {
-  x = fmaxf(x, -126.f);
-  const float r = x + 12582912.f;
-  const float f = x - (r - 12582912.f);
-  float p = fmaf(0.0559220351f, f, 0.242640078f);
-  p = fmaf(p, f, 0.693121016f);
-  p = fmaf(p, f, 0.999924481f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
-}
-
-#ifndef ASC_ATTN_POLY_MASK
-#define ASC_ATTN_POLY_MASK 0x00   // bit i set: of every 8 consecutive scores, element i takes the polynomial
-#endif
-
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -212,8 +194,8 @@ __device__ __forceinline__ bool softmax_role(const AttnParams& p, AttnCtl& ctl, 
         // (measured +2-5 % over scalar FFMA / FADD: the softmax warps are issue-bound)
         const float2 x = __ffma2_rn(make_float2(__uint_as_float(s[c][2 * i]), __uint_as_float(s[c][2 * i + 1])),
                                     make_float2(sl2, sl2), make_float2(neg_m, neg_m));
-        const float e0 = ((ASC_ATTN_POLY_MASK >> ((2 * i) & 7)) & 1) ? exp2_poly(x.x) : ex2_approx(x.x);
-        const float e1 = ((ASC_ATTN_POLY_MASK >> ((2 * i + 1) & 7)) & 1) ? exp2_poly(x.y) : ex2_approx(x.y);
+        const float e0 = ex2_approx(x.x);
+        const float e1 = ex2_approx(x.y);
         if (i & 1) {
           const float2 t2 = __fadd2_rn(make_float2(l2, l3), make_float2(e0, e1));
           l2 = t2.x;

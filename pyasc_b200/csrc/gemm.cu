@@ -64,7 +64,7 @@ struct GemmParams {
   // split-K kernel only: every 128 x 256 tile is computed by `split_k` CTAs, each over its own range of K
   int32_t split_k;
   uint32_t* arrivals;   // one counter per tile, zero at launch: slices whose partial tile is in the workspace
-  uint32_t* partials;   // [tiles][split_k][128][256] 32-bit accumulator words
+  uint32_t* partials;   // [tiles][split_k] partial tiles of 128 x 256 32-bit accumulator words
 };
 
 struct SharedCtl {
@@ -666,6 +666,97 @@ __device__ __forceinline__ void splitk_store_pair(const GemmParams& p, int64_t r
   }
 }
 
+// Four neighbouring columns of one output row: one 8- or 16-byte store where the output allows it.
+template <int kMode>
+__device__ __forceinline__ void splitk_store_quad(const GemmParams& p, int64_t row, int64_t col, const uint4& v) {
+  if (row >= p.M || col >= p.N) return;
+  if (p.vec_ok && col + 4 <= p.N) {
+    if (kMode == EPI_F16 || kMode == EPI_BF16) {
+      float f[4] = {__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w)};
+      if (p.relu) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) f[i] = fmaxf(f[i], 0.f);
+      }
+      uint2 w;
+      if (kMode == EPI_F16) {
+        const __half2 a = __floats2half2_rn(f[0], f[1]), b = __floats2half2_rn(f[2], f[3]);
+        w = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+      } else {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+        w = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+      }
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.c) + row * p.ldc + col) = w;
+      return;
+    }
+    if (kMode == EPI_F32 && !p.accumulate) {
+      float4 f = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+      if (p.relu) f = make_float4(fmaxf(f.x, 0.f), fmaxf(f.y, 0.f), fmaxf(f.z, 0.f), fmaxf(f.w, 0.f));
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.c) + row * p.ldc + col) = f;
+      return;
+    }
+    if (kMode == EPI_I8 && p.deq == nullptr) {
+      *reinterpret_cast<uint4*>(reinterpret_cast<int32_t*>(p.c) + row * p.ldc + col) = v;
+      return;
+    }
+  }
+  splitk_store_pair<kMode>(p, row, col, v.x, v.y);
+  splitk_store_pair<kMode>(p, row, col + 2, v.z, v.w);
+}
+
+// Sums rows [r_lo, r_lo + n_rows) of one tile over all slices and stores them.  The words of one item are added in
+// slice order 0, 1, 2, ... whatever kItems is, so the result does not depend on the load schedule.
+template <int kMode, int kItems>
+__device__ __forceinline__ void splitk_reduce_band(const GemmParams& p, const uint32_t* first, uint32_t e, int r_lo,
+                                                   int n_rows, int64_t m_blk, int64_t n_blk) {
+  constexpr int kBatch = 16 / kItems;
+  const int total = n_rows * (kBlockN / 4);
+  for (int item0 = static_cast<int>(e); item0 < total; item0 += 128 * kItems) {
+    const uint4* src[kItems];
+    uint4 v[kItems];
+#pragma unroll
+    for (int j = 0; j < kItems; ++j) {
+      const int item = item0 + j * 128 < total ? item0 + j * 128 : item0;     // past the end: repeat a valid item
+      src[j] = reinterpret_cast<const uint4*>(first) + (item / n_rows) * kBlockM + r_lo + item % n_rows;
+      v[j] = __ldcg(src[j]);
+    }
+    for (int s0 = 1; s0 < p.split_k; s0 += kBatch) {
+      uint4 w[kItems][kBatch];
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i)
+#pragma unroll
+        for (int j = 0; j < kItems; ++j)
+          if (s0 + i < p.split_k) w[j][i] = __ldcg(src[j] + static_cast<int64_t>(s0 + i) * (kTileWords / 4));
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) {
+        if (s0 + i < p.split_k) {
+#pragma unroll
+          for (int j = 0; j < kItems; ++j) {
+            if (kMode == EPI_I8) {
+              v[j].x += w[j][i].x;
+              v[j].y += w[j][i].y;
+              v[j].z += w[j][i].z;
+              v[j].w += w[j][i].w;
+            } else {
+              v[j].x = __float_as_uint(__fadd_rn(__uint_as_float(v[j].x), __uint_as_float(w[j][i].x)));
+              v[j].y = __float_as_uint(__fadd_rn(__uint_as_float(v[j].y), __uint_as_float(w[j][i].y)));
+              v[j].z = __float_as_uint(__fadd_rn(__uint_as_float(v[j].z), __uint_as_float(w[j][i].z)));
+              v[j].w = __float_as_uint(__fadd_rn(__uint_as_float(v[j].w), __uint_as_float(w[j][i].w)));
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kItems; ++j) {
+      const int item = item0 + j * 128;
+      if (item < total) {
+        const int64_t row = m_blk * kBlockM + r_lo + item % n_rows, c0 = n_blk * kBlockN + (item / n_rows) * 4;
+        splitk_store_quad<kMode>(p, row, c0, v[j]);
+      }
+    }
+  }
+}
+
 template <int kElemBytes, int kMode>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -777,21 +868,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       ok = mbar_wait_warp<kWaitHintNs>(smem_u32(&ctl.tmem_full[0]), 0, abort_flag, p.status, ASC_DEV_TIMEOUT_TMEM_FULL);
       if (ok) {
         tc_fence_after();
+        // Layout of a partial tile: groups of four columns, and inside a group the 128 rows side by side, 16 bytes
+        // each.  A thread owns a row, so a warp's store of one column group is 512 contiguous bytes.
         const uint32_t taddr = tmem_base + ((quarter * 32u) << 16);
-        uint4* dst = reinterpret_cast<uint4*>(mine + (quarter * 32u + lane) * kBlockN);
+        uint4* dst = reinterpret_cast<uint4*>(mine) + (quarter * 32u + lane);
 #pragma unroll 1
         for (int c = 0; c < kBlockN / 32; ++c) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(taddr + c * 32, r);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 8; ++i) dst[c * 8 + i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+          for (int i = 0; i < 8; ++i)
+            dst[(c * 8 + i) * kBlockM] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
         }
         tc_fence_before();
       }
     } else {
       // a slice without K blocks (more slices than blocks never happens by construction, kept for safety)
-      for (uint32_t i = e; i < kTileWords; i += 128) mine[i] = 0u;
+      for (uint32_t i = e; i < kTileWords; i += 128) mine[i] = 0u;     // (all zero in any layout)
     }
     __threadfence();
     named_bar_sync(1, 128);
@@ -816,20 +910,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
       const int r_lo = static_cast<int>(slice) * rows_each;
       const int r_hi = r_lo + rows_each < kBlockM ? r_lo + rows_each : kBlockM;
       const uint32_t* first = p.partials + tile * p.split_k * static_cast<int64_t>(kTileWords);
-      for (int r = r_lo; r < r_hi; ++r) {
-        const uint2* src = reinterpret_cast<const uint2*>(first + r * kBlockN) + e;
-        uint2 v = __ldcg(src);
-        for (int s2 = 1; s2 < p.split_k; ++s2) {
-          const uint2 w = __ldcg(src + s2 * (kTileWords / 2));
-          if (kMode == EPI_I8) {
-            v.x += w.x;
-            v.y += w.y;
-          } else {
-            v.x = __float_as_uint(__fadd_rn(__uint_as_float(v.x), __uint_as_float(w.x)));
-            v.y = __float_as_uint(__fadd_rn(__uint_as_float(v.y), __uint_as_float(w.y)));
-          }
-        }
-        splitk_store_pair<kMode>(p, m_blk * kBlockM + r, n_blk * kBlockN + 2 * e, v.x, v.y);
+      // An item is four columns of one row; consecutive threads take consecutive rows of a column group, whose
+      // words lie side by side in every partial tile.  Sixteen loads are in flight per thread: with few slices a
+      // thread works on several items at once, with many it fetches one item's slices sixteen at a time.
+      const int n_rows = r_hi - r_lo;
+      if (p.split_k <= 2) {
+        splitk_reduce_band<kMode, 8>(p, first, e, r_lo, n_rows, m_blk, n_blk);
+      } else if (p.split_k <= 4) {
+        splitk_reduce_band<kMode, 4>(p, first, e, r_lo, n_rows, m_blk, n_blk);
+      } else if (p.split_k <= 8) {
+        splitk_reduce_band<kMode, 2>(p, first, e, r_lo, n_rows, m_blk, n_blk);
+      } else {
+        splitk_reduce_band<kMode, 1>(p, first, e, r_lo, n_rows, m_blk, n_blk);
       }
     }
   }
@@ -1038,15 +1130,27 @@ constexpr size_t kSplitHeaderBytes = 1024;
 constexpr int kSplitMaxTiles = static_cast<int>(kSplitHeaderBytes / sizeof(uint32_t));
 constexpr size_t kPartialTileBytes = static_cast<size_t>(kTileWords) * sizeof(uint32_t);
 
-// How many slices of K each 128 x 256 tile is cut into when `ctas` CTAs may run at once: as many as fill the GPU,
-// but at least four K blocks per slice (below that the pipeline fill and the reduction cost more than the
-// parallelism returns) and at most one slice per row band of 2 rows.  1 means: do not split.
+// How many slices of K each 128 x 256 tile is cut into when `ctas` CTAs may run at once (at least four K blocks per
+// slice, at most 64 slices).  1 means: do not split.
 inline int split_k_slices(int64_t tiles, int64_t num_kb, int64_t ctas) {
-  if (tiles <= 0 || tiles > kSplitMaxTiles || tiles * 2 > ctas) return 1;
-  int64_t s = ctas / tiles;
-  if (s > num_kb / 4) s = num_kb / 4;
-  if (s > 64) s = 64;
-  return s < 2 ? 1 : static_cast<int>(s);
+  if (tiles <= 0 || tiles > kSplitMaxTiles || tiles * 2 > ctas || num_kb < 16) return 1;
+  // Measured on B200: a K block of the main loop costs about 0.29 us per CTA; publishing the partial tiles, waiting
+  // for the other slices and summing them costs about 11 us + 0.1 us per CTA of the grid.  Take the number of
+  // slices with the shortest predicted time, and split at all only for a gain of a fifth or more.
+  const double whole = 0.29 * static_cast<double>(num_kb);
+  double best = whole / 1.2;
+  int best_s = 1;
+  int64_t s_max = ctas / tiles;
+  if (s_max > num_kb / 4) s_max = num_kb / 4;
+  if (s_max > 64) s_max = 64;
+  for (int64_t s = 2; s <= s_max; ++s) {
+    const double t = 0.29 * static_cast<double>((num_kb + s - 1) / s) + 11.0 + 0.1 * static_cast<double>(tiles * s);
+    if (t < best) {
+      best = t;
+      best_s = static_cast<int>(s);
+    }
+  }
+  return best_s;
 }
 
 // Launches the split-K kernel.  `workspace` (kSplitHeaderBytes + tiles * split * 128 KiB, 256-byte aligned) is the

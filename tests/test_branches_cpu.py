@@ -1,0 +1,77 @@
+"""``if`` on a run-time scalar (the block index, a loop variable) on CPU: the kernel is traced once per path and
+every effect happens only for the blocks and iterations its conditions select (the reference emits ``scf.if``,
+python/asc/codegen/function_visitor.py:585-627).  ``DRY_RUN=1`` stops before the device launch."""
+import pytest
+import torch
+
+import asc
+import asc2
+
+N = 64
+
+
+@pytest.fixture(autouse=True)
+def dry_run(monkeypatch):
+    monkeypatch.setenv("DRY_RUN", "1")
+
+
+@asc2.jit
+def even_odd(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int], tiles: int):
+    x_gm, out_gm = asc2.tensor(x_ptr, [tiles * n]), asc2.tensor(out_ptr, [tiles * n])
+    for t in range(asc2.block_idx(), tiles, asc2.block_num()):
+        x = asc2.load(x_gm, [n], offsets=[t * n])
+        if t % 2 == 0:
+            asc2.store(x * 2, out_gm, offsets=[t * n])
+        else:
+            asc2.store(x + 1, out_gm, offsets=[t * n])
+
+
+def test_branch_on_a_loop_variable_splits_the_iterations():
+    x = torch.zeros(8 * N)
+    even_odd[3](x, torch.zeros_like(x), N, 8)
+    plan = even_odd.last_plan
+    assert plan.pattern == "elementwise:program+elementwise:program"
+    notes = [s.note for s in plan.steps]
+    assert notes[:4] == [f"2 ops over [{t * N}, {(t + 1) * N})" for t in (0, 2, 4, 6)]       # the `then` arm: even tiles
+    assert notes[4:] == [f"2 ops over [{t * N}, {(t + 1) * N})" for t in (1, 3, 5, 7)]       # the `else` arm: odd tiles
+    assert plan.writes == {1} and plan.partial_writes == {1}
+
+
+@asc2.jit
+def first_blocks_only(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int], active: int):
+    x_gm, out_gm = asc2.tensor(x_ptr, [8 * n]), asc2.tensor(out_ptr, [8 * n])
+    b = asc2.block_idx()
+    x = asc2.load(x_gm, [n], offsets=[b * n])
+    if b < active:
+        if b == 0:
+            asc2.store(x - 1, out_gm, offsets=[0])
+        else:
+            asc2.store(asc2.exp(x), out_gm, offsets=[b * n])
+    asc2.store(x, out_gm, offsets=[(b + 4) * n])          # after the join: every block
+
+
+def test_nested_branches_on_the_block_index():
+    x = torch.zeros(8 * N)
+    first_blocks_only[4](x, torch.zeros_like(x), N, 3)
+    notes = sorted(s.note for s in first_blocks_only.last_plan.steps)
+    assert notes == sorted([
+        f"2 ops over [1, {N}] pitches [{N}, {N}] from [0] to 0",             # block 0: x - 1 (stored at a fixed place)
+        f"2 ops over [{N}, {3 * N})",                                         # blocks 1 and 2: exp(x), merged
+        # the copy after the join is recorded on all three paths: block 0, blocks 1-2 (merged), block 3
+        f"1 ops over [1, {N}] pitches [{N}, {N}] from [0] to {4 * N}",
+        f"1 ops over [2, {N}] pitches [{N}, {N}] from [{N}] to {5 * N}",
+        f"1 ops over [1, {N}] pitches [{N}, {N}] from [{3 * N}] to {7 * N}",
+    ])
+
+
+@asc2.jit
+def branch_on_data(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+    x_gm, out_gm = asc2.tensor(x_ptr, [n]), asc2.tensor(out_ptr, [n])
+    x = asc2.load(x_gm, [n], offsets=[0])
+    if asc2.reduce_max(x) > 0:
+        asc2.store(x, out_gm, offsets=[0])
+
+
+def test_branch_on_tile_data_is_refused():
+    with pytest.raises(NotImplementedError, match="not a function of the block index"):
+        branch_on_data[1](torch.zeros(N), torch.zeros(N), N)

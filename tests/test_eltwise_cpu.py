@@ -210,9 +210,10 @@ def test_expression_graph_that_explodes_as_a_tree_is_refused_quickly():
         doubling[1](torch.zeros(64), torch.zeros(64), 64)
 
 
-def test_tile_carried_across_loop_iterations_is_refused():
-    """A loop body is traced once, so a tile that one iteration hands to the next cannot be represented: the
-    launcher must say so instead of computing a single iteration."""
+def test_tile_carried_across_loop_iterations_unrolls_the_loop():
+    """A loop body is traced once, so a tile that one iteration hands to the next cannot be represented by that
+    trace: the launcher traces again with the short compile-time loop unrolled and plans the data flow; a loop too
+    long to unroll is refused instead of computing a single iteration."""
     @asc2.jit
     def running_sum(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int], reps: int):
         x_gm = asc2.tensor(x_ptr, [reps * n])
@@ -220,8 +221,12 @@ def test_tile_carried_across_loop_iterations_is_refused():
         for i in range(reps):
             acc = acc + asc2.load(x_gm, [n], offsets=[i * n])
         asc2.store(acc, asc2.tensor(out_ptr, [n]), offsets=[0])
+    running_sum[1](torch.zeros(256), torch.zeros(64), 64, 4)
+    (step, ) = running_sum.last_plan.steps
+    # 0 + x0 + x1 + x2 + x3: four loads from four places, four additions (the first with the constant 0)
+    assert step.note == "8 ops over [1, 64] pitches [64, 64, 64, 64, 64] from [0, 64, 128, 192] to 0"
     with pytest.raises(NotImplementedError, match="carried across iterations"):
-        running_sum[1](torch.zeros(256), torch.zeros(64), 64, 4)
+        running_sum[1](torch.zeros(6464), torch.zeros(64), 64, 101)
 
 
 def test_tile_loaded_before_an_overwrite_of_its_tensor_is_refused():
@@ -265,3 +270,31 @@ def test_reading_back_another_blocks_output_is_refused():
         asc2.store(asc2.load(x_gm, [n], offsets=[i]) + 1, y_gm, offsets=[i])      # each block reads what it wrote
     own[4](torch.zeros(256), torch.zeros(256), torch.zeros(256), 64, 256)
     assert len(own.last_plan.steps) == 2
+
+
+def test_count_mask_plans_one_call_per_tile_with_the_element_index(monkeypatch):
+    """``with asc2.mask(count=n, other=v)``: the operations inside keep their first n elements and hold v in the
+    rest, so the program compares the element index inside the tile with n; tiles are then planned one call each
+    (the index restarts with every tile) instead of being merged into one flat range."""
+    monkeypatch.setenv("DRY_RUN", "1")
+
+    @asc2.jit
+    def masked_scale(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int], count: int):
+        x_gm, out_gm = asc2.tensor(x_ptr, [4 * n]), asc2.tensor(out_ptr, [4 * n])
+        for t in range(asc2.block_idx(), 4, asc2.block_num()):
+            x = asc2.load(x_gm, [n], offsets=[t * n])
+            with asc2.mask(count=count, other=-1.0):
+                y = x * 2
+            asc2.store(y, out_gm, offsets=[t * n])
+    masked_scale[2](torch.zeros(256), torch.zeros(256), 64, 10)
+    plan = masked_scale.last_plan
+    assert [s.note.split(" from ")[1] for s in plan.steps] == [f"[{t * 64}] to {t * 64}" for t in range(4)]
+    ops = list(plan.steps[0].build({0: 0, 1: 0}, None)[0][:plan.steps[0].build({0: 0, 1: 0}, None)[2].value])
+    assert 65 in ops and 32 in ops                           # INDEX ... WHERE
+    with pytest.raises(NotImplementedError, match="bits"):
+        @asc2.jit
+        def bit_mask(x_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+            x = asc2.load(asc2.tensor(x_ptr, [n]), [n], offsets=[0])
+            with asc2.mask(bits=(0, 255)):
+                asc2.store(x + 1, asc2.tensor(x_ptr, [n]), offsets=[0])
+        bit_mask[1](torch.zeros(64), 64)

@@ -357,3 +357,42 @@ def test_random_programs_bit_exact_in_every_executor_width(lib, seed):
             assert got[n] == 0
     finally:
         lib.asc_cuda_eltwise_set_lanes(0)
+
+
+# ------------------------------------------------------------------------------- kernels specialised at first use
+def _interpreted(lib, fn):
+    assert lib.asc_cuda_eltwise_set_lanes(0x100) == 0       # every program through the interpreter
+    try:
+        return fn()
+    finally:
+        assert lib.asc_cuda_eltwise_set_lanes(0) == 0
+
+
+@pytest.mark.parametrize("name, dtype, out_type, ops, args", [
+    ("mish", torch.float32, 0, [0, 0, 11, 2 | IMM, 13, 22, 4], [0, 0, 0, fbits(1.0), 0, 0, 0]),
+    ("two_inputs", torch.float32, 0, [0, 0, 3, 9, 0, 0, 4, 2, 15, 0, 5], [0, 1, 0, 0, 0, 1, 0, 0, 0, 1, 0]),
+    ("half_chain", torch.float16, 1, [0, 0, 4, 33, 0, 2, 33, 10, 33], [0, 1, 0, 0, 0, 0, 0, 0, 0]),
+    ("bf16_where", torch.bfloat16, 2, [0, 29 | IMM, 0, 0, 4 | IMM, 34, 0, 2, 34, 32], [0, fbits(0.5), 0, 1, fbits(3.0), 0, 0, 0, 0, 0]),
+], ids=lambda v: v if isinstance(v, str) else "")
+@pytest.mark.parametrize("n", [4099, (1 << 22) + 5])
+def test_programs_built_at_first_use_equal_the_interpreter(lib, name, dtype, out_type, ops, args, n):
+    """An expression without a built-in specialised kernel gets one built with nvcc at first use; its results are
+    bit-identical to the interpreter's (and the cached library is found again by the second size)."""
+    from pyasc_b200 import jit
+    if jit.compiler() is None:
+        pytest.skip("no nvcc on this machine")
+    gen = torch.Generator().manual_seed(n)
+    x = (torch.rand(n, generator=gen) * 4 + 0.25).to(dtype).cuda()
+    y = (torch.rand(n, generator=gen) * 4 - 2).to(dtype).cuda()
+    ins = [x, y][:max(args[k] for k in range(len(ops)) if ops[k] & 0xff == 0) + 1]
+    plain = torch.zeros(n, dtype=dtype, device="cuda")
+    _interpreted(lib, lambda: call(lib, ops, args, ins, plain, out_type, n))
+    assert jit.request(0, jit.program_words(ops, args), wait=True), jit.failures()
+    before = capi.launch_count()
+    fast = torch.zeros(n, dtype=dtype, device="cuda")
+    call(lib, ops, args, ins, fast, out_type, n)
+    assert capi.launch_count() == before + 1
+    assert torch.equal(fast.view(torch.int16 if dtype != torch.float32 else torch.int32),
+                       plain.view(torch.int16 if dtype != torch.float32 else torch.int32))
+    want = E.run_program(ops, args, [t.cpu() for t in ins], out_type)
+    torch.testing.assert_close(fast.cpu().float(), want.float(), rtol=2e-3, atol=1e-5, equal_nan=True)

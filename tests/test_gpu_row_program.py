@@ -268,3 +268,36 @@ def test_random_row_programs_bit_exact(lib, seed):
     out = torch.zeros(rows, cols, device="cuda")
     run_row_program(lib, ops, args, [t.cuda() for t in inputs], out, rows, cols, None, 0)
     assert torch.equal(out.cpu(), want), f"{ops} {args}"
+
+
+@pytest.mark.parametrize("rows, cols", [(64, 512), (256, 4096), (48, 1000), (8, 8192)])
+def test_row_programs_built_at_first_use_equal_the_interpreter(rows, cols, monkeypatch):
+    """The first launches of a new row program run in the interpreter while nvcc builds the kernel specialised for
+    it; the specialised kernel then gives bit-identical results (same arithmetic, same reduction order)."""
+    from pyasc_b200 import jit
+    if jit.compiler() is None:
+        pytest.skip("no nvcc on this machine")
+    gen = torch.Generator().manual_seed(rows + cols)
+    x = (torch.randn(rows, cols, generator=gen) * 2 + 1).cuda()
+    gamma, beta = (torch.rand(1, cols, generator=gen) + 0.5).cuda(), torch.randn(1, cols, generator=gen).cuda()
+    lib = capi.load()
+
+    def run():
+        out = torch.zeros_like(x)
+        K.layer_norm_rows[8](x, gamma, beta, out, rows, cols, 4, 1e-5)
+        torch.cuda.synchronize()
+        return out
+
+    monkeypatch.setenv("ASC_CUDA_JIT", "0")
+    assert lib.asc_cuda_eltwise_set_lanes(0x100) == 0           # the interpreter, whatever is registered already
+    try:
+        plain = run()
+    finally:
+        assert lib.asc_cuda_eltwise_set_lanes(0) == 0
+    monkeypatch.setenv("ASC_CUDA_JIT", "sync")
+    fast = run()
+    (step, ) = K.layer_norm_rows.last_plan.steps
+    assert jit.request(*step.program), jit.failures()            # registered by the launch itself
+    assert torch.equal(fast, plain)
+    ref = torch.nn.functional.layer_norm(x, (cols, ), gamma[0], beta[0], 1e-5)
+    torch.testing.assert_close(fast, ref, rtol=1e-4, atol=1e-5)

@@ -152,13 +152,13 @@ def test_unsupported_pattern_raises_not_implemented():
         column_sums_of_squares[1](x, np.zeros(64, np.float32), 16, 64)
 
     @asc2.jit
-    def masked(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+    def bit_masked(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
         x = asc2.load(asc2.tensor(x_ptr, [n]), [n], offsets=[0])
-        with asc2.mask(count=8, other=0):
+        with asc2.mask(bits=(0, 0xff), other=0):          # lane masks of the Ascend vector unit: no counterpart here
             y = x + 1
         asc2.store(y, asc2.tensor(out_ptr, [n]), offsets=[0])
     with pytest.raises(NotImplementedError, match="mask"):
-        masked[1](np.zeros(64, np.float32), np.zeros(64, np.float32), 64)
+        bit_masked[1](np.zeros(64, np.float32), np.zeros(64, np.float32), 64)
 
 
 # ----------------------------------------------------------------------------- reference error behaviour
