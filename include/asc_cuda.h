@@ -229,6 +229,26 @@ int32_t asc_cuda_gemm_f16(const void* A, const void* B, void* C, int64_t M, int6
                           int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype, int32_t flags,
                           void* stream);
 
+/* asc_cuda_gemm_f16 for callers that cannot allocate device memory while they run: a latency-critical host thread
+ * that must never block in the driver's allocator, a service whose device-memory budget was handed out in full at
+ * start-up, code under a rule that forbids cudaMalloc after initialisation.  It has no counterpart in the
+ * reference.  The kernel is the
+ * split-K one (K cut over several CTAs per 128 x 256 tile, partial tiles summed in slice order), and its
+ * workspace is not allocated per call but is a fixed array inside the library, 8 MiB + 1 KiB, which every GPU
+ * that loads the library holds until the process exits.  This entry point calls no cudaMalloc, cudaFree or other
+ * allocating routine.
+ *   - Limit: C may cover at most 64 tiles, ceil(M / 128) * ceil(N / 256) <= 64 (e.g. 1024 x 2048); anything larger
+ *     returns status 6 (ASC_ERR_TOO_LARGE).  Arguments, alignment rules and flags as for asc_cuda_gemm_f16.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current) and sets a function attribute; make that first call outside any stream capture.
+ *   - All calls on a device share the one array: the part that must start at zero (the per-tile counters) is
+ *     cleared on the stream at the start of every call, but two calls that overlap on the GPU (different streams,
+ *     or graphs replayed concurrently) race on it and give wrong results.  Keep calls on one stream, or order
+ *     them with events. */
+int32_t asc_cuda_gemm_f16_static_workspace(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                                           int64_t lda, int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype,
+                                           int32_t flags, void* stream);
+
 /* fp32-input matmul with the same epilogue options (CUDA-core FMA; exists so that the fp32 case of
  * python/test/asc2/kernels/test_matmul_fixpipe.py:36-48 runs; not a tuned path). */
 int32_t asc_cuda_gemm_f32(const float* A, const float* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,

@@ -61,6 +61,8 @@ PROTOTYPES: Dict[str, Sequence] = {
     "asc_cuda_rms_norm_f16": (P, P, P, c_int64, c_int64, c_int64, c_float, P),
     "asc_cuda_gemm_f16": (P, P, P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32,
                           c_int32, P),
+    "asc_cuda_gemm_f16_static_workspace": (P, P, P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32,
+                                           c_int32, P),
     "asc_cuda_gemm_f32": (P, P, P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32, P),
     "asc_cuda_gemm_i8": (P, P, P, P, P, P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, P),
     "asc_cuda_attn_fwd_f16": (P, P, P, P, c_int32, c_int32, c_int32, c_int32, c_float, c_int32, c_int32, P),

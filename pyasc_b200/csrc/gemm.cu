@@ -1237,6 +1237,26 @@ int32_t dispatch_gemm(const void* A, const void* B, int64_t lda, int64_t ldb, CU
   return launch_gemm<kElemBytes, kMode>(A, B, lda, ldb, dt, idesc, p, max_ctas, stream);
 }
 
+// Workspace of asc_cuda_gemm_f16_static_workspace: room for the counter header and 64 partial tiles (8 MiB + 1 KiB).
+// In host code the array's name only stands for the symbol; its device address comes from cudaGetSymbolAddress,
+// looked up once per device with that device current.
+constexpr int kStaticMaxPartials = 64;
+static __device__ __align__(256) unsigned char g_static_splitk_workspace[kSplitHeaderBytes + kStaticMaxPartials * kPartialTileBytes];
+static std::atomic<void*> g_static_workspace_addr[aschost::PerDevice::kMax];
+
+int32_t static_scratch_address(void** out) {
+  int dev = 0;
+  ASC_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= aschost::PerDevice::kMax) return ASC_ERR_INVALID_ARG;
+  void* addr = g_static_workspace_addr[dev].load(std::memory_order_acquire);
+  if (addr == nullptr) {
+    ASC_CUDA_TRY(cudaGetSymbolAddress(&addr, g_static_splitk_workspace));
+    g_static_workspace_addr[dev].store(addr, std::memory_order_release);
+  }
+  *out = addr;
+  return ASC_OK;
+}
+
 int32_t check_gemm_args(const void* A, const void* B, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
                         int64_t ldc, int elem_bytes) {
   if (A == nullptr || B == nullptr) return ASC_ERR_INVALID_ARG;
@@ -1285,6 +1305,46 @@ int32_t asc_cuda_gemm_f16(const void* A, const void* B, void* C, int64_t M, int6
     case 0: return dispatch_gemm<2, EPI_F16>(A, B, lda, ldb, dt, 1, in_dtype, p, 0, s);
     case 1: return dispatch_gemm<2, EPI_BF16>(A, B, lda, ldb, dt, 1, in_dtype, p, 0, s);
     default: return dispatch_gemm<2, EPI_F32>(A, B, lda, ldb, dt, 1, in_dtype, p, 0, s);
+  }
+}
+
+// The split-K GEMM for callers that must not allocate: its workspace is the file-scope array below, which every
+// GPU that loads this library holds until the process exits.  See include/asc_cuda.h for the contract.
+int32_t asc_cuda_gemm_f16_static_workspace(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K,
+                                           int64_t lda, int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype,
+                                           int32_t flags, void* stream) {
+  if (C == nullptr) return ASC_ERR_INVALID_ARG;
+  if (in_dtype < 0 || in_dtype > 1 || out_dtype < 0 || out_dtype > 2 || (flags & ~3) != 0) return ASC_ERR_INVALID_ARG;
+  if ((flags & 2) && out_dtype != 2) return ASC_ERR_UNSUPPORTED;
+  int32_t rc = check_gemm_args(A, B, M, N, K, lda, ldb, ldc, 2);
+  if (rc != ASC_OK) return rc;
+  const int64_t tiles = ((M + kBlockM - 1) / kBlockM) * ((N + kBlockN - 1) / kBlockN);
+  if (tiles > kStaticMaxPartials) return ASC_ERR_TOO_LARGE;      // C larger than 64 tiles of 128 x 256
+  void* scratch = nullptr;
+  if ((rc = static_scratch_address(&scratch)) != ASC_OK) return rc;
+  int sms = 0;
+  if ((rc = aschost::sm_count(&sms)) != ASC_OK) return rc;
+  const int64_t num_kb = (K * 2 + kKBytes - 1) / kKBytes;
+  int64_t room = kStaticMaxPartials / tiles;                    // slices per tile the array has room for
+  if (room > sms / tiles) room = sms / tiles;                   // ... and the GPU has SMs for
+  int split = split_k_slices(tiles, num_kb, tiles * (room < 1 ? 1 : room));
+  if (tiles * split > sms) return ASC_ERR_TOO_LARGE;            // every CTA of the grid must be running at once
+  GemmParams p{};
+  p.c = C;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldc = ldc;
+  p.relu = flags & 1;
+  p.accumulate = (flags >> 1) & 1;
+  p.vec_ok = aschost::aligned16(C) && ((ldc * (out_dtype == 2 ? 4 : 2)) % 16 == 0);
+  const CUtensorMapDataType dt = in_dtype == 0 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const uint32_t idesc = make_idesc(1, in_dtype, in_dtype, 0, 1, kBlockM, kBlockN);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (out_dtype) {
+    case 0: return launch_gemm_splitk<2, EPI_F16>(A, B, lda, ldb, dt, idesc, p, split, scratch, s);
+    case 1: return launch_gemm_splitk<2, EPI_BF16>(A, B, lda, ldb, dt, idesc, p, split, scratch, s);
+    default: return launch_gemm_splitk<2, EPI_F32>(A, B, lda, ldb, dt, idesc, p, split, scratch, s);
   }
 }
 
