@@ -55,6 +55,7 @@ class Step:
         self.build = build
         self.note = note
         self.program = None      # (kind, opcode-list words) of an elementwise / row program step, see pyasc_b200/jit.py
+        self.elements = 0        # elements such a step computes
 
     def __repr__(self) -> str:
         return f"Step({self.fn_name}: {self.note})"
@@ -888,7 +889,7 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
                     ctypes.c_int64(cols), lds_arr) + tail_args + (stream, )
         step = Step(fn_name, build,
                     f"{n_ops} ops over [{call_rows}, {cols}] pitches {lds} from {list(starts[:-1])} to {starts[-1]}")
-        step.program = program_key
+        step.program, step.elements = program_key, call_rows * cols
         return step
 
     for starts, call_rows in calls:
@@ -990,7 +991,7 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
             return (ops_arr, args_arr, ctypes.c_int32(n_ops), ins, types_arr, ctypes.c_int32(n_in),
                     _p(ptrs[out_idx] + out_size * lo), ctypes.c_int32(out_type), ctypes.c_int64(hi - lo), stream)
         step = Step("asc_cuda_eltwise_program", build, f"{n_ops} ops over [{lo}, {hi})")
-        step.program = program_key
+        step.program, step.elements = program_key, hi - lo
         return [step]
 
     lds_arr = (ctypes.c_int64 * (n_in + 1))(*([tshape[-1]] * (n_in + 1)))
@@ -1004,7 +1005,7 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
                     _p(ptrs[out_idx] + out_size * first), ctypes.c_int32(out_type), ctypes.c_int64(rows),
                     ctypes.c_int64(cols), lds_arr, stream)
         step = Step("asc_cuda_eltwise_program_2d", build, f"{n_ops} ops over [{rows}, {cols}] at ({r0}, {c0})")
-        step.program = program_key
+        step.program, step.elements = program_key, rows * cols
         return step
 
     for lo, hi in intervals:

@@ -19,6 +19,7 @@ a background thread.
 """
 from __future__ import annotations
 
+import atexit
 import ctypes
 import hashlib
 import os
@@ -38,8 +39,12 @@ Key = Tuple[int, Tuple[int, ...]]
 
 _lock = threading.Lock()
 _registered: Dict[Key, ctypes.CDLL] = {}       # loaded and registered (the CDLL object keeps the code mapped)
-_pending: Dict[Key, threading.Thread] = {}
+_pending: Dict[Key, bool] = {}                   # queued or being built
+_queue: List[Key] = []
+_workers = 0
+_stopping = False
 _failed: Dict[Key, str] = {}
+_exit_hook = False
 builds: List[str] = []                          # paths of the libraries built or loaded in this process
 
 
@@ -157,9 +162,29 @@ def _build_and_register(key: Key) -> None:
             _pending.pop(key, None)
 
 
+MAX_BUILDERS = 2        # nvcc processes this module runs at a time
+
+
+def _worker() -> None:
+    while True:
+        with _lock:
+            if _stopping or not _queue:
+                global _workers
+                _workers -= 1
+                return
+            key = _queue.pop(0)
+        _build_and_register(key)
+
+
+def min_elements() -> int:
+    """Launches that touch fewer elements than this keep the interpreter: the build would cost more than it saves."""
+    return int(os.environ.get("ASC_CUDA_JIT_MIN_ELEMENTS", str(1 << 15)))
+
+
 def request(kind: int, words: Sequence[int], wait: bool = False) -> bool:
     """Make sure the specialised kernel for this program exists or is being built.  Returns True when it is
     registered (the next launch runs it), False while the interpreter still serves the program."""
+    global _workers, _exit_hook
     if mode() in ("0", "off", "no", "false") or not words:
         return False
     key: Key = (int(kind), tuple(int(w) for w in words))
@@ -168,43 +193,69 @@ def request(kind: int, words: Sequence[int], wait: bool = False) -> bool:
             return True
         if key in _failed:
             return False
-        thread = _pending.get(key)
-    if thread is None:
+        queued = key in _pending
+    if not queued:
         cached = cache_dir() / library_name(*key)
         if cached.exists() or wait or mode() == "sync":
             _build_and_register(key)
             return key in _registered
-        thread = threading.Thread(target=_build_and_register, args=(key, ), daemon=True)
         with _lock:
-            if key in _pending:
-                thread = _pending[key]
-            else:
-                _pending[key] = thread
-                thread.start()
+            if key not in _pending:
+                _pending[key] = True
+                _queue.append(key)
+                if _workers < MAX_BUILDERS:
+                    _workers += 1
+                    threading.Thread(target=_worker, daemon=True).start()
+                if not _exit_hook:
+                    atexit.register(_shutdown)
+                    _exit_hook = True
     if wait:
-        thread.join()
+        wait_all()
     return key in _registered
 
 
 def prepare(plan, wait: bool = False) -> int:
-    """Requests the specialised kernel of every program step of a launch plan; returns how many are registered."""
+    """Requests the specialised kernel of every program step of a launch plan that is large enough to gain from it;
+    returns how many are registered."""
     ready = 0
+    work: Dict[Key, int] = {}
     for step in plan.steps:
         prog = getattr(step, "program", None)
-        if prog is not None and request(prog[0], prog[1], wait=wait):
+        if prog is not None:
+            work[prog] = work.get(prog, 0) + int(getattr(step, "elements", 0))
+    least = 0 if wait else min_elements()
+    for prog, elements in work.items():
+        if elements >= least and request(prog[0], prog[1], wait=wait):
             ready += 1
     return ready
 
 
 def wait_all() -> None:
-    """Blocks until every build started so far has finished."""
+    """Blocks until every build requested so far has finished."""
+    import time
     while True:
         with _lock:
-            threads = list(_pending.values())
-        if not threads:
-            return
-        for t in threads:
-            t.join()
+            if not _pending:
+                return
+        time.sleep(0.02)
+
+
+def _shutdown() -> None:
+    """At interpreter exit: builds not yet started are dropped, the ones running finish (their libraries land in
+    the cache whole)."""
+    global _stopping
+    import time
+    with _lock:
+        _stopping = True
+        for key in _queue:
+            _pending.pop(key, None)
+        _queue.clear()
+    deadline = time.time() + 30
+    while time.time() < deadline:
+        with _lock:
+            if not _pending:
+                return
+        time.sleep(0.02)
 
 
 def failures() -> Dict[Key, str]:
