@@ -282,7 +282,10 @@ int32_t launch_reg(const float* x, float* out, int64_t rows, int64_t cols, int64
       if (occupancy < 1) occupancy = 1;
       resident.set(dev, occupancy);
     }
-    ctas_per_sm = 4 * occupancy;
+    // ... unless that leaves a CTA fewer than 32 rows: then one wave, whose CTAs each keep a row in flight behind
+    // the one they work on (measured at 4096 columns: 2048 rows 12.9 vs 15.6 us, 4096 rows 22.4 vs 24.8, 8192 rows
+    // 42.8 vs 43.2, 16384 rows 89.0 vs 82.7)
+    ctas_per_sm = rows >= static_cast<int64_t>(32) * sms * occupancy ? 4 * occupancy : occupancy;
   }
   int64_t grid = static_cast<int64_t>(sms) * ctas_per_sm;
   if (grid > rows) grid = rows;
@@ -308,7 +311,8 @@ int32_t launch_reg16(const __half* x, __half* out, int64_t rows, int64_t cols, i
     if (occupancy < 1) occupancy = 1;
     resident.set(dev, occupancy);
   }
-  int64_t grid = static_cast<int64_t>(sms) * 4 * occupancy;   // four whole waves, as for fp32 rows
+  // four whole waves, or one when a CTA would get fewer than 32 rows, as for fp32 rows
+  int64_t grid = static_cast<int64_t>(sms) * (rows >= static_cast<int64_t>(32) * sms * occupancy ? 4 : 1) * occupancy;
   if (grid > rows) grid = rows;
   softmax_rows_reg16_kernel<kThreads, kVec><<<static_cast<unsigned>(grid), kThreads, 0, stream>>>(
       x, out, rows, static_cast<int>(cols / 8), ld / 8);
