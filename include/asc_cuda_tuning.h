@@ -36,7 +36,8 @@ int32_t asc_cuda_gemm_set_mode(int32_t mode);
 
 /* bits 0-7: elements each thread evaluates per opcode dispatch in asc_cuda_eltwise_program's aligned path
  * (4, 8 or 16; anything else: chosen by program length); bit 8: run every program in the interpreter, also
- * those with a compile-time specialised kernel.  Process-wide. */
+ * those with a compile-time specialised kernel; bits 16-23: waves of resident CTAs in the grid (0: four).
+ * Process-wide. */
 int32_t asc_cuda_eltwise_set_lanes(int32_t lanes);
 
 /* Self-test of the bounded device-side waits: launches one warp that waits on a barrier nobody arrives on, with a

@@ -888,7 +888,8 @@ __global__ void __launch_bounds__(kThreads) row_compiled_kernel(const __grid_con
 }
 
 // ---- launch helpers of the generated translation units (CUDA runtime calls only) ----
-// Grid sizing as for the kernels built into the library: four waves of resident CTAs, CTAs stride beyond.
+// Grid sizing as for the kernels built into the library: four waves of resident CTAs (one for small launches), CTAs
+// stride beyond.
 template <class P>
 inline int jit_launch_eltwise(const EltProgram& prog, int64_t n, int oct, int sms, cudaStream_t stream) {
   auto launch = [&](auto kernel, int lanes) -> int {
@@ -898,7 +899,8 @@ inline int jit_launch_eltwise(const EltProgram& prog, int64_t n, int oct, int sm
     if (resident < 1) resident = 1;
     const int64_t per_cta = static_cast<int64_t>(kThreads) * lanes;
     int64_t ctas = (n + per_cta - 1) / per_cta;
-    const int64_t cap = static_cast<int64_t>(sms) * resident * 4;
+    const int64_t wave = static_cast<int64_t>(sms) * resident;
+    const int64_t cap = wave * (ctas <= 8 * wave ? 1 : 4);
     if (ctas > cap) ctas = cap;
     kernel<<<static_cast<unsigned>(ctas), kThreads, 0, stream>>>(prog, n);
     return static_cast<int>(cudaGetLastError());

@@ -283,8 +283,8 @@ int32_t launch_reg(const float* x, float* out, int64_t rows, int64_t cols, int64
       resident.set(dev, occupancy);
     }
     // ... unless that leaves a CTA fewer than 32 rows: then one wave, whose CTAs each keep a row in flight behind
-    // the one they work on (measured at 4096 columns: 2048 rows 12.9 vs 15.6 us, 4096 rows 22.4 vs 24.8, 8192 rows
-    // 42.8 vs 43.2, 16384 rows 89.0 vs 82.7)
+    // the one they work on (measured at 4096 columns: 2048 rows 13.0 vs 15.6 us, 4096 rows 22.1 vs 24.8, 8192 rows
+    // 43.4 vs 43.2, 16384 rows 89.0 vs 82.0)
     ctas_per_sm = rows >= static_cast<int64_t>(32) * sms * occupancy ? 4 * occupancy : occupancy;
   }
   int64_t grid = static_cast<int64_t>(sms) * ctas_per_sm;
