@@ -75,3 +75,63 @@ def branch_on_data(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.
 def test_branch_on_tile_data_is_refused():
     with pytest.raises(NotImplementedError, match="not a function of the block index"):
         branch_on_data[1](torch.zeros(N), torch.zeros(N), N)
+
+
+@asc2.jit
+def branch_in_every_iteration(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+    x_gm, out_gm = asc2.tensor(x_ptr, [8 * n]), asc2.tensor(out_ptr, [8 * n])
+    for t in range(8):
+        x = asc2.load(x_gm, [n], offsets=[t * n])
+        if t < 3:
+            x = x + 1
+        if t % 4 == 0:
+            x = x * 2
+        asc2.store(x, out_gm, offsets=[t * n])
+
+
+def test_two_branches_in_a_loop_give_four_guarded_stores():
+    x = torch.zeros(8 * N)
+    branch_in_every_iteration[1](x, torch.zeros_like(x), N)
+    plan = branch_in_every_iteration.last_plan
+    notes = sorted(s.note for s in plan.steps)
+    # t < 3 and t % 4 == 0: t = 0; t < 3 only: t = 1, 2; t % 4 == 0 only: t = 4; neither: 3, 5, 6, 7
+    assert notes == sorted([f"3 ops over [0, {N})", f"2 ops over [{N}, {3 * N})", f"2 ops over [{4 * N}, {5 * N})",
+                            f"1 ops over [{3 * N}, {4 * N})", f"1 ops over [{5 * N}, {8 * N})"])
+
+
+def test_compile_time_conditions_do_not_fork(monkeypatch):
+    from asc.codegen import tracer
+    runs = []
+    real = tracer.TraceContext
+
+    class Counting(real):
+        def __init__(self, *a, **k):
+            runs.append(1)
+            super().__init__(*a, **k)
+    monkeypatch.setattr(tracer, "TraceContext", Counting)
+
+    @asc2.jit
+    def static_if(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int], flag: asc.ConstExpr[bool],
+                  count: int):
+        x = asc2.load(asc2.tensor(x_ptr, [n]), [n], offsets=[0])
+        if flag:
+            x = x + 1
+        if count > 2:              # a launch argument: known while tracing
+            x = x * 2
+        asc2.store(x, asc2.tensor(out_ptr, [n]), offsets=[0])
+    static_if[1](torch.zeros(N), torch.zeros(N), N, True, 5)
+    assert len(runs) == 1
+    assert static_if.last_plan.steps[0].note.startswith("3 ops")
+
+
+def test_too_many_paths_are_refused():
+    @asc2.jit
+    def seven_branches(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
+        b = asc2.block_idx()
+        x = asc2.load(asc2.tensor(x_ptr, [n]), [n], offsets=[0])
+        for k in asc.static_range(7):
+            if (b // (2 ** k)) % 2 == 1:
+                x = x + 1
+        asc2.store(x, asc2.tensor(out_ptr, [128 * n]), offsets=[b * n])
+    with pytest.raises(NotImplementedError, match="more than 64 paths"):
+        seven_branches[128](torch.zeros(N), torch.zeros(128 * N), N)
