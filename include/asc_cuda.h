@@ -173,6 +173,16 @@ int32_t asc_cuda_row_program(const int32_t* ops, const int32_t* args, int32_t n_
                              const int32_t* input_types, int32_t n_inputs, void* out, int32_t out_type, int64_t rows,
                              int64_t cols, const int64_t* lds, int32_t row_result, void* stream);
 
+/* An elementwise program (no row opcodes) over a [rows, cols] window, reduced along the rows: out[c] = kind over r of
+ * program(r, c); kind: 0 sum, 1 max, 2 min, 3 product, combined in fp32 and rounded once to out_type (fp32, fp16 or
+ * bf16).  lds: the row pitch of every input (0: a row every window row reads), NULL: all pitches equal cols.  With
+ * rows == 0 every out[c] receives the identity of the reduction.  Serves asc2.reduce_*(expression, 0) on tile-sized
+ * windows (python/asc/language/tile/reduction_ops.py:33-188; ReduceOp, lib/Conversion/LowerToAsc/LowerAscTile.cpp:428-459):
+ * a thread owns a column, so the grid covers the columns only. */
+int32_t asc_cuda_col_program(const int32_t* ops, const int32_t* args, int32_t n_ops, const void* const* inputs,
+                             const int32_t* input_types, int32_t n_inputs, void* out, int32_t out_type, int64_t rows,
+                             int64_t cols, const int64_t* lds, int32_t kind, void* stream);
+
 /* Registers a kernel specialised for one program, so that asc_cuda_eltwise_program[_2d] (kind 0) or
  * asc_cuda_row_program (kind 1000 + columns per thread: 1, 2, 4, ... 32) runs it instead of the interpreter whenever
  * that program is submitted.  `words[k]` = ops[k] | (args[k] << 16 for a LOAD, TEE or TMP) | (1 << 24 for a LOAD of

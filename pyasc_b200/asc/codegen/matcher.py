@@ -619,7 +619,8 @@ class _EltProgram:
     def _row_reduction(self, node: Node, dtype: DataType) -> Optional[_Frag]:
         """``reduce_*`` along the last dimension of a computed tile: the tile's code, then a ROW opcode."""
         src = node.args[0]
-        if dtype != KT.float32 or src.dtype != KT.float32 or node.attrs["kind"] not in _ROW_CODE:
+        # fp16 / bf16 rows are reduced in fp32 and the result is rounded once (as torch's CPU reductions do)
+        if dtype not in (KT.float32, KT.float16, KT.bfloat16) or src.dtype != dtype or node.attrs["kind"] not in _ROW_CODE:
             return None
         dims = node.attrs["dims"]
         if self.full_shape is not None:
@@ -643,7 +644,7 @@ class _EltProgram:
             return None
         inner = inner.pushed()
         self.row_ops = True
-        return _Frag(inner.code + [(_ROW_CODE[node.attrs["kind"]], 0)], inner.need)
+        return self._rounded(_Frag(inner.code + [(_ROW_CODE[node.attrs["kind"]], 0)], inner.need), dtype)
 
     def _finish(self, frag: _Frag) -> None:
         """The final program.  In a row program a value that occurs again is computed once: its first occurrence
@@ -1081,11 +1082,12 @@ def _match_row_result(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     """``store(f(reduce(g(tiles), 1), ...), vector)``: a [rows] (or [rows, 1]) tile whose elements are functions of
     row reductions of computed tiles, e.g. ``reduce_sum(x * x, 1)``.  One row program, one stored element per row."""
     value, out_t = eff.args
-    if not isinstance(value, Tile) or eff.kind != "store" or out_t.dtype != KT.float32 or value.dtype != KT.float32:
+    if not isinstance(value, Tile) or eff.kind != "store" or value.dtype != out_t.dtype or \
+            value.dtype not in (KT.float32, KT.float16, KT.bfloat16):
         return None
     direct = _node(value, "reduce")
-    if direct is not None and direct.args[0].node.kind in ("load", "copy"):
-        return None                        # a reduction of a loaded tile has its own kernel
+    if direct is not None and direct.args[0].node.kind in ("load", "copy") and value.dtype == KT.float32:
+        return None                        # a reduction of a loaded fp32 tile has its own kernel
     red = _find_row_reduction(value)
     if red is None:
         return None
@@ -1164,6 +1166,93 @@ def _match_row_scalar(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
 # Pattern: reduction of a loaded tile along one axis, or of the whole tile broadcast into the store
 # --------------------------------------------------------------------------------------------------
 _REDUCE_KIND = {"sum": 0, "max": 1, "min": 2, "prod": 3}
+
+
+def _match_col_reduce(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
+    """``store(reduce_*(expression, 0), vector)``: a 2-D tile that is computed (or loaded as fp16 / bf16) and reduced
+    along its first dimension: one column program per tile, a thread per column (``asc_cuda_col_program``).  A loaded
+    fp32 tile keeps the dedicated reduction kernel."""
+    value, out_t = eff.args
+    node = _node(value, "reduce") if isinstance(value, Tile) and eff.kind == "store" else None
+    if node is None or node.attrs["dims"] != (0, ):
+        return None
+    src = node.args[0]
+    dtype = value.dtype
+    if len(src.shape) != 2 or dtype not in (KT.float32, KT.float16, KT.bfloat16) or src.dtype != dtype or out_t.dtype != dtype:
+        return None
+    if src.node.kind in ("load", "copy") and dtype == KT.float32:
+        return None
+    rows, cols = src.shape
+    if value.shape not in ((cols, ), (1, cols)) or node.attrs["kind"] not in _REDUCE_KIND:
+        return None
+    offsets = eff.attrs["offsets"]
+    prog = _EltProgram(src.shape, offsets, out_t)
+    frag = prog.gen(src)
+    if frag is None or prog.row_ops or prog.reshaped:
+        return None
+    prog._finish(frag)
+    _check_program_limits(prog)
+    _check_fits(out_t)
+    for t in prog.inputs:
+        _check_fits(t)
+    window = _flat_window(out_t, offsets, value.shape)
+    if window is None:
+        raise _unsupported("column reduction whose result is not stored as one contiguous range")
+    env = enumerate_instances(trace.core_num, eff.loops, eff.guards)
+    n = env_count(env)
+    if n > MAX_CALLS:
+        raise _unsupported("column reduction of a computed tile in more than 4096 tiles")
+    out0 = eval_int(window[0], env, n)
+    if n and (out0.min() < 0 or (out0 + cols).max() > out_t.base.numel):
+        raise _unsupported("column reduction whose result reaches past the end of its tensor")
+    geoms = [_Geometry(o.tensor, o.offsets, o.shape, o.scalar, env, n) for o in prog.operands]
+    lds: List[int] = []
+    for o, g in zip(prog.operands, geoms):
+        if o.bcast:
+            if g.numel != cols:
+                raise _unsupported("broadcast of a tile that is not one row of the reduced tile")
+            lds.append(0)
+        elif g.pitch is not None:
+            if (g.rows, g.cols) != (rows, cols):
+                raise _unsupported("operand window of a different shape than the reduced tile")
+            lds.append(g.pitch)
+        else:
+            if g.numel != rows * cols:
+                raise _unsupported("operand tile with a different number of elements than the reduced tile")
+            lds.append(cols)
+    out_idx = out_t.base.index
+    in_idx = [o.tensor.base.index for o in prog.operands]
+    if out_idx in in_idx:
+        raise _unsupported("column reduction that stores into a tensor it loads")
+    calls = sorted(set(tuple(int(g.start[j]) for g in geoms) + (int(out0[j]), ) for j in range(n)), key=lambda c: c[-1])
+    if any(b[-1] < a[-1] + cols for a, b in zip(calls, calls[1:])):
+        raise _unsupported("column reductions of different tiles stored into overlapping ranges (the last writer would win)")
+    if not calls:
+        raise _unsupported("column reduction without any tile")
+    in_size = [o.tensor.dtype.bitwidth // 8 for o in prog.operands]
+    out_size = out_t.dtype.bitwidth // 8
+    n_ops, n_in, ops_arr, args_arr, types_arr, out_type = _program_arrays(prog, out_t)
+    lds_arr = (ctypes.c_int64 * max(1, len(lds)))(*lds)
+    kind = _REDUCE_KIND[node.attrs["kind"]]
+    plan = Plan(f"reduce:{node.attrs['kind']}:columns")
+    plan.reads.update(in_idx)
+    plan.writes.add(out_idx)
+    covered = calls[0][-1] == 0 and all(b[-1] == a[-1] + cols for a, b in zip(calls, calls[1:]))
+    if not (covered and calls[-1][-1] + cols == out_t.base.numel):
+        plan.partial_writes.add(out_idx)
+
+    def make_step(starts: Tuple[int, ...]) -> Step:
+        def build(ptrs, stream):
+            ins = (ctypes.c_void_p * max(1, n_in))(*[ptrs[i] + sz * st for i, sz, st in zip(in_idx, in_size, starts)])
+            return (ops_arr, args_arr, ctypes.c_int32(n_ops), ins, types_arr, ctypes.c_int32(n_in),
+                    _p(ptrs[out_idx] + out_size * starts[-1]), ctypes.c_int32(out_type), ctypes.c_int64(rows),
+                    ctypes.c_int64(cols), lds_arr, ctypes.c_int32(kind), stream)
+        return Step("asc_cuda_col_program", build,
+                    f"{node.attrs['kind']} over the rows of {n_ops} ops on [{rows}, {cols}] from {list(starts[:-1])} to {starts[-1]}")
+
+    for starts in calls:
+        plan.steps.append(make_step(starts))
+    return plan
 
 
 def _match_reduce(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
@@ -1978,7 +2067,7 @@ def _check_effect_order(trace: KernelTrace, first: Effect, second: Effect, cache
 # Entry point
 # --------------------------------------------------------------------------------------------------
 _MATCHERS = (_match_attention, _match_softmax, _match_rms_norm, _match_elementwise, _match_matmul, _match_eltwise_program,
-             _match_row_result, _match_row_scalar, _match_reduce)
+             _match_row_result, _match_row_scalar, _match_col_reduce, _match_reduce)
 
 
 def _is_identity_store(eff: Effect) -> bool:

@@ -377,6 +377,43 @@ extern "C" int32_t asc_cuda_row_program(const int32_t* ops, const int32_t* args,
   return launch_row_program<32>(prog, rows, max_depth, n_tmp, rr, sms, st);
 }
 
+// out[c] = reduce_kind over the rows r of program(r, c) for a [rows, cols] window; kind: 0 sum, 1 max, 2 min,
+// 3 product.  lds: row pitch of every input (0: one row that every window row reads); NULL: all pitches equal cols.
+extern "C" int32_t asc_cuda_col_program(const int32_t* ops, const int32_t* args, int32_t n_ops, const void* const* inputs,
+                                        const int32_t* input_types, int32_t n_inputs, void* out, int32_t out_type,
+                                        int64_t rows, int64_t cols, const int64_t* lds, int32_t kind, void* stream) {
+  if (rows < 0 || cols < 0 || n_inputs < 0 || n_inputs > kMaxInputs || n_ops <= 0 || n_ops > kMaxOps)
+    return ASC_ERR_INVALID_ARG;
+  if (ops == nullptr || args == nullptr || out == nullptr || (n_inputs > 0 && (inputs == nullptr || input_types == nullptr)))
+    return ASC_ERR_INVALID_ARG;
+  if (out_type < 0 || out_type >= T_COUNT || kind < 0 || kind > 3) return ASC_ERR_INVALID_ARG;
+  if (out_type == T_I32 || out_type == T_I16) return ASC_ERR_UNSUPPORTED;     // the combination runs on fp32 words
+  if (rows >= (int64_t{1} << 32) || cols >= (int64_t{1} << 31) || rows * cols >= (int64_t{1} << 32)) return ASC_ERR_TOO_LARGE;
+  EltProgram prog{};
+  int max_depth = 0;
+  int32_t rc = fill_program(ops, args, n_ops, inputs, input_types, n_inputs, false, prog, max_depth);
+  if (rc != ASC_OK) return rc;
+  if (reinterpret_cast<uintptr_t>(out) % elem_size(out_type) != 0) return ASC_ERR_MISALIGNED;
+  for (int k = 0; k < n_inputs; ++k) {
+    const int64_t ld = lds != nullptr ? lds[k] : cols;
+    if ((ld != 0 && ld < cols) || ld >= (int64_t{1} << 32)) return ASC_ERR_INVALID_ARG;
+    prog.ld[k] = static_cast<uint32_t>(ld);
+  }
+  if (cols == 0) return ASC_OK;
+  prog.out = out;
+  prog.out_type = out_type;
+  prog.cols = static_cast<uint32_t>(cols);
+  prog.ld[n_inputs] = static_cast<uint32_t>(cols);
+  const int row_op = OP_ROW_SUM + (kind == 0 ? 0 : kind == 1 ? 1 : kind == 2 ? 2 : 3);
+  const size_t smem = static_cast<size_t>(max_depth > 1 ? max_depth - 1 : 1) * kThreads * 4 * sizeof(float);
+  const int64_t ctas = (cols + kThreads - 1) / kThreads;
+  col_program_kernel<<<static_cast<unsigned>(ctas), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      prog, static_cast<uint32_t>(rows), row_op);
+  aschost::count_launch();
+  ASC_CUDA_TRY(cudaGetLastError());
+  return ASC_OK;
+}
+
 // Registers the entry point of a program specialised at first use (see find_jit): `words` are the opcode-list
 // words the unit was generated from, `fn` its `asc_jit_run`.  Registering the same list again replaces the entry.
 extern "C" int32_t asc_cuda_register_program(int32_t kind, const int32_t* words, int32_t n_words, void* fn) {

@@ -341,8 +341,14 @@ struct Interpreter {
   // opcodes, operand indices and stack depth.
   template <int kV>
   __device__ __forceinline__ static void run(const EltProgram& prog, int64_t i, float* stack_mem) {
-    const StackSlots<kV> slots{stack_mem + threadIdx.x * (kV >= 4 ? 4 : 1)};
     float top[kV];
+    eval<kV>(prog, i, stack_mem, top);
+    store_group<kV>(prog, i, top);
+  }
+  // The program's value for the kV lanes of element index i, without storing it.
+  template <int kV>
+  __device__ __forceinline__ static void eval(const EltProgram& prog, int64_t i, float* stack_mem, float (&top)[kV]) {
+    const StackSlots<kV> slots{stack_mem + threadIdx.x * (kV >= 4 ? 4 : 1)};
     int depth = 0;  // entries on the stack, the top included
 #define ASC_LANES _Pragma("unroll") for (int e = 0; e < kV; ++e)
 #define ASC_BIN(CODE)                                                   \
@@ -403,7 +409,6 @@ struct Interpreter {
 #undef ASC_UN
 #undef ASC_BIN
 #undef ASC_LANES
-    store_group<kV>(prog, i, top);
   }
 };
 
@@ -884,6 +889,26 @@ __global__ void __launch_bounds__(kThreads) row_compiled_kernel(const __grid_con
     float st[kStack][kV];
     float tmp[kMaxTmp][kV];
     RowStep<P, kV, 0, 0, 0u, 0u>::run(prog, r, cols, full, row_result, st, tmp, red);
+  }
+}
+
+// ---- executor 5: an elementwise program reduced along the columns of its window ----
+// out[c] = reduce over r of program(r, c) for a [rows, cols] window: a thread owns a column and walks its rows,
+// evaluating the program per element in the interpreter (consecutive threads read consecutive columns, so every
+// access of a warp is one contiguous run) and combining as it goes.  Made for the tile-sized windows of
+// asc2.reduce_*(expression, 0); the grid covers the columns, not the rows.
+__global__ void __launch_bounds__(kThreads) col_program_kernel(const __grid_constant__ EltProgram prog, uint32_t rows,
+                                                               int row_op) {
+  extern __shared__ __align__(16) float stack_mem[];
+  const uint32_t cols = prog.cols;
+  for (uint32_t c = blockIdx.x * kThreads + threadIdx.x; c < cols; c += gridDim.x * kThreads) {
+    float acc = row_identity(row_op);
+    for (uint32_t r = 0; r < rows; ++r) {
+      float v[1];
+      Interpreter::eval<1>(prog, static_cast<int64_t>(r) * cols + c, stack_mem, v);
+      acc = row_combine(row_op, acc, v[0]);
+    }
+    store_elem(prog.out, prog.out_type, c, acc);
   }
 }
 

@@ -209,7 +209,7 @@ def request(kind: int, words: Sequence[int], wait: bool = False) -> bool:
                 if not _exit_hook:
                     atexit.register(_shutdown)
                     _exit_hook = True
-    if wait:
+    if wait or mode() == "sync":     # also when another caller queued this program before: its build is under way
         wait_all()
     return key in _registered
 

@@ -4,6 +4,7 @@ the device launch."""
 import pytest
 import torch
 
+import asc
 import asc2
 
 import asc2_scripts as K
@@ -62,8 +63,13 @@ def test_reduction_rejections():
     x = torch.zeros(64, 32)
     with pytest.raises(NotImplementedError, match="past the end"):
         K.reduce_axis[1](x, torch.zeros(32), 0, [64, 32], [32, 0], [32], [0], asc2.reduce_sum, False)
+    # fp16 tiles reduced along the first axis take the column program (fp32 combination, one rounding) ...
+    K.reduce_axis[1](x.half(), torch.zeros(32, dtype=torch.float16), 0, [64, 32], [0, 0], [32], [0], asc2.reduce_sum,
+                     False)
+    assert step_of(K.reduce_axis)[0].pattern == "reduce:sum:columns"
+    # ... integer tiles have no reduction kernel
     with pytest.raises(NotImplementedError, match="float32 only"):
-        K.reduce_axis[1](x.half(), torch.zeros(32, dtype=torch.float16), 0, [64, 32], [0, 0], [32], [0], asc2.reduce_sum,
+        K.reduce_axis[1](x.int(), torch.zeros(32, dtype=torch.int32), 0, [64, 32], [0, 0], [32], [0], asc2.reduce_sum,
                          False)
 
 
@@ -102,3 +108,40 @@ def test_rms_norm_plans():
     K.rms_norm_1d[1](torch.zeros(256, dtype=torch.float16), torch.ones(256, dtype=torch.float16),
                      torch.empty(256, dtype=torch.float16), 256)
     assert step_of(K.rms_norm_1d)[1].fn_name == "asc_cuda_rms_norm_f16"
+
+
+def test_column_reduction_of_a_computed_tile_plans_one_column_program_per_tile(monkeypatch):
+    monkeypatch.setenv("DRY_RUN", "1")
+
+    @asc2.jit
+    def col_norms(x_ptr: asc.GlobalAddress, w_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, tiles: int,
+                  rows: asc.ConstExpr[int], cols: asc.ConstExpr[int]):
+        x_gm = asc2.tensor(x_ptr, [tiles * rows, cols])
+        out_gm = asc2.tensor(out_ptr, [tiles, cols])
+        w = asc2.load(asc2.tensor(w_ptr, [1, cols]), [1, cols], offsets=[0, 0])
+        for t in range(asc2.block_idx(), tiles, asc2.block_num()):
+            x = asc2.load(x_gm, [rows, cols], offsets=[t * rows, 0])
+            y = x * w.broadcast_to(rows, cols)
+            asc2.store(asc2.reduce_max(y * y, 0, keep_dims=True), out_gm, offsets=[t, 0])
+    x = torch.zeros(6 * 32, 256)
+    col_norms[4](x, torch.zeros(1, 256), torch.zeros(6, 256), 6, 32, 256)
+    plan = col_norms.last_plan
+    assert plan.pattern == "reduce:max:columns" and plan.reads == {0, 1} and plan.writes == {2}
+    assert [s.note.split(" from ")[1] for s in plan.steps] == [f"[{t * 32 * 256}, 0] to {t * 256}" for t in range(6)]
+    assert not plan.partial_writes                    # six rows of 256: the whole output
+
+
+def test_half_precision_row_reductions_plan_as_row_programs(monkeypatch):
+    monkeypatch.setenv("DRY_RUN", "1")
+
+    @asc2.jit
+    def row_sums(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: int, cols: asc.ConstExpr[int],
+                 rpt: asc.ConstExpr[int]):
+        x_gm, out_gm = asc2.tensor(x_ptr, [rows, cols]), asc2.tensor(out_ptr, [rows])
+        for i in range(asc2.block_idx() * rpt, rows, asc2.block_num() * rpt):
+            asc2.store(asc2.reduce_sum(asc2.load(x_gm, [rpt, cols], offsets=[i, 0]), 1), out_gm, offsets=[i])
+    for dtype, round_op in ((torch.float16, 33), (torch.bfloat16, 34)):
+        row_sums[4](torch.zeros(64, 512, dtype=dtype), torch.zeros(64, dtype=dtype), 64, 512, 8)
+        (step, ) = row_sums.last_plan.steps
+        built = step.build({0: 0, 1: 0}, None)
+        assert list(built[0][:3]) == [0, 59, round_op]          # LOAD, ROW_SUM in fp32, one rounding to the tile type

@@ -147,9 +147,11 @@ def test_unsupported_pattern_raises_not_implemented():
                                c: asc.ConstExpr[int]):
         x = asc2.load(asc2.tensor(x_ptr, [r, c]), [r, c], offsets=[0, 0])
         asc2.store(asc2.reduce_sum(x * x, 0), asc2.tensor(out_ptr, [c]), offsets=[0])
-    x = np.zeros((16, 64), np.float32)
+    x = np.zeros((16, 64), np.int32)          # integer tiles: column reductions of computed tiles are floating-point only
     with pytest.raises(NotImplementedError, match="no kernel for this pattern"):
-        column_sums_of_squares[1](x, np.zeros(64, np.float32), 16, 64)
+        column_sums_of_squares[1](x, np.zeros(64, np.int32), 16, 64)
+    column_sums_of_squares[1](np.zeros((16, 64), np.float32), np.zeros(64, np.float32), 16, 64)
+    assert column_sums_of_squares.last_plan.pattern == "reduce:sum:columns"
 
     @asc2.jit
     def bit_masked(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, n: asc.ConstExpr[int]):
