@@ -407,6 +407,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
             if (lane == 0) {
               issue_qk(t, kst);
               umma_commit(smem_u32(&ctl.s_full[t]));
+              if ((t == 0 ? n0 : n1) == 1) umma_commit(smem_u32(&ctl.q_empty[t]));   // the tile's only Q K^T
             }
             __syncwarp();
           }
@@ -436,9 +437,11 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
                 if (j + 1 < nt) {
                   issue_qk(t, kst);
                   umma_commit(smem_u32(&ctl.s_full[t]));
+                  // The tile's last Q K^T of this item: once it retires the producer may load the next item's
+                  // Q tile, a whole key step before this item ends, so that the load is off the critical path.
+                  if (j + 2 == nt) umma_commit(smem_u32(&ctl.q_empty[t]));
                 } else {
                   umma_commit(smem_u32(&ctl.o_full[t]));
-                  umma_commit(smem_u32(&ctl.q_empty[t]));   // every Q K^T of this item's tile has retired
                 }
               }
               __syncwarp();
