@@ -531,8 +531,8 @@ __global__ void __launch_bounds__(kThreads) eltwise_program_kernel(const __grid_
 }
 
 // ---- executor 3: programs with row reductions ----
-// One CTA evaluates one row of the window at a time; thread t owns columns t, t + 256, ... (kV of them), so
-// the loads and stores of consecutive threads are consecutive.  The top of the stack is in registers, lower
+// One CTA evaluates one row of the window at a time; thread t owns kV columns of it (row_col: t, t + 256, ... for short
+// rows, quads of consecutive columns for long ones), so the loads and stores of consecutive threads are consecutive.  The top of the stack is in registers, lower
 // levels in shared memory ([level][lane][thread]: conflict-free).  A ROW_* opcode reduces the thread's lanes,
 // then the CTA (shuffles + one exchange through shared memory), and every lane of the top takes the result:
 // the reduced value is from then on an ordinary operand, which is how `x - max(x)`, `x / sum(x)` or a
@@ -566,19 +566,54 @@ __device__ __forceinline__ float row_combine(int op, float a, float b) {
 
 __device__ __forceinline__ int16_t word_to_i16(float v) { return static_cast<int16_t>(__float_as_int(v)); }
 
-// The lanes of one thread for one operand: element c = thread + e * 256 of row `base`.  The element type is
-// resolved once per operand, and a row that fills every lane skips the bounds checks.
+// Which column of the row lane e of this thread holds.  Rows of up to 512 columns: thread + e * 256.  Longer rows:
+// quads of consecutive columns, 4 * thread + (e / 4) * 1024 + e % 4, so that a thread's accesses are 128-bit (64-bit
+// for 16-bit elements) wherever the operand's row start is aligned for them; the mapping itself does not depend on
+// alignment, so neither does the order in which a row is summed.
+template <int kV>
+__device__ __forceinline__ uint32_t row_col(int e) {
+  if constexpr (kV >= 4) return 4u * threadIdx.x + static_cast<uint32_t>(e >> 2) * (4u * kThreads) + static_cast<uint32_t>(e & 3);
+  return threadIdx.x + static_cast<uint32_t>(e) * kThreads;
+}
+
+template <typename T>
+struct Quad;                       // four consecutive elements as one memory access
+template <>
+struct Quad<float> { using type = float4; };
+template <>
+struct Quad<int32_t> { using type = int4; };
+template <>
+struct Quad<__half> { using type = uint2; };
+template <>
+struct Quad<__nv_bfloat16> { using type = uint2; };
+template <>
+struct Quad<int16_t> { using type = uint2; };
+
+// The lanes of one thread for one operand: columns row_col(e) of the row that starts at element `base`.  The element
+// type is resolved once per operand, and a row that fills every lane skips the bounds checks.
 template <int kV>
 __device__ __forceinline__ void row_load(const void* p, int type, int64_t base, uint32_t cols, bool full, float (&v)[kV]) {
-#define ASC_ROW_LOAD(T, CONV)                                                         \
-  {                                                                                   \
-    const T* q = reinterpret_cast<const T*>(p) + base + threadIdx.x;                  \
-    if (full) {                                                                       \
-      _Pragma("unroll") for (int e = 0; e < kV; ++e) v[e] = CONV(q[e * kThreads]);    \
-    } else {                                                                          \
-      _Pragma("unroll") for (int e = 0; e < kV; ++e)                                  \
-        v[e] = threadIdx.x + e * kThreads < cols ? CONV(q[e * kThreads]) : 0.f;       \
-    }                                                                                 \
+#define ASC_ROW_LOAD(T, CONV)                                                                         \
+  {                                                                                                   \
+    const T* row = reinterpret_cast<const T*>(p) + base;                                              \
+    if constexpr (kV >= 4) {                                                                          \
+      using Q = typename Quad<T>::type;                                                               \
+      const bool vec = (reinterpret_cast<uintptr_t>(row) & (sizeof(Q) - 1)) == 0;                     \
+      _Pragma("unroll") for (int g = 0; g < kV / 4; ++g) {                                            \
+        const uint32_t c0 = row_col<kV>(4 * g);                                                       \
+        if (vec && (full || c0 + 3 < cols)) {                                                         \
+          const Q quad = *reinterpret_cast<const Q*>(row + c0);                                       \
+          const T* t4 = reinterpret_cast<const T*>(&quad);                                            \
+          _Pragma("unroll") for (int i = 0; i < 4; ++i) v[4 * g + i] = CONV(t4[i]);                   \
+        } else {                                                                                      \
+          _Pragma("unroll") for (int i = 0; i < 4; ++i)                                               \
+            v[4 * g + i] = (full || c0 + i < cols) ? CONV(row[c0 + i]) : 0.f;                         \
+        }                                                                                             \
+      }                                                                                               \
+    } else {                                                                                          \
+      _Pragma("unroll") for (int e = 0; e < kV; ++e)                                                  \
+        v[e] = (full || row_col<kV>(e) < cols) ? CONV(row[row_col<kV>(e)]) : 0.f;                     \
+    }                                                                                                 \
   }
   switch (type) {
     case T_F16: ASC_ROW_LOAD(__half, __half2float) break;
@@ -592,11 +627,28 @@ __device__ __forceinline__ void row_load(const void* p, int type, int64_t base, 
 
 template <int kV>
 __device__ __forceinline__ void row_store(void* p, int type, int64_t base, uint32_t cols, bool full, const float (&v)[kV]) {
-#define ASC_ROW_STORE(T, CONV)                                                          \
-  {                                                                                     \
-    T* q = reinterpret_cast<T*>(p) + base + threadIdx.x;                                \
-    _Pragma("unroll") for (int e = 0; e < kV; ++e)                                      \
-      if (full || threadIdx.x + e * kThreads < cols) q[e * kThreads] = CONV(v[e]);      \
+#define ASC_ROW_STORE(T, CONV)                                                                        \
+  {                                                                                                   \
+    T* row = reinterpret_cast<T*>(p) + base;                                                          \
+    if constexpr (kV >= 4) {                                                                          \
+      using Q = typename Quad<T>::type;                                                               \
+      const bool vec = (reinterpret_cast<uintptr_t>(row) & (sizeof(Q) - 1)) == 0;                     \
+      _Pragma("unroll") for (int g = 0; g < kV / 4; ++g) {                                            \
+        const uint32_t c0 = row_col<kV>(4 * g);                                                       \
+        if (vec && (full || c0 + 3 < cols)) {                                                         \
+          Q quad;                                                                                     \
+          T* t4 = reinterpret_cast<T*>(&quad);                                                        \
+          _Pragma("unroll") for (int i = 0; i < 4; ++i) t4[i] = CONV(v[4 * g + i]);                   \
+          *reinterpret_cast<Q*>(row + c0) = quad;                                                     \
+        } else {                                                                                      \
+          _Pragma("unroll") for (int i = 0; i < 4; ++i)                                               \
+            if (full || c0 + i < cols) row[c0 + i] = CONV(v[4 * g + i]);                              \
+        }                                                                                             \
+      }                                                                                               \
+    } else {                                                                                          \
+      _Pragma("unroll") for (int e = 0; e < kV; ++e)                                                  \
+        if (full || row_col<kV>(e) < cols) row[row_col<kV>(e)] = CONV(v[e]);                          \
+    }                                                                                                 \
   }
   switch (type) {
     case T_F16: ASC_ROW_STORE(__half, __float2half_rn) break;
@@ -672,7 +724,7 @@ __global__ void __launch_bounds__(kThreads) row_program_kernel(const __grid_cons
     if (full) {                                                                                    \
       ASC_LANES v = row_combine(CODE, v, top[e]);                                                  \
     } else {                                                                                       \
-      ASC_LANES if (threadIdx.x + e * kThreads < cols) v = row_combine(CODE, v, top[e]);           \
+      ASC_LANES if (row_col<kV>(e) < cols) v = row_combine(CODE, v, top[e]);                     \
     }                                                                                              \
     _Pragma("unroll") for (int o = 16; o > 0; o >>= 1) v = row_combine(CODE, v, __shfl_xor_sync(0xffffffffu, v, o)); \
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;                                        \
@@ -709,7 +761,7 @@ __global__ void __launch_bounds__(kThreads) row_program_kernel(const __grid_cons
           break;
         case OP_INDEX:
           ASC_PUSH(false)
-          ASC_LANES top[e] = __int_as_float(static_cast<int>(r * cols + threadIdx.x + e * kThreads));
+          ASC_LANES top[e] = __int_as_float(static_cast<int>(r * cols + row_col<kV>(e)));
           break;
         case OP_WHERE: {
           float c[kV];
@@ -802,7 +854,7 @@ struct RowStep {
         RowStep<P, kV, K + 1, D + 1, U | (1u << D), TU>::run(prog, r, cols, full, row_result, st, tmp, red);
       } else if constexpr (op == OP_INDEX) {
 #pragma unroll
-        for (int e = 0; e < kV; ++e) st[D][e] = __int_as_float(static_cast<int>(r * cols + threadIdx.x + e * kThreads));
+        for (int e = 0; e < kV; ++e) st[D][e] = __int_as_float(static_cast<int>(r * cols + row_col<kV>(e)));
         RowStep<P, kV, K + 1, D + 1, U & ~(1u << D), TU>::run(prog, r, cols, full, row_result, st, tmp, red);
       } else if constexpr (is_binary_op(op) && imm) {
         const float w = __int_as_float(prog.arg[K]);
@@ -841,7 +893,7 @@ struct RowStep {
         } else {
 #pragma unroll
           for (int e = 0; e < kV; ++e)
-            if (threadIdx.x + e * kThreads < cols) v = row_combine(op, v, st[D - 1][e]);
+            if (row_col<kV>(e) < cols) v = row_combine(op, v, st[D - 1][e]);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) v = row_combine(op, v, __shfl_xor_sync(0xffffffffu, v, o));
