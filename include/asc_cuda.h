@@ -201,6 +201,12 @@ int32_t asc_cuda_register_program(int32_t kind, const int32_t* words, int32_t n_
  * as exercised by python/test/asc2/operations/test_reduce_ops.py:17-104. */
 int32_t asc_cuda_reduce_f32(const float* x, float* out, int64_t rows, int64_t cols, int64_t ld, int32_t axis,
                             int32_t kind, int64_t n_fill, void* stream);
+/* The whole-window form (axis -1 above) for fp16 (dtype 0) or bf16 (dtype 1) windows: combined in fp32, rounded once,
+ * out[0 .. n_fill) all receive the result.  asc2.reduce_*(tile) without dimensions on a 16-bit tile
+ * (ReduceAs1dOp, lib/Conversion/LowerToAsc/LowerAscTile.cpp:427-458).  Along one axis 16-bit tiles go through
+ * asc_cuda_row_program / asc_cuda_col_program. */
+int32_t asc_cuda_reduce_all_f16(const void* x, void* out, int64_t rows, int64_t cols, int64_t ld, int32_t kind,
+                                int64_t n_fill, int32_t dtype, void* stream);
 
 /* Row softmax over the last dimension of a contiguous [rows, cols] fp32 matrix with max
  * subtraction.  `ld` is the row pitch in elements (>= cols).  Replaces both asc2 softmax forms:

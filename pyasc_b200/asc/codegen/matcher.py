@@ -1272,8 +1272,9 @@ def _match_reduce(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     view = resolve_view(src) if _node(src, "load") or _node(src, "copy") else None
     if view is None:
         raise _unsupported("reduction of a tile that is not loaded from global memory")
-    if src.dtype != KT.float32 or out_t.dtype != KT.float32 or view.tensor.dtype != KT.float32:
-        raise _unsupported(f"reduction of {src.dtype} tiles (float32 only)")
+    dtype = src.dtype
+    if dtype not in (KT.float32, KT.float16, KT.bfloat16) or out_t.dtype != dtype or view.tensor.dtype != dtype:
+        raise _unsupported(f"reduction of {src.dtype} tiles (float32 only; float16 and bfloat16 along one axis or of a whole tile)")
     if len(view.shape) > 2:
         raise _unsupported("reduction of a tile of rank > 2")
     _check_fits(out_t)
@@ -1292,6 +1293,8 @@ def _match_reduce(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         n_out = t_rows if axis == 1 else t_cols
     if value.size != n_out:
         return None
+    if dtype != KT.float32 and axis != -1:        # (loaded 16-bit tiles along an axis are row / column programs)
+        raise _unsupported(f"reduction of {src.dtype} tiles along an axis in this form")
     window = _flat_window(out_t, offsets, value.shape)
     if window is None:
         raise _unsupported("reduction whose result is not stored as one contiguous range")
@@ -1337,13 +1340,23 @@ def _match_reduce(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         plan.partial_writes.add(out_idx)
     kind = _REDUCE_KIND[node.attrs["kind"]]
 
+    esize = dtype.bitwidth // 8
+
     def make_step(r0: int, c0: int, o0: int, rows: int) -> Step:
+        note = (f"{node.attrs['kind']} axis {axis} of [{rows}, {t_cols}] at ({r0}, {c0}) -> "
+                f"[{o0}, +{rows if axis == 1 else n_out})")
+        if dtype != KT.float32:          # a whole 16-bit tile: fp32 combination, one rounding
+            def build16(ptrs, stream):
+                return (_p(ptrs[x_idx] + esize * (r0 * x_cols + c0)), _p(ptrs[out_idx] + esize * o0), ctypes.c_int64(rows),
+                        ctypes.c_int64(t_cols), ctypes.c_int64(x_cols), ctypes.c_int32(kind), ctypes.c_int64(n_fill or 1),
+                        ctypes.c_int32(1 if dtype == KT.bfloat16 else 0), stream)
+            return Step("asc_cuda_reduce_all_f16", build16, note)
+
         def build(ptrs, stream):
             return (_p(ptrs[x_idx] + 4 * (r0 * x_cols + c0)), _p(ptrs[out_idx] + 4 * o0), ctypes.c_int64(rows),
                     ctypes.c_int64(t_cols), ctypes.c_int64(x_cols), ctypes.c_int32(axis), ctypes.c_int32(kind),
                     ctypes.c_int64(n_fill or 1), stream)
-        return Step("asc_cuda_reduce_f32", build, f"{node.attrs['kind']} axis {axis} of [{rows}, {t_cols}] at "
-                                                   f"({r0}, {c0}) -> [{o0}, +{rows if axis == 1 else n_out})")
+        return Step("asc_cuda_reduce_f32", build, note)
 
     for r0, c0, o0, rows in merged:
         plan.steps.append(make_step(r0, c0, o0, rows))

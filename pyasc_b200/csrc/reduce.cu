@@ -9,6 +9,9 @@
 // addresses; the full reduction of one window runs in a single CTA.
 #include <cfloat>
 
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+
 #include "../../include/asc_cuda.h"
 #include "host_common.h"
 
@@ -116,13 +119,20 @@ __global__ void __launch_bounds__(256) reduce_cols_kernel(const float* __restric
 }
 
 // everything: out[0 .. n_fill) = reduce of the whole window (one CTA: windows are on-chip sized)
-template <int kKind>
-__global__ void __launch_bounds__(1024) reduce_all_kernel(const float* __restrict__ x, float* __restrict__ out,
+__device__ __forceinline__ float widen(float v) { return v; }
+__device__ __forceinline__ float widen(__half v) { return __half2float(v); }
+__device__ __forceinline__ float widen(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ void narrow(float v, float& out) { out = v; }
+__device__ __forceinline__ void narrow(float v, __half& out) { out = __float2half_rn(v); }
+__device__ __forceinline__ void narrow(float v, __nv_bfloat16& out) { out = __float2bfloat16_rn(v); }
+
+template <int kKind, typename T>
+__global__ void __launch_bounds__(1024) reduce_all_kernel(const T* __restrict__ x, T* __restrict__ out,
                                                           int64_t rows, int64_t cols, int64_t ld, int64_t n_fill) {
   __shared__ float part[32];
   float v = identity<kKind>();
   const int64_t n = rows * cols;
-  for (int64_t i = threadIdx.x; i < n; i += 1024) v = combine<kKind>(v, x[(i / cols) * ld + (i % cols)]);
+  for (int64_t i = threadIdx.x; i < n; i += 1024) v = combine<kKind>(v, widen(x[(i / cols) * ld + (i % cols)]));
   v = warp_combine<kKind>(v);
   if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
   __syncthreads();
@@ -131,7 +141,8 @@ __global__ void __launch_bounds__(1024) reduce_all_kernel(const float* __restric
     if (threadIdx.x == 0) part[0] = t;
   }
   __syncthreads();
-  const float result = part[0];
+  T result;
+  narrow(part[0], result);       // 16-bit tiles: combined in fp32, rounded once
   for (int64_t i = threadIdx.x; i < n_fill; i += 1024) out[i] = result;
 }
 
@@ -159,7 +170,23 @@ int32_t launch_reduce(const float* x, float* out, int64_t rows, int64_t cols, in
     if (grid > static_cast<int64_t>(sms) * 16) grid = static_cast<int64_t>(sms) * 16;
     reduce_cols_kernel<kKind><<<static_cast<unsigned>(grid), 256, 0, stream>>>(x, out, rows, cols, ld);
   } else {
-    reduce_all_kernel<kKind><<<1, 1024, 0, stream>>>(x, out, rows, cols, ld, n_fill);
+    reduce_all_kernel<kKind, float><<<1, 1024, 0, stream>>>(x, out, rows, cols, ld, n_fill);
+  }
+  aschost::count_launch();
+  ASC_CUDA_TRY(cudaGetLastError());
+  return ASC_OK;
+}
+
+template <typename T>
+int32_t launch_reduce_all_16(const void* x, void* out, int64_t rows, int64_t cols, int64_t ld, int32_t kind, int64_t n_fill,
+                             cudaStream_t stream) {
+  const T* xi = static_cast<const T*>(x);
+  T* oi = static_cast<T*>(out);
+  switch (kind) {
+    case R_SUM: reduce_all_kernel<R_SUM, T><<<1, 1024, 0, stream>>>(xi, oi, rows, cols, ld, n_fill); break;
+    case R_MAX: reduce_all_kernel<R_MAX, T><<<1, 1024, 0, stream>>>(xi, oi, rows, cols, ld, n_fill); break;
+    case R_MIN: reduce_all_kernel<R_MIN, T><<<1, 1024, 0, stream>>>(xi, oi, rows, cols, ld, n_fill); break;
+    default: reduce_all_kernel<R_PROD, T><<<1, 1024, 0, stream>>>(xi, oi, rows, cols, ld, n_fill); break;
   }
   aschost::count_launch();
   ASC_CUDA_TRY(cudaGetLastError());
@@ -167,6 +194,19 @@ int32_t launch_reduce(const float* x, float* out, int64_t rows, int64_t cols, in
 }
 
 }  // namespace
+
+extern "C" int32_t asc_cuda_reduce_all_f16(const void* x, void* out, int64_t rows, int64_t cols, int64_t ld, int32_t kind,
+                                           int64_t n_fill, int32_t dtype, void* stream) {
+  if (rows < 0 || cols < 0 || ld < cols || kind < 0 || kind > 3 || n_fill < 0 || dtype < 0 || dtype > 1)
+    return ASC_ERR_INVALID_ARG;
+  if (n_fill == 0) return ASC_OK;
+  if (out == nullptr || (x == nullptr && rows * cols > 0)) return ASC_ERR_INVALID_ARG;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) & 1) return ASC_ERR_MISALIGNED;
+  if (rows * cols > (int64_t{1} << 24)) return ASC_ERR_TOO_LARGE;  // one CTA reduces the window
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return dtype == 1 ? launch_reduce_all_16<__nv_bfloat16>(x, out, rows, cols, ld, kind, n_fill, s)
+                    : launch_reduce_all_16<__half>(x, out, rows, cols, ld, kind, n_fill, s);
+}
 
 extern "C" int32_t asc_cuda_reduce_f32(const float* x, float* out, int64_t rows, int64_t cols, int64_t ld,
                                        int32_t axis, int32_t kind, int64_t n_fill, void* stream) {

@@ -167,3 +167,44 @@ def test_half_precision_row_reductions_through_asc2(op, torch_op, dtype):
     else:
         tol = 2e-3 if dtype == torch.float16 else 1.6e-2
         torch.testing.assert_close(out.float(), want.float(), rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=str)
+@pytest.mark.parametrize("op, torch_op", [(asc2.reduce_sum, torch.sum), (asc2.reduce_max, torch.amax),
+                                          (asc2.reduce_min, torch.amin), (asc2.reduce_prod, torch.prod)],
+                         ids=lambda v: getattr(v, "__name__", ""))
+def test_whole_tile_reductions_of_half_precision_tiles(op, torch_op, dtype, lib):
+    """asc2.reduce_*(tile) without dimensions on a 16-bit tile, stored through asc2.full (the reference's
+    test_reduce_all body, python/test/asc2/operations/test_reduce_ops.py, with a 16-bit dtype)."""
+    import asc2_scripts as K
+    gen = torch.Generator().manual_seed(21)
+    x = torch.randn(32, 32, generator=gen)
+    if op is asc2.reduce_prod:
+        x = 1.0 + x * 0.02
+    x = x.to(dtype)
+    out = torch.zeros(32, dtype=dtype)
+    K.reduce_all[1](x, out, [32, 32], [0, 0], [32], [0], op)
+    want = torch_op(x.float()).to(dtype)
+    if op in (asc2.reduce_max, asc2.reduce_min):
+        assert torch.equal(out, want.expand(32))
+    else:
+        tol = 2e-3 if dtype == torch.float16 else 1.6e-2
+        torch.testing.assert_close(out.float(), want.float().expand(32), rtol=tol, atol=tol)
+    # the C ABI directly: a window inside a wider matrix, NaN propagation of max, rejections
+    xd = torch.randn(40, 72, generator=gen).to(dtype).cuda()
+    od = torch.full((9, ), 7.0, dtype=dtype, device="cuda")
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    dt = 1 if dtype == torch.bfloat16 else 0
+    assert lib.asc_cuda_reduce_all_f16(P(xd), P(od), 40, 64, 72, 0, 8, dt, None) == 0
+    capi.check_device_status(None)
+    want = xd[:, :64].float().sum().to(dtype)
+    tol = 4e-3 if dtype == torch.float16 else 3e-2
+    torch.testing.assert_close(od[:8].float().cpu(), want.float().cpu().expand(8), rtol=tol, atol=tol)
+    assert od[8].item() == 7.0
+    xd[3, 5] = float("nan")
+    assert lib.asc_cuda_reduce_all_f16(P(xd), P(od), 40, 64, 72, 1, 1, dt, None) == 0
+    assert bool(od[0].isnan())
+    assert lib.asc_cuda_reduce_all_f16(P(xd), P(od), 40, 64, 72, 0, 0, dt, None) == 0        # nothing to fill
+    assert lib.asc_cuda_reduce_all_f16(P(xd), P(od), 40, 64, 63, 0, 1, dt, None) == 1        # pitch shorter than a row
+    assert lib.asc_cuda_reduce_all_f16(P(xd), P(od), 40, 64, 72, 0, 1, 2, None) == 1         # unknown element type
+    assert lib.asc_cuda_reduce_all_f16(P(xd), P(od), 1 << 13, 1 << 12, 1 << 12, 0, 1, dt, None) == 6   # larger than a tile

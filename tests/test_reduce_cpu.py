@@ -67,7 +67,10 @@ def test_reduction_rejections():
     K.reduce_axis[1](x.half(), torch.zeros(32, dtype=torch.float16), 0, [64, 32], [0, 0], [32], [0], asc2.reduce_sum,
                      False)
     assert step_of(K.reduce_axis)[0].pattern == "reduce:sum:columns"
-    # ... integer tiles have no reduction kernel
+    # ... a whole fp16 tile has the 16-bit form of the whole-window kernel ...
+    K.reduce_all[1](x.half(), torch.zeros(32, dtype=torch.float16), [64, 32], [0, 0], [32], [0], asc2.reduce_max)
+    assert step_of(K.reduce_all)[1].fn_name == "asc_cuda_reduce_all_f16"
+    # ... integer tiles have no reduction kernel (nor has the reference: Ascend C reduces half and float)
     with pytest.raises(NotImplementedError, match="float32 only"):
         K.reduce_axis[1](x.int(), torch.zeros(32, dtype=torch.int32), 0, [64, 32], [0, 0], [32], [0], asc2.reduce_sum,
                          False)
