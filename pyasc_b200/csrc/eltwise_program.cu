@@ -379,6 +379,28 @@ extern "C" int32_t asc_cuda_row_program(const int32_t* ops, const int32_t* args,
 
 // out[c] = reduce_kind over the rows r of program(r, c) for a [rows, cols] window; kind: 0 sum, 1 max, 2 min,
 // 3 product.  lds: row pitch of every input (0: one row that every window row reads); NULL: all pitches equal cols.
+namespace {
+// ---- executor 5: an elementwise program reduced along the columns of its window ----
+// out[c] = reduce over r of program(r, c) for a [rows, cols] window: a thread owns a column and walks its rows,
+// evaluating the program per element in the interpreter (consecutive threads read consecutive columns, so every
+// access of a warp is one contiguous run) and combining as it goes.  Made for the tile-sized windows of
+// asc2.reduce_*(expression, 0); the grid covers the columns, not the rows.
+__global__ void __launch_bounds__(kThreads) col_program_kernel(const __grid_constant__ EltProgram prog, uint32_t rows,
+                                                               int row_op) {
+  extern __shared__ __align__(16) float stack_mem[];
+  const uint32_t cols = prog.cols;
+  for (uint32_t c = blockIdx.x * kThreads + threadIdx.x; c < cols; c += gridDim.x * kThreads) {
+    float acc = row_identity(row_op);
+    for (uint32_t r = 0; r < rows; ++r) {
+      float v[1];
+      Interpreter::eval<1>(prog, static_cast<int64_t>(r) * cols + c, stack_mem, v);
+      acc = row_combine(row_op, acc, v[0]);
+    }
+    store_elem(prog.out, prog.out_type, c, acc);
+  }
+}
+}  // namespace
+
 extern "C" int32_t asc_cuda_col_program(const int32_t* ops, const int32_t* args, int32_t n_ops, const void* const* inputs,
                                         const int32_t* input_types, int32_t n_inputs, void* out, int32_t out_type,
                                         int64_t rows, int64_t cols, const int64_t* lds, int32_t kind, void* stream) {

@@ -944,26 +944,6 @@ __global__ void __launch_bounds__(kThreads) row_compiled_kernel(const __grid_con
   }
 }
 
-// ---- executor 5: an elementwise program reduced along the columns of its window ----
-// out[c] = reduce over r of program(r, c) for a [rows, cols] window: a thread owns a column and walks its rows,
-// evaluating the program per element in the interpreter (consecutive threads read consecutive columns, so every
-// access of a warp is one contiguous run) and combining as it goes.  Made for the tile-sized windows of
-// asc2.reduce_*(expression, 0); the grid covers the columns, not the rows.
-__global__ void __launch_bounds__(kThreads) col_program_kernel(const __grid_constant__ EltProgram prog, uint32_t rows,
-                                                               int row_op) {
-  extern __shared__ __align__(16) float stack_mem[];
-  const uint32_t cols = prog.cols;
-  for (uint32_t c = blockIdx.x * kThreads + threadIdx.x; c < cols; c += gridDim.x * kThreads) {
-    float acc = row_identity(row_op);
-    for (uint32_t r = 0; r < rows; ++r) {
-      float v[1];
-      Interpreter::eval<1>(prog, static_cast<int64_t>(r) * cols + c, stack_mem, v);
-      acc = row_combine(row_op, acc, v[0]);
-    }
-    store_elem(prog.out, prog.out_type, c, acc);
-  }
-}
-
 // ---- launch helpers of the generated translation units (CUDA runtime calls only) ----
 // Grid sizing as for the kernels built into the library: four waves of resident CTAs (one for small launches), CTAs
 // stride beyond.
