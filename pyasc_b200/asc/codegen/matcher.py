@@ -786,7 +786,7 @@ def _check_program_limits(prog: "_EltProgram") -> None:
 
 def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", out_t: Tensor,
                           offsets: Sequence[PlainValue], out_shape: Tuple[int, ...], scalar_store: bool,
-                          in_place_operand: Optional[int], dedupe: bool,
+                          dedupe: bool,
                           row_shape: Optional[Tuple[int, int]] = None, row_result: bool = False) -> Plan:
     """Operands addressed differently from the result (other tensor shapes or offsets, reshapes, a broadcast row,
     an accumulation into a fixed window): one call per (block, iteration) instance, in program order."""
@@ -845,7 +845,12 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
     in_size = [o.tensor.dtype.bitwidth // 8 for o in prog.operands]
     out_size = out_t.dtype.bitwidth // 8
     for k, (i, g) in enumerate(zip(in_idx, geoms)):
-        if i == out_idx and not (k == in_place_operand and lds[k] == lds[-1] and np.array_equal(g.start, out_g.start)):
+        # An operand taken from the tensor that is stored to must be the stored window itself, element for element:
+        # a thread then reads exactly what it overwrites (`y = x + y` in place, the target of an atomic).
+        o = prog.operands[k]
+        same_window = (not o.bcast and not o.per_row and not prog.reshaped and lds[k] == lds[-1]
+                       and np.array_equal(g.start, out_g.start))
+        if i == out_idx and not same_window:
             raise _unsupported("elementwise kernel that stores into a tensor it also loads at other positions")
     plan = Plan("row:program" if row_shape is not None else "elementwise:program")
     plan.reads.update(in_idx)
@@ -941,10 +946,10 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         rows = 1
         for d in out_shape[:-1]:
             rows *= d
-        return _plan_general_program(trace, eff, prog, out_t, offsets, out_shape, False, None, dedupe=True,
+        return _plan_general_program(trace, eff, prog, out_t, offsets, out_shape, False, dedupe=True,
                                      row_shape=(rows, out_shape[-1]))
     if not aligned or not prog.operands:
-        return _plan_general_program(trace, eff, prog, out_t, offsets, out_shape, scalar_store, None, dedupe=True)
+        return _plan_general_program(trace, eff, prog, out_t, offsets, out_shape, scalar_store, dedupe=True)
     numel = 1
     for d in tshape:
         numel *= d
@@ -1046,7 +1051,7 @@ def _match_atomic(trace: KernelTrace, eff: Effect) -> Plan:
     _check_fits(out_t)
     for t in prog.inputs:
         _check_fits(t)
-    plan = _plan_general_program(trace, eff, prog, out_t, offsets, value.shape, False, 0, dedupe=False)
+    plan = _plan_general_program(trace, eff, prog, out_t, offsets, value.shape, False, dedupe=False)
     plan.pattern = f"atomic:{eff.attrs['kind']}"
     return plan
 
@@ -1104,7 +1109,7 @@ def _match_row_result(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     _check_fits(out_t)
     for t in prog.inputs:
         _check_fits(t)
-    return _plan_general_program(trace, eff, prog, out_t, offsets, value.shape, False, None, dedupe=True,
+    return _plan_general_program(trace, eff, prog, out_t, offsets, value.shape, False, dedupe=True,
                                  row_shape=(full_shape[0], full_shape[1]), row_result=True)
 
 
@@ -1158,7 +1163,7 @@ def _match_row_scalar(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     _check_fits(out_t)
     for t in prog.inputs:
         _check_fits(t)
-    return _plan_general_program(trace, eff, prog, out_t, offsets, (1, ), True, None, dedupe=True,
+    return _plan_general_program(trace, eff, prog, out_t, offsets, (1, ), True, dedupe=True,
                                  row_shape=(1, src.shape[-1]), row_result=True)
 
 

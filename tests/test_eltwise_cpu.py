@@ -298,3 +298,32 @@ def test_count_mask_plans_one_call_per_tile_with_the_element_index(monkeypatch):
             with asc2.mask(bits=(0, 255)):
                 asc2.store(x + 1, asc2.tensor(x_ptr, [n]), offsets=[0])
         bit_mask[1](torch.zeros(64), 64)
+
+
+def test_in_place_update_of_the_stored_window_plans_and_other_positions_are_refused():
+    """`y = x + y` through scalar-sized tiles, as in the reference's loop-unrolling note
+    (docs/design/software-pipelining.md:55-66): the operand taken from the stored tensor is the stored window
+    itself, so each element is read by the thread that overwrites it.  Shifted by one element it is refused."""
+    @asc2.jit()
+    def accumulate(x, y, size: int):
+        x_gm = asc2.tensor(x, [size])
+        y_gm = asc2.tensor(y, [size])
+        for i in asc2.range(size, unroll_factor=2, parallel=True):
+            x_val = asc2.load(x_gm, [1], offsets=[i])
+            y_val = asc2.load(y_gm, [1], offsets=[i])
+            asc2.store(x_val + y_val, y_gm, offsets=[i])
+
+    accumulate[1](torch.zeros(64), torch.zeros(64), 64)
+    plan = accumulate.last_plan
+    assert plan.pattern == "elementwise:program" and plan.reads == {0, 1} and plan.writes == {1}
+    assert len(plan.steps) == 1 and plan.pipeline is None            # the 64 one-element windows merge into one call
+
+    @asc2.jit
+    def shifted(x, y, size: int):
+        x_gm = asc2.tensor(x, [size])
+        y_gm = asc2.tensor(y, [size])
+        for i in asc2.range(size - 1):
+            asc2.store(asc2.load(x_gm, [1], offsets=[i]) + asc2.load(y_gm, [1], offsets=[i + 1]), y_gm, offsets=[i])
+
+    with pytest.raises(NotImplementedError, match="other positions"):
+        shifted[1](torch.zeros(64), torch.zeros(64), 64)

@@ -10,7 +10,9 @@ import numpy as np
 import pytest
 import torch
 
+import asc
 import asc.runtime.config as config
+import asc2
 
 import asc2_scripts as K
 import eltwise_cases as C
@@ -396,3 +398,38 @@ def test_programs_built_at_first_use_equal_the_interpreter(lib, name, dtype, out
                        plain.view(torch.int16 if dtype != torch.float32 else torch.int32))
     want = E.run_program(ops, args, [t.cpu() for t in ins], out_type)
     torch.testing.assert_close(fast.cpu().float(), want.float(), rtol=2e-3, atol=1e-5, equal_nan=True)
+
+
+def test_in_place_updates_through_asc2():
+    """An operand taken from the stored tensor at the stored window: `y = x + y` with scalar-sized tiles (the
+    reference's docs/design/software-pipelining.md:55-66) and a 2-D tile scaled in place by a broadcast row."""
+    @asc2.jit()
+    def accumulate(x, y, size: int):
+        x_gm = asc2.tensor(x, [size])
+        y_gm = asc2.tensor(y, [size])
+        for i in asc2.range(size, unroll_factor=2, parallel=True):
+            x_val = asc2.load(x_gm, [1], offsets=[i])
+            y_val = asc2.load(y_gm, [1], offsets=[i])
+            asc2.store(x_val + y_val, y_gm, offsets=[i])
+
+    gen = torch.Generator().manual_seed(31)
+    x, y = torch.randn(64, generator=gen), torch.randn(64, generator=gen)
+    want = x + y
+    accumulate[1](x, y, 64)
+    assert torch.equal(y, want)
+
+    @asc2.jit
+    def scale_rows(m_ptr: asc.GlobalAddress, w_ptr: asc.GlobalAddress, rows: int, cols: asc.ConstExpr[int],
+                   rpt: asc.ConstExpr[int]):
+        m_gm = asc2.tensor(m_ptr, [rows, cols])
+        w = asc2.load(asc2.tensor(w_ptr, [1, cols]), [1, cols], offsets=[0, 0])
+        for r in range(asc2.block_idx() * rpt, rows, asc2.block_num() * rpt):
+            m = asc2.load(m_gm, [rpt, cols], offsets=[r, 0])
+            asc2.store(m * w.broadcast_to(rpt, cols) + 1.0, m_gm, offsets=[r, 0])
+
+    m, w = torch.randn(256, 512, generator=gen), torch.randn(1, 512, generator=gen)
+    want = m * w + 1.0
+    md = m.cuda()
+    scale_rows[8](md, w.cuda(), 256, 512, 8)
+    torch.cuda.synchronize()
+    assert torch.equal(md.cpu(), want)
