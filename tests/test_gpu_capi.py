@@ -271,6 +271,9 @@ def test_gemm_f16_full_size(lib):
     # checksum of checksums: (1^T A) B == 1^T C  up to fp16 rounding of C
     col_sum = (ad.float().sum(0, keepdim=True) @ bd.float()).squeeze(0)
     torch.testing.assert_close(c.float().sum(0), col_sum, atol=5e-3, rtol=5e-3)
+    # every element: a second, independent implementation (torch.matmul on the GPU) as cross-check; the CPU oracle
+    # above stays the reference for the sampled rows
+    torch.testing.assert_close(c, torch.matmul(ad, bd), atol=2e-3, rtol=2e-3)
 
 
 # ----------------------------------------------------------------------------------------- int8 GEMM
@@ -344,6 +347,11 @@ def test_gemm_i8_full_size_bit_exact(lib):
     lhs = acc.to(torch.int64).sum(0)
     rhs = (ad.to(torch.float64).sum(0, keepdim=True) @ bd.to(torch.float64)).squeeze(0).to(torch.int64)
     assert torch.equal(lhs, rhs)
+    # every element, exactly: the product in float64 on the GPU (all integers involved are far below 2^53) as a
+    # second, independent implementation; the CPU oracle above stays the reference for the sampled rows
+    for r0 in range(0, m, 2048):
+        full = (ad[r0:r0 + 2048].to(torch.float64) @ bd.to(torch.float64)).to(torch.int32)
+        assert torch.equal(acc[r0:r0 + 2048], full)
 
 
 # ----------------------------------------------------------------------------------------- attention
@@ -394,6 +402,11 @@ def test_attention_properties_full_size(lib):
             G.assert_half_close(o[bi:bi + 1, hi:hi + 1], ref)
         if causal:   # row 0 sees key 0 only
             assert torch.equal(o[:, :, 0], vd[:, :, 0])
+        # every (batch, head): a second, independent implementation (torch's fused attention on the GPU, fp32
+        # inputs) as cross-check; the CPU oracle above stays the reference for the sampled heads
+        sdpa = torch.nn.functional.scaled_dot_product_attention(qd.float(), kd.float(), vd.float(), is_causal=causal)
+        torch.testing.assert_close(o.float(), sdpa, atol=2e-3, rtol=2e-3)
+        del sdpa
     # with V == 1 every output is exactly 1 (softmax rows sum to one)
     ones = torch.ones_like(vd)
     o = attn(lib, qd, kd, ones, False)
