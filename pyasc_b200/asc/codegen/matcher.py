@@ -413,6 +413,11 @@ class _Operand:
                 and _same_offsets(self.offsets, offsets))
 
 
+# Values that are read back from a temporary device buffer instead of being compiled into the program: node id ->
+# the operand to load.  Filled only while _match_matmul_then_program plans the expression around a matmul.
+_MATERIALISED: Dict[int, "_Operand"] = {}
+
+
 class _EltProgram:
     """Compiles the expression tree of a stored tile into a postfix program.  Scalar operands become
     immediates; of two tile operands the one needing the deeper stack is evaluated first (with the
@@ -529,6 +534,8 @@ class _EltProgram:
             return self._row_reduction(node, v.dtype)
         if v.shape != self.shape:
             return None
+        if id(node) in _MATERIALISED:       # a value another kernel has written to a temporary (a matmul result)
+            return self._load(_MATERIALISED[id(node)])
         if node.kind == "iota":
             if self.full_shape is not None:
                 return None
@@ -1884,6 +1891,67 @@ def _match_matmul(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     return plan
 
 
+def _matmul_leaves(value: Any, limit: int = 4096) -> List[Tile]:
+    """The matmul results (``matmul`` / ``matmul_acc`` accumulators) an expression is computed from."""
+    found: List[Tile] = []
+    seen = set()
+    stack = [value]
+    while stack and len(seen) < limit:
+        v = stack.pop()
+        if isinstance(v, Tile):
+            if id(v.node) in seen:
+                continue
+            seen.add(id(v.node))
+            if v.node.kind in ("matmul", "acc"):
+                found.append(v)
+                continue
+            stack.extend(v.node.args)
+            stack.extend(a for a in v.node.attrs.values() if isinstance(a, (Tile, PlainValue)))
+        elif isinstance(v, PlainValue) and v.op not in ("const", "sym"):
+            stack.extend(a for a in v.args if isinstance(a, (Tile, PlainValue)))
+    return found
+
+
+def _match_matmul_then_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
+    """``store(f(a @ b, other tiles...))`` with an elementwise ``f`` the matmul epilogues do not cover (a bias row,
+    an activation, a residual): the product goes to a temporary matrix of the result's shape, then one elementwise
+    program reads it back together with the other operands.  The reference fuses such an expression on chip between
+    the cube unit's output buffer and the vector unit (MatmulOp + vector calls, lib/Conversion/LowerToAsc/
+    LowerAscTile.cpp); here it costs one extra pass over the fp32 product."""
+    value, out_t = eff.args
+    if eff.kind != "store" or not isinstance(value, Tile) or len(value.shape) != 2 or value.node.kind in ("matmul", "acc"):
+        return None
+    leaves = _matmul_leaves(value)
+    if not leaves:
+        return None
+    if len(leaves) != 1:
+        raise _unsupported("expression that combines several matmul results")
+    mm = leaves[0]
+    if mm.shape != value.shape or len(out_t.static_shape()) != 2:
+        raise _unsupported("matmul result reshaped or stored to a tensor that is not 2-D before its elementwise epilogue")
+    offsets = eff.attrs["offsets"]
+    plan = Plan("matmul+program")
+    key = f"tmp{len(plan.temps)}"
+    rows, cols = out_t.static_shape()
+    tmp = _fake_tensor(key, (rows, cols), mm.dtype)
+    plan.temps[key] = rows * cols * mm.dtype.sizeof()
+    if not _plan_matmul_value(trace, mm, tmp, offsets, eff.loops, plan, eff.guards):
+        return None
+    _MATERIALISED[id(mm.node)] = _Operand(tmp, offsets, mm.shape)
+    try:
+        tail = _match_eltwise_program(trace, eff)
+    finally:
+        _MATERIALISED.clear()
+    if tail is None:
+        raise _unsupported("expression around a matmul result that is not elementwise")
+    tail.reads.discard(key)
+    plan.steps.extend(tail.steps)
+    plan.reads.update(tail.reads)
+    plan.writes.update(tail.writes)
+    plan.partial_writes.update(tail.partial_writes)
+    return plan
+
+
 # --------------------------------------------------------------------------------------------------
 # Pattern: attention forward, written per query tile as softmax(scale * Q K^T [+ causal mask]) V
 # --------------------------------------------------------------------------------------------------
@@ -2084,7 +2152,8 @@ def _check_effect_order(trace: KernelTrace, first: Effect, second: Effect, cache
 # --------------------------------------------------------------------------------------------------
 # Entry point
 # --------------------------------------------------------------------------------------------------
-_MATCHERS = (_match_attention, _match_softmax, _match_rms_norm, _match_elementwise, _match_matmul, _match_eltwise_program,
+_MATCHERS = (_match_attention, _match_softmax, _match_rms_norm, _match_elementwise, _match_matmul,
+             _match_matmul_then_program, _match_eltwise_program,
              _match_row_result, _match_row_scalar, _match_col_reduce, _match_reduce)
 
 

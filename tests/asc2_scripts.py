@@ -110,6 +110,32 @@ def matmul_chained(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, c_ptr: as
     asc2.store(c_l0a @ b, c_gm, offsets=[0, 0])
 
 
+@asc2.jit(always_compile=True)
+def matmul_bias_act(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, bias_ptr: asc.GlobalAddress,
+                    res_ptr: asc.GlobalAddress, c_ptr: asc.GlobalAddress, m: int, n: asc.ConstExpr[int],
+                    k: asc.ConstExpr[int], m_tile: asc.ConstExpr[int], mode: asc.ConstExpr[int],
+                    out_dtype: asc.ConstExpr):
+    """A linear layer written the way a user of asc2 would: the product, a bias row, then an activation
+    (0: none, 1: ReLU, 2: leaky ReLU, 3: tanh-form GELU plus a residual tile), optionally cast for the store."""
+    a_gm, b_gm, c_gm = asc2.tensor(a_ptr, [m, k]), asc2.tensor(b_ptr, [k, n]), asc2.tensor(c_ptr, [m, n])
+    res_gm = asc2.tensor(res_ptr, [m, n])
+    bias = asc2.load(asc2.tensor(bias_ptr, [1, n]), [1, n], offsets=[0, 0])
+    for i in range(asc2.block_idx() * m_tile, m, asc2.block_num() * m_tile):
+        a = asc2.load(a_gm, [m_tile, k], offsets=[i, 0])
+        b = asc2.load(b_gm, [k, n], offsets=[0, 0])
+        t = asc2.matmul(a, b) + bias.broadcast_to(m_tile, n)
+        if mode == 1:
+            t = asc2.relu(t)
+        elif mode == 2:
+            t = asc2.where(t >= 0, t, t * 0.01)
+        elif mode == 3:
+            t = t - t / (asc2.exp(t * (t * t * 0.0713548162726 + 1.5957691216057308)) + 1)
+            t = t + asc2.load(res_gm, [m_tile, n], offsets=[i, 0])
+        if out_dtype != asc.float32:
+            t = t.to(out_dtype)
+        asc2.store(t, c_gm, offsets=[i, 0])
+
+
 def mn_tiles_per_block(m, n, core_num, m_tile, n_tile, n_tiles_per_block):
     """Host-side tile bookkeeping of the M/N-blocked kernel (even distribution over blocks)."""
     m_tiles, n_tiles = m // m_tile, n // n_tile

@@ -110,6 +110,30 @@ def test_matmul_fixpipe(m, k, n, dtype):
     torch.testing.assert_close(c, c_ref, atol=1e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize("out_dtype, torch_dtype", [(asc.float32, torch.float32), (asc.float16, torch.float16)], ids=str)
+@pytest.mark.parametrize("mode", [0, 1, 2, 3])
+@pytest.mark.parametrize("m, n, k, m_tile", [(512, 256, 128, 64), (2048, 1024, 2048, 128)])
+def test_matmul_bias_activation(m, n, k, m_tile, mode, out_dtype, torch_dtype):
+    """A product followed by a bias row and an activation (and a residual, and a cast): the GEMM writes fp32 to a
+    temporary, one elementwise program finishes the expression.  Golden: the same expression in torch on the CPU."""
+    gen = torch.Generator().manual_seed(m + mode)
+    a = ((torch.rand(m, k, generator=gen) - .5) * 2 * k ** -0.5).half()
+    b = (torch.rand(k, n, generator=gen) - .5).half()
+    bias = torch.randn(1, n, generator=gen)
+    res = torch.randn(m, n, generator=gen)
+    c = torch.zeros(m, n, dtype=torch_dtype)
+    K.matmul_bias_act[8](a, b, bias, res, c, m, n, k, m_tile, mode, out_dtype)
+    assert K.matmul_bias_act.last_plan.pattern == "matmul+program"
+    t = a.float() @ b.float() + bias
+    if mode == 1:
+        t = t.relu()
+    elif mode == 2:
+        t = torch.where(t >= 0, t, t * 0.01)
+    elif mode == 3:
+        t = t - t / (torch.exp(t * (t * t * 0.0713548162726 + 1.5957691216057308)) + 1) + res
+    torch.testing.assert_close(c, t.to(torch_dtype), atol=2e-3, rtol=2e-3)
+
+
 @pytest.mark.parametrize("m, k, n, torch_dtype, pyasc_dtype", [(32, 64, 64, torch.float16, asc.float16),
                                                               (64, 64, 64, torch.bfloat16, asc.bfloat16)])
 def test_matmul_l0c_to_l1(m, k, n, torch_dtype, pyasc_dtype):

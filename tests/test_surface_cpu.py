@@ -213,3 +213,31 @@ def test_config_backend_selection():
     if not torch.cuda.is_available():
         with pytest.raises(RuntimeError, match="not available"):
             config.set_platform("CUDA")
+
+
+def test_matmul_followed_by_an_elementwise_expression_plans_a_product_and_a_program(monkeypatch):
+    """bias + activation (+ residual, + cast) after a matmul is not one of the GEMM epilogues: the product goes to a
+    temporary fp32 matrix of the result's shape and one elementwise program reads it back."""
+    monkeypatch.setenv("DRY_RUN", "1")
+    import asc2_scripts as K
+    m, n, k = 512, 256, 128
+    a, b = torch.zeros(m, k, dtype=torch.float16), torch.zeros(k, n, dtype=torch.float16)
+    for mode, reads in ((0, {0, 1, 2}), (1, {0, 1, 2}), (2, {0, 1, 2}), (3, {0, 1, 2, 3})):
+        for out_dtype, torch_dtype in ((asc.float32, torch.float32), (asc.float16, torch.float16)):
+            K.matmul_bias_act[4](a, b, torch.zeros(1, n), torch.zeros(m, n), torch.zeros(m, n, dtype=torch_dtype), m, n, k, 64,
+                                 mode, out_dtype)
+            plan = K.matmul_bias_act.last_plan
+            assert plan.pattern == "matmul+program" and [s.fn_name for s in plan.steps] == \
+                ["asc_cuda_gemm_f16", "asc_cuda_eltwise_program_2d"]          # the eight row blocks merge in both
+            assert plan.reads == reads and plan.writes == {4} and not plan.partial_writes
+            assert plan.temps == {"tmp0": m * n * 4} and plan.pipeline is None
+    # two products in one expression would need two temporaries: refused
+    @asc2.jit
+    def two_products(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, c_ptr: asc.GlobalAddress):
+        a_gm, b_gm, c_gm = asc2.tensor(a_ptr, [64, 64]), asc2.tensor(b_ptr, [64, 64]), asc2.tensor(c_ptr, [64, 64])
+        x = asc2.load(a_gm, [64, 64], offsets=[0, 0])
+        y = asc2.load(b_gm, [64, 64], offsets=[0, 0])
+        asc2.store(asc2.matmul(x, y) + asc2.matmul(y, x), c_gm, offsets=[0, 0])
+    h = torch.zeros(64, 64, dtype=torch.float16)
+    with pytest.raises(NotImplementedError, match="several matmul results"):
+        two_products[1](h, h, torch.zeros(64, 64))
