@@ -1772,8 +1772,8 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
     if inst.size and inst.min() < 0:
         raise RuntimeError("Negative tile offset in kernel")
     ro, co, ar, ak, bk, bc = (inst[:, i] for i in range(6))
-    if np.any(ak != bk):
-        raise _unsupported("A and B operands read different K ranges")
+    # (A's K range starts at column ak, B's at row bk: equal when both index one K axis, different when B is a stack
+    # of matrices, as in a loop over a batch)
     if epi.row_scale is not None and (np.any(inst[:, 6] != ar) or np.any(inst[:, 7] != bc)
                                       or epi.row_scale.shape[0] != mt or epi.col_scale.shape[0] != nt):
         raise _unsupported("dequantisation scales that are not indexed by the tile's rows / columns")
@@ -1789,7 +1789,7 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
     # one call when the tiles form a full grid over a rectangle, else one call per tile
     calls: List[Tuple[int, ...]] = []   # (ro, co, ar, bc, k0, M, N, K)
     ru, cu = np.unique(ro[keep]), np.unique(co[keep])
-    grid_ok = (keep.all() and inst.shape[0] == ru.size * cu.size and np.all(ak == ak[0]) and
+    grid_ok = (keep.all() and inst.shape[0] == ru.size * cu.size and np.all(ak == ak[0]) and np.all(bk == bk[0]) and
                np.all(k_eff == k_eff[0]) and np.all(ar - ro == ar[0] - ro[0]) and np.all(bc - co == bc[0] - co[0]) and
                np.array_equal(ru, ru[0] + mt * np.arange(ru.size)) and
                np.array_equal(cu, cu[0] + nt * np.arange(cu.size)) and
@@ -1798,11 +1798,11 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
         M = int(min(ru[-1] + mt, c_rows) - ru[0])
         N = int(min(cu[-1] + nt, c_cols) - cu[0])
         calls.append((int(ru[0]), int(cu[0]), int(ru[0] + ar[0] - ro[0]), int(cu[0] + bc[0] - co[0]), int(ak[0]),
-                      M, N, int(k_eff[0])))
+                      M, N, int(k_eff[0]), int(bk[0])))
     else:
         for i in np.nonzero(keep)[0]:
             calls.append((int(ro[i]), int(co[i]), int(ar[i]), int(bc[i]), int(ak[i]), int(m_eff[i]), int(n_eff[i]),
-                          int(k_eff[i])))
+                          int(k_eff[i]), int(bk[i])))
         if len(calls) > MAX_CALLS:
             raise _unsupported("matmul kernel whose tiles do not form a grid and exceed 4096 calls")
         if calls:
@@ -1838,11 +1838,12 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
     else:
         raise _unsupported(f"matmul on {in_dtype} operands")
 
-    def gemm_step(r0: int, c0: int, a0: int, b0: int, k0: int, M: int, N: int, K: int) -> Step:
-        a_off, b_off, c_off = (a0 * lda + k0) * es, (k0 * ldb + b0) * es, (r0 * ldc + c0) * osz
+    def gemm_step(r0: int, c0: int, a0: int, b0: int, k0: int, M: int, N: int, K: int, kb: Optional[int] = None) -> Step:
+        kb = k0 if kb is None else kb         # first row of B's K range
+        a_off, b_off, c_off = (a0 * lda + k0) * es, (kb * ldb + b0) * es, (r0 * ldc + c0) * osz
         dims = (ctypes.c_int64(M), ctypes.c_int64(N), ctypes.c_int64(K), ctypes.c_int64(lda), ctypes.c_int64(ldb),
                 ctypes.c_int64(ldc))
-        note = f"C[{r0}:{r0 + M}, {c0}:{c0 + N}] = A[{a0}:, {k0}:{k0 + K}] @ B[{k0}:, {b0}:]"
+        note = f"C[{r0}:{r0 + M}, {c0}:{c0 + N}] = A[{a0}:, {k0}:{k0 + K}] @ B[{kb}:, {b0}:]"
         if in_dtype == KT.int8:
             if sa_idx is not None:
                 def build(ptrs, stream):
@@ -1870,9 +1871,9 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
         plan.steps.append(gemm_step(*call))
     # one full-output call whose operands are plain global tensors: rows of A and C can be streamed
     if (len(calls) == 1 and c_idx not in plan.partial_writes and calls[0][2] == 0 and calls[0][3] == 0 and
-            calls[0][4] == 0 and all(isinstance(i, int) for i in (a_idx, b_idx, c_idx)) and
+            calls[0][4] == 0 and calls[0][8] == 0 and all(isinstance(i, int) for i in (a_idx, b_idx, c_idx)) and
             len({a_idx, b_idx, c_idx}) == 3 and in_dtype != KT.float32):
-        _, _, _, _, _, M, N, K = calls[0]
+        _, _, _, _, _, M, N, K, _ = calls[0]
         streamed = {a_idx: lda * es, c_idx: ldc * osz}
         resident = {b_idx}
         if sa_idx is not None:

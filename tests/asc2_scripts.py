@@ -136,6 +136,17 @@ def matmul_bias_act(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, bias_ptr
         asc2.store(t, c_gm, offsets=[i, 0])
 
 
+@asc2.jit(always_compile=True)
+def matmul_batched(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, c_ptr: asc.GlobalAddress,
+                   batch: asc.ConstExpr[int], m: asc.ConstExpr[int], n: asc.ConstExpr[int], k: asc.ConstExpr[int]):
+    """A batch of independent products, one per loop iteration: A, B and C are stacks of matrices."""
+    a_gm, b_gm, c_gm = asc2.tensor(a_ptr, [batch * m, k]), asc2.tensor(b_ptr, [batch * k, n]), asc2.tensor(c_ptr, [batch * m, n])
+    for i in range(asc2.block_idx(), batch, asc2.block_num()):
+        a = asc2.load(a_gm, [m, k], offsets=[i * m, 0])
+        b = asc2.load(b_gm, [k, n], offsets=[i * k, 0])
+        asc2.store(asc2.matmul(a, b), c_gm, offsets=[i * m, 0])
+
+
 def mn_tiles_per_block(m, n, core_num, m_tile, n_tile, n_tiles_per_block):
     """Host-side tile bookkeeping of the M/N-blocked kernel (even distribution over blocks)."""
     m_tiles, n_tiles = m // m_tile, n // n_tile

@@ -110,6 +110,16 @@ def test_matmul_fixpipe(m, k, n, dtype):
     torch.testing.assert_close(c, c_ref, atol=1e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize("batch, m, n, k", [(8, 128, 256, 64), (5, 200, 144, 80), (3, 1024, 1024, 1024)])
+def test_matmul_batched_loop(batch, m, n, k):
+    gen = torch.Generator().manual_seed(batch * m)
+    a = ((torch.rand(batch, m, k, generator=gen) - .5) * 2 * k ** -0.5).half()
+    b = (torch.rand(batch, k, n, generator=gen) - .5).half()
+    c = torch.zeros(batch * m, n)
+    K.matmul_batched[4](a.reshape(batch * m, k), b.reshape(batch * k, n), c, batch, m, n, k)
+    torch.testing.assert_close(c.reshape(batch, m, n), torch.bmm(a.float(), b.float()), atol=2e-3, rtol=2e-3)
+
+
 @pytest.mark.parametrize("out_dtype, torch_dtype", [(asc.float32, torch.float32), (asc.float16, torch.float16)], ids=str)
 @pytest.mark.parametrize("mode", [0, 1, 2, 3])
 @pytest.mark.parametrize("m, n, k, m_tile", [(512, 256, 128, 64), (2048, 1024, 2048, 128)])

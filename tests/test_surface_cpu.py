@@ -241,3 +241,15 @@ def test_matmul_followed_by_an_elementwise_expression_plans_a_product_and_a_prog
     h = torch.zeros(64, 64, dtype=torch.float16)
     with pytest.raises(NotImplementedError, match="several matmul results"):
         two_products[1](h, h, torch.zeros(64, 64))
+
+
+def test_batched_matmul_loop_plans_one_product_per_matrix(monkeypatch):
+    """B stacked along its rows: the K range of B starts at another row than the K range of A starts at a column."""
+    monkeypatch.setenv("DRY_RUN", "1")
+    import asc2_scripts as K
+    a, b = torch.zeros(8 * 128, 64, dtype=torch.float16), torch.zeros(8 * 64, 256, dtype=torch.float16)
+    K.matmul_batched[4](a, b, torch.zeros(8 * 128, 256), 8, 128, 256, 64)
+    plan = K.matmul_batched.last_plan
+    assert plan.pattern == "matmul" and len(plan.steps) == 8
+    assert [s.note for s in plan.steps[:2]] == ["C[0:128, 0:256] = A[0:, 0:64] @ B[0:, 0:]",
+                                                "C[128:256, 0:256] = A[128:, 0:64] @ B[64:, 0:]"]
