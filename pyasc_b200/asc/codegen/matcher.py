@@ -806,7 +806,13 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
     # the window every call walks: rows x cols
     rows, cols = (out_g.rows, out_g.cols) if out_g.pitch is not None else (1, out_g.numel)
     for o, g in zip(prog.operands, geoms):
-        if o.bcast and out_g.pitch is None:
+        if out_g.pitch is None and g.pitch is not None and not o.bcast and not o.per_row and g.numel == out_g.numel \
+                and tuple(out_shape[-2:]) == (g.rows, g.cols):
+            # the result is a contiguous run of rows, an operand a window of a wider matrix (one half of each row,
+            # say): the call walks the window's rows x cols, the result with a pitch of one row
+            rows, cols = g.rows, g.cols
+    for o, g in zip(prog.operands, geoms):
+        if o.bcast and out_g.pitch is None and rows == 1:
             if out_g.numel % g.numel:
                 raise _unsupported("broadcast of a row whose length does not divide the stored tile")
             rows, cols = out_g.numel // g.numel, g.numel
@@ -1928,6 +1934,8 @@ def _match_matmul_then_program(trace: KernelTrace, eff: Effect) -> Optional[Plan
     if len(leaves) != 1:
         raise _unsupported("expression that combines several matmul results")
     mm = leaves[0]
+    if _value_from_deeper_loop(value, eff.loops, stop=(id(mm.node), )):
+        return None          # something besides the accumulator is carried out of a loop
     if mm.shape != value.shape or len(out_t.static_shape()) != 2:
         raise _unsupported("matmul result reshaped or stored to a tensor that is not 2-D before its elementwise epilogue")
     offsets = eff.attrs["offsets"]
@@ -2165,7 +2173,7 @@ def _is_identity_store(eff: Effect) -> bool:
             and view.tensor.static_shape() == out_t.static_shape() and _same_offsets(view.offsets, eff.attrs["offsets"]))
 
 
-def _value_from_deeper_loop(value: Any, loops: Tuple[Loop, ...]) -> bool:
+def _value_from_deeper_loop(value: Any, loops: Tuple[Loop, ...], stop: Tuple[int, ...] = ()) -> bool:
     """True when the stored value (or a value it is computed from) was produced inside a loop that does not
     enclose the store: a tile carried from one iteration to the next, or out of its loop.  A loop body is traced
     once, so such a value stands for a single iteration; only the matmul patterns, which read a sum over the
@@ -2180,6 +2188,8 @@ def _value_from_deeper_loop(value: Any, loops: Tuple[Loop, ...]) -> bool:
         if isinstance(v, Tile):
             v = v.node
         if isinstance(v, Node):
+            if id(v) in stop:            # (a matmul accumulator: the matmul matchers read it as a sum over its loop)
+                continue
             if len(v.loops) > len(loops) or any(a is not b for a, b in zip(v.loops, loops)):
                 return True
             stack.extend(v.args)
@@ -2281,7 +2291,7 @@ def build_plan(trace: KernelTrace) -> Plan:
         carried = _value_from_deeper_loop(eff.args[0], eff.loops)
         if carried:
             # only the matmul patterns read a loop-carried value as a sum over the loop
-            matchers = tuple(m for m in matchers if m in (_match_matmul, _match_attention))
+            matchers = tuple(m for m in matchers if m in (_match_matmul, _match_attention, _match_matmul_then_program))
         for matcher in matchers:
             plan = matcher(trace, eff)
             if plan is not None:

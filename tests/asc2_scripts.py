@@ -147,6 +147,32 @@ def matmul_batched(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, c_ptr: as
         asc2.store(asc2.matmul(a, b), c_gm, offsets=[i * m, 0])
 
 
+@asc2.jit(always_compile=True)
+def matmul_k_tiled_bias_relu(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, bias_ptr: asc.GlobalAddress,
+                             c_ptr: asc.GlobalAddress, m: asc.ConstExpr[int], n: asc.ConstExpr[int],
+                             k: asc.ConstExpr[int], k_tile: asc.ConstExpr[int]):
+    """An accumulation over a K loop, then a bias row and a ReLU on the accumulator."""
+    a_gm, b_gm, c_gm = asc2.tensor(a_ptr, [m, k]), asc2.tensor(b_ptr, [k, n]), asc2.tensor(c_ptr, [m, n])
+    bias = asc2.load(asc2.tensor(bias_ptr, [1, n]), [1, n], offsets=[0, 0])
+    acc = asc2.zeros_acc([m, n], dtype=asc.float32)
+    for kk in range(0, k, k_tile):
+        a = asc2.load(a_gm, [m, k_tile], offsets=[0, kk])
+        b = asc2.load(b_gm, [k_tile, n], offsets=[kk, 0])
+        asc2.matmul_acc(a, b, acc)
+    asc2.store(asc2.relu(acc + bias.broadcast_to(m, n)), c_gm, offsets=[0, 0])
+
+
+@asc2.jit(always_compile=True)
+def glu_rows(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: int, cols: asc.ConstExpr[int],
+             rpt: asc.ConstExpr[int]):
+    """A gated linear unit: the two halves of every row of x, a * sigmoid(g)."""
+    x_gm, out_gm = asc2.tensor(x_ptr, [rows, 2 * cols]), asc2.tensor(out_ptr, [rows, cols])
+    for r in range(asc2.block_idx() * rpt, rows, asc2.block_num() * rpt):
+        a = asc2.load(x_gm, [rpt, cols], offsets=[r, 0])
+        g = asc2.load(x_gm, [rpt, cols], offsets=[r, cols])
+        asc2.store(a / (asc2.exp(-g) + 1), out_gm, offsets=[r, 0])
+
+
 def mn_tiles_per_block(m, n, core_num, m_tile, n_tile, n_tiles_per_block):
     """Host-side tile bookkeeping of the M/N-blocked kernel (even distribution over blocks)."""
     m_tiles, n_tiles = m // m_tile, n // n_tile

@@ -110,6 +110,21 @@ def test_matmul_fixpipe(m, k, n, dtype):
     torch.testing.assert_close(c, c_ref, atol=1e-3, rtol=1e-3)
 
 
+def test_k_loop_accumulator_with_an_epilogue_and_glu():
+    gen = torch.Generator().manual_seed(77)
+    m, n, k = 128, 256, 1024
+    a = ((torch.rand(m, k, generator=gen) - .5) * 2 * k ** -0.5).half()
+    b = (torch.rand(k, n, generator=gen) - .5).half()
+    bias = torch.randn(1, n, generator=gen)
+    c = torch.zeros(m, n)
+    K.matmul_k_tiled_bias_relu[1](a, b, bias, c, m, n, k, 128)
+    torch.testing.assert_close(c, (a.float() @ b.float() + bias).relu(), atol=2e-3, rtol=2e-3)
+    x = torch.randn(256, 1024, generator=gen)
+    out = torch.zeros(256, 512)
+    K.glu_rows[4](x, out, 256, 512, 8)
+    torch.testing.assert_close(out, x[:, :512] / (torch.exp(-x[:, 512:]) + 1), rtol=2e-6, atol=1e-6)
+
+
 @pytest.mark.parametrize("batch, m, n, k", [(8, 128, 256, 64), (5, 200, 144, 80), (3, 1024, 1024, 1024)])
 def test_matmul_batched_loop(batch, m, n, k):
     gen = torch.Generator().manual_seed(batch * m)

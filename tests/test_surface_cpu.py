@@ -253,3 +253,19 @@ def test_batched_matmul_loop_plans_one_product_per_matrix(monkeypatch):
     assert plan.pattern == "matmul" and len(plan.steps) == 8
     assert [s.note for s in plan.steps[:2]] == ["C[0:128, 0:256] = A[0:, 0:64] @ B[0:, 0:]",
                                                 "C[128:256, 0:256] = A[128:, 0:64] @ B[64:, 0:]"]
+
+
+def test_k_loop_accumulator_with_an_epilogue_and_windows_of_a_wider_matrix(monkeypatch):
+    monkeypatch.setenv("DRY_RUN", "1")
+    import asc2_scripts as K
+    h = torch.float16
+    K.matmul_k_tiled_bias_relu[1](torch.zeros(128, 512, dtype=h), torch.zeros(512, 128, dtype=h), torch.zeros(1, 128),
+                                  torch.zeros(128, 128), 128, 128, 512, 128)
+    plan = K.matmul_k_tiled_bias_relu.last_plan            # the K loop folds into one product of K = 512
+    assert plan.pattern == "matmul+program" and [s.fn_name for s in plan.steps] == ["asc_cuda_gemm_f16", "asc_cuda_eltwise_program_2d"]
+    assert plan.steps[0].note == "C[0:128, 0:128] = A[0:, 0:512] @ B[0:, 0:]"
+    # the two halves of every row: operand windows with the pitch of the wide matrix, a contiguous result
+    K.glu_rows[4](torch.zeros(256, 1024), torch.zeros(256, 512), 256, 512, 8)
+    plan = K.glu_rows.last_plan
+    assert plan.pattern == "elementwise:program" and len(plan.steps) == 1 and not plan.partial_writes
+    assert plan.steps[0].note.endswith("over [256, 512] pitches [1024, 1024, 512] from [0, 512] to 0")
