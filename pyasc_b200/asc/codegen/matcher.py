@@ -430,6 +430,8 @@ class _EltProgram:
         self.reshaped = False       # a reshape was seen: element order is the flat (row-major) order
         self.row_ops = False        # the program reduces over rows: it runs as a row program
         self.uses_index = False     # the program reads the element index inside the tile: one call per tile
+        self.whole_tile = False     # a reduction of a whole multi-row tile: the tile is walked as one long row
+        self.per_row_reductions = False
         self.n_tmp = 0              # temporary slots the finished program uses
         self.visits = 0             # values visited while generating code
         self.full_shape: Optional[Tuple[int, ...]] = None   # set while code for a per-row value is generated
@@ -565,10 +567,13 @@ class _EltProgram:
             src = node.args[0]
             if _node(src, "full") is not None:
                 return self.gen(src.node.attrs["value"], v.dtype)
-            # a single row repeated along the leading dimension
-            if len(self.shape) == 2 and src.size == self.shape[1] and src.shape[-1] == self.shape[1] \
-                    and src.node.kind in ("load", "copy"):
-                return self._view_operand(src, bcast=True)
+            # a single row repeated along the leading dimension (also a loaded vector reshaped to one row)
+            row = src
+            while row.node.kind == "reshape" and row.node.args[0].size == row.size:
+                row = row.node.args[0]
+            if len(self.shape) == 2 and row.size == self.shape[1] and row.shape[-1] == self.shape[1] \
+                    and src.shape[-1] == self.shape[1] and row.node.kind in ("load", "copy"):
+                return self._view_operand(row, bcast=True)
             # one value per row repeated along the row: an expression over reductions of tiles of this shape
             # along their last dimension (every element of the row evaluates it, the values agree)
             if len(self.shape) == 2 and self.full_shape is None and src.size == self.shape[0] \
@@ -634,18 +639,22 @@ class _EltProgram:
             # per-row mode: the reduced tile has the full shape and loses its last dimension
             if src.shape != self.full_shape or dims != (len(src.shape) - 1, ):
                 return None
+            self.per_row_reductions = True
             outer, outer_full, self.shape, self.full_shape = self.shape, self.full_shape, src.shape, None
             try:
                 inner = self.gen(src)
             finally:
                 self.shape, self.full_shape = outer, outer_full
         else:
-            # the scalar reduction of a tile that is a single row of the stored shape
+            # the scalar reduction of a whole tile of the stored shape: a single row, or several rows that the
+            # row machine walks as one long row (the planner then wants every operand to be a contiguous range)
             rows = 1
             for d in self.shape[:-1]:
                 rows *= d
-            if dims != () or rows != 1 or src.shape != self.shape:
+            if dims != () or src.shape != self.shape:
                 return None
+            if rows != 1:
+                self.whole_tile = True
             inner = self.gen(src)
         if inner is None:
             return None
@@ -959,6 +968,11 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         rows = 1
         for d in out_shape[:-1]:
             rows *= d
+        if prog.whole_tile:
+            if prog.per_row_reductions or prog.uses_index:
+                raise _unsupported("reductions of a whole tile and along its rows in one expression")
+            return _plan_general_program(trace, eff, prog, out_t, offsets, out_shape, False, dedupe=True,
+                                         row_shape=(1, rows * out_shape[-1]))
         return _plan_general_program(trace, eff, prog, out_t, offsets, out_shape, False, dedupe=True,
                                      row_shape=(rows, out_shape[-1]))
     if not aligned or not prog.operands:

@@ -173,6 +173,26 @@ def glu_rows(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: int, co
         asc2.store(a / (asc2.exp(-g) + 1), out_gm, offsets=[r, 0])
 
 
+@asc2.jit(always_compile=True)
+def tile_over_its_own_reduction(x_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress,
+                                rows: int, cols: asc.ConstExpr[int], rpt: asc.ConstExpr[int], op: asc.ConstExpr):
+    """Every [rpt, cols] tile divided by a reduction of the whole tile, plus a 1-D bias vector reshaped to a row."""
+    x_gm, b_gm, out_gm = asc2.tensor(x_ptr, [rows, cols]), asc2.tensor(b_ptr, [cols]), asc2.tensor(out_ptr, [rows, cols])
+    for r in range(asc2.block_idx() * rpt, rows, asc2.block_num() * rpt):
+        x = asc2.load(x_gm, [rpt, cols], offsets=[r, 0])
+        asc2.store(x / op(x), out_gm, offsets=[r, 0])
+
+
+@asc2.jit(always_compile=True)
+def add_vector_bias(x_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: int,
+                    cols: asc.ConstExpr[int], rpt: asc.ConstExpr[int]):
+    x_gm, b_gm, out_gm = asc2.tensor(x_ptr, [rows, cols]), asc2.tensor(b_ptr, [cols]), asc2.tensor(out_ptr, [rows, cols])
+    bias = asc2.load(b_gm, [cols], offsets=[0])
+    for r in range(asc2.block_idx() * rpt, rows, asc2.block_num() * rpt):
+        asc2.store(asc2.load(x_gm, [rpt, cols], offsets=[r, 0]) + bias.reshape(1, cols).broadcast_to(rpt, cols), out_gm,
+                   offsets=[r, 0])
+
+
 def mn_tiles_per_block(m, n, core_num, m_tile, n_tile, n_tiles_per_block):
     """Host-side tile bookkeeping of the M/N-blocked kernel (even distribution over blocks)."""
     m_tiles, n_tiles = m // m_tile, n // n_tile

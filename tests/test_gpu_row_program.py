@@ -301,3 +301,24 @@ def test_row_programs_built_at_first_use_equal_the_interpreter(rows, cols, monke
     assert torch.equal(fast, plain)
     ref = torch.nn.functional.layer_norm(x, (cols, ), gamma[0], beta[0], 1e-5)
     torch.testing.assert_close(fast, ref, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("op, torch_op", [(asc2.reduce_max, torch.amax), (asc2.reduce_sum, torch.sum)],
+                         ids=lambda v: getattr(v, "__name__", ""))
+def test_tile_divided_by_a_reduction_of_the_whole_tile(op, torch_op):
+    """`x / reduce(x)` on multi-row tiles: each [32, 64] tile is walked as one row of 2048 elements."""
+    gen = torch.Generator().manual_seed(5)
+    x = torch.rand(256, 64, generator=gen) + 0.5
+    out = torch.zeros_like(x)
+    K.tile_over_its_own_reduction[4](x, torch.zeros(64), out, 256, 64, 32, op)
+    tiles = x.reshape(8, 32 * 64)
+    want = (tiles / torch_op(tiles, 1, keepdim=True)).reshape(256, 64)
+    torch.testing.assert_close(out, want, rtol=2e-6, atol=0)
+
+
+def test_vector_bias_reshaped_to_a_row():
+    gen = torch.Generator().manual_seed(6)
+    x, b = torch.randn(256, 64, generator=gen), torch.randn(64, generator=gen)
+    out = torch.zeros_like(x)
+    K.add_vector_bias[4](x, b, out, 256, 64, 32)
+    assert torch.equal(out, x + b)

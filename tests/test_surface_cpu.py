@@ -269,3 +269,25 @@ def test_k_loop_accumulator_with_an_epilogue_and_windows_of_a_wider_matrix(monke
     plan = K.glu_rows.last_plan
     assert plan.pattern == "elementwise:program" and len(plan.steps) == 1 and not plan.partial_writes
     assert plan.steps[0].note.endswith("over [256, 512] pitches [1024, 1024, 512] from [0, 512] to 0")
+
+
+def test_whole_tile_reduction_as_an_operand_and_a_reshaped_bias_vector(monkeypatch):
+    monkeypatch.setenv("DRY_RUN", "1")
+    import asc2_scripts as K
+    x = torch.zeros(256, 64)
+    K.tile_over_its_own_reduction[4](x, torch.zeros(64), torch.zeros_like(x), 256, 64, 32, asc2.reduce_max)
+    plan = K.tile_over_its_own_reduction.last_plan
+    # a [32, 64] tile is walked as one row of 2048 elements, so that the reduction spans the whole tile
+    assert plan.pattern == "row:program" and len(plan.steps) == 1
+    assert " over [8, 2048] " in plan.steps[0].note
+    K.add_vector_bias[4](x, torch.zeros(64), torch.zeros_like(x), 256, 64, 32)
+    plan = K.add_vector_bias.last_plan
+    assert plan.pattern == "elementwise:program" and plan.steps[0].note.endswith("pitches [64, 0, 64] from [0, 0] to 0")
+    # a tile that is a window of a wider matrix cannot be walked as one row
+    @asc2.jit
+    def windowed(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress):
+        x_gm, out_gm = asc2.tensor(x_ptr, [64, 128]), asc2.tensor(out_ptr, [64, 128])
+        t = asc2.load(x_gm, [64, 64], offsets=[0, 64])
+        asc2.store(t / asc2.reduce_max(t), out_gm, offsets=[0, 64])
+    with pytest.raises(NotImplementedError):
+        windowed[1](torch.zeros(64, 128), torch.zeros(64, 128))
