@@ -96,7 +96,14 @@ class TraceContext:
         self.masks: List[Tuple[PlainValue, Optional[PlainValue]]] = []     # active ``asc2.mask`` contexts, innermost last
 
     # -- branches ---------------------------------------------------------------------------------
+    MAX_BRANCHES = 256      # run-time conditions one trace may evaluate
+
     def branch(self, cond: PlainValue) -> bool:
+        if len(self.taken) >= self.MAX_BRANCHES:
+            # a `while` on a run-time value never ends while tracing: every evaluation is another taken branch
+            raise NotImplementedError(
+                f"kernel '{self.fn_name}' evaluated more than {self.MAX_BRANCHES} run-time conditions in one trace: a "
+                "`while` loop on a run-time value is not supported, iterate with `for ... in asc2.range(...)`")
         outcome = self.forced[len(self.taken)] if len(self.taken) < len(self.forced) else True
         self.taken.append((cond, outcome))
         return outcome

@@ -135,3 +135,18 @@ def test_too_many_paths_are_refused():
         asc2.store(x, asc2.tensor(out_ptr, [128 * n]), offsets=[b * n])
     with pytest.raises(NotImplementedError, match="more than 64 paths"):
         seven_branches[128](torch.zeros(N), torch.zeros(128 * N), N)
+
+
+def test_a_while_loop_on_a_run_time_value_is_refused_instead_of_tracing_forever(monkeypatch):
+    monkeypatch.setenv("DRY_RUN", "1")
+
+    @asc2.jit
+    def while_loop(x_ptr: asc.GlobalAddress, o_ptr: asc.GlobalAddress, n: int, tile: asc.ConstExpr[int]):
+        x_gm, o_gm = asc2.tensor(x_ptr, [n]), asc2.tensor(o_ptr, [n])
+        i = asc2.block_idx() * tile
+        while i < n:
+            asc2.store(asc2.load(x_gm, [tile], offsets=[i]) * 3.0, o_gm, offsets=[i])
+            i += asc2.block_num() * tile
+
+    with pytest.raises(NotImplementedError, match="while"):
+        while_loop[4](torch.zeros(4096), torch.zeros(4096), 4096, 256)
