@@ -67,6 +67,80 @@ def _pointer_proxy(name: str, value: Any, index: int) -> Optional[GlobalAddress]
 MAX_PATHS = 64      # paths through ``if``s on run-time scalars one kernel may have
 
 
+class _Signatures:
+    """Structural digests of traced values: two values recorded by different runs of the kernel get the same digest
+    when they are the same computation (same operations on the same tensors at the same offsets inside loops with the
+    same bounds).  Digests are computed bottom-up and memoised per object, so shared subexpressions cost once."""
+
+    def __init__(self):
+        self._memo: Dict[int, str] = {}
+        self._keep: List[Any] = []        # the memo is keyed by id(): keep the objects alive
+
+    def of(self, x: Any) -> str:
+        from ..language.tile.tensor import Tensor
+        from ..language.tile.tile import Tile
+        from ..language.tile.trace import Loop, Node
+        if isinstance(x, (Tile, Node, PlainValue, Tensor, Loop, Effect)):
+            key = id(x)
+            hit = self._memo.get(key)
+            if hit is not None:
+                return hit
+            if isinstance(x, Tile):
+                parts = ("T", repr(x.shape), x.dtype.name, self.of(x.node))
+            elif isinstance(x, Node):
+                parts = ("N", x.kind, self.of(x.args), self.of(x.attrs), self.of(x.loops))
+            elif isinstance(x, PlainValue):
+                parts = ("P", x.op, x.dtype.name, self.of(x.args))
+            elif isinstance(x, Tensor):
+                parts = ("X", repr(x.base.index), x.dtype.name, self.of(x.shape))
+            elif isinstance(x, Loop):
+                parts = ("L", x.name, self.of(x.start), self.of(x.stop), self.of(x.step))
+            else:
+                parts = ("E", x.kind, self.of(x.args), self.of(x.attrs), self.of(x.loops))
+            import hashlib
+            digest = hashlib.blake2b("\x1f".join(parts).encode(), digest_size=12).hexdigest()
+            self._memo[key] = digest
+            self._keep.append(x)
+            return digest
+        if isinstance(x, (tuple, list)):
+            return "(" + ",".join(self.of(v) for v in x) + ")"
+        if isinstance(x, dict):
+            return "{" + ",".join(f"{k}:{self.of(v)}" for k, v in sorted(x.items(), key=lambda kv: str(kv[0]))) + "}"
+        if isinstance(x, GlobalAddress):
+            return f"G{x.index!r}"
+        return repr(x)
+
+
+def _merge_paths(effects: List[Effect]) -> List[Effect]:
+    """Statements after an ``if`` on a run-time scalar are traced once per path, so each shows up as several effects
+    that differ only in the outcome of that ``if``.  Two effects that are the same computation under guards that agree
+    except for opposite outcomes of their last condition happen whichever way that condition goes: they become one
+    effect without it (repeatedly, for nests and sequences of ``if``s).  The merged effect takes the place of the
+    earlier one; the two never both happen for one block and iteration."""
+    if not any(e.guards for e in effects):
+        return effects
+    sig = _Signatures()
+    effects = list(effects)
+    merged = True
+    while merged:
+        merged = False
+        seen: Dict[tuple, int] = {}
+        for i, e in enumerate(effects):
+            if not e.guards:
+                continue
+            head = tuple((sig.of(c), o) for c, o in e.guards[:-1])
+            cond, outcome = e.guards[-1]
+            key = (sig.of(e), head, sig.of(cond))
+            j = seen.get(key + (not outcome, ))
+            if j is not None:
+                effects[j].guards = effects[j].guards[:-1]
+                del effects[i]
+                merged = True
+                break
+            seen[key + (outcome, )] = i
+    return effects
+
+
 def trace_kernel(fn: Callable, runtime_args: Dict[str, Any], constexprs: Dict[str, ConstExpr], core_num: int,
                  custom_builtins: Optional[Dict[str, Any]] = None, unroll_limit: int = 0) -> KernelTrace:
     call_args: Dict[str, Any] = {}
@@ -108,4 +182,4 @@ def trace_kernel(fn: Callable, runtime_args: Dict[str, Any], constexprs: Dict[st
         outcomes = tuple(o for _, o in ctx.taken)
         for j in range(len(ctx.taken) - 1, len(forced) - 1, -1):
             pending.append(outcomes[:j] + (not outcomes[j], ))
-    return KernelTrace(fn.__name__, core_num, effects, pointers)
+    return KernelTrace(fn.__name__, core_num, _merge_paths(effects), pointers)

@@ -57,10 +57,9 @@ def test_nested_branches_on_the_block_index():
     assert notes == sorted([
         f"2 ops over [1, {N}] pitches [{N}, {N}] from [0] to 0",             # block 0: x - 1 (stored at a fixed place)
         f"2 ops over [{N}, {3 * N})",                                         # blocks 1 and 2: exp(x), merged
-        # the copy after the join is recorded on all three paths: block 0, blocks 1-2 (merged), block 3
-        f"1 ops over [1, {N}] pitches [{N}, {N}] from [0] to {4 * N}",
-        f"1 ops over [2, {N}] pitches [{N}, {N}] from [{N}] to {5 * N}",
-        f"1 ops over [1, {N}] pitches [{N}, {N}] from [{3 * N}] to {7 * N}",
+        # the copy after the join is traced on all three paths; the three recordings are one computation under
+        # complementary conditions and merge into one effect for all four blocks
+        f"1 ops over [4, {N}] pitches [{N}, {N}] from [0] to {4 * N}",
     ])
 
 
