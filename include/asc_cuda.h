@@ -192,6 +192,13 @@ int32_t asc_cuda_col_program(const int32_t* ops, const int32_t* args, int32_t n_
  * reference's first-use build and cache of device code (python/asc/runtime/jit.py:158-202, cache.py:57-112). */
 int32_t asc_cuda_register_program(int32_t kind, const int32_t* words, int32_t n_words, void* fn);
 
+/* Copy of a window of `rows` rows of `row_bytes` bytes between two device matrices with their own row pitches (bytes;
+ * each at least row_bytes).  The windows must not overlap.  Serves asc2.store(asc2.load(...)) of tiles of element
+ * types the elementwise kernels do not compute on (8-bit and 64-bit types): a pure move, which the reference lowers
+ * to DataCopy between global and on-chip memory (python/asc/language/tile/memory_ops.py). */
+int32_t asc_cuda_copy_2d(void* dst, const void* src, int64_t rows, int64_t row_bytes, int64_t dst_pitch,
+                         int64_t src_pitch, void* stream);
+
 /* Reduction of a row-major [rows, cols] fp32 window with row pitch `ld` (elements).  kind: 0 sum, 1 max,
  * 2 min, 3 product.  axis 1: out[r] = reduce over the columns of row r; axis 0: out[c] = reduce over the
  * rows of column c; axis -1: out[0 .. n_fill) all receive the reduction of the whole window (the window is

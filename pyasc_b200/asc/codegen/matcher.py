@@ -1912,6 +1912,72 @@ def _match_matmul(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     return plan
 
 
+def _match_copy(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
+    """``store(load(...))`` of a tile whose element type the elementwise kernels do not compute on (8-bit and 64-bit
+    types): a move of bytes, window by window (``asc_cuda_copy_2d``).  Types the programs know keep their path."""
+    value, out_t = eff.args
+    if eff.kind != "store" or not isinstance(value, Tile) or value.dtype.name in _ELT_TYPE or value.dtype != out_t.dtype:
+        return None
+    view = resolve_view(value) if value.node.kind in ("load", "copy") else None
+    if view is None or view.tensor.dtype != value.dtype or tuple(view.shape) != tuple(value.shape):
+        return None
+    _check_fits(out_t)
+    _check_fits(view.tensor)
+    offsets = eff.attrs["offsets"]
+    env = enumerate_instances(trace.core_num, eff.loops, eff.guards)
+    n = env_count(env)
+    if n > MAX_CALLS:
+        raise _unsupported("copy kernel with more than 4096 tiles")
+    src_g = _Geometry(view.tensor, view.offsets, view.shape, False, env, n)      # refuses tiles past the end
+    dst_g = _Geometry(out_t, offsets, value.shape, False, env, n)
+    esize = value.dtype.sizeof()
+    # the window one call moves: rows x cols elements with a pitch on either side
+    if src_g.pitch is None and dst_g.pitch is None:
+        rows, cols = 1, src_g.numel
+    else:
+        rows, cols = (src_g.rows, src_g.cols) if src_g.pitch is not None else (dst_g.rows, dst_g.cols)
+        for g in (src_g, dst_g):
+            if g.pitch is not None and (g.rows, g.cols) != (rows, cols):
+                raise _unsupported("copy between windows of different shapes")
+    src_ld = src_g.pitch if src_g.pitch is not None else cols
+    dst_ld = dst_g.pitch if dst_g.pitch is not None else cols
+    src_idx, dst_idx = view.tensor.base.index, out_t.base.index
+    if src_idx == dst_idx:
+        raise _unsupported("copy inside one tensor")
+    pairs = sorted(set(zip(src_g.start.tolist(), dst_g.start.tolist())), key=lambda p: p[1])
+    rect = _flat_rects(out_t.static_shape()[-1] if out_t.static_shape() else 1, np.array([p[1] for p in pairs], dtype=np.int64),
+                       dst_g.numel, dst_g.rows, dst_g.cols, dst_g.pitch)
+    clash = _rects_overlap(rect, rect)
+    np.fill_diagonal(clash, False)
+    if clash.any():
+        raise _unsupported("copies of different tiles into overlapping ranges (the last writer would win)")
+    calls: List[Tuple[int, int, int]] = []       # (first source element, first destination element, rows)
+    for s0, d0 in pairs:
+        if calls:
+            ps, pd, prow = calls[-1]
+            if s0 == ps + prow * src_ld and d0 == pd + prow * dst_ld:
+                calls[-1] = (ps, pd, prow + rows)      # the next rows of the same two matrices
+                continue
+        calls.append((s0, d0, rows))
+    if not calls:
+        raise _unsupported("copy kernel without any tile")
+    plan = Plan("copy")
+    plan.reads.add(src_idx)
+    plan.writes.add(dst_idx)
+    if not (len(calls) == 1 and calls[0][1] == 0 and dst_ld == cols and calls[0][2] * cols == out_t.base.numel):
+        plan.partial_writes.add(dst_idx)
+
+    def make_step(s0: int, d0: int, call_rows: int) -> Step:
+        def build(ptrs, stream):
+            return (_p(ptrs[dst_idx] + esize * d0), _p(ptrs[src_idx] + esize * s0), ctypes.c_int64(call_rows),
+                    ctypes.c_int64(cols * esize), ctypes.c_int64(dst_ld * esize), ctypes.c_int64(src_ld * esize), stream)
+        return Step("asc_cuda_copy_2d", build, f"[{call_rows}, {cols}] {value.dtype.name} from {s0} to {d0}")
+
+    for call in calls:
+        plan.steps.append(make_step(*call))
+    return plan
+
+
 def _matmul_leaves(value: Any, limit: int = 4096) -> List[Tile]:
     """The matmul results (``matmul`` / ``matmul_acc`` accumulators) an expression is computed from."""
     found: List[Tile] = []
@@ -2176,7 +2242,7 @@ def _check_effect_order(trace: KernelTrace, first: Effect, second: Effect, cache
 # Entry point
 # --------------------------------------------------------------------------------------------------
 _MATCHERS = (_match_attention, _match_softmax, _match_rms_norm, _match_elementwise, _match_matmul,
-             _match_matmul_then_program, _match_eltwise_program,
+             _match_matmul_then_program, _match_eltwise_program, _match_copy,
              _match_row_result, _match_row_scalar, _match_col_reduce, _match_reduce)
 
 

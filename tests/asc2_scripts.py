@@ -193,6 +193,16 @@ def add_vector_bias(x_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, out_ptr:
                    offsets=[r, 0])
 
 
+@asc2.jit(always_compile=True)
+def copy_window(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: int, x_cols: asc.ConstExpr[int],
+                out_cols: asc.ConstExpr[int], cols: asc.ConstExpr[int], x_col0: asc.ConstExpr[int],
+                out_col0: asc.ConstExpr[int], rpt: asc.ConstExpr[int]):
+    """Moves a [rows, cols] window of one matrix into a window of another, rpt rows at a time, whatever the type."""
+    x_gm, out_gm = asc2.tensor(x_ptr, [rows, x_cols]), asc2.tensor(out_ptr, [rows, out_cols])
+    for r in range(asc2.block_idx() * rpt, rows, asc2.block_num() * rpt):
+        asc2.store(asc2.load(x_gm, [rpt, cols], offsets=[r, x_col0]), out_gm, offsets=[r, out_col0])
+
+
 def mn_tiles_per_block(m, n, core_num, m_tile, n_tile, n_tiles_per_block):
     """Host-side tile bookkeeping of the M/N-blocked kernel (even distribution over blocks)."""
     m_tiles, n_tiles = m // m_tile, n // n_tile

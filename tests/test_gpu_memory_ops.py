@@ -121,3 +121,47 @@ def test_window_program_rejections(lib):
     assert call(-1, 8, (8, 8)) == 1
     assert call(1 << 20, 1 << 12, (1 << 13, 1 << 13)) == 6
     assert call(0, 8, (16, 16)) == 0                     # empty
+
+
+@pytest.mark.parametrize("dtype", [torch.int8, torch.uint8, torch.float64, torch.int64], ids=str)
+def test_copy_of_tiles_of_any_element_type(dtype):
+    """asc2.store(asc2.load(...)) moves bytes: 8-bit and 64-bit tiles, windows of matrices of different widths."""
+    import asc2_scripts as K
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randint(-100, 100, (64, 256), generator=gen).to(dtype)
+    out = torch.full((64, 512), 7, dtype=dtype)
+    K.copy_window[4](x, out, 64, 256, 512, 128, 64, 32, 8)
+    want = torch.full((64, 512), 7, dtype=dtype)
+    want[:, 32:160] = x[:, 64:192]
+    assert torch.equal(out, want)
+    # whole matrices, and a window whose byte offsets are not multiples of 16
+    y = torch.randint(-100, 100, (64, 128), generator=gen).to(dtype)
+    out2 = torch.zeros_like(y)
+    K.copy_window[4](y, out2, 64, 128, 128, 128, 0, 0, 8)
+    assert torch.equal(out2, y)
+    if dtype in (torch.int8, torch.uint8):
+        out3 = torch.full((64, 512), 7, dtype=dtype)
+        K.copy_window[4](x, out3, 64, 256, 512, 96, 32, 32, 8)
+        want3 = torch.full((64, 512), 7, dtype=dtype)
+        want3[:, 32:128] = x[:, 32:128]
+        assert torch.equal(out3, want3)
+
+
+def test_capi_copy_2d_vector_and_byte_paths():
+    lib = capi.load()
+    gen = torch.Generator().manual_seed(4)
+    src = torch.randint(0, 255, (300, 1000), generator=gen).to(torch.uint8).cuda()
+    P = lambda t, off=0: ctypes.c_void_p(t.data_ptr() + off)
+    for (rows, row_bytes, s_off, d_off) in ((300, 1000, 0, 0), (257, 333, 7, 5), (64, 512, 16, 32), (1, 1, 999, 3), (0, 10, 0, 0)):
+        dst = torch.full((300, 1200), 9, dtype=torch.uint8, device="cuda")
+        rc = lib.asc_cuda_copy_2d(P(dst, d_off), P(src, s_off), rows, row_bytes, 1200, 1000, None)
+        assert rc == 0, capi.status_string(rc)
+        capi.check_device_status(None)
+        want = torch.full((300, 1200), 9, dtype=torch.uint8)
+        flat_s, flat_d = src.cpu().reshape(-1), want.reshape(-1)
+        for r in range(rows):
+            flat_d[d_off + r * 1200:d_off + r * 1200 + row_bytes] = flat_s[s_off + r * 1000:s_off + r * 1000 + row_bytes]
+        assert torch.equal(dst.cpu(), want), (rows, row_bytes, s_off, d_off)
+    dst = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    assert lib.asc_cuda_copy_2d(P(dst), P(src), 2, 16, 8, 1000, None) == 1          # pitch shorter than a row
+    assert lib.asc_cuda_copy_2d(None, P(src), 2, 8, 8, 1000, None) == 1

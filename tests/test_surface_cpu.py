@@ -291,3 +291,24 @@ def test_whole_tile_reduction_as_an_operand_and_a_reshaped_bias_vector(monkeypat
         asc2.store(t / asc2.reduce_max(t), out_gm, offsets=[0, 64])
     with pytest.raises(NotImplementedError):
         windowed[1](torch.zeros(64, 128), torch.zeros(64, 128))
+
+
+def test_copy_of_tiles_of_types_the_programs_do_not_compute_on(monkeypatch):
+    monkeypatch.setenv("DRY_RUN", "1")
+    import asc2_scripts as K
+    x = torch.zeros(64, 256, dtype=torch.int8)
+    K.copy_window[4](x, torch.zeros(64, 512, dtype=torch.int8), 64, 256, 512, 128, 64, 32, 8)
+    plan = K.copy_window.last_plan
+    assert plan.pattern == "copy" and plan.reads == {0} and plan.writes == {1} and plan.partial_writes == {1}
+    (step, ) = plan.steps                                     # the eight row blocks continue each other
+    assert step.fn_name == "asc_cuda_copy_2d" and step.note == "[64, 128] int8 from 64 to 32"
+    built = step.build({0: 1 << 20, 1: 2 << 20}, None)
+    assert [a.value for a in built[:6]] == [(2 << 20) + 32, (1 << 20) + 64, 64, 128, 512, 256]
+    d = torch.zeros(64, 128, dtype=torch.float64)
+    K.copy_window[4](d, torch.zeros_like(d), 64, 128, 128, 128, 0, 0, 8)
+    plan = K.copy_window.last_plan                            # whole matrices: one contiguous move, a full write
+    assert plan.steps[0].note == "[8, 1024] float64 from 0 to 0" and not plan.partial_writes
+    # a float32 copy stays with the elementwise program
+    f = torch.zeros(64, 128)
+    K.copy_window[4](f, torch.zeros_like(f), 64, 128, 128, 128, 0, 0, 8)
+    assert K.copy_window.last_plan.pattern == "elementwise:program"
