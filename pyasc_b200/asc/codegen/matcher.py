@@ -870,7 +870,7 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
         # An operand taken from the tensor that is stored to must be the stored window itself, element for element:
         # a thread then reads exactly what it overwrites (`y = x + y` in place, the target of an atomic).
         o = prog.operands[k]
-        same_window = (not o.bcast and not o.per_row and not prog.reshaped and lds[k] == lds[-1]
+        same_window = (not o.bcast and (not o.per_row or row_result) and not prog.reshaped and lds[k] == lds[-1]
                        and np.array_equal(g.start, out_g.start))
         if i == out_idx and not same_window:
             raise _unsupported("elementwise kernel that stores into a tensor it also loads at other positions")
@@ -1067,18 +1067,35 @@ def _match_atomic(trace: KernelTrace, eff: Effect) -> Plan:
     if not isinstance(value, Tile) or out_t.dtype.name not in _ELT_TYPE or value.dtype != out_t.dtype:
         raise _unsupported(f"atomic_{eff.attrs['kind']} of a {getattr(value, 'dtype', type(value).__name__)} tile into a "
                            f"{out_t.dtype} tensor")
+    table = _BINARY_CODE if out_t.dtype.is_float() else _INT_BINARY_CODE
     prog = _EltProgram(value.shape, offsets, out_t)
     current = prog._load(_Operand(out_t, offsets, value.shape))
     update = prog.gen(value)
+    row_shape = None
     if current is None or update is None or prog.row_ops:
-        raise _unsupported("atomic operation on a tile that is not an elementwise expression of loaded tiles")
-    table = _BINARY_CODE if out_t.dtype.is_float() else _INT_BINARY_CODE
+        # one value per row, computed from reductions along the rows of a tile (partial row sums of a column block
+        # accumulated into a vector): a row program that loads the target element of its row and stores it back
+        red = _find_row_reduction(value)
+        full_shape = red.args[0].shape if red is not None else None
+        if red is None or value.shape not in ((full_shape[0], ), (full_shape[0], 1)) or not out_t.dtype.is_float():
+            raise _unsupported("atomic operation on a tile that is neither an elementwise expression of loaded tiles nor "
+                               "one value per row of a tile reduced along its rows")
+        prog = _EltProgram(value.shape, offsets, out_t)
+        update = prog._per_row(value, full_shape)
+        current = prog._load(_Operand(out_t, offsets, value.shape, per_row=True))
+        if update is None or current is None or not prog.row_ops:
+            raise _unsupported("atomic operation on an expression of row reductions that is not expressible")
+        row_shape = (full_shape[0], full_shape[1])
     prog._finish(prog._rounded(prog._binary(table[eff.attrs["kind"]], current, update), out_t.dtype))
     _check_program_limits(prog)
     _check_fits(out_t)
     for t in prog.inputs:
         _check_fits(t)
-    plan = _plan_general_program(trace, eff, prog, out_t, offsets, value.shape, False, dedupe=False)
+    if row_shape is not None:
+        plan = _plan_general_program(trace, eff, prog, out_t, offsets, value.shape, False, dedupe=False,
+                                     row_shape=row_shape, row_result=True)
+    else:
+        plan = _plan_general_program(trace, eff, prog, out_t, offsets, value.shape, False, dedupe=False)
     plan.pattern = f"atomic:{eff.attrs['kind']}"
     return plan
 

@@ -203,6 +203,17 @@ def copy_window(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: int,
         asc2.store(asc2.load(x_gm, [rpt, cols], offsets=[r, x_col0]), out_gm, offsets=[r, out_col0])
 
 
+@asc2.jit(always_compile=True)
+def split_row_reduce(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: asc.ConstExpr[int],
+                     cols: asc.ConstExpr[int], col_tile: asc.ConstExpr[int], op: asc.ConstExpr, atomic: asc.ConstExpr):
+    """Row reductions split over column blocks: every block reduces its [rows, col_tile] tiles along the rows and
+    accumulates the partial results into the output vector with an atomic."""
+    x_gm, out_gm = asc2.tensor(x_ptr, [rows, cols]), asc2.tensor(out_ptr, [rows])
+    for c in range(asc2.block_idx() * col_tile, cols, asc2.block_num() * col_tile):
+        x = asc2.load(x_gm, [rows, col_tile], offsets=[0, c])
+        atomic(op(x * x, 1), out_gm, offsets=[0])
+
+
 def mn_tiles_per_block(m, n, core_num, m_tile, n_tile, n_tiles_per_block):
     """Host-side tile bookkeeping of the M/N-blocked kernel (even distribution over blocks)."""
     m_tiles, n_tiles = m // m_tile, n // n_tile

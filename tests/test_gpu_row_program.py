@@ -322,3 +322,23 @@ def test_vector_bias_reshaped_to_a_row():
     out = torch.zeros_like(x)
     K.add_vector_bias[4](x, b, out, 256, 64, 32)
     assert torch.equal(out, x + b)
+
+
+@pytest.mark.parametrize("op, atomic, torch_op", [(asc2.reduce_sum, asc2.atomic_add, torch.sum),
+                                                  (asc2.reduce_max, asc2.atomic_max, torch.amax),
+                                                  (asc2.reduce_min, asc2.atomic_min, torch.amin)],
+                         ids=lambda v: getattr(v, "__name__", ""))
+def test_row_reductions_split_over_column_blocks_accumulate_atomically(op, atomic, torch_op):
+    gen = torch.Generator().manual_seed(8)
+    x = torch.randn(64, 2048, generator=gen)
+    start = {asc2.atomic_add: 0.5, asc2.atomic_max: 0.0, asc2.atomic_min: 100.0}[atomic]
+    out = torch.full((64, ), start)
+    K.split_row_reduce[4](x, out, 64, 2048, 256, op, atomic)
+    sq = x * x
+    if atomic is asc2.atomic_add:
+        torch.testing.assert_close(out, sq.sum(1) + start, rtol=1e-5, atol=1e-5)
+    elif atomic is asc2.atomic_max:
+        assert torch.equal(out, torch.maximum(sq.amax(1), torch.tensor(start)))
+    else:
+        # the minimum of the per-block minima of x * x, and of the starting value
+        assert torch.equal(out, torch.minimum(sq.reshape(64, 8, 256).amin(2).amin(1), torch.tensor(start)))

@@ -312,3 +312,14 @@ def test_copy_of_tiles_of_types_the_programs_do_not_compute_on(monkeypatch):
     f = torch.zeros(64, 128)
     K.copy_window[4](f, torch.zeros_like(f), 64, 128, 128, 128, 0, 0, 8)
     assert K.copy_window.last_plan.pattern == "elementwise:program"
+
+
+def test_atomic_accumulation_of_row_reductions(monkeypatch):
+    monkeypatch.setenv("DRY_RUN", "1")
+    import asc2_scripts as K
+    K.split_row_reduce[4](torch.zeros(64, 2048), torch.zeros(64), 64, 2048, 256, asc2.reduce_sum, asc2.atomic_add)
+    plan = K.split_row_reduce.last_plan
+    assert plan.pattern == "atomic:add" and len(plan.steps) == 8 and plan.reads == {0, 1} and plan.writes == {1}
+    assert all(s.fn_name == "asc_cuda_row_program" for s in plan.steps)
+    # x, x, MUL, ROW_SUM, the row's element of the target, ADD: one stored element per row
+    assert list(plan.steps[0].build({0: 0, 1: 0}, None)[0]) == [0, 0, 4, 59, 0, 2]
