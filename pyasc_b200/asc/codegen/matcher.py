@@ -430,6 +430,7 @@ class _EltProgram:
         self.reshaped = False       # a reshape was seen: element order is the flat (row-major) order
         self.row_ops = False        # the program reduces over rows: it runs as a row program
         self.uses_index = False     # the program reads the element index inside the tile: one call per tile
+        self.row_expr = False       # generating code for a [1, cols] row that every row of the result repeats
         self.whole_tile = False     # a reduction of a whole multi-row tile: the tile is walked as one long row
         self.per_row_reductions = False
         self.n_tmp = 0              # temporary slots the finished program uses
@@ -551,7 +552,7 @@ class _EltProgram:
                     return None
                 self.row_ops = True
                 return self._load(_Operand(view.tensor, view.offsets, view.shape, per_row=True))
-            return self._view_operand(v)
+            return self._view_operand(v, bcast=self.row_expr)
         if node.kind == "reshape":
             # row-major element order is kept, so elementwise code commutes with the reshape
             src = node.args[0]
@@ -574,6 +575,15 @@ class _EltProgram:
             if len(self.shape) == 2 and row.size == self.shape[1] and row.shape[-1] == self.shape[1] \
                     and src.shape[-1] == self.shape[1] and row.node.kind in ("load", "copy"):
                 return self._view_operand(row, bcast=True)
+            # a row computed from other rows (statistics along the first axis that have been written to a temporary, a
+            # loaded row): every element evaluates the expression for its own column
+            if len(self.shape) == 2 and self.full_shape is None and not self.row_expr and row.shape[-1] == self.shape[1] \
+                    and row.size == self.shape[1] and _MATERIALISED:
+                outer, self.shape, self.row_expr = self.shape, row.shape, True
+                try:
+                    return self.gen(row, scalar_dtype)
+                finally:
+                    self.shape, self.row_expr = outer, False
             # one value per row repeated along the row: an expression over reductions of tiles of this shape
             # along their last dimension (every element of the row evaluates it, the values agree)
             if len(self.shape) == 2 and self.full_shape is None and src.size == self.shape[0] \
@@ -1995,6 +2005,75 @@ def _match_copy(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     return plan
 
 
+def _column_reductions(value: Any, shape: Tuple[int, ...], limit: int = 4096) -> List[Tile]:
+    """The reductions along the first axis of [rows, cols] tiles that the expression of ``value`` uses (through a
+    ``broadcast_to(rows, cols)`` of a row computed from them), innermost first."""
+    found: List[Tile] = []
+    seen = set()
+
+    def visit(v: Any) -> None:
+        if len(seen) > limit:
+            return
+        if isinstance(v, Tile):
+            if id(v.node) in seen:
+                return
+            seen.add(id(v.node))
+            for a in v.node.args:
+                visit(a)
+            for a in v.node.attrs.values():
+                if isinstance(a, (Tile, PlainValue)):
+                    visit(a)
+            if v.node.kind == "reduce" and v.node.attrs["dims"] == (0, ) and v.node.args[0].shape == shape:
+                found.append(v)
+        elif isinstance(v, PlainValue) and v.op not in ("const", "sym"):
+            for a in v.args:
+                if isinstance(a, (Tile, PlainValue)):
+                    visit(a)
+    visit(value)
+    return found
+
+
+def _match_column_statistics(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
+    """``store(f(x, reduce(g(x), 0, keep_dims=True).broadcast_to(rows, cols), ...))``: an elementwise expression that
+    uses reductions of [rows, cols] tiles along their first axis, repeated over the rows (a softmax or a normalisation
+    down the columns).  Every such reduction is computed first, innermost first, by a column program into a temporary
+    matrix of the result's shape (the row of the tile's own window, so every tile has its own), and is then an
+    ordinary broadcast-row operand of what follows; the last step is one elementwise program."""
+    value, out_t = eff.args
+    if eff.kind != "store" or not isinstance(value, Tile) or len(value.shape) != 2 or len(out_t.static_shape()) != 2:
+        return None
+    reductions = _column_reductions(value, value.shape)
+    if not reductions or value.node.kind == "reduce":
+        return None
+    offsets = eff.attrs["offsets"]
+    rows, cols = value.shape
+    plan = Plan("column:statistics")
+    try:
+        for src in reductions:
+            key = f"tmp{len(plan.temps)}"
+            tmp = _fake_tensor(key, out_t.static_shape(), src.dtype)
+            plan.temps[key] = out_t.base.numel * src.dtype.sizeof()
+            row_tile = Tile((1, cols), src.dtype, src.node, src.location)           # the reduction, kept as one row
+            sub_eff = Effect("store", (row_tile, tmp), {"offsets": offsets}, eff.loops, eff.guards)
+            sub = _match_col_reduce(trace, sub_eff) or _match_reduce(trace, sub_eff)
+            if sub is None:
+                raise _unsupported("reduction along the first axis that no kernel computes")
+            sub.reads.discard(key)
+            plan.steps.extend(sub.steps)
+            plan.reads.update(r for r in sub.reads if not (isinstance(r, str) and r.startswith("tmp")))
+            _MATERIALISED[id(src.node)] = _Operand(tmp, offsets, (1, cols), bcast=True)
+        tail = _match_eltwise_program(trace, eff)
+    finally:
+        _MATERIALISED.clear()
+    if tail is None:
+        raise _unsupported("expression around reductions along the first axis that is not elementwise")
+    plan.steps.extend(tail.steps)
+    plan.reads.update(r for r in tail.reads if not (isinstance(r, str) and r.startswith("tmp")))
+    plan.writes.update(tail.writes)
+    plan.partial_writes.update(tail.partial_writes)
+    return plan
+
+
 def _matmul_leaves(value: Any, limit: int = 4096) -> List[Tile]:
     """The matmul results (``matmul`` / ``matmul_acc`` accumulators) an expression is computed from."""
     found: List[Tile] = []
@@ -2259,7 +2338,7 @@ def _check_effect_order(trace: KernelTrace, first: Effect, second: Effect, cache
 # Entry point
 # --------------------------------------------------------------------------------------------------
 _MATCHERS = (_match_attention, _match_softmax, _match_rms_norm, _match_elementwise, _match_matmul,
-             _match_matmul_then_program, _match_eltwise_program, _match_copy,
+             _match_matmul_then_program, _match_column_statistics, _match_eltwise_program, _match_copy,
              _match_row_result, _match_row_scalar, _match_col_reduce, _match_reduce)
 
 

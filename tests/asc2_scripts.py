@@ -214,6 +214,29 @@ def split_row_reduce(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows:
         atomic(op(x * x, 1), out_gm, offsets=[0])
 
 
+@asc2.jit(always_compile=True)
+def column_softmax(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, tiles: int, rows: asc.ConstExpr[int],
+                   cols: asc.ConstExpr[int]):
+    """Softmax down the columns of every [rows, cols] tile: reductions along the first axis, repeated over the rows."""
+    x_gm, out_gm = asc2.tensor(x_ptr, [tiles * rows, cols]), asc2.tensor(out_ptr, [tiles * rows, cols])
+    for t in range(asc2.block_idx(), tiles, asc2.block_num()):
+        x = asc2.load(x_gm, [rows, cols], offsets=[t * rows, 0])
+        e = asc2.exp(x - asc2.reduce_max(x, 0, keep_dims=True).broadcast_to(rows, cols))
+        asc2.store(e / asc2.reduce_sum(e, 0, keep_dims=True).broadcast_to(rows, cols), out_gm, offsets=[t * rows, 0])
+
+
+@asc2.jit(always_compile=True)
+def column_standardise(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, tiles: int, rows: asc.ConstExpr[int],
+                       cols: asc.ConstExpr[int], eps: float):
+    """(x - mean) / sqrt(var + eps) with the statistics taken down the columns of every tile (a batch norm's core)."""
+    x_gm, out_gm = asc2.tensor(x_ptr, [tiles * rows, cols]), asc2.tensor(out_ptr, [tiles * rows, cols])
+    for t in range(asc2.block_idx(), tiles, asc2.block_num()):
+        x = asc2.load(x_gm, [rows, cols], offsets=[t * rows, 0])
+        d = x - (asc2.reduce_sum(x, 0, keep_dims=True) * (1.0 / rows)).broadcast_to(rows, cols)
+        var = asc2.reduce_sum(d * d, 0, keep_dims=True) * (1.0 / rows)
+        asc2.store(d * asc2.rsqrt(var + eps).broadcast_to(rows, cols), out_gm, offsets=[t * rows, 0])
+
+
 def mn_tiles_per_block(m, n, core_num, m_tile, n_tile, n_tiles_per_block):
     """Host-side tile bookkeeping of the M/N-blocked kernel (even distribution over blocks)."""
     m_tiles, n_tiles = m // m_tile, n // n_tile

@@ -208,3 +208,26 @@ def test_whole_tile_reductions_of_half_precision_tiles(op, torch_op, dtype, lib)
     assert lib.asc_cuda_reduce_all_f16(P(xd), P(od), 40, 64, 63, 0, 1, dt, None) == 1        # pitch shorter than a row
     assert lib.asc_cuda_reduce_all_f16(P(xd), P(od), 40, 64, 72, 0, 1, 2, None) == 1         # unknown element type
     assert lib.asc_cuda_reduce_all_f16(P(xd), P(od), 1 << 13, 1 << 12, 1 << 12, 0, 1, dt, None) == 6   # larger than a tile
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16], ids=str)
+def test_softmax_and_standardisation_down_the_columns(dtype):
+    """Reductions along the first axis used inside the expression (`x - reduce_max(x, 0, keep_dims=True)
+    .broadcast_to(...)`): each is computed into a temporary first, then read back as a broadcast row."""
+    import asc2_scripts as K
+    tiles, rows, cols = 4, 64, 256
+    gen = torch.Generator().manual_seed(12)
+    x = torch.randn(tiles * rows, cols, generator=gen).to(dtype)
+    out = torch.zeros_like(x)
+    K.column_softmax[2](x, out, tiles, rows, cols)
+    assert K.column_softmax.last_plan.pattern == "column:statistics"
+    want = torch.softmax(x.float().reshape(tiles, rows, cols), dim=1).reshape(tiles * rows, cols)
+    tol = 1e-5 if dtype == torch.float32 else 2e-3
+    torch.testing.assert_close(out.float(), want, rtol=tol, atol=tol)
+    out2 = torch.zeros_like(x)
+    K.column_standardise[2](x, out2, tiles, rows, cols, 1e-5)
+    t = x.float().reshape(tiles, rows, cols)
+    d = t - t.mean(1, keepdim=True)
+    want2 = (d * torch.rsqrt((d * d).mean(1, keepdim=True) + 1e-5)).reshape(tiles * rows, cols)
+    tol = 1e-5 if dtype == torch.float32 else 4e-3
+    torch.testing.assert_close(out2.float(), want2, rtol=tol, atol=tol)

@@ -323,3 +323,21 @@ def test_atomic_accumulation_of_row_reductions(monkeypatch):
     assert all(s.fn_name == "asc_cuda_row_program" for s in plan.steps)
     # x, x, MUL, ROW_SUM, the row's element of the target, ADD: one stored element per row
     assert list(plan.steps[0].build({0: 0, 1: 0}, None)[0]) == [0, 0, 4, 59, 0, 2]
+
+
+def test_statistics_down_the_columns_plan_reductions_into_temporaries_then_one_program(monkeypatch):
+    monkeypatch.setenv("DRY_RUN", "1")
+    import asc2_scripts as K
+    x = torch.zeros(4 * 64, 256)
+    K.column_softmax[2](x, torch.zeros_like(x), 4, 64, 256)
+    plan = K.column_softmax.last_plan
+    assert plan.pattern == "column:statistics" and plan.reads == {0} and plan.writes == {1}
+    assert plan.temps == {"tmp0": 4 * 64 * 256 * 4, "tmp1": 4 * 64 * 256 * 4}
+    # per tile: the maximum (a loaded fp32 tile: the reduction kernel), the sum of exp(x - max) (a column program
+    # that reads the maximum back as a broadcast row), the quotient (an elementwise program with two broadcast rows)
+    assert [s.fn_name for s in plan.steps] == ["asc_cuda_reduce_f32"] * 4 + ["asc_cuda_col_program"] * 4 + \
+        ["asc_cuda_eltwise_program_2d"] * 4
+    K.column_standardise[2](x.half(), torch.zeros_like(x).half(), 4, 64, 256, 1e-5)
+    plan = K.column_standardise.last_plan
+    assert plan.pattern == "column:statistics" and len(plan.temps) == 2
+    assert [s.fn_name for s in plan.steps] == ["asc_cuda_col_program"] * 8 + ["asc_cuda_eltwise_program_2d"] * 4
