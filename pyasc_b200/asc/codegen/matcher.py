@@ -17,6 +17,7 @@ fallback behind this module.
 from __future__ import annotations
 
 import ctypes
+import threading
 from typing import Any, Callable, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -415,7 +416,29 @@ class _Operand:
 
 # Values that are read back from a temporary device buffer instead of being compiled into the program: node id ->
 # the operand to load.  Filled only while _match_matmul_then_program plans the expression around a matmul.
-_MATERIALISED: Dict[int, "_Operand"] = {}
+class _Materialised(threading.local):
+    """Per thread, so that kernels planned from different threads do not see each other's temporaries."""
+
+    def __init__(self):
+        self.table: Dict[int, "_Operand"] = {}
+
+    def __contains__(self, key: int) -> bool:
+        return key in self.table
+
+    def __getitem__(self, key: int) -> "_Operand":
+        return self.table[key]
+
+    def __setitem__(self, key: int, value: "_Operand") -> None:
+        self.table[key] = value
+
+    def __bool__(self) -> bool:
+        return bool(self.table)
+
+    def clear(self) -> None:
+        self.table.clear()
+
+
+_MATERIALISED = _Materialised()
 
 
 class _EltProgram:
