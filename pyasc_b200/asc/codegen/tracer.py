@@ -114,8 +114,8 @@ class _Signatures:
 def _merge_paths(effects: List[Effect]) -> List[Effect]:
     """Statements after an ``if`` on a run-time scalar are traced once per path, so each shows up as several effects
     that differ only in the outcome of that ``if``.  Two effects that are the same computation under guards that agree
-    except for opposite outcomes of their last condition happen whichever way that condition goes: they become one
-    effect without it (repeatedly, for nests and sequences of ``if``s).  The merged effect takes the place of the
+    except for opposite outcomes of one condition happen whichever way that condition goes: they become one effect
+    without it (repeatedly, for nests and sequences of ``if``s).  The merged effect takes the place of the
     earlier one; the two never both happen for one block and iteration."""
     if not any(e.guards for e in effects):
         return effects
@@ -128,16 +128,24 @@ def _merge_paths(effects: List[Effect]) -> List[Effect]:
         for i, e in enumerate(effects):
             if not e.guards:
                 continue
-            head = tuple((sig.of(c), o) for c, o in e.guards[:-1])
-            cond, outcome = e.guards[-1]
-            key = (sig.of(e), head, sig.of(cond))
-            j = seen.get(key + (not outcome, ))
-            if j is not None:
-                effects[j].guards = effects[j].guards[:-1]
+            body = sig.of(e)
+            conds = [sig.of(c) for c, _ in e.guards]
+            hit = None
+            for k, (_, outcome) in enumerate(e.guards):
+                # the same computation under the same guards except for the other outcome of condition k
+                others = tuple((c, o) for j, ((_, o), c) in enumerate(zip(e.guards, conds)) if j != k)
+                key = (body, k, conds[k], others)
+                j = seen.get(key + (not outcome, ))
+                if j is not None:
+                    hit = (j, k)
+                    break
+                seen[key + (outcome, )] = i
+            if hit is not None:
+                j, k = hit
+                effects[j].guards = effects[j].guards[:k] + effects[j].guards[k + 1:]
                 del effects[i]
                 merged = True
                 break
-            seen[key + (outcome, )] = i
     return effects
 
 

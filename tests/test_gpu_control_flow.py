@@ -86,3 +86,35 @@ def test_count_mask_keeps_the_first_elements_of_every_tile(rows, cols, count):
     inner = torch.where(active, torch.exp(x), torch.tensor(0.5))          # exp under the mask
     want = torch.where(active, inner + 1, torch.tensor(0.5)) * 2          # + 1 under the mask, * 2 outside it
     torch.testing.assert_close(out, want, rtol=2e-6, atol=0)
+
+
+def _leaky(t, slope):
+    """A Python helper called from kernels: it is traced like the kernel's own statements."""
+    return asc2.where(t >= 0, t, t * slope)
+
+
+@asc2.jit
+def spare_blocks_return_early(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, flag_ptr: asc.GlobalAddress, n: int,
+                              tile: asc.ConstExpr[int], active: int):
+    if asc2.block_idx() >= active:
+        return
+    x_gm, out_gm, flag_gm = asc2.tensor(x_ptr, [n]), asc2.tensor(out_ptr, [n]), asc2.tensor(flag_ptr, [tile])
+    if asc2.block_idx() == 0:
+        asc2.store(asc2.full([tile], 1.0, dtype=asc.float32), flag_gm, offsets=[0])
+    for i in range(asc2.block_idx() * tile, n, active * tile):
+        if i + tile <= n:                                         # the ragged tail is left alone
+            asc2.store(_leaky(asc2.load(x_gm, [tile], offsets=[i]), 0.2), out_gm, offsets=[i])
+
+
+def test_early_return_helper_function_and_a_guarded_tail():
+    n, tile = 5000, 256
+    x = torch.randn(n, generator=torch.Generator().manual_seed(14))
+    out, flag = torch.full((n, ), 7.0), torch.zeros(tile)
+    spare_blocks_return_early[8](x, out, flag, n, tile, 3)
+    plan = spare_blocks_return_early.last_plan
+    full = (n // tile) * tile
+    want = torch.full((n, ), 7.0)
+    want[:full] = torch.where(x[:full] >= 0, x[:full], x[:full] * 0.2)
+    assert torch.equal(out, want) and bool((flag == 1).all())
+    # the loop's store is traced on both sides of `if block_idx() == 0` and merges back into one effect: two kernels
+    assert len(plan.steps) == 2, [s.note for s in plan.steps]
