@@ -415,7 +415,8 @@ class _Operand:
 
 
 # Values that are read back from a temporary device buffer instead of being compiled into the program: node id ->
-# the operand to load.  Filled only while _match_matmul_then_program plans the expression around a matmul.
+# the operand to load.  Filled only while _match_matmul_then_program and _match_column_statistics plan the expression
+# around a value they have already planned into a temporary (a matmul result, a reduction along the first axis).
 class _Materialised(threading.local):
     """Per thread, so that kernels planned from different threads do not see each other's temporaries."""
 
