@@ -10,6 +10,8 @@ shapes, scalar values, core_num); ``always_compile=True`` re-traces on every cal
 from __future__ import annotations
 
 import inspect
+import os
+import sys
 from dataclasses import fields
 from typing import Any, Callable, Dict, List, Optional, Tuple, Type, Union
 
@@ -166,6 +168,21 @@ class JITFunction(Function[P, T]):
             self.kernel_cache[key] = plan
         return plan
 
+    def explain(self, plan: Optional[Plan] = None) -> str:
+        """What a launch of this kernel runs: the recognised pattern, the library calls in order, the temporaries."""
+        plan = plan if plan is not None else self.last_plan
+        if plan is None:
+            return f"kernel '{self.fn_name}': not launched yet"
+        lines = [f"kernel '{self.fn_name}' -> {plan.pattern}: {len(plan.steps)} call(s), reads arguments "
+                 f"{sorted(plan.reads, key=str)}, writes {sorted(plan.writes, key=str)}"]
+        lines += [f"  temporary {k}: {v} bytes" for k, v in plan.temps.items()]
+        shown = plan.steps if len(plan.steps) <= 16 else plan.steps[:8] + plan.steps[-4:]
+        for i, step in enumerate(shown):
+            if len(plan.steps) > 16 and i == 8:
+                lines.append(f"  ... {len(plan.steps) - 12} more ...")
+            lines.append(f"  {step.fn_name}: {step.note}")
+        return "\n".join(lines)
+
     def _run(self, *args: P.args, **kwargs: P.kwargs) -> None:
         merged = dict(self.default_options)
         merged.update(kwargs)
@@ -177,6 +194,10 @@ class JITFunction(Function[P, T]):
         runtime_args, constexprs = self.split_args(call_args, get_annotations(self.fn))
         plan = self._cache_kernel(runtime_args, constexprs, codegen_options, compile_options)
         self.last_plan = plan
+        if compile_options.print_ir_before_all or os.environ.get("ASC_CUDA_EXPLAIN"):
+            # the reference prints its IR here (print_ir_before_all, python/asc/runtime/compiler.py); this platform's
+            # counterpart of the IR is the plan: the library calls the launch is made of
+            print(self.explain(plan), file=sys.stderr)
         self.launcher(self.launch_options).run(plan, self.fn_name, tuple(runtime_args.values()))
 
 

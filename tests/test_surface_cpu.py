@@ -341,3 +341,14 @@ def test_statistics_down_the_columns_plan_reductions_into_temporaries_then_one_p
     plan = K.column_standardise.last_plan
     assert plan.pattern == "column:statistics" and len(plan.temps) == 2
     assert [s.fn_name for s in plan.steps] == ["asc_cuda_col_program"] * 8 + ["asc_cuda_eltwise_program_2d"] * 4
+
+
+def test_explain_lists_the_library_calls_of_a_launch(monkeypatch, capsys):
+    monkeypatch.setenv("DRY_RUN", "1")
+    import asc2_scripts as K
+    x = torch.zeros(4 * 64, 256)
+    K.column_softmax[2](x, torch.zeros_like(x), 4, 64, 256, print_ir_before_all=True)     # the reference's option
+    err = capsys.readouterr().err
+    assert "kernel 'column_softmax' -> column:statistics: 12 call(s)" in err and "temporary tmp0: 262144 bytes" in err
+    text = K.column_softmax.explain()
+    assert text.splitlines()[3].strip() == "asc_cuda_reduce_f32: max axis 0 of [64, 256] at (0, 0) -> [0, +256)"
