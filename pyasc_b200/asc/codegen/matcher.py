@@ -1715,10 +1715,10 @@ def _strip_epilogue(value: Tile) -> Tuple[Tile, _Epilogue]:
                     outer_is_col = sv[0] == "col"
             if inner is not None:
                 break
-        if inner is not None:
-            if not outer_is_col:
-                # (acc * b_scale) * a_scale rounds differently from (acc * a_scale) * b_scale
-                raise _unsupported("int8 dequantisation must be written as acc * a_scale[row] * b_scale[col]")
+        if inner is not None and outer_is_col:
+            # (the fused epilogue computes (acc * a_scale[row]) * b_scale[col]; written the other way round the
+            # product rounds differently, and the expression is left to the general path: the int32 product in a
+            # temporary, then an elementwise program that multiplies in the order the kernel wrote)
             epi.row_scale, epi.col_scale = found["row"], found["col"]
             v = inner
     return v, epi

@@ -110,6 +110,32 @@ def test_matmul_fixpipe(m, k, n, dtype):
     torch.testing.assert_close(c, c_ref, atol=1e-3, rtol=1e-3)
 
 
+@asc2.jit(always_compile=True)
+def dequant_scales_in_the_other_order(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, sa_ptr: asc.GlobalAddress,
+                                      sb_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, m: asc.ConstExpr[int],
+                                      n: asc.ConstExpr[int], k: asc.ConstExpr[int]):
+    a_gm, b_gm, out_gm = asc2.tensor(a_ptr, [m, k]), asc2.tensor(b_ptr, [k, n]), asc2.tensor(out_ptr, [m, n])
+    acc = asc2.matmul(asc2.load(a_gm, [m, k], offsets=[0, 0]), asc2.load(b_gm, [k, n], offsets=[0, 0]))
+    sa = asc2.load(asc2.tensor(sa_ptr, [m]), [m], offsets=[0]).reshape(m, 1).broadcast_to(m, n)
+    sb = asc2.load(asc2.tensor(sb_ptr, [n]), [n], offsets=[0]).reshape(1, n).broadcast_to(m, n)
+    asc2.store((acc.to(asc.float32) * sb * sa).to(asc.float16), out_gm, offsets=[0, 0])
+
+
+def test_int8_dequantisation_written_column_scale_first():
+    """(acc * b_scale[col]) * a_scale[row] rounds differently from the fused epilogue's order: it takes the general
+    path (int32 product in a temporary, then a program that multiplies in the order written) and is exact."""
+    gen = torch.Generator().manual_seed(41)
+    m, n, k = 128, 256, 512
+    a = torch.randint(-128, 128, (m, k), generator=gen).to(torch.int8)
+    b = torch.randint(-128, 128, (k, n), generator=gen).to(torch.int8)
+    sa, sb = torch.rand(m, generator=gen) * 0.01 + 0.001, torch.rand(n, generator=gen) * 0.01 + 0.001
+    out = torch.zeros(m, n, dtype=torch.float16)
+    dequant_scales_in_the_other_order[1](a, b, sa, sb, out, m, n, k)
+    assert dequant_scales_in_the_other_order.last_plan.pattern == "matmul+program"
+    acc = (a.to(torch.int32) @ b.to(torch.int32)).to(torch.float32)
+    assert torch.equal(out, ((acc * sb[None, :]) * sa[:, None]).to(torch.float16))
+
+
 def test_k_loop_accumulator_with_an_epilogue_and_glu():
     gen = torch.Generator().manual_seed(77)
     m, n, k = 128, 256, 1024
