@@ -1958,8 +1958,20 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
 def _match_matmul(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     value, out_t = eff.args
     plan = Plan("matmul")
-    if not _plan_matmul_value(trace, value, out_t, eff.attrs["offsets"], eff.loops, plan, eff.guards):
-        return None
+    try:
+        if not _plan_matmul_value(trace, value, out_t, eff.attrs["offsets"], eff.loops, plan, eff.guards):
+            return None
+    except NotImplementedError as refusal:
+        # an epilogue the GEMM kernels do not fuse (an int8 product cast to fp32, a ReLU on one, ...): the general
+        # path computes the bare product into a temporary and finishes the expression with a program
+        if isinstance(value, Tile) and value.node.kind not in ("matmul", "acc"):
+            try:
+                alt = _match_matmul_then_program(trace, eff)
+            except NotImplementedError:
+                alt = None
+            if alt is not None:
+                return alt
+        raise refusal
     return plan
 
 

@@ -136,6 +136,31 @@ def test_int8_dequantisation_written_column_scale_first():
     assert torch.equal(out, ((acc * sb[None, :]) * sa[:, None]).to(torch.float16))
 
 
+@pytest.mark.parametrize("form", ["to_fp32", "relu", "scaled"])
+def test_int8_products_with_epilogues_the_gemm_does_not_fuse(form):
+    """An int8 product cast to fp32, clamped by a ReLU or scaled by a scalar: the GEMM kernels refuse the epilogue, the
+    general path (product in a temporary, then a program) computes it exactly."""
+    body = {"to_fp32": lambda acc: acc.to(asc.float32), "relu": lambda acc: asc2.relu(acc),
+            "scaled": lambda acc: acc.to(asc.float32) * 0.5}[form]
+
+    @asc2.jit
+    def kernel(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, m: asc.ConstExpr[int],
+               n: asc.ConstExpr[int], k: asc.ConstExpr[int]):
+        a_gm, b_gm, out_gm = asc2.tensor(a_ptr, [m, k]), asc2.tensor(b_ptr, [k, n]), asc2.tensor(out_ptr, [m, n])
+        acc = asc2.matmul(asc2.load(a_gm, [m, k], offsets=[0, 0]), asc2.load(b_gm, [k, n], offsets=[0, 0]))
+        asc2.store(body(acc), out_gm, offsets=[0, 0])
+
+    gen = torch.Generator().manual_seed(43)
+    m, n, k = 128, 256, 192
+    a = torch.randint(-128, 128, (m, k), generator=gen).to(torch.int8)
+    b = torch.randint(-128, 128, (k, n), generator=gen).to(torch.int8)
+    acc = a.to(torch.int32) @ b.to(torch.int32)
+    want = {"to_fp32": acc.float(), "relu": acc.relu(), "scaled": acc.float() * 0.5}[form]
+    out = torch.zeros(m, n, dtype=want.dtype)
+    kernel[1](a, b, out, m, n, k)
+    assert kernel.last_plan.pattern == "matmul+program" and torch.equal(out, want)
+
+
 def test_k_loop_accumulator_with_an_epilogue_and_glu():
     gen = torch.Generator().manual_seed(77)
     m, n, k = 128, 256, 1024
