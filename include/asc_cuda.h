@@ -252,6 +252,17 @@ int32_t asc_cuda_gemm_f16(const void* A, const void* B, void* C, int64_t M, int6
                           int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype, int32_t flags,
                           void* stream);
 
+/* asc_cuda_gemm_f16 with a bias row in the epilogue: C = cast(relu?(A @ B + bias[col])), the addition in fp32
+ * (round to nearest) on the fp32 accumulator before the ReLU and the one rounding of the store.  bias holds N
+ * values, one per output column; bias_dtype: 0 fp16, 1 bf16, 2 fp32 (widened to fp32 before the addition); no
+ * alignment rule.  flags: bit0 ReLU; bit1 (accumulate into C) is refused with status 3.  Everything else as
+ * asc_cuda_gemm_f16.  Replaces a matmul whose fixpipe result gets a broadcast row added on the vector unit before
+ * the store (python/asc/language/tile/binary_ops.py:181-221 followed by add, binary_ops.py:112; the reference runs the
+ * addition as a separate vector pass over the product). */
+int32_t asc_cuda_gemm_f16_bias(const void* A, const void* B, void* C, const void* bias, int64_t M, int64_t N,
+                               int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype,
+                               int32_t bias_dtype, int32_t flags, void* stream);
+
 /* asc_cuda_gemm_f16 for callers that cannot allocate device memory while they run: a latency-critical host thread
  * that must never block in the driver's allocator, a service whose device-memory budget was handed out in full at
  * start-up, code under a rule that forbids cudaMalloc after initialisation.  It has no counterpart in the

@@ -1648,6 +1648,7 @@ class _Epilogue:
     out_dtype: Optional[DataType] = None
     row_scale: Optional[GmView] = None   # int8 dequant: per-row scale vector
     col_scale: Optional[GmView] = None   # int8 dequant: per-column scale vector
+    bias: Optional[GmView] = None        # one loaded row added to every row of the product before the ReLU
 
 
 def _peel_identity_copies(tile: Tile) -> Tile:
@@ -1680,6 +1681,26 @@ def _scale_vector(tile: Any, full_shape: Tuple[int, int]) -> Optional[Tuple[str,
     return kind, view
 
 
+def _bias_row(tile: Any, full_shape: Tuple[int, int]) -> Optional[GmView]:
+    """``tile`` is one loaded row (fp32, or fp16 / bf16 cast to fp32) broadcast over the rows of ``full_shape``."""
+    b = _node(tile, "broadcast")
+    if b is None or tile.shape != full_shape or tile.dtype != KT.float32:
+        return None
+    src = b.args[0]
+    if not isinstance(src, Tile) or src.shape != (1, full_shape[1]):
+        return None
+    casts = 0
+    while isinstance(src, Tile) and src.node.kind in ("reshape", "cast"):
+        casts += src.node.kind == "cast"
+        src = src.node.args[0]
+    view = resolve_view(src) if _node(src, "load") else None
+    if view is None or casts > 1 or view.tensor.dtype.name not in _OUT_CODE or not _is_zero_pad(view):
+        return None
+    if tuple(view.shape) not in ((full_shape[1],), (1, full_shape[1])) or len(view.tensor.static_shape()) != len(view.shape):
+        return None
+    return view
+
+
 def _strip_epilogue(value: Tile) -> Tuple[Tile, _Epilogue]:
     epi = _Epilogue()
     epi.out_dtype = value.dtype
@@ -1695,6 +1716,14 @@ def _strip_epilogue(value: Tile) -> Tuple[Tile, _Epilogue]:
             v = r.args[0]
             continue
         break
+    # a bias row on the fp32 product: (a @ b) + row or row + (a @ b)
+    add = _node(v, "binary", op="add")
+    if add is not None and v.dtype == KT.float32 and len(v.shape) == 2:
+        for core, other in ((add.args[0], add.args[1]), (add.args[1], add.args[0])):
+            row = _bias_row(other, v.shape)
+            if row is not None and isinstance(core, Tile) and core.node.kind in ("matmul", "acc"):
+                epi.bias = row
+                return core, epi
     # int8 dequantisation: cast_f32(acc) * row_scale * col_scale (either order)
     m1 = _node(v, "binary", op="mul")
     if m1 is not None and v.dtype == KT.float32 and len(v.shape) == 2:
@@ -1839,6 +1868,14 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
     cols = [ro, co, ar, ak, bk, bc]
     if epi.row_scale is not None:
         cols += [eval_int(epi.row_scale.offsets[0], env, n), eval_int(epi.col_scale.offsets[0], env, n)]
+    if epi.bias is not None:
+        if in_dtype.name not in _DTYPE_CODE_16:
+            raise _unsupported(f"bias row in the epilogue of a {in_dtype} matmul")
+        _check_fits(epi.bias.tensor)
+        bias_ld = epi.bias.tensor.static_shape()[-1]
+        bias_col = eval_int(epi.bias.offsets[-1], env, n)
+        bias_row = eval_int(epi.bias.offsets[0], env, n) if len(epi.bias.offsets) == 2 else np.zeros(n, dtype=np.int64)
+        cols += [bias_row, bias_col]
     inst = np.unique(np.stack(cols, axis=1), axis=0)   # identical instances (e.g. every block) collapse
     if inst.size and inst.min() < 0:
         raise RuntimeError("Negative tile offset in kernel")
@@ -1848,6 +1885,12 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
     if epi.row_scale is not None and (np.any(inst[:, 6] != ar) or np.any(inst[:, 7] != bc)
                                       or epi.row_scale.shape[0] != mt or epi.col_scale.shape[0] != nt):
         raise _unsupported("dequantisation scales that are not indexed by the tile's rows / columns")
+    bias_at = np.zeros(inst.shape[0], dtype=np.int64)     # element offset of each tile's first bias value
+    if epi.bias is not None:
+        rows_of_bias = epi.bias.tensor.static_shape()[0] if len(epi.bias.offsets) == 2 else 1
+        if np.any(inst[:, 6] >= rows_of_bias) or np.any(inst[:, 7] + np.minimum(nt, c_cols - co) > bias_ld):
+            raise _unsupported("bias row that reaches past the end of its tensor (zero padding)")
+        bias_at = inst[:, 6] * bias_ld + inst[:, 7]
     k_eff = np.minimum(np.minimum(a_w.cols, a_cols - ak), b_rows - bk)
     m_eff = np.minimum(mt, c_rows - ro)
     n_eff = np.minimum(nt, c_cols - co)
@@ -1862,6 +1905,7 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
     ru, cu = np.unique(ro[keep]), np.unique(co[keep])
     grid_ok = (keep.all() and inst.shape[0] == ru.size * cu.size and np.all(ak == ak[0]) and np.all(bk == bk[0]) and
                np.all(k_eff == k_eff[0]) and np.all(ar - ro == ar[0] - ro[0]) and np.all(bc - co == bc[0] - co[0]) and
+               (epi.bias is None or np.all(bias_at - co == bias_at[0] - co[0])) and
                np.array_equal(ru, ru[0] + mt * np.arange(ru.size)) and
                np.array_equal(cu, cu[0] + nt * np.arange(cu.size)) and
                np.unique(np.stack([ro, co], axis=1), axis=0).shape[0] == inst.shape[0])
@@ -1869,11 +1913,11 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
         M = int(min(ru[-1] + mt, c_rows) - ru[0])
         N = int(min(cu[-1] + nt, c_cols) - cu[0])
         calls.append((int(ru[0]), int(cu[0]), int(ru[0] + ar[0] - ro[0]), int(cu[0] + bc[0] - co[0]), int(ak[0]),
-                      M, N, int(k_eff[0]), int(bk[0])))
+                      M, N, int(k_eff[0]), int(bk[0]), int(cu[0] + bias_at[0] - co[0])))
     else:
         for i in np.nonzero(keep)[0]:
             calls.append((int(ro[i]), int(co[i]), int(ar[i]), int(bc[i]), int(ak[i]), int(m_eff[i]), int(n_eff[i]),
-                          int(k_eff[i]), int(bk[i])))
+                          int(k_eff[i]), int(bk[i]), int(bias_at[i])))
         if len(calls) > MAX_CALLS:
             raise _unsupported("matmul kernel whose tiles do not form a grid and exceed 4096 calls")
         if calls:
@@ -1894,7 +1938,11 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
     osz = out_t.dtype.sizeof()
     lda, ldb, ldc = a_cols, b_cols, c_cols
     flags = 1 if epi.relu else 0
-    sa_idx = sb_idx = None
+    sa_idx = sb_idx = bias_idx = None
+    if epi.bias is not None:
+        bias_idx, bias_code = epi.bias.tensor.base.index, _OUT_CODE[epi.bias.tensor.dtype.name]
+        bias_size = epi.bias.tensor.dtype.sizeof()
+        plan.reads.add(bias_idx)
     if in_dtype == KT.int8:
         if epi.relu:
             raise _unsupported("ReLU on an int8 matmul")
@@ -1909,7 +1957,8 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
     else:
         raise _unsupported(f"matmul on {in_dtype} operands")
 
-    def gemm_step(r0: int, c0: int, a0: int, b0: int, k0: int, M: int, N: int, K: int, kb: Optional[int] = None) -> Step:
+    def gemm_step(r0: int, c0: int, a0: int, b0: int, k0: int, M: int, N: int, K: int, kb: Optional[int] = None,
+                  bias0: int = 0) -> Step:
         kb = k0 if kb is None else kb         # first row of B's K range
         a_off, b_off, c_off = (a0 * lda + k0) * es, (kb * ldb + b0) * es, (r0 * ldc + c0) * osz
         dims = (ctypes.c_int64(M), ctypes.c_int64(N), ctypes.c_int64(K), ctypes.c_int64(lda), ctypes.c_int64(ldb),
@@ -1932,6 +1981,12 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
                         ctypes.c_int32(oc), ctypes.c_int32(flags), stream)
             return Step("asc_cuda_gemm_f32", build, note)
         ic = _DTYPE_CODE_16[in_dtype.name]
+        if bias_idx is not None:
+            def build(ptrs, stream):
+                return (_p(ptrs[a_idx] + a_off), _p(ptrs[b_idx] + b_off), _p(ptrs[c_idx] + c_off),
+                        _p(ptrs[bias_idx] + bias0 * bias_size), *dims, ctypes.c_int32(ic), ctypes.c_int32(oc),
+                        ctypes.c_int32(bias_code), ctypes.c_int32(flags), stream)
+            return Step("asc_cuda_gemm_f16_bias", build, note + f" + bias[{bias0}:{bias0 + N}]")
 
         def build(ptrs, stream):
             return (_p(ptrs[a_idx] + a_off), _p(ptrs[b_idx] + b_off), _p(ptrs[c_idx] + c_off), *dims,
@@ -1943,15 +1998,18 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
     # one full-output call whose operands are plain global tensors: rows of A and C can be streamed
     if (len(calls) == 1 and c_idx not in plan.partial_writes and calls[0][2] == 0 and calls[0][3] == 0 and
             calls[0][4] == 0 and calls[0][8] == 0 and all(isinstance(i, int) for i in (a_idx, b_idx, c_idx)) and
-            len({a_idx, b_idx, c_idx}) == 3 and in_dtype != KT.float32):
-        _, _, _, _, _, M, N, K, _ = calls[0]
+            len({a_idx, b_idx, c_idx}) == 3 and in_dtype != KT.float32 and
+            (bias_idx is None or (isinstance(bias_idx, int) and bias_idx not in (a_idx, c_idx)))):
+        _, _, _, _, _, M, N, K, _, bias_first = calls[0]
         streamed = {a_idx: lda * es, c_idx: ldc * osz}
         resident = {b_idx}
         if sa_idx is not None:
             streamed[sa_idx] = 4
             resident.add(sb_idx)
+        if bias_idx is not None:
+            resident.add(bias_idx)
         plan.pipeline = PipelineSpec(M, 256, streamed, resident,
-                                     lambda lo, hi: [gemm_step(lo, 0, lo, 0, 0, hi - lo, N, K)])
+                                     lambda lo, hi: [gemm_step(lo, 0, lo, 0, 0, hi - lo, N, K, None, bias_first)])
     return True
 
 

@@ -64,6 +64,8 @@ PROTOTYPES: Dict[str, Sequence] = {
     "asc_cuda_rms_norm_f16": (P, P, P, c_int64, c_int64, c_int64, c_float, P),
     "asc_cuda_gemm_f16": (P, P, P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32,
                           c_int32, P),
+    "asc_cuda_gemm_f16_bias": (P, P, P, P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32,
+                               c_int32, c_int32, P),
     "asc_cuda_gemm_f16_static_workspace": (P, P, P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32,
                                            c_int32, P),
     "asc_cuda_gemm_f32": (P, P, P, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32, P),

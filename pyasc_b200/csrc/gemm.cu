@@ -56,6 +56,8 @@ struct GemmParams {
   const float* b_scale; // EPI_I8 only: per-column scale
   int64_t M, N, K;      // K in elements
   int64_t ldc;
+  const void* bias;     // one value per output column, added before the ReLU (nullable); see bias_type
+  int32_t bias_type;    // 0 none, 1 fp32, 2 fp16, 3 bf16
   int32_t relu;
   int32_t accumulate;   // EPI_F32 only: C += A @ B
   int32_t vec_ok;       // 16-byte vector stores allowed (alignment of c/deq and ldc)
@@ -87,6 +89,20 @@ __device__ __forceinline__ void tile_coords(int64_t tile, int64_t num_m, int64_t
   n_blk = r / gm;
 }
 
+__device__ __forceinline__ float bias_at(const void* bias, int32_t bias_type, int64_t col) {
+  if (bias_type == 1) return __ldg(static_cast<const float*>(bias) + col);
+  if (bias_type == 2) return __half2float(__ldg(static_cast<const __half*>(bias) + col));
+  return __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(bias) + col));
+}
+
+// The floating-point epilogue of one element of output column `col`: the bias row, then the ReLU (a NaN stays a
+// NaN, as in torch.relu).
+__device__ __forceinline__ float epi_finish(const GemmParams& p, float v, int64_t col) {
+  if (p.bias_type != 0 && col < p.N) v = __fadd_rn(v, bias_at(p.bias, p.bias_type, col));
+  if (p.relu) v = v < 0.f ? 0.f : v;
+  return v;
+}
+
 template <int kMode>
 __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const uint32_t (&r)[32], int64_t row,
                                                      int64_t col0) {
@@ -97,11 +113,8 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const 
     uint32_t packed[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      float a = __uint_as_float(r[2 * i]), b = __uint_as_float(r[2 * i + 1]);
-      if (p.relu) {
-        a = fmaxf(a, 0.f);
-        b = fmaxf(b, 0.f);
-      }
+      const float a = epi_finish(p, __uint_as_float(r[2 * i]), col0 + 2 * i);
+      const float b = epi_finish(p, __uint_as_float(r[2 * i + 1]), col0 + 2 * i + 1);
       if (kMode == EPI_F16) {
         __half2 h = __floats2half2_rn(a, b);
         packed[i] = *reinterpret_cast<uint32_t*>(&h);
@@ -131,9 +144,9 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const 
       for (int i = 0; i < 32; ++i)
         if (col0 + i < p.N) v[i] += dst[i];
     }
-    if (p.relu) {
+    if (p.relu || p.bias_type != 0) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = fmaxf(v[i], 0.f);
+      for (int i = 0; i < 32; ++i) v[i] = epi_finish(p, v[i], col0 + i);
     }
     if (full) {
 #pragma unroll
@@ -378,14 +391,11 @@ __device__ __forceinline__ void staged_store_64cols(uint32_t stage_smem, const u
 }
 
 template <int kMode>
-__device__ __forceinline__ void pack16(const GemmParams& p, const uint32_t (&r)[32], uint32_t* packed) {
+__device__ __forceinline__ void pack16(const GemmParams& p, const uint32_t (&r)[32], uint32_t* packed, int64_t col0) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
-    float a = __uint_as_float(r[2 * i]), b = __uint_as_float(r[2 * i + 1]);
-    if (p.relu) {
-      a = fmaxf(a, 0.f);
-      b = fmaxf(b, 0.f);
-    }
+    const float a = epi_finish(p, __uint_as_float(r[2 * i]), col0 + 2 * i);
+    const float b = epi_finish(p, __uint_as_float(r[2 * i + 1]), col0 + 2 * i + 1);
     if (kMode == EPI_F16) {
       __half2 h = __floats2half2_rn(a, b);
       packed[i] = *reinterpret_cast<uint32_t*>(&h);
@@ -572,8 +582,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
           tmem_ld_32x32b_x32(taddr + c * 64, r0);
           tmem_ld_32x32b_x32(taddr + c * 64 + 32, r1);
           tmem_ld_wait();
-          pack16<kMode>(p, r0, packed);
-          pack16<kMode>(p, r1, packed + 16);
+          pack16<kMode>(p, r0, packed, n_blk * kBlockN + c * 64);
+          pack16<kMode>(p, r1, packed + 16, n_blk * kBlockN + c * 64 + 32);
           staged_store_64cols(stage_smem, packed, reinterpret_cast<uint16_t*>(p.c), p.ldc, row0, n_blk * kBlockN + c * 64,
                               lane);
         }
@@ -643,18 +653,14 @@ __device__ __forceinline__ void splitk_store_pair(const GemmParams& p, int64_t r
       a += dst[0];
       if (two) b += dst[1];
     }
-    if (p.relu) {
-      a = fmaxf(a, 0.f);
-      b = fmaxf(b, 0.f);
-    }
+    a = epi_finish(p, a, col);
+    b = epi_finish(p, b, col + 1);
     dst[0] = a;
     if (two) dst[1] = b;
     return;
   }
-  if (p.relu) {
-    a = fmaxf(a, 0.f);
-    b = fmaxf(b, 0.f);
-  }
+  a = epi_finish(p, a, col);
+  b = epi_finish(p, b, col + 1);
   if (kMode == EPI_F16) {
     __half* dst = reinterpret_cast<__half*>(p.c) + row * p.ldc + col;
     dst[0] = __float2half_rn(a);
@@ -673,10 +679,8 @@ __device__ __forceinline__ void splitk_store_quad(const GemmParams& p, int64_t r
   if (p.vec_ok && col + 4 <= p.N) {
     if (kMode == EPI_F16 || kMode == EPI_BF16) {
       float f[4] = {__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w)};
-      if (p.relu) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) f[i] = fmaxf(f[i], 0.f);
-      }
+      for (int i = 0; i < 4; ++i) f[i] = epi_finish(p, f[i], col + i);
       uint2 w;
       if (kMode == EPI_F16) {
         const __half2 a = __floats2half2_rn(f[0], f[1]), b = __floats2half2_rn(f[2], f[3]);
@@ -690,7 +694,8 @@ __device__ __forceinline__ void splitk_store_quad(const GemmParams& p, int64_t r
     }
     if (kMode == EPI_F32 && !p.accumulate) {
       float4 f = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
-      if (p.relu) f = make_float4(fmaxf(f.x, 0.f), fmaxf(f.y, 0.f), fmaxf(f.z, 0.f), fmaxf(f.w, 0.f));
+      f = make_float4(epi_finish(p, f.x, col), epi_finish(p, f.y, col + 1), epi_finish(p, f.z, col + 2),
+                      epi_finish(p, f.w, col + 3));
       *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.c) + row * p.ldc + col) = f;
       return;
     }
@@ -952,7 +957,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
     gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ B, void* __restrict__ C, int64_t M,
                      int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int out_dtype, int relu,
-                     int accumulate) {
+                     int accumulate, const void* __restrict__ bias, int bias_type) {
   __shared__ float as[32][33];
   __shared__ float bs[32][33];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
@@ -982,6 +987,7 @@ __global__ void __launch_bounds__(256)
     if (r < M && c < N) {
       float v = acc[i];
       if (accumulate && out_dtype == 2) v += reinterpret_cast<float*>(C)[r * ldc + c];
+      if (bias_type != 0) v = __fadd_rn(v, bias_at(bias, bias_type, c));
       if (relu) v = v < 0.f ? 0.f : v;          // NaN stays NaN, as in torch.relu
       if (out_dtype == 2) {
         reinterpret_cast<float*>(C)[r * ldc + c] = v;
@@ -996,11 +1002,13 @@ __global__ void __launch_bounds__(256)
 
 template <typename T>
 int32_t launch_gemm_simt(const T* A, const T* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
-                         int64_t ldc, int32_t out_dtype, int32_t flags, cudaStream_t stream) {
+                         int64_t ldc, int32_t out_dtype, int32_t flags, cudaStream_t stream, const void* bias = nullptr,
+                         int32_t bias_type = 0) {
   const int64_t gx = (N + 31) / 32, gy = (M + 31) / 32;
   if (gy > 65535) return ASC_ERR_TOO_LARGE;
   dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
-  gemm_simt_kernel<T><<<grid, 256, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc, out_dtype, flags & 1, (flags >> 1) & 1);
+  gemm_simt_kernel<T><<<grid, 256, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc, out_dtype, flags & 1, (flags >> 1) & 1,
+                                                bias, bias_type);
   aschost::count_launch();
   ASC_CUDA_TRY(cudaGetLastError());
   return ASC_OK;
@@ -1268,13 +1276,9 @@ int32_t check_gemm_args(const void* A, const void* B, int64_t M, int64_t N, int6
   return ASC_OK;
 }
 
-}  // namespace
-
-extern "C" {
-
-int32_t asc_cuda_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
-                          int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype, int32_t flags,
-                          void* stream) {
+int32_t gemm_f16_entry(const void* A, const void* B, void* C, const void* bias, int32_t bias_type, int64_t M, int64_t N,
+                       int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype,
+                       int32_t flags, void* stream) {
   if (C == nullptr) return ASC_ERR_INVALID_ARG;
   if (in_dtype < 0 || in_dtype > 1 || out_dtype < 0 || out_dtype > 2 || (flags & ~3) != 0) return ASC_ERR_INVALID_ARG;
   if ((flags & 2) && out_dtype != 2) return ASC_ERR_UNSUPPORTED;
@@ -1287,6 +1291,8 @@ int32_t asc_cuda_gemm_f16(const void* A, const void* B, void* C, int64_t M, int6
   p.K = K;
   p.ldc = ldc;
   p.relu = flags & 1;
+  p.bias = bias;
+  p.bias_type = bias_type;
   p.accumulate = (flags >> 1) & 1;
   const int out_bytes = out_dtype == 2 ? 4 : 2;
   p.vec_ok = aschost::aligned16(C) && ((ldc * out_bytes) % 16 == 0);
@@ -1297,15 +1303,35 @@ int32_t asc_cuda_gemm_f16(const void* A, const void* B, void* C, int64_t M, int6
     // a small product whose fp32 result the caller keeps: exact products, round-to-nearest sums
     if (in_dtype == 0)
       return launch_gemm_simt<__half>(static_cast<const __half*>(A), static_cast<const __half*>(B), C, M, N, K, lda, ldb,
-                                      ldc, out_dtype, flags, s);
+                                      ldc, out_dtype, flags, s, bias, bias_type);
     return launch_gemm_simt<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(B), C, M,
-                                           N, K, lda, ldb, ldc, out_dtype, flags, s);
+                                           N, K, lda, ldb, ldc, out_dtype, flags, s, bias, bias_type);
   }
   switch (out_dtype) {
     case 0: return dispatch_gemm<2, EPI_F16>(A, B, lda, ldb, dt, 1, in_dtype, p, 0, s);
     case 1: return dispatch_gemm<2, EPI_BF16>(A, B, lda, ldb, dt, 1, in_dtype, p, 0, s);
     default: return dispatch_gemm<2, EPI_F32>(A, B, lda, ldb, dt, 1, in_dtype, p, 0, s);
   }
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t asc_cuda_gemm_f16(const void* A, const void* B, void* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                          int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype, int32_t flags,
+                          void* stream) {
+  return gemm_f16_entry(A, B, C, nullptr, 0, M, N, K, lda, ldb, ldc, in_dtype, out_dtype, flags, stream);
+}
+
+int32_t asc_cuda_gemm_f16_bias(const void* A, const void* B, void* C, const void* bias, int64_t M, int64_t N,
+                               int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int32_t in_dtype, int32_t out_dtype,
+                               int32_t bias_dtype, int32_t flags, void* stream) {
+  if (bias == nullptr || bias_dtype < 0 || bias_dtype > 2) return ASC_ERR_INVALID_ARG;
+  if (flags & 2) return ASC_ERR_UNSUPPORTED;              // C += A @ B + bias: the caller adds the bias once instead
+  // bias_dtype: 0 fp16, 1 bf16, 2 fp32 (the codes of out_dtype)
+  return gemm_f16_entry(A, B, C, bias, bias_dtype == 2 ? 1 : bias_dtype == 0 ? 2 : 3, M, N, K, lda, ldb, ldc, in_dtype,
+                        out_dtype, flags, stream);
 }
 
 // The split-K GEMM for callers that must not allocate: its workspace is the file-scope array below, which every

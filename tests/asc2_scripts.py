@@ -163,6 +163,29 @@ def matmul_k_tiled_bias_relu(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress,
 
 
 @asc2.jit(always_compile=True)
+def linear_mn_tiles(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, bias_ptr: asc.GlobalAddress,
+                    c_ptr: asc.GlobalAddress, m: int, n: asc.ConstExpr[int], k: asc.ConstExpr[int],
+                    m_tile: asc.ConstExpr[int], n_tile: asc.ConstExpr[int], relu: asc.ConstExpr[int],
+                    out_dtype: asc.ConstExpr):
+    """A linear layer tiled over M and N: every tile adds its own slice of a bias vector (of any floating type,
+    widened to fp32) to the product, then an optional ReLU and a cast."""
+    a_gm, b_gm, c_gm = asc2.tensor(a_ptr, [m, k]), asc2.tensor(b_ptr, [k, n]), asc2.tensor(c_ptr, [m, n])
+    bias_gm = asc2.tensor(bias_ptr, [n])
+    n_blocks = asc.ceildiv(n, n_tile)
+    for t in range(asc2.block_idx(), asc.ceildiv(m, m_tile) * n_blocks, asc2.block_num()):
+        i, j = (t // n_blocks) * m_tile, (t % n_blocks) * n_tile
+        a = asc2.load(a_gm, [m_tile, k], offsets=[i, 0])
+        b = asc2.load(b_gm, [k, n_tile], offsets=[0, j])
+        bias = asc2.load(bias_gm, [n_tile], offsets=[j]).to(asc.float32)
+        v = bias.reshape(1, n_tile).broadcast_to(m_tile, n_tile) + asc2.matmul(a, b)
+        if relu:
+            v = asc2.relu(v)
+        if out_dtype != asc.float32:
+            v = v.to(out_dtype)
+        asc2.store(v, c_gm, offsets=[i, j])
+
+
+@asc2.jit(always_compile=True)
 def glu_rows(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: int, cols: asc.ConstExpr[int],
              rpt: asc.ConstExpr[int]):
     """A gated linear unit: the two halves of every row of x, a * sigmoid(g)."""

@@ -186,12 +186,34 @@ def test_matmul_batched_loop(batch, m, n, k):
     torch.testing.assert_close(c.reshape(batch, m, n), torch.bmm(a.float(), b.float()), atol=2e-3, rtol=2e-3)
 
 
+@pytest.mark.parametrize("bias_dtype", [torch.float32, torch.float16, torch.bfloat16], ids=str)
+@pytest.mark.parametrize("m, n, k, m_tile, n_tile, relu, out_dtype, torch_dtype", [
+    (512, 768, 128, 128, 256, 1, asc.float16, torch.float16), (500, 704, 128, 128, 256, 0, asc.float32, torch.float32),
+    (2048, 2048, 1024, 256, 512, 1, asc.bfloat16, torch.bfloat16), (96, 160, 64, 32, 32, 1, asc.float32, torch.float32)])
+def test_linear_layer_tiled_over_m_and_n_with_bias_slices(m, n, k, m_tile, n_tile, relu, out_dtype, torch_dtype, bias_dtype):
+    """Every tile adds its own slice of the bias vector: the tiles merge into one GEMM call with the bias row in its
+    epilogue.  Golden: the expression in torch on the CPU, fp32 accumulation."""
+    gen = torch.Generator().manual_seed(m + n)
+    a = ((torch.rand(m, k, generator=gen) - .5) * 2 * k ** -0.5).half()
+    b = (torch.rand(k, n, generator=gen) - .5).half()
+    bias = torch.randn(n, generator=gen).to(bias_dtype)
+    c = torch.zeros(m, n, dtype=torch_dtype)
+    K.linear_mn_tiles[8](a, b, bias, c, m, n, k, m_tile, n_tile, relu, out_dtype)
+    plan = K.linear_mn_tiles.last_plan
+    assert plan.pattern == "matmul" and [s.fn_name for s in plan.steps] == ["asc_cuda_gemm_f16_bias"]
+    t = a.float() @ b.float() + bias.float()
+    t = (t.relu() if relu else t).to(torch_dtype)
+    tol = 1.6e-2 if torch_dtype == torch.bfloat16 else 2e-3
+    torch.testing.assert_close(c, t, atol=tol, rtol=tol)
+
+
 @pytest.mark.parametrize("out_dtype, torch_dtype", [(asc.float32, torch.float32), (asc.float16, torch.float16)], ids=str)
 @pytest.mark.parametrize("mode", [0, 1, 2, 3])
 @pytest.mark.parametrize("m, n, k, m_tile", [(512, 256, 128, 64), (2048, 1024, 2048, 128)])
 def test_matmul_bias_activation(m, n, k, m_tile, mode, out_dtype, torch_dtype):
-    """A product followed by a bias row and an activation (and a residual, and a cast): the GEMM writes fp32 to a
-    temporary, one elementwise program finishes the expression.  Golden: the same expression in torch on the CPU."""
+    """A product followed by a bias row and an activation (and a residual, and a cast).  The bias row, a ReLU and the
+    cast ride in the GEMM's epilogue; for any other activation the GEMM writes fp32 to a temporary and one elementwise
+    program finishes the expression.  Golden: the same expression in torch on the CPU."""
     gen = torch.Generator().manual_seed(m + mode)
     a = ((torch.rand(m, k, generator=gen) - .5) * 2 * k ** -0.5).half()
     b = (torch.rand(k, n, generator=gen) - .5).half()
@@ -199,7 +221,7 @@ def test_matmul_bias_activation(m, n, k, m_tile, mode, out_dtype, torch_dtype):
     res = torch.randn(m, n, generator=gen)
     c = torch.zeros(m, n, dtype=torch_dtype)
     K.matmul_bias_act[8](a, b, bias, res, c, m, n, k, m_tile, mode, out_dtype)
-    assert K.matmul_bias_act.last_plan.pattern == "matmul+program"
+    assert K.matmul_bias_act.last_plan.pattern == ("matmul" if mode < 2 else "matmul+program")
     t = a.float() @ b.float() + bias
     if mode == 1:
         t = t.relu()

@@ -261,6 +261,67 @@ def test_gemm_f16_split_k(lib, m, n, k, out_dtype):
         assert torch.equal(acc, c + plain)
 
 
+def gemm16_bias(lib, a, b, bias, out_dtype, flags=0):
+    m, k = a.shape
+    n = b.shape[1]
+    c = torch.full((m, n), -7.0, dtype=out_dtype, device="cuda")
+    code = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+    run(lib, "asc_cuda_gemm_f16_bias", P(a), P(b), P(c), P(bias), m, n, k, k, n, n, code[a.dtype], code[out_dtype],
+        code[bias.dtype], flags)
+    return c
+
+
+@pytest.mark.parametrize("m, n, k", [(16, 16, 16), (129, 264, 72), (256, 256, 8192), (1024, 1024, 1024),
+                                     (2048, 4096, 512), (300, 8, 4096), (500, 704, 128)])
+@pytest.mark.parametrize("bias_dtype", [torch.float32, torch.float16, torch.bfloat16], ids=str)
+def test_gemm_f16_bias_row_in_the_epilogue(lib, m, n, k, bias_dtype):
+    """C = cast(relu?(A @ B + bias)): the same accumulators as the plain product, one fp32 addition rounded to
+    nearest, then the ReLU and the one rounding of the store, so the result equals the fp32 product finished in
+    torch bit for bit, in every kernel variant (one CTA per tile, CTA pairs, split-K, the FMA pipe)."""
+    a, b = G.gemm_f16_inputs(m, n, k, seed=m + k)
+    ad, bd = dev(a), dev(b)
+    bias = (torch.randn(n, generator=torch.Generator().manual_seed(n)) * 0.5).to(bias_dtype).cuda()
+    for mode in (0x10, 0):                                  # fp32 results from the tensor core, then as dispatched
+        assert lib.asc_cuda_gemm_set_mode(mode) == 0
+        try:
+            plain = gemm16(lib, ad, bd, torch.float32)
+            outs = (torch.float32, torch.float16, torch.bfloat16) if mode else (torch.float32, )
+            for out_dtype in outs:
+                for relu in (0, 1):
+                    got = gemm16_bias(lib, ad, bd, bias, out_dtype, flags=relu)
+                    want = plain + bias.float()
+                    want = (want.relu() if relu else want).to(out_dtype)
+                    assert torch.equal(got, want), (hex(mode), out_dtype, relu)
+        finally:
+            assert lib.asc_cuda_gemm_set_mode(0) == 0
+    ref = G.gemm_f32acc(a, b) + bias.float().cpu()          # ... and against the CPU expression
+    got = gemm16_bias(lib, ad, bd, bias, torch.float16, flags=1)
+    G.assert_half_close(got, ref.relu().half())
+
+
+def test_gemm_f16_bias_argument_checks_and_nan(lib):
+    a, b = G.gemm_f16_inputs(256, 512, 384)
+    ad, bd = dev(a), dev(b)
+    bias = torch.zeros(512, device="cuda")
+    c = torch.zeros(256, 512, device="cuda")
+    args = (256, 512, 384, 384, 512, 512, 0, 2)
+    assert lib.asc_cuda_gemm_f16_bias(P(ad), P(bd), P(c), None, *args, 2, 0, None) == 1       # no bias
+    assert lib.asc_cuda_gemm_f16_bias(P(ad), P(bd), P(c), P(bias), *args, 3, 0, None) == 1    # bad bias type
+    assert lib.asc_cuda_gemm_f16_bias(P(ad), P(bd), P(c), P(bias), *args, 2, 2, None) == 3    # C += ... + bias
+    # a NaN in the accumulator stays a NaN through the ReLU, as in torch.relu (fmaxf would have returned 0)
+    ad[3, 5] = float("nan")
+    for out_dtype in (torch.float32, torch.float16):
+        for mode in (0, 0x10):
+            assert lib.asc_cuda_gemm_set_mode(mode) == 0
+            try:
+                got = gemm16_bias(lib, ad, bd, bias, out_dtype, flags=1)
+                plain = gemm16(lib, ad, bd, out_dtype, flags=1)
+            finally:
+                assert lib.asc_cuda_gemm_set_mode(0) == 0
+            for t in (got, plain):
+                assert t[3].isnan().all() and not t[:3].isnan().any() and not t[4:].isnan().any()
+
+
 def test_gemm_f16_full_size(lib):
     m = n = k = 8192
     a, b = G.gemm_f16_inputs(m, n, k)

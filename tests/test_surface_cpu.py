@@ -216,13 +216,23 @@ def test_config_backend_selection():
 
 
 def test_matmul_followed_by_an_elementwise_expression_plans_a_product_and_a_program(monkeypatch):
-    """bias + activation (+ residual, + cast) after a matmul is not one of the GEMM epilogues: the product goes to a
-    temporary fp32 matrix of the result's shape and one elementwise program reads it back."""
+    """A bias row, a ReLU and a cast ride in the GEMM's epilogue (one step).  Any other activation (+ residual) after
+    a matmul is not one of the GEMM epilogues: the product goes to a temporary fp32 matrix of the result's shape and
+    one elementwise program reads it back."""
     monkeypatch.setenv("DRY_RUN", "1")
     import asc2_scripts as K
     m, n, k = 512, 256, 128
     a, b = torch.zeros(m, k, dtype=torch.float16), torch.zeros(k, n, dtype=torch.float16)
-    for mode, reads in ((0, {0, 1, 2}), (1, {0, 1, 2}), (2, {0, 1, 2}), (3, {0, 1, 2, 3})):
+    for mode in (0, 1):
+        for out_dtype, torch_dtype in ((asc.float32, torch.float32), (asc.float16, torch.float16)):
+            K.matmul_bias_act[4](a, b, torch.zeros(1, n), torch.zeros(m, n), torch.zeros(m, n, dtype=torch_dtype), m, n, k,
+                                 64, mode, out_dtype)
+            plan = K.matmul_bias_act.last_plan
+            assert plan.pattern == "matmul" and [s.fn_name for s in plan.steps] == ["asc_cuda_gemm_f16_bias"]
+            assert plan.steps[0].note == "C[0:512, 0:256] = A[0:, 0:128] @ B[0:, 0:] + bias[0:256]"
+            assert plan.reads == {0, 1, 2} and plan.writes == {4} and not plan.temps and not plan.partial_writes
+            assert plan.pipeline is not None and 2 in plan.pipeline.resident
+    for mode, reads in ((2, {0, 1, 2}), (3, {0, 1, 2, 3})):
         for out_dtype, torch_dtype in ((asc.float32, torch.float32), (asc.float16, torch.float16)):
             K.matmul_bias_act[4](a, b, torch.zeros(1, n), torch.zeros(m, n), torch.zeros(m, n, dtype=torch_dtype), m, n, k, 64,
                                  mode, out_dtype)
@@ -241,6 +251,49 @@ def test_matmul_followed_by_an_elementwise_expression_plans_a_product_and_a_prog
     h = torch.zeros(64, 64, dtype=torch.float16)
     with pytest.raises(NotImplementedError, match="several matmul results"):
         two_products[1](h, h, torch.zeros(64, 64))
+
+
+def test_bias_slices_of_an_mn_tiled_linear_layer_merge_or_stay_per_tile(monkeypatch):
+    monkeypatch.setenv("DRY_RUN", "1")
+    import asc2_scripts as K
+    h = torch.float16
+    a, b = torch.zeros(512, 128, dtype=h), torch.zeros(128, 768, dtype=h)
+    for bias_dtype in (torch.float32, torch.float16, torch.bfloat16):
+        K.linear_mn_tiles[8](a, b, torch.zeros(768, dtype=bias_dtype), torch.zeros(512, 768, dtype=h), 512, 768, 128,
+                             128, 256, 1, asc.float16)
+        plan = K.linear_mn_tiles.last_plan        # the tiles form a grid and every tile's bias slice starts at its column
+        assert plan.pattern == "matmul" and [s.note for s in plan.steps] == \
+            ["C[0:512, 0:768] = A[0:, 0:128] @ B[0:, 0:] + bias[0:768]"]
+    # ragged edges: 500 x 700 in 128 x 256 tiles is still one call, clipped to the tensor
+    K.linear_mn_tiles[8](torch.zeros(500, 128, dtype=h), torch.zeros(128, 704, dtype=h), torch.zeros(704),
+                         torch.zeros(500, 704), 500, 704, 128, 128, 256, 0, asc.float32)
+    assert [s.note for s in K.linear_mn_tiles.last_plan.steps] == ["C[0:500, 0:704] = A[0:, 0:128] @ B[0:, 0:] + bias[0:704]"]
+
+    # a bias row that is not the tile's own columns of one vector: per-tile calls, each with its own slice
+    @asc2.jit
+    def shifted_bias(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, bias_ptr: asc.GlobalAddress, c_ptr: asc.GlobalAddress):
+        a_gm, b_gm, c_gm = asc2.tensor(a_ptr, [128, 64]), asc2.tensor(b_ptr, [64, 512]), asc2.tensor(c_ptr, [128, 512])
+        bias_gm = asc2.tensor(bias_ptr, [2, 256])
+        for j in range(2):
+            x = asc2.load(a_gm, [128, 64], offsets=[0, 0])
+            y = asc2.load(b_gm, [64, 256], offsets=[0, 256 * j])
+            row = asc2.load(bias_gm, [1, 256], offsets=[1 - j, 0])
+            asc2.store(asc2.matmul(x, y) + row.broadcast_to(128, 256), c_gm, offsets=[0, 256 * j])
+    shifted_bias[1](torch.zeros(128, 64, dtype=h), torch.zeros(64, 512, dtype=h), torch.zeros(2, 256), torch.zeros(128, 512))
+    assert [s.note for s in shifted_bias.last_plan.steps] == [
+        "C[0:128, 0:256] = A[0:, 0:64] @ B[0:, 0:] + bias[256:512]",
+        "C[0:128, 256:512] = A[0:, 0:64] @ B[0:, 256:] + bias[0:256]"]
+
+    # a bias tile that reaches past its vector would add zero padding: neither the epilogue nor a program reads that
+    @asc2.jit
+    def padded_bias(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, bias_ptr: asc.GlobalAddress, c_ptr: asc.GlobalAddress):
+        a_gm, b_gm, c_gm = asc2.tensor(a_ptr, [128, 64]), asc2.tensor(b_ptr, [64, 256]), asc2.tensor(c_ptr, [128, 256])
+        row = asc2.load(asc2.tensor(bias_ptr, [1, 200]), [1, 256], offsets=[0, 0])
+        x, y = asc2.load(a_gm, [128, 64], offsets=[0, 0]), asc2.load(b_gm, [64, 256], offsets=[0, 0])
+        asc2.store(asc2.matmul(x, y) + row.broadcast_to(128, 256), c_gm, offsets=[0, 0])
+    with pytest.raises(NotImplementedError, match="bias row that reaches past the end of its tensor"):
+        padded_bias[1](torch.zeros(128, 64, dtype=h), torch.zeros(64, 256, dtype=h), torch.zeros(1, 200),
+                       torch.zeros(128, 256))
 
 
 def test_batched_matmul_loop_plans_one_product_per_matrix(monkeypatch):
@@ -262,8 +315,8 @@ def test_k_loop_accumulator_with_an_epilogue_and_windows_of_a_wider_matrix(monke
     K.matmul_k_tiled_bias_relu[1](torch.zeros(128, 512, dtype=h), torch.zeros(512, 128, dtype=h), torch.zeros(1, 128),
                                   torch.zeros(128, 128), 128, 128, 512, 128)
     plan = K.matmul_k_tiled_bias_relu.last_plan            # the K loop folds into one product of K = 512
-    assert plan.pattern == "matmul+program" and [s.fn_name for s in plan.steps] == ["asc_cuda_gemm_f16", "asc_cuda_eltwise_program_2d"]
-    assert plan.steps[0].note == "C[0:128, 0:128] = A[0:, 0:512] @ B[0:, 0:]"
+    assert plan.pattern == "matmul" and [s.fn_name for s in plan.steps] == ["asc_cuda_gemm_f16_bias"]
+    assert plan.steps[0].note == "C[0:128, 0:128] = A[0:, 0:512] @ B[0:, 0:] + bias[0:128]"
     # the two halves of every row: operand windows with the pitch of the wide matrix, a contiguous result
     K.glu_rows[4](torch.zeros(256, 1024), torch.zeros(256, 512), 256, 512, 8)
     plan = K.glu_rows.last_plan
