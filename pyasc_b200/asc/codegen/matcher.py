@@ -1930,6 +1930,9 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
                                    "(the last writer would win)")
 
     a_idx, b_idx, c_idx = a_w.tensor.base.index, b_w.tensor.base.index, out_t.base.index
+    if c_idx in (a_idx, b_idx):
+        # (tiles of the product run concurrently: one would overwrite operand rows or columns another still reads)
+        raise _unsupported("matmul stored into one of its own operands")
     plan.writes.add(c_idx)
     if not (len(calls) == 1 and calls[0][0] == 0 and calls[0][1] == 0 and calls[0][5] == c_rows and
             calls[0][6] == c_cols and c_rows * c_cols == out_t.base.numel):
@@ -1942,6 +1945,8 @@ def _plan_matmul_value(trace: KernelTrace, value: Tile, out_t: Tensor, out_offse
     if epi.bias is not None:
         bias_idx, bias_code = epi.bias.tensor.base.index, _OUT_CODE[epi.bias.tensor.dtype.name]
         bias_size = epi.bias.tensor.dtype.sizeof()
+        if bias_idx == out_t.base.index:
+            raise _unsupported("bias row loaded from the tensor the product is stored to")
         plan.reads.add(bias_idx)
     if in_dtype == KT.int8:
         if epi.relu:

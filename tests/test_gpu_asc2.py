@@ -176,6 +176,26 @@ def test_k_loop_accumulator_with_an_epilogue_and_glu():
     torch.testing.assert_close(out, x[:, :512] / (torch.exp(-x[:, 512:]) + 1), rtol=2e-6, atol=1e-6)
 
 
+def test_matmul_stored_over_its_own_operand():
+    """x = x @ w, tile by tile: every product is complete (in a temporary) before any row of x is overwritten."""
+    @asc2.jit
+    def in_place(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, m: asc.ConstExpr[int], k: asc.ConstExpr[int],
+                 m_tile: asc.ConstExpr[int]):
+        a_gm, b_gm = asc2.tensor(a_ptr, [m, k]), asc2.tensor(b_ptr, [k, k])
+        for i in range(asc2.block_idx() * m_tile, m, asc2.block_num() * m_tile):
+            x, y = asc2.load(a_gm, [m_tile, k], offsets=[i, 0]), asc2.load(b_gm, [k, k], offsets=[0, 0])
+            asc2.store(asc2.matmul(x, y).to(asc.float16), a_gm, offsets=[i, 0])
+
+    gen = torch.Generator().manual_seed(5)
+    m, k = 2048, 1024
+    a = ((torch.rand(m, k, generator=gen) - .5) * 2 * k ** -0.5).half()
+    w = (torch.rand(k, k, generator=gen) - .5).half()
+    want = (a.float() @ w.float()).half()
+    in_place[8](a, w, m, k, 128)
+    assert in_place.last_plan.pattern == "matmul+program"
+    torch.testing.assert_close(a, want, atol=2e-3, rtol=2e-3)
+
+
 @pytest.mark.parametrize("batch, m, n, k", [(8, 128, 256, 64), (5, 200, 144, 80), (3, 1024, 1024, 1024)])
 def test_matmul_batched_loop(batch, m, n, k):
     gen = torch.Generator().manual_seed(batch * m)

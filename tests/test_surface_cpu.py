@@ -296,6 +296,37 @@ def test_bias_slices_of_an_mn_tiled_linear_layer_merge_or_stay_per_tile(monkeypa
                        torch.zeros(128, 256))
 
 
+def test_matmul_stored_into_its_own_operand_goes_through_a_temporary(monkeypatch):
+    """Tiles of one GEMM call run concurrently, so a product may not land in a tensor the call reads: with a cast
+    around it the product goes to a temporary first (every tile done before the program stores), bare it is refused;
+    so is a bias row taken from the output tensor."""
+    monkeypatch.setenv("DRY_RUN", "1")
+    h = torch.float16
+
+    @asc2.jit
+    def in_place(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, cast: asc.ConstExpr[int], dtype: asc.ConstExpr):
+        a_gm, b_gm = asc2.tensor(a_ptr, [256, 128]), asc2.tensor(b_ptr, [128, 128])
+        for i in range(2):
+            x, y = asc2.load(a_gm, [128, 128], offsets=[128 * i, 0]), asc2.load(b_gm, [128, 128], offsets=[0, 0])
+            v = asc2.matmul(x, y)
+            asc2.store(v.to(dtype) if cast else v, a_gm, offsets=[128 * i, 0])
+    in_place[1](torch.zeros(256, 128, dtype=h), torch.zeros(128, 128, dtype=h), 1, asc.float16)
+    plan = in_place.last_plan
+    assert plan.pattern == "matmul+program" and plan.temps == {"tmp0": 256 * 128 * 4} and plan.writes == {0}
+    assert [s.fn_name for s in plan.steps] == ["asc_cuda_gemm_f16", "asc_cuda_eltwise_program"]
+    with pytest.raises(NotImplementedError, match="stored into one of its own operands"):
+        in_place[1](torch.zeros(256, 128), torch.zeros(128, 128), 0, asc.float32)
+
+    @asc2.jit
+    def bias_from_the_output(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, c_ptr: asc.GlobalAddress):
+        a_gm, b_gm, c_gm = asc2.tensor(a_ptr, [128, 64]), asc2.tensor(b_ptr, [64, 256]), asc2.tensor(c_ptr, [128, 256])
+        row = asc2.load(c_gm, [1, 256], offsets=[5, 0])
+        x, y = asc2.load(a_gm, [128, 64], offsets=[0, 0]), asc2.load(b_gm, [64, 256], offsets=[0, 0])
+        asc2.store(asc2.matmul(x, y) + row.broadcast_to(128, 256), c_gm, offsets=[0, 0])
+    with pytest.raises(NotImplementedError, match="bias row loaded from the tensor the product is stored to"):
+        bias_from_the_output[1](torch.zeros(128, 64, dtype=h), torch.zeros(64, 256, dtype=h), torch.zeros(128, 256))
+
+
 def test_batched_matmul_loop_plans_one_product_per_matrix(monkeypatch):
     """B stacked along its rows: the K range of B starts at another row than the K range of A starts at a column."""
     monkeypatch.setenv("DRY_RUN", "1")
