@@ -2310,6 +2310,9 @@ def _match_attention(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         raise _unsupported("attention kernel whose tiles do not cover every query tile of every head exactly once")
     plan = Plan("attention")
     idx = [t.base.index for t in (qv.tensor, kv.tensor, vv.tensor, out_t)]
+    if idx[3] in idx[1:3]:
+        # (every query tile reads all keys and values of its head while other tiles already store their results)
+        raise _unsupported("attention stored into its own K or V tensor")
     plan.reads.update(idx[:3])
     plan.writes.add(idx[3])
     if rows * D != out_t.base.numel:
