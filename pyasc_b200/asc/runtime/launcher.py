@@ -106,6 +106,7 @@ class Launcher:
             except RuntimeError as e:
                 raise TypeError(f"Unsupported kernel argument of type {type(arg)}") from e
         all_on_device = all(isinstance(h, TorchCudaTensorArgument) for h in handles.values())
+        self._check_device_aliasing(plan, handles)
         user_stream = self.options.stream
         if user_stream is not None:
             stream = user_stream if isinstance(user_stream, ctypes.c_void_p) else ctypes.c_void_p(int(user_stream))
@@ -149,6 +150,32 @@ class Launcher:
                 handle.release_memory()
             for mem in temps:
                 rt.free(mem)
+
+    # Patterns whose kernels read everything an output element depends on (its own position, or its own row held in
+    # registers) before they write it: an output argument may be the very buffer of an input argument.
+    _IN_PLACE_PATTERNS = ("elementwise", "softmax", "rms_norm", "row")
+
+    @classmethod
+    def _check_device_aliasing(cls, plan: Plan, handles: Dict[int, MemoryHandle]) -> None:
+        """Two kernel arguments that are views of one device buffer.  Host arguments get a device buffer each, so
+        they never alias; device tensors are used where they lie.  The planner reasons per argument: it cannot see
+        that the matrix a GEMM stores is also the matrix its other tiles are still reading."""
+        dev = {i: (h.tensor.data_ptr(), h.nbytes) for i, h in handles.items()
+               if isinstance(h, TorchCudaTensorArgument) and h.nbytes}
+        for w in plan.writes:
+            if w not in dev:
+                continue
+            w_ptr, w_bytes = dev[w]
+            for i, (ptr, nbytes) in dev.items():
+                if i == w or (i not in plan.reads and i not in plan.writes):
+                    continue
+                if ptr >= w_ptr + w_bytes or w_ptr >= ptr + nbytes:
+                    continue
+                same = (ptr, nbytes) == (w_ptr, w_bytes) and i not in plan.writes
+                if same and all(part.startswith(cls._IN_PLACE_PATTERNS) for part in plan.pattern.split("+")):
+                    continue
+                raise ValueError(f"Kernel arguments {i} and {w} overlap in device memory and argument {w} is written by "
+                                 f"a '{plan.pattern}' launch, whose tiles run concurrently; pass separate buffers")
 
     # ------------------------------------------------------------------------------------------
     # chunked launch: upload / kernel / download of neighbouring chunks overlap

@@ -176,6 +176,22 @@ def test_k_loop_accumulator_with_an_epilogue_and_glu():
     torch.testing.assert_close(out, x[:, :512] / (torch.exp(-x[:, 512:]) + 1), rtol=2e-6, atol=1e-6)
 
 
+def test_device_tensors_that_share_a_buffer():
+    """x += y through two arguments that are one device buffer works (every element is read before it is written);
+    a GEMM whose output argument is also an operand argument is refused before anything is launched."""
+    gen = torch.Generator().manual_seed(9)
+    x, y = torch.randn(8192, generator=gen).cuda(), torch.randn(8192, generator=gen).cuda()
+    want = (x + y).cpu()
+    K.vadd[16](x, y, x, 8192, 128, 4)
+    assert torch.equal(x.cpu(), want)
+    a = torch.randn(128, 128, generator=gen).half().cuda()
+    b = torch.randn(128, 128, generator=gen).half().cuda()
+    before = a.clone()
+    with pytest.raises(ValueError, match="overlap in device memory"):
+        K.matmul_relu_cast[1](a, b, a, a.shape, b.shape, a.shape)
+    assert torch.equal(a, before)
+
+
 def test_matmul_stored_over_its_own_operand():
     """x = x @ w, tile by tile: every product is complete (in a temporary) before any row of x is overwritten."""
     @asc2.jit

@@ -436,3 +436,31 @@ def test_explain_lists_the_library_calls_of_a_launch(monkeypatch, capsys):
     assert "kernel 'column_softmax' -> column:statistics: 12 call(s)" in err and "temporary tmp0: 262144 bytes" in err
     text = K.column_softmax.explain()
     assert text.splitlines()[3].strip() == "asc_cuda_reduce_f32: max axis 0 of [64, 256] at (0, 0) -> [0, +256)"
+
+
+def test_device_arguments_that_share_a_buffer():
+    """An output argument may be the buffer of an input argument only for kernels that read an element (or its row)
+    before they write it; overlapping views and GEMM / attention / reduction outputs over their inputs are refused."""
+    from asc.codegen.matcher import Plan
+    from asc.runtime.launcher import Launcher
+    from asc.runtime.memory_handle import TorchCudaTensorArgument as Dev
+    buf = torch.zeros(4096)
+    x, y, shifted, other = Dev(buf[:2048]), Dev(buf[:2048]), Dev(buf[1024:3072]), Dev(torch.zeros(2048))
+
+    def plan(pattern, reads, writes):
+        p = Plan(pattern)
+        p.reads.update(reads)
+        p.writes.update(writes)
+        return p
+    check = Launcher._check_device_aliasing
+    for pattern in ("elementwise:vadd", "elementwise:program", "row:program", "softmax", "rms_norm"):
+        check(plan(pattern, {0, 1}, {2}), {0: x, 1: other, 2: y})                 # x += other
+    check(plan("matmul", {0, 1}, {2}), {0: x, 1: x, 2: other})                     # inputs may alias each other
+    check(plan("matmul", {0}, {2}), {0: other, 1: y, 2: y})                        # argument 1 is not used by the plan
+    for pattern in ("matmul", "matmul+program", "attention", "reduce:sum", "copy", "atomic:add", "elementwise:program+matmul"):
+        with pytest.raises(ValueError, match="overlap in device memory"):
+            check(plan(pattern, {0, 1}, {2}), {0: x, 1: other, 2: y})
+    with pytest.raises(ValueError, match="overlap in device memory"):              # a shifted view: never
+        check(plan("elementwise:program", {0}, {1}), {0: x, 1: shifted})
+    with pytest.raises(ValueError, match="overlap in device memory"):              # two outputs in one buffer
+        check(plan("elementwise:program", {0}, {1, 2}), {0: other, 1: x, 2: y})
