@@ -336,6 +336,29 @@ def test_workload_attention_script(causal):
     G.assert_half_close(o, G.attention(q, k, v, causal))
 
 
+def test_attention_stored_over_its_queries():
+    """O written into Q's tensor: a query tile is read by the one CTA that later stores the same rows."""
+    @asc2.jit
+    def attn(q_ptr: asc.GlobalAddress, k_ptr: asc.GlobalAddress, v_ptr: asc.GlobalAddress, heads: asc.ConstExpr[int],
+             seq: asc.ConstExpr[int]):
+        q_gm, k_gm, v_gm = (asc2.tensor(p, [heads * seq, 128]) for p in (q_ptr, k_ptr, v_ptr))
+        per_head = seq // 128
+        for t in range(asc2.block_idx(), heads * per_head, asc2.block_num()):
+            head_row, q_off = (t // per_head) * seq, (t % per_head) * 128
+            q = asc2.load(q_gm, [128, 128], offsets=[head_row + q_off, 0])
+            k = asc2.load(k_gm, [seq, 128], offsets=[head_row, 0])
+            v = asc2.load(v_gm, [seq, 128], offsets=[head_row, 0])
+            p = asc2.softmax(asc2.matmul(q, k, trans_b=True) * 0.08838834764831845).to(asc.float16)
+            asc2.store(asc2.matmul(p, v).to(asc.float16), q_gm, offsets=[head_row + q_off, 0])
+
+    q, k, v = G.attention_inputs(2, 40, 1024)             # 640 query tiles: several per CTA
+    want = G.attention(q, k, v, False)
+    qd = q.cuda()
+    attn[148](qd, k.cuda(), v.cuda(), 80, 1024)
+    assert attn.last_plan.pattern == "attention"
+    G.assert_half_close(qd.cpu(), want)
+
+
 def test_user_stream_and_profiler():
     import ctypes
     from asc.lib import runtime as rt

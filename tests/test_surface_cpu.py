@@ -464,3 +464,26 @@ def test_device_arguments_that_share_a_buffer():
         check(plan("elementwise:program", {0}, {1}), {0: x, 1: shifted})
     with pytest.raises(ValueError, match="overlap in device memory"):              # two outputs in one buffer
         check(plan("elementwise:program", {0}, {1, 2}), {0: other, 1: x, 2: y})
+
+
+def test_attention_stored_into_its_own_keys_is_refused():
+    """Every query tile reads all keys and values of its head while other tiles already store: O may be Q's tensor
+    (a tile reads its own queries before it stores), not K's or V's."""
+    def make(out_name):
+        @asc2.jit
+        def attn(q_ptr: asc.GlobalAddress, k_ptr: asc.GlobalAddress, v_ptr: asc.GlobalAddress):
+            gm = {n: asc2.tensor(p, [512, 128]) for n, p in (("q", q_ptr), ("k", k_ptr), ("v", v_ptr))}
+            for t in range(asc2.block_idx(), 4, asc2.block_num()):
+                q = asc2.load(gm["q"], [128, 128], offsets=[t * 128, 0])
+                k = asc2.load(gm["k"], [512, 128], offsets=[0, 0])
+                v = asc2.load(gm["v"], [512, 128], offsets=[0, 0])
+                p = asc2.softmax(asc2.matmul(q, k, trans_b=True) * 0.125).to(asc.float16)
+                asc2.store(asc2.matmul(p, v).to(asc.float16), gm[out_name], offsets=[t * 128, 0])
+        return attn
+    x = torch.zeros(512, 128, dtype=torch.float16)
+    attn = make("q")
+    attn[4](x, x.clone(), x.clone())
+    assert attn.last_plan.pattern == "attention" and attn.last_plan.writes == {0}
+    for name in ("k", "v"):
+        with pytest.raises(NotImplementedError, match="attention stored into its own K or V"):
+            make(name)[4](x, x.clone(), x.clone())
