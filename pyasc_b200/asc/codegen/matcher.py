@@ -174,6 +174,11 @@ def resolve_view(tile: Any) -> Optional[GmView]:
     if not isinstance(tile, Tile):
         return None
     node = tile.node
+    if id(node) in _MATERIALISED:           # a value already planned into a temporary reads like a load from it
+        op = _MATERIALISED[id(node)]
+        if op.bcast or op.scalar or op.per_row:
+            return None
+        return GmView(op.tensor, op.offsets, op.shape, 0)
     if node.kind == "load":
         return GmView(node.args[0], node.attrs["offsets"], node.attrs["shape"], node.attrs["pad_value"])
     if node.kind == "copy":
@@ -183,6 +188,10 @@ def resolve_view(tile: Any) -> Optional[GmView]:
         offs = tuple(a + b for a, b in zip(inner.offsets, node.attrs["offsets"]))
         return GmView(inner.tensor, offs, node.attrs["shape"], inner.pad_value)
     return None
+
+
+def _is_materialised(tile: Any) -> bool:
+    return isinstance(tile, Tile) and id(tile.node) in _MATERIALISED
 
 
 def _is_zero_pad(view: GmView) -> bool:
@@ -1492,8 +1501,10 @@ def _match_softmax(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     src = _softmax_source(value)
     if src is None:
         return None
-    view = resolve_view(src) if _node(src, "load") else None
+    view = resolve_view(src) if _node(src, "load") or _is_materialised(src) else None
     if view is None:
+        if not _MATERIALISED and _matmul_leaves(src):
+            return None        # a matmul result: _match_matmul_then_program writes it to a temporary and comes back
         raise _unsupported("softmax of a tile that is not loaded directly from global memory")
     if not _same_offsets(view.offsets, eff.attrs["offsets"]) or view.shape != value.shape:
         raise _unsupported("softmax stored at a different position than it was loaded from")
@@ -1564,9 +1575,11 @@ def _match_rms_norm(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         raise _unsupported(f"rms_norm on {dtype} tiles (float32 and float16, one type throughout)")
     esize = dtype.bitwidth // 8
     fn_name = "asc_cuda_rms_norm_f32" if dtype == KT.float32 else "asc_cuda_rms_norm_f16"
-    view = resolve_view(src) if _node(src, "load") else None
+    view = resolve_view(src) if _node(src, "load") or _is_materialised(src) else None
     gview = resolve_view(gamma) if _node(gamma, "load") else None
     if view is None or gview is None:
+        if gview is not None and not _MATERIALISED and _matmul_leaves(src):
+            return None        # a matmul result: _match_matmul_then_program writes it to a temporary and comes back
         raise _unsupported("rms_norm of tiles that are not loaded directly from global memory")
     if not eps.is_const:
         raise _unsupported("rms_norm with an epsilon that varies between blocks or iterations")
@@ -2173,6 +2186,9 @@ def _match_column_statistics(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     return plan
 
 
+_MAX_PRODUCTS = 4      # matmul results one stored expression may combine (a temporary matrix each)
+
+
 def _matmul_leaves(value: Any, limit: int = 4096) -> List[Tile]:
     """The matmul results (``matmul`` / ``matmul_acc`` accumulators) an expression is computed from."""
     found: List[Tile] = []
@@ -2206,29 +2222,42 @@ def _match_matmul_then_program(trace: KernelTrace, eff: Effect) -> Optional[Plan
     leaves = _matmul_leaves(value)
     if not leaves:
         return None
-    if len(leaves) != 1:
-        raise _unsupported("expression that combines several matmul results")
-    mm = leaves[0]
-    if _value_from_deeper_loop(value, eff.loops, stop=(id(mm.node), )):
-        return None          # something besides the accumulator is carried out of a loop
-    if mm.shape != value.shape or len(out_t.static_shape()) != 2:
+    if len(leaves) > _MAX_PRODUCTS:
+        raise _unsupported(f"expression that combines more than {_MAX_PRODUCTS} matmul results")
+    if _value_from_deeper_loop(value, eff.loops, stop=tuple(id(mm.node) for mm in leaves)):
+        return None          # something besides the accumulators is carried out of a loop
+    if any(mm.shape != value.shape for mm in leaves) or len(out_t.static_shape()) != 2:
         raise _unsupported("matmul result reshaped or stored to a tensor that is not 2-D before its elementwise epilogue")
     offsets = eff.attrs["offsets"]
     plan = Plan("matmul+program")
-    key = f"tmp{len(plan.temps)}"
     rows, cols = out_t.static_shape()
-    tmp = _fake_tensor(key, (rows, cols), mm.dtype)
-    plan.temps[key] = rows * cols * mm.dtype.sizeof()
-    if not _plan_matmul_value(trace, mm, tmp, offsets, eff.loops, plan, eff.guards):
-        return None
-    _MATERIALISED[id(mm.node)] = _Operand(tmp, offsets, mm.shape)
+    keys = []
     try:
-        tail = _match_eltwise_program(trace, eff)
+        for mm in leaves:
+            key = f"tmp{len(plan.temps)}"
+            tmp = _fake_tensor(key, (rows, cols), mm.dtype)
+            plan.temps[key] = rows * cols * mm.dtype.sizeof()
+            if not _plan_matmul_value(trace, mm, tmp, offsets, eff.loops, plan, eff.guards):
+                return None
+            keys.append(key)
+            _MATERIALISED[id(mm.node)] = _Operand(tmp, offsets, mm.shape)
+        # the rest of the expression reads the products like loaded tiles: a fused row kernel where one fits
+        # (softmax, rms_norm of the product), else an elementwise or row program
+        tail, refusal = None, None
+        for finish in (_match_softmax, _match_rms_norm, _match_eltwise_program):
+            try:
+                tail = finish(trace, eff)
+            except NotImplementedError as e:      # e.g. softmax of a scaled product: the row program takes it
+                refusal = refusal or e
+                continue
+            if tail is not None:
+                break
     finally:
         _MATERIALISED.clear()
     if tail is None:
-        raise _unsupported("expression around a matmul result that is not elementwise")
-    tail.reads.discard(key)
+        raise refusal or _unsupported("expression around a matmul result that is not elementwise")
+    for key in keys:
+        tail.reads.discard(key)
     plan.steps.extend(tail.steps)
     plan.reads.update(tail.reads)
     plan.writes.update(tail.writes)

@@ -176,6 +176,53 @@ def test_k_loop_accumulator_with_an_epilogue_and_glu():
     torch.testing.assert_close(out, x[:, :512] / (torch.exp(-x[:, 512:]) + 1), rtol=2e-6, atol=1e-6)
 
 
+def test_expressions_over_several_products_and_fused_row_kernels_over_a_product():
+    """SwiGLU (two products of one input combined elementwise), softmax and rms_norm of a product: every product is
+    written to its own temporary, then one program or fused row kernel reads them like loaded tiles."""
+    gen = torch.Generator().manual_seed(21)
+    m, k, n = 512, 256, 1024
+    x = ((torch.rand(m, k, generator=gen) - .5) * 2 * k ** -0.5).half()
+    w1, w3 = ((torch.rand(k, n, generator=gen) - .5).half() for _ in range(2))
+
+    @asc2.jit
+    def swiglu(x_ptr: asc.GlobalAddress, w1_ptr: asc.GlobalAddress, w3_ptr: asc.GlobalAddress, o_ptr: asc.GlobalAddress,
+               m: asc.ConstExpr[int], k: asc.ConstExpr[int], n: asc.ConstExpr[int], m_tile: asc.ConstExpr[int]):
+        x_gm, w1_gm, w3_gm = asc2.tensor(x_ptr, [m, k]), asc2.tensor(w1_ptr, [k, n]), asc2.tensor(w3_ptr, [k, n])
+        o_gm = asc2.tensor(o_ptr, [m, n])
+        for i in range(asc2.block_idx() * m_tile, m, asc2.block_num() * m_tile):
+            xt = asc2.load(x_gm, [m_tile, k], offsets=[i, 0])
+            g = asc2.matmul(xt, asc2.load(w1_gm, [k, n], offsets=[0, 0]))
+            u = asc2.matmul(xt, asc2.load(w3_gm, [k, n], offsets=[0, 0]))
+            asc2.store((g / (asc2.exp(-g) + 1) * u).to(asc.float16), o_gm, offsets=[i, 0])
+    out = torch.zeros(m, n, dtype=torch.float16)
+    swiglu[4](x, w1, w3, out, m, k, n, 128)
+    plan = swiglu.last_plan
+    assert plan.pattern == "matmul+program" and len(plan.temps) == 2 and len(plan.steps) == 3
+    g, u = x.float() @ w1.float(), x.float() @ w3.float()
+    torch.testing.assert_close(out, (g / (torch.exp(-g) + 1) * u).half(), atol=2e-3, rtol=2e-3)
+
+    @asc2.jit
+    def scores(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, g_ptr: asc.GlobalAddress, o_ptr: asc.GlobalAddress,
+               m: asc.ConstExpr[int], k: asc.ConstExpr[int], n: asc.ConstExpr[int], m_tile: asc.ConstExpr[int],
+               norm: asc.ConstExpr[int]):
+        a_gm, b_gm, o_gm = asc2.tensor(a_ptr, [m, k]), asc2.tensor(b_ptr, [k, n]), asc2.tensor(o_ptr, [m, n])
+        gamma = asc2.load(asc2.tensor(g_ptr, [n]), [n], offsets=[0])
+        for i in range(asc2.block_idx() * m_tile, m, asc2.block_num() * m_tile):
+            s = asc2.matmul(asc2.load(a_gm, [m_tile, k], offsets=[i, 0]), asc2.load(b_gm, [k, n], offsets=[0, 0]))
+            asc2.store(asc2.rms_norm(s, gamma, 1e-6) if norm else asc2.softmax(s), o_gm, offsets=[i, 0])
+    xs = (x.float() * 8).half()                     # scores with a spread of a few units
+    s = xs.float() @ w1.float()
+    gamma = torch.rand(n, generator=gen) + 0.5
+    out = torch.zeros(m, n)
+    scores[4](xs, w1, gamma, out, m, k, n, 128, 0)
+    assert [st.fn_name for st in scores.last_plan.steps] == ["asc_cuda_gemm_f16", "asc_cuda_softmax_f32"]
+    torch.testing.assert_close(out, torch.softmax(s, dim=-1), atol=1e-5, rtol=2e-3)
+    scores[4](xs, w1, gamma, out, m, k, n, 128, 1)
+    assert [st.fn_name for st in scores.last_plan.steps] == ["asc_cuda_gemm_f16", "asc_cuda_rms_norm_f32"]
+    want = s * torch.rsqrt((s * s).mean(dim=-1, keepdim=True) + 1e-6) * gamma
+    torch.testing.assert_close(out, want, atol=2e-3, rtol=2e-3)
+
+
 def test_device_tensors_that_share_a_buffer():
     """x += y through two arguments that are one device buffer works (every element is read before it is written);
     a GEMM whose output argument is also an operand argument is refused before anything is launched."""

@@ -241,16 +241,36 @@ def test_matmul_followed_by_an_elementwise_expression_plans_a_product_and_a_prog
                 ["asc_cuda_gemm_f16", "asc_cuda_eltwise_program_2d"]          # the eight row blocks merge in both
             assert plan.reads == reads and plan.writes == {4} and not plan.partial_writes
             assert plan.temps == {"tmp0": m * n * 4} and plan.pipeline is None
-    # two products in one expression would need two temporaries: refused
+    # several products in one expression: a temporary each, then one program over all of them
     @asc2.jit
-    def two_products(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, c_ptr: asc.GlobalAddress):
+    def products(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, c_ptr: asc.GlobalAddress, count: asc.ConstExpr[int]):
         a_gm, b_gm, c_gm = asc2.tensor(a_ptr, [64, 64]), asc2.tensor(b_ptr, [64, 64]), asc2.tensor(c_ptr, [64, 64])
         x = asc2.load(a_gm, [64, 64], offsets=[0, 0])
         y = asc2.load(b_gm, [64, 64], offsets=[0, 0])
-        asc2.store(asc2.matmul(x, y) + asc2.matmul(y, x), c_gm, offsets=[0, 0])
+        total = asc2.matmul(x, y)
+        for scale in (2.0, 3.0, 4.0, 5.0)[:count - 1]:
+            total = total + asc2.matmul(y, x) * scale
+        asc2.store(total, c_gm, offsets=[0, 0])
     h = torch.zeros(64, 64, dtype=torch.float16)
-    with pytest.raises(NotImplementedError, match="several matmul results"):
-        two_products[1](h, h, torch.zeros(64, 64))
+    products[1](h, h, torch.zeros(64, 64), 2)
+    plan = products.last_plan
+    assert plan.pattern == "matmul+program" and plan.temps == {"tmp0": 64 * 64 * 4, "tmp1": 64 * 64 * 4}
+    assert [s.fn_name for s in plan.steps] == ["asc_cuda_gemm_f16", "asc_cuda_gemm_f16", "asc_cuda_eltwise_program"]
+    assert plan.reads == {0, 1} and plan.writes == {2}
+    with pytest.raises(NotImplementedError, match="more than 4 matmul results"):
+        products[1](h, h, torch.zeros(64, 64), 5)
+
+    # a fused row kernel over the product: the product reads like a loaded tile once it is in its temporary
+    @asc2.jit
+    def product_softmax(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, c_ptr: asc.GlobalAddress):
+        a_gm, b_gm, c_gm = asc2.tensor(a_ptr, [128, 64]), asc2.tensor(b_ptr, [64, 256]), asc2.tensor(c_ptr, [128, 256])
+        for i in range(asc2.block_idx() * 64, 128, asc2.block_num() * 64):
+            s = asc2.matmul(asc2.load(a_gm, [64, 64], offsets=[i, 0]), asc2.load(b_gm, [64, 256], offsets=[0, 0]))
+            asc2.store(asc2.softmax(s), c_gm, offsets=[i, 0])
+    product_softmax[2](torch.zeros(128, 64, dtype=torch.float16), torch.zeros(64, 256, dtype=torch.float16), torch.zeros(128, 256))
+    plan = product_softmax.last_plan
+    assert plan.pattern == "matmul+program" and [s.fn_name for s in plan.steps] == ["asc_cuda_gemm_f16", "asc_cuda_softmax_f32"]
+    assert plan.steps[0].note == "C[0:128, 0:256] = A[0:, 0:64] @ B[0:, 0:]" and plan.temps == {"tmp0": 128 * 256 * 4}
 
 
 def test_bias_slices_of_an_mn_tiled_linear_layer_merge_or_stay_per_tile(monkeypatch):
