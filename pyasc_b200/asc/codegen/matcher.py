@@ -1794,6 +1794,27 @@ def _fake_tensor(key: str, shape: Tuple[int, int], dtype: DataType) -> Tensor:
     return Tensor(base, tuple(PlainValue.const(d) for d in shape))
 
 
+def _materialise_operand(trace: KernelTrace, tile: Tile, plan: Plan) -> Optional[_Window]:
+    """A matmul operand computed elementwise from loaded tiles (a cast, an activation, a mask applied on the way
+    from global memory to the cube unit): one program writes it, over every block and iteration that loads it, into
+    a temporary laid out like the tensor its tile was loaded from; the product then reads the temporary there."""
+    anchor = next((n for n in _loads_of(tile) if tuple(n.attrs["shape"]) == tile.shape and len(tile.shape) == 2
+                   and len(n.args[0].static_shape()) == 2), None)
+    if anchor is None:
+        return None
+    source = anchor.args[0]
+    key = f"tmp{len(plan.temps)}"
+    tmp = _fake_tensor(key, source.static_shape(), tile.dtype)
+    offsets = anchor.attrs["offsets"]
+    sub = _match_eltwise_program(trace, Effect("store", (tile, tmp), {"offsets": offsets}, tile.node.loops))
+    if sub is None:
+        return None
+    plan.temps[key] = source.static_shape()[0] * source.static_shape()[1] * tile.dtype.sizeof()
+    plan.steps.extend(sub.steps)
+    plan.reads.update(r for r in sub.reads if r != key)
+    return _Window(tmp, offsets[0], offsets[1], tile.shape[0], tile.shape[1])
+
+
 def _operand_window(trace: KernelTrace, tile: Tile, plan: Plan) -> _Window:
     tile = _peel_identity_copies(tile)
     view = resolve_view(tile)
@@ -1805,6 +1826,11 @@ def _operand_window(trace: KernelTrace, tile: Tile, plan: Plan) -> _Window:
         _check_fits(view.tensor)
         plan.reads.add(view.tensor.base.index)
         return _Window(view.tensor, view.offsets[0], view.offsets[1], view.shape[0], view.shape[1])
+    if not _matmul_leaves(tile):
+        w = _materialise_operand(trace, tile, plan)
+        if w is None:
+            raise _unsupported(f"matmul operand produced by '{tile.node.kind}'")
+        return w
     # an operand computed on chip (chained matmul): materialise it in a temporary device buffer
     key = f"tmp{len(plan.temps)}"
     tmp = _fake_tensor(key, tile.shape, tile.dtype)

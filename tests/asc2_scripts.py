@@ -186,6 +186,23 @@ def linear_mn_tiles(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, bias_ptr
 
 
 @asc2.jit(always_compile=True)
+def matmul_of_computed_operands(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, s_ptr: asc.GlobalAddress,
+                                c_ptr: asc.GlobalAddress, m: int, k: asc.ConstExpr[int], n: asc.ConstExpr[int],
+                                m_tile: asc.ConstExpr[int], k_tile: asc.ConstExpr[int]):
+    """Operands prepared on the way to the cube unit: fp32 activations cast to fp16 (after a ReLU), weights scaled
+    elementwise by a second matrix; accumulated over a K loop."""
+    a_gm, b_gm, s_gm = asc2.tensor(a_ptr, [m, k]), asc2.tensor(b_ptr, [k, n]), asc2.tensor(s_ptr, [k, n])
+    c_gm = asc2.tensor(c_ptr, [m, n])
+    for i in range(asc2.block_idx() * m_tile, m, asc2.block_num() * m_tile):
+        acc = asc2.zeros_acc([m_tile, n], dtype=asc.float32)
+        for kk in range(0, k, k_tile):
+            a = asc2.relu(asc2.load(a_gm, [m_tile, k_tile], offsets=[i, kk])).to(asc.float16)
+            b = asc2.load(b_gm, [k_tile, n], offsets=[kk, 0]) * asc2.load(s_gm, [k_tile, n], offsets=[kk, 0])
+            asc2.matmul_acc(a, b, acc)
+        asc2.store(acc, c_gm, offsets=[i, 0])
+
+
+@asc2.jit(always_compile=True)
 def glu_rows(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: int, cols: asc.ConstExpr[int],
              rpt: asc.ConstExpr[int]):
     """A gated linear unit: the two halves of every row of x, a * sigmoid(g)."""

@@ -223,6 +223,22 @@ def test_expressions_over_several_products_and_fused_row_kernels_over_a_product(
     torch.testing.assert_close(out, want, atol=2e-3, rtol=2e-3)
 
 
+@pytest.mark.parametrize("m, k, n, m_tile, k_tile", [(512, 256, 128, 128, 64), (1000, 512, 272, 128, 128)])
+def test_matmul_of_operands_computed_from_loaded_tiles(m, k, n, m_tile, k_tile):
+    """relu(A).to(fp16) @ (B * S) over a K loop: each operand is written to a temporary by one program, then one GEMM.
+    Golden: the same expression in torch on the CPU (operands rounded to fp16 exactly as the kernel rounds them)."""
+    gen = torch.Generator().manual_seed(m)
+    a = (torch.rand(m, k, generator=gen) - .5) * 2 * k ** -0.5
+    b = (torch.rand(k, n, generator=gen) - .5).half()
+    s = (torch.rand(k, n, generator=gen) + .5).half()
+    c = torch.zeros(m, n)
+    K.matmul_of_computed_operands[8](a, b, s, c, m, k, n, m_tile, k_tile)
+    plan = K.matmul_of_computed_operands.last_plan
+    assert plan.pattern == "matmul" and len(plan.temps) == 2 and plan.steps[-1].fn_name == "asc_cuda_gemm_f16"
+    want = a.relu().half().float() @ (b * s).float()
+    torch.testing.assert_close(c, want, atol=2e-3, rtol=2e-3)
+
+
 def test_device_tensors_that_share_a_buffer():
     """x += y through two arguments that are one device buffer works (every element is read before it is written);
     a GEMM whose output argument is also an operand argument is refused before anything is launched."""

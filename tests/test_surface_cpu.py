@@ -347,6 +347,31 @@ def test_matmul_stored_into_its_own_operand_goes_through_a_temporary(monkeypatch
         bias_from_the_output[1](torch.zeros(128, 64, dtype=h), torch.zeros(64, 256, dtype=h), torch.zeros(128, 256))
 
 
+def test_matmul_operands_computed_from_loaded_tiles_are_written_to_temporaries(monkeypatch):
+    monkeypatch.setenv("DRY_RUN", "1")
+    import asc2_scripts as K
+    h = torch.float16
+    K.matmul_of_computed_operands[4](torch.zeros(512, 256), torch.zeros(256, 128, dtype=h), torch.zeros(256, 128, dtype=h),
+                                     torch.zeros(512, 128), 512, 256, 128, 128, 64)
+    plan = K.matmul_of_computed_operands.last_plan
+    # one program per operand over the whole matrix (every block's and iteration's tile), then one product
+    assert plan.pattern == "matmul" and plan.temps == {"tmp0": 512 * 256 * 2, "tmp1": 256 * 128 * 2}
+    assert [s.fn_name for s in plan.steps] == ["asc_cuda_eltwise_program", "asc_cuda_eltwise_program", "asc_cuda_gemm_f16"]
+    assert plan.steps[0].note.endswith("over [0, 131072)") and plan.steps[1].note.endswith("over [0, 32768)")
+    assert plan.steps[2].note == "C[0:512, 0:128] = A[0:, 0:256] @ B[0:, 0:]"
+    assert plan.reads == {0, 1, 2} and plan.writes == {3}
+
+    # an operand normalised by its row maximum: a row program writes the temporary
+    @asc2.jit
+    def reduced_operand(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddress, c_ptr: asc.GlobalAddress):
+        a_gm, b_gm, c_gm = asc2.tensor(a_ptr, [64, 64]), asc2.tensor(b_ptr, [64, 64]), asc2.tensor(c_ptr, [64, 64])
+        x = asc2.load(a_gm, [64, 64], offsets=[0, 0])
+        col = asc2.reduce_max(x, 1, keep_dims=True).broadcast_to(64, 64)
+        asc2.store(asc2.matmul((x / col).to(asc.float16), asc2.load(b_gm, [64, 64], offsets=[0, 0])), c_gm, offsets=[0, 0])
+    reduced_operand[1](torch.zeros(64, 64), torch.zeros(64, 64, dtype=h), torch.zeros(64, 64))
+    assert [s.fn_name for s in reduced_operand.last_plan.steps] == ["asc_cuda_row_program", "asc_cuda_gemm_f16"]
+
+
 def test_batched_matmul_loop_plans_one_product_per_matrix(monkeypatch):
     """B stacked along its rows: the K range of B starts at another row than the K range of A starts at a column."""
     monkeypatch.setenv("DRY_RUN", "1")
