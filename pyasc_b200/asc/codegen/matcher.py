@@ -1174,7 +1174,8 @@ def _match_row_result(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     """``store(f(reduce(g(tiles), 1), ...), vector)``: a [rows] (or [rows, 1]) tile whose elements are functions of
     row reductions of computed tiles, e.g. ``reduce_sum(x * x, 1)``.  One row program, one stored element per row."""
     value, out_t = eff.args
-    if not isinstance(value, Tile) or eff.kind != "store" or value.dtype != out_t.dtype or \
+    # (a tile of one element, the reduction of a one-row tile, arrives as a scalar store)
+    if not isinstance(value, Tile) or eff.kind not in ("store", "store_scalar") or value.dtype != out_t.dtype or \
             value.dtype not in (KT.float32, KT.float16, KT.bfloat16):
         return None
     direct = _node(value, "reduce")
@@ -1196,7 +1197,7 @@ def _match_row_result(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     _check_fits(out_t)
     for t in prog.inputs:
         _check_fits(t)
-    return _plan_general_program(trace, eff, prog, out_t, offsets, value.shape, False, dedupe=True,
+    return _plan_general_program(trace, eff, prog, out_t, offsets, value.shape, eff.kind == "store_scalar", dedupe=True,
                                  row_shape=(full_shape[0], full_shape[1]), row_result=True)
 
 

@@ -203,6 +203,23 @@ def matmul_of_computed_operands(a_ptr: asc.GlobalAddress, b_ptr: asc.GlobalAddre
 
 
 @asc2.jit(always_compile=True)
+def row_losses(x_ptr: asc.GlobalAddress, t_ptr: asc.GlobalAddress, mse_ptr: asc.GlobalAddress, ce_ptr: asc.GlobalAddress,
+               rows: int, cols: asc.ConstExpr[int]):
+    """Two losses per row, one row per iteration (a one-row tile reduced to one element is stored as a scalar):
+    the mean squared error, and the cross entropy of the row's logits against a row of target probabilities."""
+    x_gm, t_gm = asc2.tensor(x_ptr, [rows, cols]), asc2.tensor(t_ptr, [rows, cols])
+    mse_gm, ce_gm = asc2.tensor(mse_ptr, [rows]), asc2.tensor(ce_ptr, [rows])
+    for i in range(asc2.block_idx(), rows, asc2.block_num()):
+        x = asc2.load(x_gm, [1, cols], offsets=[i, 0])
+        t = asc2.load(t_gm, [1, cols], offsets=[i, 0])
+        d = x - t
+        asc2.store(asc2.reduce_sum(d * d, 1) / cols, mse_gm, offsets=[i])
+        mx = asc2.reduce_max(x, 1, keep_dims=True).broadcast_to(1, cols)
+        lse = asc2.log(asc2.reduce_sum(asc2.exp(x - mx), 1)) + asc2.reduce_max(x, 1)
+        asc2.store(lse - asc2.reduce_sum(x * t, 1), ce_gm, offsets=[i])
+
+
+@asc2.jit(always_compile=True)
 def glu_rows(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: int, cols: asc.ConstExpr[int],
              rpt: asc.ConstExpr[int]):
     """A gated linear unit: the two halves of every row of x, a * sigmoid(g)."""

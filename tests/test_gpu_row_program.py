@@ -52,6 +52,17 @@ def test_scalar_store_of_reductions_of_a_computed_row():
     torch.testing.assert_close(out, x.pow(2).sum(1) / 1024 + x.abs().amax(1), rtol=1e-5, atol=1e-6)
 
 
+def test_losses_per_row_from_one_row_tiles():
+    gen = torch.Generator().manual_seed(14)
+    x = torch.randn(300, 1000, generator=gen) * 3
+    t = torch.softmax(torch.randn(300, 1000, generator=gen), dim=1)
+    mse, ce = torch.zeros(300), torch.zeros(300)
+    K.row_losses[16](x, t, mse, ce, 300, 1000)
+    assert K.row_losses.last_plan.pattern == "row:program+row:program"
+    torch.testing.assert_close(mse, (x - t).pow(2).mean(1), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(ce, torch.logsumexp(x, 1) - (x * t).sum(1), rtol=1e-5, atol=1e-5)
+
+
 def test_loaded_columns_repeat_along_the_row():
     gen = torch.Generator().manual_seed(13)
     x, scale, bias = torch.randn(96, 640, generator=gen), torch.randn(96, generator=gen), torch.randn(96, generator=gen)

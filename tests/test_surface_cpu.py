@@ -532,3 +532,13 @@ def test_attention_stored_into_its_own_keys_is_refused():
     for name in ("k", "v"):
         with pytest.raises(NotImplementedError, match="attention stored into its own K or V"):
             make(name)[4](x, x.clone(), x.clone())
+
+
+def test_per_row_results_of_one_row_tiles_arrive_as_scalar_stores():
+    """reduce(...) of a [1, cols] tile has one element, which asc2.store records as a scalar store: still one value
+    per row of a row program, and the 64 one-row tiles merge into one call."""
+    x = torch.zeros(64, 512)
+    K.row_losses[8](x, x, torch.zeros(64), torch.zeros(64), 64, 512)
+    plan = K.row_losses.last_plan
+    assert plan.pattern == "row:program+row:program" and [s.fn_name for s in plan.steps] == ["asc_cuda_row_program"] * 2
+    assert all(" over [64, 512] " in s.note for s in plan.steps) and plan.reads == {0, 1} and plan.writes == {2, 3}
