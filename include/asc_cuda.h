@@ -129,7 +129,8 @@ int32_t asc_cuda_vmuladd_f32(const float* x, const float* y, const float* z, flo
  * 50 IRELU, 51 CVT_I2F, 52 CVT_F2I (truncating), 53 WRAP_I16 (sign-extend the low half); with the
  * operands swapped (rhs op lhs) 54 RSUB, 55 RDIV, 56 IRSUB, 57 IRSHL, 58 IRSHR.  A binary opcode
  * with bit 8 set (| 0x100) takes args[j] as its left operand instead of a stack entry.
- * Element types: 0 fp32, 1 fp16, 2 bf16, 3 int32, 4 int16; at most 6 inputs.
+ * Element types: 0 fp32, 1 fp16, 2 bf16, 3 int32, 4 int16, and the storage-only types 5 int8 and 6 uint8 (a load
+ * widens them to an int32 word, sign- or zero-extended; a store keeps the low byte of the word); at most 6 inputs.
  * The program is validated on the host (status 1 for a malformed one, 6 for a stack deeper than 8).
  * Replaces the per-op vector calls the reference lowers such kernels to
  * (python/asc/language/tile/binary_ops.py, unary_ops.py, indexing_ops.py:where;

@@ -358,6 +358,10 @@ _INT_COMPARE_CODE = {"eq": 42, "ne": 43, "gt": 44, "ge": 45, "lt": 46, "le": 47}
 _INT_UNARY_CODE = {"neg": 48, "abs": 49, "relu": 50}
 _OP_CVT_I2F, _OP_CVT_F2I, _OP_WRAP_I16 = 51, 52, 53
 _ELT_TYPE = {"float32": 0, "float16": 1, "bfloat16": 2, "int32": 3, "int16": 4}
+# 8-bit integers are storage types: a load widens them to int32 words and a store keeps the low byte, so a program
+# may load them (to compare, or to cast to a wider integer) and may store an integer cast to them; it does not
+# compute on 8-bit tiles (that would need a wrap after every operation).
+_STORAGE_TYPE = {**_ELT_TYPE, "int8": 5, "uint8": 6}
 _ROUND_CODE = {"float16": _OP_ROUND_F16, "bfloat16": _OP_ROUND_BF16, "int16": _OP_WRAP_I16}
 ELT_MAX_OPS, ELT_MAX_INPUTS, ELT_MAX_STACK = 48, 6, 8
 _ROW_CODE = {"sum": 59, "max": 60, "min": 61, "prod": 62}     # row programs: reduce the top of the stack over the row
@@ -468,6 +472,7 @@ class _EltProgram:
         self.per_row_reductions = False
         self.n_tmp = 0              # temporary slots the finished program uses
         self.visits = 0             # values visited while generating code
+        self.root: Any = None       # the value compile() was asked for (the one the program stores)
         self.full_shape: Optional[Tuple[int, ...]] = None   # set while code for a per-row value is generated
         self.ops: List[int] = []
         self.args: List[int] = []
@@ -504,7 +509,7 @@ class _EltProgram:
         return _Frag(lhs.code + rhs.code + [(code, 0)], max(lhs.need, rhs.need + 1))
 
     def _load(self, operand: _Operand) -> Optional[_Frag]:
-        if operand.tensor.dtype.name not in _ELT_TYPE:
+        if operand.tensor.dtype.name not in _STORAGE_TYPE:
             return None
         for k, o in enumerate(self.operands):
             if o.same(operand):
@@ -624,6 +629,8 @@ class _EltProgram:
                 return self._per_row(src, self.shape)
             return None
         if v.dtype.name not in _ELT_TYPE and node.kind != "compare":
+            if node.kind == "cast" and v is self.root and v.dtype.name in _STORAGE_TYPE and not node.args[0].dtype.is_float():
+                return self.gen(node.args[0])       # the stored value: the store keeps the low byte of the word
             return None
         if node.kind == "binary":
             code = (_BINARY_CODE if v.dtype.is_float() else _INT_BINARY_CODE).get(node.attrs["op"])
@@ -633,7 +640,7 @@ class _EltProgram:
             return self._rounded(self._binary(code, lhs, rhs), v.dtype)
         if node.kind == "compare":
             dt = node.args[0].dtype
-            if dt.name not in _ELT_TYPE:
+            if dt.name not in _STORAGE_TYPE:
                 return None
             lhs, rhs = self.gen(node.args[0], dt), self.gen(node.args[1], dt)
             if lhs is None or rhs is None:
@@ -654,7 +661,7 @@ class _EltProgram:
             return self._rounded(_Frag(src.code + [(code, 0)], src.need), v.dtype)
         if node.kind == "cast":
             src_t = node.args[0]
-            src = self.gen(src_t) if src_t.dtype.name in _ELT_TYPE else None
+            src = self.gen(src_t) if src_t.dtype.name in _STORAGE_TYPE else None
             if src is None:
                 return None
             src = src.pushed()
@@ -748,6 +755,7 @@ class _EltProgram:
         self.n_tmp = len(slots)
 
     def compile(self, v: Any) -> bool:
+        self.root = v
         frag = self.gen(v)
         if frag is None:
             return False
@@ -823,8 +831,8 @@ class _Geometry:
 def _program_arrays(prog: "_EltProgram", out_t: Tensor):
     n_ops, n_in = len(prog.ops), len(prog.operands)
     return (n_ops, n_in, (ctypes.c_int32 * n_ops)(*prog.ops), (ctypes.c_int32 * n_ops)(*prog.args),
-            (ctypes.c_int32 * max(1, n_in))(*[_ELT_TYPE[o.tensor.dtype.name] | (_ROW_SCALAR_INPUT if o.per_row else 0)
-                                              for o in prog.operands]), _ELT_TYPE[out_t.dtype.name])
+            (ctypes.c_int32 * max(1, n_in))(*[_STORAGE_TYPE[o.tensor.dtype.name] | (_ROW_SCALAR_INPUT if o.per_row else 0)
+                                              for o in prog.operands]), _STORAGE_TYPE[out_t.dtype.name])
 
 
 def _program_key(prog: "_EltProgram", row_cols: Optional[int] = None):
@@ -990,8 +998,10 @@ def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
     value, out_t = eff.args
     offsets = eff.attrs["offsets"]
     scalar_store = eff.kind == "store_scalar"
-    if not isinstance(value, (Tile, PlainValue)) or out_t.dtype.name not in _ELT_TYPE or value.dtype != out_t.dtype:
+    if not isinstance(value, (Tile, PlainValue)) or out_t.dtype.name not in _STORAGE_TYPE or value.dtype != out_t.dtype:
         return None
+    if out_t.dtype.name not in _ELT_TYPE and not (isinstance(value, Tile) and value.node.kind == "cast"):
+        return None          # (a loaded 8-bit tile stored as it is: a copy)
     tshape = out_t.static_shape()
     out_shape = (1, ) if scalar_store else value.shape
     prog = _EltProgram(out_shape, offsets, out_t, scalar_store)

@@ -220,6 +220,28 @@ def row_losses(x_ptr: asc.GlobalAddress, t_ptr: asc.GlobalAddress, mse_ptr: asc.
 
 
 @asc2.jit(always_compile=True)
+def quantise_int8(x_ptr: asc.GlobalAddress, q_ptr: asc.GlobalAddress, inv_scale: float, n: int, tile: asc.ConstExpr[int]):
+    """fp32 -> int8: round half up, clamp to [-128, 127], narrow through int32 (the reference casts between floats
+    and integers of one width only, and between integers of any widths)."""
+    x_gm, q_gm = asc2.tensor(x_ptr, [n]), asc2.tensor(q_ptr, [n])
+    for i in range(asc2.block_idx() * tile, n, asc2.block_num() * tile):
+        x = asc2.load(x_gm, [tile], offsets=[i])
+        r = asc2.minimum(asc2.maximum(asc2.floor(x * inv_scale + 0.5), -128.0), 127.0)
+        asc2.store(r.to(asc.int32).to(asc.int8), q_gm, offsets=[i])
+
+
+@asc2.jit(always_compile=True)
+def dequantise_int8(q_ptr: asc.GlobalAddress, keep_ptr: asc.GlobalAddress, x_ptr: asc.GlobalAddress, scale: float, n: int,
+                    tile: asc.ConstExpr[int]):
+    """int8 -> fp32 through int32, zeroed where a uint8 keep mask is 0 (unsigned tiles can be compared, not cast)."""
+    q_gm, keep_gm, x_gm = asc2.tensor(q_ptr, [n]), asc2.tensor(keep_ptr, [n]), asc2.tensor(x_ptr, [n])
+    for i in range(asc2.block_idx() * tile, n, asc2.block_num() * tile):
+        q = asc2.load(q_gm, [tile], offsets=[i]).to(asc.int32).to(asc.float32)
+        keep = asc2.load(keep_gm, [tile], offsets=[i])
+        asc2.store(asc2.where(keep != 0, q * scale, 0.0), x_gm, offsets=[i])
+
+
+@asc2.jit(always_compile=True)
 def glu_rows(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: int, cols: asc.ConstExpr[int],
              rpt: asc.ConstExpr[int]):
     """A gated linear unit: the two halves of every row of x, a * sigmoid(g)."""

@@ -239,6 +239,30 @@ def test_matmul_of_operands_computed_from_loaded_tiles(m, k, n, m_tile, k_tile):
     torch.testing.assert_close(c, want, atol=2e-3, rtol=2e-3)
 
 
+@pytest.mark.parametrize("n, tile", [(5000, 512), (1 << 20, 4096)])
+def test_quantise_and_dequantise_through_8_bit_tensors(n, tile):
+    gen = torch.Generator().manual_seed(n)
+    x = torch.randn(n, generator=gen) * 6
+    q = torch.zeros(n, dtype=torch.int8)
+    K.quantise_int8[8](x, q, 16.0, n, tile)
+    want_q = torch.clamp(torch.floor(x * 16.0 + 0.5), -128, 127).to(torch.int8)
+    assert torch.equal(q, want_q) and int(q.min()) == -128 and int(q.max()) == 127
+    keep = (torch.rand(n, generator=gen) > 0.25).to(torch.uint8)
+    back = torch.full((n, ), 7.0)
+    K.dequantise_int8[8](q, keep, back, 0.0625, n, tile)
+    assert torch.equal(back, torch.where(keep != 0, q.float() * 0.0625, torch.zeros(n)))
+    # a loaded 8-bit tile stored as it is stays a copy; arithmetic on 8-bit tiles is refused
+    assert K.quantise_int8.last_plan.pattern == "elementwise:program"
+
+    @asc2.jit
+    def add_bytes(a_ptr: asc.GlobalAddress, o_ptr: asc.GlobalAddress):
+        a_gm, o_gm = asc2.tensor(a_ptr, [1024]), asc2.tensor(o_ptr, [1024])
+        a = asc2.load(a_gm, [1024], offsets=[0])
+        asc2.store(a + a, o_gm, offsets=[0])
+    with pytest.raises(NotImplementedError):
+        add_bytes[1](q[:1024].clone(), torch.zeros(1024, dtype=torch.int8))
+
+
 def test_device_tensors_that_share_a_buffer():
     """x += y through two arguments that are one device buffer works (every element is read before it is written);
     a GEMM whose output argument is also an operand argument is refused before anything is launched."""

@@ -542,3 +542,31 @@ def test_per_row_results_of_one_row_tiles_arrive_as_scalar_stores():
     plan = K.row_losses.last_plan
     assert plan.pattern == "row:program+row:program" and [s.fn_name for s in plan.steps] == ["asc_cuda_row_program"] * 2
     assert all(" over [64, 512] " in s.note for s in plan.steps) and plan.reads == {0, 1} and plan.writes == {2, 3}
+
+
+def test_8_bit_tensors_are_loaded_compared_and_stored_not_computed_on():
+    n = 5000
+    K.quantise_int8[4](torch.zeros(n), torch.zeros(n, dtype=torch.int8), 8.0, n, 512)
+    plan, step = only_step(K.quantise_int8)
+    assert plan.pattern == "elementwise:program" and step.note.endswith("over [0, 5000)")
+    K.dequantise_int8[4](torch.zeros(n, dtype=torch.int8), torch.zeros(n, dtype=torch.uint8), torch.zeros(n), 0.125, n, 512)
+    plan, step = only_step(K.dequantise_int8)
+    assert plan.pattern == "elementwise:program" and plan.reads == {0, 1} and plan.writes == {2}
+
+    @asc2.jit
+    def add_bytes(a_ptr: asc.GlobalAddress, o_ptr: asc.GlobalAddress, form: asc.ConstExpr[int]):
+        a_gm, o_gm = asc2.tensor(a_ptr, [1024]), asc2.tensor(o_ptr, [1024])
+        a = asc2.load(a_gm, [1024], offsets=[0])
+        if form == 0:
+            asc2.store(a + a, o_gm, offsets=[0])                                       # would need a wrap per operation
+        elif form == 1:
+            asc2.store((a.to(asc.int32) * 3).to(asc.int8), o_gm, offsets=[0])          # computed as int32, low byte stored
+        else:
+            asc2.store(a, o_gm, offsets=[0])                                           # a move of bytes
+    b = torch.zeros(1024, dtype=torch.int8)
+    with pytest.raises(NotImplementedError):
+        add_bytes[1](b, b.clone(), 0)
+    add_bytes[1](b, b.clone(), 1)
+    assert add_bytes.last_plan.pattern == "elementwise:program"
+    add_bytes[1](b, b.clone(), 2)
+    assert add_bytes.last_plan.pattern == "copy"
