@@ -473,6 +473,7 @@ class _EltProgram:
         self.n_tmp = 0              # temporary slots the finished program uses
         self.visits = 0             # values visited while generating code
         self.root: Any = None       # the value compile() was asked for (the one the program stores)
+        self.expanded: Dict[int, Tile] = {}   # asc2.softmax nodes of computed tiles -> their row-reduction expression
         self.full_shape: Optional[Tuple[int, ...]] = None   # set while code for a per-row value is generated
         self.ops: List[int] = []
         self.args: List[int] = []
@@ -628,6 +629,8 @@ class _EltProgram:
                     and src.shape in ((self.shape[0], ), (self.shape[0], 1)):
                 return self._per_row(src, self.shape)
             return None
+        if node.kind == "softmax" and v.dtype == KT.float32 and len(v.shape) == 2:
+            return self.gen(self._softmax_expression(v))
         if v.dtype.name not in _ELT_TYPE and node.kind != "compare":
             if node.kind == "cast" and v is self.root and v.dtype.name in _STORAGE_TYPE and not node.args[0].dtype.is_float():
                 return self.gen(node.args[0])       # the stored value: the store keeps the low byte of the word
@@ -669,6 +672,28 @@ class _EltProgram:
                 src = _Frag(src.code + [(_OP_CVT_F2I if src_t.dtype.is_float() else _OP_CVT_I2F, 0)], src.need)
             return self._rounded(src, v.dtype)
         return None
+
+    def _softmax_expression(self, v: Tile) -> Tile:
+        """``asc2.softmax`` of a computed fp32 tile, spelled out as the row reductions a row program runs:
+        ``e / sum(e)`` with ``e = exp(x - max(x))`` along the last dimension (python/asc/language/tile/unary_ops.py:213-223)."""
+        cached = self.expanded.get(id(v.node))
+        if cached is not None:
+            return cached
+        x, loops = v.node.args[0], v.node.loops
+        last = len(x.shape) - 1
+        column = x.shape[:-1] + (1, )
+
+        def tile(of_shape, node_kind, args, attrs):
+            return Tile(of_shape, x.dtype, Node(node_kind, args, attrs, loops), v.location)
+
+        def along_rows(t, which):
+            r = tile(column, "reduce", (t, ), {"kind": which, "dims": (last, ), "keep_dims": True})
+            return tile(x.shape, "broadcast", (r, ), {"shape": x.shape})
+        shifted = tile(x.shape, "binary", (x, along_rows(x, "max")), {"op": "sub"})
+        e = tile(x.shape, "unary", (shifted, ), {"op": "exp"})
+        out = tile(x.shape, "binary", (e, along_rows(e, "sum")), {"op": "div"})
+        self.expanded[id(v.node)] = out
+        return out
 
     def _per_row(self, v: Tile, full_shape: Tuple[int, ...]) -> Optional[_Frag]:
         """Code for a tile that holds one value per row of ``full_shape``."""
@@ -1514,9 +1539,11 @@ def _match_softmax(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         return None
     view = resolve_view(src) if _node(src, "load") or _is_materialised(src) else None
     if view is None:
-        if not _MATERIALISED and _matmul_leaves(src):
-            return None        # a matmul result: _match_matmul_then_program writes it to a temporary and comes back
-        raise _unsupported("softmax of a tile that is not loaded directly from global memory")
+        if _MATERIALISED:
+            raise _unsupported("softmax of a tile that is not loaded directly from global memory")
+        # a matmul result (_match_matmul_then_program writes it to a temporary and comes back) or another computed
+        # tile (a row program computes exp(x - max) / sum over it)
+        return None
     if not _same_offsets(view.offsets, eff.attrs["offsets"]) or view.shape != value.shape:
         raise _unsupported("softmax stored at a different position than it was loaded from")
     if value.dtype not in (KT.float32, KT.float16) or out_t.dtype != value.dtype or view.tensor.dtype != value.dtype:

@@ -60,7 +60,7 @@ std::atomic<bool> g_use_compiled{true};  // tuning hook can force the interprete
 
 template <class Exec, int kLanes>
 int32_t launch_program(const EltProgram& prog, int64_t n, size_t smem, int sms, cudaStream_t stream) {
-  if (smem > 48 * 1024) {
+  if (smem + 1024 > 48 * 1024) {     // dynamic plus the kernel's few static words: beyond the default limit
     static aschost::PerDevice attr_set;
     int dev = 0;
     ASC_CUDA_TRY(cudaGetDevice(&dev));
@@ -145,7 +145,7 @@ int32_t launch_row_program(const EltProgram& prog, int64_t rows, int max_depth, 
   const int tmp_level = max_depth > 2 ? max_depth - 2 : 1;   // the two upper stack entries are registers
   const size_t smem = static_cast<size_t>(tmp_level + n_tmp) * kV * kThreads * sizeof(float);
   if (smem > 200 * 1024) return ASC_ERR_TOO_LARGE;
-  if (smem > 48 * 1024) {
+  if (smem + 1024 > 48 * 1024) {     // dynamic plus the kernel's few static words: beyond the default limit
     static aschost::PerDevice attr_set;
     int dev = 0;
     ASC_CUDA_TRY(cudaGetDevice(&dev));

@@ -242,6 +242,17 @@ def dequantise_int8(q_ptr: asc.GlobalAddress, keep_ptr: asc.GlobalAddress, x_ptr
 
 
 @asc2.jit(always_compile=True)
+def softmax_with_temperature(x_ptr: asc.GlobalAddress, bias_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress,
+                             inv_t: float, rows: int, cols: asc.ConstExpr[int], rpt: asc.ConstExpr[int]):
+    """asc2.softmax of a computed tile: scaled logits plus a bias row."""
+    x_gm, out_gm = asc2.tensor(x_ptr, [rows, cols]), asc2.tensor(out_ptr, [rows, cols])
+    bias = asc2.load(asc2.tensor(bias_ptr, [1, cols]), [1, cols], offsets=[0, 0])
+    for i in range(asc2.block_idx() * rpt, rows, asc2.block_num() * rpt):
+        x = asc2.load(x_gm, [rpt, cols], offsets=[i, 0])
+        asc2.store(asc2.softmax(x * inv_t + bias.broadcast_to(rpt, cols)), out_gm, offsets=[i, 0])
+
+
+@asc2.jit(always_compile=True)
 def glu_rows(x_ptr: asc.GlobalAddress, out_ptr: asc.GlobalAddress, rows: int, cols: asc.ConstExpr[int],
              rpt: asc.ConstExpr[int]):
     """A gated linear unit: the two halves of every row of x, a * sigmoid(g)."""

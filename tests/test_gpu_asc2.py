@@ -209,7 +209,10 @@ def test_expressions_over_several_products_and_fused_row_kernels_over_a_product(
         gamma = asc2.load(asc2.tensor(g_ptr, [n]), [n], offsets=[0])
         for i in range(asc2.block_idx() * m_tile, m, asc2.block_num() * m_tile):
             s = asc2.matmul(asc2.load(a_gm, [m_tile, k], offsets=[i, 0]), asc2.load(b_gm, [k, n], offsets=[0, 0]))
-            asc2.store(asc2.rms_norm(s, gamma, 1e-6) if norm else asc2.softmax(s), o_gm, offsets=[i, 0])
+            if norm == 2:
+                asc2.store(asc2.softmax(s * 0.5), o_gm, offsets=[i, 0])        # a computed tile: a row program
+            else:
+                asc2.store(asc2.rms_norm(s, gamma, 1e-6) if norm else asc2.softmax(s), o_gm, offsets=[i, 0])
     xs = (x.float() * 8).half()                     # scores with a spread of a few units
     s = xs.float() @ w1.float()
     gamma = torch.rand(n, generator=gen) + 0.5
@@ -221,6 +224,9 @@ def test_expressions_over_several_products_and_fused_row_kernels_over_a_product(
     assert [st.fn_name for st in scores.last_plan.steps] == ["asc_cuda_gemm_f16", "asc_cuda_rms_norm_f32"]
     want = s * torch.rsqrt((s * s).mean(dim=-1, keepdim=True) + 1e-6) * gamma
     torch.testing.assert_close(out, want, atol=2e-3, rtol=2e-3)
+    scores[4](xs, w1, gamma, out, m, k, n, 128, 2)
+    assert [st.fn_name for st in scores.last_plan.steps] == ["asc_cuda_gemm_f16", "asc_cuda_row_program"]
+    torch.testing.assert_close(out, torch.softmax(s * 0.5, dim=-1), atol=1e-5, rtol=2e-3)
 
 
 @pytest.mark.parametrize("m, k, n, m_tile, k_tile", [(512, 256, 128, 128, 64), (1000, 512, 272, 128, 128)])

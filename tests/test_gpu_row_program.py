@@ -63,6 +63,17 @@ def test_losses_per_row_from_one_row_tiles():
     torch.testing.assert_close(ce, torch.logsumexp(x, 1) - (x * t).sum(1), rtol=1e-5, atol=1e-5)
 
 
+@pytest.mark.parametrize("rows, cols, rpt", [(64, 1024, 4), (104, 1000, 8), (16, 4096, 1)])
+def test_softmax_of_a_computed_tile(rows, cols, rpt):
+    gen = torch.Generator().manual_seed(rows)
+    x = torch.randn(rows, cols, generator=gen) * 4
+    bias = torch.randn(1, cols, generator=gen)
+    out = torch.zeros_like(x)
+    K.softmax_with_temperature[8](x, bias, out, 0.7, rows, cols, rpt)
+    assert K.softmax_with_temperature.last_plan.pattern == "row:program"
+    torch.testing.assert_close(out, torch.softmax(x * 0.7 + bias, dim=1), rtol=1e-5, atol=1e-8)
+
+
 def test_loaded_columns_repeat_along_the_row():
     gen = torch.Generator().manual_seed(13)
     x, scale, bias = torch.randn(96, 640, generator=gen), torch.randn(96, generator=gen), torch.randn(96, generator=gen)

@@ -570,3 +570,11 @@ def test_8_bit_tensors_are_loaded_compared_and_stored_not_computed_on():
     assert add_bytes.last_plan.pattern == "elementwise:program"
     add_bytes[1](b, b.clone(), 2)
     assert add_bytes.last_plan.pattern == "copy"
+
+
+def test_softmax_of_a_computed_tile_is_spelled_out_as_a_row_program():
+    x = torch.zeros(64, 1024)
+    K.softmax_with_temperature[8](x, torch.zeros(1, 1024), torch.zeros_like(x), 0.5, 64, 1024, 4)
+    plan, step = only_step(K.softmax_with_temperature)
+    assert plan.pattern == "row:program" and step.fn_name == "asc_cuda_row_program" and " over [64, 1024] " in step.note
+    assert plan.reads == {0, 1} and plan.writes == {2}
