@@ -134,6 +134,36 @@ def test_capi_row_program_against_oracle(lib, rows, cols, pad):
     assert pad == 0 or bool((out[:, cols:] == -3.0).all())
 
 
+@pytest.mark.parametrize("cols", [200, 500, 1000, 2048, 4096, 8192])
+def test_capi_row_program_every_stack_depth_and_temporary_count(lib, cols):
+    """Stack depths 2 to 8 with 0 to 4 temporaries at every lane count: shared memory from nothing to beyond the
+    200 KiB the kernel accepts (status 6), through the 48 KiB above which a launch has to opt in."""
+    rows = 24
+    gen = torch.Generator().manual_seed(cols)
+    x = torch.rand(rows, cols, generator=gen) + 0.5
+    xd = x.cuda()
+    per_thread = -(-cols // 256)
+    lanes = 1
+    while lanes < per_thread:
+        lanes *= 2
+    for depth in range(2, 9):
+        for n_tmp in range(0, 5):
+            # x, kept in n_tmp slots; then depth loads folded from the top (x * (x + (x * ...))); the slots added; x / row sum
+            ops = [0] + [63] * n_tmp + [0] * (depth - 1) + [4 if k % 2 else 2 for k in range(depth - 1)]
+            args = [0] + list(range(n_tmp)) + [0] * (2 * (depth - 1))
+            for k in range(n_tmp):
+                ops += [64, 2]
+                args += [k, 0]
+            ops += [59, 0, 55]                  # ROW_SUM, LOAD x, RDIV: x / sum
+            args += [0, 0, 0]
+            smem = (max(depth - 2, 1) + n_tmp) * lanes * 256 * 4
+            out = torch.zeros(rows, cols, device="cuda")
+            run_row_program(lib, ops, args, [xd], out, rows, cols, None, 0, expect=6 if smem > 200 * 1024 else 0)
+            if smem <= 200 * 1024:
+                want = E.run_program(ops, args, [x], 0)
+                torch.testing.assert_close(out.cpu(), want, rtol=1e-5, atol=1e-30, msg=lambda m: f"depth {depth}, {n_tmp} slots: {m}")
+
+
 def test_capi_row_result_and_fp16_operands(lib):
     x = torch.randn(1000, 777, device="cuda").half()
     out = torch.zeros(1000, device="cuda")
