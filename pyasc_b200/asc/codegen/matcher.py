@@ -819,13 +819,17 @@ class _Geometry:
     contiguous range of ``numel`` elements (``pitch`` None) or ``rows`` x ``cols`` with a row pitch."""
 
     def __init__(self, tensor: Tensor, offsets: Sequence[PlainValue], shape: Tuple[int, ...], scalar: bool,
-                 env: Dict[str, np.ndarray], n: int):
+                 env: Dict[str, np.ndarray], n: int, clip: bool = False):
+        """``clip``: a tile may reach past the last row (or the last element of a flat range) of its tensor; how far
+        every instance's tile lies inside is kept in ``avail`` (elements of a flat range, rows of a window) for the
+        planner to cut the call short, as a clipped store and a padded load of elements nobody stores would."""
         tshape = tensor.static_shape()
         numel = 1
         for d in tshape:
             numel *= d
         self.pitch: Optional[int] = None
         self.rows, self.cols = 1, 1
+        self.avail: Optional[np.ndarray] = None
         if scalar:
             self.start = eval_int(_flat_scalar_offset(tshape, offsets), env, n)
             self.numel, ends = 1, None
@@ -838,9 +842,10 @@ class _Geometry:
                 r0, c0 = eval_int(offsets[0], env, n), eval_int(offsets[1], env, n)
                 if n and (r0.min() < 0 or c0.min() < 0):
                     raise RuntimeError("Negative tile offset in kernel")
-                if n and ((r0 + shape[0]).max() > tshape[0] or (c0 + shape[1]).max() > tshape[1]):
+                if n and (((r0 + shape[0]).max() > tshape[0] and not clip) or (c0 + shape[1]).max() > tshape[1]):
                     raise _unsupported("tile that reaches past the end of its tensor in a kernel whose operands are "
                                        "addressed differently from its result")
+                self.avail = tshape[0] - r0
                 self.start = r0 * tshape[1] + c0
                 self.rows, self.cols, self.pitch = shape[0], shape[1], tshape[1]
                 self.numel = shape[0] * shape[1]
@@ -848,9 +853,11 @@ class _Geometry:
                 raise _unsupported("tile that is neither a contiguous range nor a 2-D window of a matrix")
         if n and self.start.min() < 0:
             raise RuntimeError("Negative tile offset in kernel")
-        if self.pitch is None and n and (self.start + self.numel).max() > numel:
+        if self.pitch is None and n and (self.start + self.numel).max() > numel and not (clip and not scalar):
             raise _unsupported("tile that reaches past the end of its tensor in a kernel whose operands are addressed "
                                "differently from its result")
+        if self.pitch is None and not scalar:
+            self.avail = numel - self.start
 
 
 def _program_arrays(prog: "_EltProgram", out_t: Tensor):
@@ -886,8 +893,8 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
     n = env_count(env)
     if n > MAX_CALLS:
         raise _unsupported("elementwise kernel with differently addressed operands and more than 4096 tiles")
-    out_g = _Geometry(out_t, offsets, out_shape, scalar_store, env, n)
-    geoms = [_Geometry(o.tensor, o.offsets, o.shape, o.scalar, env, n) for o in prog.operands]
+    out_g = _Geometry(out_t, offsets, out_shape, scalar_store, env, n, clip=True)
+    geoms = [_Geometry(o.tensor, o.offsets, o.shape, o.scalar, env, n, clip=True) for o in prog.operands]
     # the window every call walks: rows x cols
     rows, cols = (out_g.rows, out_g.cols) if out_g.pitch is not None else (1, out_g.numel)
     for o, g in zip(prog.operands, geoms):
@@ -959,8 +966,39 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
     fn_name = "asc_cuda_row_program" if row_shape is not None else "asc_cuda_eltwise_program_2d"
     tail_args = (ctypes.c_int32(1 if row_result else 0), ) if row_shape is not None else ()
     program_key = _program_key(prog, cols if row_shape is not None else None)
-    calls: List[Tuple[Tuple[int, ...], int]] = []      # (first element of every operand and of the result, rows)
-    all_starts = [tuple(int(g.start[j]) for g in geoms) + (int(out_g.start[j]), ) for j in range(n)]
+    # Tiles that reach past the end of their tensors (the last block of a row count that is no multiple of the tile):
+    # the store is clipped there, so the call is cut to the rows (for a one-row call: the elements) that exist in the
+    # result; every operand must hold at least those, or the kernel would have computed on padding.
+    out_cols = 1 if row_result else cols
+    full = np.full(n, rows if rows > 1 or row_shape is not None else cols, dtype=np.int64)
+    by_rows = rows > 1 or row_shape is not None
+
+    def supply(g: "_Geometry", per_unit: int) -> np.ndarray:
+        """Call rows (or, in a one-row call, elements) of each instance's tile that lie inside the tensor."""
+        if g.avail is None:
+            return full
+        if g.pitch is not None:
+            return g.avail if by_rows else np.where(g.avail >= 1, full, 0)
+        return g.avail // per_unit if by_rows else g.avail
+    have = np.minimum(full, np.maximum(supply(out_g, out_cols), 0))
+    if by_rows and out_g.pitch is None and out_g.avail is not None and np.any((np.minimum(out_g.avail, out_g.numel) % out_cols) != 0):
+        raise _unsupported("tile whose part inside the tensor is not a whole number of rows")
+    for o, g in zip(prog.operands, geoms):
+        if o.bcast or o.scalar:
+            if g.avail is not None and np.any(g.avail < (g.numel if g.pitch is None else g.rows)):
+                raise _unsupported("broadcast row that reaches past the end of its tensor (zero padding)")
+            continue
+        if np.any(supply(g, 1 if o.per_row else cols) < have):
+            raise _unsupported("operand tile that reaches past the end of its tensor where the result does not "
+                               "(zero padding would be computed on)")
+    calls: List[Tuple[Tuple[int, ...], int, int]] = []  # (first element of every operand and of the result, rows, cols)
+    keep = [j for j in range(n) if have[j] > 0]
+    extent = {}
+    all_starts = []
+    for j in keep:
+        st = tuple(int(g.start[j]) for g in geoms) + (int(out_g.start[j]), )
+        all_starts.append(st)
+        extent[st] = max(extent.get(st, 0), int(have[j]))
     if dedupe and len(set(all_starts)) > 1:
         # Instances that differ in where they read from but write overlapping elements do not commute: the last
         # writer (in block order, then iteration order) must win, so such a kernel keeps one call per instance in
@@ -968,7 +1006,12 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
         uniq = sorted(set(all_starts))
         u = np.array(uniq, dtype=np.int64)
         width = out_t.static_shape()[-1] if out_t.static_shape() else 1
-        rect = _flat_rects(width, u[:, -1], out_g.numel, out_g.rows, out_g.cols, out_g.pitch)
+        if out_g.pitch is None:
+            # flat ranges, cut at the end of the tensor where a tile reaches past it
+            ends = np.minimum(u[:, -1] + out_g.numel, out_t.base.numel)
+            rect = np.stack([np.zeros_like(ends), np.ones_like(ends), u[:, -1], ends], axis=1)
+        else:
+            rect = _flat_rects(width, u[:, -1], out_g.numel, out_g.rows, out_g.cols, out_g.pitch)
         clash = _rects_overlap(rect, rect)
         np.fill_diagonal(clash, False)
         if clash.any():
@@ -977,29 +1020,31 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
         # stores are idempotent and independent: drop repeats, and let windows that continue each other row
         # after row (every operand advancing by its own pitch, a broadcast row staying put) become one call
         for starts in sorted(set(all_starts), key=lambda st: st[-1]):
+            here = (extent[starts], cols) if by_rows else (rows, extent[starts])
             if calls and cols > 0 and not prog.uses_index:      # (an element index restarts with every tile)
-                prev, prev_rows = calls[-1]
-                if all(st == p0 + prev_rows * ld for st, p0, ld in zip(starts, prev, lds)):
-                    calls[-1] = (prev, prev_rows + rows)
+                prev, prev_rows, prev_cols = calls[-1]
+                if prev_cols == here[1] and all(st == p0 + prev_rows * ld for st, p0, ld in zip(starts, prev, lds)):
+                    calls[-1] = (prev, prev_rows + here[0], prev_cols)
                     continue
-            calls.append((starts, rows))
+            calls.append((starts, ) + here)
     else:
-        calls = [(starts, rows) for starts in all_starts]
-    def make_step(starts: Tuple[int, ...], call_rows: int) -> Step:
+        calls = [(all_starts[k], int(have[j]), cols) if by_rows else (all_starts[k], rows, int(have[j]))
+                 for k, j in enumerate(keep)]
+
+    def make_step(starts: Tuple[int, ...], call_rows: int, call_cols: int = cols) -> Step:
         def build(ptrs, stream):
             ins = (ctypes.c_void_p * max(1, n_in))(*[ptrs[i] + sz * st for i, sz, st in zip(in_idx, in_size, starts)])
             return (ops_arr, args_arr, ctypes.c_int32(n_ops), ins, types_arr, ctypes.c_int32(n_in),
                     _p(ptrs[out_idx] + out_size * starts[-1]), ctypes.c_int32(out_type), ctypes.c_int64(call_rows),
-                    ctypes.c_int64(cols), lds_arr) + tail_args + (stream, )
+                    ctypes.c_int64(call_cols), lds_arr) + tail_args + (stream, )
         step = Step(fn_name, build,
-                    f"{n_ops} ops over [{call_rows}, {cols}] pitches {lds} from {list(starts[:-1])} to {starts[-1]}")
-        step.program, step.elements = program_key, call_rows * cols
+                    f"{n_ops} ops over [{call_rows}, {call_cols}] pitches {lds} from {list(starts[:-1])} to {starts[-1]}")
+        step.program, step.elements = program_key, call_rows * call_cols
         return step
 
-    for starts, call_rows in calls:
-        plan.steps.append(make_step(starts, call_rows))
-    out_cols = 1 if row_result else cols
-    covered = sum(r for _, r in calls) * out_cols
+    for starts, call_rows, call_cols in calls:
+        plan.steps.append(make_step(starts, call_rows, call_cols))
+    covered = sum(r * (1 if row_result else c) for _, r, c in calls)
     if dedupe and len(calls) == 1 and lds[-1] == out_cols and calls[0][0][-1] == 0 and covered == out_t.base.numel:
         plan.partial_writes.discard(out_idx)
     if not plan.steps:
@@ -1007,7 +1052,7 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
     if row_shape is not None and not plan.partial_writes and len(calls) == 1:
         # whole rows of whole tensors: chunks of rows can be uploaded, computed and downloaded independently;
         # a broadcast row is needed by every chunk
-        starts0, total_rows = calls[0]
+        starts0, total_rows, _ = calls[0]
         whole = all(st == 0 and (ld == 0 or ld * total_rows == o.tensor.base.numel)
                     for st, ld, o in zip(starts0, lds, prog.operands))
         if whole and len(set(in_idx)) == len(in_idx) and out_idx not in in_idx:

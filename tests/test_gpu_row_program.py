@@ -6,6 +6,7 @@ import numpy as np
 import pytest
 import torch
 
+import asc
 import asc.runtime.config as config
 import asc2
 
@@ -22,7 +23,7 @@ def platform():
 
 
 @pytest.mark.parametrize("rows, cols, block, blocks", [(64, 512, 8, 4), (256, 4096, 4, 16), (32, 8, 8, 2),
-                                                       (48, 1000, 2, 3)])
+                                                       (48, 1000, 2, 3), (100, 512, 8, 4), (5, 1024, 4, 16)])
 def test_layer_norm(rows, cols, block, blocks):
     gen = torch.Generator().manual_seed(rows + cols)
     x = torch.randn(rows, cols, generator=gen) * 2 + 1
@@ -63,7 +64,7 @@ def test_losses_per_row_from_one_row_tiles():
     torch.testing.assert_close(ce, torch.logsumexp(x, 1) - (x * t).sum(1), rtol=1e-5, atol=1e-5)
 
 
-@pytest.mark.parametrize("rows, cols, rpt", [(64, 1024, 4), (104, 1000, 8), (16, 4096, 1)])
+@pytest.mark.parametrize("rows, cols, rpt", [(64, 1024, 4), (104, 1000, 8), (16, 4096, 1), (100, 1000, 8), (7, 512, 16)])
 def test_softmax_of_a_computed_tile(rows, cols, rpt):
     gen = torch.Generator().manual_seed(rows)
     x = torch.randn(rows, cols, generator=gen) * 4
@@ -368,12 +369,33 @@ def test_tile_divided_by_a_reduction_of_the_whole_tile(op, torch_op):
     torch.testing.assert_close(out, want, rtol=2e-6, atol=0)
 
 
-def test_vector_bias_reshaped_to_a_row():
+@pytest.mark.parametrize("rows", [256, 100, 33, 7])
+def test_vector_bias_reshaped_to_a_row(rows):
+    """Also with a row count that is no multiple of the 32-row tile: the last tile is cut to the rows that exist."""
     gen = torch.Generator().manual_seed(6)
-    x, b = torch.randn(256, 64, generator=gen), torch.randn(64, generator=gen)
-    out = torch.zeros_like(x)
-    K.add_vector_bias[4](x, b, out, 256, 64, 32)
-    assert torch.equal(out, x + b)
+    x, b = torch.randn(rows, 64, generator=gen), torch.randn(64, generator=gen)
+    out = torch.full((rows + 4, 64), 9.0)
+    K.add_vector_bias[4](x, b, out[:rows], rows, 64, 32)
+    assert torch.equal(out[:rows], x + b) and bool((out[rows:] == 9.0).all())
+
+
+def test_ragged_last_tiles_with_shifted_and_strided_operands():
+    gen = torch.Generator().manual_seed(8)
+    x = torch.randn(100, 1024, generator=gen)
+    out = torch.zeros(100, 512)
+    K.glu_rows[4](x, out, 100, 512, 8)
+    torch.testing.assert_close(out, x[:, :512] / (torch.exp(-x[:, 512:]) + 1), rtol=2e-6, atol=1e-6)
+
+    @asc2.jit
+    def shifted(x_ptr: asc.GlobalAddress, y_ptr: asc.GlobalAddress, o_ptr: asc.GlobalAddress, n: int, tile: asc.ConstExpr[int]):
+        x_gm, y_gm, o_gm = asc2.tensor(x_ptr, [n + 8]), asc2.tensor(y_ptr, [n]), asc2.tensor(o_ptr, [n])
+        for i in range(asc2.block_idx() * tile, n, asc2.block_num() * tile):
+            asc2.store(asc2.load(x_gm, [tile], offsets=[i + 8]) + asc2.load(y_gm, [tile], offsets=[i]), o_gm, offsets=[i])
+    for n in (1000, 5, 256):
+        a, b = torch.randn(n + 8, generator=gen), torch.randn(n, generator=gen)
+        o = torch.full((n + 3, ), 9.0)
+        shifted[2](a, b, o[:n], n, 256)
+        assert torch.equal(o[:n], a[8:] + b) and bool((o[n:] == 9.0).all())
 
 
 @pytest.mark.parametrize("op, atomic, torch_op", [(asc2.reduce_sum, asc2.atomic_add, torch.sum),

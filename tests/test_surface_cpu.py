@@ -578,3 +578,39 @@ def test_softmax_of_a_computed_tile_is_spelled_out_as_a_row_program():
     plan, step = only_step(K.softmax_with_temperature)
     assert plan.pattern == "row:program" and step.fn_name == "asc_cuda_row_program" and " over [64, 1024] " in step.note
     assert plan.reads == {0, 1} and plan.writes == {2}
+
+
+def test_ragged_last_tiles_of_kernels_whose_operands_are_addressed_differently():
+    """A row count that is no multiple of the tile: the last tile reaches past the tensors, its store is clipped
+    and the call is cut to the rows that exist.  An operand that ends before the result would bring zero padding
+    into stored elements: refused."""
+    x = torch.zeros(100, 64)
+    K.add_vector_bias[4](x, torch.zeros(64), torch.zeros_like(x), 100, 64, 32)
+    assert only_step(K.add_vector_bias)[1].note == "3 ops over [100, 64] pitches [64, 0, 64] from [0, 0] to 0"
+    x = torch.zeros(100, 1000)
+    K.softmax_with_temperature[8](x, torch.zeros(1, 1000), torch.zeros_like(x), 0.5, 100, 1000, 8)
+    assert " over [100, 1000] " in only_step(K.softmax_with_temperature)[1].note
+    K.glu_rows[4](torch.zeros(100, 1024), torch.zeros(100, 512), 100, 512, 8)
+    assert " over [100, 512] pitches [1024, 1024, 512] " in only_step(K.glu_rows)[1].note
+
+    @asc2.jit
+    def shifted(x_ptr: asc.GlobalAddress, y_ptr: asc.GlobalAddress, o_ptr: asc.GlobalAddress, n: int, extra: asc.ConstExpr[int],
+                tile: asc.ConstExpr[int]):
+        x_gm, y_gm, o_gm = asc2.tensor(x_ptr, [n + extra]), asc2.tensor(y_ptr, [n]), asc2.tensor(o_ptr, [n])
+        for i in range(asc2.block_idx() * tile, n, asc2.block_num() * tile):
+            asc2.store(asc2.load(x_gm, [tile], offsets=[i + extra]) + asc2.load(y_gm, [tile], offsets=[i]), o_gm, offsets=[i])
+    shifted[2](torch.zeros(1008), torch.zeros(1000), torch.zeros(1000), 1000, 8, 256)
+    assert [s.note for s in shifted.last_plan.steps] == [
+        "3 ops over [3, 256] pitches [256, 256, 256] from [8, 0] to 0",
+        "3 ops over [1, 232] pitches [256, 256, 256] from [776, 768] to 768"]
+    with pytest.raises(NotImplementedError, match="zero padding would be computed on"):
+        _short_operand()
+
+
+def _short_operand():
+    @asc2.jit
+    def short(x_ptr: asc.GlobalAddress, y_ptr: asc.GlobalAddress, o_ptr: asc.GlobalAddress, n: int, tile: asc.ConstExpr[int]):
+        x_gm, y_gm, o_gm = asc2.tensor(x_ptr, [n - 8]), asc2.tensor(y_ptr, [n]), asc2.tensor(o_ptr, [n])
+        for i in range(asc2.block_idx() * tile, n, asc2.block_num() * tile):
+            asc2.store(asc2.load(x_gm, [tile], offsets=[i]) + asc2.load(y_gm, [tile], offsets=[i]), o_gm, offsets=[i])
+    short[2](torch.zeros(992), torch.zeros(1000), torch.zeros(1000), 1000, 256)
