@@ -129,8 +129,7 @@ int32_t asc_cuda_vmuladd_f32(const float* x, const float* y, const float* z, flo
  * 50 IRELU, 51 CVT_I2F, 52 CVT_F2I (truncating), 53 WRAP_I16 (sign-extend the low half); with the
  * operands swapped (rhs op lhs) 54 RSUB, 55 RDIV, 56 IRSUB, 57 IRSHL, 58 IRSHR.  A binary opcode
  * with bit 8 set (| 0x100) takes args[j] as its left operand instead of a stack entry.
- * Element types: 0 fp32, 1 fp16, 2 bf16, 3 int32, 4 int16, and the storage-only types 5 int8 and 6 uint8 (a load
- * widens them to an int32 word, sign- or zero-extended; a store keeps the low byte of the word); at most 6 inputs.
+ * Element types: 0 fp32, 1 fp16, 2 bf16, 3 int32, 4 int16; at most 6 inputs.
  * The program is validated on the host (status 1 for a malformed one, 6 for a stack deeper than 8).
  * Replaces the per-op vector calls the reference lowers such kernels to
  * (python/asc/language/tile/binary_ops.py, unary_ops.py, indexing_ops.py:where;
@@ -199,6 +198,13 @@ int32_t asc_cuda_register_program(int32_t kind, const int32_t* words, int32_t n_
  * to DataCopy between global and on-chip memory (python/asc/language/tile/memory_ops.py). */
 int32_t asc_cuda_copy_2d(void* dst, const void* src, int64_t rows, int64_t row_bytes, int64_t dst_pitch,
                          int64_t src_pitch, void* stream);
+
+/* 8-bit integers <-> int32 words, n elements.  mode 0: int8 -> int32 (sign-extended), 1: uint8 -> int32
+ * (zero-extended), 2: int32 -> its low byte (int8 and uint8 alike).  The 32-bit side must be 4-byte aligned.
+ * The elementwise programs compute on 32- and 16-bit types; a kernel that loads or stores an int8 / uint8 tile gets its
+ * bytes widened into, or narrowed out of, an int32 temporary by this call.  Replaces the CastOp between integer
+ * widths around such a tile (python/asc/language/tile/tile.py:60-78; ConvertCast, lib/Conversion/LowerToAsc/LowerAscTile.cpp:129-160). */
+int32_t asc_cuda_convert_bytes(void* dst, const void* src, int64_t n, int32_t mode, void* stream);
 
 /* Reduction of a row-major [rows, cols] fp32 window with row pitch `ld` (elements).  kind: 0 sum, 1 max,
  * 2 min, 3 product.  axis 1: out[r] = reduce over the columns of row r; axis 0: out[c] = reduce over the

@@ -29,8 +29,7 @@ _ROW = {59: lambda t: t.sum(-1, keepdim=True), 60: lambda t: t.amax(-1, keepdim=
         61: lambda t: t.amin(-1, keepdim=True), 62: lambda t: t.prod(-1, keepdim=True)}
 IMM = 0x100
 INDEX = 65                 # the element's row-major index inside the window, as int32
-TYPES = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16, 3: torch.int32, 4: torch.int16, 5: torch.int8,
-         6: torch.uint8}      # 8-bit types are storage only: widened by the load, the low byte kept by the store
+TYPES = {0: torch.float32, 1: torch.float16, 2: torch.bfloat16, 3: torch.int32, 4: torch.int16}
 
 
 def run_program(ops: Sequence[int], args: Sequence[int], inputs: List[torch.Tensor], out_type: int) -> torch.Tensor:
@@ -78,7 +77,7 @@ def run_program(ops: Sequence[int], args: Sequence[int], inputs: List[torch.Tens
             stack.append(_I_SWAPPED[op](b, a))
         elif op == WHERE:
             b, a, c = stack.pop(), stack.pop(), as_float(stack.pop())
-            int_kind = any(isinstance(v, torch.Tensor) and v.dtype == torch.int32 for v in (a, b)) or out_type in (3, 4, 5, 6)
+            int_kind = any(isinstance(v, torch.Tensor) and v.dtype == torch.int32 for v in (a, b)) or out_type in (3, 4)
             conv = as_int if int_kind else as_float
             stack.append(torch.where(c != 0, conv(a), conv(b)))
         elif op in _F_UNARY:

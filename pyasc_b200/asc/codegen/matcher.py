@@ -358,10 +358,12 @@ _INT_COMPARE_CODE = {"eq": 42, "ne": 43, "gt": 44, "ge": 45, "lt": 46, "le": 47}
 _INT_UNARY_CODE = {"neg": 48, "abs": 49, "relu": 50}
 _OP_CVT_I2F, _OP_CVT_F2I, _OP_WRAP_I16 = 51, 52, 53
 _ELT_TYPE = {"float32": 0, "float16": 1, "bfloat16": 2, "int32": 3, "int16": 4}
-# 8-bit integers are storage types: a load widens them to int32 words and a store keeps the low byte, so a program
-# may load them (to compare, or to cast to a wider integer) and may store an integer cast to them; it does not
-# compute on 8-bit tiles (that would need a wrap after every operation).
-_STORAGE_TYPE = {**_ELT_TYPE, "int8": 5, "uint8": 6}
+# 8-bit integers are storage types: a program may load them (to compare, or to cast to a wider integer) and may
+# store an int32 cast to them; it does not compute on 8-bit tiles (that would need a wrap after every operation).
+# The kernels never see them: an int8 / uint8 tensor a program loads is first widened, whole, into an int32
+# temporary (its "twin"), and an 8-bit result is narrowed out of one (asc_cuda_convert_bytes).
+_BYTE_TYPES = ("int8", "uint8")
+_STORAGE_TYPE = {**_ELT_TYPE, "int8": 3, "uint8": 3}
 _ROUND_CODE = {"float16": _OP_ROUND_F16, "bfloat16": _OP_ROUND_BF16, "int16": _OP_WRAP_I16}
 ELT_MAX_OPS, ELT_MAX_INPUTS, ELT_MAX_STACK = 48, 6, 8
 _ROW_CODE = {"sum": 59, "max": 60, "min": 61, "prod": 62}     # row programs: reduce the top of the stack over the row
@@ -474,6 +476,8 @@ class _EltProgram:
         self.visits = 0             # values visited while generating code
         self.root: Any = None       # the value compile() was asked for (the one the program stores)
         self.expanded: Dict[int, Tile] = {}   # asc2.softmax nodes of computed tiles -> their row-reduction expression
+        self.allow_bytes = False    # the caller widens int8 / uint8 operands into int32 twins before the program runs
+        self.twins: Dict[str, Tuple[Tensor, Tensor]] = {}   # twin key -> (int32 twin, the 8-bit tensor)
         self.full_shape: Optional[Tuple[int, ...]] = None   # set while code for a per-row value is generated
         self.ops: List[int] = []
         self.args: List[int] = []
@@ -509,8 +513,20 @@ class _EltProgram:
             return _Frag(rhs.code + lhs.code + [(_SWAPPED[code], 0)], max(rhs.need, lhs.need + 1))
         return _Frag(lhs.code + rhs.code + [(code, 0)], max(lhs.need, rhs.need + 1))
 
+    def _twin(self, tensor: Tensor) -> Tensor:
+        """The int32 stand-in of an int8 / uint8 tensor (one per tensor, so that equal operands stay equal)."""
+        key = _twin_key(tensor)
+        if key not in self.twins:
+            self.twins[key] = (_fake_like(key, tensor, KT.int32), tensor)
+        return self.twins[key][0]
+
     def _load(self, operand: _Operand) -> Optional[_Frag]:
-        if operand.tensor.dtype.name not in _STORAGE_TYPE:
+        if operand.tensor.dtype.name in _BYTE_TYPES:
+            if not self.allow_bytes:
+                return None
+            operand = _Operand(self._twin(operand.tensor), operand.offsets, operand.shape, operand.bcast, operand.scalar,
+                               operand.per_row)
+        if operand.tensor.dtype.name not in _ELT_TYPE:
             return None
         for k, o in enumerate(self.operands):
             if o.same(operand):
@@ -632,8 +648,6 @@ class _EltProgram:
         if node.kind == "softmax" and v.dtype == KT.float32 and len(v.shape) == 2:
             return self.gen(self._softmax_expression(v))
         if v.dtype.name not in _ELT_TYPE and node.kind != "compare":
-            if node.kind == "cast" and v is self.root and v.dtype.name in _STORAGE_TYPE and not node.args[0].dtype.is_float():
-                return self.gen(node.args[0])       # the stored value: the store keeps the low byte of the word
             return None
         if node.kind == "binary":
             code = (_BINARY_CODE if v.dtype.is_float() else _INT_BINARY_CODE).get(node.attrs["op"])
@@ -863,8 +877,8 @@ class _Geometry:
 def _program_arrays(prog: "_EltProgram", out_t: Tensor):
     n_ops, n_in = len(prog.ops), len(prog.operands)
     return (n_ops, n_in, (ctypes.c_int32 * n_ops)(*prog.ops), (ctypes.c_int32 * n_ops)(*prog.args),
-            (ctypes.c_int32 * max(1, n_in))(*[_STORAGE_TYPE[o.tensor.dtype.name] | (_ROW_SCALAR_INPUT if o.per_row else 0)
-                                              for o in prog.operands]), _STORAGE_TYPE[out_t.dtype.name])
+            (ctypes.c_int32 * max(1, n_in))(*[_ELT_TYPE[o.tensor.dtype.name] | (_ROW_SCALAR_INPUT if o.per_row else 0)
+                                              for o in prog.operands]), _ELT_TYPE[out_t.dtype.name])
 
 
 def _program_key(prog: "_EltProgram", row_cols: Optional[int] = None):
@@ -1064,17 +1078,86 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
     return plan
 
 
+def _twin_key(tensor: Tensor) -> str:
+    return f"wide{tensor.base.index}"
+
+
+def _fake_like(key: str, tensor: Tensor, dtype: DataType) -> Tensor:
+    """A temporary of ``tensor``'s shape and another element type."""
+    from ..language.core.ir_value import GlobalAddress
+    base = GlobalAddress(key, dtype, key, tensor.base.numel)  # type: ignore[arg-type]
+    return Tensor(base, tuple(PlainValue.const(d) for d in tensor.static_shape()))
+
+
+def _convert_step(dst: Any, src: Any, n: int, mode: int, note: str) -> Step:
+    def build(ptrs, stream):
+        return (_p(ptrs[dst]), _p(ptrs[src]), ctypes.c_int64(n), ctypes.c_int32(mode), stream)
+    return Step("asc_cuda_convert_bytes", build, note)
+
+
 def _match_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
+    """An elementwise or row program.  int8 / uint8 tensors take part through int32 twins: every 8-bit tensor the
+    program loads is widened, whole, into a temporary first; an 8-bit result (an int32 value cast down) is computed
+    into the twin of the output tensor and narrowed out of it afterwards -- the twin is filled from the tensor
+    first where the kernel writes only part of it, so that the rest keeps its bytes."""
+    value, out_t = eff.args
+    narrow = None
+    if out_t.dtype.name in _BYTE_TYPES:
+        cast = _node(value, "cast") if isinstance(value, Tile) else None
+        if cast is None or value.dtype != out_t.dtype or cast.args[0].dtype != KT.int32:
+            return None          # (a loaded 8-bit tile stored as it is: a copy)
+        narrow = (_fake_like(_twin_key(out_t), out_t, KT.int32), out_t)
+        eff = Effect(eff.kind, (cast.args[0], narrow[0]), eff.attrs, eff.loops, eff.guards)
+    found = _plan_eltwise_program(trace, eff)
+    if found is None:
+        return None
+    plan, prog = found
+    if not prog.twins and narrow is None:
+        return plan
+    before: List[Step] = []
+    for key, (twin, real) in prog.twins.items():
+        if narrow is not None and real.base.index == narrow[1].base.index:
+            raise _unsupported("8-bit tensor that a kernel both loads and stores")
+        plan.temps[key] = 4 * real.base.numel
+        before.append(_convert_step(key, real.base.index, real.base.numel, 0 if real.dtype.name == "int8" else 1,
+                                    f"{real.dtype.name}[{real.base.numel}] -> int32 temporary"))
+        plan.reads.discard(key)
+        plan.reads.add(real.base.index)
+    after: List[Step] = []
+    if narrow is not None:
+        twin, real = narrow
+        key, idx, n = twin.base.index, real.base.index, real.base.numel
+        plan.temps[key] = 4 * n
+        if key in plan.partial_writes:
+            before.append(_convert_step(key, idx, n, 0 if real.dtype.name == "int8" else 1,
+                                        f"{real.dtype.name}[{n}] -> int32 temporary (the part the kernel leaves)"))
+            plan.partial_writes.discard(key)
+            plan.partial_writes.add(idx)
+        after.append(_convert_step(idx, key, n, 2, f"int32 temporary -> {real.dtype.name}[{n}]"))
+        plan.writes.discard(key)
+        plan.writes.add(idx)
+    plan.steps = before + plan.steps + after
+    plan.pipeline = None
+    return plan
+
+
+def _plan_eltwise_program(trace: KernelTrace, eff: Effect) -> Optional[Tuple[Plan, "_EltProgram"]]:
+    plan_prog: List[Any] = []
+    plan = _plan_eltwise_program_with(trace, eff, plan_prog)
+    return None if plan is None else (plan, plan_prog[0])
+
+
+def _plan_eltwise_program_with(trace: KernelTrace, eff: Effect, made: List[Any]) -> Optional[Plan]:
     value, out_t = eff.args
     offsets = eff.attrs["offsets"]
     scalar_store = eff.kind == "store_scalar"
-    if not isinstance(value, (Tile, PlainValue)) or out_t.dtype.name not in _STORAGE_TYPE or value.dtype != out_t.dtype:
+    if not isinstance(value, (Tile, PlainValue)) or out_t.dtype.name not in _ELT_TYPE or value.dtype != out_t.dtype:
         return None
-    if out_t.dtype.name not in _ELT_TYPE and not (isinstance(value, Tile) and value.node.kind == "cast"):
-        return None          # (a loaded 8-bit tile stored as it is: a copy)
     tshape = out_t.static_shape()
     out_shape = (1, ) if scalar_store else value.shape
     prog = _EltProgram(out_shape, offsets, out_t, scalar_store)
+    prog.allow_bytes = True
+    made.append(prog)
     if not prog.compile(value):
         return None
     _check_program_limits(prog)
@@ -1893,6 +1976,7 @@ def _materialise_operand(trace: KernelTrace, tile: Tile, plan: Plan) -> Optional
     if sub is None:
         return None
     plan.temps[key] = source.static_shape()[0] * source.static_shape()[1] * tile.dtype.sizeof()
+    plan.temps.update(sub.temps)
     plan.steps.extend(sub.steps)
     plan.reads.update(r for r in sub.reads if r != key)
     return _Window(tmp, offsets[0], offsets[1], tile.shape[0], tile.shape[1])
@@ -2288,6 +2372,7 @@ def _match_column_statistics(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
         _MATERIALISED.clear()
     if tail is None:
         raise _unsupported("expression around reductions along the first axis that is not elementwise")
+    plan.temps.update(tail.temps)
     plan.steps.extend(tail.steps)
     plan.reads.update(r for r in tail.reads if not (isinstance(r, str) and r.startswith("tmp")))
     plan.writes.update(tail.writes)
@@ -2367,6 +2452,7 @@ def _match_matmul_then_program(trace: KernelTrace, eff: Effect) -> Optional[Plan
         raise refusal or _unsupported("expression around a matmul result that is not elementwise")
     for key in keys:
         tail.reads.discard(key)
+    plan.temps.update(tail.temps)
     plan.steps.extend(tail.steps)
     plan.reads.update(tail.reads)
     plan.writes.update(tail.writes)

@@ -56,6 +56,7 @@ PROTOTYPES: Dict[str, Sequence] = {
     "asc_cuda_col_program": (P, P, c_int32, P, P, c_int32, P, c_int32, c_int64, c_int64, P, c_int32, P),
     "asc_cuda_register_program": (c_int32, P, c_int32, P),
     "asc_cuda_copy_2d": (P, P, c_int64, c_int64, c_int64, c_int64, P),
+    "asc_cuda_convert_bytes": (P, P, c_int64, c_int32, P),
     "asc_cuda_reduce_f32": (P, P, c_int64, c_int64, c_int64, c_int32, c_int32, c_int64, P),
     "asc_cuda_reduce_all_f16": (P, P, c_int64, c_int64, c_int64, c_int32, c_int64, c_int32, P),
     "asc_cuda_softmax_f32": (P, P, c_int64, c_int64, c_int64, P),

@@ -104,10 +104,7 @@ using GeluErf = OpList<LD(0), LD(0), OP_MUL | I, OP_ERF, OP_ADD | I, OP_MUL, OP_
 using GeluTanh = OpList<LD(0), LD(0), OP_MUL, OP_MUL | I, OP_ADD | I, LD(0), OP_MUL, OP_EXP, OP_ADD | I, LD(0), OP_RDIV,
                         LD(0), OP_RSUB>;
 
-int elem_size(int type) {
-  if (type == T_I8 || type == T_U8) return 1;
-  return (type == T_F16 || type == T_BF16 || type == T_I16) ? 2 : 4;
-}
+int elem_size(int type) { return (type == T_F16 || type == T_BF16 || type == T_I16) ? 2 : 4; }
 
 // 1 / (1 + exp(-x)) and x / (exp(-x) + 1): the usual spellings of sigmoid and SiLU
 using Sigmoid = OpList<LD(0), OP_NEG, OP_EXP, OP_ADD | I, OP_DIV | I>;
@@ -412,7 +409,7 @@ extern "C" int32_t asc_cuda_col_program(const int32_t* ops, const int32_t* args,
   if (ops == nullptr || args == nullptr || out == nullptr || (n_inputs > 0 && (inputs == nullptr || input_types == nullptr)))
     return ASC_ERR_INVALID_ARG;
   if (out_type < 0 || out_type >= T_COUNT || kind < 0 || kind > 3) return ASC_ERR_INVALID_ARG;
-  if (out_type == T_I32 || out_type == T_I16 || out_type == T_I8 || out_type == T_U8) return ASC_ERR_UNSUPPORTED;     // the combination runs on fp32 words
+  if (out_type == T_I32 || out_type == T_I16) return ASC_ERR_UNSUPPORTED;     // the combination runs on fp32 words
   if (rows >= (int64_t{1} << 32) || cols >= (int64_t{1} << 31) || rows * cols >= (int64_t{1} << 32)) return ASC_ERR_TOO_LARGE;
   EltProgram prog{};
   int max_depth = 0;

@@ -47,13 +47,7 @@ enum EltOp : int32_t {
   OP_IMM = 0x100,
 };
 
-// 8-bit integers are storage types: a load widens to a 32-bit word (sign- or zero-extended), a store keeps the
-// low byte; the program computes on them as int32.
-enum EltType : int32_t { T_F32 = 0, T_F16 = 1, T_BF16 = 2, T_I32 = 3, T_I16 = 4, T_I8 = 5, T_U8 = 6, T_COUNT = 7 };
-
-__device__ __forceinline__ float byte_to_word(uint32_t byte, int type) {
-  return __int_as_float(type == T_I8 ? static_cast<int>(static_cast<int8_t>(byte)) : static_cast<int>(byte));
-}
+enum EltType : int32_t { T_F32 = 0, T_F16 = 1, T_BF16 = 2, T_I32 = 3, T_I16 = 4, T_COUNT = 5 };
 
 __host__ __device__ constexpr bool is_row_op(int op) { return op >= OP_ROW_SUM && op <= OP_ROW_PROD; }
 constexpr int kMaxTmp = 4;   // temporary slots of a row program
@@ -112,10 +106,6 @@ __device__ __forceinline__ void load_quad(const void* p, int type, bool reused, 
     const int4 t = load_vec(reinterpret_cast<const int4*>(p) + (i >> 2), reused);
     v[0] = __int_as_float(t.x); v[1] = __int_as_float(t.y);
     v[2] = __int_as_float(t.z); v[3] = __int_as_float(t.w);
-  } else if (type == T_I8 || type == T_U8) {
-    const uint32_t t = load_vec(reinterpret_cast<const uint32_t*>(p) + (i >> 2), reused);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) v[k] = byte_to_word((t >> (8 * k)) & 0xffu, type);
   } else {
     const uint2 t = load_vec(reinterpret_cast<const uint2*>(p) + (i >> 2), reused);
     if (type == T_I16) {
@@ -141,11 +131,6 @@ __device__ __forceinline__ void store_quad(void* p, int type, int64_t i, const f
   } else if (type == T_I32) {
     __stcs(reinterpret_cast<int4*>(p) + (i >> 2),
            make_int4(__float_as_int(v[0]), __float_as_int(v[1]), __float_as_int(v[2]), __float_as_int(v[3])));
-  } else if (type == T_I8 || type == T_U8) {
-    uint32_t t = 0;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) t |= (static_cast<uint32_t>(__float_as_int(v[k])) & 0xffu) << (8 * k);
-    __stcs(reinterpret_cast<uint32_t*>(p) + (i >> 2), t);
   } else {
     uint2 t;
     if (type == T_I16) {
@@ -216,8 +201,6 @@ __device__ __forceinline__ void load_group(const EltProgram& prog, int input, in
       case T_BF16: v[0] = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]); break;
       case T_I32: v[0] = __int_as_float(reinterpret_cast<const int32_t*>(p)[i]); break;
       case T_I16: v[0] = __int_as_float(static_cast<int>(reinterpret_cast<const int16_t*>(p)[i])); break;
-      case T_I8:
-      case T_U8: v[0] = byte_to_word(reinterpret_cast<const uint8_t*>(p)[i], type); break;
       default: v[0] = reinterpret_cast<const float*>(p)[i]; break;
     }
   }
@@ -237,8 +220,6 @@ __device__ __forceinline__ void store_group(const EltProgram& prog, int64_t i, c
       case T_BF16: reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v[0]); break;
       case T_I32: reinterpret_cast<int32_t*>(p)[i] = __float_as_int(v[0]); break;
       case T_I16: reinterpret_cast<int16_t*>(p)[i] = static_cast<int16_t>(__float_as_int(v[0])); break;
-      case T_I8:
-      case T_U8: reinterpret_cast<uint8_t*>(p)[i] = static_cast<uint8_t>(__float_as_int(v[0])); break;
       default: reinterpret_cast<float*>(p)[i] = v[0]; break;
     }
   }
@@ -563,8 +544,6 @@ __device__ __forceinline__ float load_elem(const void* p, int type, int64_t i) {
     case T_BF16: return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
     case T_I32: return __int_as_float(reinterpret_cast<const int32_t*>(p)[i]);
     case T_I16: return __int_as_float(static_cast<int>(reinterpret_cast<const int16_t*>(p)[i]));
-    case T_I8:
-    case T_U8: return byte_to_word(reinterpret_cast<const uint8_t*>(p)[i], type);
     default: return reinterpret_cast<const float*>(p)[i];
   }
 }
@@ -574,8 +553,6 @@ __device__ __forceinline__ void store_elem(void* p, int type, int64_t i, float v
     case T_BF16: reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v); break;
     case T_I32: reinterpret_cast<int32_t*>(p)[i] = __float_as_int(v); break;
     case T_I16: reinterpret_cast<int16_t*>(p)[i] = static_cast<int16_t>(__float_as_int(v)); break;
-    case T_I8:
-    case T_U8: reinterpret_cast<uint8_t*>(p)[i] = static_cast<uint8_t>(__float_as_int(v)); break;
     default: reinterpret_cast<float*>(p)[i] = v; break;
   }
 }
@@ -588,8 +565,6 @@ __device__ __forceinline__ float row_combine(int op, float a, float b) {
 }
 
 __device__ __forceinline__ int16_t word_to_i16(float v) { return static_cast<int16_t>(__float_as_int(v)); }
-__device__ __forceinline__ int8_t word_to_i8(float v) { return static_cast<int8_t>(__float_as_int(v)); }
-__device__ __forceinline__ uint8_t word_to_u8(float v) { return static_cast<uint8_t>(__float_as_int(v)); }
 
 // Which column of the row lane e of this thread holds.  Rows of up to 512 columns: thread + e * 256.  Longer rows:
 // quads of consecutive columns, 4 * thread + (e / 4) * 1024 + e % 4, so that a thread's accesses are 128-bit (64-bit
@@ -613,10 +588,6 @@ template <>
 struct Quad<__nv_bfloat16> { using type = uint2; };
 template <>
 struct Quad<int16_t> { using type = uint2; };
-template <>
-struct Quad<int8_t> { using type = uint32_t; };
-template <>
-struct Quad<uint8_t> { using type = uint32_t; };
 
 // The lanes of one thread for one operand: columns row_col(e) of the row that starts at element `base`.  The element
 // type is resolved once per operand, and a row that fills every lane skips the bounds checks.
@@ -649,8 +620,6 @@ __device__ __forceinline__ void row_load(const void* p, int type, int64_t base, 
     case T_BF16: ASC_ROW_LOAD(__nv_bfloat16, __bfloat162float) break;
     case T_I32: ASC_ROW_LOAD(int32_t, __int_as_float) break;
     case T_I16: ASC_ROW_LOAD(int16_t, __int_as_float) break;
-    case T_I8: ASC_ROW_LOAD(int8_t, __int_as_float) break;
-    case T_U8: ASC_ROW_LOAD(uint8_t, __int_as_float) break;
     default: ASC_ROW_LOAD(float, ) break;
   }
 #undef ASC_ROW_LOAD
@@ -686,8 +655,6 @@ __device__ __forceinline__ void row_store(void* p, int type, int64_t base, uint3
     case T_BF16: ASC_ROW_STORE(__nv_bfloat16, __float2bfloat16_rn) break;
     case T_I32: ASC_ROW_STORE(int32_t, __float_as_int) break;
     case T_I16: ASC_ROW_STORE(int16_t, word_to_i16) break;
-    case T_I8: ASC_ROW_STORE(int8_t, word_to_i8) break;
-    case T_U8: ASC_ROW_STORE(uint8_t, word_to_u8) break;
     default: ASC_ROW_STORE(float, ) break;
   }
 #undef ASC_ROW_STORE

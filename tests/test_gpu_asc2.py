@@ -257,8 +257,11 @@ def test_quantise_and_dequantise_through_8_bit_tensors(n, tile):
     back = torch.full((n, ), 7.0)
     K.dequantise_int8[8](q, keep, back, 0.0625, n, tile)
     assert torch.equal(back, torch.where(keep != 0, q.float() * 0.0625, torch.zeros(n)))
-    # a loaded 8-bit tile stored as it is stays a copy; arithmetic on 8-bit tiles is refused
-    assert K.quantise_int8.last_plan.pattern == "elementwise:program"
+    # a kernel that writes part of an 8-bit tensor leaves the other bytes as they were
+    part = torch.full((n, ), 5, dtype=torch.int8)
+    K.quantise_int8[8](x, part, 16.0, n - 1000, tile)
+    assert torch.equal(part[:n - 1000], want_q[:n - 1000]) and bool((part[n - 1000:] == 5).all())
+    # arithmetic on 8-bit tiles is refused
 
     @asc2.jit
     def add_bytes(a_ptr: asc.GlobalAddress, o_ptr: asc.GlobalAddress):

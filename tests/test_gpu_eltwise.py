@@ -91,8 +91,7 @@ def call(lib, ops, args, inputs, out, out_type, n, expect=0):
     ops_a = (ctypes.c_int32 * len(ops))(*ops)
     args_a = (ctypes.c_int32 * len(ops))(*args)
     ins = (ctypes.c_void_p * max(1, len(inputs)))(*[t.data_ptr() for t in inputs])
-    code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2, torch.int32: 3, torch.int16: 4, torch.int8: 5,
-            torch.uint8: 6}
+    code = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2, torch.int32: 3, torch.int16: 4}
     types = (ctypes.c_int32 * max(1, len(inputs)))(*[code[t.dtype] for t in inputs])
     rc = lib.asc_cuda_eltwise_program(ops_a, args_a, len(ops), ins, types, len(inputs),
                                       ctypes.c_void_p(out.data_ptr()), out_type, n, None)
@@ -151,32 +150,27 @@ def test_program_integer_ops_wrap_like_torch(lib):
     assert torch.equal(out16.cpu(), a * 7)
 
 
-@pytest.mark.parametrize("n, offset", [(4099, 0), (4096, 3), ((1 << 20) + 8, 0), (7, 1)])
-def test_program_8_bit_storage_types(lib, n, offset):
-    """int8 / uint8 are storage types: the load widens to an int32 word (sign / zero extension), the store keeps
-    the low byte.  Aligned and misaligned ranges (4 bytes make a quad), against the CPU evaluator bit for bit."""
-    gen = torch.Generator().manual_seed(n)
-    s8 = torch.randint(-128, 128, (n + offset, ), generator=gen).to(torch.int8)
-    u8 = torch.randint(0, 256, (n + offset, ), generator=gen).to(torch.uint8)
-    x = torch.randn(n + offset, generator=gen)
-    sd, ud, xd = s8.cuda(), u8.cuda(), x.cuda()
-    # (s8 * 3 - u8) as int32 and as its low byte, signed and unsigned
-    ops, args = [0, 1, 37, 0, 36], [0, 3, 0, 1, 0]
-    for out_dtype, out_type in ((torch.int32, 3), (torch.int8, 5), (torch.uint8, 6), (torch.int16, 4)):
-        out = torch.zeros(n + offset + 1, dtype=out_dtype, device="cuda")
-        call(lib, ops, args, [sd[offset:], ud[offset:]], out[offset:], out_type, n)
-        want = E.run_program(ops, args, [s8[offset:], u8[offset:]], out_type)
-        got = out.cpu()
-        assert torch.equal(got[offset:offset + n], want), out_dtype
-        assert got[offset + n] == 0 and bool((got[:offset] == 0).all())
-    assert torch.equal(want.to(torch.int32), ((s8[offset:].int() * 3 - u8[offset:].int()) << 16 >> 16))   # the evaluator itself
-    # where(u8 != 0 and s8 < 0, float(s8) * x, x): 8-bit masks beside fp32 data
-    ops = [0, 43 | IMM, 0, 44 | IMM, 4, 0, 51, 0, 4, 0, 32]
-    args = [1, 0, 0, 0, 0, 0, 0, 2, 0, 2, 0]
-    out = torch.zeros(n + offset, device="cuda")
-    call(lib, ops, args, [sd[offset:], ud[offset:], xd[offset:]], out[offset:], 0, n)
-    want = torch.where((u8[offset:] != 0) & (s8[offset:] < 0), s8[offset:].float() * x[offset:], x[offset:])
-    assert torch.equal(out.cpu()[offset:], want)
+@pytest.mark.parametrize("n, offset", [(4099, 0), (4096, 3), ((1 << 20) + 8, 0), (7, 1), (0, 0)])
+def test_bytes_widened_to_words_and_back(lib, n, offset):
+    """asc_cuda_convert_bytes: int8 / uint8 -> int32 (sign / zero extension) and int32 -> its low byte, at aligned
+    and misaligned byte addresses, writing nothing outside the range."""
+    gen = torch.Generator().manual_seed(n + 1)
+    s8 = torch.randint(-128, 128, (n + offset, ), generator=gen).to(torch.int8).cuda()
+    u8 = torch.randint(0, 256, (n + offset, ), generator=gen).to(torch.uint8).cuda()
+    words = torch.randint(-2**31, 2**31 - 1, (n, ), dtype=torch.int64, generator=gen).to(torch.int32).cuda()
+    P = lambda t: ctypes.c_void_p(t.data_ptr())
+    for src, mode in ((s8, 0), (u8, 1)):
+        out = torch.full((n + 1, ), 77, dtype=torch.int32, device="cuda")
+        assert lib.asc_cuda_convert_bytes(P(out), P(src[offset:]), n, mode, None) == 0
+        assert torch.equal(out[:n], src[offset:].to(torch.int32)) and int(out[n]) == 77
+    for dtype in (torch.int8, torch.uint8):
+        out = torch.full((n + offset + 1, ), 77, dtype=dtype, device="cuda")
+        assert lib.asc_cuda_convert_bytes(P(out[offset:]), P(words), n, 2, None) == 0
+        assert torch.equal(out[offset:offset + n], words.to(dtype)) and int(out[offset + n]) == 77 and bool((out[:offset] == 77).all())
+    capi.check_device_status(None)
+    if n:
+        assert lib.asc_cuda_convert_bytes(P(words), P(s8), n, 3, None) == 1                 # no such mode
+        assert lib.asc_cuda_convert_bytes(ctypes.c_void_p(words.data_ptr() + 2), P(s8), 1, 0, None) == 2     # misaligned words
 
 
 def test_program_max_min_relu_propagate_nan(lib):

@@ -546,12 +546,20 @@ def test_per_row_results_of_one_row_tiles_arrive_as_scalar_stores():
 
 def test_8_bit_tensors_are_loaded_compared_and_stored_not_computed_on():
     n = 5000
+    # the kernels compute on 32- and 16-bit types: 8-bit tensors are widened into (narrowed out of) int32 temporaries
     K.quantise_int8[4](torch.zeros(n), torch.zeros(n, dtype=torch.int8), 8.0, n, 512)
-    plan, step = only_step(K.quantise_int8)
-    assert plan.pattern == "elementwise:program" and step.note.endswith("over [0, 5000)")
+    plan = K.quantise_int8.last_plan
+    assert plan.pattern == "elementwise:program" and plan.temps == {"wide1": 4 * n} and not plan.partial_writes
+    assert [s.fn_name for s in plan.steps] == ["asc_cuda_eltwise_program", "asc_cuda_convert_bytes"]
+    assert plan.steps[0].note.endswith("over [0, 5000)") and plan.reads == {0} and plan.writes == {1}
+    K.quantise_int8[4](torch.zeros(n), torch.zeros(n, dtype=torch.int8), 8.0, n - 1000, 512)       # part of the output only
+    plan = K.quantise_int8.last_plan
+    assert [s.fn_name for s in plan.steps] == ["asc_cuda_convert_bytes", "asc_cuda_eltwise_program", "asc_cuda_convert_bytes"]
+    assert plan.partial_writes == {1}
     K.dequantise_int8[4](torch.zeros(n, dtype=torch.int8), torch.zeros(n, dtype=torch.uint8), torch.zeros(n), 0.125, n, 512)
-    plan, step = only_step(K.dequantise_int8)
-    assert plan.pattern == "elementwise:program" and plan.reads == {0, 1} and plan.writes == {2}
+    plan = K.dequantise_int8.last_plan
+    assert [s.fn_name for s in plan.steps] == ["asc_cuda_convert_bytes"] * 2 + ["asc_cuda_eltwise_program"]
+    assert plan.pattern == "elementwise:program" and plan.reads == {0, 1} and plan.writes == {2} and plan.pipeline is None
 
     @asc2.jit
     def add_bytes(a_ptr: asc.GlobalAddress, o_ptr: asc.GlobalAddress, form: asc.ConstExpr[int]):
