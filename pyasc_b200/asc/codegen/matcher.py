@@ -1062,7 +1062,7 @@ def _plan_general_program(trace: KernelTrace, eff: Effect, prog: "_EltProgram", 
     if dedupe and len(calls) == 1 and lds[-1] == out_cols and calls[0][0][-1] == 0 and covered == out_t.base.numel:
         plan.partial_writes.discard(out_idx)
     if not plan.steps:
-        raise _unsupported("elementwise kernel without any tile")
+        return plan          # no block has a tile inside the tensors (an empty tensor): nothing to launch
     if row_shape is not None and not plan.partial_writes and len(calls) == 1:
         # whole rows of whole tensors: chunks of rows can be uploaded, computed and downloaded independently;
         # a broadcast row is needed by every chunk
@@ -1252,7 +1252,7 @@ def _plan_eltwise_program_with(trace: KernelTrace, eff: Effect, made: List[Any])
     for w in windows:
         plan.steps.append(make_2d(*w))
     if not plan.steps:
-        raise _unsupported("elementwise kernel whose tiles all lie outside the tensor")
+        return plan          # no block has a tile inside the tensor (an empty tensor): nothing to launch
     if not plan.partial_writes and len(intervals) == 1:
         streamed = {i: sz for i, sz in zip(in_idx, in_size)}
         streamed[out_idx] = out_size
@@ -2291,8 +2291,6 @@ def _match_copy(trace: KernelTrace, eff: Effect) -> Optional[Plan]:
                 calls[-1] = (ps, pd, prow + rows)      # the next rows of the same two matrices
                 continue
         calls.append((s0, d0, rows))
-    if not calls:
-        raise _unsupported("copy kernel without any tile")
     plan = Plan("copy")
     plan.reads.add(src_idx)
     plan.writes.add(dst_idx)

@@ -105,6 +105,8 @@ class Launcher:
                 handles[index] = resolve_memory_handle(arg)
             except RuntimeError as e:
                 raise TypeError(f"Unsupported kernel argument of type {type(arg)}") from e
+        if not plan.steps:
+            return                  # no block has a tile inside its tensors (empty tensors): nothing is written
         all_on_device = all(isinstance(h, TorchCudaTensorArgument) for h in handles.values())
         self._check_device_aliasing(plan, handles)
         user_stream = self.options.stream

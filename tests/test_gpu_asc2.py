@@ -272,6 +272,17 @@ def test_quantise_and_dequantise_through_8_bit_tensors(n, tile):
         add_bytes[1](q[:1024].clone(), torch.zeros(1024, dtype=torch.int8))
 
 
+def test_launches_over_empty_tensors_do_nothing():
+    for dev in ("cpu", "cuda"):
+        x = torch.zeros(0, device=dev)
+        K.vadd[16](x, x.clone(), x.clone(), 0, 128, 4)
+        K.add_vector_bias[4](torch.zeros(0, 64, device=dev), torch.ones(64, device=dev), torch.zeros(0, 64, device=dev), 0, 64, 32)
+    # tensors with elements, a length argument of 0: the output keeps its contents
+    out = torch.full((256, ), 3.0)
+    K.vadd[16](torch.ones(256), torch.ones(256), out, 0, 128, 4)
+    assert bool((out == 3.0).all())
+
+
 def test_device_tensors_that_share_a_buffer():
     """x += y through two arguments that are one device buffer works (every element is read before it is written);
     a GEMM whose output argument is also an operand argument is refused before anything is launched."""

@@ -622,3 +622,17 @@ def _short_operand():
         for i in range(asc2.block_idx() * tile, n, asc2.block_num() * tile):
             asc2.store(asc2.load(x_gm, [tile], offsets=[i]) + asc2.load(y_gm, [tile], offsets=[i]), o_gm, offsets=[i])
     short[2](torch.zeros(992), torch.zeros(1000), torch.zeros(1000), 1000, 256)
+
+
+def test_empty_tensors_plan_no_calls():
+    """A launch over tensors without elements (or whose every tile lies outside): nothing to do, as on the reference,
+    where the blocks' loops simply do not run."""
+    x = np.zeros(0, np.float32)
+    K.vadd[16](x, x, x.copy(), 0, 128, 4)
+    assert K.vadd.last_plan.steps == []
+    K.add_vector_bias[4](torch.zeros(0, 64), torch.zeros(64), torch.zeros(0, 64), 0, 64, 32)
+    assert K.add_vector_bias.last_plan.steps == [] and K.add_vector_bias.last_plan.writes == {2}
+    K.row_losses[8](torch.zeros(0, 512), torch.zeros(0, 512), torch.zeros(0), torch.zeros(0), 0, 512)
+    assert K.row_losses.last_plan.steps == []
+    K.copy_window[4](torch.zeros(0, 64, dtype=torch.int8), torch.zeros(0, 64, dtype=torch.int8), 0, 64, 64, 64, 0, 0, 8)
+    assert K.copy_window.last_plan.steps == []
