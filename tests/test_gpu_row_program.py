@@ -75,11 +75,13 @@ def test_softmax_of_a_computed_tile(rows, cols, rpt):
     torch.testing.assert_close(out, torch.softmax(x * 0.7 + bias, dim=1), rtol=1e-5, atol=1e-8)
 
 
-def test_loaded_columns_repeat_along_the_row():
+@pytest.mark.parametrize("rows", [96, 100, 5])
+def test_loaded_columns_repeat_along_the_row(rows):
+    """Also with a row count that is no multiple of the 8-row tile: the last tile's rows past the end are left out."""
     gen = torch.Generator().manual_seed(13)
-    x, scale, bias = torch.randn(96, 640, generator=gen), torch.randn(96, generator=gen), torch.randn(96, generator=gen)
+    x, scale, bias = torch.randn(rows, 640, generator=gen), torch.randn(rows, generator=gen), torch.randn(rows, generator=gen)
     out = torch.zeros_like(x)
-    K.scale_rows[4](x, scale, bias, out, 96, 640, 8)
+    K.scale_rows[4](x, scale, bias, out, rows, 640, 8)
     assert torch.equal(out, x * scale[:, None] + bias[:, None])
 
 
