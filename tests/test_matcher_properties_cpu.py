@@ -95,3 +95,68 @@ def test_matmul_blocked_plan_is_one_gemm(m_tiles, n_tiles, k, cores):
     K.matmul_mn_blocked[cores](a, b, torch.zeros(m, n), a.shape, b.shape, (m, n), m_tile, mtpb, n_tile, ntpb)
     plan = K.matmul_mn_blocked.last_plan
     assert len(plan.steps) == 1 and plan.steps[0].fn_name == "asc_cuda_gemm_f16" and not plan.partial_writes
+
+
+def covered_windows(plan, rows, cols, pitches_of):
+    """Rows x cols windows of the general program calls: which output elements they write, and that every operand
+    window stays inside its tensor."""
+    mask = np.zeros(rows * cols, dtype=bool)
+    for step in plan.steps:
+        m = re.search(r"over \[(\d+), (\d+)\] pitches \[([\d, ]+)\] from \[([\d, ]*)\] to (\d+)$", step.note)
+        assert m, step.note
+        r, c = int(m.group(1)), int(m.group(2))
+        lds = [int(v) for v in m.group(3).split(",")]
+        starts = [int(v) for v in m.group(4).split(",")] + [int(m.group(5))]
+        for k, (ld, st0, limit) in enumerate(zip(lds, starts, pitches_of)):
+            last = st0 + (r - 1) * ld + c
+            assert 0 <= st0 and last <= limit, (step.note, k)        # no operand reads or writes past its tensor
+        out_ld, out0 = lds[-1], starts[-1]
+        for i in range(r):
+            seg = mask[out0 + i * out_ld: out0 + i * out_ld + c]
+            assert not seg.any(), step.note                          # no element planned twice
+            seg[:] = True
+    return mask
+
+
+@settings(max_examples=60, deadline=None)
+@given(rows=st.integers(1, 200), cols=st.sampled_from([8, 64, 136]), rpt=st.sampled_from([1, 3, 8, 32]),
+       cores=st.integers(1, 6))
+def test_bias_row_plan_with_ragged_tiles_covers_exactly_the_matrix(rows, cols, rpt, cores):
+    """x + bias row, rpt rows per tile, blocks striding over the tiles: the last tile usually reaches past the
+    matrix; the calls must cover every element once and stay inside x, the bias vector and the result."""
+    x = torch.zeros(rows, cols)
+    K.add_vector_bias[cores](x, torch.zeros(cols), torch.zeros_like(x), rows, cols, rpt)
+    plan = K.add_vector_bias.last_plan
+    mask = covered_windows(plan, rows, cols, [rows * cols, cols, rows * cols])
+    assert mask.all() and plan.reads == {0, 1} and plan.writes == {2}
+
+
+@settings(max_examples=40, deadline=None)
+@given(n=st.integers(1, 3000), tile=st.sampled_from([8, 64, 256]), shift=st.integers(0, 40), cores=st.integers(1, 5))
+def test_shifted_operand_plan_with_a_ragged_tail(n, tile, shift, cores):
+    import asc2
+
+    @asc2.jit
+    def shifted(x_ptr: asc.GlobalAddress, y_ptr: asc.GlobalAddress, o_ptr: asc.GlobalAddress, n: int, shift: asc.ConstExpr[int],
+                tile: asc.ConstExpr[int]):
+        x_gm, y_gm, o_gm = asc2.tensor(x_ptr, [n + shift]), asc2.tensor(y_ptr, [n]), asc2.tensor(o_ptr, [n])
+        for i in range(asc2.block_idx() * tile, n, asc2.block_num() * tile):
+            asc2.store(asc2.load(x_gm, [tile], offsets=[i + shift]) * asc2.load(y_gm, [tile], offsets=[i]), o_gm, offsets=[i])
+    shifted[cores](torch.zeros(n + shift), torch.zeros(n), torch.zeros(n), n, shift, tile)
+    plan = shifted.last_plan
+    mask = np.zeros(n, dtype=bool)
+    for step in plan.steps:
+        flat = re.search(r"over \[(\d+), (\d+)\)$", step.note)       # operands addressed like the result (shift 0)
+        if flat:
+            lo, hi = int(flat.group(1)), int(flat.group(2))
+            assert shift == 0 and 0 <= lo < hi <= n and not mask[lo:hi].any()
+            mask[lo:hi] = True
+            continue
+        m = re.search(r"over \[(\d+), (\d+)\] pitches \[(\d+), (\d+), (\d+)\] from \[(\d+), (\d+)\] to (\d+)$", step.note)
+        assert m, step.note
+        r, c, ldx, ldy, ldo, x0, y0, o0 = (int(v) for v in m.groups())
+        assert x0 == o0 + shift and y0 == o0 and (r == 1 or ldx == ldy == ldo == c)
+        assert x0 + (r - 1) * ldx + c <= n + shift and o0 + (r - 1) * ldo + c <= n
+        assert not mask[o0:o0 + r * c].any()
+        mask[o0:o0 + r * c] = True
+    assert mask.all()
