@@ -363,7 +363,7 @@ _ELT_TYPE = {"float32": 0, "float16": 1, "bfloat16": 2, "int32": 3, "int16": 4}
 # The kernels never see them: an int8 / uint8 tensor a program loads is first widened, whole, into an int32
 # temporary (its "twin"), and an 8-bit result is narrowed out of one (asc_cuda_convert_bytes).
 _BYTE_TYPES = ("int8", "uint8")
-_STORAGE_TYPE = {**_ELT_TYPE, "int8": 3, "uint8": 3}
+_STORAGE_TYPE = frozenset(_ELT_TYPE) | frozenset(_BYTE_TYPES)      # element types a program may load or compare
 _ROUND_CODE = {"float16": _OP_ROUND_F16, "bfloat16": _OP_ROUND_BF16, "int16": _OP_WRAP_I16}
 ELT_MAX_OPS, ELT_MAX_INPUTS, ELT_MAX_STACK = 48, 6, 8
 _ROW_CODE = {"sum": 59, "max": 60, "min": 61, "prod": 62}     # row programs: reduce the top of the stack over the row
