@@ -47,7 +47,10 @@ constexpr uint32_t kSmemB = kBlockN * kKBytes;                // 32 KiB per stag
 constexpr uint32_t kStageBytes = kSmemA + kSmemB;             // 48 KiB
 constexpr uint32_t kGemmSmem = kStages * kStageBytes + 1024;  // + slack for 1024-byte alignment
 
-enum EpiMode : int { EPI_F16 = 0, EPI_BF16 = 1, EPI_F32 = 2, EPI_I8 = 3 };
+// kMode of the kernels: the output form, | EPI_BIAS for the variants that add a bias row in the epilogue (their own
+// instantiations: with the bias as a run-time case the plain fp16 GEMM needed 138 registers instead of 98 and ran
+// 1.5-3 % slower at 8192^3)
+enum EpiMode : int { EPI_F16 = 0, EPI_BF16 = 1, EPI_F32 = 2, EPI_I8 = 3, EPI_BIAS = 8 };
 
 struct GemmParams {
   void* c;              // fp16 / bf16 / fp32 output, or int32 accumulator output for EPI_I8 (nullable there)
@@ -97,8 +100,11 @@ __device__ __forceinline__ float bias_at(const void* bias, int32_t bias_type, in
 
 // The floating-point epilogue of one element of output column `col`: the bias row, then the ReLU (a NaN stays a
 // NaN, as in torch.relu).
+template <int kMode>
 __device__ __forceinline__ float epi_finish(const GemmParams& p, float v, int64_t col) {
-  if (p.bias_type != 0 && col < p.N) v = __fadd_rn(v, bias_at(p.bias, p.bias_type, col));
+  if constexpr ((kMode & EPI_BIAS) != 0) {
+    if (col < p.N) v = __fadd_rn(v, bias_at(p.bias, p.bias_type, col));
+  }
   if (p.relu) v = v < 0.f ? 0.f : v;
   return v;
 }
@@ -109,13 +115,13 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const 
   // this thread owns 32 consecutive columns [col0, col0+32) of output row `row`
   if (row >= p.M || col0 >= p.N) return;
   const bool full = (col0 + 32 <= p.N) && p.vec_ok;
-  if (kMode == EPI_F16 || kMode == EPI_BF16) {
+  if ((kMode & 7) == EPI_F16 || (kMode & 7) == EPI_BF16) {
     uint32_t packed[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      const float a = epi_finish(p, __uint_as_float(r[2 * i]), col0 + 2 * i);
-      const float b = epi_finish(p, __uint_as_float(r[2 * i + 1]), col0 + 2 * i + 1);
-      if (kMode == EPI_F16) {
+      const float a = epi_finish<kMode>(p, __uint_as_float(r[2 * i]), col0 + 2 * i);
+      const float b = epi_finish<kMode>(p, __uint_as_float(r[2 * i + 1]), col0 + 2 * i + 1);
+      if ((kMode & 7) == EPI_F16) {
         __half2 h = __floats2half2_rn(a, b);
         packed[i] = *reinterpret_cast<uint32_t*>(&h);
       } else {
@@ -134,7 +140,7 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const 
       for (int i = 0; i < 32; ++i)
         if (col0 + i < p.N) dst[i] = static_cast<uint16_t>((packed[i >> 1] >> ((i & 1) * 16)) & 0xffffu);
     }
-  } else if (kMode == EPI_F32) {
+  } else if ((kMode & 7) == EPI_F32) {
     float* dst = reinterpret_cast<float*>(p.c) + row * p.ldc + col0;
     float v[32];
 #pragma unroll
@@ -144,9 +150,9 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmParams& p, const 
       for (int i = 0; i < 32; ++i)
         if (col0 + i < p.N) v[i] += dst[i];
     }
-    if (p.relu || p.bias_type != 0) {
+    if (p.relu || (kMode & EPI_BIAS) != 0) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = epi_finish(p, v[i], col0 + i);
+      for (int i = 0; i < 32; ++i) v[i] = epi_finish<kMode>(p, v[i], col0 + i);
     }
     if (full) {
 #pragma unroll
@@ -394,9 +400,9 @@ template <int kMode>
 __device__ __forceinline__ void pack16(const GemmParams& p, const uint32_t (&r)[32], uint32_t* packed, int64_t col0) {
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
-    const float a = epi_finish(p, __uint_as_float(r[2 * i]), col0 + 2 * i);
-    const float b = epi_finish(p, __uint_as_float(r[2 * i + 1]), col0 + 2 * i + 1);
-    if (kMode == EPI_F16) {
+    const float a = epi_finish<kMode>(p, __uint_as_float(r[2 * i]), col0 + 2 * i);
+    const float b = epi_finish<kMode>(p, __uint_as_float(r[2 * i + 1]), col0 + 2 * i + 1);
+    if ((kMode & 7) == EPI_F16) {
       __half2 h = __floats2half2_rn(a, b);
       packed[i] = *reinterpret_cast<uint32_t*>(&h);
     } else {
@@ -573,7 +579,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
       const int64_t row0 = m_blk * kPairM + rank * kBlockM + quarter * 32;
       const int64_t row = row0 + lane;
       const uint32_t taddr = tmem_base + ((quarter * 32u) << 16) + acc * kBlockN;
-      if ((kMode == EPI_F16 || kMode == EPI_BF16) && p.vec_ok && row0 + 32 <= p.M &&
+      if (((kMode & 7) == EPI_F16 || (kMode & 7) == EPI_BF16) && p.vec_ok && row0 + 32 <= p.M &&
           (n_blk + 1) * kBlockN <= p.N) {
         const uint32_t stage_smem = smem_base + kPairStageRing + quarter * kEpiStageBytes;
 #pragma unroll 1
@@ -631,7 +637,7 @@ __device__ __forceinline__ void splitk_store_pair(const GemmParams& p, int64_t r
   // two neighbouring columns of one output row; w0 / w1 are fp32 (or, for int8, int32) sums over all slices
   if (row >= p.M || col >= p.N) return;
   const bool two = col + 1 < p.N;
-  if (kMode == EPI_I8) {
+  if ((kMode & 7) == EPI_I8) {
     if (p.c != nullptr) {
       int32_t* dst = reinterpret_cast<int32_t*>(p.c) + row * p.ldc + col;
       dst[0] = static_cast<int32_t>(w0);
@@ -647,21 +653,21 @@ __device__ __forceinline__ void splitk_store_pair(const GemmParams& p, int64_t r
     return;
   }
   float a = __uint_as_float(w0), b = __uint_as_float(w1);
-  if (kMode == EPI_F32) {
+  if ((kMode & 7) == EPI_F32) {
     float* dst = reinterpret_cast<float*>(p.c) + row * p.ldc + col;
     if (p.accumulate) {
       a += dst[0];
       if (two) b += dst[1];
     }
-    a = epi_finish(p, a, col);
-    b = epi_finish(p, b, col + 1);
+    a = epi_finish<kMode>(p, a, col);
+    b = epi_finish<kMode>(p, b, col + 1);
     dst[0] = a;
     if (two) dst[1] = b;
     return;
   }
-  a = epi_finish(p, a, col);
-  b = epi_finish(p, b, col + 1);
-  if (kMode == EPI_F16) {
+  a = epi_finish<kMode>(p, a, col);
+  b = epi_finish<kMode>(p, b, col + 1);
+  if ((kMode & 7) == EPI_F16) {
     __half* dst = reinterpret_cast<__half*>(p.c) + row * p.ldc + col;
     dst[0] = __float2half_rn(a);
     if (two) dst[1] = __float2half_rn(b);
@@ -677,12 +683,12 @@ template <int kMode>
 __device__ __forceinline__ void splitk_store_quad(const GemmParams& p, int64_t row, int64_t col, const uint4& v) {
   if (row >= p.M || col >= p.N) return;
   if (p.vec_ok && col + 4 <= p.N) {
-    if (kMode == EPI_F16 || kMode == EPI_BF16) {
+    if ((kMode & 7) == EPI_F16 || (kMode & 7) == EPI_BF16) {
       float f[4] = {__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w)};
 #pragma unroll
-      for (int i = 0; i < 4; ++i) f[i] = epi_finish(p, f[i], col + i);
+      for (int i = 0; i < 4; ++i) f[i] = epi_finish<kMode>(p, f[i], col + i);
       uint2 w;
-      if (kMode == EPI_F16) {
+      if ((kMode & 7) == EPI_F16) {
         const __half2 a = __floats2half2_rn(f[0], f[1]), b = __floats2half2_rn(f[2], f[3]);
         w = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
       } else {
@@ -692,14 +698,14 @@ __device__ __forceinline__ void splitk_store_quad(const GemmParams& p, int64_t r
       *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.c) + row * p.ldc + col) = w;
       return;
     }
-    if (kMode == EPI_F32 && !p.accumulate) {
+    if ((kMode & 7) == EPI_F32 && !p.accumulate) {
       float4 f = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
-      f = make_float4(epi_finish(p, f.x, col), epi_finish(p, f.y, col + 1), epi_finish(p, f.z, col + 2),
-                      epi_finish(p, f.w, col + 3));
+      f = make_float4(epi_finish<kMode>(p, f.x, col), epi_finish<kMode>(p, f.y, col + 1), epi_finish<kMode>(p, f.z, col + 2),
+                      epi_finish<kMode>(p, f.w, col + 3));
       *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.c) + row * p.ldc + col) = f;
       return;
     }
-    if (kMode == EPI_I8 && p.deq == nullptr) {
+    if ((kMode & 7) == EPI_I8 && p.deq == nullptr) {
       *reinterpret_cast<uint4*>(reinterpret_cast<int32_t*>(p.c) + row * p.ldc + col) = v;
       return;
     }
@@ -736,7 +742,7 @@ __device__ __forceinline__ void splitk_reduce_band(const GemmParams& p, const ui
         if (s0 + i < p.split_k) {
 #pragma unroll
           for (int j = 0; j < kItems; ++j) {
-            if (kMode == EPI_I8) {
+            if ((kMode & 7) == EPI_I8) {
               v[j].x += w[j][i].x;
               v[j].y += w[j][i].y;
               v[j].z += w[j][i].z;
@@ -1306,6 +1312,13 @@ int32_t gemm_f16_entry(const void* A, const void* B, void* C, const void* bias, 
                                       ldc, out_dtype, flags, s, bias, bias_type);
     return launch_gemm_simt<__nv_bfloat16>(static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(B), C, M,
                                            N, K, lda, ldb, ldc, out_dtype, flags, s, bias, bias_type);
+  }
+  if (bias_type != 0) {
+    switch (out_dtype) {
+      case 0: return dispatch_gemm<2, EPI_F16 | EPI_BIAS>(A, B, lda, ldb, dt, 1, in_dtype, p, 0, s);
+      case 1: return dispatch_gemm<2, EPI_BF16 | EPI_BIAS>(A, B, lda, ldb, dt, 1, in_dtype, p, 0, s);
+      default: return dispatch_gemm<2, EPI_F32 | EPI_BIAS>(A, B, lda, ldb, dt, 1, in_dtype, p, 0, s);
+    }
   }
   switch (out_dtype) {
     case 0: return dispatch_gemm<2, EPI_F16>(A, B, lda, ldb, dt, 1, in_dtype, p, 0, s);
