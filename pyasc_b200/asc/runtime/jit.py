@@ -13,11 +13,12 @@ import inspect
 import os
 import sys
 from dataclasses import fields
-from typing import Any, Callable, Dict, List, Optional, Tuple, Type, Union
+from typing import Any, Callable, Dict, List, Optional, Tuple, Type, Union, get_args, get_origin
 
 import numpy as np
 
 from ..codegen.function import Function, P, T, get_annotations
+from ..language.core.constexpr import ConstExpr, require_constexpr
 from ..codegen.matcher import Plan, build_plan
 from ..codegen.tracer import trace_kernel
 from ..language.core.dtype import DataType, KnownTypes as KT
@@ -57,6 +58,14 @@ class JITFunction(Function[P, T]):
         self.launch_options = LaunchOptions()
         self.kernel_cache: Dict[Any, Plan] = {}
         self.last_plan: Optional[Plan] = None
+        # the function's signature and annotations do not change between launches: looked up once
+        self._signature = inspect.signature(fn)
+        self._annotations = get_annotations(fn)
+        self._constexpr_args: Dict[str, tuple] = {}      # ConstExpr-annotated parameter -> the types it accepts
+        for name, ann in self._annotations.items():
+            origin = get_origin(ann) or ann
+            if isinstance(origin, type) and issubclass(origin, ConstExpr):
+                self._constexpr_args[name] = get_args(ann)
 
     def __getitem__(self, user_launch_options: Union[int, tuple]) -> Callable:
         try:
@@ -97,12 +106,17 @@ class JITFunction(Function[P, T]):
             pass
         raise TypeError(f"Argument type in JIT function is not supported: {value.__class__.__name__}")
 
+    _field_names: Dict[Type, Tuple[str, ...]] = {}
+
     @staticmethod
     def extract_kwargs(dataclass: Type, base_kwargs: Dict[str, Any]) -> Any:
+        names = JITFunction._field_names.get(dataclass)
+        if names is None:
+            names = JITFunction._field_names[dataclass] = tuple(f.name for f in fields(dataclass))
         kwargs = {}
-        for f in fields(dataclass):
-            if f.name in base_kwargs:
-                kwargs[f.name] = base_kwargs.pop(f.name)
+        for name in names:
+            if name in base_kwargs:
+                kwargs[name] = base_kwargs.pop(name)
         return dataclass(**kwargs)
 
     @classmethod
@@ -190,8 +204,18 @@ class JITFunction(Function[P, T]):
         compile_options = self.extract_kwargs(CompileOptions, merged)
         if self.launch_options.core_num <= 0:
             raise ValueError("Core number should be large than 0")
-        call_args = inspect.signature(self.fn).bind(*args, **merged).arguments
-        runtime_args, constexprs = self.split_args(call_args, get_annotations(self.fn))
+        call_args = self._signature.bind(*args, **merged).arguments
+        # (split_args with the annotation look-ups done once, in __init__)
+        runtime_args: Dict[str, Any] = {}
+        constexprs: Dict[str, ConstExpr] = {}
+        for name, value in call_args.items():
+            accepted = self._constexpr_args.get(name)
+            if accepted is None:
+                runtime_args[name] = value
+            else:
+                if accepted:
+                    require_constexpr(value, *accepted, arg_name=name)
+                constexprs[name] = ConstExpr(value)
         plan = self._cache_kernel(runtime_args, constexprs, codegen_options, compile_options)
         self.last_plan = plan
         if compile_options.print_ir_before_all or os.environ.get("ASC_CUDA_EXPLAIN"):

@@ -65,6 +65,9 @@ def _new_event() -> ctypes.c_void_p:
 def _torch_current_stream() -> Optional[ctypes.c_void_p]:
     try:
         import torch
+        raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)      # the handle without a Stream object around it
+        if raw is not None:
+            return ctypes.c_void_p(raw(torch.cuda.current_device()))
         return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     except Exception:
         return None
