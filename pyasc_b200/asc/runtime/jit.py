@@ -58,14 +58,19 @@ class JITFunction(Function[P, T]):
         self.launch_options = LaunchOptions()
         self.kernel_cache: Dict[Any, Plan] = {}
         self.last_plan: Optional[Plan] = None
-        # the function's signature and annotations do not change between launches: looked up once
-        self._signature = inspect.signature(fn)
-        self._annotations = get_annotations(fn)
+        # the function's signature and annotations do not change between launches: looked up at the first one (string
+        # annotations may name things that are defined after the decorator has run)
+        self._signature: Optional[inspect.Signature] = None
         self._constexpr_args: Dict[str, tuple] = {}      # ConstExpr-annotated parameter -> the types it accepts
-        for name, ann in self._annotations.items():
-            origin = get_origin(ann) or ann
-            if isinstance(origin, type) and issubclass(origin, ConstExpr):
-                self._constexpr_args[name] = get_args(ann)
+
+    def _bind(self, args: tuple, kwargs: Dict[str, Any]) -> Dict[str, Any]:
+        if self._signature is None:
+            for name, ann in get_annotations(self.fn).items():
+                origin = get_origin(ann) or ann
+                if isinstance(origin, type) and issubclass(origin, ConstExpr):
+                    self._constexpr_args[name] = get_args(ann)
+            self._signature = inspect.signature(self.fn)
+        return self._signature.bind(*args, **kwargs).arguments
 
     def __getitem__(self, user_launch_options: Union[int, tuple]) -> Callable:
         try:
@@ -204,7 +209,7 @@ class JITFunction(Function[P, T]):
         compile_options = self.extract_kwargs(CompileOptions, merged)
         if self.launch_options.core_num <= 0:
             raise ValueError("Core number should be large than 0")
-        call_args = self._signature.bind(*args, **merged).arguments
+        call_args = self._bind(args, merged)
         # (split_args with the annotation look-ups done once, in __init__)
         runtime_args: Dict[str, Any] = {}
         constexprs: Dict[str, ConstExpr] = {}
